@@ -1,0 +1,425 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory (128B swizzle) ->
+// tcgen05.mma with fp32 accumulators in tensor memory -> epilogue warps (tcgen05.ld) -> global.
+//
+//   C[M,N] (=|+=) opA(A) * opB(B)
+//
+// Operand majors cover the three products a linear layer needs without any transposes in memory:
+//   forward   Y  = X  * W^T   A = X  [M,K] K-major,  B = W [N,K] K-major
+//   dgrad     dX = dY * W     A = dY [M,K] K-major,  B = W [K,N] stored row-major  -> MN-major
+//   wgrad     dW = dY^T * X   A = dY [K,M] stored row-major -> MN-major, B = X [K,N] -> MN-major
+// (replaces the cuBLAS calls behind nn.Linear in the reference: src/olmo_core/nn/feed_forward.py:161-171,
+//  src/olmo_core/nn/attention/__init__.py:379-390, src/olmo_core/nn/lm_head.py:174)
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (one TMEM lane quadrant each). Tile 128 x 256 x 64, 4-stage smem ring,
+// two 256-column fp32 accumulators in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
+// All waits are bounded (see common.cuh).
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+#include "ocb_api.h"
+
+namespace ocb {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+enum : int { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_BF16_ACC = 3 };
+
+struct GemmParams {
+  void* C;
+  long long ldc;
+  int M, N, K;
+  int group_m;  // rasterisation group size (in M tiles)
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int gm = min(tiles_m - first_m, group_m);
+  const int r = tile - g * per_group;
+  tm = first_m + (r % gm);
+  tn = r / gm;
+}
+
+template <int A_MN, int B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (64 * BK * 2), &tma_a, &full_bar[stage], m0 + j * 64, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (64 * BK * 2), &tma_b, &full_bar[stage], n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Give copies that are still in flight time to land before the CTA's shared memory goes away.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      // K-major: rows are 128 B apart inside an 8-row swizzle atom, atoms 1024 B apart (SBO); LBO unused (=1).
+      // MN-major: 64-element column chunks are one [64 x BK] TMA box apart (LBO); 8 k-rows = 1024 B (SBO).
+      constexpr uint32_t a_lbo = A_MN ? 64 * BK * 2 : 16, b_lbo = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t a_kstep = A_MN ? 2048 : 32, b_kstep = B_MN ? 2048 : 32;  // bytes per UMMA_K = 16
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kStatusTimeoutMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+      ok = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (!row_ok || col >= p.N) continue;
+        if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              if (EPI == EPI_BF16_ACC) {
+                const uint4 old = reinterpret_cast<const uint4*>(dst)[v];
+                const float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
+                             a3 = unpack_bf16x2(old.w);
+                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) + a0.x, __uint_as_float(r[8 * v + 1]) + a0.y);
+                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) + a1.x, __uint_as_float(r[8 * v + 3]) + a1.y);
+                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) + a2.x, __uint_as_float(r[8 * v + 5]) + a2.y);
+                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) + a3.x, __uint_as_float(r[8 * v + 7]) + a3.y);
+              } else {
+                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              }
+              reinterpret_cast<uint4*>(dst)[v] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < p.N) {
+                float v = __uint_as_float(r[j]);
+                if (EPI == EPI_BF16_ACC) v += __bfloat162float(dst[j]);
+                dst[j] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
+                                     __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+              if (EPI == EPI_F32_ACC) {
+                const float4 old = reinterpret_cast<const float4*>(dst)[v];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              reinterpret_cast<float4*>(dst)[v] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < p.N) {
+                float v = __uint_as_float(r[j]);
+                if (EPI == EPI_F32_ACC) v += dst[j];
+                dst[j] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side: tensor-map construction (cached) and launch.
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+static thread_local int g_last_tmap_error = 0;
+
+struct TmapKey {
+  const void* ptr;
+  uint64_t d0, d1, d2, stride1, stride2;
+  uint32_t b0, b1, b2;
+  uint32_t dtype;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && stride1 == o.stride1 && stride2 == o.stride2 &&
+           b0 == o.b0 && b1 == o.b1 && b2 == o.b2 && dtype == o.dtype;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.d0); mix(k.d1); mix(k.d2); mix(k.stride1); mix(k.stride2); mix(k.b0); mix(k.b1); mix(k.b2); mix(k.dtype);
+    return h;
+  }
+};
+
+// Builds (or fetches) a tiled tensor map with 128-byte swizzle. rank 2 or 3; inner box must span 128 bytes.
+bool get_tensor_map(CUtensorMap* out, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, int elem_bytes) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{ptr, dims[0], dims[1], rank > 2 ? dims[2] : 1, strides_bytes[0], rank > 2 ? strides_bytes[1] : 0,
+              box[0], box[1], rank > 2 ? box[2] : 1, static_cast<uint32_t>(elem_bytes)};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t gdim[3] = {dims[0], dims[1], rank > 2 ? dims[2] : 1};
+  cuuint64_t gstr[2] = {strides_bytes[0], rank > 2 ? strides_bytes[1] : 0};
+  cuuint32_t bdim[3] = {box[0], box[1], rank > 2 ? box[2] : 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                           : (elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+  CUresult r = enc(out, dt, rank, const_cast<void*>(ptr), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    // A thread that has not touched the runtime yet (e.g. an autograd worker) may have no context bound.
+    cudaFree(nullptr);
+    r = enc(out, dt, rank, const_cast<void*>(ptr), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  g_last_tmap_error = static_cast<int>(r);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int A_MN, int B_MN, int EPI>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -3;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ocb
+
+using namespace ocb;
+
+// Returns 0 on success, negative on a host-side failure (bad argument, tensor-map error, launch error).
+extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                             long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status,
+                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -1;
+  CUtensorMap ta, tb;
+  {
+    // Stored layout of A: K-major -> [M rows, K inner]; MN-major -> [K rows, M inner].
+    uint64_t dims[2] = {static_cast<uint64_t>(a_mn_major ? M : K), static_cast<uint64_t>(a_mn_major ? K : M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(a_mn_major ? BK : BM)};
+    if (!get_tensor_map(&ta, A, 2, dims, str, box, 2)) return -(1000 + g_last_tmap_error);
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(b_mn_major ? N : K), static_cast<uint64_t>(b_mn_major ? K : N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(b_mn_major ? BK : BN)};
+    if (!get_tensor_map(&tb, B, 2, dims, str, box, 2)) return -(2000 + g_last_tmap_error);
+  }
+  GemmParams p;
+  p.C = C;
+  p.ldc = ldc;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.group_m = 8;
+  p.status = status;
+
+#define OCB_DISPATCH_EPI(AM, BMJ)                                                       \
+  switch (epilogue) {                                                                   \
+    case EPI_BF16: return launch_gemm<AM, BMJ, EPI_BF16>(ta, tb, p, stream);            \
+    case EPI_F32_ACC: return launch_gemm<AM, BMJ, EPI_F32_ACC>(ta, tb, p, stream);      \
+    case EPI_F32: return launch_gemm<AM, BMJ, EPI_F32>(ta, tb, p, stream);              \
+    case EPI_BF16_ACC: return launch_gemm<AM, BMJ, EPI_BF16_ACC>(ta, tb, p, stream);    \
+    default: return -1;                                                                 \
+  }
+  if (!a_mn_major && !b_mn_major) { OCB_DISPATCH_EPI(0, 0) }
+  if (!a_mn_major && b_mn_major) { OCB_DISPATCH_EPI(0, 1) }
+  if (a_mn_major && b_mn_major) { OCB_DISPATCH_EPI(1, 1) }
+  OCB_DISPATCH_EPI(1, 0)
+#undef OCB_DISPATCH_EPI
+}

@@ -1,0 +1,85 @@
+// C entry points of the sm_100a kernel library. Every launcher is asynchronous on `stream`, returns 0
+// on success and a negative value on a host-side failure (bad argument / launch error). Kernels that
+// can wait on the device additionally report through an `int* status` device word (see common.cuh).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// dtype codes for activation tensors
+#define OCB_BF16 0
+#define OCB_F32 1
+
+// ---- GEMM (gemm_sm100.cu) ---------------------------------------------------------------------------
+// epilogue: 0 = bf16 store, 1 = fp32 accumulate (C += AB), 2 = fp32 store, 3 = bf16 accumulate.
+int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                  long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status, cudaStream_t stream);
+
+// ---- normalisation / rotary / activation (elementwise.cu) -------------------------------------------
+// y = rmsnorm(x) * w  (+ resid).  x,y,resid: [rows, cols] with row strides ldx/ldy/ldr. w: [cols].
+// group = width of one normalisation group (cols for a full-row norm, head_dim for a per-head norm).
+int ocb_rmsnorm_fwd(const void* x, const void* w, const void* resid, void* y, float* rstd, int rows, int cols,
+                    int group, long long ldx, long long ldy, long long ldr, float eps, int act_dtype, int w_dtype,
+                    cudaStream_t stream);
+// dx = d rmsnorm; dw_partial: [n_partial, cols] fp32 scratch (n_partial returned by ocb_norm_bwd_partials()).
+int ocb_norm_bwd_partials();
+int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                    int rows, int cols, int group, long long lddy, long long ldx, long long lddx, int act_dtype,
+                    int w_dtype, cudaStream_t stream);
+// out[c] (+)= sum_p partial[p, c]; out is fp32 or bf16.
+int ocb_reduce_partials(const float* partial, void* out, int n_partial, int cols, int accumulate, int out_dtype,
+                        cudaStream_t stream);
+
+// Fused (optional) RMSNorm + rotary embedding over [rows, n_heads*head_dim] rows.
+// norm_mode: 0 = none, 1 = full-row norm, 2 = per-head norm. sin/cos: [max_pos, head_dim] fp32.
+// pos_ids: optional int32 [rows]; when null the position is (row % seq_len) + pos_offset.
+int ocb_norm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* sin_t, const float* cos_t,
+                      const int* pos_ids, int rows, int n_heads, int head_dim, int seq_len, int pos_offset,
+                      int norm_mode, long long ldx, long long ldy, float eps, int act_dtype, int w_dtype,
+                      cudaStream_t stream);
+int ocb_norm_rope_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                      const float* sin_t, const float* cos_t, const int* pos_ids, int rows, int n_heads, int head_dim,
+                      int seq_len, int pos_offset, int norm_mode, long long lddy, long long ldx, long long lddx,
+                      int act_dtype, int w_dtype, cudaStream_t stream);
+
+// out = silu(a) * b ; (da, db) = d/d(a,b) given dout.
+int ocb_swiglu_fwd(const void* a, const void* b, void* out, long long rows, int cols, long long lda, long long ldb,
+                   long long ldo, int act_dtype, cudaStream_t stream);
+int ocb_swiglu_bwd(const void* dout, const void* a, const void* b, void* da, void* db, long long rows, int cols,
+                   long long lddo, long long lda, long long ldb, long long ldda, long long lddb, int act_dtype,
+                   cudaStream_t stream);
+
+// ---- loss (elementwise.cu) -------------------------------------------------------------------------
+// Row-wise cross entropy + z-loss over logits [rows, vocab] (bf16 or fp32, row stride ld).
+// Writes ce[row], z[row] (0 for ignored rows) and, when dlogits != null, the gradient
+//   grad_scale * ((softmax - onehot) + 2*z_mult*lse*softmax)   (may alias logits).
+int ocb_cross_entropy_fwd_bwd(const void* logits, const long long* labels, float* ce, float* z, void* dlogits,
+                              int rows, int vocab, long long ld, long long ldd, long long ignore_index, float z_mult,
+                              const float* grad_scale, int act_dtype, cudaStream_t stream);
+
+// ---- embedding --------------------------------------------------------------------------------------
+int ocb_embedding_fwd(const long long* ids, const void* table, void* out, int rows, int dim, long long vocab,
+                      int act_dtype, cudaStream_t stream);
+// dtable[ids[r]] += dout[r]  (fp32 atomics)
+int ocb_embedding_bwd(const long long* ids, const void* dout, float* dtable, int rows, int dim, long long vocab,
+                      int act_dtype, cudaStream_t stream);
+
+// ---- optimiser --------------------------------------------------------------------------------------
+// SkipStep-AdamW over a flat fp32 range. step / step_factor / grad_scale are device scalars (fp32);
+// grad_scale and step_factor may be null (=1). p_lowp (bf16 copy of the updated parameters) may be null.
+int ocb_adamw_step(float* p, float* m, float* v, const void* g, void* p_lowp, long long n, float lr, float beta1,
+                   float beta2, float eps, float weight_decay, const float* step, const float* step_factor,
+                   const float* grad_scale, int grad_dtype, cudaStream_t stream);
+// out[0] (+)= sum(x^2). scratch: fp32 [ocb_sumsq_partials()] device buffer.
+int ocb_sumsq_partials();
+int ocb_sumsq(const void* x, long long n, float* scratch, float* out, int accumulate, int dtype, cudaStream_t stream);
+// y = bf16(x * scale) / generic cast helpers
+int ocb_cast_f32_to_bf16(const float* x, void* y, long long n, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

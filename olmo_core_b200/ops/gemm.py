@@ -1,0 +1,171 @@
+"""
+bf16 GEMM on tcgen05 tensor cores and the autograd-aware linear layer built on it.
+
+``gemm`` drives ``csrc/gemm_sm100.cu`` (TMA -> 128B-swizzled smem -> ``tcgen05.mma`` -> TMEM -> epilogue).
+``linear`` is the op behind every dense projection of the models (it replaces ``nn.Linear`` /
+``F.linear`` used by the reference at src/olmo_core/nn/attention/__init__.py:379-390,
+src/olmo_core/nn/feed_forward.py:161-171 and src/olmo_core/nn/lm_head.py:174). On CPU tensors both fall
+back to ``torch.matmul``, which is also the numerical oracle in the tests.
+
+Weight-gradient fusion: when the weight carries a ``main_grad`` attribute (an fp32 buffer owned by the
+sharded-parameter runtime) the wgrad GEMM accumulates straight into it from its epilogue
+(``C += A^T B`` in fp32) and autograd sees no gradient for the weight.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+__all__ = ["gemm", "linear", "LinearFunction", "compute_weight"]
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise _lib.KernelError("GEMM operands must be 2-D with unit inner stride")
+    return t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    trans_a: bool = False,
+    trans_b: bool = True,
+    out: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """
+    ``out (=|+=) op(a) @ op(b)`` with fp32 accumulation.
+
+    Stored shapes: ``a`` is ``[M, K]`` (or ``[K, M]`` when ``trans_a``), ``b`` is ``[N, K]`` when
+    ``trans_b`` (the ``nn.Linear`` weight layout) or ``[K, N]`` otherwise. Both must be bf16 on CUDA;
+    ``out`` may be bf16 or fp32.
+    """
+    if trans_a:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if trans_b:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    if K != Kb:
+        raise ValueError(f"GEMM inner dimensions differ: {K} vs {Kb}")
+
+    if not a.is_cuda:
+        af = a.float().t() if trans_a else a.float()
+        bf = b.float().t() if trans_b else b.float()
+        res = af @ bf
+        if out is None:
+            return res.to(out_dtype or a.dtype)
+        if accumulate:
+            out.add_(res.to(out.dtype))
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise _lib.KernelError(f"tcgen05 GEMM takes bfloat16 operands, got {a.dtype} and {b.dtype}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+    if out.shape != (M, N):
+        raise ValueError(f"output has shape {tuple(out.shape)}, expected {(M, N)}")
+    if out.dtype == torch.bfloat16:
+        epi = _lib.EPI_BF16_ACC if accumulate else _lib.EPI_BF16
+    elif out.dtype == torch.float32:
+        epi = _lib.EPI_F32_ACC if accumulate else _lib.EPI_F32
+    else:
+        raise _lib.KernelError(f"unsupported GEMM output dtype {out.dtype}")
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        if not accumulate:
+            out.zero_()
+        return out
+    rc = _lib.lib().ocb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+        _row_stride(a), _row_stride(b), _row_stride(out),
+        1 if trans_a else 0, 0 if trans_b else 1, epi,
+        _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr(),
+    )
+    _lib.check(rc, "ocb_gemm_bf16")
+    return out
+
+
+def compute_weight(weight: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """
+    The tensor to feed the tensor cores for ``weight``: its resident low-precision copy when the
+    sharded-parameter runtime attached one (``weight._lowp``), else a cast of the parameter itself.
+    """
+    lowp = getattr(weight, "_lowp", None)
+    if lowp is not None and lowp.dtype == dtype:
+        return lowp
+    return weight if weight.dtype == dtype else weight.to(dtype)
+
+
+class LinearFunction(torch.autograd.Function):
+    """``y = x @ W^T`` for CUDA bf16 activations, with dgrad/wgrad on the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
+        w = compute_weight(weight, torch.bfloat16)
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        y = gemm(x2, w, trans_b=True)
+        ctx.save_for_backward(x2, w)
+        ctx.weight_ref = weight
+        ctx.x_shape = x.shape
+        ctx.x_dtype = x.dtype
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy: torch.Tensor):  # type: ignore[override]
+        x2, w = ctx.saved_tensors
+        weight = ctx.weight_ref
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = None
+        dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, trans_b=False).view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                gemm(dy2, x2, trans_a=True, trans_b=False, out=main_grad, accumulate=True)
+                if hasattr(weight, "grad_added_to_main_grad"):
+                    weight.grad_added_to_main_grad = True
+            else:
+                dw = gemm(dy2, x2, trans_a=True, trans_b=False, out_dtype=torch.float32)
+                if dw.dtype != weight.dtype:
+                    dw = dw.to(weight.dtype)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """
+    Dense projection. CUDA + (bf16 activations or an attached low-precision weight copy) runs the
+    tcgen05 kernel; anything else (CPU, fp32 debugging runs) uses ``F.linear``.
+    """
+    if x.is_cuda and (x.dtype == torch.bfloat16 or getattr(weight, "_lowp", None) is not None):
+        y = LinearFunction.apply(x, weight)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        return y
+    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    b = None if bias is None else bias.to(x.dtype)
+    return torch.nn.functional.linear(x, w, b)
