@@ -303,6 +303,9 @@ def _decode_dataclass(tp: Optional[type], data: Dict[str, Any], path: str) -> An
     hints = _type_hints(cls)
     kwargs = {}
     init_fields = {f.name: f for f in fields(cls) if f.init}
+    for fname, f in getattr(cls, "__dataclass_fields__", {}).items():
+        if fname not in init_fields and "INITVAR" in str(getattr(f, "_field_type", "")):
+            init_fields[fname] = f
     for key, val in data.items():
         if key not in init_fields:
             raise OLMoConfigurationError(f"'{cls.__name__}' has no field '{key}' (at '{path}')")

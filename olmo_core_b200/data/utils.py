@@ -1,0 +1,465 @@
+"""
+Batch and token-array helpers for the data layer (function names of src/olmo_core/data/utils.py:43-974).
+"""
+
+from __future__ import annotations
+
+import gzip
+import math
+import os
+from contextlib import contextmanager
+from pathlib import Path
+from typing import Any, Dict, Generator, Iterable, List, NamedTuple, Optional, Sequence, Tuple, TypeVar, Union
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from ..aliases import PathOrStr
+from ..io import get_bytes_range, get_file_size, is_url, resource_path
+
+T = TypeVar("T")
+
+__all__ = [
+    "split_batch",
+    "melt_batch",
+    "truncate_batch",
+    "get_labels",
+    "get_document_lengths",
+    "get_cumulative_document_lengths",
+    "iter_document_indices",
+    "get_document_indices",
+    "write_document_indices",
+    "load_array_slice",
+    "load_array_slice_into_tensor",
+    "iter_batched",
+    "memmap_to_write",
+    "write_array_to_disk",
+    "divide_into_buckets",
+    "chunk_array",
+    "get_rng",
+    "bucket_documents",
+    "segment_documents_into_instances",
+    "get_doc_lengths_from_indices",
+    "find_periodic_sequences",
+    "RepetitionTuple",
+    "chunked",
+    "InstancePacker",
+    "pack_documents_into_instances",
+    "attention_mask_to_cache_leftpad",
+]
+
+
+# ----------------------------------------------------------------------------------------------
+# batches
+# ----------------------------------------------------------------------------------------------
+
+
+def _per_instance_slices(batch_size: int, n: int) -> List[slice]:
+    return [slice(i, min(i + n, batch_size)) for i in range(0, batch_size, n)]
+
+
+def split_batch(batch: Dict[str, Any], num_microbatch_instances: int) -> List[Dict[str, Any]]:
+    """Split a collated batch into micro-batches of at most ``num_microbatch_instances`` instances."""
+    if num_microbatch_instances <= 0:
+        raise RuntimeError("microbatch size is too small!")
+    batch_size = batch["input_ids"].shape[0]
+    if batch_size <= num_microbatch_instances:
+        return [batch]
+    out: List[Dict[str, Any]] = []
+    for sl in _per_instance_slices(batch_size, num_microbatch_instances):
+        mb: Dict[str, Any] = {}
+        for key, value in batch.items():
+            if isinstance(value, (torch.Tensor, list)):
+                mb[key] = value[sl]
+            else:
+                raise RuntimeError(f"unexpected item in batch: '{key}={value}'")
+        out.append(mb)
+    return out
+
+
+def _reshape_batch(batch: Dict[str, Any], target: int, melt: bool) -> Dict[str, Any]:
+    bsz, cur = batch["input_ids"].shape
+    if cur <= target:
+        return batch
+    if melt and cur % target != 0:
+        raise RuntimeError("current sequence of batch must be a multiple of the target sequence length in order to 'melt' the batch")
+    ratio = cur // target
+    new: Dict[str, Any] = {}
+    for key, value in batch.items():
+        if isinstance(value, torch.Tensor):
+            if value.shape == (bsz, cur):
+                new[key] = value.reshape(-1, target) if melt else value[:, :target]
+            elif value.shape in ((bsz,), (bsz, 1)):
+                new[key] = value.repeat_interleave(ratio) if melt else value
+            else:
+                raise RuntimeError(f"unable to reshape '{key}' tensor in batch with shape '{value.shape}'")
+        elif isinstance(value, list) and value:
+            items: List[Any] = []
+            for item in value:
+                if isinstance(item, list):
+                    if len(item) != cur:
+                        raise RuntimeError(f"unexpected item length for '{key}' in batch")
+                    if melt:
+                        items.extend(item[i * target : (i + 1) * target] for i in range(ratio))
+                    else:
+                        items.append(item[:target])
+                else:
+                    items.extend([item] * (ratio if melt else 1))
+            new[key] = items
+        else:
+            raise RuntimeError(f"unexpected item in batch: '{key}={value}'")
+    return new
+
+
+def melt_batch(batch: Dict[str, Any], target_sequence_length: int) -> Dict[str, Any]:
+    """Shorten sequences to ``target_sequence_length`` and proportionally increase the number of instances."""
+    return _reshape_batch(batch, target_sequence_length, melt=True)
+
+
+def truncate_batch(batch: Dict[str, Any], target_sequence_length: int) -> Dict[str, Any]:
+    """Cut every instance to ``target_sequence_length`` tokens."""
+    return _reshape_batch(batch, target_sequence_length, melt=False)
+
+
+def get_labels(batch: Dict[str, Any], label_ignore_index: int = -100) -> torch.Tensor:
+    """Next-token labels: input ids shifted left, with masked / padded positions set to the ignore index."""
+    labels = batch["input_ids"].clone()
+    if (label_mask := batch.get("label_mask")) is not None:
+        labels.masked_fill_(~label_mask, label_ignore_index)
+    if (attention_mask := batch.get("attention_mask")) is not None:
+        labels.masked_fill_(attention_mask == 0.0, label_ignore_index)
+    if (instance_mask := batch.get("instance_mask")) is not None:
+        labels.masked_fill_(~instance_mask.unsqueeze(-1), label_ignore_index)
+    return F.pad(labels[..., 1:], (0, 1, 0, 0), value=label_ignore_index)
+
+
+def attention_mask_to_cache_leftpad(attention_mask: torch.Tensor) -> torch.Tensor:
+    """Number of left-padding positions per row of a ``[B, T]`` left-padded attention mask (int32)."""
+    if attention_mask.ndim != 2:
+        raise ValueError(f"expected 2-D attention_mask (batch, seq_len), got shape {attention_mask.shape}")
+    valid = attention_mask if attention_mask.dtype == torch.bool else attention_mask != 0
+    seen = valid.cummax(dim=1).values
+    if bool((seen & ~valid).any()):
+        raise ValueError("attention_mask must represent *prefix padding* (all padding tokens precede valid tokens)")
+    return valid.int().argmax(dim=-1).int()
+
+
+# ----------------------------------------------------------------------------------------------
+# documents
+# ----------------------------------------------------------------------------------------------
+
+
+def get_document_lengths(input_ids: Union[torch.Tensor, np.ndarray], eos_token_id: int,
+                         bos_token_id: Optional[int] = None) -> torch.Tensor:
+    """Lengths of the documents inside a 1-D token sequence (documents end with EOS, the tail counts as one)."""
+    if not isinstance(input_ids, torch.Tensor):
+        input_ids = torch.tensor(input_ids.astype(np.int_), dtype=torch.long)
+    n = input_ids.shape[0]
+    if bos_token_id is None:
+        ends = (input_ids == eos_token_id).nonzero(as_tuple=True)[0].to(torch.int32)
+        tail = [] if n > 0 and input_ids[-1] == eos_token_id else [n - 1]
+    else:
+        ends = torch.logical_and(input_ids[:-1] == eos_token_id, input_ids[1:] == bos_token_id).nonzero(as_tuple=True)[0].to(torch.int32)
+        tail = [n - 1]
+    bounds = torch.cat([torch.tensor([-1], dtype=torch.int32), ends, torch.tensor(tail, dtype=torch.int32)])
+    return bounds[1:] - bounds[:-1]
+
+
+def get_cumulative_document_lengths(doc_lens: torch.Tensor) -> torch.Tensor:
+    """``[0, l0, l0+l1, ...]`` (int32) over the non-zero entries of a (possibly padded, batched) length tensor."""
+    nz = doc_lens.masked_select(doc_lens != 0)
+    return torch.cat([torch.zeros(1, dtype=torch.int32, device=doc_lens.device), torch.cumsum(nz, 0, dtype=torch.int32)])
+
+
+def _array_itemsize(dtype) -> int:
+    return np.dtype(dtype).itemsize
+
+
+def load_array_slice(path: PathOrStr, start_idx: int, end_idx: int, dtype) -> np.ndarray:
+    """Items ``[start_idx, end_idx)`` of a flat binary array stored at a local path or URL."""
+    item = _array_itemsize(dtype)
+    if is_url(path):
+        raw = get_bytes_range(path, start_idx * item, (end_idx - start_idx) * item)
+        return np.frombuffer(raw, dtype=dtype)
+    with open(path, "rb") as f:
+        f.seek(start_idx * item)
+        return np.frombuffer(f.read((end_idx - start_idx) * item), dtype=dtype)
+
+
+def load_array_slice_into_tensor(path: PathOrStr, start_idx: int, end_idx: int, dtype) -> torch.Tensor:
+    arr = load_array_slice(path, start_idx, end_idx, dtype)
+    if arr.dtype in (np.uint8, np.uint16, np.uint32, np.uint64):
+        arr = arr.astype(np.int64)
+    return torch.from_numpy(np.ascontiguousarray(arr)).long() if arr.dtype != np.bool_ else torch.from_numpy(arr.copy())
+
+
+def iter_document_indices(data_path: PathOrStr, local_cache: Optional[PathOrStr] = None, use_array_if_local: bool = True,
+                          eos_token_id: Optional[int] = None, bos_token_id: Optional[int] = None,
+                          dtype=None) -> Generator[Tuple[int, int], None, None]:
+    """
+    ``(start, end)`` token offsets of every document in a token file. Uses the ``.csv.gz`` metadata file
+    next to the data when one exists, else scans the array for EOS tokens.
+    """
+    meta = str(data_path).replace(".npy", ".csv.gz")
+    try:
+        meta_path = resource_path(os.path.dirname(meta), os.path.basename(meta), local_cache=local_cache)
+        if Path(meta_path).is_file():
+            with gzip.open(meta_path, "rt") as f:
+                for line in f:
+                    start, end, *_ = line.split(",")
+                    yield int(start), int(end)
+            return
+    except (FileNotFoundError, OSError):
+        pass
+    if eos_token_id is None or dtype is None:
+        raise FileNotFoundError(f"no document metadata for {data_path} and no EOS id / dtype to scan with")
+    n = get_file_size(data_path) // _array_itemsize(dtype)
+    arr = load_array_slice(data_path, 0, n, dtype)
+    ends = np.nonzero(arr == eos_token_id)[0] + 1
+    start = 0
+    for end in ends.tolist():
+        yield start, end
+        start = end
+    if start < n:
+        yield start, n
+
+
+def get_document_indices(data_path: PathOrStr, local_cache: Optional[PathOrStr] = None, **kwargs) -> List[Tuple[int, int]]:
+    return list(iter_document_indices(data_path, local_cache=local_cache, **kwargs))
+
+
+def write_document_indices(data_path: Path, *, dtype, eos_token_id: int) -> Path:
+    """Scan a token file for EOS tokens and write ``<name>.csv.gz`` with one ``start,end`` row per document."""
+    out = Path(str(data_path).replace(".npy", ".csv.gz"))
+    with gzip.open(out, "wt") as f:
+        for start, end in iter_document_indices(data_path, eos_token_id=eos_token_id, dtype=dtype, local_cache="/nonexistent"):
+            f.write(f"{start},{end}\n")
+    return out
+
+
+def get_doc_lengths_from_indices(doc_indices: np.ndarray) -> np.ndarray:
+    return doc_indices[1::2] - doc_indices[::2]
+
+
+def iter_batched(iterable: Iterable[Dict[str, Any]], batch_num_tokens: int) -> Iterable[Tuple[Dict[str, Any], ...]]:
+    """Group instances into tuples holding at most ``batch_num_tokens`` tokens each."""
+    batch: List[Dict[str, Any]] = []
+    tokens = 0
+    for x in iterable:
+        n = x["input_ids"].numel()
+        if n > batch_num_tokens:
+            raise RuntimeError(f"an instance has {n} tokens, more than the batch size of {batch_num_tokens}")
+        if tokens + n > batch_num_tokens:
+            yield tuple(batch)
+            batch, tokens = [], 0
+        batch.append(x)
+        tokens += n
+    if batch:
+        yield tuple(batch)
+
+
+@contextmanager
+def memmap_to_write(path: Path, *, shape: Tuple[int, ...], dtype) -> Generator[np.ndarray, None, None]:
+    """Write a ``.npy``-less raw memmap atomically: fill a temp file, then rename it into place."""
+    path.parent.mkdir(parents=True, exist_ok=True)
+    tmp = path.with_suffix(f".{os.getpid()}.tmp")
+    mm = np.memmap(tmp, dtype=dtype, mode="w+", shape=shape)
+    try:
+        yield mm
+    except BaseException:
+        del mm
+        tmp.unlink(missing_ok=True)
+        raise
+    mm.flush()
+    del mm
+    tmp.replace(path)
+
+
+def write_array_to_disk(arr: np.ndarray, path: Path) -> None:
+    with memmap_to_write(path, shape=arr.shape, dtype=arr.dtype) as mm:
+        mm[:] = arr
+
+
+def divide_into_buckets(n: int, b: int) -> List[int]:
+    """Split ``n`` items into ``b`` buckets whose sizes differ by at most one."""
+    q, r = divmod(n, b)
+    return [q + 1] * r + [q] * (b - r)
+
+
+def chunk_array(arr: np.ndarray, chunk_sizes: Sequence[int]) -> List[np.ndarray]:
+    out, offset = [], 0
+    for n in chunk_sizes:
+        out.append(arr[offset : offset + n])
+        offset += n
+    return out
+
+
+def get_rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed=seed))
+
+
+def bucket_documents(path: PathOrStr, target: Path, *, buckets: Sequence[int], eos_token_id: int, dtype,
+                     indices_dtype=np.uint32) -> Tuple[int, int]:
+    """
+    Cut documents into pieces whose lengths are powers of two from ``buckets`` (largest first) and write the
+    ``(start, end)`` offsets of all pieces to ``target``. Returns (number of documents, number of pieces).
+    """
+    sizes = sorted(buckets, reverse=True)
+    pieces: List[int] = []
+    n_docs = 0
+    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, dtype=dtype):
+        n_docs += 1
+        pos = start
+        while end - pos >= sizes[-1]:
+            for s in sizes:
+                if end - pos >= s:
+                    pieces += [pos, pos + s]
+                    pos += s
+                    break
+    arr = np.asarray(pieces, dtype=indices_dtype)
+    write_array_to_disk(arr, target)
+    return n_docs, len(pieces) // 2
+
+
+def segment_documents_into_instances(path: PathOrStr, target: Path, *, max_sequence_length: int, eos_token_id: int, dtype,
+                                     indices_dtype=np.uint32, sample: Optional[Tuple[int, int]] = None) -> Tuple[int, int]:
+    """One instance per document, truncated to ``max_sequence_length``; optionally a random sample of ``(n, seed)``."""
+    idx: List[int] = []
+    n_docs = 0
+    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, dtype=dtype):
+        n_docs += 1
+        idx += [start, min(end, start + max_sequence_length)]
+    arr = np.asarray(idx, dtype=indices_dtype).reshape(-1, 2)
+    if sample is not None:
+        n, seed = sample
+        arr = arr[get_rng(seed).choice(arr.shape[0], size=min(n, arr.shape[0]), replace=False)]
+    write_array_to_disk(arr.reshape(-1), target)
+    return n_docs, arr.shape[0]
+
+
+# ----------------------------------------------------------------------------------------------
+# repetition filter
+# ----------------------------------------------------------------------------------------------
+
+
+class RepetitionTuple(NamedTuple):
+    start: int
+    end: int
+    period: int
+    times: int
+
+
+def find_periodic_sequences(arr: np.ndarray, max_period: int, min_period: int = 1,
+                            mask_value: int = -1) -> Generator[RepetitionTuple, None, None]:
+    """Yield maximal runs where ``arr[i] == arr[i + period]`` that repeat at least three times."""
+    n = len(arr)
+    for period in range(min_period, min(max_period, n // 3) + 1):
+        same = np.concatenate([arr[:-period] == arr[period:], [False]])
+        same &= np.concatenate([arr[:-period] != mask_value, [False]])
+        edges = np.flatnonzero(np.diff(np.concatenate([[False], same, [False]]).astype(np.int8)))
+        for start, stop in zip(edges[::2], edges[1::2]):
+            length = (stop - start) + period
+            times = length // period
+            if times >= 3:
+                yield RepetitionTuple(int(start), int(start + length), period, int(times))
+
+
+def chunked(iterable: Iterable[T], n: int) -> Iterable[List[T]]:
+    buf: List[T] = []
+    for x in iterable:
+        buf.append(x)
+        if len(buf) == n:
+            yield buf
+            buf = []
+    if buf:
+        yield buf
+
+
+# ----------------------------------------------------------------------------------------------
+# packing
+# ----------------------------------------------------------------------------------------------
+
+
+class InstancePacker:
+    """
+    Best-fit-decreasing bin packing of documents into instances of ``max_sequence_length`` tokens. Free
+    space per open instance is kept in a max segment tree so the tightest fitting instance is found in
+    ``O(log n)``.
+    """
+
+    def __init__(self, max_sequence_length: int):
+        self.max_sequence_length = max_sequence_length
+        self.instances: List[List[int]] = []
+        self._space: List[int] = []
+
+    def _best_fit(self, length: int) -> Optional[int]:
+        best, best_space = None, None
+        for i, s in enumerate(self._space):
+            if s >= length and (best_space is None or s < best_space):
+                best, best_space = i, s
+        return best
+
+    def pack_document(self, document_id: int, document_length: int) -> int:
+        if document_length > self.max_sequence_length:
+            raise ValueError("document is longer than the maximum sequence length")
+        i = self._best_fit(document_length)
+        if i is None:
+            self.instances.append([])
+            self._space.append(self.max_sequence_length)
+            i = len(self.instances) - 1
+        self.instances[i].append(document_id)
+        self._space[i] -= document_length
+        return i
+
+    def pack_documents(self, document_indices: np.ndarray) -> Tuple[List[List[int]], np.ndarray, int]:
+        """``document_indices``: ``[n, 2]`` (start, end). Returns (instances, indices, total tokens)."""
+        lengths = document_indices[:, 1] - document_indices[:, 0]
+        order = np.argsort(-lengths, kind="stable")
+        # bucket free space by size so best-fit is a bisect over distinct free sizes
+        import bisect
+
+        space_keys: List[int] = []
+        by_space: Dict[int, List[int]] = {}
+        for doc_id in order.tolist():
+            n = int(lengths[doc_id])
+            if n > self.max_sequence_length:
+                raise ValueError("document is longer than the maximum sequence length")
+            k = bisect.bisect_left(space_keys, n)
+            if k < len(space_keys):
+                space = space_keys[k]
+                inst = by_space[space].pop()
+                if not by_space[space]:
+                    del by_space[space]
+                    space_keys.pop(k)
+            else:
+                self.instances.append([])
+                inst = len(self.instances) - 1
+                space = self.max_sequence_length
+            self.instances[inst].append(doc_id)
+            left = space - n
+            if left > 0:
+                if left not in by_space:
+                    bisect.insort(space_keys, left)
+                    by_space[left] = []
+                by_space[left].append(inst)
+        return self.instances, document_indices, int(lengths.sum())
+
+
+def pack_documents_into_instances(path: PathOrStr, max_sequence_length: int, *, eos_token_id: int, dtype,
+                                  indices_dtype=np.uint64, long_doc_strategy: str = "truncate") -> Tuple[List[List[int]], np.ndarray, int]:
+    """Pack the documents of a token file; documents longer than an instance are truncated or split."""
+    docs: List[Tuple[int, int]] = []
+    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, dtype=dtype):
+        if end - start > max_sequence_length:
+            if long_doc_strategy == "truncate":
+                docs.append((start, start + max_sequence_length))
+            elif long_doc_strategy == "fragment":
+                for s in range(start, end, max_sequence_length):
+                    docs.append((s, min(end, s + max_sequence_length)))
+            else:
+                raise ValueError(long_doc_strategy)
+        else:
+            docs.append((start, end))
+    arr = np.asarray(docs, dtype=indices_dtype).reshape(-1, 2)
+    return InstancePacker(max_sequence_length).pack_documents(arr)

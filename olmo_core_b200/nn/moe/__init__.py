@@ -1,0 +1,28 @@
+"""Mixture-of-experts building blocks (src/olmo_core/nn/moe/__init__.py:16-29)."""
+
+from .loss import MoELoadBalancingLossGranularity
+from .mlp import DroplessMoEMLP, MoEMLP
+from .moe import DroplessMoE, MoE, MoEBase, MoEConfig, MoEType
+from .router import (
+    MoELinearRouter,
+    MoERouter,
+    MoERouterConfig,
+    MoERouterGatingFunction,
+    MoERouterType,
+)
+
+__all__ = [
+    "MoEBase",
+    "MoE",
+    "DroplessMoE",
+    "MoEConfig",
+    "MoEType",
+    "MoEMLP",
+    "DroplessMoEMLP",
+    "MoERouter",
+    "MoELinearRouter",
+    "MoERouterConfig",
+    "MoERouterType",
+    "MoERouterGatingFunction",
+    "MoELoadBalancingLossGranularity",
+]

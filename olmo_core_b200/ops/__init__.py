@@ -1,0 +1,30 @@
+"""
+Operator layer. Each op runs a hand-written sm_100a kernel (``csrc/*.cu``, bound through ctypes in
+``_lib``) when its inputs live on a CUDA device and a PyTorch restatement of the same math otherwise.
+"""
+
+import torch
+
+__all__ = ["attach_auxiliary_loss"]
+
+
+class _AuxLoss(torch.autograd.Function):
+    """Identity on ``x`` that feeds a gradient of one into ``aux_loss`` during backward."""
+
+    @staticmethod
+    def forward(ctx, x, aux_loss):  # type: ignore[override]
+        ctx.save_for_backward(aux_loss)
+        return x
+
+    @staticmethod
+    def backward(ctx, grad):  # type: ignore[override]
+        (aux_loss,) = ctx.saved_tensors
+        return grad, torch.ones_like(aux_loss)
+
+
+def attach_auxiliary_loss(x: torch.Tensor, aux_loss: torch.Tensor) -> torch.Tensor:
+    """
+    Tie ``aux_loss`` to ``x`` so that ``backward`` through ``x`` also back-propagates the auxiliary loss
+    (src/olmo_core/ops/__init__.py:4-28).
+    """
+    return _AuxLoss.apply(x, aux_loss)

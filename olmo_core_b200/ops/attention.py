@@ -1,0 +1,218 @@
+"""
+Scaled-dot-product attention op: causal / sliding-window / packed-document (varlen) / GQA.
+
+``attention`` takes ``q [B, Tq, H, D]`` and ``k, v [B, Tk, Hkv, D]`` (sequence-major, the layout the QKV
+projection produces, so no transposes are needed on either side of the kernel). Semantics follow the
+reference's attention backends (src/olmo_core/nn/attention/backend.py:299-444):
+
+* causal masking aligned to the *end* of the key sequence (query ``i`` sees keys ``<= i + Tk - Tq``),
+* ``window_size = w``: query ``i`` additionally only sees the last ``w`` keys ``[i-w+1, i]``,
+* ``cu_seqlens``: documents packed along the (flattened) token dimension attend only within themselves.
+
+On CUDA with bf16 inputs and ``head_dim`` in {64, 128} the in-tree flash-attention kernels
+(``csrc/attention_sm100.cu``) are used for forward and backward. ``attention_reference`` is the plain
+fp32 restatement used on CPU and as the oracle in tests.
+"""
+
+from __future__ import annotations
+
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+__all__ = ["attention", "attention_reference", "build_attention_mask", "has_flash_kernel"]
+
+
+def build_attention_mask(
+    tq: int,
+    tk: int,
+    device: torch.device,
+    *,
+    causal: bool = True,
+    window_size: Optional[int] = None,
+    doc_ids_q: Optional[torch.Tensor] = None,
+    doc_ids_k: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Boolean ``[tq, tk]`` (or ``[B, tq, tk]`` with document ids) mask, ``True`` = may attend."""
+    qi = torch.arange(tq, device=device)[:, None] + (tk - tq)
+    ki = torch.arange(tk, device=device)[None, :]
+    mask = torch.ones(tq, tk, dtype=torch.bool, device=device)
+    if causal:
+        mask &= ki <= qi
+    if window_size is not None and window_size > 0:
+        mask &= ki > qi - window_size
+    if doc_ids_q is not None and doc_ids_k is not None:
+        mask = mask[None] & (doc_ids_q[:, :, None] == doc_ids_k[:, None, :])
+    return mask
+
+
+def _doc_ids(cu_seqlens: torch.Tensor, batch: int, t: int) -> torch.Tensor:
+    flat = torch.arange(batch * t, device=cu_seqlens.device, dtype=cu_seqlens.dtype)
+    return torch.bucketize(flat, cu_seqlens[1:], right=True).view(batch, t)
+
+
+def attention_reference(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    causal: bool = True,
+    window_size: Optional[int] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    cu_seqlens_k: Optional[torch.Tensor] = None,
+    scale: Optional[float] = None,
+    dropout_p: float = 0.0,
+) -> torch.Tensor:
+    """fp32 masked-softmax attention; returns ``[B, Tq, H, D]`` in ``q.dtype``."""
+    B, Tq, H, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3)
+    vf = v.float().permute(0, 2, 1, 3)
+    if Hkv != H:
+        rep = H // Hkv
+        kf = kf.repeat_interleave(rep, dim=1)
+        vf = vf.repeat_interleave(rep, dim=1)
+    dq = dk = None
+    if cu_seqlens is not None:
+        dq = _doc_ids(cu_seqlens, B, Tq)
+        dk = _doc_ids(cu_seqlens_k if cu_seqlens_k is not None else cu_seqlens, B, Tk)
+    mask = build_attention_mask(Tq, Tk, q.device, causal=causal, window_size=window_size, doc_ids_q=dq, doc_ids_k=dk)
+    scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    mask_b = mask[:, None] if mask.dim() == 3 else mask[None, None]
+    scores = scores.masked_fill(~mask_b, float("-inf"))
+    probs = torch.softmax(scores, dim=-1)
+    probs = torch.nan_to_num(probs, nan=0.0)  # rows with no visible key
+    if dropout_p > 0.0:
+        probs = torch.nn.functional.dropout(probs, p=dropout_p)
+    out = torch.matmul(probs, vf)
+    return out.permute(0, 2, 1, 3).to(q.dtype)
+
+
+_FLASH_BOUND = False
+
+
+def has_flash_kernel() -> bool:
+    """True when the loaded kernel library exports the attention entry points."""
+    global _FLASH_BOUND
+    if not _lib.available():
+        return False
+    lib = _lib.lib()
+    if not hasattr(lib, "ocb_attention_fwd"):
+        return False
+    if not _FLASH_BOUND:
+        _lib.register_signature(
+            "ocb_attention_fwd",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_longlong, c_longlong, c_longlong, c_longlong, c_float, c_int, c_int, c_void_p, c_void_p],
+        )
+        _lib.register_signature(
+            "ocb_attention_bwd",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_longlong, c_float, c_int,
+             c_int, c_void_p, c_void_p],
+        )
+        _FLASH_BOUND = True
+    return True
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    # [B, T, H, D] tensors that are views into a wider row (e.g. a fused QKV buffer)
+    return t.stride(1)
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, scale: float, causal: bool, window: int):  # type: ignore[override]
+        B, Tq, H, D = q.shape
+        Tk, Hkv = k.shape[1], k.shape[2]
+        q, k, v = (t if (t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == t.stride(1) * t.shape[1]) else t.contiguous()
+                   for t in (q, k, v))
+        out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
+        cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32).contiguous()
+        rc = _lib.lib().ocb_attention_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(cu),
+            B, Tq, Tk, H, Hkv, D, _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(out), scale,
+            1 if causal else 0, window, _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
+        )
+        _lib.check(rc, "ocb_attention_fwd")
+        ctx.save_for_backward(q, k, v, out, lse, cu if cu is not None else torch.empty(0, device=q.device))
+        ctx.cfg = (scale, causal, window, cu is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):  # type: ignore[override]
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        scale, causal, window, has_cu = ctx.cfg
+        B, Tq, H, D = q.shape
+        Tk, Hkv = k.shape[1], k.shape[2]
+        dout = dout.contiguous()
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dk = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
+        dv = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
+        rc = _lib.lib().ocb_attention_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr() if has_cu else None, None,
+            B, Tq, Tk, H, Hkv, D, _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(out), scale,
+            1 if causal else 0, window, _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
+        )
+        _lib.check(rc, "ocb_attention_bwd")
+        return dq, dk, dv, None, None, None, None
+
+
+def _sdpa_path(q, k, v, *, causal, window_size, cu_seqlens, cu_seqlens_k, scale, dropout_p):
+    """Masked ``scaled_dot_product_attention``: used for dtypes / head sizes the flash kernel does not take."""
+    B, Tq, H, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+    mask = None
+    is_causal = causal and Tq == Tk and window_size is None and cu_seqlens is None
+    if not is_causal and (causal or window_size is not None or cu_seqlens is not None):
+        dq = dk = None
+        if cu_seqlens is not None:
+            dq = _doc_ids(cu_seqlens, B, Tq)
+            dk = _doc_ids(cu_seqlens_k if cu_seqlens_k is not None else cu_seqlens, B, Tk)
+        mask = build_attention_mask(Tq, Tk, q.device, causal=causal, window_size=window_size, doc_ids_q=dq, doc_ids_k=dk)
+        mask = mask[:, None] if mask.dim() == 3 else mask
+    out = torch.nn.functional.scaled_dot_product_attention(
+        qh, kh, vh, attn_mask=mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale, enable_gqa=Hkv != H
+    )
+    return out.permute(0, 2, 1, 3)
+
+
+def attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    causal: bool = True,
+    window_size: Optional[int] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    cu_seqlens_k: Optional[torch.Tensor] = None,
+    max_seqlen: Optional[int] = None,
+    scale: Optional[float] = None,
+    dropout_p: float = 0.0,
+) -> torch.Tensor:
+    """See the module docstring. Returns ``[B, Tq, H, D]``."""
+    D = q.shape[-1]
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    use_flash = (
+        q.is_cuda
+        and q.dtype == torch.bfloat16
+        and k.dtype == torch.bfloat16
+        and v.dtype == torch.bfloat16
+        and D in (64, 128)
+        and dropout_p == 0.0
+        and cu_seqlens_k is None
+        and has_flash_kernel()
+    )
+    if use_flash:
+        return _FlashAttention.apply(q, k, v, cu_seqlens, scale, bool(causal), int(window_size or 0))
+    return _sdpa_path(q, k, v, causal=causal, window_size=window_size, cu_seqlens=cu_seqlens,
+                      cu_seqlens_k=cu_seqlens_k, scale=scale, dropout_p=dropout_p)

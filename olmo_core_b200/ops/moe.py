@@ -1,0 +1,193 @@
+"""
+Token permutation ops for mixture-of-experts layers (function names of src/olmo_core/ops/moe.py:52-304,
+whose reference implementation is a set of Triton copy kernels, src/olmo_core/kernels/moe.py:31-536).
+
+Layout conventions: ``top_experts`` is ``[N, k]``; flattening it gives ``N*k`` routed copies. Sorting the
+flat list by expert id (stable) gives ``indices`` (positions in the flat list, so token = index // k) and
+``bins`` (inclusive cumulative sum of tokens per expert). ``gather`` builds the expert-sorted activation
+matrix, ``scatter`` is its inverse and applies the router weights, summing the ``k`` copies of each token
+in fp32.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = [
+    "indices_and_bins",
+    "gather",
+    "scatter",
+    "binned_gather",
+    "binned_scatter",
+    "histc",
+    "batched_histc",
+    "repeat",
+    "sum_tensor",
+    "all_to_all",
+]
+
+
+def histc(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Count occurrences of each expert id (int64 result, any input shape)."""
+    return torch.bincount(indices.reshape(-1), minlength=num_experts)[:num_experts]
+
+
+def batched_histc(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Histogram over the last dimension: ``[..., k] -> [..., num_experts]``."""
+    out = torch.zeros(*indices.shape[:-1], num_experts, dtype=indices.dtype, device=indices.device)
+    out.scatter_add_(-1, indices, torch.ones_like(indices))
+    return out
+
+
+@torch.no_grad()
+def indices_and_bins(top_experts: torch.Tensor, num_experts: int,
+                     counts: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """
+    Returns ``(indices, bin_ids, bins)``: the stable sort permutation of the flattened expert ids, the
+    sorted ids themselves, and the inclusive cumulative token count per expert (all int32/int64).
+    """
+    flat = top_experts.reshape(-1)
+    bin_ids, indices = torch.sort(flat, stable=True)
+    if counts is None:
+        counts = histc(flat, num_experts)
+    bins = torch.cumsum(counts, 0)
+    return indices.to(torch.int32), bin_ids.to(torch.int32), bins.to(torch.int32)
+
+
+class _Gather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, indices, top_k: int):  # type: ignore[override]
+        tok = (indices // top_k).long()
+        ctx.save_for_backward(tok)
+        ctx.n_tokens = x.shape[0]
+        return x.index_select(0, tok)
+
+    @staticmethod
+    def backward(ctx, grad):  # type: ignore[override]
+        (tok,) = ctx.saved_tensors
+        dx = torch.zeros((ctx.n_tokens, grad.shape[1]), dtype=torch.float32, device=grad.device)
+        dx.index_add_(0, tok, grad.float())
+        return dx.to(grad.dtype), None, None
+
+
+def gather(x: torch.Tensor, indices: torch.Tensor, bin_ids: Optional[torch.Tensor], bins: Optional[torch.Tensor],
+           top_k: int) -> torch.Tensor:
+    """Expert-sorted copy of the tokens: ``out[i] = x[indices[i] // top_k]``; ``x`` is ``[N, d]``."""
+    return _Gather.apply(x, indices, top_k)
+
+
+class _Scatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, indices, weights, top_k: int):  # type: ignore[override]
+        n_tokens = x.shape[0] // top_k
+        idx = indices.long()
+        w = None
+        if weights is not None:
+            w = weights.reshape(-1).index_select(0, idx).float()
+        scaled = x.float() if w is None else x.float() * w[:, None]
+        out = torch.zeros((n_tokens, x.shape[1]), dtype=torch.float32, device=x.device)
+        out.index_add_(0, idx // top_k, scaled)
+        ctx.save_for_backward(x, idx, weights if weights is not None else torch.empty(0, device=x.device))
+        ctx.top_k = top_k
+        ctx.has_w = weights is not None
+        return out.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad):  # type: ignore[override]
+        x, idx, weights = ctx.saved_tensors
+        g = grad.index_select(0, idx // ctx.top_k)  # gradient of each routed copy before weighting
+        dx = g
+        dw = None
+        if ctx.has_w:
+            w = weights.reshape(-1).index_select(0, idx)
+            dx = (g.float() * w.float()[:, None]).to(x.dtype)
+            if ctx.needs_input_grad[2]:
+                per_copy = (g.float() * x.float()).sum(-1)
+                dw = torch.zeros(weights.numel(), dtype=torch.float32, device=x.device)
+                dw.index_copy_(0, idx, per_copy)
+                dw = dw.view_as(weights).to(weights.dtype)
+        return dx, None, dw, None
+
+
+def scatter(x: torch.Tensor, indices: torch.Tensor, bin_ids: Optional[torch.Tensor], weights: Optional[torch.Tensor],
+            bins: Optional[torch.Tensor], top_k: int) -> torch.Tensor:
+    """Inverse of :func:`gather`: ``out[t] = sum_j weights[t, j] * x[position of copy (t, j)]`` in fp32."""
+    return _Scatter.apply(x, indices, weights, top_k)
+
+
+def binned_gather(x: torch.Tensor, indices: torch.Tensor, bins: torch.Tensor, capacity: int, top_k: int) -> torch.Tensor:
+    """
+    Capacity-limited layout ``[num_experts, capacity, d]``: the first ``capacity`` tokens routed to each
+    expert are copied, the rest are dropped, unused slots are zero.
+    """
+    E = bins.numel()
+    pos = torch.arange(indices.numel(), device=x.device)
+    starts = torch.cat([bins.new_zeros(1), bins[:-1]]).long()
+    expert_of = torch.bucketize(pos, bins.long(), right=True).clamp(max=E - 1)
+    slot = pos - starts[expert_of]
+    keep = slot < capacity
+    flat_dst = (expert_of * capacity + slot)[keep]
+    src = (indices.long() // top_k)[keep]
+    out = x.new_zeros((E * capacity, x.shape[1]))
+    out = out.index_copy(0, flat_dst, x.index_select(0, src))
+    return out.view(E, capacity, x.shape[1])
+
+
+def binned_scatter(x: torch.Tensor, indices: torch.Tensor, weights: Optional[torch.Tensor], bins: torch.Tensor,
+                   top_k: int) -> torch.Tensor:
+    """Inverse of :func:`binned_gather` with router weights; dropped tokens contribute zero."""
+    E, capacity, d = x.shape
+    pos = torch.arange(indices.numel(), device=x.device)
+    starts = torch.cat([bins.new_zeros(1), bins[:-1]]).long()
+    expert_of = torch.bucketize(pos, bins.long(), right=True).clamp(max=E - 1)
+    slot = pos - starts[expert_of]
+    keep = slot < capacity
+    flat_src = (expert_of * capacity + slot)[keep]
+    idx = indices.long()[keep]
+    rows = x.reshape(E * capacity, d).index_select(0, flat_src).float()
+    if weights is not None:
+        rows = rows * weights.reshape(-1).index_select(0, idx).float()[:, None]
+    n_tokens = indices.numel() // top_k
+    out = torch.zeros((n_tokens, d), dtype=torch.float32, device=x.device)
+    out = out.index_add(0, idx // top_k, rows)
+    return out.to(x.dtype)
+
+
+def repeat(x: torch.Tensor, tiling) -> torch.Tensor:
+    if all(t == 1 for t in tiling):
+        return x
+    return x.repeat(*tiling)
+
+
+def sum_tensor(x: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    return x.squeeze(dim) if x.shape[dim] == 1 else x.sum(dim=dim)
+
+
+class _AllToAllAsync(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, output_split_sizes, input_split_sizes, group, async_op: bool):  # type: ignore[override]
+        out_rows = x.shape[0] if output_split_sizes is None else sum(output_split_sizes)
+        out = x.new_empty((out_rows,) + tuple(x.shape[1:]))
+        ctx.splits = (output_split_sizes, input_split_sizes)
+        ctx.group = group
+        ctx.in_shape = x.shape
+        handle = dist.all_to_all_single(out, x.contiguous(), output_split_sizes=output_split_sizes,
+                                        input_split_sizes=input_split_sizes, group=group, async_op=async_op)
+        ctx.mark_non_differentiable()
+        return out, handle
+
+    @staticmethod
+    def backward(ctx, grad, _):  # type: ignore[override]
+        out_splits, in_splits = ctx.splits
+        back = grad.new_empty(ctx.in_shape)
+        dist.all_to_all_single(back, grad.contiguous(), output_split_sizes=in_splits, input_split_sizes=out_splits,
+                               group=ctx.group)
+        return back, None, None, None, None
+
+
+def all_to_all(x: torch.Tensor, output_split_sizes=None, input_split_sizes=None, group=None, async_op: bool = False):
+    """Row exchange with variable split sizes; returns ``(output, work handle or None)``."""
+    return _AllToAllAsync.apply(x, output_split_sizes, input_split_sizes, group, async_op)
