@@ -1,0 +1,244 @@
+"""
+Headline benchmark: OLMo-2 7B pre-training throughput (tokens/s, whole job) with sharded data parallelism
+in bf16 on N B200 GPUs of one node, synthetic uniform-random token ids, random-init weights.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+``--impl reference`` runs the unmodified reference implementation installed under ``baseline/_ref`` through
+its own public API on the same config and prints the same JSON line.
+
+A *step* is one optimizer step on the named config: micro-batch 2 x 4096 tokens per GPU, 128 sequences per
+GPU per step (global batch 1024 sequences at 8 GPUs), AdamW with gradient clipping at 1.0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+PEAK_BF16_FLOPS = 2.25e15  # dense bf16 peak the reference's MFU meter uses for B200
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--model", default="olmo2_7B")
+    ap.add_argument("--layers", type=int, default=None, help="override the number of layers (debugging only)")
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--micro-batch", type=int, default=2, help="sequences per micro-batch per GPU")
+    ap.add_argument("--seqs-per-gpu", type=int, default=128, help="sequences per GPU per optimizer step")
+    ap.add_argument("--vocab-size", type=int, default=100352)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                 str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        clocks, maxc, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxc.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(maxc) if maxc else None,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, REPO)
+    from olmo_core_b200.config import DType
+    from olmo_core_b200.nn.lm_head import LMLossImplementation
+    from olmo_core_b200.nn.transformer import TransformerConfig
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.optim import AdamWConfig, OptimGroupOverride
+    from olmo_core_b200.train.train_module import TransformerDataParallelConfig, TransformerTrainModuleConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        from olmo_core_b200.distributed.utils import init_distributed
+
+        init_distributed(backend="cpu:gloo,cuda:nccl")
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+    kwargs = {}
+    if args.layers is not None:
+        kwargs["n_layers"] = args.layers
+    cfg = getattr(TransformerConfig, args.model)(vocab_size=args.vocab_size, **kwargs)
+    cfg.lm_head.loss_implementation = LMLossImplementation.fused_linear
+    model = cfg.build(init_device="meta")
+    flops_per_token = model.num_flops_per_token(args.seq_len)
+    tm = TransformerTrainModuleConfig(
+        rank_microbatch_size=args.micro_batch * args.seq_len,
+        max_sequence_length=args.seq_len,
+        optim=AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
+                          group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
+        max_grad_norm=1.0,
+        z_loss_multiplier=1e-5,
+        dp_config=TransformerDataParallelConfig(name="fsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32),
+    ).build(model, device=device)
+
+    seqs = args.seqs_per_gpu
+    tokens_per_step_global = seqs * args.seq_len * world
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_host_batches = args.warmup + 2 * args.steps
+    host_batches = [torch.randint(0, args.vocab_size, (seqs, args.seq_len), generator=gen, dtype=torch.int64).pin_memory()
+                    for _ in range(min(n_host_batches, 4))]
+
+    def step_device(ids_dev):
+        tm.zero_grads()
+        tm.train_batch({"input_ids": ids_dev})
+        tm.optim_step()
+
+    def step_e2e(ids_host):
+        tm.zero_grads()
+        tm.train_batch({"input_ids": ids_host})  # the train module copies each micro-batch to the device
+        tm.optim_step()
+        return float(tm.last_ce_loss.item()) if hasattr(tm, "last_ce_loss") else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step_device(host_batches[i % len(host_batches)].to(device, non_blocking=True))
+    _lib.check_device_status(device)
+
+    dev_inputs = [b.to(device) for b in host_batches]
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = _lib.launch_count
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step_device(dev_inputs[i % len(dev_inputs)])
+    end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = _lib.launch_count - launches0
+    ms = start.elapsed_time(end)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+    _lib.check_device_status(device)
+    del dev_inputs
+
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        h2d = d2h = 0
+        for i in range(args.steps):
+            ids = host_batches[i % len(host_batches)]
+            tm.zero_grads()
+            tm.train_batch({"input_ids": ids})
+            tm.optim_step()
+            loss = tm.latest_ce_loss.item()  # device -> host read of the step's result
+            h2d += ids.numel() * ids.element_size() * 2  # input ids and labels of every micro-batch
+            d2h += 4
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=device)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": tokens_per_step_global * args.steps / dt.item(), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps, "last_loss": loss}
+
+    value = tokens_per_step_global / (ms_per_step / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "tokens/sec (whole job), OLMo-2 7B FSDP bf16, device-timed",
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform-random token ids, random-init weights",
+            "tokens_per_sec_per_gpu": value / world,
+            "mfu": value / world * flops_per_token / PEAK_BF16_FLOPS,
+            "config": {"model": args.model, "n_layers": cfg.n_layers, "global_batch": seqs * world, "seq_len": args.seq_len,
+                       "micro_batch": args.micro_batch, "parallelism": f"fsdp{world}", "optimizer": "AdamW, clip 1.0",
+                       "l2": "working set per step (14.6 GB bf16 weights + activations) is far larger than the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "impl": "ours",
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline.run_reference import main as ref_main
+
+    ref_main(args)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        sys.path.insert(0, REPO)
+        run_reference(a)
+    else:
+        run_ours(a)

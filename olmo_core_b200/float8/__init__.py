@@ -1,0 +1,100 @@
+"""
+Float8 training configuration (API of src/olmo_core/float8/__init__.py:17-162 and src/olmo_core/float8/ao.py:54-239).
+
+The reference swaps ``nn.Linear`` for torchao's ``Float8Linear`` / ``MXLinear``. Here the same config classes
+select the in-tree scaled-fp8 linear op (``olmo_core_b200.ops.fp8``): row-wise (per-token activation scale,
+per-output-channel weight scale, power-of-two rounding optional) e4m3 quantisation of both GEMM operands with
+fp32 accumulation, bf16 output; gradients use the bf16 tcgen05 GEMM unless ``cast_grads`` is set.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from fnmatch import fnmatch
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..config import Config, StrEnum
+from ..exceptions import OLMoConfigurationError
+
+__all__ = ["Float8Config", "AOFloat8LinearConfig", "AOFloat8LinearRecipe", "AOMXLinearConfig", "refresh_float8_scales"]
+
+
+class AOFloat8LinearRecipe(StrEnum):
+    tensorwise = "tensorwise"
+    rowwise = "rowwise"
+    rowwise_with_gw_hp = "rowwise_with_gw_hp"
+
+
+@dataclass
+class AOFloat8LinearConfig(Config):
+    """Scaling granularity and options of the fp8 linear layers."""
+
+    enable_fsdp_float8_all_gather: bool = False
+    force_recompute_fp8_weight_in_bwd: bool = False
+    round_scales_to_power_of_2: bool = False
+    recipe: Optional[AOFloat8LinearRecipe] = None
+
+    @classmethod
+    def recommended(cls, **kwargs) -> "AOFloat8LinearConfig":
+        kwargs.setdefault("enable_fsdp_float8_all_gather", True)
+        kwargs.setdefault("force_recompute_fp8_weight_in_bwd", True)
+        kwargs.setdefault("round_scales_to_power_of_2", True)
+        return cls(**kwargs)
+
+
+@dataclass
+class AOMXLinearConfig(Config):
+    """Micro-scaling (32-element blocks, E8M0 scales) variant; requires compute capability 10.0."""
+
+    block_size: int = 32
+    elem_dtype: str = "float8_e4m3fn"
+    scale_rounding: str = "rceil"
+
+    @classmethod
+    def mxfp8_cublas_rceil(cls) -> "AOMXLinearConfig":
+        return cls(block_size=32, elem_dtype="float8_e4m3fn", scale_rounding="rceil")
+
+
+@dataclass
+class Float8Config(Config):
+    ao: Optional[AOFloat8LinearConfig] = None
+    ao_recipe: Optional[AOFloat8LinearRecipe] = None
+    ao_mx: Optional[AOMXLinearConfig] = None
+    modules_to_ignore: Optional[List[str]] = None
+    enabled: bool = True
+
+    def __post_init__(self):
+        if sum(x is not None for x in (self.ao, self.ao_recipe, self.ao_mx)) > 1:
+            raise OLMoConfigurationError("specify at most one of 'ao', 'ao_recipe' and 'ao_mx'")
+
+    @property
+    def recipe(self) -> AOFloat8LinearRecipe:
+        if self.ao_recipe is not None:
+            return AOFloat8LinearRecipe(self.ao_recipe)
+        if self.ao is not None and self.ao.recipe is not None:
+            return AOFloat8LinearRecipe(self.ao.recipe)
+        return AOFloat8LinearRecipe.tensorwise if self.ao is not None else AOFloat8LinearRecipe.rowwise
+
+    def apply_float8_linear(self, model: nn.Module, modules_to_ignore: Optional[List[str]] = None) -> None:
+        """Mark every eligible projection (all dims multiples of 16, not the LM head) to run in fp8."""
+        if not self.enabled:
+            return
+        from ..nn.feed_forward import Linear
+
+        ignore = set(self.modules_to_ignore or []) | set(modules_to_ignore or []) | {"lm_head.w_out"}
+        pow2 = bool(self.ao is not None and self.ao.round_scales_to_power_of_2)
+        for name, module in model.named_modules():
+            if not isinstance(module, Linear):
+                continue
+            if any(name == pat or fnmatch(name, pat) for pat in ignore):
+                continue
+            if module.in_features % 16 != 0 or module.out_features % 16 != 0:
+                continue
+            module.float8 = dict(recipe=self.recipe, pow2_scales=pow2, mx=self.ao_mx)  # type: ignore[attr-defined]
+
+
+def refresh_float8_scales(model: nn.Module) -> None:
+    """Hook after each optimizer step. Scales are computed dynamically inside the quantisation kernel, so nothing is cached."""

@@ -170,7 +170,9 @@ class DroplessMoEMLP(MoEMLPBase):
         E = self.num_local_experts
         if x.is_cuda and x.dtype == torch.bfloat16:
             return _GroupedLinear.apply(x, w, batch_sizes, trans_b)
-        wv = w.view(E, self.hidden_size, self.d_model).to(x.dtype)
+        from ...ops.param import full_param
+
+        wv = full_param(w, x.dtype).view(E, self.hidden_size, self.d_model)
         outs = []
         r = 0
         for e, n in enumerate(batch_sizes):

@@ -118,7 +118,13 @@ def dt(t: torch.Tensor) -> int:
     raise KernelError(f"unsupported dtype {t.dtype}: the sm_100a kernels take bfloat16 or float32")
 
 
+launch_count = 0
+
+
 def check(rc: int, what: str) -> None:
+    """Validate a launcher's return code; also counts launcher calls (see ``launch_count``)."""
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
 

@@ -151,7 +151,9 @@ def rms_norm(
     group = group or x.shape[-1]
     if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and group % 8 == 0 and group <= 32768:
         return _RMSNormFunction.apply(x, weight, residual, float(eps), int(group))
-    return rms_norm_reference(x, weight, eps, residual, group)
+    from .param import full_param
+
+    return rms_norm_reference(x, full_param(weight), eps, residual, group)
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -280,7 +282,9 @@ def norm_rope(
     if ok:
         return _NormRopeFunction.apply(x, weight, sin.contiguous(), cos.contiguous(), n_heads, float(eps),
                                        int(norm_mode), pos_ids, int(pos_offset))
-    return norm_rope_reference(x, weight, sin, cos, n_heads, eps, norm_mode, pos_ids, pos_offset)
+    from .param import full_param
+
+    return norm_rope_reference(x, full_param(weight), sin, cos, n_heads, eps, norm_mode, pos_ids, pos_offset)
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -371,4 +375,6 @@ def embedding(ids: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch
     out_dtype = out_dtype or (getattr(weight, "_lowp", weight)).dtype
     if weight.is_cuda and out_dtype in (torch.bfloat16, torch.float32) and weight.shape[1] % 8 == 0:
         return _EmbeddingFunction.apply(ids, weight, out_dtype)
-    return F.embedding(ids, weight).to(out_dtype)
+    from .param import full_param
+
+    return F.embedding(ids, full_param(weight)).to(out_dtype)

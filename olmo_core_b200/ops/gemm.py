@@ -161,11 +161,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     Dense projection. CUDA + (bf16 activations or an attached low-precision weight copy) runs the
     tcgen05 kernel; anything else (CPU, fp32 debugging runs) uses ``F.linear``.
     """
-    if x.is_cuda and (x.dtype == torch.bfloat16 or getattr(weight, "_lowp", None) is not None):
+    lowp = getattr(weight, "_lowp", None)
+    if x.is_cuda and ((x.dtype == torch.bfloat16 and lowp is None) or (lowp is not None and lowp.dtype == torch.bfloat16)):
         y = LinearFunction.apply(x, weight)
         if bias is not None:
             y = y + bias.to(y.dtype)
         return y
-    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    from .param import full_param
+
     b = None if bias is None else bias.to(x.dtype)
-    return torch.nn.functional.linear(x, w, b)
+    return torch.nn.functional.linear(x, full_param(weight, x.dtype), b)

@@ -198,7 +198,9 @@ def fused_linear_cross_entropy(
             scale = scale.to(device=h.device, dtype=torch.float32).reshape(())
         ce, z = _FusedLinearCEFunction.apply(h, weight, labels, scale, ignore_index, z_mult, int(chunk_rows))
         return ce, (z if z_loss_multiplier is not None else None)
-    logits = F.linear(h, weight.to(h.dtype))
+    from .param import full_param
+
+    logits = F.linear(h, full_param(weight, h.dtype))
     ce, z = cross_entropy_with_z_loss(logits, labels, ignore_index=ignore_index, reduction="sum",
                                       compute_z_loss=z_loss_multiplier is not None,
                                       z_loss_multiplier=z_mult)

@@ -1,0 +1,27 @@
+from .config import (
+    TransformerActivationCheckpointingConfig,
+    TransformerActivationCheckpointingMode,
+    TransformerContextParallelConfig,
+    TransformerDataParallelConfig,
+    TransformerDataParallelWrappingStrategy,
+    TransformerExpertParallelConfig,
+    TransformerPipelineParallelConfig,
+    TransformerTensorParallelConfig,
+    TransformerTrainModuleConfig,
+)
+from .pipeline_train_module import TransformerPipelineTrainModule
+from .train_module import TransformerTrainModule
+
+__all__ = [
+    "TransformerTrainModule",
+    "TransformerTrainModuleConfig",
+    "TransformerPipelineTrainModule",
+    "TransformerActivationCheckpointingConfig",
+    "TransformerActivationCheckpointingMode",
+    "TransformerDataParallelConfig",
+    "TransformerDataParallelWrappingStrategy",
+    "TransformerExpertParallelConfig",
+    "TransformerTensorParallelConfig",
+    "TransformerContextParallelConfig",
+    "TransformerPipelineParallelConfig",
+]

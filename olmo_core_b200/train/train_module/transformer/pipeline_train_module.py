@@ -1,0 +1,178 @@
+"""
+Train module for pipeline-parallel transformers
+(role of src/olmo_core/train/train_module/transformer/pipeline_train_module.py:68-701): the model is cut into
+stages, each rank owns one or more stages with their own optimizer, micro-batches flow through a
+``torch.distributed.pipelining`` schedule whose stage-to-stage transfers are NCCL point-to-point.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ....data.utils import get_labels
+from ....distributed.parallel import PipelineSchedule, build_world_mesh, get_dp_process_group, get_pp_mesh, get_world_mesh
+from ....distributed.utils import get_world_size
+from ....exceptions import OLMoConfigurationError
+from ....nn.functional import cross_entropy_loss
+from ....optim import OptimConfig, SkipStepOptimizer
+from ....utils import get_default_device, move_to_device
+from ...common import ReduceType
+from ..train_module import EvalBatchSpec, TrainModule
+from .common import parallelize_model
+
+log = logging.getLogger(__name__)
+
+__all__ = ["TransformerPipelineTrainModule"]
+
+
+class TransformerPipelineTrainModule(TrainModule):
+    def __init__(self, model, optim: OptimConfig, rank_microbatch_size: int, max_sequence_length: int, pp_config,
+                 compile_model: bool = False, float8_config=None, dp_config=None, tp_config=None, cp_config=None,
+                 ep_config=None, ac_config=None, z_loss_multiplier: Optional[float] = None,
+                 autocast_precision: Optional[torch.dtype] = None, max_grad_norm: Optional[float] = None,
+                 scheduler=None, device: Optional[torch.device] = None, state_dict_save_opts=None,
+                 state_dict_load_opts=None, load_key_mapping=None, label_ignore_index: int = -100):
+        super().__init__()
+        if cp_config is not None or ep_config is not None:
+            raise OLMoConfigurationError("context / expert parallelism are not supported together with pipeline parallelism")
+        self.device = device or get_default_device()
+        self.world_mesh = get_world_mesh() or build_world_mesh(dp=dp_config, tp=tp_config, pp=pp_config,
+                                                               device_type=self.device.type)
+        self.pp_config = pp_config
+        self.pp_mesh = get_pp_mesh(self.world_mesh)
+        self.rank_microbatch_size = rank_microbatch_size
+        self.max_sequence_length = max_sequence_length
+        self.z_loss_multiplier = z_loss_multiplier
+        self.max_grad_norm = max_grad_norm
+        self.scheduler = scheduler
+        self.label_ignore_index = label_ignore_index
+        stages, parts = pp_config.split_model(model, pp_mesh=self.pp_mesh, device=self.device)
+        self.model_parts: List[Any] = []
+        for i, part in enumerate(parts):
+            self.model_parts.append(parallelize_model(
+                part, world_mesh=self.world_mesh, device=self.device, max_sequence_length=max_sequence_length,
+                rank_microbatch_size=rank_microbatch_size, compile_model=compile_model, float8_config=float8_config,
+                dp_config=dp_config, tp_config=tp_config, ac_config=ac_config, pp_enabled=True))
+        self._stages = stages
+        self.optimizers = [optim.build(p, strict=False) for p in self.model_parts]
+        self._schedule: Optional[PipelineSchedule] = None
+        self._batch_tokens_for_loss: Optional[torch.Tensor] = None
+
+    @property
+    def dp_process_group(self):
+        return get_dp_process_group(self.world_mesh)
+
+    @property
+    def eval_batch_spec(self) -> EvalBatchSpec:
+        return EvalBatchSpec(self.rank_microbatch_size, max_sequence_length=self.max_sequence_length)
+
+    def _loss_fn(self, logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        ce, z = cross_entropy_loss(logits.view(-1, logits.size(-1)), labels.view(-1), ignore_index=self.label_ignore_index,
+                                   reduction="sum", compute_z_loss=self.z_loss_multiplier is not None,
+                                   z_loss_multiplier=self.z_loss_multiplier or 1e-4)
+        loss = ce if z is None else ce + z
+        return loss / self._batch_tokens_for_loss
+
+    def _get_schedule(self, num_microbatches: int) -> PipelineSchedule:
+        if self._schedule is None or self._schedule.num_microbatches != num_microbatches:
+            self._schedule = PipelineSchedule(model_parts=self.model_parts, stages=self._stages, pp_mesh=self.pp_mesh,
+                                              schedule_name=self.pp_config.schedule, loss_fn=self._loss_fn,
+                                              num_microbatches=num_microbatches)
+        return self._schedule
+
+    def state_dict(self, *, optim: Optional[bool] = None) -> Dict[str, Any]:
+        sd: Dict[str, Any] = {"model": {}, "optim": {}}
+        for part, opt in zip(self.model_parts, self.optimizers):
+            sd["model"].update({n: p.data for n, p in part.named_parameters()})
+            if optim is not False:
+                names = {id(p): n for n, p in part.named_parameters()}
+                for g in opt.param_groups:
+                    for p in g["params"]:
+                        for f, v in opt.state.get(p, {}).items():
+                            sd["optim"][f"state.{names[id(p)]}.{f}"] = v
+        if optim is False:
+            sd.pop("optim")
+        return sd
+
+    def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
+        with torch.no_grad():
+            for part in self.model_parts:
+                for n, p in part.named_parameters():
+                    if n in state_dict["model"]:
+                        p.data.copy_(state_dict["model"][n])
+                rt = getattr(part, "_sharding_runtime", None)
+                if rt is not None:
+                    rt.sync_lowp()
+
+    def train_batch(self, batch: Dict[str, Any], dry_run: bool = False) -> None:
+        for p in self.model_parts:
+            p.train()
+        if "labels" not in batch:
+            batch["labels"] = get_labels(batch, self.label_ignore_index)
+        self._batch_tokens_for_loss = move_to_device((batch["labels"] != self.label_ignore_index).sum(), self.device)
+        seq_len = batch["input_ids"].shape[1]
+        n_mb = max(1, batch["input_ids"].shape[0] // max(1, self.rank_microbatch_size // seq_len))
+        sched = self._get_schedule(n_mb)
+        input_ids = move_to_device(batch["input_ids"], self.device)
+        labels = move_to_device(batch["labels"], self.device)
+        _, loss = sched.step(input_ids, target=labels)
+        if dry_run:
+            return
+        # The loss lives on the rank with the last stage: average over DP there, then hand it down the pipe.
+        value = loss.detach() if loss is not None else torch.zeros((), device=self.device)
+        pp_group = self.pp_mesh.get_group()
+        dist.all_reduce(value, group=pp_group)  # only the last-stage rank contributes a non-zero value
+        self.record_ce_loss(value, ReduceType.mean)
+        for opt in self.optimizers:
+            if isinstance(opt, SkipStepOptimizer):
+                opt.latest_loss = value
+
+    def eval_batch(self, batch: Dict[str, Any], labels: Optional[Any] = None) -> Any:
+        raise NotImplementedError("evaluation is not supported with pipeline parallelism")
+
+    def optim_step(self) -> None:
+        norms_sq = torch.zeros((), device=self.device)
+        for part in self.model_parts:
+            rt = getattr(part, "_sharding_runtime", None)
+            if rt is not None:
+                rt.reduce_gradients()
+                norms_sq += rt.grad_norm_sq()
+            else:
+                for p in part.parameters():
+                    if p.grad is not None:
+                        norms_sq += p.grad.float().pow(2).sum()
+        dist.all_reduce(norms_sq, group=self.pp_mesh.get_group())
+        grad_norm = norms_sq.sqrt()
+        self.record_metric("total grad norm", grad_norm, namespace="optim")
+        coef = None
+        if self.max_grad_norm is not None:
+            coef = torch.clamp(self.max_grad_norm / (grad_norm + 1e-6), max=1.0)
+        for opt in self.optimizers:
+            if isinstance(opt, SkipStepOptimizer):
+                opt.latest_grad_norm = grad_norm
+            if coef is not None and hasattr(opt, "grad_scale"):
+                opt.grad_scale = coef
+            if self.scheduler is not None:
+                for group in opt.param_groups:
+                    self.scheduler.set_lr(group, self.trainer)
+            opt.step()
+        for part in self.model_parts:
+            part.post_optim_step()
+
+    def zero_grads(self) -> None:
+        for part, opt in zip(self.model_parts, self.optimizers):
+            rt = getattr(part, "_sharding_runtime", None)
+            if rt is not None:
+                rt.zero_grad()
+            opt.zero_grad(set_to_none=True)
+
+    def num_flops_per_token(self, seq_len: int) -> Optional[int]:
+        return sum(p.num_flops_per_token(seq_len) for p in self.model_parts)
+
+    def global_num_flops_in_batch(self, batch: Dict[str, Any]) -> Optional[int]:
+        # every PP rank holds a slice of the model; the per-device share is accounted by the speed monitor
+        return self.num_flops_per_token(batch["input_ids"].shape[1]) * self.trainer.data_loader.global_num_tokens_in_batch(batch)
