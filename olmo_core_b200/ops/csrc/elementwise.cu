@@ -928,3 +928,89 @@ extern "C" int ocb_cast_f32_to_bf16(const float* x, void* y, long long n, cudaSt
   cast_f32_bf16_kernel<<<grid, 256, 0, stream>>>(x, static_cast<bf16*>(y), n);
   return OCB_CHECK_LAUNCH();
 }
+
+// ---- RMSNorm backward without any allocation (declared and documented in ocb_static_scratch.h) ------
+#include <mutex>
+
+#include "ocb_static_scratch.h"
+
+// Weight-gradient partials of one call: one row per block of the persistent backward grid. Shared by all
+// calls on the device, which is why the launcher clears the rows it is about to use on the caller's stream.
+static __device__ __align__(256) float g_static_norm_partials[ocb::kNormBwdBlocks * OCB_STATIC_SCRATCH_MAX_GROUP];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+float* g_static_partials_ptr[kStaticMaxDevices] = {};
+std::mutex g_static_partials_mutex;
+
+// Device address of the scratch array on the current device; resolved once per device.
+int static_partials(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return OCB_ERR_STATIC_SCRATCH_SETUP;
+  std::lock_guard<std::mutex> lock(g_static_partials_mutex);
+  if (g_static_partials_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_norm_partials) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();  // leave no sticky error behind for the caller's next launch check
+      return OCB_ERR_STATIC_SCRATCH_SETUP;
+    }
+    g_static_partials_ptr[dev] = p;
+  }
+  *out = g_static_partials_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int ocb_rmsnorm_bwd_static_max_group() { return OCB_STATIC_SCRATCH_MAX_GROUP; }
+
+extern "C" const char* ocb_rmsnorm_bwd_static_strerror(int code) {
+  switch (code) {
+    case 0: return "success";
+    case -1: return "invalid argument: group must divide cols, be a multiple of 8 and at most 8192";
+    case -4: return "CUDA launch or memset failed";
+    case OCB_ERR_STATIC_SCRATCH_TOO_SMALL:
+      return "group exceeds OCB_STATIC_SCRATCH_MAX_GROUP (4096): the built-in scratch array is too small; "
+             "use ocb_rmsnorm_bwd with a caller-provided partials buffer";
+    case OCB_ERR_STATIC_SCRATCH_SETUP:
+      return "could not resolve the device address of the built-in scratch array on the current device";
+    default: return "unknown error code";
+  }
+}
+
+extern "C" int ocb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                      void* dw, int dw_accumulate, int rows, int cols, int group, long long lddy,
+                                      long long ldx, long long lddx, int act_dtype, int w_dtype, int dw_dtype,
+                                      cudaStream_t stream) {
+  using namespace ocb;
+  if (rows <= 0) return 0;
+  if (group <= 0 || cols % group != 0 || group % 8 != 0) return -1;
+  if (dw != nullptr && group > OCB_STATIC_SCRATCH_MAX_GROUP) return OCB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  const int gpr = cols / group;
+  const long long n_groups = static_cast<long long>(rows) * gpr;
+  const int tpg = pick_tpg(group);
+  if ((group / 8 + tpg - 1) / tpg > kMaxVec) return -1;
+  const int gpb = kNormThreads / tpg;
+  const long long want = (n_groups + gpb - 1) / gpb;
+  const int grid = static_cast<int>(want < kNormBwdBlocks ? want : kNormBwdBlocks);
+  float* partial = nullptr;
+  if (dw != nullptr) {
+    const int rc = static_partials(&partial);
+    if (rc != 0) return rc;
+    // Only the `grid` rows this call accumulates into (and later folds) have to start at zero.
+    if (cudaMemsetAsync(partial, 0, sizeof(float) * static_cast<size_t>(grid) * group, stream) != cudaSuccess) return -4;
+  }
+  OCB_DISPATCH_TW(act_dtype, w_dtype, {
+    rmsnorm_bwd_kernel<T, W><<<grid, kNormThreads, 0, stream>>>(
+        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+        partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+  })
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (dw != nullptr) {
+    const int threads = 256, rgrid = (group + threads - 1) / threads;
+    if (dw_dtype == OCB_F32)
+      reduce_partials_kernel<float><<<rgrid, threads, 0, stream>>>(partial, static_cast<float*>(dw), grid, group, dw_accumulate);
+    else
+      reduce_partials_kernel<bf16><<<rgrid, threads, 0, stream>>>(partial, static_cast<bf16*>(dw), grid, group, dw_accumulate);
+  }
+  return OCB_CHECK_LAUNCH();
+}
