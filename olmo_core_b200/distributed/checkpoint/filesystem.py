@@ -43,7 +43,7 @@ from torch.futures import Future
 
 from ...aliases import PathOrStr
 from ...exceptions import OLMoCheckpointError
-from ...io import file_exists, get_bytes_range, init_client, is_url, join_path, normalize_path, upload
+from ...io import file_exists, get_bytes_range, init_client, is_url, join_path, normalize_path, read_bytes, upload
 from ...utils import generate_uuid, get_default_thread_count, get_element_size
 from ..utils import do_n_at_a_time
 
@@ -241,8 +241,6 @@ class RemoteFileSystemReader(dist_cp.StorageReader):
         if self.pre_download and is_url(self.path):
             local = self._local_cache.get(info.relative_path)
             if local is None:
-                from ...io import read_bytes
-
                 d = Path(self.work_dir or tempfile.mkdtemp())
                 d.mkdir(parents=True, exist_ok=True)
                 local = str(d / info.relative_path)
@@ -277,8 +275,6 @@ class RemoteFileSystemReader(dist_cp.StorageReader):
     def read_metadata(self) -> Metadata:
         if self._metadata is None:
             try:
-                from ...io import read_bytes
-
                 self._metadata = _CompatUnpickler(io.BytesIO(read_bytes(f"{self.path}/.metadata"))).load()
             except FileNotFoundError as e:
                 raise FileNotFoundError(f"'{self.path}' is not a distributed checkpoint folder (no .metadata)") from e
