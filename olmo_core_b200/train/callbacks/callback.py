@@ -49,6 +49,13 @@ class Callback:
     def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
         del state_dict
 
+    def block_ephemeral_checkpoints(self) -> None:
+        """Hold back ephemeral checkpoints for as long as at least one callback asks for it."""
+        self.trainer._blocking_ephemeral_checkpoints.add(self.trainer.get_callback_name(self))
+
+    def unblock_ephemeral_checkpoints(self) -> None:
+        self.trainer._blocking_ephemeral_checkpoints.discard(self.trainer.get_callback_name(self))
+
     # -- hooks ---------------------------------------------------------------------------------------
     def post_attach(self) -> None:
         pass
