@@ -143,12 +143,6 @@ def run_ours(args):
         tm.train_batch({"input_ids": ids_dev})
         tm.optim_step()
 
-    def step_e2e(ids_host):
-        tm.zero_grads()
-        tm.train_batch({"input_ids": ids_host})  # the train module copies each micro-batch to the device
-        tm.optim_step()
-        return float(tm.last_ce_loss.item()) if hasattr(tm, "last_ce_loss") else None
-
     def barrier():
         if world > 1:
             dist.barrier()
@@ -202,7 +196,7 @@ def run_ours(args):
     value = tokens_per_step_global / (ms_per_step / 1e3)
     if rank == 0:
         out = {
-            "metric": "tokens/sec (whole job), OLMo-2 7B FSDP bf16, device-timed",
+            "metric": "tokens/sec/GPU + MFU, OLMo-2 7B FSDP bf16 at 1/2/4/8 B200, device-timed (value = whole-job tokens/s)",
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
@@ -230,15 +224,23 @@ def run_ours(args):
 
 
 def run_reference(args):
-    from baseline.run_reference import main as ref_main
-
-    ref_main(args)
+    """Replace this process with ``baseline/run_reference.py`` running against ``baseline/_ref`` (never our package)."""
+    ref = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "olmo_core")):
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing: the offline install of the "
+                              "reference has not been done on this machine"}), flush=True)
+        return
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([os.path.join(REPO, "baseline", "shims"), ref])
+    script = os.path.join(REPO, "baseline", "run_reference.py")
+    os.chdir(os.path.join(REPO, "baseline"))  # keep the repo root (and its 'olmo_core' alias package) off sys.path
+    os.execve(sys.executable, [sys.executable, script] + sys.argv[1:], env)
 
 
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
-        sys.path.insert(0, REPO)
         run_reference(a)
     else:
         run_ours(a)
