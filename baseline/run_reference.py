@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--vocab-size", type=int, default=100352)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-compile", action="store_true", help="debugging only: skip torch.compile")
+    ap.add_argument("--ac", choices=["none", "full"], default="none",
+                    help="activation checkpointing; 'full' is selected automatically when one GPU runs out of memory")
     return ap.parse_args()
 
 
@@ -130,6 +132,8 @@ def main() -> None:
         from olmo_core.train import Duration, TrainerConfig, prepare_training_environment, teardown_training_environment
         from olmo_core.train.callbacks import Callback, CheckpointerCallback
         from olmo_core.train.train_module import (
+            TransformerActivationCheckpointingConfig,
+            TransformerActivationCheckpointingMode,
             TransformerDataParallelConfig,
             TransformerDataParallelWrappingStrategy,
             TransformerTrainModuleConfig,
@@ -167,6 +171,8 @@ def main() -> None:
         dp_config=TransformerDataParallelConfig(name=DataParallelType.fsdp, param_dtype=DType.bfloat16,
                                                 reduce_dtype=DType.float32,
                                                 wrapping_strategy=TransformerDataParallelWrappingStrategy.blocks),
+        ac_config=(TransformerActivationCheckpointingConfig(mode=TransformerActivationCheckpointingMode.full)
+                   if args.ac == "full" else None),
         z_loss_multiplier=1e-5,
         max_grad_norm=1.0,
         scheduler=CosWithWarmup(warmup_steps=2000),
@@ -249,6 +255,13 @@ def main() -> None:
     try:
         trainer.fit()
     except torch.OutOfMemoryError as e:
+        if world == 1 and args.ac == "none":
+            # fp32 parameters, gradients and Adam moments of 7.3 B parameters take 117 GB unsharded; with the activations
+            # of 32 layers that exceeds one GPU. Start over in a fresh process with the reference's own full activation
+            # checkpointing, which is how the reference fits such a run.
+            print("reference ran out of memory on one GPU; retrying with full activation checkpointing", flush=True)
+            sys.stdout.flush()
+            os.execv(sys.executable, [sys.executable] + sys.argv + ["--ac", "full"])
         _unavailable(f"reference ran out of device memory on this config: {e}")
         return
 
@@ -267,7 +280,7 @@ def main() -> None:
             "config": {"model": args.model, "n_layers": model_config.n_layers, "global_batch": seqs * world,
                        "seq_len": seq_len, "micro_batch": args.micro_batch, "parallelism": f"fsdp{world}",
                        "optimizer": "SkipStepAdamW, clip 1.0", "attention_backend": str(backend),
-                       "compile_model": not args.no_compile,
+                       "compile_model": not args.no_compile, "activation_checkpointing": args.ac,
                        "l2": "working set per step is far larger than the 126 MB L2"},
             "clocks": result["clocks"],
             "e2e": {"value": tokens_per_step * args.steps / (ms[1].item() / 1e3), "unit": "tokens/s",

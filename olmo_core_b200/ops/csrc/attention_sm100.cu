@@ -1,0 +1,323 @@
+// Flash attention for sm_100a: tcgen05 tensor-core tiles with TMEM accumulators, operands staged by TMA.
+//
+// Semantics follow the reference's attention (src/olmo_core/nn/attention/__init__.py:560-640 with the flash
+// backends of src/olmo_core/nn/attention/backend.py): softmax(scale * Q K^T + causal mask) V over
+// [batch, seq, heads, head_dim] tensors, grouped-query heads, fp32 softmax statistics, bf16 in/out, and the
+// per-row log-sum-exp kept for the backward pass.
+//
+// Forward design (head_dim 128, 128-row tiles):
+//   * one CTA per (128 query rows, head, batch); 192 threads = TMA warp + MMA warp + 4 softmax warps (one query
+//     row per thread = one TMEM lane per thread, so no cross-thread reductions);
+//   * S = Q K^T is a 128x128x128 tcgen05.mma from shared memory into TMEM columns [0,128); the softmax warps read
+//     their rows with tcgen05.ld, and write P = exp2(S*scale - m) as packed bf16 back into TMEM columns [0,64)
+//     (over the part of S already consumed), from where it is the A operand of the O += P V tcgen05.mma
+//     (accumulator in TMEM columns [128,256)) -- P never touches shared memory;
+//   * the running maximum is only refreshed when it grows by more than 2^8 (a stale maximum keeps exp2 within range
+//     and makes rescaling O, a TMEM read-modify-write, rare);
+//   * K and V tiles are single-buffered; overlap comes from two CTAs per SM (96 KB shared memory and 256 TMEM
+//     columns each), so one CTA's softmax runs under the other's tensor-core work.
+// Every wait is bounded (see common.cuh); a kernel that gives up sets the status word and frees its TMEM.
+
+#include "common.cuh"
+#include "ocb_api.h"
+#include "tmap.h"
+
+namespace ocb {
+
+constexpr int AT_TILE = 128;                       // rows of a Q tile and of a K/V tile
+constexpr int AT_D = 128;                          // head dim
+constexpr int AT_TILE_BYTES = AT_TILE * AT_D * 2;  // 32 KB
+constexpr int AT_HALF_BYTES = AT_TILE_BYTES / 2;   // one [128 x 64] TMA box
+constexpr int AT_THREADS = 192;
+constexpr int AT_FWD_SMEM = 3 * AT_TILE_BYTES + 1024 + 256;
+constexpr uint32_t AT_FWD_TMEM_COLS = 256;
+constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct AttnFwdParams {
+  __nv_bfloat16* out;
+  float* lse;
+  long long ld_out;  // elements between consecutive tokens of `out`
+  int T, H, Hkv;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  int* status;
+};
+
+// K-major operand tile [128 rows x 128 cols] held as two [128 x 64] boxes: descriptor of k-step `k` (16 columns).
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_addr, int k) {
+  return make_smem_desc_sw128(tile_addr + (k >> 2) * AT_HALF_BYTES + (k & 3) * 32, 16, 1024);
+}
+// MN-major B operand (V: [kv rows x d cols], d contiguous): k-step `k` covers kv rows [16k, 16k+16).
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_addr, int k) {
+  return make_smem_desc_sw128(tile_addr + k * 2048, AT_HALF_BYTES, 1024);
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                const __grid_constant__ CUtensorMap tma_v, const AttnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + AT_TILE_BYTES;
+  uint8_t* sV = smem + 2 * AT_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * AT_TILE_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int n_kv = p.causal ? qt + 1 : p.T / AT_TILE;
+  const int q_row0 = b * p.T + qt * AT_TILE;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tma_q);
+    tma_prefetch_desc(&tma_k);
+    tma_prefetch_desc(&tma_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_FWD_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;        // fp32 scores, columns [0,128)
+  const uint32_t tmem_P = tmem_base;        // bf16 probabilities packed two per column, columns [0,64)
+  const uint32_t tmem_O = tmem_base + 128;  // fp32 output accumulator, columns [128,256)
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, AT_TILE_BYTES);
+      tma_load_2d(sQ, &tma_q, q_full, h * AT_D, q_row0);
+      tma_load_2d(sQ + AT_HALF_BYTES, &tma_q, q_full, h * AT_D + 64, q_row0);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t ph = j & 1;
+        const int kv_row0 = b * p.T + j * AT_TILE;
+        ok = mbar_wait_bounded(k_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(k_full, AT_TILE_BYTES);
+        tma_load_2d(sK, &tma_k, k_full, hk * AT_D, kv_row0);
+        tma_load_2d(sK + AT_HALF_BYTES, &tma_k, k_full, hk * AT_D + 64, kv_row0);
+        ok = mbar_wait_bounded(v_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(v_full, AT_TILE_BYTES);
+        tma_load_2d(sV, &tma_v, v_full, hk * AT_D, kv_row0);
+        tma_load_2d(sV + AT_HALF_BYTES, &tma_v, v_full, hk * AT_D + 64, kv_row0);
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before shared memory goes away
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(AT_TILE, AT_TILE, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(AT_TILE, AT_D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t ph = j & 1;
+        ok = mbar_wait_bounded(k_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        if (j > 0) {
+          // P of the previous tile lives where S is about to be written: wait until O += P V has read it.
+          ok = mbar_wait_bounded(o_full, ph ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
+          if (!ok) break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k) umma_f16_ss(tmem_S, kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_qk, k != 0);
+        umma_commit(k_empty);
+        umma_commit(s_full);
+        ok = mbar_wait_bounded(p_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        ok = mbar_wait_bounded(v_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < AT_TILE / 16; ++k)
+          umma_f16_ts(tmem_O, tmem_P + k * 8, mnmajor_desc(aV, k), idesc_pv, (j | k) != 0);
+        umma_commit(v_empty);
+        umma_commit(o_full);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------------------- softmax + epilogue
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // query row within the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    float m_ref = -INFINITY;  // reference maximum (log2 units) the stored probabilities are relative to
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const uint32_t ph = j & 1;
+      ok = mbar_wait_bounded(s_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && j == qt;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(r[i]) * p.scale_log2;
+          mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : s);
+        }
+      }
+      const bool grow = mx > m_ref + AT_RESCALE_THRESHOLD;  // also true for the first tile (m_ref = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : m_ref;
+        const float alpha = grow ? exp2f(m_ref - m_new) : 1.f;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_O + lane_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tmem_O + lane_addr + c * 32, r);
+          }
+        }
+        l *= alpha;
+        m_ref = m_new;
+      }
+      // pass 2: probabilities relative to m_ref, written as bf16 pairs over the consumed part of S
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_ref));
+          float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_ref));
+          if (diag) {
+            if (c * 32 + 2 * i > row) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+          }
+          sum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(tmem_P + lane_addr + c * 16, pk);
+      }
+      l += sum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok) {
+      ok = mbar_wait_bounded(o_full, (n_kv - 1) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      const long long token = static_cast<long long>(q_row0) + row;
+      __nv_bfloat16* dst = p.out + token * p.ld_out + h * AT_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_O + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * inv_l, __uint_as_float(r[8 * v + 1]) * inv_l);
+          o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * inv_l, __uint_as_float(r[8 * v + 3]) * inv_l);
+          o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * inv_l, __uint_as_float(r[8 * v + 5]) * inv_l);
+          o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * inv_l, __uint_as_float(r[8 * v + 7]) * inv_l);
+          reinterpret_cast<uint4*>(dst + c * 32)[v] = o;
+        }
+      }
+      // natural-log log-sum-exp of the scaled scores
+      p.lse[(static_cast<long long>(b) * p.H + h) * p.T + qt * AT_TILE + row] = m_ref * 0.6931471805599453f + logf(l);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, AT_FWD_TMEM_COLS);
+  }
+}
+
+static bool make_qkv_map(CUtensorMap* map, const void* ptr, long long rows, int heads, long long ld) {
+  uint64_t dims[2] = {static_cast<uint64_t>(heads) * AT_D, static_cast<uint64_t>(rows)};
+  uint64_t str[1] = {static_cast<uint64_t>(ld) * 2};
+  uint32_t box[2] = {64, AT_TILE};
+  return get_tensor_map(map, ptr, 2, dims, str, box, 2);
+}
+
+}  // namespace ocb
+
+using namespace ocb;
+
+// q,out: [B, Tq, H, D]; k,v: [B, Tk, Hkv, D]; bf16, D contiguous, heads contiguous (stride D), tokens `ld*` elements
+// apart and batches Tq*ld (Tk*ld) apart. lse: [B, H, Tq] fp32. Supported: D == 128, Tq == Tk, T % 128 == 0, no
+// sliding window, no document boundaries; anything else returns -5 so that the caller can take another path.
+extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+                                 int B, int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
+                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  if (D != AT_D || Tq != Tk || (Tq % AT_TILE) != 0 || window > 0 || cu_seqlens != nullptr || Hkv <= 0 || (H % Hkv) != 0)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  CUtensorMap mq, mk, mv;
+  if (!make_qkv_map(&mq, q, static_cast<long long>(B) * Tq, H, ldq)) return -1001;
+  if (!make_qkv_map(&mk, k, static_cast<long long>(B) * Tk, Hkv, ldk)) return -1002;
+  if (!make_qkv_map(&mv, v, static_cast<long long>(B) * Tk, Hkv, ldv)) return -1003;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  AttnFwdParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.ld_out = ldo;
+  p.T = Tq;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = status;
+  dim3 grid(Tq / AT_TILE, H, B);
+  attn_fwd_kernel<<<grid, AT_THREADS, AT_FWD_SMEM, stream>>>(mq, mk, mv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
