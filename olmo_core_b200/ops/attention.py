@@ -9,9 +9,10 @@ reference's attention backends (src/olmo_core/nn/attention/backend.py:299-444):
 * ``window_size = w``: query ``i`` additionally only sees the last ``w`` keys ``[i-w+1, i]``,
 * ``cu_seqlens``: documents packed along the (flattened) token dimension attend only within themselves.
 
-On CUDA with bf16 inputs and ``head_dim`` in {64, 128} the in-tree flash-attention kernels
-(``csrc/attention_sm100.cu``) are used for forward and backward. ``attention_reference`` is the plain
-fp32 restatement used on CPU and as the oracle in tests.
+On CUDA with bf16 inputs, ``head_dim`` 128, equal query / key lengths that are a multiple of 128, and neither a
+sliding window nor document boundaries, the in-tree tcgen05 flash-attention kernels (``csrc/attention_sm100.cu``,
+``csrc/attention_bwd_sm100.cu``) run forward and backward. Other cases take the masked PyTorch path.
+``attention_reference`` is the plain fp32 restatement used on CPU and as the oracle in tests.
 """
 
 from __future__ import annotations
@@ -153,12 +154,13 @@ class _FlashAttention(torch.autograd.Function):
         B, Tq, H, D = q.shape
         Tk, Hkv = k.shape[1], k.shape[2]
         dout = dout.contiguous()
-        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         dk = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
         dv = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
+        delta = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
         rc = _lib.lib().ocb_attention_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr() if has_cu else None, None,
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr() if has_cu else None, delta.data_ptr(),
             B, Tq, Tk, H, Hkv, D, _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(out), scale,
             1 if causal else 0, window, _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
         )
@@ -207,9 +209,13 @@ def attention(
         and q.dtype == torch.bfloat16
         and k.dtype == torch.bfloat16
         and v.dtype == torch.bfloat16
-        and D in (64, 128)
+        and D == 128
         and dropout_p == 0.0
+        and cu_seqlens is None
         and cu_seqlens_k is None
+        and not window_size
+        and q.shape[1] == k.shape[1]
+        and q.shape[1] % 128 == 0
         and has_flash_kernel()
     )
     if use_flash:

@@ -1,0 +1,508 @@
+// Flash attention backward for sm_100a (tcgen05 / TMEM / TMA), head_dim 128, 128-row tiles.
+//
+// Math (per head; P = softmax(scale * Q K^T + mask), O = P V, delta_i = sum_d O_id dO_id):
+//     dV = P^T dO            dP = dO V^T            dS = P o (dP - delta) * scale
+//     dK = dS^T Q            dQ = dS K
+// as in the reference's flash backends (src/olmo_core/nn/attention/backend.py) -- P is recomputed from Q, K and the
+// saved log-sum-exp instead of being stored.
+//
+// Three launches, none of which needs atomics or a cross-CTA reduction:
+//   1. attn_delta_kernel : delta = rowsum(O o dO)                                  (memory bound)
+//   2. attn_dkdv_kernel  : one CTA per (K/V tile, kv head, batch) walks the query tiles (and the query heads of its
+//      group); S and dP are tcgen05.mma results in TMEM, the softmax warps turn them into bf16 P and dS tiles in
+//      shared memory laid out so that the SAME tile serves as a K-major and as an MN-major UMMA operand, and
+//      dV += P^T dO, dK += dS^T Q accumulate in TMEM (4 x 128 columns = all of TMEM);
+//   3. attn_dq_kernel    : one CTA per (query tile, head, batch) walks the K/V tiles; dS goes back to TMEM as packed
+//      bf16 and is the A operand of dQ += dS K straight from tensor memory.
+// Recomputing S and dP in both kernels costs two extra tile products (7 instead of 5) and buys independence.
+
+#include "common.cuh"
+#include "ocb_api.h"
+#include "tmap.h"
+
+namespace ocb {
+namespace {
+
+constexpr int BT = 128;                    // tile rows (queries and keys)
+constexpr int BD = 128;                    // head dim
+constexpr int TILE_BYTES = BT * BD * 2;    // 32 KB
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int BWD_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnBwdParams {
+  const float* lse;    // [B, H, T] natural log
+  const float* delta;  // [B, H, T]
+  __nv_bfloat16* dq;   // [B, T, H, D]
+  __nv_bfloat16* dk;   // [B, T, Hkv, D]
+  __nv_bfloat16* dv;
+  long long ld_dq, ld_dk, ld_dv;
+  int T, H, Hkv;
+  float scale, scale_log2;
+  int causal;
+  int* status;
+};
+
+// [128 rows x 128 cols] bf16 tile stored as two [128 x 64] boxes with 128-byte swizzle.
+// K-major view (contraction over the columns): k-step k = columns [16k, 16k+16).
+__device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
+  return make_smem_desc_sw128(tile + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
+}
+// MN-major view (contraction over the rows): k-step k = rows [16k, 16k+16).
+__device__ __forceinline__ uint64_t desc_mn(uint32_t tile, int k) {
+  return make_smem_desc_sw128(tile + k * 2048, HALF_BYTES, 1024);
+}
+
+// Store 32 consecutive bf16 pairs... i.e. columns [32c, 32c+32) of row `row` (16 packed words) into a swizzled tile.
+__device__ __forceinline__ void store_tile_row_chunk(uint8_t* tile, int row, int c, const uint32_t (&w)[16]) {
+  uint8_t* base = tile + (c >> 1) * HALF_BYTES + row * 128;
+  const int slot0 = (c & 1) * 4;  // 16-byte slot of the first 8 columns of this chunk inside the 128-byte row
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const int slot = (slot0 + v) ^ (row & 7);
+    *reinterpret_cast<uint4*>(base + slot * 16) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+  }
+}
+
+__device__ __forceinline__ void store_acc_row(__nv_bfloat16* dst, uint32_t tmem_addr) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(tmem_addr + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint4 o;
+      o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+      o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+      o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+      o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+      reinterpret_cast<uint4*>(dst + c * 32)[v] = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 1. delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]      (one warp per (token, head))
+// ------------------------------------------------------------------------------------------------------------
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, long long rows, int T, int H, long long ld_o, long long ld_do) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= rows * H) return;
+  const long long token = w / H;
+  const int h = static_cast<int>(w % H);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + token * ld_o + h * BD + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(dout + token * ld_do + h * BD + lane * 4);
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
+  float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  s = warp_sum(s);
+  if (lane == 0) delta[(token / T * H + h) * T + token % T] = s;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 2. dK, dV
+// ------------------------------------------------------------------------------------------------------------
+constexpr int DKDV_SMEM = 6 * TILE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                 const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do,
+                 const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + 1 * TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;
+  uint8_t* sdO = smem + 3 * TILE_BYTES;
+  uint8_t* sP = smem + 4 * TILE_BYTES;   // [q rows x kv cols]
+  uint8_t* sdS = smem + 5 * TILE_BYTES;  // [q rows x kv cols]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;   // S and dP are in TMEM
+  uint64_t* pds_full = bars + 4;   // P and dS tiles are in shared memory (4 warp arrivals)
+  uint64_t* pds_empty = bars + 5;  // the MMAs that read P / dS have finished
+  uint64_t* acc_full = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jt = blockIdx.x;  // K/V tile
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int n_q = p.T / BT;
+  const int i_first = p.causal ? jt : 0;
+  const int iters = (n_q - i_first) * group;  // (query head of the group, query tile) pairs
+  const int kv_row0 = b * p.T + jt * BT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_empty, 1);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_2d(sK, &tma_k, kv_full, hk * BD, kv_row0);
+      tma_load_2d(sK + HALF_BYTES, &tma_k, kv_full, hk * BD + 64, kv_row0);
+      tma_load_2d(sV, &tma_v, kv_full, hk * BD, kv_row0);
+      tma_load_2d(sV + HALF_BYTES, &tma_v, kv_full, hk * BD + 64, kv_row0);
+      bool ok = true;
+      for (int it = 0; it < iters && ok; ++it) {
+        const int h = hk * group + it / (n_q - i_first);
+        const int q_row0 = b * p.T + (i_first + it % (n_q - i_first)) * BT;
+        ok = mbar_wait_bounded(qdo_empty, (it & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+        tma_load_2d(sQ, &tma_q, qdo_full, h * BD, q_row0);
+        tma_load_2d(sQ + HALF_BYTES, &tma_q, qdo_full, h * BD + 64, q_row0);
+        tma_load_2d(sdO, &tma_do, qdo_full, h * BD, q_row0);
+        tma_load_2d(sdO + HALF_BYTES, &tma_do, qdo_full, h * BD + 64, q_row0);
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);  // both operands contracted over their columns
+      constexpr uint32_t idesc_mm = make_idesc_bf16(BT, BD, 1, 1);  // both operands contracted over their rows
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      for (int it = 0; it < iters && ok; ++it) {
+        const uint32_t ph = it & 1;
+        ok = mbar_wait_bounded(qdo_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q K^T and dP = dO V^T (S / dP of the previous pair were consumed before P / dS were published)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
+        umma_commit(sdp_full);
+        ok = mbar_wait_bounded(pds_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+        // dV += P^T dO and dK += dS^T Q
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdV, desc_mn(aP, k), desc_mn(adO, k), idesc_mm, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdK, desc_mn(adS, k), desc_mn(aQ, k), idesc_mm, (it | k) != 0);
+        umma_commit(qdo_empty);
+        umma_commit(pds_empty);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // query row within the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t ph = it & 1;
+      const int h = hk * group + it / (n_q - i_first);
+      const int qi = i_first + it % (n_q - i_first);
+      const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qi * BT + row;
+      const float lse2 = p.lse[stat] * LOG2E;
+      const float dl = p.delta[stat];
+      const bool diag = p.causal && qi == jt;
+      ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (it > 0) {
+        ok = mbar_wait_bounded(pds_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutEpilogue);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], g[32];
+        tmem_ld_32x32(tS + lane_addr + c * 32, s);
+        tmem_ld_32x32(tdP + lane_addr + c * 32, g);
+        tmem_ld_wait();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            if (c * 32 + 2 * i > row) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale;
+          const float d1 = p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale;
+          pw[i] = pack_bf16x2(p0, p1);
+          dw[i] = pack_bf16x2(d0, d1);
+        }
+        store_tile_row_chunk(sP, row, c, pw);
+        store_tile_row_chunk(sdS, row, c, dw);
+      }
+      fence_proxy_async_smem();  // make the tiles visible to the tensor core (async proxy)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    if (ok) {
+      ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const long long token = static_cast<long long>(kv_row0) + row;  // accumulator row = key row
+      store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr);
+      store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 3. dQ
+// ------------------------------------------------------------------------------------------------------------
+constexpr int DQ_SMEM = 4 * TILE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+               const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do,
+               const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + 1 * TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;
+  uint8_t* sV = smem + 3 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * TILE_BYTES);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* ds_full = bars + 4;   // dS is in TMEM (4 warp arrivals)
+  uint64_t* dq_done = bars + 5;   // dQ += dS K has read dS (and K): S may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int n_kv = p.causal ? qt + 1 : p.T / BT;
+  const int q_row0 = b * p.T + qt * BT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_full, 4);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdS = tmem_base /* packed bf16 over S */, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+      tma_load_2d(sQ, &tma_q, qdo_full, h * BD, q_row0);
+      tma_load_2d(sQ + HALF_BYTES, &tma_q, qdo_full, h * BD + 64, q_row0);
+      tma_load_2d(sdO, &tma_do, qdo_full, h * BD, q_row0);
+      tma_load_2d(sdO + HALF_BYTES, &tma_do, qdo_full, h * BD + 64, q_row0);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int kv_row0 = b * p.T + j * BT;
+        ok = mbar_wait_bounded(kv_empty, (j & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+        tma_load_2d(sK, &tma_k, kv_full, hk * BD, kv_row0);
+        tma_load_2d(sK + HALF_BYTES, &tma_k, kv_full, hk * BD + 64, kv_row0);
+        tma_load_2d(sV, &tma_v, kv_full, hk * BD, kv_row0);
+        tma_load_2d(sV + HALF_BYTES, &tma_v, kv_full, hk * BD + 64, kv_row0);
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BT, BD, 0, 1);  // A = dS from TMEM, B = K contracted over its rows
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t ph = j & 1;
+        ok = mbar_wait_bounded(kv_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        if (j > 0) {
+          ok = mbar_wait_bounded(dq_done, ph ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
+          if (!ok) break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
+        umma_commit(sdp_full);
+        ok = mbar_wait_bounded(ds_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdS + k * 8, desc_mn(aK, k), idesc_dq, (j | k) != 0);
+        umma_commit(kv_empty);
+        umma_commit(dq_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qt * BT + row;
+    const float lse2 = p.lse[stat] * LOG2E;
+    const float dl = p.delta[stat];
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const uint32_t ph = j & 1;
+      const bool diag = p.causal && j == qt;
+      ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], g[32];
+        tmem_ld_32x32(tS + lane_addr + c * 32, s);
+        tmem_ld_32x32(tdP + lane_addr + c * 32, g);
+        tmem_ld_wait();
+        uint32_t dw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            if (c * 32 + 2 * i > row) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+          }
+          dw[i] = pack_bf16x2(p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale,
+                              p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale);
+        }
+        tmem_st_32x16(tdS + lane_addr + c * 16, dw);  // over columns of S that have been consumed
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (ok) {
+      ok = mbar_wait_bounded(dq_done, (n_kv - 1) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const long long token = static_cast<long long>(q_row0) + row;
+      store_acc_row(p.dq + token * p.ld_dq + h * BD, tdQ + lane_addr);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, int heads, long long ld) {
+  uint64_t dims[2] = {static_cast<uint64_t>(heads) * BD, static_cast<uint64_t>(rows)};
+  uint64_t str[1] = {static_cast<uint64_t>(ld) * 2};
+  uint32_t box[2] = {64, BT};
+  return get_tensor_map(map, ptr, 2, dims, str, box, 2);
+}
+
+}  // namespace
+}  // namespace ocb
+
+using namespace ocb;
+
+// Gradients of ocb_attention_fwd. dout/out/q/dq: [B, T, H, D]; k, v, dk, dv: [B, T, Hkv, D]; lse: [B, H, T] from the
+// forward pass; delta: [B, H, T] fp32 scratch (written here). dq/dk/dv are written densely (row stride heads * D).
+extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                 const float* lse, void* dq, void* dk, void* dv, const int* cu_seqlens, float* delta, int B,
+                                 int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
+                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  if (D != BD || Tq != Tk || (Tq % BT) != 0 || window > 0 || cu_seqlens != nullptr || Hkv <= 0 || (H % Hkv) != 0 ||
+      delta == nullptr)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  const long long rows = static_cast<long long>(B) * Tq;
+  const long long ld_do = static_cast<long long>(H) * BD;  // dout is dense
+  CUtensorMap mq, mk, mv, mdo;
+  if (!make_map(&mq, q, rows, H, ldq)) return -1001;
+  if (!make_map(&mk, k, rows, Hkv, ldk)) return -1002;
+  if (!make_map(&mv, v, rows, Hkv, ldv)) return -1003;
+  if (!make_map(&mdo, dout, rows, H, ld_do)) return -1004;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKDV_SMEM) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  {
+    const long long warps = rows * H;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), delta, rows, Tq, H, ldo, ld_do);
+  }
+  AttnBwdParams p;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq = static_cast<__nv_bfloat16*>(dq);
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.ld_dq = static_cast<long long>(H) * BD;
+  p.ld_dk = p.ld_dv = static_cast<long long>(Hkv) * BD;
+  p.T = Tq;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.scale = scale;
+  p.scale_log2 = scale * LOG2E;
+  p.causal = causal;
+  p.status = status;
+  attn_dkdv_kernel<<<dim3(Tq / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq, mk, mv, mdo, p);
+  attn_dq_kernel<<<dim3(Tq / BT, H, B), BWD_THREADS, DQ_SMEM, stream>>>(mq, mk, mv, mdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
