@@ -14,6 +14,8 @@
 //      dV += P^T dO, dK += dS^T Q accumulate in TMEM (4 x 128 columns = all of TMEM);
 //   3. attn_dq_kernel    : one CTA per (query tile, head, batch) walks the K/V tiles; dS goes back to TMEM as packed
 //      bf16 and is the A operand of dQ += dS K straight from tensor memory.
+// In both, every query row is shared by two softmax threads (columns [0,64) and [64,128)) in warps whose rank modulo
+// four -- the TMEM lane quadrant a warp may access -- is the same.
 // Recomputing S and dP in both kernels costs two extra tile products (7 instead of 5) and buys independence.
 
 #include "common.cuh"
@@ -27,7 +29,7 @@ constexpr int BT = 128;                    // tile rows (queries and keys)
 constexpr int BD = 128;                    // head dim
 constexpr int TILE_BYTES = BT * BD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp + MMA warp + 8 softmax warps (two threads per query row)
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnBwdParams {
@@ -64,9 +66,9 @@ __device__ __forceinline__ void store_tile_row_chunk(uint8_t* tile, int row, int
   }
 }
 
-__device__ __forceinline__ void store_acc_row(__nv_bfloat16* dst, uint32_t tmem_addr) {
+__device__ __forceinline__ void store_acc_row(__nv_bfloat16* dst, uint32_t tmem_addr, int c_begin) {
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = c_begin; c < c_begin + 2; ++c) {
     uint32_t r[32];
     tmem_ld_32x32(tmem_addr + c * 32, r);
     tmem_ld_wait();
@@ -142,7 +144,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -215,6 +217,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   } else {
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // query row within the tile
+    const int c_begin = ((warp - 2) >> 2) * 2;  // warps 2-5 take columns [0,64), warps 6-9 columns [64,128)
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
@@ -234,17 +237,24 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         if (!ok) break;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], g[32];
-        tmem_ld_32x32(tS + lane_addr + c * 32, s);
-        tmem_ld_32x32(tdP + lane_addr + c * 32, g);
+      uint32_t s0[32], g0[32], s1[32], g1[32];
+      tmem_ld_32x32(tS + lane_addr + c_begin * 32, s0);
+      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, g0);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c_begin + cc;
+        uint32_t(&s)[32] = cc ? s1 : s0;
+        uint32_t(&g)[32] = cc ? g1 : g0;
         tmem_ld_wait();
+        if (cc == 0) {  // second chunk's loads fly while the first is processed
+          tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, s1);
+          tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, g1);
+        }
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
+          float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
           if (diag) {
             if (c * 32 + 2 * i > row) p0 = 0.f;
             if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
@@ -269,8 +279,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     if (ok) {
       tc_fence_after();
       const long long token = static_cast<long long>(kv_row0) + row;  // accumulator row = key row
-      store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr);
-      store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr);
+      store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr, c_begin);
+      store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr, c_begin);
     }
   }
 
@@ -319,7 +329,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     mbar_init(kv_full, 1);
     mbar_init(kv_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -332,7 +342,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdS = tmem_base /* packed bf16 over S */, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256, tdS = tmem_base + 384 /* packed bf16 */;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -388,6 +398,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   } else {
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
+    const int c_begin = ((warp - 2) >> 2) * 2;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qt * BT + row;
     const float lse2 = p.lse[stat] * LOG2E;
@@ -400,17 +411,24 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], g[32];
-        tmem_ld_32x32(tS + lane_addr + c * 32, s);
-        tmem_ld_32x32(tdP + lane_addr + c * 32, g);
+      uint32_t s0[32], g0[32], s1[32], g1[32];
+      tmem_ld_32x32(tS + lane_addr + c_begin * 32, s0);
+      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, g0);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c_begin + cc;
+        uint32_t(&s)[32] = cc ? s1 : s0;
+        uint32_t(&g)[32] = cc ? g1 : g0;
         tmem_ld_wait();
+        if (cc == 0) {
+          tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, s1);
+          tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, g1);
+        }
         uint32_t dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
+          float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
           if (diag) {
             if (c * 32 + 2 * i > row) p0 = 0.f;
             if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
@@ -418,7 +436,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
           dw[i] = pack_bf16x2(p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale,
                               p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale);
         }
-        tmem_st_32x16(tdS + lane_addr + c * 16, dw);  // over columns of S that have been consumed
+        tmem_st_32x16(tdS + lane_addr + c * 16, dw);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -432,7 +450,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     if (ok) {
       tc_fence_after();
       const long long token = static_cast<long long>(q_row0) + row;
-      store_acc_row(p.dq + token * p.ld_dq + h * BD, tdQ + lane_addr);
+      store_acc_row(p.dq + token * p.ld_dq + h * BD, tdQ + lane_addr, c_begin);
     }
   }
 

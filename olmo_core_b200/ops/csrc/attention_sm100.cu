@@ -182,19 +182,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const bool diag = p.causal && j == qt;
-      // pass 1: row maximum
+      // pass 1: row maximum. The next chunk's TMEM load is in flight while the current chunk is processed.
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
-        tmem_ld_wait();
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32(tmem_S + lane_addr, ra);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]) * p.scale_log2;
-          mx = fmaxf(mx, (diag && c * 32 + i > row) ? -INFINITY : s);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        tmem_ld_wait();
+        if (c < 3) tmem_ld_32x32(tmem_S + lane_addr + (c + 1) * 32, nxt);
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx = fmaxf(mx, (c * 32 + i > row) ? -INFINITY : __uint_as_float(cur[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
         }
       }
+      mx *= p.scale_log2;  // the scale is positive, so it commutes with the maximum
       const bool grow = mx > m_ref + AT_RESCALE_THRESHOLD;  // also true for the first tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_ref;
@@ -215,16 +222,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
       // pass 2: probabilities relative to m_ref, written as bf16 pairs over the consumed part of S
       float sum = 0.f;
-#pragma unroll 1
+      tmem_ld_32x32(tmem_S + lane_addr, ra);
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
         tmem_ld_wait();
+        if (c < 3) tmem_ld_32x32(tmem_S + lane_addr + (c + 1) * 32, nxt);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_ref));
-          float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_ref));
+          float p0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, -m_ref));
+          float p1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, -m_ref));
           if (diag) {
             if (c * 32 + 2 * i > row) p0 = 0.f;
             if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
@@ -232,6 +241,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           sum += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
+        // P chunk c lands on S columns [16c, 16c+16): all of them were loaded (chunks <= c+1 are in registers)
         tmem_st_32x16(tmem_P + lane_addr + c * 16, pk);
       }
       l += sum;
