@@ -165,6 +165,16 @@ class SkipStepAdamW(SkipStepOptimizer):
             state = self.state[p]
             lowp = rt._own_rows_lowp(slot) if slot.aware and rt.lowp is not None and rt.lowp.dtype == torch.bfloat16 else None
             lr = group["lr"]
+            if rt.symmetric and state["exp_avg"].dtype == torch.float32:
+                # one kernel: AdamW on this rank's rows + bf16 stores into every peer's parameter buffer (the all-gather)
+                step_in = state["step"] if self.stepfix else torch.zeros_like(state["step"])
+                if rt.adamw_scatter(slot, state["exp_avg"], state["exp_avg_sq"], step_in,
+                                    lr=float(lr) if not torch.is_tensor(lr) else float(lr.item()), betas=group["betas"],
+                                    eps=group["eps"], weight_decay=group["weight_decay"], step_factor=f,
+                                    grad_scale=self.grad_scale):
+                    if self.stepfix:
+                        state["step"].add_(f.to(state["step"].dtype))
+                    continue
             adamw_step(p.data, g.reshape(p.shape), lr=float(lr) if not torch.is_tensor(lr) else float(lr.item()),
                        betas=group["betas"], eps=group["eps"], weight_decay=group["weight_decay"],
                        exp_avg=state["exp_avg"], exp_avg_sq=state["exp_avg_sq"], step=state["step"], step_factor=f,
@@ -172,7 +182,8 @@ class SkipStepAdamW(SkipStepOptimizer):
                        lowp=lowp if lowp is not None and lowp.is_contiguous() else None)
             if slot.aware and rt.lowp is not None and (lowp is None or not lowp.is_contiguous()):
                 rt._own_rows_lowp(slot).copy_(p.data)
-        rt.all_gather_lowp()
+        rt.all_gather_lowp(only_unfused=rt.symmetric)
+        rt.finish_scatter()
 
 
 @OptimConfig.register("adamw")

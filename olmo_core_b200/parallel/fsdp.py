@@ -170,8 +170,16 @@ class ShardedParamRuntime:
         self.master = torch.zeros(self._master_numel, dtype=torch.float32, device=device)
         if self._full_numel > 0:
             # without a low-precision compute dtype the full copy is fp32 (same layout, same code paths)
-            self.lowp = torch.zeros(self._full_numel, dtype=self.param_dtype or torch.float32, device=device)
-            self.main_grad = torch.zeros(self._full_numel, dtype=self.reduce_dtype, device=device)
+            lowp_dtype = self.param_dtype or torch.float32
+            self._sym_lowp = self._sym_grad = None
+            if (self.shard and self.replicate_group is None and lowp_dtype == torch.bfloat16
+                    and self.reduce_dtype == torch.float32):
+                self._try_symmetric(device)
+            if self._sym_grad is not None:
+                self.lowp, self.main_grad = self._sym_lowp.tensor, self._sym_grad.tensor
+            else:
+                self.lowp = torch.zeros(self._full_numel, dtype=lowp_dtype, device=device)
+                self.main_grad = torch.zeros(self._full_numel, dtype=self.reduce_dtype, device=device)
         if self.world_size > 1 or self.main_grad is None or self.reduce_dtype != torch.float32:
             self.grad_shard = torch.zeros(self._master_numel, dtype=torch.float32, device=device)
         else:
@@ -199,6 +207,88 @@ class ShardedParamRuntime:
         self._materialized = True
 
     # ------------------------------------------------------------------------------------------------
+    # peer-mapped buffers for the fused optimizer step
+    # ------------------------------------------------------------------------------------------------
+    @property
+    def symmetric(self) -> bool:
+        """True when gradients / parameters live in peer-mapped memory and the fused kernels do the collectives."""
+        return getattr(self, "_sym_grad", None) is not None
+
+    def _try_symmetric(self, device: torch.device) -> None:
+        from .symmetric import SymmetricBuffer, symmetric_memory_enabled
+
+        if not symmetric_memory_enabled(device, self.group):
+            return
+        try:
+            self._sym_lowp = SymmetricBuffer(self._full_numel, torch.bfloat16, device, self.group)
+            self._sym_grad = SymmetricBuffer(self._full_numel, torch.float32, device, self.group)
+            from ..ops import _lib
+            from ctypes import c_float, c_int, c_longlong, c_void_p
+
+            _lib.register_signature("ocb_fused_partials", [])
+            _lib.register_signature("ocb_peer_reduce_sumsq", [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_float,
+                                                              c_void_p, c_void_p, c_void_p, c_void_p])
+            _lib.register_signature("ocb_adamw_peer_scatter", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                               c_int, c_longlong, c_longlong, c_float, c_float, c_float,
+                                                               c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p])
+            self._fused_scratch = torch.zeros(_lib.lib().ocb_fused_partials(), dtype=torch.float32, device=device)
+            self._sumsq = torch.zeros(2, dtype=torch.float32, device=device)  # [sharded rows, replicated]
+            self._sumsq_valid = False
+            log.info(f"Sharded-parameter runtime uses peer-mapped buffers: {self._sym_grad}")
+        except Exception as e:  # no peer access, allocation failure, ...: the NCCL path still works
+            log.warning(f"Peer-mapped buffers unavailable ({type(e).__name__}: {e}); using NCCL collectives")
+            self._sym_lowp = self._sym_grad = None
+
+    def _fusable(self, slot: ParamSlot) -> bool:
+        n = slot.local_numel if slot.sharded else slot.full_numel
+        return slot.aware and n % 4 == 0 and slot.full_offset % 4 == 0 and slot.master_offset % 4 == 0
+
+    def shard_range(self, slot: ParamSlot) -> Tuple[int, int]:
+        """``(offset, count)`` of this rank's elements of ``slot`` inside the full flat buffers."""
+        if slot.sharded:
+            return slot.full_offset + self.rank * slot.local_numel, slot.local_numel
+        return slot.full_offset, slot.full_numel
+
+    @torch.no_grad()
+    def _reduce_gradients_fused(self) -> None:
+        from ..ops import _lib
+
+        lib, stream = _lib.lib(), _lib.stream_ptr()
+        sym = self._sym_grad
+        self._sumsq.zero_()
+        sym.barrier()  # every rank has finished accumulating into its gradient buffer
+        for slot in self.slots:
+            if not slot.param.requires_grad:
+                continue
+            out = self.grad_shard[slot.master_offset: slot.master_offset + slot.local_numel]
+            if slot.aware and slot.param.grad is not None:
+                raise RuntimeError(f"parameter '{slot.name}' received an autograd gradient besides its fused main_grad")
+            if self._fusable(slot):
+                offset, n = self.shard_range(slot)
+                rc = lib.ocb_peer_reduce_sumsq(sym.peer_ptrs, sym.multicast_ptr, self.world_size, offset, n,
+                                               1.0 / self.world_size, out.data_ptr(), self._fused_scratch.data_ptr(),
+                                               self._sumsq[0 if slot.sharded else 1:].data_ptr(), stream)
+                _lib.check(rc, "ocb_peer_reduce_sumsq")
+                continue
+            # small or oddly sized parameters: NCCL all-reduce of the whole tensor
+            if slot.aware:
+                full = self.main_grad[slot.full_offset: slot.full_offset + slot.full_numel]
+                dist.all_reduce(full, op=dist.ReduceOp.SUM, group=self.group)
+                src = full.view(slot.full_shape).narrow(0, slot.row_start, slot.local_rows).reshape(-1) if slot.sharded else full
+                out.copy_(src).div_(self.world_size)
+            else:
+                g = slot.param.grad
+                if g is None:
+                    out.zero_()
+                else:
+                    out.copy_(g.reshape(-1).to(torch.float32))
+                    slot.param.grad = None
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+                out.div_(self.world_size)
+            self._sumsq[0 if slot.sharded else 1] += out.float().pow(2).sum()
+        self._sumsq_valid = True
+
+    # ------------------------------------------------------------------------------------------------
     # parameter synchronisation
     # ------------------------------------------------------------------------------------------------
     def _own_rows_lowp(self, slot: ParamSlot) -> torch.Tensor:
@@ -216,11 +306,14 @@ class ShardedParamRuntime:
         self.all_gather_lowp()
 
     @torch.no_grad()
-    def all_gather_lowp(self) -> None:
-        """All-gather every sharded parameter's bf16 rows into the full resident copy (in place)."""
+    def all_gather_lowp(self, only_unfused: bool = False) -> None:
+        """
+        All-gather every sharded parameter's bf16 rows into the full resident copy (in place). With ``only_unfused``
+        the parameters whose rows the fused optimizer kernel has already stored into all peers are left out.
+        """
         if not self.shard or self.lowp is None:
             return
-        sharded = [s for s in self.slots if s.aware and s.sharded]
+        sharded = [s for s in self.slots if s.aware and s.sharded and not (only_unfused and self._fusable(s))]
         if not sharded:
             return
         backend_batch = getattr(dist, "_coalescing_manager", None)
@@ -251,6 +344,42 @@ class ShardedParamRuntime:
             self.main_grad.zero_()
         for slot in self.slots:
             slot.param.grad = None
+        if self.symmetric:
+            self._sumsq_valid = False
+
+    @torch.no_grad()
+    def adamw_scatter(self, slot: ParamSlot, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, step: torch.Tensor, *,
+                      lr: float, betas: Tuple[float, float], eps: float, weight_decay: float,
+                      step_factor: Optional[torch.Tensor], grad_scale: Optional[torch.Tensor]) -> bool:
+        """
+        Fused AdamW + all-gather for ``slot``: updates this rank's master rows and stores their bf16 copies into every
+        peer's parameter buffer. Returns False (nothing done) when the slot does not qualify; ``step`` is incremented
+        by the caller.
+        """
+        if not self.symmetric or not self._fusable(slot):
+            return False
+        from ..ops import _lib
+
+        offset, n = self.shard_range(slot)
+        sym = self._sym_lowp
+        g = self.grad_shard[slot.master_offset: slot.master_offset + slot.local_numel]
+        if slot.sharded:
+            peers, mc, world = sym.peer_ptrs, sym.multicast_ptr, self.world_size
+        else:  # replicated parameter: every rank computes the same update and writes only its own copy
+            import ctypes
+
+            peers, mc, world = (ctypes.c_void_p * 1)(sym.tensor.data_ptr()), None, 1
+        rc = _lib.lib().ocb_adamw_peer_scatter(
+            slot.param.data.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), g.data_ptr(), peers, mc, world, offset, n,
+            lr, betas[0], betas[1], eps, weight_decay, step.data_ptr(), _lib.ptr(step_factor), _lib.ptr(grad_scale),
+            _lib.stream_ptr())
+        _lib.check(rc, "ocb_adamw_peer_scatter")
+        return True
+
+    def finish_scatter(self) -> None:
+        """Barrier after the last :meth:`adamw_scatter` of a step: all peers' parameter stores have landed."""
+        if self.symmetric:
+            self._sym_lowp.barrier()
 
     @torch.no_grad()
     def reduce_gradients(self) -> None:
@@ -258,6 +387,9 @@ class ShardedParamRuntime:
         Average gradients over the data-parallel group: reduce-scatter for sharded parameters (each rank
         receives its rows), all-reduce for replicated ones. Afterwards ``grad_view(slot)`` is valid.
         """
+        if self.symmetric:
+            self._reduce_gradients_fused()
+            return
         ws = self.world_size
         single_fp32 = self.grad_shard is None
         for slot in self.slots:
@@ -311,6 +443,11 @@ class ShardedParamRuntime:
     @torch.no_grad()
     def grad_norm_sq(self) -> torch.Tensor:
         """Squared global L2 norm of the (reduced) gradients as an fp32 scalar tensor on the device."""
+        if self.symmetric and self._sumsq_valid:
+            # accumulated by the fused reduce kernels; rows are disjoint over ranks, replicated parameters count once
+            sharded_part = self._sumsq[0].clone()
+            dist.all_reduce(sharded_part, op=dist.ReduceOp.SUM, group=self.group)
+            return sharded_part + self._sumsq[1]
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         if self.grad_shard is None:
             optim_ops.sumsq(self.main_grad, out=total, accumulate=True)
