@@ -48,15 +48,8 @@ def symmetric_memory_enabled(device: torch.device, group: Optional[dist.ProcessG
 
 def ensure_symmetric_group(group: Optional[dist.ProcessGroup]) -> str:
     """Make ``group`` known to the symmetric-memory allocator; returns its name."""
-    import torch.distributed._symmetric_memory as symm
-
     group = group if group is not None else dist.group.WORLD
-    name = group.group_name
-    try:
-        symm.enable_symm_mem_for_group(name)
-    except Exception:  # newer versions register groups lazily at rendezvous
-        pass
-    return name
+    return group.group_name  # groups are registered with the allocator lazily, at rendezvous
 
 
 class SymmetricBuffer:
