@@ -172,8 +172,9 @@ class ShardedParamRuntime:
             # without a low-precision compute dtype the full copy is fp32 (same layout, same code paths)
             lowp_dtype = self.param_dtype or torch.float32
             self._sym_lowp = self._sym_grad = None
+            tensor_parallel = any(hasattr(s.param, "_tp_sharded") or hasattr(s.param, "_tp_partial_grad") for s in self.slots)
             if (self.shard and self.replicate_group is None and lowp_dtype == torch.bfloat16
-                    and self.reduce_dtype == torch.float32):
+                    and self.reduce_dtype == torch.float32 and not tensor_parallel):
                 self._try_symmetric(device)
             if self._sym_grad is not None:
                 self.lowp, self.main_grad = self._sym_lowp.tensor, self._sym_grad.tensor
@@ -194,6 +195,9 @@ class ShardedParamRuntime:
                 view.copy_(src.narrow(0, slot.row_start, slot.local_rows) if slot.sharded else src)
             new = nn.Parameter(view, requires_grad=old.requires_grad)
             new._shard_info = ShardInfo(slot.full_shape, slot.row_start, slot.sharded)  # type: ignore[attr-defined]
+            for attr in ("_tp_partial_grad", "_tp_sharded"):  # set by olmo_core_b200.parallel.tensor
+                if hasattr(old, attr):
+                    setattr(new, attr, getattr(old, attr))
             if slot.aware:
                 new._lowp = self.lowp[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
                 new.main_grad = self.main_grad[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
@@ -390,6 +394,31 @@ class ShardedParamRuntime:
         if self.symmetric:
             self._reduce_gradients_fused()
             return
+        self._reduce_gradients_nccl()
+        self._sync_tensor_parallel_partials()
+
+    def _tp_groups(self):
+        """Tensor-parallel groups that parameters of this model were sliced / marked with (usually none or one)."""
+        seen = {}
+        for slot in self.slots:
+            g = getattr(slot.param, "_tp_partial_grad", None)
+            if g is not None:
+                seen[id(g)] = g
+        return list(seen.values())
+
+    @torch.no_grad()
+    def _sync_tensor_parallel_partials(self) -> None:
+        """Sum, over the tensor-parallel group, the gradients of replicated parameters that saw only a sequence shard."""
+        for slot in self.slots:
+            group = getattr(slot.param, "_tp_partial_grad", None)
+            if group is None or not slot.param.requires_grad:
+                continue
+            g = self.grad_view(slot) if (slot.aware or self.grad_shard is not None) else slot.param.grad
+            if g is not None:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+
+    @torch.no_grad()
+    def _reduce_gradients_nccl(self) -> None:
         ws = self.world_size
         single_fp32 = self.grad_shard is None
         for slot in self.slots:
@@ -443,6 +472,22 @@ class ShardedParamRuntime:
     @torch.no_grad()
     def grad_norm_sq(self) -> torch.Tensor:
         """Squared global L2 norm of the (reduced) gradients as an fp32 scalar tensor on the device."""
+        tp_group = next((getattr(s.param, "_tp_partial_grad", None) for s in self.slots
+                         if getattr(s.param, "_tp_partial_grad", None) is not None), None)
+        if tp_group is not None:
+            # four kinds of gradients: rows split over data-parallel ranks or not, columns/heads split over the
+            # tensor-parallel group or not; split ones are summed over the group that splits them, others count once
+            buckets = torch.zeros(2, 2, dtype=torch.float32, device=self.device)
+            for slot in self.slots:
+                g = self.grad_view(slot) if (slot.aware or self.grad_shard is not None) else slot.param.grad
+                if g is not None and slot.param.requires_grad:
+                    dp_split = int(slot.sharded and self.grad_shard is not None)
+                    buckets[dp_split, int(getattr(slot.param, "_tp_sharded", False))] += g.float().pow(2).sum()
+            if self.world_size > 1:
+                dist.all_reduce(buckets[1], op=dist.ReduceOp.SUM, group=self.group)
+            tp_part = buckets[:, 1].sum()
+            dist.all_reduce(tp_part, op=dist.ReduceOp.SUM, group=tp_group)
+            return tp_part + buckets[:, 0].sum()
         if self.symmetric and self._sumsq_valid:
             # accumulated by the fused reduce kernels; rows are disjoint over ranks, replicated parameters count once
             sharded_part = self._sumsq[0].clone()

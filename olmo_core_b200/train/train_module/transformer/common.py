@@ -67,6 +67,10 @@ def parallelize_model(
         log.info(f"Applied '{ac_config.mode}' activation checkpointing")
     if compile_model:
         model.apply_compile()
+    if dp_config is None and tp_config is not None:
+        # the parameter runtime also owns the tensor-parallel gradient bookkeeping (partial-gradient sums, global norm)
+        dp_mesh = get_dp_model_mesh(world_mesh) if world_mesh is not None else None
+        model.apply_ddp(dp_mesh=dp_mesh, param_dtype=None)
     if dp_config is not None:
         dp_mesh = get_dp_model_mesh(world_mesh) if world_mesh is not None else None
         param_dtype = dp_config.param_dtype.as_pt() if dp_config.param_dtype is not None else None
