@@ -1,0 +1,73 @@
+"""Context-parallel attention (zig-zag and contiguous layouts, Ulysses head exchange) on gloo ranks vs one device."""
+
+import pytest
+import torch
+
+from olmo_core_b200.testing import run_distributed_test
+
+B, T, H, HKV, D = 2, 64, 4, 2, 16
+
+
+def _full(seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, H, D, generator=g)
+    k = torch.randn(B, T, HKV, D, generator=g)
+    v = torch.randn(B, T, HKV, D, generator=g)
+    return q, k, v
+
+
+def _ring_worker(layout: str):
+    import torch.distributed as dist
+
+    from olmo_core_b200.nn.attention.backend import TorchAttentionBackend
+    from olmo_core_b200.nn.attention.ring import (
+        RingAttentionLlama3LoadBalancer,
+        RingAttentionZigZagLoadBalancer,
+        RingContextParallelStyle,
+    )
+    from olmo_core_b200.ops.attention import attention_reference
+    from olmo_core_b200.parallel.context import ring_attention
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    q, k, v = _full()
+    want = attention_reference(q, k, v, causal=True)
+    if layout == "zig_zag":
+        lb, style = RingAttentionZigZagLoadBalancer(cp_rank=rank, cp_world_size=ws), RingContextParallelStyle.zig_zag()
+    else:
+        lb, style = RingAttentionLlama3LoadBalancer(cp_rank=rank, cp_world_size=ws), RingContextParallelStyle.llama3()
+    ql, kl, vl, wl = lb.batch_shard(inputs=[q, k, v, want], seq_dims=[1, 1, 1, 1])
+    ql, kl, vl = (t.clone().requires_grad_(True) for t in (ql, kl, vl))
+    backend = TorchAttentionBackend(head_dim=D, n_heads=H, n_kv_heads=HKV)
+    out = ring_attention(backend, ql, kl, vl, group=dist.group.WORLD, style=style)
+    torch.testing.assert_close(out, wl, rtol=1e-4, atol=1e-5)
+    # gradients: d(sum of all outputs)/dk on the owners must equal the single-device gradient shard
+    out.sum().backward()
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    attention_reference(qf, kf, vf, causal=True).sum().backward()
+    (kg,) = lb.batch_shard(inputs=[kf.grad], seq_dims=[1])
+    torch.testing.assert_close(kl.grad, kg, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("layout", ["zig_zag", "llama3"])
+def test_ring_attention_matches_single_device(layout):
+    run_distributed_test(_ring_worker, world_size=2, func_args=(layout,))
+
+
+def _ulysses_worker():
+    import torch.distributed as dist
+
+    from olmo_core_b200.distributed.parallel.context_parallel import all_to_all_cp2hp, all_to_all_single_hp2cp
+    from olmo_core_b200.ops.attention import attention_reference
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    q, k, v = _full(1)
+    want = attention_reference(q, k, v, causal=True)
+    sl = slice(rank * T // ws, (rank + 1) * T // ws)
+    qh, kh, vh = all_to_all_cp2hp([q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous()], dist.group.WORLD)
+    assert qh.shape == (B, T, H // ws, D)  # full sequence, a slice of the heads
+    out = all_to_all_single_hp2cp(attention_reference(qh, kh, vh, causal=True), dist.group.WORLD)
+    torch.testing.assert_close(out, want[:, sl], rtol=1e-4, atol=1e-5)
+
+
+def test_ulysses_head_exchange_matches_single_device():
+    run_distributed_test(_ulysses_worker, world_size=2)
