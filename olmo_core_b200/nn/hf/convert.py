@@ -1,0 +1,124 @@
+"""
+Parameter-name (and layout) mapping between this framework's transformer state dicts and Hugging Face causal-LM
+state dicts (role of src/olmo_core/nn/hf/convert.py).
+
+The mapping is a table of name templates: ``{layer}`` and ``{expert}`` are expanded over the model's layers / experts.
+Dense models map one to one. Mixture-of-experts weights are stored here as stacked ``[E * in, out]`` / ``[E * out, in]``
+matrices and on the HF side as one ``nn.Linear`` per expert, so they are split / concatenated (and transposed) on the
+way. RoPE uses the same "rotate half" convention on both sides, so projections need no permutation.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+__all__ = ["convert_state_to_hf", "convert_state_from_hf", "get_converter_to_hf", "get_converter_from_hf",
+           "OLMO_CORE_TO_HF_TEMPLATES", "StateConverter"]
+
+# (this framework, Hugging Face). Norm names depend on the block type, see ``_norm_templates``.
+OLMO_CORE_TO_HF_TEMPLATES: List[Tuple[str, str]] = [
+    ("embeddings.weight", "model.embed_tokens.weight"),
+    ("lm_head.norm.weight", "model.norm.weight"),
+    ("lm_head.w_out.weight", "lm_head.weight"),
+    ("blocks.{layer}.attention.w_q.weight", "model.layers.{layer}.self_attn.q_proj.weight"),
+    ("blocks.{layer}.attention.w_k.weight", "model.layers.{layer}.self_attn.k_proj.weight"),
+    ("blocks.{layer}.attention.w_v.weight", "model.layers.{layer}.self_attn.v_proj.weight"),
+    ("blocks.{layer}.attention.w_out.weight", "model.layers.{layer}.self_attn.o_proj.weight"),
+    ("blocks.{layer}.attention.w_q.bias", "model.layers.{layer}.self_attn.q_proj.bias"),
+    ("blocks.{layer}.attention.w_k.bias", "model.layers.{layer}.self_attn.k_proj.bias"),
+    ("blocks.{layer}.attention.w_v.bias", "model.layers.{layer}.self_attn.v_proj.bias"),
+    ("blocks.{layer}.attention.w_out.bias", "model.layers.{layer}.self_attn.o_proj.bias"),
+    ("blocks.{layer}.attention.q_norm.weight", "model.layers.{layer}.self_attn.q_norm.weight"),
+    ("blocks.{layer}.attention.k_norm.weight", "model.layers.{layer}.self_attn.k_norm.weight"),
+    ("blocks.{layer}.feed_forward.w1.weight", "model.layers.{layer}.mlp.gate_proj.weight"),
+    ("blocks.{layer}.feed_forward.w2.weight", "model.layers.{layer}.mlp.down_proj.weight"),
+    ("blocks.{layer}.feed_forward.w3.weight", "model.layers.{layer}.mlp.up_proj.weight"),
+    ("blocks.{layer}.feed_forward_moe.router.weight", "model.layers.{layer}.mlp.gate.weight"),
+]
+
+_MOE_EXPERT_TEMPLATES = [  # (stacked name here, per-expert HF name, transpose when splitting)
+    ("blocks.{layer}.feed_forward_moe.experts.mlp.w1", "model.layers.{layer}.mlp.experts.{expert}.gate_proj.weight", True),
+    ("blocks.{layer}.feed_forward_moe.experts.mlp.w2", "model.layers.{layer}.mlp.experts.{expert}.down_proj.weight", False),
+    ("blocks.{layer}.feed_forward_moe.experts.mlp.w3", "model.layers.{layer}.mlp.experts.{expert}.up_proj.weight", True),
+]
+
+
+def _norm_templates(reordered_norm: bool) -> List[Tuple[str, str]]:
+    if reordered_norm:  # OLMo-2 / OLMo-3: norms are applied to the sub-layer outputs
+        return [("blocks.{layer}.attention_norm.weight", "model.layers.{layer}.post_attention_layernorm.weight"),
+                ("blocks.{layer}.feed_forward_norm.weight", "model.layers.{layer}.post_feedforward_layernorm.weight")]
+    return [("blocks.{layer}.attention_norm.weight", "model.layers.{layer}.input_layernorm.weight"),
+            ("blocks.{layer}.feed_forward_norm.weight", "model.layers.{layer}.post_attention_layernorm.weight")]
+
+
+class StateConverter:
+    """Expands the templates for a concrete number of layers / experts and renames (splits, merges) tensors."""
+
+    def __init__(self, n_layers: int, n_experts: int = 0, reordered_norm: bool = True):
+        self.n_layers, self.n_experts = n_layers, n_experts
+        self.pairs: List[Tuple[str, str]] = []
+        for ours, theirs in OLMO_CORE_TO_HF_TEMPLATES + _norm_templates(reordered_norm):
+            if "{layer}" in ours:
+                self.pairs += [(ours.format(layer=i), theirs.format(layer=i)) for i in range(n_layers)]
+            else:
+                self.pairs.append((ours, theirs))
+
+    def to_hf(self, state: Dict[str, Any]) -> Dict[str, Any]:
+        out = {theirs: state[ours] for ours, theirs in self.pairs if ours in state}
+        for ours_t, theirs_t, transpose in _MOE_EXPERT_TEMPLATES:
+            for i in range(self.n_layers):
+                ours = ours_t.format(layer=i)
+                if ours not in state:
+                    continue
+                for e, piece in enumerate(state[ours].chunk(self.n_experts, dim=0)):
+                    out[theirs_t.format(layer=i, expert=e)] = piece.t().contiguous() if transpose else piece.contiguous()
+        return out
+
+    def from_hf(self, hf_state: Dict[str, Any]) -> Dict[str, Any]:
+        out = {ours: hf_state[theirs] for ours, theirs in self.pairs if theirs in hf_state}
+        for ours_t, theirs_t, transpose in _MOE_EXPERT_TEMPLATES:
+            for i in range(self.n_layers):
+                names = [theirs_t.format(layer=i, expert=e) for e in range(self.n_experts)]
+                if not names or names[0] not in hf_state:
+                    continue
+                pieces = [hf_state[n].t() if transpose else hf_state[n] for n in names]
+                out[ours_t.format(layer=i)] = torch.cat(pieces, dim=0).contiguous()
+        return out
+
+
+def _converter_for(hf_config, n_experts: Optional[int] = None) -> StateConverter:
+    model_type = getattr(hf_config, "model_type", "olmo2")
+    reordered = model_type in ("olmo2", "olmo3", "flex_olmo", "olmoe") and model_type != "olmoe"
+    experts = n_experts if n_experts is not None else int(getattr(hf_config, "num_experts", 0) or 0)
+    return StateConverter(hf_config.num_hidden_layers, n_experts=experts, reordered_norm=reordered)
+
+
+def get_converter_to_hf(hf_config=None, model_type: Optional[str] = None) -> StateConverter:
+    if hf_config is None:
+        raise ValueError("an HF config is needed to expand the name templates")
+    return _converter_for(hf_config)
+
+
+def get_converter_from_hf(hf_config=None, model_type: Optional[str] = None) -> StateConverter:
+    return get_converter_to_hf(hf_config, model_type)
+
+
+def convert_state_to_hf(hf_config, state: Dict[str, Any]) -> Dict[str, Any]:
+    """State dict of this framework's transformer -> state dict of the HF causal LM described by ``hf_config``."""
+    converted = _converter_for(hf_config).to_hf(state)
+    if getattr(hf_config, "tie_word_embeddings", False):
+        converted.pop("lm_head.weight", None)
+    missing = [k for k in state if not any(k == ours for ours, _ in _converter_for(hf_config).pairs)
+               and "experts.mlp" not in k]
+    if missing:
+        raise KeyError(f"no Hugging Face counterpart for parameters: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
+    return converted
+
+
+def convert_state_from_hf(hf_config, hf_state: Dict[str, Any], model_type: Optional[str] = None) -> Dict[str, Any]:
+    converted = _converter_for(hf_config).from_hf(hf_state)
+    if "lm_head.w_out.weight" not in converted and "embeddings.weight" in converted:
+        converted["lm_head.w_out.weight"] = converted["embeddings.weight"]  # tied embeddings
+    return converted
