@@ -35,6 +35,10 @@ __all__ = [
     "requires_gpu",
     "requires_multi_gpu",
     "run_distributed_test",
+    "FLASH_2_MARKS", "FLASH_3_MARKS", "FLASH_4_MARKS", "GROUPED_GEMM_MARKS", "TE_MARKS",
+    "has_flash_attn_2", "has_flash_attn_3", "has_flash_attn_4", "has_grouped_gemm", "has_torchao", "has_quack",
+    "requires_flash_attn_2", "requires_flash_attn_3", "requires_flash_attn_4", "requires_grouped_gemm", "requires_fla",
+    "requires_quack", "requires_dion", "requires_te", "requires_compute_capability",
 ]
 
 has_cuda = torch.cuda.is_available()
@@ -56,6 +60,64 @@ def requires_gpu(func):
 
 def requires_multi_gpu(func):
     return _apply(MULTI_GPU_MARKS, func)
+
+
+def _kernels_available() -> bool:
+    if not has_cuda:
+        return False
+    from ..ops.attention import has_flash_kernel
+
+    return has_flash_kernel()
+
+
+# The capabilities that the reference gates on optional wheels are built in here: each probe answers whether this
+# package's own kernel for that role can run on the current machine.
+has_flash_attn_2 = has_flash_attn_3 = has_flash_attn_4 = _kernels_available()
+has_grouped_gemm = has_cuda
+has_torchao = has_cuda  # float8 training uses this package's own GEMMs
+has_quack = has_cuda  # fused RMSNorm / cross-entropy kernels are built in
+has_te = False
+
+FLASH_2_MARKS = FLASH_3_MARKS = FLASH_4_MARKS = (
+    pytest.mark.gpu, pytest.mark.skipif(not has_flash_attn_2, reason="Requires the flash-attention kernels (B200)"))
+GROUPED_GEMM_MARKS = GPU_MARKS
+TE_MARKS = (pytest.mark.gpu, pytest.mark.skipif(True, reason="Transformer Engine is not used by this framework"))
+
+
+def requires_flash_attn_2(func):
+    return _apply(FLASH_2_MARKS, func)
+
+
+requires_flash_attn_3 = requires_flash_attn_4 = requires_flash_attn_2
+
+
+def requires_grouped_gemm(func):
+    return _apply(GROUPED_GEMM_MARKS, func)
+
+
+def requires_fla(func):  # the gated delta rule is built in and runs everywhere
+    return func
+
+
+def requires_quack(func):
+    return _apply(GPU_MARKS, func)
+
+
+def requires_dion(func):  # the Dion optimizer is built in
+    return func
+
+
+def requires_te(func):
+    return _apply(TE_MARKS, func)
+
+
+def requires_compute_capability(min_cc: int):
+    """``min_cc`` as major * 10 + minor, e.g. 100 for sm_100."""
+    def decorator(func):
+        ok = has_cuda and (lambda c: c[0] * 10 + c[1])(torch.cuda.get_device_capability()) >= min_cc
+        return _apply((pytest.mark.gpu, pytest.mark.skipif(not ok, reason=f"Requires compute capability >= {min_cc}")), func)
+
+    return decorator
 
 
 INIT_DEVICES = [

@@ -29,6 +29,7 @@ from ..config import StrEnum
 from ..exceptions import OLMoCLIError, OLMoEnvironmentError, OLMoError, OLMoThreadError
 
 __all__ = [
+    "LOG_FILTER_TYPE_ENV_VAR",
     "generate_uuid",
     "get_default_thread_count",
     "wait_for",
@@ -279,10 +280,13 @@ def set_env_variables() -> None:
     os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
 
 
+LOG_FILTER_TYPE_ENV_VAR = "LOG_FILTER_TYPE"
+
+
 def prepare_cli_environment(log_filter_type: Optional[LogFilterType] = None) -> None:
     """Logging, exception hook, warning filters and env vars for a command-line entry point."""
     if log_filter_type is None:
-        log_filter_type = LogFilterType(os.environ.get("LOG_FILTER_TYPE", "rank0_only"))
+        log_filter_type = LogFilterType(os.environ.get(LOG_FILTER_TYPE_ENV_VAR, "rank0_only"))
     setup_logging(log_filter_type)
     install_excepthook()
     filter_warnings()
