@@ -1,0 +1,4 @@
+"""Module path of src/olmo_core/data/composable/mixing_token_source.py; the classes live in :mod:`.token_source`."""
+
+from .configs import *  # noqa: F401,F403  (attaches the ``Config`` attributes)
+from .token_source import MixingTokenSource, MixingTokenSourceSpec  # noqa: F401
