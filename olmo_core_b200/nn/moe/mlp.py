@@ -93,57 +93,38 @@ class MoEMLP(MoEMLPBase):
 class _GroupedLinear(torch.autograd.Function):
     """
     ``y[rows of expert e] = x[rows of expert e] @ w_e^T`` (``trans_b``) or ``@ w_e``, for expert-sorted rows.
-    One tcgen05 GEMM per non-empty expert for forward, dgrad and wgrad; the weight gradient accumulates
-    into ``weight.main_grad`` when the sharded-parameter runtime provides one.
+    Forward, dgrad and wgrad are ONE grouped tcgen05 GEMM launch each; the group boundaries are a device tensor
+    (``offsets``, int32 ``[E + 1]``), so the host never waits for the routing result. The weight gradient accumulates into
+    ``weight.main_grad`` when the sharded-parameter runtime provides one.
     """
 
     @staticmethod
-    def forward(ctx, x, weight, sizes: List[int], trans_b: bool):  # type: ignore[override]
-        from ...ops.gemm import compute_weight
+    def forward(ctx, x, weight, offsets, trans_b: bool):  # type: ignore[override]
+        from ...ops.gemm import compute_weight, grouped_gemm
 
         w = compute_weight(weight, torch.bfloat16)
-        E = len(sizes)
-        wv = w.view(E, -1, w.shape[-1])
-        out_dim = wv.shape[1] if trans_b else wv.shape[2]
-        y = torch.empty((x.shape[0], out_dim), dtype=x.dtype, device=x.device)
-        r = 0
-        for e, n in enumerate(sizes):
-            if n:
-                gemm(x[r:r + n], wv[e], trans_b=trans_b, out=y[r:r + n])
-            r += n
-        ctx.save_for_backward(x, w)
-        ctx.sizes, ctx.trans_b, ctx.weight_ref = sizes, trans_b, weight
+        x = x.contiguous()
+        y = grouped_gemm(x, w, offsets, trans_b=trans_b)
+        ctx.save_for_backward(x, w, offsets)
+        ctx.trans_b, ctx.weight_ref = trans_b, weight
         return y
 
     @staticmethod
     def backward(ctx, dy):  # type: ignore[override]
-        x, w = ctx.saved_tensors
-        sizes, trans_b, weight = ctx.sizes, ctx.trans_b, ctx.weight_ref
-        E = len(sizes)
-        wv = w.view(E, -1, w.shape[-1])
+        from ...ops.gemm import grouped_gemm, grouped_gemm_wgrad
+
+        x, w, offsets = ctx.saved_tensors
+        trans_b, weight = ctx.trans_b, ctx.weight_ref
         dy = dy.contiguous()
-        dx = torch.empty_like(x)
+        # y = x w^T: dx = dy w, dw = dy^T x.   y = x w: dx = dy w^T, dw = x^T dy.
+        dx = grouped_gemm(dy, w, offsets, trans_b=not trans_b)
         main_grad = getattr(weight, "main_grad", None)
-        if main_grad is not None:
-            dw = main_grad.view(wv.shape)
-            acc = True
-        else:
-            dw = torch.zeros(wv.shape, dtype=torch.float32, device=x.device)
-            acc = False
-        r = 0
-        for e, n in enumerate(sizes):
-            if n:
-                xs, ds = x[r:r + n], dy[r:r + n]
-                # y = x w^T: dx = dy w, dw = dy^T x.   y = x w: dx = dy w^T, dw = x^T dy.
-                gemm(ds, wv[e], trans_b=not trans_b, out=dx[r:r + n])
-                if trans_b:
-                    gemm(ds, xs, trans_a=True, trans_b=False, out=dw[e], accumulate=acc)
-                else:
-                    gemm(xs, ds, trans_a=True, trans_b=False, out=dw[e], accumulate=acc)
-            r += n
+        dw = main_grad if main_grad is not None else torch.empty(w.shape, dtype=torch.float32, device=x.device)
+        a, b = (dy, x) if trans_b else (x, dy)
+        grouped_gemm_wgrad(a, b, offsets, dw.view(w.shape), accumulate=main_grad is not None)
         if main_grad is not None:
             return dx, None, None, None
-        return dx, dw.view(weight.shape).to(weight.dtype), None, None
+        return dx, dw.to(weight.dtype), None, None
 
 
 class DroplessMoEMLP(MoEMLPBase):
@@ -165,11 +146,16 @@ class DroplessMoEMLP(MoEMLPBase):
     def extra_repr(self) -> str:
         return f"num_experts={self.num_experts}, in_features={self.d_model}, hidden_size={self.hidden_size}"
 
-    def gmm(self, x: torch.Tensor, w: torch.Tensor, batch_sizes: List[int], trans_b: bool = False) -> torch.Tensor:
-        """Grouped matmul over expert-sorted rows. ``w``: ``[E_local * hidden, d_model]``."""
+    def gmm(self, x: torch.Tensor, w: torch.Tensor, batch_sizes, trans_b: bool = False) -> torch.Tensor:
+        """
+        Grouped matmul over expert-sorted rows. ``w``: ``[E_local * hidden, d_model]``. ``batch_sizes``: rows per expert,
+        a list or a tensor; on the kernel path a device tensor is consumed as is (no host synchronisation).
+        """
         E = self.num_local_experts
         if x.is_cuda and x.dtype == torch.bfloat16:
-            return _GroupedLinear.apply(x, w, batch_sizes, trans_b)
+            return _GroupedLinear.apply(x, w, self._offsets(batch_sizes, x.device), trans_b)
+        if torch.is_tensor(batch_sizes):
+            batch_sizes = batch_sizes.tolist()
         from ...ops.param import full_param
 
         wv = full_param(w, x.dtype).view(E, self.hidden_size, self.d_model)
@@ -181,9 +167,23 @@ class DroplessMoEMLP(MoEMLPBase):
             r += n
         return torch.cat(outs, dim=0) if outs else x.new_zeros((0, wv.shape[1] if trans_b else wv.shape[2]))
 
+    @staticmethod
+    def _offsets(batch_sizes, device) -> torch.Tensor:
+        """Row prefix sums ``[E + 1]`` (int32, on ``device``) from rows per expert; a ready ``[E + 1]`` tensor passes through."""
+        if torch.is_tensor(batch_sizes) and getattr(batch_sizes, "_is_offsets", False):
+            return batch_sizes
+        sizes = batch_sizes if torch.is_tensor(batch_sizes) else torch.tensor(list(batch_sizes), dtype=torch.int32)
+        sizes = sizes.to(device=device, dtype=torch.int32, non_blocking=True)
+        offsets = torch.zeros(sizes.numel() + 1, dtype=torch.int32, device=device)
+        torch.cumsum(sizes, 0, out=offsets[1:])
+        offsets._is_offsets = True  # type: ignore[attr-defined]
+        return offsets
+
     def forward(self, x: torch.Tensor, batch_size_per_expert) -> torch.Tensor:
         """``x``: ``[rows, d]`` sorted by local expert; ``batch_size_per_expert``: list or tensor of row counts."""
-        sizes = batch_size_per_expert.tolist() if torch.is_tensor(batch_size_per_expert) else list(batch_size_per_expert)
+        sizes = batch_size_per_expert
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            sizes = self._offsets(batch_size_per_expert, x.device)  # computed once, shared by the three products
         w1, w2, w3 = (get_local_tensor(w) for w in (self.w1, self.w2, self.w3))
         a = self.gmm(x, w1, sizes, trans_b=True)
         b = self.gmm(x, w3, sizes, trans_b=True)

@@ -102,7 +102,12 @@ class ParallelDroplessMLP(ParallelMLPBase):
     def forward_once(self, x, expert_weights, expert_indices, batch_size_per_expert) -> torch.Tensor:
         indices, bin_ids, bins = self.indices_and_bins(expert_indices, batch_size_per_expert)
         xs = ops.gather(x, indices, bin_ids, bins, self.top_k)
-        ys = self.mlp(xs, batch_size_per_expert.tolist())
+        offsets = getattr(bins, "_offsets", None)  # set by the CUDA counting sort: the kernels read it on the device
+        if offsets is not None and xs.is_cuda and xs.dtype == torch.bfloat16:
+            offsets._is_offsets = True  # type: ignore[attr-defined]
+            ys = self.mlp(xs, offsets)
+        else:
+            ys = self.mlp(xs, batch_size_per_expert.tolist())
         return ops.scatter(ys, indices, bin_ids, expert_weights, bins, self.top_k)
 
     def parallel_forward_once(self, x, expert_weights, expert_indices, batch_size_per_expert) -> torch.Tensor:

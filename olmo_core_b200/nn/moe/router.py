@@ -68,6 +68,42 @@ class MoERouterConfig(ModuleConfig):
             raise OLMoConfigurationError(f"invalid options for '{self.name}' {self.__class__.__name__}, {e}") from e
 
 
+class _FusedSoftmaxTopK(torch.autograd.Function):
+    """
+    ``logits [N, E] -> (softmax scores [N, E], top-k weights [N, k], expert ids [N, k], tokens per expert [E])`` in one
+    kernel (one warp per token keeps its row in registers). Backward is the softmax Jacobian applied to the sum of the
+    gradients that arrive through the scores (auxiliary loss) and through the selected weights.
+    """
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, top_k: int):  # type: ignore[override]
+        from ...ops import _lib
+
+        n, e = logits.shape
+        scores = torch.empty((n, e), dtype=torch.float32, device=logits.device)
+        weights = torch.empty((n, top_k), dtype=torch.float32, device=logits.device)
+        experts = torch.empty((n, top_k), dtype=torch.int32, device=logits.device)
+        counts = torch.empty(e, dtype=torch.int32, device=logits.device)
+        rc = _lib.lib().ocb_moe_router_topk(logits.data_ptr(), scores.data_ptr(), weights.data_ptr(), experts.data_ptr(),
+                                            counts.data_ptr(), n, e, top_k, 0, 0, logits.stride(0), _lib.dt(logits),
+                                            _lib.stream_ptr())
+        _lib.check(rc, "ocb_moe_router_topk")
+        ids = experts.long()
+        ctx.save_for_backward(scores, ids)
+        ctx.mark_non_differentiable(ids, counts)
+        ctx.in_dtype = logits.dtype
+        return scores, weights, ids, counts
+
+    @staticmethod
+    def backward(ctx, d_scores, d_weights, _ids, _counts):  # type: ignore[override]
+        scores, ids = ctx.saved_tensors
+        g = torch.zeros_like(scores) if d_scores is None else d_scores.float().clone()
+        if d_weights is not None:
+            g.scatter_add_(1, ids, d_weights.float())
+        d_logits = scores * (g - (g * scores).sum(dim=-1, keepdim=True))
+        return d_logits.to(ctx.in_dtype), None
+
+
 class MoERouter(nn.Module):
     def __init__(
         self,
@@ -206,16 +242,29 @@ class MoERouter(nn.Module):
         """
         x = self.jitter(x)
         logits = self.get_expert_logits(x).float()
-        if self.gating_function == MoERouterGatingFunction.softmax:
+        fused = (logits.is_cuda and self.gating_function == MoERouterGatingFunction.softmax and self.bias_gamma is None
+                 and not self.uniform_expert_assignment and self.num_experts <= 1024 and self.top_k <= 32)
+        if fused:
+            flat = logits.reshape(-1, self.num_experts)
+            scores, weights, indices, kernel_counts = _FusedSoftmaxTopK.apply(flat, self.top_k)
+            scores = scores.view_as(logits)
+            weights = weights.view(*logits.shape[:-1], self.top_k)
+            indices = indices.view(*logits.shape[:-1], self.top_k)
+        elif self.gating_function == MoERouterGatingFunction.softmax:
             scores = logits.softmax(dim=-1)
+            weights, indices = self.get_top_k(scores)
         else:
             scores = torch.sigmoid(logits) + 1e-7
-        weights, indices = self.get_top_k(scores)
+            weights, indices = self.get_top_k(scores)
         if self.normalize_expert_weights is not None:
             weights = weights / torch.norm(weights, p=self.normalize_expert_weights, dim=-1, keepdim=True)
         with torch.no_grad():
-            per_seq = moe_ops.batched_histc(indices, self.num_experts).sum(dim=1)  # [B, E]
-            counts = per_seq.sum(dim=0)
+            if fused and self.lb_loss_granularity != MoELoadBalancingLossGranularity.instance:
+                counts = kernel_counts.long()
+                per_seq = counts.unsqueeze(0)  # only the per-instance loss reads the per-sequence histogram
+            else:
+                per_seq = moe_ops.batched_histc(indices, self.num_experts).sum(dim=1)  # [B, E]
+                counts = per_seq.sum(dim=0)
         aux: Optional[torch.Tensor] = None
         if self.training and torch.is_grad_enabled():
             with torch.autocast(enabled=False, device_type=x.device.type):

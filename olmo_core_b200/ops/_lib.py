@@ -36,6 +36,14 @@ class KernelError(RuntimeError):
 _SIGS = {
     "ocb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                       c_int, c_int, c_void_p, c_void_p],
+    "ocb_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                              c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "ocb_moe_router_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                            c_longlong, c_int, c_void_p],
+    "ocb_moe_sort": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ocb_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
+    "ocb_moe_scatter": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
+    "ocb_moe_rowdot": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
     "ocb_rmsnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                         c_longlong, c_float, c_int, c_int, c_void_p],
     "ocb_norm_bwd_partials": [],

@@ -43,6 +43,11 @@ struct GemmParams {
   int M, N, K;
   int group_m;  // rasterisation group size (in M tiles)
   int* status;
+  // Grouped modes (see ocb_grouped_gemm_bf16): row prefix sums of the groups and per-group operand strides.
+  const int* offsets;
+  int num_groups;
+  int b_group_rows;  // rows of the stacked B operand per group (outer TMA coordinate)
+  int c_group_rows;  // rows of the stacked C per group (reduction-grouped mode)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -55,7 +60,67 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gm;
 }
 
-template <int A_MN, int B_MN, int EPI>
+enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_REDUCTION = 2 };
+
+// Everything a role needs to know about one output tile.
+struct TileInfo {
+  int m0, n0;     // tile origin: A rows (or A columns when A is MN-major) and B columns
+  int m_end;      // first row that must not be stored
+  int k0;         // first reduction index
+  int num_kb;     // number of BK-deep blocks of the reduction (0: the tile is all zeros)
+  int k_tail;     // valid reduction rows in the last block (BK when it is full)
+  int b_off;      // added to the outer coordinate of B
+  int c_row_off;  // added to the output row
+};
+
+// Walks the tiles of one CTA (tile = blockIdx.x, += gridDim.x) and resolves them to coordinates. In the grouped modes the
+// group boundaries live in device memory, so the mapping is computed here and not on the host.
+template <int GROUPED>
+struct TileWalker {
+  const GemmParams& p;
+  int tiles_n, tiles_m, tile;
+  int g, base;  // GROUP_ROWS: current group and the index of its first tile
+  __device__ TileWalker(const GemmParams& params) : p(params), g(0), base(0) {
+    tiles_n = (p.N + BN - 1) / BN;
+    tiles_m = (p.M + BM - 1) / BM;
+    tile = blockIdx.x;
+  }
+  __device__ bool next(TileInfo& t) {
+    if (GROUPED == GROUP_NONE) {
+      if (tile >= tiles_m * tiles_n) return false;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+      t.m0 = tm * BM; t.n0 = tn * BN; t.m_end = p.M; t.k0 = 0;
+      t.num_kb = (p.K + BK - 1) / BK; t.k_tail = BK; t.b_off = 0; t.c_row_off = 0;
+    } else if (GROUPED == GROUP_ROWS) {
+      int lo, rows, tm_g;
+      while (true) {
+        if (g >= p.num_groups) return false;
+        lo = p.offsets[g];
+        rows = p.offsets[g + 1] - lo;
+        tm_g = (rows + BM - 1) / BM;
+        if (tile < base + tm_g * tiles_n) break;
+        base += tm_g * tiles_n;
+        ++g;
+      }
+      const int local = tile - base;
+      t.m0 = lo + (local % tm_g) * BM; t.n0 = (local / tm_g) * BN; t.m_end = lo + rows; t.k0 = 0;
+      t.num_kb = (p.K + BK - 1) / BK; t.k_tail = BK; t.b_off = g * p.b_group_rows; t.c_row_off = 0;
+    } else {
+      const int per_group = tiles_m * tiles_n;
+      if (tile >= per_group * p.num_groups) return false;
+      const int grp = tile / per_group, local = tile - grp * per_group;
+      const int lo = p.offsets[grp], rows = p.offsets[grp + 1] - lo;
+      t.m0 = (local % tiles_m) * BM; t.n0 = (local / tiles_m) * BN; t.m_end = p.M; t.k0 = lo;
+      t.num_kb = (rows + BK - 1) / BK; t.k_tail = rows - (t.num_kb - 1) * BK; t.b_off = 0;
+      t.c_row_off = grp * p.c_group_rows;
+    }
+    tile += gridDim.x;
+    return true;
+  }
+};
+
+template <int A_MN, int B_MN, int EPI, int GROUPED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmParams p) {
@@ -70,11 +135,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  const int tiles_m = (p.M + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -107,17 +167,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+      TileWalker<GROUPED> walker(p);
+      TileInfo t;
+      while (ok && walker.next(t)) {
+        const int m0 = t.m0, n0 = t.n0;
+        for (int kb = 0; kb < t.num_kb; ++kb) {
           ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
           if (!ok) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = t.k0 + kb * BK;
+          // The innermost TMA coordinate is k0 for K-major operands (a multiple of 64 there: k0 starts at 0) and
+          // m0 / n0 for MN-major ones (multiples of 64); the group offsets only ever enter an OUTER coordinate.
           if (A_MN == 0) {
             tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
           } else {
@@ -125,10 +187,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (64 * BK * 2), &tma_a, &full_bar[stage], m0 + j * 64, k0);
           }
           if (B_MN == 0) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tma_b, &full_bar[stage], k0, t.b_off + n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (64 * BK * 2), &tma_b, &full_bar[stage], n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (64 * BK * 2), &tma_b, &full_bar[stage], n0 + j * 64, t.b_off + k0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -140,7 +203,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // In the reduction-grouped mode the whole warp runs the loop (all lanes help to blank the ragged tail of a group);
+    // otherwise only the issuing lane does.
+    if (lane == 0 || GROUPED == GROUP_REDUCTION) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       // K-major: rows are 128 B apart inside an 8-row swizzle atom, atoms 1024 B apart (SBO); LBO unused (=1).
       // MN-major: 64-element column chunks are one [64 x BK] TMA box apart (LBO); 8 k-rows = 1024 B (SBO).
@@ -150,29 +215,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      TileWalker<GROUPED> walker(p);
+      TileInfo t;
+      for (; ok && walker.next(t); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
+        if (GROUPED == GROUP_REDUCTION) ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < t.num_kb; ++kb) {
           ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kStatusTimeoutMma);
+          if (GROUPED == GROUP_REDUCTION) ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
-          const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
+          if (GROUPED == GROUP_REDUCTION && A_MN == 1 && kb == t.num_kb - 1 && t.k_tail < BK) {
+            // The last block reaches into the next group's rows. A reduction row is one 128-byte line of each
+            // [BK x 64] box (the swizzle only permutes within a line), so blanking A's lines [k_tail, BK) makes those
+            // rows contribute exactly zero whatever B holds there.
+            const int first = t.k_tail * 8, count = (BK - t.k_tail) * 8;  // in 16-byte units
+            uint8_t* sa_ptr = smem + stage * STAGE_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
+            for (int j = 0; j < BM / 64; ++j) {
+              uint4* box = reinterpret_cast<uint4*>(sa_ptr + j * (64 * BK * 2)) + first;
+              for (int i = lane; i < count; i += 32) box[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
           }
-          umma_commit(&empty_bar[stage]);
+          if (lane == 0) {
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
+            }
+            umma_commit(&empty_bar[stage]);
+          }
+          if (GROUPED == GROUP_REDUCTION) __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);
+        if (ok && lane == 0) {
+          if (t.num_kb > 0) umma_commit(&tfull_bar[acc]);
+          else mbar_arrive(&tfull_bar[acc]);  // nothing was issued for a group without rows
+        }
       }
     }
   } else {
@@ -180,27 +269,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quad = warp & 3;
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    TileWalker<GROUPED> walker(p);
+    TileInfo t;
+    for (; ok && walker.next(t); ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
       ok = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * BM + quad * 32 + lane;
-      const int n0 = tn * BN;
-      const bool row_ok = row < p.M;
+      const int row_in = t.m0 + quad * 32 + lane;
+      const long long row = static_cast<long long>(t.c_row_off) + row_in;
+      const int n0 = t.n0;
+      const bool row_ok = row_in < t.m_end;
+      const bool empty = t.num_kb == 0;  // a group without rows: the accumulator was never written
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
+        if (GROUPED == GROUP_REDUCTION && empty) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
         if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
           if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -232,7 +327,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
         } else {
-          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
           if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
@@ -361,16 +456,21 @@ static int num_sms() {
   return n;
 }
 
-template <int A_MN, int B_MN, int EPI>
+template <int A_MN, int B_MN, int EPI, int GROUPED = GROUP_NONE>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, GROUPED>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -3;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms() ? tiles : num_sms();
+  // Upper bound of the tile count (the exact count of the row-grouped mode depends on device data: every group may
+  // add one partly filled row of tiles).
+  long long tiles_m = (p.M + BM - 1) / BM;
+  if (GROUPED == GROUP_ROWS) tiles_m += p.num_groups;
+  if (GROUPED == GROUP_REDUCTION) tiles_m *= p.num_groups;
+  const long long tiles = tiles_m * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? static_cast<int>(tiles) : num_sms();
   kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -408,6 +508,10 @@ extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.K = K;
   p.group_m = 8;
   p.status = status;
+  p.offsets = nullptr;
+  p.num_groups = 0;
+  p.b_group_rows = 0;
+  p.c_group_rows = 0;
 
 #define OCB_DISPATCH_EPI(AM, BMJ)                                                       \
   switch (epilogue) {                                                                   \
@@ -422,4 +526,69 @@ extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (a_mn_major && b_mn_major) { OCB_DISPATCH_EPI(1, 1) }
   OCB_DISPATCH_EPI(1, 0)
 #undef OCB_DISPATCH_EPI
+}
+
+// Grouped GEMM over rows sorted by group (the experts of a mixture-of-experts layer), one launch for all groups.
+// offsets: int32 [num_groups + 1] DEVICE array of row prefix sums (offsets[0] = 0, offsets[G] <= total_rows); it is read
+// by the kernel, so no host synchronisation is needed to know the group sizes.
+//   mode 1, rows grouped:       C[r, :N] = A[r, :K] * op(B_g) for the rows r of group g.
+//       A: [total_rows, K] K-major. B: the G operands stacked along the outer dimension, K-major ([G*N, K], y = x W^T)
+//       or MN-major ([G*K, N], y = x W). C: [total_rows, N].
+//   mode 2, reduction grouped:  C_g[M, N] (=|+=) A[rows of g, :M]^T * B[rows of g, :N]   (weight gradients)
+//       A: [total_rows, M] and B: [total_rows, N], both MN-major. C: [G*M, N].
+// epilogue as in ocb_gemm_bf16. Groups without rows produce zeros (mode 2) or nothing (mode 1).
+extern "C" int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offsets, int num_groups, int mode,
+                                     int total_rows, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                                     int b_mn_major, int epilogue, int* status, cudaStream_t stream) {
+  if (num_groups <= 0 || total_rows <= 0 || N <= 0) return 0;
+  if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -1;
+  if (mode != GROUP_ROWS && mode != GROUP_REDUCTION) return -1;
+  CUtensorMap ta, tb;
+  GemmParams p;
+  p.C = C;
+  p.ldc = ldc;
+  p.N = N;
+  p.group_m = 8;
+  p.status = status;
+  p.offsets = offsets;
+  p.num_groups = num_groups;
+  p.b_group_rows = 0;
+  p.c_group_rows = 0;
+  if (mode == GROUP_ROWS) {
+    if (K <= 0) return 0;
+    p.M = total_rows;
+    p.K = K;
+    p.b_group_rows = b_mn_major ? K : N;
+    uint64_t adims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(total_rows)};
+    uint64_t astr[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t abox[2] = {64, static_cast<uint32_t>(BM)};
+    if (!get_tensor_map(&ta, A, 2, adims, astr, abox, 2)) return -(1000 + g_last_tmap_error);
+    uint64_t bdims[2] = {static_cast<uint64_t>(b_mn_major ? N : K),
+                         static_cast<uint64_t>(num_groups) * static_cast<uint64_t>(b_mn_major ? K : N)};
+    uint64_t bstr[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t bbox[2] = {64, static_cast<uint32_t>(b_mn_major ? BK : BN)};
+    if (!get_tensor_map(&tb, B, 2, bdims, bstr, bbox, 2)) return -(2000 + g_last_tmap_error);
+    if (epilogue != EPI_BF16) return -1;
+    return b_mn_major ? launch_gemm<0, 1, EPI_BF16, GROUP_ROWS>(ta, tb, p, stream)
+                      : launch_gemm<0, 0, EPI_BF16, GROUP_ROWS>(ta, tb, p, stream);
+  }
+  if (M <= 0) return 0;
+  p.M = M;
+  p.K = total_rows;
+  p.c_group_rows = M;
+  uint64_t adims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(total_rows)};
+  uint64_t astr[1] = {static_cast<uint64_t>(lda) * 2};
+  uint32_t abox[2] = {64, static_cast<uint32_t>(BK)};
+  if (!get_tensor_map(&ta, A, 2, adims, astr, abox, 2)) return -(1000 + g_last_tmap_error);
+  uint64_t bdims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(total_rows)};
+  uint64_t bstr[1] = {static_cast<uint64_t>(ldb) * 2};
+  uint32_t bbox[2] = {64, static_cast<uint32_t>(BK)};
+  if (!get_tensor_map(&tb, B, 2, bdims, bstr, bbox, 2)) return -(2000 + g_last_tmap_error);
+  switch (epilogue) {
+    case EPI_F32_ACC: return launch_gemm<1, 1, EPI_F32_ACC, GROUP_REDUCTION>(ta, tb, p, stream);
+    case EPI_F32: return launch_gemm<1, 1, EPI_F32, GROUP_REDUCTION>(ta, tb, p, stream);
+    case EPI_BF16: return launch_gemm<1, 1, EPI_BF16, GROUP_REDUCTION>(ta, tb, p, stream);
+    default: return -1;
+  }
 }

@@ -19,6 +19,34 @@ extern "C" {
 int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                   long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status, cudaStream_t stream);
 
+// Grouped GEMM over rows sorted by group; offsets: int32 [num_groups + 1] device array of row prefix sums.
+// mode 1: C[r, :N] = A[r, :K] * op(B_g) for the rows r of group g (B: groups stacked along the outer dimension).
+// mode 2: C_g[M, N] (=|+=) A[rows of g, :M]^T * B[rows of g, :N] (both operands MN-major; C: [G*M, N]).
+int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offsets, int num_groups, int mode,
+                          int total_rows, int M, int N, int K, long long lda, long long ldb, long long ldc, int b_mn_major,
+                          int epilogue, int* status, cudaStream_t stream);
+
+// ---- mixture of experts (moe_sm100.cu) --------------------------------------------------------------
+// scores = softmax (mode 0) or sigmoid (mode 1) of logits [n_tokens, n_experts]; weights / experts: [n_tokens, top_k];
+// counts: int32 [n_experts] tokens per expert (may be null); scores may be null.
+int ocb_moe_router_topk(const void* logits, float* scores, float* weights, int* experts, int* counts, int n_tokens,
+                        int n_experts, int top_k, int mode, int normalize, long long ld, int act_dtype,
+                        cudaStream_t stream);
+// Stable counting sort of n routed copies by expert id. dest[j]: row of copy j in the sorted layout; src: its inverse;
+// sorted_experts (may be null): expert of every row; offsets: int32 [n_experts + 1] prefix sums.
+long long ocb_moe_sort_scratch_ints(int n, int n_experts);
+int ocb_moe_sort(const int* experts, int* dest, int* src, int* sorted_experts, int* offsets, int* scratch, int n,
+                 int n_experts, cudaStream_t stream);
+// out[r] = (w[src[r]] *) x[src[r] / top_k]   (bf16 rows, cols % 8 == 0; w fp32 or null)
+int ocb_moe_gather(const void* x, const int* src, const float* w, void* out, int n_rows, int cols, int top_k,
+                   long long ldx, long long ldo, cudaStream_t stream);
+// y[t] = sum_j w[t*top_k + j] * ys[dest[t*top_k + j]]   (fp32 accumulation in a fixed order)
+int ocb_moe_scatter(const void* ys, const int* dest, const float* w, void* y, int n_tokens, int cols, int top_k,
+                    long long lds, long long ldy, cudaStream_t stream);
+// dw[j] = <ys[dest[j]], dy[j / top_k]>
+int ocb_moe_rowdot(const void* ys, const int* dest, const void* dy, float* dw, int n_copies, int cols, int top_k,
+                   long long lds, long long ldd, cudaStream_t stream);
+
 // ---- normalisation / rotary / activation (elementwise.cu) -------------------------------------------
 // y = rmsnorm(x) * w  (+ resid).  x,y,resid: [rows, cols] with row strides ldx/ldy/ldr. w: [cols].
 // group = width of one normalisation group (cols for a full-row norm, head_dim for a per-head norm).

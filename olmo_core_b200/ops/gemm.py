@@ -171,3 +171,58 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
     b = None if bias is None else bias.to(x.dtype)
     return torch.nn.functional.linear(x, full_param(weight, x.dtype), b)
+
+
+def grouped_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, *, trans_b: bool,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """
+    ``y[rows of group g] = x[rows of group g] @ op(W_g)`` in ONE kernel launch. ``x``: ``[R, K]`` bf16 sorted by group;
+    ``offsets``: int32 ``[G + 1]`` device tensor of row prefix sums (read by the kernel: no host sync);
+    ``weight``: the ``G`` operands stacked, ``[G * N, K]`` with ``trans_b`` (``y = x W^T``) else ``[G * K, N]``.
+    """
+    G = offsets.numel() - 1
+    R, K = x.shape
+    N = weight.shape[0] // G if trans_b else weight.shape[1]
+    if (weight.shape[1] if trans_b else weight.shape[0] // G) != K:
+        raise ValueError("grouped GEMM inner dimensions differ")
+    if out is None:
+        out = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)
+    if R == 0:
+        return out
+    if offsets.dtype != torch.int32 or not offsets.is_cuda:
+        raise _lib.KernelError("offsets must be an int32 CUDA tensor")
+    rc = _lib.lib().ocb_grouped_gemm_bf16(
+        x.data_ptr(), weight.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, 1, R, 0, N, K, _row_stride(x),
+        _row_stride(weight), _row_stride(out), 0 if trans_b else 1, _lib.EPI_BF16,
+        _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "ocb_grouped_gemm_bf16")
+    return out
+
+
+def grouped_gemm_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor, *,
+                       accumulate: bool) -> torch.Tensor:
+    """
+    ``out_g (=|+=) a[rows of g]^T @ b[rows of g]`` for every group in one launch: ``a [R, M]``, ``b [R, N]`` bf16 sorted by
+    group, ``out [G * M, N]`` fp32 (or bf16 without accumulation). Groups without rows give zeros (or leave ``out`` as is
+    when accumulating).
+    """
+    G = offsets.numel() - 1
+    R, M = a.shape
+    N = b.shape[1]
+    if out.shape != (G * M, N):
+        raise ValueError(f"output has shape {tuple(out.shape)}, expected {(G * M, N)}")
+    if out.dtype == torch.float32:
+        epi = _lib.EPI_F32_ACC if accumulate else _lib.EPI_F32
+    elif out.dtype == torch.bfloat16 and not accumulate:
+        epi = _lib.EPI_BF16
+    else:
+        raise _lib.KernelError("grouped wgrad writes fp32 (optionally accumulating) or bf16")
+    if R == 0:
+        if not accumulate:
+            out.zero_()
+        return out
+    rc = _lib.lib().ocb_grouped_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, 2, R, M, N, 0, _row_stride(a), _row_stride(b),
+        _row_stride(out), 1, epi, _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "ocb_grouped_gemm_bf16")
+    return out

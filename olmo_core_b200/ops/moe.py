@@ -42,14 +42,47 @@ def batched_histc(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
     return out
 
 
+def _use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0 and t.stride(1) == 1
+
+
+def _inverse(indices: torch.Tensor) -> torch.Tensor:
+    """``dest`` with ``dest[indices[r]] = r``: the row of every routed copy (cached on the tensor by ``indices_and_bins``)."""
+    dest = getattr(indices, "_dest", None)
+    if dest is None:
+        dest = torch.empty_like(indices)
+        dest[indices.long()] = torch.arange(indices.numel(), device=indices.device, dtype=indices.dtype)
+    return dest
+
+
 @torch.no_grad()
 def indices_and_bins(top_experts: torch.Tensor, num_experts: int,
                      counts: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """
     Returns ``(indices, bin_ids, bins)``: the stable sort permutation of the flattened expert ids, the
-    sorted ids themselves, and the inclusive cumulative token count per expert (all int32/int64).
+    sorted ids themselves, and the inclusive cumulative token count per expert (all int32).
+
+    On CUDA this is one counting sort (three small kernels, no host synchronisation). The inverse permutation and the
+    exclusive offsets ``[E + 1]`` that the grouped GEMM consumes ride along as ``indices._dest`` / ``bins._offsets``.
     """
     flat = top_experts.reshape(-1)
+    if flat.is_cuda and num_experts <= 1024:
+        from . import _lib
+
+        n = flat.numel()
+        experts = flat if flat.dtype == torch.int32 else flat.to(torch.int32)
+        dest = torch.empty(n, dtype=torch.int32, device=flat.device)
+        src = torch.empty_like(dest)
+        bin_ids = torch.empty_like(dest)
+        offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=flat.device)
+        scratch = torch.empty(n + ((n + 2047) // 2048) * num_experts, dtype=torch.int32, device=flat.device)
+        rc = _lib.lib().ocb_moe_sort(experts.data_ptr(), dest.data_ptr(), src.data_ptr(), bin_ids.data_ptr(),
+                                     offsets.data_ptr(), scratch.data_ptr(), n, num_experts, _lib.stream_ptr())
+        _lib.check(rc, "ocb_moe_sort")
+        bins = offsets[1:]
+        src._dest = dest  # type: ignore[attr-defined]
+        bins._offsets = offsets  # type: ignore[attr-defined]
+        return src, bin_ids, bins
     bin_ids, indices = torch.sort(flat, stable=True)
     if counts is None:
         counts = histc(flat, num_experts)
@@ -57,19 +90,54 @@ def indices_and_bins(top_experts: torch.Tensor, num_experts: int,
     return indices.to(torch.int32), bin_ids.to(torch.int32), bins.to(torch.int32)
 
 
+def _gather_rows(x: torch.Tensor, indices: torch.Tensor, weights: Optional[torch.Tensor], top_k: int) -> torch.Tensor:
+    from . import _lib
+
+    out = torch.empty((indices.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    rc = _lib.lib().ocb_moe_gather(x.data_ptr(), indices.data_ptr(), _lib.ptr(weights), out.data_ptr(), indices.numel(),
+                                   x.shape[1], top_k, x.stride(0), out.stride(0), _lib.stream_ptr())
+    _lib.check(rc, "ocb_moe_gather")
+    return out
+
+
+def _scatter_rows(ys: torch.Tensor, dest: torch.Tensor, weights: Optional[torch.Tensor], top_k: int) -> torch.Tensor:
+    from . import _lib
+
+    n_tokens = dest.numel() // top_k
+    out = torch.empty((n_tokens, ys.shape[1]), dtype=ys.dtype, device=ys.device)
+    rc = _lib.lib().ocb_moe_scatter(ys.data_ptr(), dest.data_ptr(), _lib.ptr(weights), out.data_ptr(), n_tokens,
+                                    ys.shape[1], top_k, ys.stride(0), out.stride(0), _lib.stream_ptr())
+    _lib.check(rc, "ocb_moe_scatter")
+    return out
+
+
+def _flat_weights(weights: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if weights is None:
+        return None
+    w = weights.reshape(-1)
+    return w.contiguous() if w.dtype == torch.float32 else w.float()
+
+
 class _Gather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, indices, top_k: int):  # type: ignore[override]
+        ctx.n_tokens, ctx.top_k = x.shape[0], top_k
+        if _use_kernels(x) and indices.dtype == torch.int32:
+            ctx.kernel = True
+            ctx.save_for_backward(_inverse(indices))
+            return _gather_rows(x, indices, None, top_k)
+        ctx.kernel = False
         tok = (indices // top_k).long()
         ctx.save_for_backward(tok)
-        ctx.n_tokens = x.shape[0]
         return x.index_select(0, tok)
 
     @staticmethod
     def backward(ctx, grad):  # type: ignore[override]
-        (tok,) = ctx.saved_tensors
+        (saved,) = ctx.saved_tensors
+        if ctx.kernel:  # the k copies of a token sum up: the same kernel as the forward scatter, without weights
+            return _scatter_rows(grad.contiguous(), saved, None, ctx.top_k), None, None
         dx = torch.zeros((ctx.n_tokens, grad.shape[1]), dtype=torch.float32, device=grad.device)
-        dx.index_add_(0, tok, grad.float())
+        dx.index_add_(0, saved, grad.float())
         return dx.to(grad.dtype), None, None
 
 
@@ -82,6 +150,16 @@ def gather(x: torch.Tensor, indices: torch.Tensor, bin_ids: Optional[torch.Tenso
 class _Scatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, indices, weights, top_k: int):  # type: ignore[override]
+        ctx.top_k = top_k
+        ctx.has_w = weights is not None
+        if _use_kernels(x) and indices.dtype == torch.int32:
+            ctx.kernel = True
+            dest = _inverse(indices)
+            w = _flat_weights(weights)
+            ctx.save_for_backward(x, indices, dest, w if w is not None else torch.empty(0, device=x.device))
+            ctx.w_meta = None if weights is None else (weights.shape, weights.dtype)
+            return _scatter_rows(x, dest, w, top_k)
+        ctx.kernel = False
         n_tokens = x.shape[0] // top_k
         idx = indices.long()
         w = None
@@ -91,12 +169,26 @@ class _Scatter(torch.autograd.Function):
         out = torch.zeros((n_tokens, x.shape[1]), dtype=torch.float32, device=x.device)
         out.index_add_(0, idx // top_k, scaled)
         ctx.save_for_backward(x, idx, weights if weights is not None else torch.empty(0, device=x.device))
-        ctx.top_k = top_k
-        ctx.has_w = weights is not None
         return out.to(x.dtype)
 
     @staticmethod
     def backward(ctx, grad):  # type: ignore[override]
+        if ctx.kernel:
+            from . import _lib
+
+            x, indices, dest, w = ctx.saved_tensors
+            grad = grad.contiguous()
+            dx = _gather_rows(grad, indices, w if ctx.has_w else None, ctx.top_k)
+            dw = None
+            if ctx.has_w and ctx.needs_input_grad[2]:
+                shape, dtype = ctx.w_meta
+                dwf = torch.empty(indices.numel(), dtype=torch.float32, device=x.device)
+                rc = _lib.lib().ocb_moe_rowdot(x.data_ptr(), dest.data_ptr(), grad.data_ptr(), dwf.data_ptr(),
+                                               indices.numel(), x.shape[1], ctx.top_k, x.stride(0), grad.stride(0),
+                                               _lib.stream_ptr())
+                _lib.check(rc, "ocb_moe_rowdot")
+                dw = dwf.view(shape).to(dtype)
+            return dx, None, dw, None
         x, idx, weights = ctx.saved_tensors
         g = grad.index_select(0, idx // ctx.top_k)  # gradient of each routed copy before weighting
         dx = g
