@@ -131,8 +131,10 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const W* __restrict__ w, const T* __
 // same thread->column mapping every iteration so dw accumulates in registers (up to kMaxVec vectors).
 constexpr int kMaxVec = 4;
 
-template <typename T, typename W>
-__global__ void __launch_bounds__(kNormThreads)
+// MAXV = 8-element vectors per thread: 2 covers groups up to 4096 columns with two blocks per SM (the persistent grid size); 4 covers up to
+// 8192 columns at one block per SM.
+template <typename T, typename W, int MAXV>
+__global__ void __launch_bounds__(kNormThreads, MAXV == 2 ? 2 : 1)
 rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const W* __restrict__ w,
                    const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ dw_partial,
                    long long n_groups, int groups_per_row, int group, int tpg, long long lddy, long long ldx,
@@ -141,11 +143,14 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const W* _
   const int gpb = kNormThreads / tpg;
   const int gi = threadIdx.x / tpg, ti = threadIdx.x % tpg;
   const int nvec = group / 8;
-  float dw[kMaxVec][8];
+  float dw[MAXV][8], wf[MAXV][8];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i)
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = ti + i * tpg;  // the thread's columns are the same for every group it visits: load w once
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) { dw[i][j] = 0.f; wf[i][j] = 1.f; }
+    if (w != nullptr && v < nvec) Vec8<W>::load(w + v * 8, wf[i]);
+  }
 
   for (long long g0 = static_cast<long long>(blockIdx.x) * gpb; g0 < n_groups; g0 += static_cast<long long>(gridDim.x) * gpb) {
     const long long g = g0 + gi;
@@ -155,44 +160,39 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const W* _
     const T* xr = x + row * ldx + gcol;
     const T* dyr = dy + row * lddy + gcol;
     const float rstd = active ? rstd_in[g] : 0.f;
-    float dot = 0.f;
-    if (active) {
-      for (int v = ti; v < nvec; v += tpg) {
-        float xf[8], gf[8], wf[8];
-        Vec8<T>::load(xr + v * 8, xf);
-        Vec8<T>::load(dyr + v * 8, gf);
-        if (w) {
-          Vec8<W>::load(w + v * 8, wf);
-        } else {
+    // Every load of the row is issued before anything is consumed (2 * MAXV 16-byte loads in flight per thread); the
+    // values stay in registers for the second phase, so global memory is read exactly once.
+    float xf[MAXV][8], gf[MAXV][8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) wf[j] = 1.f;
-        }
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = ti + i * tpg;
+      if (active && v < nvec) {
+        Vec8<T>::load(xr + v * 8, xf[i]);
+        Vec8<T>::load(dyr + v * 8, gf[i]);
+      } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dot += gf[j] * wf[j] * xf[j] * rstd;
+        for (int j = 0; j < 8; ++j) xf[i][j] = gf[i][j] = 0.f;
       }
     }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += gf[i][j] * wf[i][j] * xf[i][j] * rstd;
     dot = group_sum(dot, tpg, sbuf);
     const float c = dot / static_cast<float>(group);
     if (active) {
       T* dxr = dx + row * lddx + gcol;
 #pragma unroll
-      for (int i = 0; i < kMaxVec; ++i) {
+      for (int i = 0; i < MAXV; ++i) {
         const int v = ti + i * tpg;
         if (v < nvec) {
-          float xf[8], gf[8], wf[8], o[8];
-          Vec8<T>::load(xr + v * 8, xf);
-          Vec8<T>::load(dyr + v * 8, gf);
-          if (w) {
-            Vec8<W>::load(w + v * 8, wf);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) wf[j] = 1.f;
-          }
+          float o[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float xhat = xf[j] * rstd;
-            o[j] = rstd * (gf[j] * wf[j] - xhat * c);
-            dw[i][j] += gf[j] * xhat;
+            const float xhat = xf[i][j] * rstd;
+            o[j] = rstd * (gf[i][j] * wf[i][j] - xhat * c);
+            dw[i][j] += gf[i][j] * xhat;
           }
           Vec8<T>::store(dxr + v * 8, o);
         }
@@ -204,7 +204,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const W* _
     // so they are combined with atomics on the block's private partial row (zeroed by the launcher).
     float* prow = dw_partial + static_cast<long long>(blockIdx.x) * group;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int v = ti + i * tpg;
       if (v < nvec) {
 #pragma unroll
@@ -217,15 +217,26 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const W* _
   }
 }
 
+// out[c] (+)= sum_p partial[p, c]. Block = 32 columns x 32 slices of the partial rows: every thread adds up its slice with
+// independent loads, the slices meet in shared memory, and the summation order is fixed (deterministic).
 template <typename O>
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, O* __restrict__ out, int n_partial, int cols,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(1024)
+reduce_partials_kernel(const float* __restrict__ partial, O* __restrict__ out, int n_partial, int cols, int accumulate) {
+  __shared__ float tile[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < n_partial; ++p) s += partial[static_cast<long long>(p) * cols + c];
-  if (accumulate) s += static_cast<float>(out[c]);
-  out[c] = static_cast<O>(s);
+  if (c < cols) {
+    for (int p = threadIdx.y; p < n_partial; p += 32) s += partial[static_cast<long long>(p) * cols + c];
+  }
+  tile[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += tile[y][threadIdx.x];
+    if (accumulate) t += static_cast<float>(out[c]);
+    out[c] = static_cast<O>(t);
+  }
 }
 
 // ----------------------------------------------------------------------------------------------------
@@ -309,11 +320,15 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
 #pragma unroll
             for (int j = 0; j < 8; ++j) { ya[j] = xa[i][j]; yb[j] = xb[i][j]; }
           }
-          float oa[8], ob[8];
+          float oa[8], ob[8], c_lo[8], s_lo[8], c_hi[8], s_hi[8];
+          Vec8<float>::load(cr + o, c_lo);
+          Vec8<float>::load(sr + o, s_lo);
+          Vec8<float>::load(cr + half + o, c_hi);
+          Vec8<float>::load(sr + half + o, s_hi);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            oa[j] = ya[j] * cr[o + j] - yb[j] * sr[o + j];
-            ob[j] = yb[j] * cr[half + o + j] + ya[j] * sr[half + o + j];
+            oa[j] = ya[j] * c_lo[j] - yb[j] * s_lo[j];
+            ob[j] = yb[j] * c_hi[j] + ya[j] * s_hi[j];
           }
           Vec8<T>::store(outr + h * head_dim + o, oa);
           Vec8<T>::store(outr + h * head_dim + half + o, ob);
@@ -331,13 +346,17 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
         const int h = on ? pv / pv_per_head : 0, o = on ? (pv % pv_per_head) * 8 : 0;
         float dot = 0.f;
         if (on) {
-          float da[8], db[8];
+          float da[8], db[8], c_lo[8], s_lo[8], c_hi[8], s_hi[8];
           Vec8<T>::load(inr + h * head_dim + o, da);
           Vec8<T>::load(inr + h * head_dim + half + o, db);
+          Vec8<float>::load(cr + o, c_lo);
+          Vec8<float>::load(sr + o, s_lo);
+          Vec8<float>::load(cr + half + o, c_hi);
+          Vec8<float>::load(sr + half + o, s_hi);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {  // transpose of the rotation
-            ga[i][j] = da[j] * cr[o + j] + db[j] * sr[half + o + j];
-            gb[i][j] = db[j] * cr[half + o + j] - da[j] * sr[o + j];
+            ga[i][j] = da[j] * c_lo[j] + db[j] * s_hi[j];
+            gb[i][j] = db[j] * c_hi[j] - da[j] * s_lo[j];
           }
           if (norm_mode != 0) {
             float xa[8], xb[8], wa[8], wb[8];
@@ -705,11 +724,11 @@ static inline int ew_grid(long long work_items, int threads) {
   return static_cast<int>(b);
 }
 
-static inline int pick_tpg(int group) {
+static inline int pick_tpg(int group, int max_vec = kMaxVec) {
   // threads per normalisation group: enough that each thread sees <= kMaxVec vectors where possible
   int nvec = group / 8;
   int tpg = 1;
-  while (tpg < kNormThreads && tpg * kMaxVec < nvec) tpg <<= 1;
+  while (tpg < kNormThreads && tpg * max_vec < nvec) tpg <<= 1;
   if (tpg < 8 && nvec >= 8) tpg = 8;
   while (tpg > nvec && tpg > 1) tpg >>= 1;
   return tpg;
@@ -761,8 +780,9 @@ extern "C" int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   if (group <= 0 || cols % group != 0 || group % 8 != 0) return -1;
   const int gpr = cols / group;
   const long long n_groups = static_cast<long long>(rows) * gpr;
-  const int tpg = pick_tpg(group);
-  if ((group / 8 + tpg - 1) / tpg > kMaxVec) return -1;  // group too wide for the register-resident dw
+  const int maxv = group <= 2 * kNormThreads * 8 ? 2 : kMaxVec;
+  const int tpg = pick_tpg(group, maxv);
+  if ((group / 8 + tpg - 1) / tpg > maxv) return -1;  // group too wide for the register-resident row
   const int gpb = kNormThreads / tpg;
   long long want = (n_groups + gpb - 1) / gpb;
   const int grid = static_cast<int>(want < kNormBwdBlocks ? want : kNormBwdBlocks);
@@ -771,9 +791,14 @@ extern "C" int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
       return -4;
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
-    rmsnorm_bwd_kernel<T, W><<<grid, kNormThreads, 0, stream>>>(
-        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
-        dw_partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+    if (maxv == 2)
+      rmsnorm_bwd_kernel<T, W, 2><<<grid, kNormThreads, 0, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+          dw_partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+    else
+      rmsnorm_bwd_kernel<T, W, kMaxVec><<<grid, kNormThreads, 0, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+          dw_partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
   })
   return OCB_CHECK_LAUNCH();
 }
@@ -781,7 +806,8 @@ extern "C" int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
 extern "C" int ocb_reduce_partials(const float* partial, void* out, int n_partial, int cols, int accumulate,
                                    int out_dtype, cudaStream_t stream) {
   if (cols <= 0) return 0;
-  const int threads = 256, grid = (cols + threads - 1) / threads;
+  const dim3 threads(32, 32);
+  const int grid = (cols + 31) / 32;
   if (out_dtype == OCB_F32)
     reduce_partials_kernel<float><<<grid, threads, 0, stream>>>(partial, static_cast<float*>(out), n_partial, cols, accumulate);
   else
@@ -987,8 +1013,9 @@ extern "C" int ocb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
   if (dw != nullptr && group > OCB_STATIC_SCRATCH_MAX_GROUP) return OCB_ERR_STATIC_SCRATCH_TOO_SMALL;
   const int gpr = cols / group;
   const long long n_groups = static_cast<long long>(rows) * gpr;
-  const int tpg = pick_tpg(group);
-  if ((group / 8 + tpg - 1) / tpg > kMaxVec) return -1;
+  const int maxv = group <= 2 * kNormThreads * 8 ? 2 : kMaxVec;
+  const int tpg = pick_tpg(group, maxv);
+  if ((group / 8 + tpg - 1) / tpg > maxv) return -1;
   const int gpb = kNormThreads / tpg;
   const long long want = (n_groups + gpb - 1) / gpb;
   const int grid = static_cast<int>(want < kNormBwdBlocks ? want : kNormBwdBlocks);
@@ -1000,13 +1027,19 @@ extern "C" int ocb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
     if (cudaMemsetAsync(partial, 0, sizeof(float) * static_cast<size_t>(grid) * group, stream) != cudaSuccess) return -4;
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
-    rmsnorm_bwd_kernel<T, W><<<grid, kNormThreads, 0, stream>>>(
-        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
-        partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+    if (maxv == 2)
+      rmsnorm_bwd_kernel<T, W, 2><<<grid, kNormThreads, 0, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+          partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+    else
+      rmsnorm_bwd_kernel<T, W, kMaxVec><<<grid, kNormThreads, 0, stream>>>(
+          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+          partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
   })
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (dw != nullptr) {
-    const int threads = 256, rgrid = (group + threads - 1) / threads;
+    const dim3 threads(32, 32);
+    const int rgrid = (group + 31) / 32;
     if (dw_dtype == OCB_F32)
       reduce_partials_kernel<float><<<rgrid, threads, 0, stream>>>(partial, static_cast<float*>(dw), grid, group, dw_accumulate);
     else
