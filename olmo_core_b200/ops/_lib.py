@@ -27,6 +27,7 @@ EPI_BF16 = 0
 EPI_F32_ACC = 1
 EPI_F32 = 2
 EPI_BF16_ACC = 3
+EPI_F32_RED_PEER = 4
 
 
 class KernelError(RuntimeError):
@@ -38,6 +39,8 @@ _SIGS = {
                       c_int, c_int, c_void_p, c_void_p],
     "ocb_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
                               c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "ocb_gemm_bf16_tp": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+                         c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ocb_moe_router_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                             c_longlong, c_int, c_void_p],
     "ocb_moe_sort": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -35,7 +35,8 @@ constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ 
 constexpr int GEMM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
-enum : int { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_BF16_ACC = 3 };
+enum : int { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_BF16_ACC = 3, EPI_F32_RED_PEER = 4 };
+constexpr int MAX_PEERS = 8;
 
 struct GemmParams {
   void* C;
@@ -48,6 +49,11 @@ struct GemmParams {
   int num_groups;
   int b_group_rows;  // rows of the stacked B operand per group (outer TMA coordinate)
   int c_group_rows;  // rows of the stacked C per group (reduction-grouped mode)
+  // Tensor-parallel modes: A gathered from the peers' row shards (GROUP_GATHER) and / or C reduced into the row shard of
+  // its owner (EPI_F32_RED_PEER). m_local = rows per rank.
+  const CUtensorMap* peer_a_maps;  // [world] tensor maps of the peers' A shards, in global memory
+  float* peer_c[MAX_PEERS];        // the peers' fp32 output shards
+  int world, rank, m_local;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -60,7 +66,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gm;
 }
 
-enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_REDUCTION = 2 };
+enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_REDUCTION = 2, GROUP_GATHER = 3 };
 
 // Everything a role needs to know about one output tile.
 struct TileInfo {
@@ -71,6 +77,8 @@ struct TileInfo {
   int k_tail;     // valid reduction rows in the last block (BK when it is full)
   int b_off;      // added to the outer coordinate of B
   int c_row_off;  // added to the output row
+  int a_map;      // GROUP_GATHER: whose shard of A the tile reads
+  int a_row0;     // GROUP_GATHER: first row inside that shard
 };
 
 // Walks the tiles of one CTA (tile = blockIdx.x, += gridDim.x) and resolves them to coordinates. In the grouped modes the
@@ -86,10 +94,21 @@ struct TileWalker {
     tile = blockIdx.x;
   }
   __device__ bool next(TileInfo& t) {
-    if (GROUPED == GROUP_NONE) {
+    if (GROUPED == GROUP_NONE || GROUPED == GROUP_GATHER) {
       if (tile >= tiles_m * tiles_n) return false;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+      if (p.world > 1) {
+        // Every rank starts at a different row shard (its own when gathering, its neighbour's when scattering), so that
+        // at any moment the ranks pull from / push to different peers.
+        const int per_shard = p.m_local / BM;
+        const int shift = (GROUPED == GROUP_GATHER ? p.rank : p.rank + 1) * per_shard;
+        tm = (tm + shift) % tiles_m;
+      }
+      if (GROUPED == GROUP_GATHER) {
+        t.a_map = (tm * BM) / p.m_local;
+        t.a_row0 = tm * BM - t.a_map * p.m_local;
+      }
       t.m0 = tm * BM; t.n0 = tn * BN; t.m_end = p.M; t.k0 = 0;
       t.num_kb = (p.K + BK - 1) / BK; t.k_tail = BK; t.b_off = 0; t.c_row_off = 0;
     } else if (GROUPED == GROUP_ROWS) {
@@ -180,7 +199,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const int k0 = t.k0 + kb * BK;
           // The innermost TMA coordinate is k0 for K-major operands (a multiple of 64 there: k0 starts at 0) and
           // m0 / n0 for MN-major ones (multiples of 64); the group offsets only ever enter an OUTER coordinate.
-          if (A_MN == 0) {
+          if (GROUPED == GROUP_GATHER) {
+            // A tile of a peer's shard, read straight from that GPU's memory (a plain TMA load, no multicast).
+            tma_load_2d(sa, &p.peer_a_maps[t.a_map], &full_bar[stage], k0, t.a_row0);
+          } else if (A_MN == 0) {
             tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
           } else {
 #pragma unroll
@@ -323,6 +345,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 float v = __uint_as_float(r[j]);
                 if (EPI == EPI_BF16_ACC) v += __bfloat162float(dst[j]);
                 dst[j] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        } else if (EPI == EPI_F32_RED_PEER) {
+          // The row belongs to the shard of rank `owner`: add the partial product into that GPU's buffer with fire-and-
+          // forget fp32 reductions over NVLink (no reply is awaited, so the next tile's loads are not held up).
+          const int owner = row_in / p.m_local;
+          float* dst = p.peer_c[owner] + static_cast<long long>(row_in - owner * p.m_local) * p.ldc + col;
+          if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * v),
+                           "f"(__uint_as_float(r[4 * v + 0])), "f"(__uint_as_float(r[4 * v + 1])),
+                           "f"(__uint_as_float(r[4 * v + 2])), "f"(__uint_as_float(r[4 * v + 3]))
+                           : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < p.N) {
+                asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dst + j), "f"(__uint_as_float(r[j])) : "memory");
               }
             }
           }
@@ -512,6 +555,10 @@ extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.num_groups = 0;
   p.b_group_rows = 0;
   p.c_group_rows = 0;
+  p.peer_a_maps = nullptr;
+  p.world = 1;
+  p.rank = 0;
+  p.m_local = M;
 
 #define OCB_DISPATCH_EPI(AM, BMJ)                                                       \
   switch (epilogue) {                                                                   \
@@ -555,6 +602,10 @@ extern "C" int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, cons
   p.num_groups = num_groups;
   p.b_group_rows = 0;
   p.c_group_rows = 0;
+  p.peer_a_maps = nullptr;
+  p.world = 1;
+  p.rank = 0;
+  p.m_local = 0;
   if (mode == GROUP_ROWS) {
     if (K <= 0) return 0;
     p.M = total_rows;
@@ -591,4 +642,97 @@ extern "C" int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, cons
     case EPI_BF16: return launch_gemm<1, 1, EPI_BF16, GROUP_REDUCTION>(ta, tb, p, stream);
     default: return -1;
   }
+}
+
+// Device copies of the per-peer tensor maps of ocb_gemm_bf16_tp: a ring of slots, one per call. A slot is rewritten only
+// after 64 further calls, and the copy into it is ordered on the caller's stream behind the kernels that read it.
+static CUtensorMap* peer_map_slot(const CUtensorMap* host_maps, int world, cudaStream_t stream) {
+  constexpr int kSlots = 64;
+  static CUtensorMap* ring = nullptr;
+  static int next = 0;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> g(mu);
+  if (ring == nullptr && cudaMalloc(&ring, sizeof(CUtensorMap) * MAX_PEERS * kSlots) != cudaSuccess) return nullptr;
+  CUtensorMap* slot = ring + static_cast<size_t>(next) * MAX_PEERS;
+  next = (next + 1) % kSlots;
+  if (cudaMemcpyAsync(slot, host_maps, sizeof(CUtensorMap) * world, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return nullptr;
+  return slot;
+}
+
+// Tensor-parallel GEMMs that move their operand / result over NVLink from inside the kernel, tile by tile.
+//   gather_a != 0 (all-gather -> GEMM):  C[world*m_local, N] = [A_0; ...; A_{world-1}] * op(B), where A_r ([m_local, K],
+//       K-major, row stride lda) lives on rank r: a_ptrs[r] is its address as mapped on this GPU. Every tile loads its
+//       A block straight from the owner's memory with a plain (non-multicast) TMA load. C is local (epilogue bf16/fp32).
+//   scatter_c != 0 (GEMM -> reduce-scatter):  A ([world*m_local, K] local, K-major) * op(B) is a partial sum; rows
+//       [r*m_local, (r+1)*m_local) are added into c_ptrs[r] (fp32 [m_local, N], row stride ldc, zeroed by the owner
+//       beforehand) with vector reductions over NVLink. The sum is complete after a barrier across the ranks.
+// m_local must be a multiple of 128. The callers order these kernels against the peers with their own barriers.
+extern "C" int ocb_gemm_bf16_tp(const void* const* a_ptrs, const void* B, void* const* c_ptrs, int m_local, int N, int K,
+                                long long lda, long long ldb, long long ldc, int world, int rank, int gather_a,
+                                int scatter_c, int b_mn_major, int epilogue, int* status, cudaStream_t stream) {
+  if (m_local <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || (m_local % BM) != 0) return -1;
+  if (gather_a == scatter_c) return -1;  // exactly one of the two fusions per call
+  if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  const int M = world * m_local;
+  GemmParams p;
+  p.ldc = ldc;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.group_m = 8;
+  p.status = status;
+  p.offsets = nullptr;
+  p.num_groups = 0;
+  p.b_group_rows = 0;
+  p.c_group_rows = 0;
+  p.peer_a_maps = nullptr;
+  p.world = world;
+  p.rank = rank;
+  p.m_local = m_local;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(b_mn_major ? N : K), static_cast<uint64_t>(b_mn_major ? K : N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(b_mn_major ? BK : BN)};
+    if (!get_tensor_map(&tb, B, 2, dims, str, box, 2)) return -(2000 + g_last_tmap_error);
+  }
+  if (gather_a) {
+    CUtensorMap maps[MAX_PEERS];
+    for (int r = 0; r < world; ++r) {
+      if (reinterpret_cast<uintptr_t>(a_ptrs[r]) & 15) return -1;
+      uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(m_local)};
+      uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+      uint32_t box[2] = {64, static_cast<uint32_t>(BM)};
+      if (!get_tensor_map(&maps[r], a_ptrs[r], 2, dims, str, box, 2)) return -(1000 + g_last_tmap_error);
+    }
+    ta = maps[rank];
+    p.peer_a_maps = peer_map_slot(maps, world, stream);
+    if (p.peer_a_maps == nullptr) return -3;
+    p.C = c_ptrs[0];
+    if (b_mn_major) {
+      switch (epilogue) {
+        case EPI_BF16: return launch_gemm<0, 1, EPI_BF16, GROUP_GATHER>(ta, tb, p, stream);
+        case EPI_F32: return launch_gemm<0, 1, EPI_F32, GROUP_GATHER>(ta, tb, p, stream);
+        default: return -1;
+      }
+    }
+    switch (epilogue) {
+      case EPI_BF16: return launch_gemm<0, 0, EPI_BF16, GROUP_GATHER>(ta, tb, p, stream);
+      case EPI_F32: return launch_gemm<0, 0, EPI_F32, GROUP_GATHER>(ta, tb, p, stream);
+      default: return -1;
+    }
+  }
+  if (reinterpret_cast<uintptr_t>(a_ptrs[0]) & 15) return -1;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(BM)};
+    if (!get_tensor_map(&ta, a_ptrs[0], 2, dims, str, box, 2)) return -(1000 + g_last_tmap_error);
+  }
+  p.C = nullptr;
+  for (int r = 0; r < world; ++r) p.peer_c[r] = static_cast<float*>(c_ptrs[r]);
+  return b_mn_major ? launch_gemm<0, 1, EPI_F32_RED_PEER, GROUP_NONE>(ta, tb, p, stream)
+                    : launch_gemm<0, 0, EPI_F32_RED_PEER, GROUP_NONE>(ta, tb, p, stream);
 }

@@ -26,6 +26,13 @@ int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* offs
                           int total_rows, int M, int N, int K, long long lda, long long ldb, long long ldc, int b_mn_major,
                           int epilogue, int* status, cudaStream_t stream);
 
+// Tensor-parallel GEMMs with the collective inside the kernel (m_local % 128 == 0, world <= 8):
+// gather_a: C[world*m_local, N] = [A_0; ...; A_{world-1}] * op(B), A_r read from a_ptrs[r] (peer memory) tile by tile.
+// scatter_c: rows of rank r of A * op(B) are added into c_ptrs[r] (fp32 [m_local, N]) with reductions over NVLink.
+int ocb_gemm_bf16_tp(const void* const* a_ptrs, const void* B, void* const* c_ptrs, int m_local, int N, int K,
+                     long long lda, long long ldb, long long ldc, int world, int rank, int gather_a, int scatter_c,
+                     int b_mn_major, int epilogue, int* status, cudaStream_t stream);
+
 // ---- mixture of experts (moe_sm100.cu) --------------------------------------------------------------
 // scores = softmax (mode 0) or sigmoid (mode 1) of logits [n_tokens, n_experts]; weights / experts: [n_tokens, top_k];
 // counts: int32 [n_experts] tokens per expert (may be null); scores may be null.

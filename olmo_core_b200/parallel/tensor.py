@@ -271,6 +271,35 @@ def shard_feed_forward_(ff: nn.Module, tp_mesh) -> None:
         ff.hidden_size //= ws
     ff.tp_group = group  # type: ignore[attr-defined]
     _wrap_forward(ff, group)
+    _fuse_feed_forward(ff, group)
+
+
+def _fuse_feed_forward(ff: nn.Module, group) -> None:
+    """
+    Route a bias-free SwiGLU MLP through the kernels that carry the collective themselves: both up-projections gather
+    their input from the peers while they run, the down-projection reduces its partial sums into the owners' shards from
+    its epilogue. The MLP acts on rows independently, so the rank-major row order of the gathered activations needs no
+    re-ordering. Anything else (biases, other activations, CPU tensors, no peer memory) keeps the wrapped forward.
+    """
+    from ..nn.feed_forward import ActivationFunction
+    from ..ops.elementwise import swiglu
+    from .tp_fused import fused_tp_available, gather_linear, linear_reduce_scatter
+
+    wrapped = ff.forward
+    if (getattr(ff, "activation", None) != ActivationFunction.silu
+            or any(getattr(getattr(ff, n), "bias", None) is not None for n in ("w1", "w2", "w3"))):
+        return
+
+    def forward(x, *args, **kwargs):
+        rows = x.numel() // x.shape[-1]
+        if args or kwargs or not fused_tp_available(x, group, rows):
+            return wrapped(x, *args, **kwargs)
+        a = gather_linear(x, ff.w1.weight, group, "ffn-up")
+        b = gather_linear(x, ff.w3.weight, group, "ffn-gate")
+        y = linear_reduce_scatter(swiglu(a, b), ff.w2.weight, group, "ffn-down")
+        return y.view(x.shape)
+
+    ff.forward = forward  # type: ignore[method-assign]
 
 
 def shard_block_(block: nn.Module, tp_mesh) -> None:

@@ -74,3 +74,60 @@ def test_fused_optimizer_collectives_match_nccl(tmp_path, multimem):
         assert a == pytest.approx(b, rel=1e-4)
     for name, want in ref["params"].items():
         torch.testing.assert_close(got["params"][name], want, rtol=0, atol=1e-2, msg=name)
+
+
+def _tp_fused_worker():
+    """All-gather -> GEMM and GEMM -> reduce-scatter kernels against NCCL collectives around a plain GEMM, with grads."""
+    import torch.distributed as dist
+
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.parallel.tp_fused import fused_tp_available, gather_linear, linear_reduce_scatter
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    group = dist.group.WORLD
+    m, K, N = 256, 320, 384  # rows per rank, model width, width of this rank's weight slice
+    gen = torch.Generator().manual_seed(7)
+    x_all = torch.randn(ws, m, K, generator=gen)
+    w_cols = torch.randn(ws, N, K, generator=gen) * 0.05  # column-parallel slices (one per rank)
+    w_rows = torch.randn(ws, K, N, generator=gen) * 0.05  # row-parallel slices: rank r holds [K, N_r]
+    x = x_all[rank].to(dev, torch.bfloat16).requires_grad_(True)
+    assert fused_tp_available(x, group, m)
+
+    # --- gather_linear: y = [x_0; x_1; ...] @ W_r^T ---------------------------------------------------------
+    w1 = w_cols[rank].to(dev, torch.bfloat16).requires_grad_(True)
+    y = gather_linear(x, w1, group, "t1")
+    ref_x = x_all.to(torch.bfloat16).float().reshape(ws * m, K)
+    ref_y = ref_x @ w_cols[rank].to(torch.bfloat16).float().t()
+    torch.testing.assert_close(y.float().cpu(), ref_y, rtol=2e-2, atol=2e-2)
+    g = torch.randn(ws * m, N, generator=torch.Generator().manual_seed(20 + rank))
+    y.backward(g.to(dev, torch.bfloat16))
+    # dx_r = sum over ranks q of (g_q @ W_q)[rows of r]
+    gb = g.to(torch.bfloat16).float()
+    partial = (gb @ w_cols[rank].to(torch.bfloat16).float()).to(dev)
+    dist.all_reduce(partial)
+    torch.testing.assert_close(x.grad.float(), partial[rank * m:(rank + 1) * m], rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(w1.grad.float().cpu(), gb.t() @ ref_x, rtol=3e-2, atol=6e-2)
+
+    # --- linear_reduce_scatter: y_r = sum_q (h_q @ V_q^T)[rows of r] ---------------------------------------
+    h = torch.randn(ws * m, N, generator=torch.Generator().manual_seed(40 + rank))
+    hq = h.to(dev, torch.bfloat16).requires_grad_(True)
+    v = w_rows[rank].to(dev, torch.bfloat16).requires_grad_(True)  # [K, N]: y = h @ v^T
+    out = linear_reduce_scatter(hq, v, group, "t2")
+    full = (h.to(torch.bfloat16).float() @ w_rows[rank].to(torch.bfloat16).float().t()).to(dev)
+    dist.all_reduce(full)
+    torch.testing.assert_close(out.float(), full[rank * m:(rank + 1) * m], rtol=3e-2, atol=3e-2)
+    go = torch.randn(m, K, generator=torch.Generator().manual_seed(60 + rank)).to(dev, torch.bfloat16)
+    out.backward(go)
+    go_all = [torch.empty_like(go) for _ in range(ws)]
+    dist.all_gather(go_all, go)
+    go_full = torch.cat(go_all).float()
+    torch.testing.assert_close(hq.grad.float(), go_full @ v.detach().float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(v.grad.float(), go_full.t() @ hq.detach().float(), rtol=3e-2, atol=6e-2)
+    _lib.check_device_status()
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+def test_tensor_parallel_fused_collective_gemms():
+    run_distributed_test(_tp_fused_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
