@@ -98,6 +98,12 @@ class _Proj(nn.Module):
             nn.init.trunc_normal_(self.weight, std=0.02, a=-0.06, b=0.06)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        f8 = getattr(self, "float8", None)  # set by Float8Config.apply_float8_linear
+        if f8 is not None and x.is_cuda and x.numel() // x.shape[-1] % 16 == 0:
+            from ..ops.fp8 import fp8_linear
+
+            return fp8_linear(x, self.weight, self.bias, pow2_scales=bool(f8.get("pow2_scales")),
+                              wgrad_high_precision=str(f8.get("recipe")) == "rowwise_with_gw_hp")
         return linear(x, self.weight, self.bias)
 
     def extra_repr(self) -> str:

@@ -41,6 +41,11 @@ _SIGS = {
                               c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "ocb_gemm_bf16_tp": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ocb_gemm_fp8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                     c_longlong, c_int, c_void_p, c_void_p],
+    "ocb_quantize_e4m3_rowwise": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p],
+    "ocb_quantize_e4m3_colwise_t": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int,
+                                    c_void_p],
     "ocb_moe_router_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                             c_longlong, c_int, c_void_p],
     "ocb_moe_sort": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

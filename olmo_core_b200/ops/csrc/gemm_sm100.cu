@@ -54,6 +54,10 @@ struct GemmParams {
   const CUtensorMap* peer_a_maps;  // [world] tensor maps of the peers' A shards, in global memory
   float* peer_c[MAX_PEERS];        // the peers' fp32 output shards
   int world, rank, m_local;
+  // 8-bit operands: elements per 128-byte line of a tile (BK for bf16, 2 * BK for e4m3) and the de-quantisation scales.
+  int bk;
+  const float* scale_a;  // [M] one per row of A
+  const float* scale_b;  // [N] one per row of B (= output column)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -110,7 +114,7 @@ struct TileWalker {
         t.a_row0 = tm * BM - t.a_map * p.m_local;
       }
       t.m0 = tm * BM; t.n0 = tn * BN; t.m_end = p.M; t.k0 = 0;
-      t.num_kb = (p.K + BK - 1) / BK; t.k_tail = BK; t.b_off = 0; t.c_row_off = 0;
+      t.num_kb = (p.K + p.bk - 1) / p.bk; t.k_tail = BK; t.b_off = 0; t.c_row_off = 0;
     } else if (GROUPED == GROUP_ROWS) {
       int lo, rows, tm_g;
       while (true) {
@@ -124,7 +128,7 @@ struct TileWalker {
       }
       const int local = tile - base;
       t.m0 = lo + (local % tm_g) * BM; t.n0 = (local / tm_g) * BN; t.m_end = lo + rows; t.k0 = 0;
-      t.num_kb = (p.K + BK - 1) / BK; t.k_tail = BK; t.b_off = g * p.b_group_rows; t.c_row_off = 0;
+      t.num_kb = (p.K + p.bk - 1) / p.bk; t.k_tail = BK; t.b_off = g * p.b_group_rows; t.c_row_off = 0;
     } else {
       const int per_group = tiles_m * tiles_n;
       if (tile >= per_group * p.num_groups) return false;
@@ -139,7 +143,7 @@ struct TileWalker {
   }
 };
 
-template <int A_MN, int B_MN, int EPI, int GROUPED>
+template <int A_MN, int B_MN, int EPI, int GROUPED, int FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmParams p) {
@@ -196,7 +200,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          const int k0 = t.k0 + kb * BK;
+          const int k0 = t.k0 + kb * p.bk;  // in elements: 64 two-byte or 128 one-byte elements fill the 128-byte line
           // The innermost TMA coordinate is k0 for K-major operands (a multiple of 64 there: k0 starts at 0) and
           // m0 / n0 for MN-major ones (multiples of 64); the group offsets only ever enter an OUTER coordinate.
           if (GROUPED == GROUP_GATHER) {
@@ -228,7 +232,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // In the reduction-grouped mode the whole warp runs the loop (all lanes help to blank the ragged tail of a group);
     // otherwise only the issuing lane does.
     if (lane == 0 || GROUPED == GROUP_REDUCTION) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = FP8 ? make_idesc_e4m3(BM, BN) : make_idesc_bf16(BM, BN, A_MN, B_MN);
       // K-major: rows are 128 B apart inside an 8-row swizzle atom, atoms 1024 B apart (SBO); LBO unused (=1).
       // MN-major: 64-element column chunks are one [64 x BK] TMA box apart (LBO); 8 k-rows = 1024 B (SBO).
       constexpr uint32_t a_lbo = A_MN ? 64 * BK * 2 : 16, b_lbo = B_MN ? 64 * BK * 2 : 16;
@@ -273,7 +277,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
-              umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
+              if (FP8) umma_f8_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
+              else umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
             }
             umma_commit(&empty_bar[stage]);
           }
@@ -316,6 +321,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
+        if (FP8) {
+          // De-quantise: the operands were scaled per row of A and per row of B (per output column).
+          const float sa = p.scale_a[row_in];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float sb = col + j < p.N ? p.scale_b[col + j] : 0.f;
+            r[j] = __float_as_uint(__uint_as_float(r[j]) * sa * sb);
+          }
+        }
         if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
           if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -499,9 +513,9 @@ static int num_sms() {
   return n;
 }
 
-template <int A_MN, int B_MN, int EPI, int GROUPED = GROUP_NONE>
+template <int A_MN, int B_MN, int EPI, int GROUPED = GROUP_NONE, int FP8 = 0>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, GROUPED>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, GROUPED, FP8>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -3;
@@ -550,6 +564,9 @@ extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.N = N;
   p.K = K;
   p.group_m = 8;
+  p.bk = BK;
+  p.scale_a = nullptr;
+  p.scale_b = nullptr;
   p.status = status;
   p.offsets = nullptr;
   p.num_groups = 0;
@@ -597,6 +614,9 @@ extern "C" int ocb_grouped_gemm_bf16(const void* A, const void* B, void* C, cons
   p.ldc = ldc;
   p.N = N;
   p.group_m = 8;
+  p.bk = BK;
+  p.scale_a = nullptr;
+  p.scale_b = nullptr;
   p.status = status;
   p.offsets = offsets;
   p.num_groups = num_groups;
@@ -682,6 +702,9 @@ extern "C" int ocb_gemm_bf16_tp(const void* const* a_ptrs, const void* B, void* 
   p.N = N;
   p.K = K;
   p.group_m = 8;
+  p.bk = BK;
+  p.scale_a = nullptr;
+  p.scale_b = nullptr;
   p.status = status;
   p.offsets = nullptr;
   p.num_groups = 0;
@@ -735,4 +758,54 @@ extern "C" int ocb_gemm_bf16_tp(const void* const* a_ptrs, const void* B, void* 
   for (int r = 0; r < world; ++r) p.peer_c[r] = static_cast<float*>(c_ptrs[r]);
   return b_mn_major ? launch_gemm<0, 1, EPI_F32_RED_PEER, GROUP_NONE>(ta, tb, p, stream)
                     : launch_gemm<0, 0, EPI_F32_RED_PEER, GROUP_NONE>(ta, tb, p, stream);
+}
+
+// C[M, N] = (A_q * B_q^T) .* (scale_a[m] * scale_b[n]) with e4m3 operands on the tensor cores (kind::f8f6f4) and fp32
+// accumulation. A_q: [M, K], B_q: [N, K], both K-major bytes with row strides lda / ldb (multiples of 16); K % 16 == 0.
+// epilogue: 0 = bf16 store, 1 = fp32 accumulate, 2 = fp32 store.
+extern "C" int ocb_gemm_fp8(const void* A, const void* B, void* C, const float* scale_a, const float* scale_b, int M, int N,
+                            int K, long long lda, long long ldb, long long ldc, int epilogue, int* status,
+                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) != 0 || (ldb % 16) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -1;
+  if (scale_a == nullptr || scale_b == nullptr) return -1;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda)};
+    uint32_t box[2] = {128, static_cast<uint32_t>(BM)};
+    if (!get_tensor_map(&ta, A, 2, dims, str, box, 1)) return -(1000 + g_last_tmap_error);
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb)};
+    uint32_t box[2] = {128, static_cast<uint32_t>(BN)};
+    if (!get_tensor_map(&tb, B, 2, dims, str, box, 1)) return -(2000 + g_last_tmap_error);
+  }
+  GemmParams p;
+  p.C = C;
+  p.ldc = ldc;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.group_m = 8;
+  p.bk = 2 * BK;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
+  p.status = status;
+  p.offsets = nullptr;
+  p.num_groups = 0;
+  p.b_group_rows = 0;
+  p.c_group_rows = 0;
+  p.peer_a_maps = nullptr;
+  p.world = 1;
+  p.rank = 0;
+  p.m_local = M;
+  switch (epilogue) {
+    case EPI_BF16: return launch_gemm<0, 0, EPI_BF16, GROUP_NONE, 1>(ta, tb, p, stream);
+    case EPI_F32_ACC: return launch_gemm<0, 0, EPI_F32_ACC, GROUP_NONE, 1>(ta, tb, p, stream);
+    case EPI_F32: return launch_gemm<0, 0, EPI_F32, GROUP_NONE, 1>(ta, tb, p, stream);
+    default: return -1;
+  }
 }

@@ -33,6 +33,19 @@ int ocb_gemm_bf16_tp(const void* const* a_ptrs, const void* B, void* const* c_pt
                      long long lda, long long ldb, long long ldc, int world, int rank, int gather_a, int scatter_c,
                      int b_mn_major, int epilogue, int* status, cudaStream_t stream);
 
+// ---- 8-bit floating point (gemm_sm100.cu, fp8_sm100.cu) -----------------------------------------------
+// C[M, N] = (A_q * B_q^T) .* (scale_a[m] * scale_b[n]); A_q [M, K], B_q [N, K] e4m3 bytes, K-major.
+// epilogue: 0 = bf16 store, 1 = fp32 accumulate, 2 = fp32 store.
+int ocb_gemm_fp8(const void* A, const void* B, void* C, const float* scale_a, const float* scale_b, int M, int N, int K,
+                 long long lda, long long ldb, long long ldc, int epilogue, int* status, cudaStream_t stream);
+// q[r, :] = e4m3(x[r, :] / scale[r]), scale[r] = amax(x[r, :]) / 448   (x bf16, cols % 8 == 0)
+// pow2 != 0 rounds every scale up to a power of two.
+int ocb_quantize_e4m3_rowwise(const void* x, void* q, float* scale, int rows, int cols, long long ldx, long long ldq,
+                              int pow2, cudaStream_t stream);
+// q_t[c, :] = e4m3(x[:, c] / scale[c]): the transposed operand, scaled per column of x. scratch: fp32 [cols].
+int ocb_quantize_e4m3_colwise_t(const void* x, void* q_t, float* scale, float* scratch, int rows, int cols, long long ldx,
+                                long long ldq, int pow2, cudaStream_t stream);
+
 // ---- mixture of experts (moe_sm100.cu) --------------------------------------------------------------
 // scores = softmax (mode 0) or sigmoid (mode 1) of logits [n_tokens, n_experts]; weights / experts: [n_tokens, top_k];
 // counts: int32 [n_experts] tokens per expert (may be null); scores may be null.
