@@ -1,0 +1,135 @@
+"""
+Named training recipes (the per-model scripts of src/scripts/train/ and src/scripts/official/, as one table).
+
+A recipe fixes the model factory, sequence length, global batch, per-GPU micro-batch, optimizer settings, duration and
+the parallelism layout; everything else follows :func:`olmo_core_b200.internal.experiment.build_config`. Micro-batches
+are quoted for 80 GB GPUs and doubled on a B200 (180 GB), except where a recipe pins them.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from functools import partial
+from typing import Any, Callable, Dict, Optional
+
+import torch
+
+from ...config import DType
+from ...distributed.parallel import DataParallelType
+from ...float8 import AOFloat8LinearConfig, Float8Config
+from ...internal.experiment import CliContext, CommonComponents, ExperimentConfig, build_config
+from ...nn.transformer import TransformerConfig
+from ...optim import CosWithWarmup, OptimGroupOverride, SkipStepAdamWConfig
+from ...train import Duration, TrainerConfig
+from ...train.callbacks import CheckpointerCallback, CometCallback, WandBCallback
+from ...train.train_module import (
+    TransformerActivationCheckpointingConfig,
+    TransformerActivationCheckpointingMode,
+    TransformerContextParallelConfig,
+    TransformerDataParallelConfig,
+    TransformerDataParallelWrappingStrategy,
+    TransformerExpertParallelConfig,
+    TransformerTrainModuleConfig,
+)
+
+__all__ = ["Recipe", "RECIPES", "config_builder_for"]
+
+
+@dataclass(frozen=True)
+class Recipe:
+    model: str  # name of a TransformerConfig factory
+    sequence_length: int = 4096
+    global_batch_sequences: int = 1024
+    microbatch_sequences: int = 2  # per GPU, on an 80 GB device
+    lr: float = 3e-4
+    warmup_steps: int = 2000
+    max_tokens: int = int(4e12)
+    dp: DataParallelType = DataParallelType.hsdp
+    shard_degree: Optional[int] = None
+    cp_degree: Optional[int] = None
+    ep_degree: Optional[int] = None
+    float8: bool = False
+    full_activation_checkpointing: bool = False
+    project: str = "OLMo-core"
+    model_kwargs: Optional[Dict[str, Any]] = None
+
+
+RECIPES: Dict[str, Recipe] = {
+    "OLMo2-1B": Recipe("olmo2_1B_v2", global_batch_sequences=512, microbatch_sequences=8, lr=4e-4, project="OLMo-core-1B"),
+    "OLMo2-7B": Recipe("olmo2_7B", project="OLMo-core-7B"),
+    "OLMo2-13B": Recipe("olmo2_13B", global_batch_sequences=2048, microbatch_sequences=1, project="OLMo-core-13B"),
+    "OLMo2-32B": Recipe("olmo2_32B", global_batch_sequences=2048, microbatch_sequences=2, lr=6e-4, max_tokens=int(6.5e12),
+                        shard_degree=64, full_activation_checkpointing=True, project="OLMo-core-32B"),
+    "OLMo3-7B": Recipe("olmo3_7B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
+                       project="OLMo3-7B"),
+    "OLMo3-7B-long-context": Recipe("olmo3_7B", sequence_length=65536, global_batch_sequences=64, microbatch_sequences=1,
+                                    lr=2e-4, warmup_steps=200, max_tokens=int(50e9), shard_degree=1, cp_degree=8,
+                                    float8=True, project="OLMo3-7B-long-context"),
+    "Llama3-8B": Recipe("llama3_8B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
+                        project="Llama3-8B"),
+    "OLMoE-1B-7B": Recipe("olmoe_1B_7B", global_batch_sequences=1024, microbatch_sequences=2, lr=4e-4, max_tokens=int(5e12),
+                          dp=DataParallelType.fsdp, project="OLMoE-1B-7B"),
+    "small-moe": Recipe("smallmoe", global_batch_sequences=256, microbatch_sequences=4, lr=4e-4, max_tokens=int(1e11),
+                        dp=DataParallelType.fsdp, ep_degree=None, project="small-moe"),
+    "nGPT-1B": Recipe("ngpt_1B", global_batch_sequences=512, microbatch_sequences=4, lr=1e-3, warmup_steps=0,
+                      project="nGPT-1B"),
+}
+
+
+def _on_b200() -> bool:
+    return torch.cuda.is_available() and "B200" in torch.cuda.get_device_name(0)
+
+
+def _model(recipe: Recipe, common: CommonComponents) -> TransformerConfig:
+    factory: Callable[..., TransformerConfig] = getattr(TransformerConfig, recipe.model)
+    return factory(vocab_size=common.tokenizer.padded_vocab_size(), **(recipe.model_kwargs or {}))
+
+
+def _train_module(recipe: Recipe, common: CommonComponents) -> TransformerTrainModuleConfig:
+    micro = recipe.microbatch_sequences * (2 if _on_b200() and recipe.sequence_length <= 8192 else 1)
+    return TransformerTrainModuleConfig(
+        rank_microbatch_size=micro * common.max_sequence_length, max_sequence_length=common.max_sequence_length,
+        optim=SkipStepAdamWConfig(lr=recipe.lr, weight_decay=0.1, betas=(0.9, 0.95),
+                                  group_overrides=[OptimGroupOverride(params=["embeddings.weight"],
+                                                                      opts=dict(weight_decay=0.0))]),
+        compile_model=True,
+        dp_config=TransformerDataParallelConfig(name=recipe.dp, param_dtype=DType.bfloat16, reduce_dtype=DType.float32,
+                                                shard_degree=recipe.shard_degree,
+                                                wrapping_strategy=TransformerDataParallelWrappingStrategy.blocks),
+        cp_config=(TransformerContextParallelConfig.llama3(degree=recipe.cp_degree, head_stride=4)
+                   if recipe.cp_degree else None),
+        ep_config=TransformerExpertParallelConfig(degree=recipe.ep_degree) if recipe.ep_degree else None,
+        ac_config=(TransformerActivationCheckpointingConfig(mode=TransformerActivationCheckpointingMode.full)
+                   if recipe.full_activation_checkpointing else None),
+        float8_config=Float8Config(enabled=recipe.float8, ao=AOFloat8LinearConfig.recommended()),
+        z_loss_multiplier=1e-5, max_grad_norm=1.0, scheduler=CosWithWarmup(warmup_steps=recipe.warmup_steps))
+
+
+def _trainer(recipe: Recipe, common: CommonComponents) -> TrainerConfig:
+    config = (
+        TrainerConfig(save_folder=common.save_folder, save_overwrite=True, metrics_collect_interval=10,
+                      cancel_check_interval=10, max_duration=Duration.tokens(recipe.max_tokens))
+        .with_callback("checkpointer", CheckpointerCallback(save_interval=10_000, ephemeral_save_interval=250,
+                                                            save_async=True))
+        .with_callback("comet", CometCallback(name=common.run_name, workspace="ai2", project=recipe.project, enabled=False,
+                                              cancel_check_interval=10))
+        .with_callback("wandb", WandBCallback(name=common.run_name, entity="ai2-llm", project=recipe.project,
+                                              enabled=False, cancel_check_interval=10))
+    )
+    cluster = common.launch.clusters[0] if common.launch is not None else "local"
+    try:
+        config = config.with_recommended_evals(common.tokenizer, common.max_sequence_length, cluster)
+    except Exception:  # evaluation data not reachable from here: train without in-loop evals
+        pass
+    return config
+
+
+def config_builder_for(name: str) -> Callable[[CliContext], ExperimentConfig]:
+    if name not in RECIPES:
+        raise KeyError(f"unknown recipe '{name}'; available: {sorted(RECIPES)}")
+    recipe = RECIPES[name]
+    return partial(
+        build_config, global_batch_size=recipe.global_batch_sequences * recipe.sequence_length,
+        max_sequence_length=recipe.sequence_length, model_config_builder=partial(_model, recipe),
+        train_module_config_builder=partial(_train_module, recipe), trainer_config_builder=partial(_trainer, recipe),
+        include_default_evals=False, include_instance_filter=False)
