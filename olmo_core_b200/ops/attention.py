@@ -127,6 +127,30 @@ def _row_stride(t: torch.Tensor) -> int:
     return t.stride(1)
 
 
+def _visibility_bounds(B: int, T: int, window: int, cu_seqlens: Optional[torch.Tensor], device) -> Optional[torch.Tensor]:
+    """
+    int32 ``[2, B * T]`` for the flash kernels: per query the lowest visible key, per key the highest query that sees it
+    (indices inside the sequence). One pair of arrays expresses sliding windows, document boundaries and both together;
+    ``None`` when neither applies. Documents never span two rows of the batch (``cu_seqlens`` counts over ``B * T``).
+    """
+    if not window and cu_seqlens is None:
+        return None
+    flat = torch.arange(B * T, device=device, dtype=torch.int64)
+    t = flat % T
+    lo = torch.zeros_like(t)
+    hi = torch.full_like(t, T - 1)
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device=device, dtype=torch.int64)
+        doc = torch.bucketize(flat, cu[1:], right=True).clamp(max=cu.numel() - 2)
+        base = flat - t
+        lo = torch.maximum(lo, cu[doc] - base)
+        hi = torch.minimum(hi, cu[doc + 1] - 1 - base)
+    if window:
+        lo = torch.maximum(lo, t - (window - 1))
+        hi = torch.minimum(hi, t + (window - 1))
+    return torch.stack([lo, hi]).to(torch.int32).contiguous()
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, scale: float, causal: bool, window: int):  # type: ignore[override]
@@ -136,7 +160,7 @@ class _FlashAttention(torch.autograd.Function):
                    for t in (q, k, v))
         out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
-        cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32).contiguous()
+        cu = _visibility_bounds(B, Tq, window, cu_seqlens, q.device)
         rc = _lib.lib().ocb_attention_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(cu),
             B, Tq, Tk, H, Hkv, D, _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(out), scale,
@@ -211,9 +235,8 @@ def attention(
         and v.dtype == torch.bfloat16
         and D == 128
         and dropout_p == 0.0
-        and cu_seqlens is None
         and cu_seqlens_k is None
-        and not window_size
+        and (causal or (cu_seqlens is None and not window_size))
         and q.shape[1] == k.shape[1]
         and q.shape[1] % 128 == 0
         and has_flash_kernel()

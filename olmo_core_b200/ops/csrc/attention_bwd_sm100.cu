@@ -42,6 +42,10 @@ struct AttnBwdParams {
   int T, H, Hkv;
   float scale, scale_log2;
   int causal;
+  // Optional visibility bounds (sliding windows and document boundaries), as indices inside the sequence, int32 [B * T],
+  // both non-decreasing: query i sees key j iff row_lo[i] <= j <= i; col_hi[j] is the last query that sees key j.
+  const int* row_lo;
+  const int* col_hi;
   int* status;
 };
 
@@ -134,7 +138,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   const int jt = blockIdx.x;  // K/V tile
   const int hk = blockIdx.y, b = blockIdx.z;
   const int group = p.H / p.Hkv;
-  const int n_q = p.T / BT;
+  // query tiles [i_first, n_q) can see this key tile: up to the tile of the last query that sees its last key
+  const int n_q = p.col_hi ? p.col_hi[b * p.T + jt * BT + BT - 1] / BT + 1 : p.T / BT;
   const int i_first = p.causal ? jt : 0;
   const int iters = (n_q - i_first) * group;  // (query head of the group, query tile) pairs
   const int kv_row0 = b * p.T + jt * BT;
@@ -227,7 +232,12 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qi * BT + row;
       const float lse2 = p.lse[stat] * LOG2E;
       const float dl = p.delta[stat];
-      const bool diag = p.causal && qi == jt;
+      const bool on_diag = p.causal && qi == jt;
+      const int my_lo = p.row_lo ? p.row_lo[b * p.T + qi * BT + row] : 0;
+      const int lo_last = p.row_lo ? p.row_lo[b * p.T + qi * BT + BT - 1] : 0;
+      const bool diag = on_diag || jt * BT < lo_last;  // the tile needs the element-wise mask
+      const int hi_col = on_diag ? row : BT - 1;       // visible key columns of this query row: [lo_col, hi_col]
+      const int lo_col = my_lo - jt * BT;
       ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -256,8 +266,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
           float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
           float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
           if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
           }
           const float d0 = p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale;
           const float d1 = p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale;
@@ -321,8 +331,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   const int qt = gridDim.x - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
-  const int n_kv = p.causal ? qt + 1 : p.T / BT;
   const int q_row0 = b * p.T + qt * BT;
+  const int lo_first = p.row_lo ? p.row_lo[q_row0] : 0;
+  const int lo_last = p.row_lo ? p.row_lo[q_row0 + BT - 1] : 0;
+  const int j_lo = lo_first / BT;  // first key tile any row of this query tile can see; `j` counts tiles from there
+  const int n_kv = (p.causal ? qt + 1 : p.T / BT) - j_lo;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -353,7 +366,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       tma_load_2d(sdO + HALF_BYTES, &tma_do, qdo_full, h * BD + 64, q_row0);
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int kv_row0 = b * p.T + j * BT;
+        const int kv_row0 = b * p.T + (j_lo + j) * BT;
         ok = mbar_wait_bounded(kv_empty, (j & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
@@ -403,10 +416,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qt * BT + row;
     const float lse2 = p.lse[stat] * LOG2E;
     const float dl = p.delta[stat];
+    const int my_lo = p.row_lo ? p.row_lo[q_row0 + row] : 0;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const uint32_t ph = j & 1;
-      const bool diag = p.causal && j == qt;
+      const int kv0 = (j_lo + j) * BT;
+      const bool on_diag = p.causal && j_lo + j == qt;
+      const bool diag = on_diag || kv0 < lo_last;
+      const int hi_col = on_diag ? row : BT - 1;
+      const int lo_col = my_lo - kv0;
       ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -430,8 +448,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
           float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
           float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
           if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
           }
           dw[i] = pack_bf16x2(p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale,
                               p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale);
@@ -477,11 +495,12 @@ using namespace ocb;
 // Gradients of ocb_attention_fwd. dout/out/q/dq: [B, T, H, D]; k, v, dk, dv: [B, T, Hkv, D]; lse: [B, H, T] from the
 // forward pass; delta: [B, H, T] fp32 scratch (written here). dq/dk/dv are written densely (row stride heads * D).
 extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                                 const float* lse, void* dq, void* dk, void* dv, const int* cu_seqlens, float* delta, int B,
+                                 const float* lse, void* dq, void* dk, void* dv, const int* bounds, float* delta, int B,
                                  int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
                                  long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
   if (B <= 0 || Tq <= 0) return 0;
-  if (D != BD || Tq != Tk || (Tq % BT) != 0 || window > 0 || cu_seqlens != nullptr || Hkv <= 0 || (H % Hkv) != 0 ||
+  (void)window;  // folded into `bounds` (int32 [2, B * T]: row_lo then col_hi, see ocb_attention_fwd) by the caller
+  if (D != BD || Tq != Tk || (Tq % BT) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0 ||
       delta == nullptr)
     return -5;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
@@ -519,6 +538,8 @@ extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, co
   p.scale = scale;
   p.scale_log2 = scale * LOG2E;
   p.causal = causal;
+  p.row_lo = bounds;
+  p.col_hi = bounds ? bounds + static_cast<long long>(B) * Tq : nullptr;
   p.status = status;
   attn_dkdv_kernel<<<dim3(Tq / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq, mk, mv, mdo, p);
   attn_dq_kernel<<<dim3(Tq / BT, H, B), BWD_THREADS, DQ_SMEM, stream>>>(mq, mk, mv, mdo, p);

@@ -40,6 +40,10 @@ struct AttnFwdParams {
   int T, H, Hkv;
   float scale_log2;  // softmax scale * log2(e)
   int causal;
+  // Optional per-query lower bound of the visible keys (index inside the sequence, int32 [B * T], non-decreasing along
+  // the sequence): key j is visible to query i iff row_lo[i] <= j (and j <= i when causal). It encodes sliding windows
+  // and document boundaries at once. nullptr = no lower bound.
+  const int* row_lo;
   int* status;
 };
 
@@ -77,8 +81,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int qt = gridDim.x - 1 - blockIdx.x;  // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
-  const int n_kv = p.causal ? qt + 1 : p.T / AT_TILE;
   const int q_row0 = b * p.T + qt * AT_TILE;
+  // The bounds are non-decreasing, so the tile's first row has the smallest one (where the key loop starts) and its last
+  // row the largest (tiles that start below it need the element-wise mask). `j` below counts tiles from j_lo.
+  const int lo_first = p.row_lo ? p.row_lo[q_row0] : 0;
+  const int lo_last = p.row_lo ? p.row_lo[q_row0 + AT_TILE - 1] : 0;
+  const int j_lo = lo_first / AT_TILE;
+  const int n_kv = (p.causal ? qt + 1 : p.T / AT_TILE) - j_lo;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -118,7 +127,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
-        const int kv_row0 = b * p.T + j * AT_TILE;
+        const int kv_row0 = b * p.T + (j_lo + j) * AT_TILE;
         ok = mbar_wait_bounded(k_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(k_full, AT_TILE_BYTES);
@@ -172,6 +181,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // query row within the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int my_lo = p.row_lo ? p.row_lo[q_row0 + row] : 0;
     float m_ref = -INFINITY;  // reference maximum (log2 units) the stored probabilities are relative to
     float l = 0.f;
     bool ok = true;
@@ -181,7 +191,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool diag = p.causal && j == qt;
+      const int kv0 = (j_lo + j) * AT_TILE;
+      const bool on_diag = p.causal && j_lo + j == qt;
+      const bool diag = on_diag || kv0 < lo_last;  // the tile needs the element-wise mask
+      const int hi_col = on_diag ? row : AT_TILE - 1;  // visible columns of this row: [lo_col, hi_col]
+      const int lo_col = my_lo - kv0;
       // pass 1: row maximum. The next chunk's TMEM load is in flight while the current chunk is processed.
       float mx = -INFINITY;
       uint32_t ra[32], rb[32];
@@ -195,7 +209,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, (c * 32 + i > row) ? -INFINITY : __uint_as_float(cur[i]));
+            mx = fmaxf(mx, (c * 32 + i > hi_col || c * 32 + i < lo_col) ? -INFINITY : __uint_as_float(cur[i]));
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
@@ -235,8 +249,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           float p0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, -m_ref));
           float p1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, -m_ref));
           if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
           }
           sum += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
@@ -300,12 +314,15 @@ using namespace ocb;
 
 // q,out: [B, Tq, H, D]; k,v: [B, Tk, Hkv, D]; bf16, D contiguous, heads contiguous (stride D), tokens `ld*` elements
 // apart and batches Tq*ld (Tk*ld) apart. lse: [B, H, Tq] fp32. Supported: D == 128, Tq == Tk, T % 128 == 0, no
-// sliding window, no document boundaries; anything else returns -5 so that the caller can take another path.
-extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+// other cases return -5 so that the caller can take another path. Sliding windows and document boundaries are passed
+// as `bounds`: int32 [2, B * T] = per-query lowest visible key, then per-key highest query that sees it (both as indices
+// inside the sequence, non-decreasing); they need causal != 0. `window` is unused (folded into the bounds by the caller).
+extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* bounds,
                                  int B, int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
                                  long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
   if (B <= 0 || Tq <= 0) return 0;
-  if (D != AT_D || Tq != Tk || (Tq % AT_TILE) != 0 || window > 0 || cu_seqlens != nullptr || Hkv <= 0 || (H % Hkv) != 0)
+  (void)window;
+  if (D != AT_D || Tq != Tk || (Tq % AT_TILE) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0)
     return -5;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
   CUtensorMap mq, mk, mv;
@@ -326,6 +343,7 @@ extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, vo
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
+  p.row_lo = bounds;
   p.status = status;
   dim3 grid(Tq / AT_TILE, H, B);
   attn_fwd_kernel<<<grid, AT_THREADS, AT_FWD_SMEM, stream>>>(mq, mk, mv, p);

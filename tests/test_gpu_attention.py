@@ -73,3 +73,47 @@ def test_unsupported_shapes_take_the_masked_path():
     out = attention(q, q, q, causal=True, window_size=16)
     ref = attention_reference(q, q, q, causal=True, window_size=16)
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def _doc_boundaries(total: int, seed: int, B: int, T: int) -> torch.Tensor:
+    """Random document boundaries over B * T tokens; every multiple of T is a boundary."""
+    g = torch.Generator().manual_seed(seed)
+    cuts = set(range(0, total + 1, T))
+    for b in range(B):
+        n = int(torch.randint(1, 6, (1,), generator=g))
+        cuts |= {b * T + int(c) for c in torch.randint(1, T, (n,), generator=g)}
+    return torch.tensor(sorted(cuts), dtype=torch.int32)
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,window,docs", [
+    (1, 512, 2, 2, 128, False),    # window of exactly one tile
+    (2, 1024, 4, 2, 100, False),   # window smaller than a tile
+    (1, 2048, 2, 1, 700, False),   # window spanning several tiles, not tile-aligned
+    (2, 1024, 2, 2, None, True),   # packed documents
+    (1, 2048, 4, 2, 300, True),    # documents and a window together
+])
+def test_flash_attention_windows_and_documents(B, T, H, Hkv, window, docs):
+    """Sliding windows and document boundaries run in the flash kernels (skipped key tiles + element-wise masks)."""
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(T + (window or 0))
+    dev = torch.device("cuda")
+    cu = _doc_boundaries(B * T, seed=T, B=B, T=T).to(dev) if docs else None
+    q = torch.randn(B, T, H, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, T, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, T, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    dout = torch.randn(B, T, H, 128, device=dev, dtype=torch.bfloat16)
+    launches = _lib.launch_count
+    out = attention(q, k, v, causal=True, window_size=window, cu_seqlens=cu)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_device_status(dev)
+    assert _lib.launch_count == launches + 2  # forward and backward launchers of the in-tree kernels
+
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qf, kf, vf, causal=True, window_size=window, cu_seqlens=cu)
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 2e-2)
