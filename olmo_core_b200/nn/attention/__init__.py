@@ -21,6 +21,7 @@ import torch.nn as nn
 from ...config import Config, DType, Registrable, StrEnum
 from ...exceptions import OLMoConfigurationError
 from ...ops.elementwise import NORM_FULL, NORM_HEAD, NORM_NONE, norm_rope
+from ...ops.gemm import multi_linear
 from ..buffer_cache import BufferCache
 from ..config import ModuleConfig
 from ..feed_forward import Linear
@@ -370,7 +371,7 @@ class Attention(SequenceMixer):
     ) -> torch.Tensor:
         B, T, _ = x.shape
         hd = self.head_dim
-        q, k, v = self.w_q(x), self.w_k(x), self.w_v(x)
+        q, k, v = multi_linear(x, (self.w_q, self.w_k, self.w_v))
         start_pos = self.kv_cache_manager.current_position() if self.kv_cache_manager is not None else None
         if self.cp_enabled and self.rope is not None and pos_sin is None and pos_cos is None and freqs_cis is None:
             raise RuntimeError("RoPE buffers must be passed to attention after being sharded by the context-parallel load balancer")
@@ -568,7 +569,7 @@ class NormalizedAttention(Attention):
         if cache_leftpad is not None:
             raise NotImplementedError("cache_leftpad is not supported for the normalized attention variant")
         B, T, _ = x.shape
-        q, k, v = self.w_q(x), self.w_k(x), self.w_v(x)
+        q, k, v = multi_linear(x, (self.w_q, self.w_k, self.w_v))
         if self.q_norm is not None and self.k_norm is not None:
             q, k = self.q_norm(q), self.k_norm(k)
         q = (self.sq * (self.sq_init_value / self.sq_init_scaling)).to(q.dtype).view(1, 1, -1) * q

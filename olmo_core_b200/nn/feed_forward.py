@@ -20,7 +20,7 @@ import torch.nn.functional as F
 from ..config import DType, StrEnum
 from ..exceptions import OLMoConfigurationError
 from ..ops.elementwise import swiglu
-from ..ops.gemm import linear
+from ..ops.gemm import linear, multi_linear
 from .config import ModuleConfig
 from .layer_norm import l2_normalize
 
@@ -134,7 +134,7 @@ class FeedForward(nn.Module):
         self.w3 = _Proj(d_model, hidden_size, bias, dtype, init_device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        a, b = self.w1(x), self.w3(x)
+        a, b = multi_linear(x, (self.w1, self.w3))  # one saved input, input gradients summed in the GEMM epilogue
         if self.activation == ActivationFunction.silu:
             return self.w2(swiglu(a, b))
         return self.w2(self._act(a) * b)

@@ -305,7 +305,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
 // ------------------------------------------------------------------------------------------------------------
 // 3. dQ
 // ------------------------------------------------------------------------------------------------------------
-constexpr int DQ_SMEM = 4 * TILE_BYTES + 1024 + 256;
+constexpr int DQ_SMEM = 6 * TILE_BYTES + 1024 + 256;  // Q, dO resident; K, V in a two-stage ring
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -315,15 +315,14 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + 1 * TILE_BYTES;
-  uint8_t* sK = smem + 2 * TILE_BYTES;
-  uint8_t* sV = smem + 3 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * TILE_BYTES);
+  uint8_t* sKV = smem + 2 * TILE_BYTES;  // stage s: K at sKV + 2 s TILE_BYTES, V one tile after it
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* ds_full = bars + 4;   // dS is in TMEM (4 warp arrivals)
-  uint64_t* dq_done = bars + 5;   // dQ += dS K has read dS (and K): S may be overwritten
+  uint64_t* kv_full = bars + 1;   // [2]: the next key/value tile is loaded while the current one is in use
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_full = bars + 6;   // dS is in TMEM (4 warp arrivals)
+  uint64_t* dq_done = bars + 7;   // dQ += dS K has read dS (and K): S may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -339,8 +338,10 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    mbar_init(kv_full, 1);
-    mbar_init(kv_empty, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(&kv_full[st], 1);
+      mbar_init(&kv_empty[st], 1);
+    }
     mbar_init(sdp_full, 1);
     mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
@@ -367,13 +368,16 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int kv_row0 = b * p.T + (j_lo + j) * BT;
-        ok = mbar_wait_bounded(kv_empty, (j & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        const int st = j & 1;
+        uint8_t* sK = sKV + st * 2 * TILE_BYTES;
+        uint8_t* sV = sK + TILE_BYTES;
+        ok = mbar_wait_bounded(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
-        tma_load_2d(sK, &tma_k, kv_full, hk * BD, kv_row0);
-        tma_load_2d(sK + HALF_BYTES, &tma_k, kv_full, hk * BD + 64, kv_row0);
-        tma_load_2d(sV, &tma_v, kv_full, hk * BD, kv_row0);
-        tma_load_2d(sV + HALF_BYTES, &tma_v, kv_full, hk * BD + 64, kv_row0);
+        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+        tma_load_2d(sK, &tma_k, &kv_full[st], hk * BD, kv_row0);
+        tma_load_2d(sK + HALF_BYTES, &tma_k, &kv_full[st], hk * BD + 64, kv_row0);
+        tma_load_2d(sV, &tma_v, &kv_full[st], hk * BD, kv_row0);
+        tma_load_2d(sV + HALF_BYTES, &tma_v, &kv_full[st], hk * BD + 64, kv_row0);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -383,11 +387,13 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, BD, 0, 1);  // A = dS from TMEM, B = K contracted over its rows
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, p.status, kStatusTimeoutMma);
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
-        ok = mbar_wait_bounded(kv_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        const int st = j & 1;
+        const uint32_t aK = smem_u32(sKV + st * 2 * TILE_BYTES), aV = aK + TILE_BYTES;
+        ok = mbar_wait_bounded(&kv_full[st], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
         if (j > 0) {
           ok = mbar_wait_bounded(dq_done, ph ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
@@ -404,7 +410,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdS + k * 8, desc_mn(aK, k), idesc_dq, (j | k) != 0);
-        umma_commit(kv_empty);
+        umma_commit(&kv_empty[st]);
         umma_commit(dq_done);
       }
     }

@@ -58,6 +58,11 @@ struct GemmParams {
   int bk;
   const float* scale_a;  // [M] one per row of A
   const float* scale_b;  // [N] one per row of B (= output column)
+  // Split of the last wave's tiles along the reduction (plain mode only): tiles >= split_first are cut into split_parts
+  // parts; partial tiles go to split_ws [slot][part][BM][BN] fp32 and arrivals are counted in split_counters [slot].
+  int split_first, split_parts;
+  float* split_ws;
+  int* split_counters;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -83,6 +88,7 @@ struct TileInfo {
   int c_row_off;  // added to the output row
   int a_map;      // GROUP_GATHER: whose shard of A the tile reads
   int a_row0;     // GROUP_GATHER: first row inside that shard
+  int split_parts, split_part, split_slot;  // reduction split of a last-wave tile (split_parts == 1: not split)
 };
 
 // Walks the tiles of one CTA (tile = blockIdx.x, += gridDim.x) and resolves them to coordinates. In the grouped modes the
@@ -98,10 +104,20 @@ struct TileWalker {
     tile = blockIdx.x;
   }
   __device__ bool next(TileInfo& t) {
+    t.split_parts = 1;
+    t.split_part = 0;
+    t.split_slot = 0;
     if (GROUPED == GROUP_NONE || GROUPED == GROUP_GATHER) {
-      if (tile >= tiles_m * tiles_n) return false;
+      // `tile` walks work units: whole tiles below split_first, then split_parts units per remaining tile
+      int out_tile = tile, part = 0;
+      const bool in_split = GROUPED == GROUP_NONE && p.split_parts > 1 && tile >= p.split_first;
+      if (in_split) {
+        out_tile = p.split_first + (tile - p.split_first) / p.split_parts;
+        part = (tile - p.split_first) % p.split_parts;
+      }
+      if (out_tile >= tiles_m * tiles_n) return false;
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+      tile_coords(out_tile, tiles_m, tiles_n, p.group_m, tm, tn);
       if (p.world > 1) {
         // Every rank starts at a different row shard (its own when gathering, its neighbour's when scattering), so that
         // at any moment the ranks pull from / push to different peers.
@@ -115,6 +131,15 @@ struct TileWalker {
       }
       t.m0 = tm * BM; t.n0 = tn * BN; t.m_end = p.M; t.k0 = 0;
       t.num_kb = (p.K + p.bk - 1) / p.bk; t.k_tail = BK; t.b_off = 0; t.c_row_off = 0;
+      if (in_split) {
+        const int per_part = (t.num_kb + p.split_parts - 1) / p.split_parts;  // the host keeps every part non-empty
+        const int kb0 = part * per_part;
+        t.k0 = kb0 * p.bk;
+        t.num_kb = min(per_part, t.num_kb - kb0);
+        t.split_parts = p.split_parts;
+        t.split_part = part;
+        t.split_slot = out_tile - p.split_first;
+      }
     } else if (GROUPED == GROUP_ROWS) {
       int lo, rows, tm_g;
       while (true) {
@@ -155,6 +180,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* split_flag = abort_flag + 1;  // epilogue warps: "this CTA completes a split tile"
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -310,17 +336,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int n0 = t.n0;
       const bool row_ok = row_in < t.m_end;
       const bool empty = t.num_kb == 0;  // a group without rows: the accumulator was never written
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        if (GROUPED == GROUP_REDUCTION && empty) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
-        }
+      // Writes 32 consecutive output columns of this thread's row: chunk c of the tile, values in r.
+      auto store_chunk = [&](uint32_t(&r)[32], int c) {
         const int col = n0 + c * 32;
-        if (!row_ok || col >= p.N) continue;
+        if (!row_ok || col >= p.N) return;
         if (FP8) {
           // De-quantise: the operands were scaled per row of A and per row of B (per output column).
           const float sa = p.scale_a[row_in];
@@ -407,10 +426,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
         }
+      };
+      // A tile of the last, partly filled wave may be split along the reduction over several CTAs (t.split_parts > 1):
+      // each part leaves its fp32 partial tile in the workspace, and the part that arrives last adds them up in part
+      // order and runs the epilogue. Nobody waits for anybody, and the order of the additions is fixed.
+      const bool split = t.split_parts > 1;
+      float* ws_row = nullptr;
+      if (split) {
+        ws_row = p.split_ws + (static_cast<long long>(t.split_slot) * t.split_parts + t.split_part) * (BM * BN) +
+                 (quad * 32 + lane) * BN;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (GROUPED == GROUP_REDUCTION && empty) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (split) {
+          uint4* dst = reinterpret_cast<uint4*>(ws_row + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) dst[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        } else {
+          store_chunk(r, c);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (split) {
+        __threadfence();  // this thread's partials are visible device-wide before the arrival is counted
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int before = atomicAdd(&p.split_counters[t.split_slot], 1);
+          *split_flag = (before == t.split_parts - 1) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = *split_flag != 0;
+        if (last) {
+          __threadfence();
+          const float* base = p.split_ws + static_cast<long long>(t.split_slot) * t.split_parts * (BM * BN) +
+                              (quad * 32 + lane) * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+            for (int q = 0; q < t.split_parts; ++q) {
+              const float4* src = reinterpret_cast<const float4*>(base + static_cast<long long>(q) * (BM * BN) + c * 32);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                const float4 x = __ldcg(src + v);
+                r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) + x.x);
+                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + x.y);
+                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + x.z);
+                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + x.w);
+              }
+            }
+            store_chunk(r, c);
+          }
+          if (warp == 2 && lane == 0) p.split_counters[t.split_slot] = 0;  // ready for the next launch on this stream
+        }
+      }
     }
   }
 
@@ -513,21 +592,82 @@ static int num_sms() {
   return n;
 }
 
+// Workspace of the last-wave reduction split, one per stream (GEMMs on different streams may run at the same time):
+// num_sms partial tiles of BM x BN fp32 and as many arrival counters (zero between launches).
+struct SplitWorkspace {
+  float* tiles = nullptr;
+  int* counters = nullptr;
+};
+
+static bool split_workspace(cudaStream_t stream, SplitWorkspace* out) {
+  static std::mutex mu;
+  static std::unordered_map<cudaStream_t, SplitWorkspace> per_stream;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = per_stream.find(stream);
+  if (it == per_stream.end()) {
+    if (per_stream.size() >= 8) return false;  // unusual: many streams issue GEMMs; those run without the split
+    SplitWorkspace w;
+    const size_t n = static_cast<size_t>(num_sms());
+    if (cudaMalloc(&w.tiles, n * BM * BN * sizeof(float)) != cudaSuccess) return false;
+    if (cudaMalloc(&w.counters, n * sizeof(int)) != cudaSuccess || cudaMemset(w.counters, 0, n * sizeof(int)) != cudaSuccess) {
+      cudaFree(w.tiles);
+      return false;
+    }
+    it = per_stream.emplace(stream, w).first;
+  }
+  *out = it->second;
+  return true;
+}
+
+static bool split_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("OCB_GEMM_SPLIT_LAST_WAVE");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
 template <int A_MN, int B_MN, int EPI, int GROUPED = GROUP_NONE, int FP8 = 0>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p_in, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, GROUPED, FP8>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -3;
     configured = true;
   }
+  GemmParams p = p_in;
+  p.split_first = 0;
+  p.split_parts = 1;
+  p.split_ws = nullptr;
+  p.split_counters = nullptr;
   // Upper bound of the tile count (the exact count of the row-grouped mode depends on device data: every group may
   // add one partly filled row of tiles).
   long long tiles_m = (p.M + BM - 1) / BM;
   if (GROUPED == GROUP_ROWS) tiles_m += p.num_groups;
   if (GROUPED == GROUP_REDUCTION) tiles_m *= p.num_groups;
-  const long long tiles = tiles_m * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms() ? static_cast<int>(tiles) : num_sms();
+  long long units = tiles_m * ((p.N + BN - 1) / BN);
+  const int sms = num_sms();
+  if (GROUPED == GROUP_NONE && EPI != EPI_F32_RED_PEER && p.world == 1 && split_enabled()) {
+    // The persistent grid runs floor(tiles / SMs) full waves and then a wave that fills only `rest` SMs. When that wave
+    // is at most half full, its tiles are cut along the reduction so that it keeps (nearly) all SMs busy for a fraction
+    // of a tile's time.
+    const int full = static_cast<int>(units / sms), rest = static_cast<int>(units % sms);
+    const int num_kb = (p.K + p.bk - 1) / p.bk;
+    if (full >= 1 && rest > 0 && 2 * rest <= sms) {
+      int parts = sms / rest;
+      if (parts > 4) parts = 4;
+      while (parts > 1 && (num_kb / parts < 8 || (parts - 1) * ((num_kb + parts - 1) / parts) >= num_kb)) --parts;
+      SplitWorkspace w;
+      if (parts > 1 && split_workspace(stream, &w)) {
+        p.split_first = full * sms;
+        p.split_parts = parts;
+        p.split_ws = w.tiles;
+        p.split_counters = w.counters;
+        units = static_cast<long long>(full) * sms + static_cast<long long>(rest) * parts;
+      }
+    }
+  }
+  const int grid = units < sms ? static_cast<int>(units) : sms;
   kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -226,3 +226,77 @@ def grouped_gemm_wgrad(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, 
         _row_stride(out), 1, epi, _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "ocb_grouped_gemm_bf16")
     return out
+
+
+class MultiLinearFunction(torch.autograd.Function):
+    """
+    Several projections of ONE input (``q, k, v = x W_q^T, x W_k^T, x W_v^T``; the two up-projections of a gated MLP).
+    Forward is one GEMM per weight on a single saved copy of ``x``. Backward accumulates the input gradient across the
+    projections in the GEMM epilogue (``dx = dy_0 W_0``, then ``dx += dy_i W_i``), so the element-wise additions that
+    autograd would run to sum the per-projection gradients never happen.
+    """
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, *weights: torch.Tensor):  # type: ignore[override]
+        ws = [compute_weight(w, torch.bfloat16) for w in weights]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, *ws)
+        ctx.weight_refs = weights
+        ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
+        return tuple(gemm(x2, w, trans_b=True).view(*x.shape[:-1], w.shape[0]) for w in ws)
+
+    @staticmethod
+    def backward(ctx, *dys: torch.Tensor):  # type: ignore[override]
+        x2, *ws = ctx.saved_tensors
+        dx = None
+        dws = []
+        for i, (dy, w, weight) in enumerate(zip(dys, ws, ctx.weight_refs)):
+            if dy is None:
+                dws.append(None)
+                continue
+            dy2 = dy.reshape(-1, dy.shape[-1])
+            if dy2.dtype != torch.bfloat16:
+                dy2 = dy2.to(torch.bfloat16)
+            if dy2.stride(1) != 1:
+                dy2 = dy2.contiguous()
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = gemm(dy2, w, trans_b=False)
+                else:
+                    gemm(dy2, w, trans_b=False, out=dx, accumulate=True)
+            dw = None
+            if ctx.needs_input_grad[1 + i]:
+                main_grad = getattr(weight, "main_grad", None)
+                if main_grad is not None:
+                    gemm(dy2, x2, trans_a=True, trans_b=False, out=main_grad, accumulate=True)
+                    if hasattr(weight, "grad_added_to_main_grad"):
+                        weight.grad_added_to_main_grad = True
+                else:
+                    dw = gemm(dy2, x2, trans_a=True, trans_b=False, out_dtype=torch.float32)
+                    if dw.dtype != weight.dtype:
+                        dw = dw.to(weight.dtype)
+            dws.append(dw)
+        if dx is not None:
+            dx = dx.view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        return (dx, *dws)
+
+
+def multi_linear(x: torch.Tensor, projections) -> tuple:
+    """
+    ``tuple(p(x) for p in projections)`` for bias-free ``Linear`` modules, through :class:`MultiLinearFunction` when
+    the kernel path applies to all of them; otherwise each projection runs on its own.
+    """
+    plain = x.is_cuda and all(
+        getattr(p, "bias", None) is None and getattr(p, "float8", None) is None
+        and ((x.dtype == torch.bfloat16 and getattr(p.weight, "_lowp", None) is None)
+             or (getattr(p.weight, "_lowp", None) is not None and p.weight._lowp.dtype == torch.bfloat16))
+        for p in projections)
+    if not plain:
+        return tuple(p(x) for p in projections)
+    return MultiLinearFunction.apply(x, *[p.weight for p in projections])

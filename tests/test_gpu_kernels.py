@@ -268,3 +268,46 @@ def test_adamw_and_sumsq(gdtype):
     x = torch.randn(1 << 20, device=DEV).to(gdtype)
     s = sumsq(x)
     assert abs(s.item() - x.float().pow(2).sum().item()) / s.item() < 1e-4
+
+
+def test_multi_linear_sums_input_gradients_in_the_epilogue():
+    from olmo_core_b200.nn.feed_forward import Linear
+    from olmo_core_b200.ops.gemm import multi_linear
+
+    torch.manual_seed(11)
+    x = torch.randn(2, 256, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    projs = [Linear(512, n, False, torch.bfloat16, DEV) for n in (512, 256, 768)]
+    outs = multi_linear(x, projs)
+    grads = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, grads)
+    xf = x.detach().float().requires_grad_(True)
+    ref = [xf @ p.weight.detach().float().t() for p in projs]
+    torch.autograd.backward(ref, [g.float() for g in grads])
+    for o, r in zip(outs, ref):
+        assert _rel_err(o, r) < 5e-3
+    assert _rel_err(x.grad, xf.grad) < 1e-2
+    for p, g, in zip(projs, grads):
+        want = g.float().reshape(-1, g.shape[-1]).t() @ x.detach().float().reshape(-1, 512)
+        assert _rel_err(p.weight.grad, want) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 8192), (4096, 11008, 2048), (19072, 256, 1024)])
+def test_gemm_last_wave_split_matches_reference(M, N, K):
+    """Tile counts that leave a thin last wave: those tiles are split along the reduction and summed in fixed order."""
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.gemm import gemm
+
+    torch.manual_seed(12)
+    a = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)  # wgrad layout: both operands reduction-major
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    base = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    out = base.clone()
+    gemm(a, b, trans_a=True, trans_b=False, out=out, accumulate=True)
+    again = base.clone()
+    gemm(a, b, trans_a=True, trans_b=False, out=again, accumulate=True)
+    _lib.check_device_status()
+    assert torch.equal(out, again)  # deterministic
+    ref = base + a.float().t() @ b.float()
+    assert _rel_err(out, ref) < 5e-3
+    y = gemm(a.t().contiguous(), b.t().contiguous(), trans_b=True)  # the same product through the bf16 epilogue
+    assert _rel_err(y, a.float().t() @ b.float()) < 5e-3
