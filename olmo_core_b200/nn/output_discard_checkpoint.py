@@ -13,7 +13,10 @@ output can be dropped as well::
 
 When gradients reach ``y`` the function is re-run, its result is written back into the very tensor object the consumer
 saved (so the consumer's backward sees valid data again), and backward of ``fn`` itself runs on the recomputed graph.
-The tensor's storage is released with ``resize_(0)`` and re-grown in place; no native helper is needed for that.
+The tensor's storage is released with ``resize_(0)``. At recomputation the native helper ``torch.ops.ocb_native.rebind_storage``
+(``nn/_csrc/storage_rebind.cpp``, built ahead of time by ``python -m olmo_core_b200.ops.build``) points the emptied
+``StorageImpl`` at the recomputed tensor's allocation, so nothing is copied; without the helper library the storage is
+re-grown in place and the recomputed bytes are copied into it.
 """
 
 from __future__ import annotations
@@ -22,7 +25,30 @@ from typing import Any, Callable, Optional, Tuple
 
 import torch
 
-__all__ = ["OutputDiscardCheckpoint"]
+__all__ = ["OutputDiscardCheckpoint", "native_rebind_available"]
+
+_native_state: Optional[bool] = None
+
+
+def native_rebind_available() -> bool:
+    """Load ``libocb_native.so`` once; True when ``torch.ops.ocb_native.rebind_storage`` can be used."""
+    global _native_state
+    if _native_state is None:
+        from ..ops.build import NATIVE_LIB_PATH
+
+        try:
+            if NATIVE_LIB_PATH.exists():
+                torch.ops.load_library(str(NATIVE_LIB_PATH))
+                _native_state = True
+            else:
+                _native_state = False
+        except OSError:
+            _native_state = False
+        if not _native_state and torch.cuda.is_available():
+            raise RuntimeError(
+                f"{NATIVE_LIB_PATH} is missing or unloadable; build it with `python -m olmo_core_b200.ops.build`"
+            )
+    return _native_state
 
 
 def _tensors(outputs: Any) -> Tuple[torch.Tensor, ...]:
@@ -106,8 +132,12 @@ class OutputDiscardCheckpoint:
     def _recompute(self, grad: torch.Tensor) -> torch.Tensor:
         assert self._run is not None and self._inputs is not None and self._outputs is not None
         self._recomputed = self._rerun(self._run, self._inputs)
+        native = native_rebind_available()
         with torch.no_grad():
             for old, new in zip(self._outputs, _tensors(self._recomputed)):
+                if native and new.is_contiguous() and new.storage_offset() == old.storage_offset():
+                    torch.ops.ocb_native.rebind_storage(old, new)  # zero-copy: same StorageImpl, new allocation
+                    continue
                 old.untyped_storage().resize_(new.numel() * new.element_size())
                 # written through `.data`: same memory, but the version counter that autograd checked when the consumer
                 # saved `old` is left alone

@@ -103,6 +103,43 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     return LIB_PATH
 
 
+NATIVE_SRC_DIR = OPS_DIR.parent / "nn" / "_csrc"
+NATIVE_LIB_PATH = OPS_DIR.parent / "nn" / "libocb_native.so"
+
+
+def build_native(force: bool = False, verbose: bool = True) -> Path:
+    """
+    Compile the host-side C++ helpers that need PyTorch's headers (``nn/_csrc/*.cpp``: the storage rebinding used by
+    ``OutputDiscardCheckpoint``) into ``nn/libocb_native.so``. They register dispatcher ops (``torch.ops.ocb_native.*``)
+    and are loaded with ``torch.ops.load_library``.
+    """
+    import torch
+    from torch.utils.cpp_extension import include_paths, library_paths
+
+    BUILD_DIR.mkdir(exist_ok=True)
+    srcs = sorted(NATIVE_SRC_DIR.glob("*.cpp"))
+    h = hashlib.sha256(torch.__version__.encode())
+    for src in srcs:
+        h.update(src.read_bytes())
+    stamp = BUILD_DIR / "native.hash"
+    if not force and NATIVE_LIB_PATH.exists() and stamp.exists() and stamp.read_text() == h.hexdigest():
+        return NATIVE_LIB_PATH
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", *map(str, srcs), "-o", str(NATIVE_LIB_PATH)]
+    for inc in include_paths():
+        cmd += ["-isystem", inc]
+    for lib_dir in library_paths():
+        cmd += [f"-L{lib_dir}", f"-Wl,-rpath,{lib_dir}"]
+    cmd += ["-ltorch", "-ltorch_cpu", "-lc10"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"native helper build failed:\n{proc.stdout}\n{proc.stderr}")
+    stamp.write_text(h.hexdigest())
+    if verbose:
+        print(f"[ocb build] linked {NATIVE_LIB_PATH}", file=sys.stderr)
+    return NATIVE_LIB_PATH
+
+
 def is_built() -> bool:
     return LIB_PATH.exists()
 
@@ -110,6 +147,7 @@ def is_built() -> bool:
 def main(argv: Optional[List[str]] = None) -> None:
     argv = sys.argv[1:] if argv is None else argv
     build(force="--force" in argv)
+    build_native(force="--force" in argv)
 
 
 if __name__ == "__main__":

@@ -109,7 +109,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 // ------------------------------------------------------------------------------------------------------------
 // 2. dK, dV
 // ------------------------------------------------------------------------------------------------------------
-constexpr int DKDV_SMEM = 6 * TILE_BYTES + 1024 + 256;
+constexpr int DKDV_SMEM = 7 * TILE_BYTES + 1024 + 256;  // K, V, two Q stages, dO, P, dS
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -119,19 +119,25 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + 1 * TILE_BYTES;
-  uint8_t* sQ = smem + 2 * TILE_BYTES;
-  uint8_t* sdO = smem + 3 * TILE_BYTES;
-  uint8_t* sP = smem + 4 * TILE_BYTES;   // [q rows x kv cols]
-  uint8_t* sdS = smem + 5 * TILE_BYTES;  // [q rows x kv cols]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  // Q is double-buffered and loaded one query tile ahead; dO has one buffer that is refilled as soon as dV += P^T dO has
+  // read it (that product is issued before dK += dS^T Q for this reason). S and dP are signalled separately, so the
+  // exponentials of a tile run while its dO is still in flight.
+  uint8_t* sQ = smem + 2 * TILE_BYTES;   // stage s at sQ + s * TILE_BYTES
+  uint8_t* sdO = smem + 4 * TILE_BYTES;
+  uint8_t* sP = smem + 5 * TILE_BYTES;   // [q rows x kv cols]
+  uint8_t* sdS = smem + 6 * TILE_BYTES;  // [q rows x kv cols]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;   // S and dP are in TMEM
-  uint64_t* pds_full = bars + 4;   // P and dS tiles are in shared memory (4 warp arrivals)
-  uint64_t* pds_empty = bars + 5;  // the MMAs that read P / dS have finished
-  uint64_t* acc_full = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_full = bars + 1;     // [2]
+  uint64_t* q_empty = bars + 3;    // [2] dK += dS^T Q has read the stage
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 6;   // dV += P^T dO has read dO
+  uint64_t* s_full = bars + 7;     // S is in TMEM
+  uint64_t* dp_full = bars + 8;    // dP is in TMEM
+  uint64_t* pds_full = bars + 9;   // P and dS tiles are in shared memory (8 warp arrivals)
+  uint64_t* pds_empty = bars + 10; // the MMAs that read P / dS have finished
+  uint64_t* acc_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,9 +152,14 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
-    mbar_init(sdp_full, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(&q_full[st], 1);
+      mbar_init(&q_empty[st], 1);
+    }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
     mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(acc_full, 1);
@@ -176,13 +187,18 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int it = 0; it < iters && ok; ++it) {
         const int h = hk * group + it / (n_q - i_first);
         const int q_row0 = b * p.T + (i_first + it % (n_q - i_first)) * BT;
-        ok = mbar_wait_bounded(qdo_empty, (it & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        const int st = it & 1;
+        uint8_t* q_dst = sQ + st * TILE_BYTES;
+        ok = mbar_wait_bounded(&q_empty[st], ((it >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
-        tma_load_2d(sQ, &tma_q, qdo_full, h * BD, q_row0);
-        tma_load_2d(sQ + HALF_BYTES, &tma_q, qdo_full, h * BD + 64, q_row0);
-        tma_load_2d(sdO, &tma_do, qdo_full, h * BD, q_row0);
-        tma_load_2d(sdO + HALF_BYTES, &tma_do, qdo_full, h * BD + 64, q_row0);
+        mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
+        tma_load_2d(q_dst, &tma_q, &q_full[st], h * BD, q_row0);
+        tma_load_2d(q_dst + HALF_BYTES, &tma_q, &q_full[st], h * BD + 64, q_row0);
+        ok = mbar_wait_bounded(do_empty, (it & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(do_full, TILE_BYTES);
+        tma_load_2d(sdO, &tma_do, do_full, h * BD, q_row0);
+        tma_load_2d(sdO + HALF_BYTES, &tma_do, do_full, h * BD + 64, q_row0);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -192,29 +208,37 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);  // both operands contracted over their columns
       constexpr uint32_t idesc_mm = make_idesc_bf16(BT, BD, 1, 1);  // both operands contracted over their rows
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
-                     adS = smem_u32(sdS);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), adO = smem_u32(sdO), aP = smem_u32(sP), adS = smem_u32(sdS);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kStatusTimeoutMma);
       for (int it = 0; it < iters && ok; ++it) {
         const uint32_t ph = it & 1;
-        ok = mbar_wait_bounded(qdo_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        const int st = it & 1;
+        const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES);
+        ok = mbar_wait_bounded(&q_full[st], (it >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
         tc_fence_after();
-        // S = Q K^T and dP = dO V^T (S / dP of the previous pair were consumed before P / dS were published)
+        // S = Q K^T (S / dP of the previous pair were consumed before P / dS were published)
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tS, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
+        umma_commit(s_full);
+        ok = mbar_wait_bounded(do_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+        // dP = dO V^T
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
-        umma_commit(sdp_full);
+        umma_commit(dp_full);
         ok = mbar_wait_bounded(pds_full, ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
         tc_fence_after();
-        // dV += P^T dO and dK += dS^T Q
+        // dV += P^T dO first: its completion frees the dO buffer for the next tile's load
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdV, desc_mn(aP, k), desc_mn(adO, k), idesc_mm, (it | k) != 0);
+        umma_commit(do_empty);
+        // dK += dS^T Q
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdK, desc_mn(adS, k), desc_mn(aQ, k), idesc_mm, (it | k) != 0);
-        umma_commit(qdo_empty);
+        umma_commit(&q_empty[st]);
         umma_commit(pds_empty);
       }
       if (ok) umma_commit(acc_full);
@@ -238,7 +262,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       const bool diag = on_diag || jt * BT < lo_last;  // the tile needs the element-wise mask
       const int hi_col = on_diag ? row : BT - 1;       // visible key columns of this query row: [lo_col, hi_col]
       const int lo_col = my_lo - jt * BT;
-      ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = mbar_wait_bounded(s_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (it > 0) {
@@ -247,20 +271,17 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         if (!ok) break;
       }
       tc_fence_after();
-      uint32_t s0[32], g0[32], s1[32], g1[32];
-      tmem_ld_32x32(tS + lane_addr + c_begin * 32, s0);
-      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, g0);
+      // phase 1, needs S only: probabilities of this thread's 64 columns (kept in registers for phase 2), P tile
+      uint32_t t0[32], t1[32];
+      float pv[2][32];
+      tmem_ld_32x32(tS + lane_addr + c_begin * 32, t0);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = c_begin + cc;
-        uint32_t(&s)[32] = cc ? s1 : s0;
-        uint32_t(&g)[32] = cc ? g1 : g0;
+        uint32_t(&s)[32] = cc ? t1 : t0;
         tmem_ld_wait();
-        if (cc == 0) {  // second chunk's loads fly while the first is processed
-          tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, s1);
-          tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, g1);
-        }
-        uint32_t pw[16], dw[16];
+        if (cc == 0) tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, t1);  // flies while the first chunk is processed
+        uint32_t pw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
@@ -269,12 +290,31 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
             if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
             if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale;
-          const float d1 = p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale;
+          pv[cc][2 * i] = p0;
+          pv[cc][2 * i + 1] = p1;
           pw[i] = pack_bf16x2(p0, p1);
-          dw[i] = pack_bf16x2(d0, d1);
         }
         store_tile_row_chunk(sP, row, c, pw);
+      }
+      // phase 2, once dP = dO V^T has landed: dS = P (dP - delta) scale
+      ok = mbar_wait_bounded(dp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, t0);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c_begin + cc;
+        uint32_t(&g)[32] = cc ? t1 : t0;
+        tmem_ld_wait();
+        if (cc == 0) tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, t1);
+        uint32_t dw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float d0 = pv[cc][2 * i] * (__uint_as_float(g[2 * i]) - dl) * p.scale;
+          const float d1 = pv[cc][2 * i + 1] * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale;
+          dw[i] = pack_bf16x2(d0, d1);
+        }
         store_tile_row_chunk(sdS, row, c, dw);
       }
       fence_proxy_async_smem();  // make the tiles visible to the tensor core (async proxy)

@@ -32,6 +32,24 @@ def test_output_discard_checkpoint_matches_plain_autograd():
         torch.testing.assert_close(a, b)
 
 
+def test_native_storage_rebind_is_zero_copy_and_reaches_saved_views():
+    from olmo_core_b200.nn.output_discard_checkpoint import native_rebind_available
+    from olmo_core_b200.ops.build import build_native
+
+    build_native(verbose=False)
+    assert native_rebind_available()
+    kept = torch.arange(12.0)
+    view = kept.view(3, 4)  # stands for an autograd-saved alias of the discarded tensor
+    impl = kept.untyped_storage()._cdata
+    kept.untyped_storage().resize_(0)
+    fresh = torch.full((12,), 7.0)
+    fresh_ptr = fresh.data_ptr()
+    torch.ops.ocb_native.rebind_storage(kept, fresh)
+    assert kept.untyped_storage()._cdata == impl and kept.data_ptr() == fresh_ptr and kept._version == 0
+    del fresh  # the borrowed allocation stays alive through the reference the rebound storage holds
+    assert torch.equal(view, torch.full((3, 4), 7.0))
+
+
 def test_causal_conv_is_causal_and_respects_documents():
     torch.manual_seed(0)
     conv = CausalConv1d(hidden_size=6, kernel_size=4, activation=None)
