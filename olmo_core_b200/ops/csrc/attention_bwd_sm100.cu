@@ -25,6 +25,18 @@
 namespace ocb {
 namespace {
 
+// Optional cycle accounting of one CTA's roles (compile with -DOCB_ATTN_PROFILE; read with ocb_attention_prof_read).
+#ifdef OCB_ATTN_PROFILE
+__device__ long long g_attn_prof[32];
+#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64()
+#define PROF_LAP(i) do { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_STORE(base, n, cond) do { if (cond) for (int i_ = 0; i_ < (n); ++i_) g_attn_prof[(base) + i_] = prof_acc[i_]; } while (0)
+#else
+#define PROF_DECL(n) do {} while (0)
+#define PROF_LAP(i) do {} while (0)
+#define PROF_STORE(base, n, cond) do {} while (0)
+#endif
+
 constexpr int BT = 128;                    // tile rows (queries and keys)
 constexpr int BD = 128;                    // head dim
 constexpr int TILE_BYTES = BT * BD * 2;    // 32 KB
@@ -256,6 +268,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qi * BT + row;
       const float lse2 = p.lse[stat] * LOG2E;
       const float dl = p.delta[stat];
+      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse2, -lse2);
+      const uint64_t scl2 = pack_f32x2(p.scale, p.scale), nds2 = pack_f32x2(-dl * p.scale, -dl * p.scale);
       const bool on_diag = p.causal && qi == jt;
       const int my_lo = p.row_lo ? p.row_lo[b * p.T + qi * BT + row] : 0;
       const int lo_last = p.row_lo ? p.row_lo[b * p.T + qi * BT + BT - 1] : 0;
@@ -273,7 +287,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       tc_fence_after();
       // phase 1, needs S only: probabilities of this thread's 64 columns (kept in registers for phase 2), P tile
       uint32_t t0[32], t1[32];
-      float pv[2][32];
+      uint64_t pv[2][16];  // the probabilities as packed fp32 pairs
       tmem_ld_32x32(tS + lane_addr + c_begin * 32, t0);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -282,17 +296,24 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         tmem_ld_wait();
         if (cc == 0) tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, t1);  // flies while the first chunk is processed
         uint32_t pw[16];
+        float p0[16], p1[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
-          if (diag) {
-            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
+          unpack_f32x2(fma_f32x2(pack_u32x2(s[2 * i], s[2 * i + 1]), sc2, nl2), p0[i], p1[i]);
+          p0[i] = fast_exp2(p0[i]);
+          p1[i] = fast_exp2(p1[i]);
+        }
+        if (diag) {  // warp-uniform: only tiles on the diagonal or on a window / document edge pay for the mask
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0[i] = 0.f;
+            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1[i] = 0.f;
           }
-          pv[cc][2 * i] = p0;
-          pv[cc][2 * i + 1] = p1;
-          pw[i] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pv[cc][i] = pack_f32x2(p0[i], p1[i]);
+          pw[i] = pack_bf16x2(p0[i], p1[i]);
         }
         store_tile_row_chunk(sP, row, c, pw);
       }
@@ -311,8 +332,9 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         uint32_t dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float d0 = pv[cc][2 * i] * (__uint_as_float(g[2 * i]) - dl) * p.scale;
-          const float d1 = pv[cc][2 * i + 1] * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale;
+          const uint64_t t = fma_f32x2(pack_u32x2(g[2 * i], g[2 * i + 1]), scl2, nds2);  // (dP - delta) scale
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(t, pv[cc][i]), d0, d1);
           dw[i] = pack_bf16x2(d0, d1);
         }
         store_tile_row_chunk(sdS, row, c, dw);
@@ -344,8 +366,18 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
 
 // ------------------------------------------------------------------------------------------------------------
 // 3. dQ
+//
+// One CTA per (query tile, head, batch) walks the key/value tiles with TWO tiles in flight: softmax warps 2-5 own the
+// even tiles, warps 6-9 the odd ones (one thread per query row, all 128 columns), so that while one group turns its S
+// into P and dS the tensor core works on the other group's tile. Tensor memory: R[0], R[1] (S of the even / odd tile,
+// later its dS as packed bf16, the A operand of dQ += dS K), X (dP of either tile, handed back as soon as it has been
+// read) and the dQ accumulator. The issue order  S(0) S(1) dP(0) | dP(j+1) dQ(j) S(j+2) ...  needs no wait between an
+// MMA and a later MMA that overwrites what it read: tcgen05.mma operations of one thread execute in order.
+// P stays in registers between the two phases as packed bf16 -- the same rounding the dV product sees.
 // ------------------------------------------------------------------------------------------------------------
-constexpr int DQ_SMEM = 6 * TILE_BYTES + 1024 + 256;  // Q, dO resident; K, V in a two-stage ring
+constexpr int DQ_KST = 3;  // K stages: a tile's K is read by S and again, much later, by dQ
+constexpr int DQ_VST = 2;  // V stages: read by dP only
+constexpr int DQ_SMEM = (2 + DQ_KST + DQ_VST) * TILE_BYTES + 1024 + 256;
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -355,15 +387,20 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + 1 * TILE_BYTES;
-  uint8_t* sKV = smem + 2 * TILE_BYTES;  // stage s: K at sKV + 2 s TILE_BYTES, V one tile after it
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint8_t* sK = smem + 2 * TILE_BYTES;             // stage s at sK + s * TILE_BYTES
+  uint8_t* sV = smem + (2 + DQ_KST) * TILE_BYTES;  // stage s at sV + s * TILE_BYTES
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + DQ_KST + DQ_VST) * TILE_BYTES);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]: the next key/value tile is loaded while the current one is in use
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* ds_full = bars + 6;   // dS is in TMEM (4 warp arrivals)
-  uint64_t* dq_done = bars + 7;   // dQ += dS K has read dS (and K): S may be overwritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* k_full = bars + 1;    // [3]
+  uint64_t* k_empty = bars + 4;   // [3] dQ += dS K has read the stage
+  uint64_t* v_full = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 9;   // [2] dP = dO V^T has read the stage
+  uint64_t* s_full = bars + 11;   // [2] S of an even / odd tile is in R[0] / R[1]
+  uint64_t* dp_full = bars + 13;  // [2] dP of an even / odd tile is in X
+  uint64_t* x_free = bars + 15;   // [2] the even / odd group has read X (4 warp arrivals)
+  uint64_t* ds_full = bars + 17;  // [2] dS of an even / odd tile is in R[0] / R[1] (4 warp arrivals)
+  uint64_t* acc_full = bars + 19;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -378,13 +415,19 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int st = 0; st < 2; ++st) {
-      mbar_init(&kv_full[st], 1);
-      mbar_init(&kv_empty[st], 1);
+    for (int st = 0; st < DQ_KST; ++st) {
+      mbar_init(&k_full[st], 1);
+      mbar_init(&k_empty[st], 1);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 8);
-    mbar_init(dq_done, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(&v_full[st], 1);
+      mbar_init(&v_empty[st], 1);
+      mbar_init(&s_full[st], 1);
+      mbar_init(&dp_full[st], 1);
+      mbar_init(&x_free[st], 4);
+      mbar_init(&ds_full[st], 4);
+    }
+    mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -396,7 +439,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256, tdS = tmem_base + 384 /* packed bf16 */;
+  const uint32_t tR = tmem_base /* R[r] at tR + 128 r */, tX = tmem_base + 256, tdQ = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -408,16 +451,19 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int kv_row0 = b * p.T + (j_lo + j) * BT;
-        const int st = j & 1;
-        uint8_t* sK = sKV + st * 2 * TILE_BYTES;
-        uint8_t* sV = sK + TILE_BYTES;
-        ok = mbar_wait_bounded(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        const int ks = j % DQ_KST, vs = j & 1;
+        uint8_t* dK_ = sK + ks * TILE_BYTES;
+        uint8_t* dV_ = sV + vs * TILE_BYTES;
+        ok = mbar_wait_bounded(&k_empty[ks], ((j / DQ_KST) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-        tma_load_2d(sK, &tma_k, &kv_full[st], hk * BD, kv_row0);
-        tma_load_2d(sK + HALF_BYTES, &tma_k, &kv_full[st], hk * BD + 64, kv_row0);
-        tma_load_2d(sV, &tma_v, &kv_full[st], hk * BD, kv_row0);
-        tma_load_2d(sV + HALF_BYTES, &tma_v, &kv_full[st], hk * BD + 64, kv_row0);
+        mbar_arrive_expect_tx(&k_full[ks], TILE_BYTES);
+        tma_load_2d(dK_, &tma_k, &k_full[ks], hk * BD, kv_row0);
+        tma_load_2d(dK_ + HALF_BYTES, &tma_k, &k_full[ks], hk * BD + 64, kv_row0);
+        ok = mbar_wait_bounded(&v_empty[vs], ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&v_full[vs], TILE_BYTES);
+        tma_load_2d(dV_, &tma_v, &v_full[vs], hk * BD, kv_row0);
+        tma_load_2d(dV_ + HALF_BYTES, &tma_v, &v_full[vs], hk * BD + 64, kv_row0);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -427,94 +473,170 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, BD, 0, 1);  // A = dS from TMEM, B = K contracted over its rows
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK0 = smem_u32(sK), aV0 = smem_u32(sV);
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      // S(j) = Q K_j^T into R[j & 1]
+      auto issue_s = [&](int j) -> bool {
+        const int ks = j % DQ_KST;
+        if (!mbar_wait_bounded(&k_full[ks], (j / DQ_KST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t aK = aK0 + ks * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tR + (j & 1) * 128, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      // dP(j) = dO V_j^T into X (the caller has made sure that X was read)
+      auto issue_dp = [&](int j) -> bool {
+        const int vs = j & 1;
+        if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t aV = aV0 + vs * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tX, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
+        umma_commit(&dp_full[j & 1]);
+        umma_commit(&v_empty[vs]);
+        return true;
+      };
+      ok = ok && issue_s(0);
+      if (n_kv > 1) ok = ok && issue_s(1);
+      ok = ok && issue_dp(0);
+      PROF_DECL(4);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const uint32_t ph = j & 1;
-        const int st = j & 1;
-        const uint32_t aK = smem_u32(sKV + st * 2 * TILE_BYTES), aV = aK + TILE_BYTES;
-        ok = mbar_wait_bounded(&kv_full[st], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma);
-        if (!ok) break;
-        if (j > 0) {
-          ok = mbar_wait_bounded(dq_done, ph ^ 1u, abort_flag, p.status, kStatusTimeoutMma);
+        const int r = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        PROF_LAP(3);
+        if (j + 1 < n_kv) {
+          ok = mbar_wait_bounded(&x_free[r], ph, abort_flag, p.status, kStatusTimeoutMma);
           if (!ok) break;
+          PROF_LAP(0);
+          ok = issue_dp(j + 1);
+          if (!ok) break;
+          PROF_LAP(1);
         }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
-        umma_commit(sdp_full);
-        ok = mbar_wait_bounded(ds_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        ok = mbar_wait_bounded(&ds_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
+        PROF_LAP(2);
         tc_fence_after();
+        const int ks = j % DQ_KST;
+        const uint32_t aK = aK0 + ks * TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdS + k * 8, desc_mn(aK, k), idesc_dq, (j | k) != 0);
-        umma_commit(&kv_empty[st]);
-        umma_commit(dq_done);
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tR + r * 128 + k * 8, desc_mn(aK, k), idesc_dq, (j | k) != 0);
+        umma_commit(&k_empty[ks]);
+        if (j + 2 < n_kv) ok = issue_s(j + 2);  // overwrites dS(j) only after dQ(j): same thread, in order
       }
+      if (ok) umma_commit(acc_full);
+      PROF_LAP(3);
+      PROF_STORE(8, 4, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   } else {
     const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;  // 0: even tiles (and dQ columns [0,64) at the end), 1: odd tiles ([64,128))
     const int row = quad * 32 + lane;
-    const int c_begin = ((warp - 2) >> 2) * 2;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qt * BT + row;
     const float lse2 = p.lse[stat] * LOG2E;
     const float dl = p.delta[stat];
     const int my_lo = p.row_lo ? p.row_lo[q_row0 + row] : 0;
+    const uint32_t tRg = tR + grp * 128 + lane_addr;
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse2, -lse2);
+    const uint64_t scl2 = pack_f32x2(p.scale, p.scale), nds2 = pack_f32x2(-dl * p.scale, -dl * p.scale);
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const uint32_t ph = j & 1;
+    PROF_DECL(8);
+    for (int j = grp; j < n_kv; j += 2) {
+      PROF_LAP(4);
+      const uint32_t ph = (j >> 1) & 1;
       const int kv0 = (j_lo + j) * BT;
       const bool on_diag = p.causal && j_lo + j == qt;
       const bool diag = on_diag || kv0 < lo_last;
       const int hi_col = on_diag ? row : BT - 1;
       const int lo_col = my_lo - kv0;
-      ok = mbar_wait_bounded(sdp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = mbar_wait_bounded(&s_full[grp], ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      PROF_LAP(0);
       tc_fence_after();
-      uint32_t s0[32], g0[32], s1[32], g1[32];
-      tmem_ld_32x32(tS + lane_addr + c_begin * 32, s0);
-      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, g0);
+      // phase 1: P of the whole row, kept as packed bf16
+      uint32_t ppk[64];
+      uint32_t g0[16], g1[16];  // 16-column pieces keep the live set under the register limit
+      tmem_ld_32x16(tRg, g0);
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = c_begin + cc;
-        uint32_t(&s)[32] = cc ? s1 : s0;
-        uint32_t(&g)[32] = cc ? g1 : g0;
+      for (int c = 0; c < 8; ++c) {
+        uint32_t(&s)[16] = (c & 1) ? g1 : g0;
+        PROF_LAP(1);
         tmem_ld_wait();
-        if (cc == 0) {
-          tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, s1);
-          tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, g1);
+        PROF_LAP(5);
+        if (c < 7) tmem_ld_32x16(tRg + (c + 1) * 16, (c & 1) ? g0 : g1);
+        uint64_t e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = fma_f32x2(pack_u32x2(s[2 * i], s[2 * i + 1]), sc2, nl2);
+        float p0[8], p1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          unpack_f32x2(e[i], p0[i], p1[i]);
+          p0[i] = fast_exp2(p0[i]);
+          p1[i] = fast_exp2(p1[i]);
         }
+        if (diag) {  // warp-uniform: only tiles on the diagonal or on a window / document edge pay for the mask
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (c * 16 + 2 * i > hi_col || c * 16 + 2 * i < lo_col) p0[i] = 0.f;
+            if (c * 16 + 2 * i + 1 > hi_col || c * 16 + 2 * i + 1 < lo_col) p1[i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ppk[c * 8 + i] = pack_bf16x2(p0[i], p1[i]);
+      }
+      // phase 2: dS = P (dP - delta) scale, written over S as packed bf16
+      PROF_LAP(1);
+      ok = mbar_wait_bounded(&dp_full[grp], ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      PROF_LAP(2);
+      tc_fence_after();
+      tmem_ld_32x16(tX + lane_addr, g0);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint32_t dw[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
-          if (diag) {
-            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t(&g)[16] = hh ? g1 : g0;
+          PROF_LAP(3);
+          tmem_ld_wait();
+          PROF_LAP(6);
+          if (c < 3 || hh == 0) {
+            tmem_ld_32x16(tX + lane_addr + (2 * c + hh + 1) * 16, hh ? g0 : g1);
+          } else {
+            tc_fence_before();  // X has been read: the next tile's dP may overwrite it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&x_free[grp]);
           }
-          dw[i] = pack_bf16x2(p0 * (__uint_as_float(g[2 * i]) - dl) * p.scale,
-                              p1 * (__uint_as_float(g[2 * i + 1]) - dl) * p.scale);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint64_t t = fma_f32x2(pack_u32x2(g[2 * i], g[2 * i + 1]), scl2, nds2);  // (dP - delta) scale
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(t, bf16x2_to_f32x2(ppk[c * 16 + hh * 8 + i])), d0, d1);
+            dw[hh * 8 + i] = pack_bf16x2(d0, d1);
+          }
         }
-        tmem_st_32x16(tdS + lane_addr + c * 16, dw);
+        tmem_st_32x16(tRg + c * 16, dw);
       }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[grp]);
+      PROF_LAP(3);
     }
+    PROF_STORE(0, 8, warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
-      ok = mbar_wait_bounded(dq_done, (n_kv - 1) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
       const long long token = static_cast<long long>(q_row0) + row;
-      store_acc_row(p.dq + token * p.ld_dq + h * BD, tdQ + lane_addr, c_begin);
+      store_acc_row(p.dq + token * p.ld_dq + h * BD, tdQ + lane_addr, grp * 2);
     }
   }
 
@@ -537,6 +659,12 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, int heads, long
 }  // namespace ocb
 
 using namespace ocb;
+
+#ifdef OCB_ATTN_PROFILE
+extern "C" int ocb_attention_prof_read(long long* host32) {
+  return cudaMemcpyFromSymbol(host32, g_attn_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // Gradients of ocb_attention_fwd. dout/out/q/dq: [B, T, H, D]; k, v, dk, dv: [B, T, Hkv, D]; lse: [B, H, T] from the
 // forward pass; delta: [B, H, T] fp32 scratch (written here). dq/dk/dv are written densely (row stride heads * D).

@@ -197,7 +197,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const int hi_col = on_diag ? row : AT_TILE - 1;  // visible columns of this row: [lo_col, hi_col]
       const int lo_col = my_lo - kv0;
       // pass 1: row maximum. The next chunk's TMEM load is in flight while the current chunk is processed.
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // four chains instead of one
       uint32_t ra[32], rb[32];
       tmem_ld_32x32(tmem_S + lane_addr, ra);
 #pragma unroll
@@ -209,12 +209,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, (c * 32 + i > hi_col || c * 32 + i < lo_col) ? -INFINITY : __uint_as_float(cur[i]));
+            mx0 = fmaxf(mx0, (c * 32 + i > hi_col || c * 32 + i < lo_col) ? -INFINITY : __uint_as_float(cur[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(cur[i]));
+            mx1 = fmaxf(mx1, __uint_as_float(cur[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(cur[i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(cur[i + 3]));
+          }
         }
       }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       mx *= p.scale_log2;  // the scale is positive, so it commutes with the maximum
       const bool grow = mx > m_ref + AT_RESCALE_THRESHOLD;  // also true for the first tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
@@ -235,7 +241,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         m_ref = m_new;
       }
       // pass 2: probabilities relative to m_ref, written as bf16 pairs over the consumed part of S
-      float sum = 0.f;
+      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nm2 = pack_f32x2(-m_ref, -m_ref);
+      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;  // packed fp32 pairs: two adds per instruction, two chains
       tmem_ld_32x32(tmem_S + lane_addr, ra);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -244,19 +251,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tmem_ld_wait();
         if (c < 3) tmem_ld_32x32(tmem_S + lane_addr + (c + 1) * 32, nxt);
         uint32_t pk[16];
+        float p0[16], p1[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, -m_ref));
-          float p1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, -m_ref));
-          if (diag) {
-            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1 = 0.f;
+          unpack_f32x2(fma_f32x2(pack_u32x2(cur[2 * i], cur[2 * i + 1]), sc2, nm2), p0[i], p1[i]);
+          p0[i] = fast_exp2(p0[i]);
+          p1[i] = fast_exp2(p1[i]);
+        }
+        if (diag) {  // warp-uniform: only tiles on the diagonal or on a window / document edge pay for the mask
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0[i] = 0.f;
+            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1[i] = 0.f;
           }
-          sum += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          sum_a = add_f32x2(sum_a, pack_f32x2(p0[i], p1[i]));
+          sum_b = add_f32x2(sum_b, pack_f32x2(p0[i + 1], p1[i + 1]));
+          pk[i] = pack_bf16x2(p0[i], p1[i]);
+          pk[i + 1] = pack_bf16x2(p0[i + 1], p1[i + 1]);
         }
         // P chunk c lands on S columns [16c, 16c+16): all of them were loaded (chunks <= c+1 are in registers)
         tmem_st_32x16(tmem_P + lane_addr + c * 16, pk);
+      }
+      float sum;
+      {
+        float s0, s1;
+        unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
+        sum = s0 + s1;
       }
       l += sum;
       tmem_st_wait();
