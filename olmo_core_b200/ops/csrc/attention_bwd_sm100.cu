@@ -8,14 +8,13 @@
 //
 // Three launches, none of which needs atomics or a cross-CTA reduction:
 //   1. attn_delta_kernel : delta = rowsum(O o dO)                                  (memory bound)
-//   2. attn_dkdv_kernel  : one CTA per (K/V tile, kv head, batch) walks the query tiles (and the query heads of its
-//      group); S and dP are tcgen05.mma results in TMEM, the softmax warps turn them into bf16 P and dS tiles in
-//      shared memory laid out so that the SAME tile serves as a K-major and as an MN-major UMMA operand, and
-//      dV += P^T dO, dK += dS^T Q accumulate in TMEM (4 x 128 columns = all of TMEM);
+//   2. attn_dkdv_kernel  : one CTA per (K/V tile, kv head, batch) walks 64-row query sub-tiles, computing S^T and dP^T
+//      so that P^T and dS^T stay in tensor memory as the A operands of dV += P^T dO and dK += dS^T Q;
 //   3. attn_dq_kernel    : one CTA per (query tile, head, batch) walks the K/V tiles; dS goes back to TMEM as packed
-//      bf16 and is the A operand of dQ += dS K straight from tensor memory.
-// In both, every query row is shared by two softmax threads (columns [0,64) and [64,128)) in warps whose rank modulo
-// four -- the TMEM lane quadrant a warp may access -- is the same.
+//      bf16 and is the A operand of dQ += dS K.
+// Both keep TWO tiles in flight: two groups of four softmax warps alternate, so the exponentials of one tile run while
+// the tensor core works on the other. The softmax loops use packed fp32-pair arithmetic (fma/mul.f32x2) and take the
+// element-wise mask only on tiles that touch the diagonal or a window / document edge.
 // Recomputing S and dP in both kernels costs two extra tile products (7 instead of 5) and buys independence.
 
 #include "common.cuh"
@@ -61,15 +60,15 @@ struct AttnBwdParams {
   int* status;
 };
 
-// [128 rows x 128 cols] bf16 tile stored as two [128 x 64] boxes with 128-byte swizzle.
-// K-major view (contraction over the columns): k-step k = columns [16k, 16k+16).
-__device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
-  return make_smem_desc_sw128(tile + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
+// [128 rows x 128 cols] bf16 tile stored as two [128 x 64] boxes with 128-byte swizzle (sub-tiles: two [64 x 64] boxes).
+// K-major view (contraction over the columns): k-step k = columns [16k, 16k+16), LBO field unused (16).
+// MN-major view (contraction over the rows): k-step k = rows [16k, 16k+16), LBO = distance between the two boxes.
+// Both as descriptor low words (see desc_lo_sw128 / umma_ss_lean): stepping costs one integer add per instruction.
+constexpr uint32_t kHi = desc_hi_sw128(1024);
+__device__ __forceinline__ constexpr uint32_t koff_k(int k, uint32_t box_bytes) {  // K-major k-step, in 16-byte units
+  return ((k >> 2) * box_bytes + (k & 3) * 32) >> 4;
 }
-// MN-major view (contraction over the rows): k-step k = rows [16k, 16k+16).
-__device__ __forceinline__ uint64_t desc_mn(uint32_t tile, int k) {
-  return make_smem_desc_sw128(tile + k * 2048, HALF_BYTES, 1024);
-}
+__device__ __forceinline__ constexpr uint32_t koff_mn(int k) { return (k * 2048) >> 4; }  // MN-major k-step
 
 // Store 32 consecutive bf16 pairs... i.e. columns [32c, 32c+32) of row `row` (16 packed words) into a swizzled tile.
 __device__ __forceinline__ void store_tile_row_chunk(uint8_t* tile, int row, int c, const uint32_t (&w)[16]) {
@@ -120,36 +119,45 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 
 // ------------------------------------------------------------------------------------------------------------
 // 2. dK, dV
+//
+// One CTA per (K/V tile, kv head, batch) walks 64-row query sub-tiles ("units": the query heads of the group, their
+// query tiles, two halves each) with TWO units in flight: softmax warps 2-5 own the even units, warps 6-9 the odd ones.
+// Everything is computed transposed so that the probabilities never leave tensor memory:
+//     S^T = K Q^T, dP^T = V dO^T           [128 keys x 64 queries], SS products with N = 64
+//     P^T, dS^T                            packed bf16 written over S^T / dP^T (one thread per key row, 64 columns)
+//     dV += P^T dO,  dK += dS^T Q          A operand straight from tensor memory, B = the 64-row dO / Q sub-tile
+// Tensor memory: dV, dK (2 x 128 columns) and, per unit parity, S^T | dP^T (2 x (64 + 64) columns). The row statistics
+// are per COLUMN here; the producer brings lse and delta of the 64 queries into shared memory with the sub-tiles.
+// Issue order  S(0) dP(0) S(1) dP(1) | dV(u) dK(u) S(u+2) dP(u+2) ...: an MMA that overwrites what an earlier MMA of
+// the same thread reads needs no wait, they execute in order.
 // ------------------------------------------------------------------------------------------------------------
-constexpr int DKDV_SMEM = 7 * TILE_BYTES + 1024 + 256;  // K, V, two Q stages, dO, P, dS
+constexpr int SUB = 64;                   // query rows per unit
+constexpr int SUB_BYTES = SUB * BD * 2;   // 16 KB: two [64 x 64] boxes
+constexpr int SUB_BOX = SUB_BYTES / 2;
+constexpr int KV_NST = 4;                 // stages of (Q sub-tile, dO sub-tile, lse, delta)
+constexpr int STAT_BYTES = 2 * SUB * 4;   // lse then delta of the 64 queries
+constexpr int DKDV_SMEM = 2 * TILE_BYTES + KV_NST * (2 * SUB_BYTES + STAT_BYTES) + 1024 + 256;
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
-attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                 const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do,
+attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, const __grid_constant__ CUtensorMap tma_k,
+                 const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do /* 64-row boxes */,
                  const AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
-  uint8_t* sV = smem + 1 * TILE_BYTES;
-  // Q is double-buffered and loaded one query tile ahead; dO has one buffer that is refilled as soon as dV += P^T dO has
-  // read it (that product is issued before dK += dS^T Q for this reason). S and dP are signalled separately, so the
-  // exponentials of a tile run while its dO is still in flight.
-  uint8_t* sQ = smem + 2 * TILE_BYTES;   // stage s at sQ + s * TILE_BYTES
-  uint8_t* sdO = smem + 4 * TILE_BYTES;
-  uint8_t* sP = smem + 5 * TILE_BYTES;   // [q rows x kv cols]
-  uint8_t* sdS = smem + 6 * TILE_BYTES;  // [q rows x kv cols]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQdO = smem + 2 * TILE_BYTES;  // stage s: Q sub-tile at sQdO + 2 s SUB_BYTES, dO one sub-tile after it
+  float* sStat = reinterpret_cast<float*>(smem + 2 * TILE_BYTES + KV_NST * 2 * SUB_BYTES);  // stage s: [lse 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * TILE_BYTES + KV_NST * (2 * SUB_BYTES + STAT_BYTES));
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;     // [2]
-  uint64_t* q_empty = bars + 3;    // [2] dK += dS^T Q has read the stage
-  uint64_t* do_full = bars + 5;
-  uint64_t* do_empty = bars + 6;   // dV += P^T dO has read dO
-  uint64_t* s_full = bars + 7;     // S is in TMEM
-  uint64_t* dp_full = bars + 8;    // dP is in TMEM
-  uint64_t* pds_full = bars + 9;   // P and dS tiles are in shared memory (8 warp arrivals)
-  uint64_t* pds_empty = bars + 10; // the MMAs that read P / dS have finished
-  uint64_t* acc_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* full = bars + 1;      // [4] Q, dO, lse, delta of a unit have landed
+  uint64_t* empty = bars + 5;     // [4] dK += dS^T Q of the unit has finished
+  uint64_t* s_full = bars + 9;    // [2] S^T of an even / odd unit is in TMEM
+  uint64_t* dp_full = bars + 11;  // [2] dP^T
+  uint64_t* p_full = bars + 13;   // [2] P^T is in TMEM (4 warp arrivals)
+  uint64_t* ds_full = bars + 15;  // [2] dS^T is in TMEM (4 warp arrivals)
+  uint64_t* acc_full = bars + 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,21 +167,24 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   // query tiles [i_first, n_q) can see this key tile: up to the tile of the last query that sees its last key
   const int n_q = p.col_hi ? p.col_hi[b * p.T + jt * BT + BT - 1] / BT + 1 : p.T / BT;
   const int i_first = p.causal ? jt : 0;
-  const int iters = (n_q - i_first) * group;  // (query head of the group, query tile) pairs
+  const int per_head = (n_q - i_first) * 2;  // units per query head
+  const int units = per_head * group;
   const int kv_row0 = b * p.T + jt * BT;
+  // last query that sees the FIRST key of the tile: units that reach beyond it need the element-wise mask
+  const int hi_first = p.col_hi ? p.col_hi[kv_row0] : p.T - 1;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int st = 0; st < 2; ++st) {
-      mbar_init(&q_full[st], 1);
-      mbar_init(&q_empty[st], 1);
+    for (int st = 0; st < KV_NST; ++st) {
+      mbar_init(&full[st], 1);
+      mbar_init(&empty[st], 1);
     }
-    mbar_init(do_full, 1);
-    mbar_init(do_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(dp_full, 1);
-    mbar_init(pds_full, 8);
-    mbar_init(pds_empty, 1);
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&s_full[r], 1);
+      mbar_init(&dp_full[r], 1);
+      mbar_init(&p_full[r], 4);
+      mbar_init(&ds_full[r], 4);
+    }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -186,7 +197,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+  const uint32_t tdV = tmem_base, tdK = tmem_base + 128, tReg = tmem_base + 256;  // unit parity r: tReg + 128 r
 
   if (warp == 0) {
     if (lane == 0) {
@@ -196,21 +207,25 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       tma_load_2d(sV, &tma_v, kv_full, hk * BD, kv_row0);
       tma_load_2d(sV + HALF_BYTES, &tma_v, kv_full, hk * BD + 64, kv_row0);
       bool ok = true;
-      for (int it = 0; it < iters && ok; ++it) {
-        const int h = hk * group + it / (n_q - i_first);
-        const int q_row0 = b * p.T + (i_first + it % (n_q - i_first)) * BT;
-        const int st = it & 1;
-        uint8_t* q_dst = sQ + st * TILE_BYTES;
-        ok = mbar_wait_bounded(&q_empty[st], ((it >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
+      for (int u = 0; u < units && ok; ++u) {
+        const int h = hk * group + u / per_head;
+        const int rem = u % per_head;
+        const int q0 = (i_first + (rem >> 1)) * BT + (rem & 1) * SUB;  // position of the unit's first query
+        const int q_row0 = b * p.T + q0;
+        const int st = u % KV_NST;
+        uint8_t* q_dst = sQdO + st * 2 * SUB_BYTES;
+        uint8_t* do_dst = q_dst + SUB_BYTES;
+        float* stat_dst = sStat + st * 2 * SUB;
+        const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + q0;
+        ok = mbar_wait_bounded(&empty[st], ((u / KV_NST) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
-        mbar_arrive_expect_tx(&q_full[st], TILE_BYTES);
-        tma_load_2d(q_dst, &tma_q, &q_full[st], h * BD, q_row0);
-        tma_load_2d(q_dst + HALF_BYTES, &tma_q, &q_full[st], h * BD + 64, q_row0);
-        ok = mbar_wait_bounded(do_empty, (it & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
-        if (!ok) break;
-        mbar_arrive_expect_tx(do_full, TILE_BYTES);
-        tma_load_2d(sdO, &tma_do, do_full, h * BD, q_row0);
-        tma_load_2d(sdO + HALF_BYTES, &tma_do, do_full, h * BD + 64, q_row0);
+        mbar_arrive_expect_tx(&full[st], 2 * SUB_BYTES + STAT_BYTES);
+        tma_load_2d(q_dst, &tma_q, &full[st], h * BD, q_row0);
+        tma_load_2d(q_dst + SUB_BOX, &tma_q, &full[st], h * BD + 64, q_row0);
+        tma_load_2d(do_dst, &tma_do, &full[st], h * BD, q_row0);
+        tma_load_2d(do_dst + SUB_BOX, &tma_do, &full[st], h * BD + 64, q_row0);
+        bulk_load_1d(stat_dst, p.lse + stat, SUB * 4, &full[st]);
+        bulk_load_1d(stat_dst + SUB, p.delta + stat, SUB * 4, &full[st]);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -218,132 +233,166 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);  // both operands contracted over their columns
-      constexpr uint32_t idesc_mm = make_idesc_bf16(BT, BD, 1, 1);  // both operands contracted over their rows
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), adO = smem_u32(sdO), aP = smem_u32(sP), adS = smem_u32(sdS);
+      constexpr uint32_t idesc_st = make_idesc_bf16(BT, SUB, 0, 0);  // [128 keys x 64 queries], both contracted over d
+      constexpr uint32_t idesc_acc = make_idesc_bf16(BT, BD, 0, 1);  // A from TMEM, B contracted over its rows
+      const uint32_t aQdO = smem_u32(sQdO);
+      const uint32_t k_lo = desc_lo_sw128(smem_u32(sK), 16), v_lo = desc_lo_sw128(smem_u32(sV), 16);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kStatusTimeoutMma);
-      for (int it = 0; it < iters && ok; ++it) {
-        const uint32_t ph = it & 1;
-        const int st = it & 1;
-        const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES);
-        ok = mbar_wait_bounded(&q_full[st], (it >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma);
-        if (!ok) break;
+      // S^T and dP^T of unit u into the region of its parity
+      auto issue_sp = [&](int u) -> bool {
+        const int st = u % KV_NST;
+        if (!mbar_wait_bounded(&full[st], (u / KV_NST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
         tc_fence_after();
-        // S = Q K^T (S / dP of the previous pair were consumed before P / dS were published)
+        const uint32_t q_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, 16), do_lo = q_lo + (SUB_BYTES >> 4);
+        const uint32_t tS = tReg + (u & 1) * 128, tP = tS + SUB;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
-        umma_commit(s_full);
-        ok = mbar_wait_bounded(do_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        for (int k = 0; k < 8; ++k)
+          umma_ss_lean<0>(tS, k_lo + koff_k(k, HALF_BYTES), q_lo + koff_k(k, SUB_BOX), kHi, idesc_st, k != 0);
+        umma_commit(&s_full[u & 1]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss_lean<0>(tP, v_lo + koff_k(k, HALF_BYTES), do_lo + koff_k(k, SUB_BOX), kHi, idesc_st, k != 0);
+        umma_commit(&dp_full[u & 1]);
+        return true;
+      };
+      ok = ok && issue_sp(0);
+      if (units > 1) ok = ok && issue_sp(1);
+      PROF_DECL(4);
+      for (int u = 0; u < units && ok; ++u) {
+        PROF_LAP(3);
+        const int r = u & 1;
+        const uint32_t ph = (u >> 1) & 1;
+        const int st = u % KV_NST;
+        // MN-major views of the unit's Q / dO sub-tiles (the box distance is the LBO field of the low word)
+        const uint32_t qmn_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, SUB_BOX), domn_lo = qmn_lo + (SUB_BYTES >> 4);
+        const uint32_t tPT = tReg + r * 128, tdST = tPT + SUB;  // packed bf16 over the first 32 columns of S^T / dP^T
+        const uint32_t acc0 = u != 0;
+        ok = mbar_wait_bounded(&p_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
+        PROF_LAP(0);
         tc_fence_after();
-        // dP = dO V^T
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
-        umma_commit(dp_full);
-        ok = mbar_wait_bounded(pds_full, ph, abort_flag, p.status, kStatusTimeoutMma);
+        for (int k = 0; k < SUB / 16; ++k)
+          umma_ts_lean(tdV, tPT + k * 8, domn_lo + koff_mn(k), kHi, idesc_acc, k == 0 ? acc0 : 1u);
+        PROF_LAP(3);
+        ok = mbar_wait_bounded(&ds_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
+        PROF_LAP(1);
         tc_fence_after();
-        // dV += P^T dO first: its completion frees the dO buffer for the next tile's load
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tdV, desc_mn(aP, k), desc_mn(adO, k), idesc_mm, (it | k) != 0);
-        umma_commit(do_empty);
-        // dK += dS^T Q
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tdK, desc_mn(adS, k), desc_mn(aQ, k), idesc_mm, (it | k) != 0);
-        umma_commit(&q_empty[st]);
-        umma_commit(pds_empty);
+        for (int k = 0; k < SUB / 16; ++k)
+          umma_ts_lean(tdK, tdST + k * 8, qmn_lo + koff_mn(k), kHi, idesc_acc, k == 0 ? acc0 : 1u);
+        umma_commit(&empty[st]);
+        PROF_LAP(3);
+        if (u + 2 < units) ok = issue_sp(u + 2);  // overwrites P^T / dS^T of unit u only after the products above
+        PROF_LAP(2);
       }
       if (ok) umma_commit(acc_full);
+      PROF_STORE(24, 4, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   } else {
     const int quad = warp & 3;
-    const int row = quad * 32 + lane;  // query row within the tile
-    const int c_begin = ((warp - 2) >> 2) * 2;  // warps 2-5 take columns [0,64), warps 6-9 columns [64,128)
+    const int grp = (warp - 2) >> 2;  // 0: even units (and columns [0,64) of dV / dK at the end), 1: odd units
+    const int row = quad * 32 + lane;  // key row within the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int kv_pos = jt * BT + row;  // position of this thread's key in the sequence
+    const int vis_lo = p.causal ? kv_pos : 0;                               // first and
+    const int vis_hi = p.col_hi ? p.col_hi[b * p.T + kv_pos] : p.T - 1;    // last query that sees the key
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nlog2 = pack_f32x2(-LOG2E, -LOG2E);
+    const uint64_t scl2 = pack_f32x2(p.scale, p.scale), nscl2 = pack_f32x2(-p.scale, -p.scale);
+    const uint32_t tS = tReg + grp * 128 + lane_addr, tP = tS + SUB;
     bool ok = true;
-    for (int it = 0; it < iters; ++it) {
-      const uint32_t ph = it & 1;
-      const int h = hk * group + it / (n_q - i_first);
-      const int qi = i_first + it % (n_q - i_first);
-      const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qi * BT + row;
-      const float lse2 = p.lse[stat] * LOG2E;
-      const float dl = p.delta[stat];
-      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse2, -lse2);
-      const uint64_t scl2 = pack_f32x2(p.scale, p.scale), nds2 = pack_f32x2(-dl * p.scale, -dl * p.scale);
-      const bool on_diag = p.causal && qi == jt;
-      const int my_lo = p.row_lo ? p.row_lo[b * p.T + qi * BT + row] : 0;
-      const int lo_last = p.row_lo ? p.row_lo[b * p.T + qi * BT + BT - 1] : 0;
-      const bool diag = on_diag || jt * BT < lo_last;  // the tile needs the element-wise mask
-      const int hi_col = on_diag ? row : BT - 1;       // visible key columns of this query row: [lo_col, hi_col]
-      const int lo_col = my_lo - jt * BT;
-      ok = mbar_wait_bounded(s_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+    PROF_DECL(5);
+    for (int u = grp; u < units; u += 2) {
+      PROF_LAP(4);
+      const uint32_t ph = (u >> 1) & 1;
+      const int rem = u % per_head;
+      const int q0 = (i_first + (rem >> 1)) * BT + (rem & 1) * SUB;
+      const int st = u % KV_NST;
+      const float* st_lse = sStat + st * 2 * SUB;
+      const float* st_dl = st_lse + SUB;
+      const bool edge = (p.causal && q0 < jt * BT + BT - 1) || q0 + SUB - 1 > hi_first;  // uniform over the CTA
+      const int c_lo = vis_lo - q0, c_hi = vis_hi - q0;  // visible columns of this key row: [c_lo, c_hi]
+      ok = mbar_wait_bounded(&full[st], (u / KV_NST) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);  // lse, delta
+      ok = ok && mbar_wait_bounded(&s_full[grp], ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (it > 0) {
-        ok = mbar_wait_bounded(pds_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutEpilogue);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+      PROF_LAP(0);
       tc_fence_after();
-      // phase 1, needs S only: probabilities of this thread's 64 columns (kept in registers for phase 2), P tile
+      // phase 1: P^T of this key row for the 64 queries, kept as packed bf16 and written over S^T
+      uint32_t ppk[32];
       uint32_t t0[32], t1[32];
-      uint64_t pv[2][16];  // the probabilities as packed fp32 pairs
-      tmem_ld_32x32(tS + lane_addr + c_begin * 32, t0);
+      tmem_ld_32x32(tS, t0);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = c_begin + cc;
         uint32_t(&s)[32] = cc ? t1 : t0;
         tmem_ld_wait();
-        if (cc == 0) tmem_ld_32x32(tS + lane_addr + (c + 1) * 32, t1);  // flies while the first chunk is processed
-        uint32_t pw[16];
+        if (cc == 0) tmem_ld_32x32(tS + 32, t1);
         float p0[16], p1[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
+          const uint64_t nl2 = mul_f32x2(*reinterpret_cast<const uint64_t*>(st_lse + cc * 32 + 2 * i), nlog2);
           unpack_f32x2(fma_f32x2(pack_u32x2(s[2 * i], s[2 * i + 1]), sc2, nl2), p0[i], p1[i]);
           p0[i] = fast_exp2(p0[i]);
           p1[i] = fast_exp2(p1[i]);
         }
-        if (diag) {  // warp-uniform: only tiles on the diagonal or on a window / document edge pay for the mask
+        if (edge) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            if (c * 32 + 2 * i > hi_col || c * 32 + 2 * i < lo_col) p0[i] = 0.f;
-            if (c * 32 + 2 * i + 1 > hi_col || c * 32 + 2 * i + 1 < lo_col) p1[i] = 0.f;
+            if (cc * 32 + 2 * i < c_lo || cc * 32 + 2 * i > c_hi) p0[i] = 0.f;
+            if (cc * 32 + 2 * i + 1 < c_lo || cc * 32 + 2 * i + 1 > c_hi) p1[i] = 0.f;
           }
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pv[cc][i] = pack_f32x2(p0[i], p1[i]);
-          pw[i] = pack_bf16x2(p0[i], p1[i]);
-        }
-        store_tile_row_chunk(sP, row, c, pw);
+        for (int i = 0; i < 16; ++i) ppk[cc * 16 + i] = pack_bf16x2(p0[i], p1[i]);
       }
-      // phase 2, once dP = dO V^T has landed: dS = P (dP - delta) scale
-      ok = mbar_wait_bounded(dp_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_ld_32x32(tdP + lane_addr + c_begin * 32, t0);
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = c_begin + cc;
-        uint32_t(&g)[32] = cc ? t1 : t0;
-        tmem_ld_wait();
-        if (cc == 0) tmem_ld_32x32(tdP + lane_addr + (c + 1) * 32, t1);
-        uint32_t dw[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint64_t t = fma_f32x2(pack_u32x2(g[2 * i], g[2 * i + 1]), scl2, nds2);  // (dP - delta) scale
-          float d0, d1;
-          unpack_f32x2(mul_f32x2(t, pv[cc][i]), d0, d1);
-          dw[i] = pack_bf16x2(d0, d1);
-        }
-        store_tile_row_chunk(sdS, row, c, dw);
+      {
+        uint32_t(&lo)[16] = *reinterpret_cast<uint32_t(*)[16]>(&ppk[0]);
+        uint32_t(&hi)[16] = *reinterpret_cast<uint32_t(*)[16]>(&ppk[16]);
+        tmem_st_32x16(tS, lo);
+        tmem_st_32x16(tS + 16, hi);
       }
-      fence_proxy_async_smem();  // make the tiles visible to the tensor core (async proxy)
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
+      if (lane == 0) mbar_arrive(&p_full[grp]);
+      // phase 2: dS^T = P^T (dP^T - delta) scale, written over dP^T
+      PROF_LAP(1);
+      ok = mbar_wait_bounded(&dp_full[grp], ph, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      PROF_LAP(2);
+      tc_fence_after();
+      uint32_t dw[32];
+      tmem_ld_32x32(tP, t0);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t(&g)[32] = cc ? t1 : t0;
+        tmem_ld_wait();
+        if (cc == 0) tmem_ld_32x32(tP + 32, t1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint64_t nds2 = mul_f32x2(*reinterpret_cast<const uint64_t*>(st_dl + cc * 32 + 2 * i), nscl2);
+          const uint64_t t = fma_f32x2(pack_u32x2(g[2 * i], g[2 * i + 1]), scl2, nds2);  // (dP - delta) scale
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(t, bf16x2_to_f32x2(ppk[cc * 16 + i])), d0, d1);
+          dw[cc * 16 + i] = pack_bf16x2(d0, d1);
+        }
+      }
+      {
+        uint32_t(&lo)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[0]);
+        uint32_t(&hi)[16] = *reinterpret_cast<uint32_t(*)[16]>(&dw[16]);
+        tmem_st_32x16(tP, lo);
+        tmem_st_32x16(tP + 16, hi);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full[grp]);
+      PROF_LAP(3);
     }
+    PROF_STORE(16, 5, warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
@@ -351,8 +400,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     if (ok) {
       tc_fence_after();
       const long long token = static_cast<long long>(kv_row0) + row;  // accumulator row = key row
-      store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr, c_begin);
-      store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr, c_begin);
+      store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr, grp * 2);
+      store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr, grp * 2);
     }
   }
 
@@ -473,16 +522,19 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, BD, 0, 1);  // A = dS from TMEM, B = K contracted over its rows
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK0 = smem_u32(sK), aV0 = smem_u32(sV);
+      const uint32_t q_lo = desc_lo_sw128(smem_u32(sQ), 16), do_lo = desc_lo_sw128(smem_u32(sdO), 16);
+      const uint32_t k_lo0 = desc_lo_sw128(smem_u32(sK), 16), v_lo0 = desc_lo_sw128(smem_u32(sV), 16);
+      const uint32_t kmn_lo0 = desc_lo_sw128(smem_u32(sK), HALF_BYTES);  // MN-major view of the K stages
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, p.status, kStatusTimeoutMma);
       // S(j) = Q K_j^T into R[j & 1]
       auto issue_s = [&](int j) -> bool {
         const int ks = j % DQ_KST;
         if (!mbar_wait_bounded(&k_full[ks], (j / DQ_KST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t aK = aK0 + ks * TILE_BYTES;
+        const uint32_t k_lo = k_lo0 + ks * (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tR + (j & 1) * 128, desc_k(aQ, k), desc_k(aK, k), idesc_kk, k != 0);
+        for (int k = 0; k < 8; ++k)
+          umma_ss_lean<0>(tR + (j & 1) * 128, q_lo + koff_k(k, HALF_BYTES), k_lo + koff_k(k, HALF_BYTES), kHi, idesc_kk, k != 0);
         umma_commit(&s_full[j & 1]);
         return true;
       };
@@ -491,9 +543,10 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
         const int vs = j & 1;
         if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t aV = aV0 + vs * TILE_BYTES;
+        const uint32_t v_lo = v_lo0 + vs * (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ss(tX, desc_k(adO, k), desc_k(aV, k), idesc_kk, k != 0);
+        for (int k = 0; k < 8; ++k)
+          umma_ss_lean<0>(tX, do_lo + koff_k(k, HALF_BYTES), v_lo + koff_k(k, HALF_BYTES), kHi, idesc_kk, k != 0);
         umma_commit(&dp_full[j & 1]);
         umma_commit(&v_empty[vs]);
         return true;
@@ -519,9 +572,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
         PROF_LAP(2);
         tc_fence_after();
         const int ks = j % DQ_KST;
-        const uint32_t aK = aK0 + ks * TILE_BYTES;
+        const uint32_t kmn_lo = kmn_lo0 + ks * (TILE_BYTES >> 4);
+        const uint32_t acc0 = j != 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tR + r * 128 + k * 8, desc_mn(aK, k), idesc_dq, (j | k) != 0);
+        for (int k = 0; k < 8; ++k)
+          umma_ts_lean(tdQ, tR + r * 128 + k * 8, kmn_lo + koff_mn(k), kHi, idesc_dq, k == 0 ? acc0 : 1u);
         umma_commit(&k_empty[ks]);
         if (j + 2 < n_kv) ok = issue_s(j + 2);  // overwrites dS(j) only after dQ(j): same thread, in order
       }
@@ -648,10 +703,10 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   }
 }
 
-bool make_map(CUtensorMap* map, const void* ptr, long long rows, int heads, long long ld) {
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, int heads, long long ld, int box_rows = BT) {
   uint64_t dims[2] = {static_cast<uint64_t>(heads) * BD, static_cast<uint64_t>(rows)};
   uint64_t str[1] = {static_cast<uint64_t>(ld) * 2};
-  uint32_t box[2] = {64, BT};
+  uint32_t box[2] = {64, static_cast<uint32_t>(box_rows)};
   return get_tensor_map(map, ptr, 2, dims, str, box, 2);
 }
 
@@ -680,7 +735,9 @@ extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, co
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
   const long long rows = static_cast<long long>(B) * Tq;
   const long long ld_do = static_cast<long long>(H) * BD;  // dout is dense
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mq_sub, mdo_sub;  // *_sub: 64-row boxes for the dK/dV kernel's query sub-tiles
+  if (!make_map(&mq_sub, q, rows, H, ldq, SUB)) return -1005;
+  if (!make_map(&mdo_sub, dout, rows, H, ld_do, SUB)) return -1006;
   if (!make_map(&mq, q, rows, H, ldq)) return -1001;
   if (!make_map(&mk, k, rows, Hkv, ldk)) return -1002;
   if (!make_map(&mv, v, rows, Hkv, ldv)) return -1003;
@@ -715,7 +772,7 @@ extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, co
   p.row_lo = bounds;
   p.col_hi = bounds ? bounds + static_cast<long long>(B) * Tq : nullptr;
   p.status = status;
-  attn_dkdv_kernel<<<dim3(Tq / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq, mk, mv, mdo, p);
+  attn_dkdv_kernel<<<dim3(Tq / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq_sub, mk, mv, mdo_sub, p);
   attn_dq_kernel<<<dim3(Tq / BT, H, B), BWD_THREADS, DQ_SMEM, stream>>>(mq, mk, mv, mdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

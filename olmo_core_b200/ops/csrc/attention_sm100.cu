@@ -24,6 +24,18 @@
 
 namespace ocb {
 
+// Optional cycle accounting of one CTA's softmax warp (compile with -DOCB_ATTN_PROFILE; read with ocb_attention_fwd_prof_read).
+#ifdef OCB_ATTN_PROFILE
+__device__ long long g_attn_fwd_prof[16];
+#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64()
+#define PROF_LAP(i) do { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_STORE(base, n, cond) do { if (cond) for (int i_ = 0; i_ < (n); ++i_) g_attn_fwd_prof[(base) + i_] = prof_acc[i_]; } while (0)
+#else
+#define PROF_DECL(n) do {} while (0)
+#define PROF_LAP(i) do {} while (0)
+#define PROF_STORE(base, n, cond) do {} while (0)
+#endif
+
 constexpr int AT_TILE = 128;                       // rows of a Q tile and of a K/V tile
 constexpr int AT_D = 128;                          // head dim
 constexpr int AT_TILE_BYTES = AT_TILE * AT_D * 2;  // 32 KB
@@ -47,14 +59,13 @@ struct AttnFwdParams {
   int* status;
 };
 
-// K-major operand tile [128 rows x 128 cols] held as two [128 x 64] boxes: descriptor of k-step `k` (16 columns).
-__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_addr, int k) {
-  return make_smem_desc_sw128(tile_addr + (k >> 2) * AT_HALF_BYTES + (k & 3) * 32, 16, 1024);
-}
-// MN-major B operand (V: [kv rows x d cols], d contiguous): k-step `k` covers kv rows [16k, 16k+16).
-__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_addr, int k) {
-  return make_smem_desc_sw128(tile_addr + k * 2048, AT_HALF_BYTES, 1024);
-}
+// Operand tiles are [128 rows x 128 cols] held as two [128 x 64] boxes. Descriptors are handled as low words (see
+// desc_lo_sw128 / umma_ss_lean): stepping through a tile costs the issuing thread one integer add per instruction.
+// K-major view (contraction over the columns): k-step k = columns [16k, 16k+16); LBO field unused.
+// MN-major view (V: contraction over the kv rows): k-step k = rows [16k, 16k+16); LBO = distance between the two boxes.
+constexpr uint32_t kHi = desc_hi_sw128(1024);
+__device__ __forceinline__ constexpr uint32_t koff_k(int k) { return ((k >> 2) * AT_HALF_BYTES + (k & 3) * 32) >> 4; }
+__device__ __forceinline__ constexpr uint32_t koff_mn(int k) { return (k * 2048) >> 4; }
 
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -148,7 +159,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(AT_TILE, AT_TILE, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(AT_TILE, AT_D, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      const uint32_t q_lo = desc_lo_sw128(smem_u32(sQ), 16), k_lo = desc_lo_sw128(smem_u32(sK), 16);
+      const uint32_t v_lo = desc_lo_sw128(smem_u32(sV), AT_HALF_BYTES);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kStatusTimeoutMma);
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
@@ -161,7 +173,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < AT_D / 16; ++k) umma_f16_ss(tmem_S, kmajor_desc(aQ, k), kmajor_desc(aK, k), idesc_qk, k != 0);
+        for (int k = 0; k < AT_D / 16; ++k)
+          umma_ss_lean<0>(tmem_S, q_lo + koff_k(k), k_lo + koff_k(k), kHi, idesc_qk, k != 0);
         umma_commit(k_empty);
         umma_commit(s_full);
         ok = mbar_wait_bounded(p_full, ph, abort_flag, p.status, kStatusTimeoutMma);
@@ -169,9 +182,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         ok = mbar_wait_bounded(v_full, ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t acc0 = j != 0;
 #pragma unroll
         for (int k = 0; k < AT_TILE / 16; ++k)
-          umma_f16_ts(tmem_O, tmem_P + k * 8, mnmajor_desc(aV, k), idesc_pv, (j | k) != 0);
+          umma_ts_lean(tmem_O, tmem_P + k * 8, v_lo + koff_mn(k), kHi, idesc_pv, k == 0 ? acc0 : 1u);
         umma_commit(v_empty);
         umma_commit(o_full);
       }
@@ -185,11 +199,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     float m_ref = -INFINITY;  // reference maximum (log2 units) the stored probabilities are relative to
     float l = 0.f;
     bool ok = true;
+    PROF_DECL(5);
     for (int j = 0; j < n_kv; ++j) {
       const uint32_t ph = j & 1;
+      PROF_LAP(4);
       ok = mbar_wait_bounded(s_full, ph, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      PROF_LAP(0);
       tc_fence_after();
       const int kv0 = (j_lo + j) * AT_TILE;
       const bool on_diag = p.causal && j_lo + j == qt;
@@ -221,6 +238,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      PROF_LAP(1);
       mx *= p.scale_log2;  // the scale is positive, so it commutes with the maximum
       const bool grow = mx > m_ref + AT_RESCALE_THRESHOLD;  // also true for the first tile (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
@@ -241,6 +259,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         m_ref = m_new;
       }
       // pass 2: probabilities relative to m_ref, written as bf16 pairs over the consumed part of S
+      PROF_LAP(2);
       const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nm2 = pack_f32x2(-m_ref, -m_ref);
       uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;  // packed fp32 pairs: two adds per instruction, two chains
       tmem_ld_32x32(tmem_S + lane_addr, ra);
@@ -286,7 +305,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      PROF_LAP(3);
     }
+    PROF_STORE(0, 5, warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     if (ok) {
       ok = mbar_wait_bounded(o_full, (n_kv - 1) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
@@ -334,6 +355,12 @@ static bool make_qkv_map(CUtensorMap* map, const void* ptr, long long rows, int 
 }  // namespace ocb
 
 using namespace ocb;
+
+#ifdef OCB_ATTN_PROFILE
+extern "C" int ocb_attention_fwd_prof_read(long long* host16) {
+  return cudaMemcpyFromSymbol(host16, g_attn_fwd_prof, sizeof(long long) * 16) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // q,out: [B, Tq, H, D]; k,v: [B, Tk, Hkv, D]; bf16, D contiguous, heads contiguous (stride D), tokens `ld*` elements
 // apart and batches Tq*ld (Tk*ld) apart. lse: [B, H, Tq] fp32. Supported: D == 128, Tq == Tk, T % 128 == 0, no

@@ -263,6 +263,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       // MN-major: 64-element column chunks are one [64 x BK] TMA box apart (LBO); 8 k-rows = 1024 B (SBO).
       constexpr uint32_t a_lbo = A_MN ? 64 * BK * 2 : 16, b_lbo = B_MN ? 64 * BK * 2 : 16;
       constexpr uint32_t a_kstep = A_MN ? 2048 : 32, b_kstep = B_MN ? 2048 : 32;  // bytes per UMMA_K = 16
+      constexpr uint32_t kDescHi = desc_hi_sw128(1024);
+      const uint32_t a_lo0 = desc_lo_sw128(smem_u32(smem), a_lbo);
+      const uint32_t b_lo0 = desc_lo_sw128(smem_u32(smem) + A_STAGE_BYTES, b_lbo);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -297,15 +300,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             __syncwarp();
           }
           if (lane == 0) {
-            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-            const uint32_t sb = sa + A_STAGE_BYTES;
-            const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
-            const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
+            // descriptor low words of this stage: the stage offset and the k-step land in the start-address field
+            const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
+            umma_ss_lean<FP8 ? 1 : 0>(d_tmem, a_lo, b_lo, kDescHi, idesc, kb != 0);
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
-              if (FP8) umma_f8_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
-              else umma_f16_ss(d_tmem, da + ((k * a_kstep) >> 4), db + ((k * b_kstep) >> 4), idesc, (kb | k) != 0);
-            }
+            for (int k = 1; k < BK / 16; ++k)
+              umma_ss_lean<FP8 ? 1 : 0>(d_tmem, a_lo + ((k * a_kstep) >> 4), b_lo + ((k * b_kstep) >> 4), kDescHi, idesc, 1);
             umma_commit(&empty_bar[stage]);
           }
           if (GROUPED == GROUP_REDUCTION) __syncwarp();

@@ -1,0 +1,75 @@
+"""Cluster placement helpers and the code-corpus export (CPU only, no network)."""
+
+import gzip
+import json
+
+import numpy as np
+import pytest
+
+from olmo_core_b200.data.misc.code_fresh_export import (
+    CODE_FRESH_LANGUAGES,
+    build_documents_and_stats,
+    flatten_documents,
+    get_export_dir_name,
+    write_document_metadata,
+    write_memmap,
+    write_stats,
+)
+from olmo_core_b200.exceptions import BeakerInsufficientResourcesError
+from olmo_core_b200.launch.reorder_ranks_in_gcp import topology_order
+from olmo_core_b200.launch.select_beaker_hosts import HostMetadata, get_hostname_constraints
+
+
+def test_topology_order_groups_by_block_and_keeps_rank_zero():
+    hosts = ["/b2/s1/m1", "/b1/s1/m1", "/b2/s2/m9", "/b1/s1/m2", "/b2/s1/m0", "/b1/s2/m5"]
+    order = topology_order(hosts)
+    assert order[0] == 0
+    # rank 0's sub-block first (its own machine, then m0), then the rest of its block, then block b1 grouped by sub-block
+    assert [hosts[r] for r in order] == ["/b2/s1/m1", "/b2/s1/m0", "/b2/s2/m9", "/b1/s1/m1", "/b1/s1/m2", "/b1/s2/m5"]
+    with pytest.raises(ValueError):
+        topology_order(["/a/b/c", "/a/b/c"])
+
+
+def _cluster(sizes):
+    return {f"{blk}-{i}": HostMetadata(blk, "s", f"m{i}") for blk, n in sizes.items() for i in range(n)}
+
+
+def test_host_selection_prefers_one_block_and_keeps_units_together():
+    meta = _cluster({"A": 10, "B": 4})
+    # a block with more free hosts than needed: every task may use the whole block
+    tasks = get_hostname_constraints(meta, num_execution_units=2, num_hosts_per_task=4, num_tasks=2)
+    assert len(tasks) == 2 and all(sorted(t) == sorted(h for h in meta if h.startswith("A-")) for t in tasks)
+    # otherwise whole execution units per block: 6 free in A, 4 in B, units of 4 hosts
+    busy = {f"A-{i}" for i in range(4)}
+    tasks = get_hostname_constraints(meta, num_execution_units=2, num_hosts_per_task=8, num_tasks=1, occupied_hosts=busy)
+    assert len(tasks[0]) == 8
+    for start in (0, 4):
+        assert len({meta[h].block for h in tasks[0][start:start + 4]}) == 1
+    with pytest.raises(BeakerInsufficientResourcesError):
+        get_hostname_constraints(meta, num_execution_units=1, num_hosts_per_task=8, num_tasks=1, occupied_hosts=busy)
+
+
+class _Tok:
+    eos_token_id = 7
+
+    def encode(self, text, add_special_tokens=False):
+        return [ord(c) % 5 for c in text]
+
+
+def test_code_export_round_trip(tmp_path):
+    rows = [{"file_contents": "  abc \n"}, {"file_contents": "   "}, {"file_contents": "hello"}]
+    docs, stats = build_documents_and_stats(rows, _Tok(), language="python")
+    assert stats.num_docs == 2 and stats.num_skipped_empty == 1 and stats.total_tokens == 4 + 6
+    assert stats.max_doc_tokens_before_eos == 5 and all(d[-1] == 7 for d in docs)
+    tokens, offsets = flatten_documents(docs)
+    assert offsets == [(0, 4), (4, 10)] and tokens.dtype == np.uint32
+    write_memmap(tmp_path / "x" / "tokens.npy", tokens)
+    write_document_metadata(tmp_path / "x" / "tokens.csv.gz", offsets)
+    write_stats(tmp_path / "x" / "stats.json", stats)
+    assert np.array_equal(np.memmap(tmp_path / "x" / "tokens.npy", dtype=np.uint32, mode="r"), tokens)
+    assert gzip.open(tmp_path / "x" / "tokens.csv.gz", "rt").read() == "0,4\n4,10\n"
+    assert json.loads((tmp_path / "x" / "stats.json").read_text())["language"] == "python"
+    assert not list((tmp_path / "x").glob("*.tmp"))
+    with pytest.raises(ValueError):
+        build_documents_and_stats([{"file_contents": "x" * 20}], _Tok(), language="c", max_doc_tokens_before_eos=10)
+    assert "python" in CODE_FRESH_LANGUAGES and get_export_dir_name("allenai/dolma2-tokenizer").endswith("dolma2-tokenizer")
