@@ -69,6 +69,24 @@ __device__ __forceinline__ constexpr uint32_t koff_k(int k, uint32_t box_bytes) 
   return ((k >> 2) * box_bytes + (k & 3) * 32) >> 4;
 }
 __device__ __forceinline__ constexpr uint32_t koff_mn(int k) { return (k * 2048) >> 4; }  // MN-major k-step
+// All k-step descriptors of a tile, materialised in registers BEFORE the issuing thread waits for the tile: once the
+// wait returns, nothing but the tcgen05.mma instructions themselves stands between the tensor core and its work.
+template <int STEPS>
+__device__ __forceinline__ void descs_k(uint64_t (&d)[STEPS], uint32_t lo, uint32_t box_bytes) {
+#pragma unroll
+  for (int k = 0; k < STEPS; ++k) {
+    d[k] = pack_u32x2(lo + koff_k(k, box_bytes), kHi);
+    asm volatile("" : "+l"(d[k]));
+  }
+}
+template <int STEPS>
+__device__ __forceinline__ void descs_mn(uint64_t (&d)[STEPS], uint32_t lo) {
+#pragma unroll
+  for (int k = 0; k < STEPS; ++k) {
+    d[k] = pack_u32x2(lo + koff_mn(k), kHi);
+    asm volatile("" : "+l"(d[k]));
+  }
+}
 
 // Store 32 consecutive bf16 pairs... i.e. columns [32c, 32c+32) of row `row` (16 packed words) into a swizzled tile.
 __device__ __forceinline__ void store_tile_row_chunk(uint8_t* tile, int row, int c, const uint32_t (&w)[16]) {
@@ -236,35 +254,43 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
       constexpr uint32_t idesc_st = make_idesc_bf16(BT, SUB, 0, 0);  // [128 keys x 64 queries], both contracted over d
       constexpr uint32_t idesc_acc = make_idesc_bf16(BT, BD, 0, 1);  // A from TMEM, B contracted over its rows
       const uint32_t aQdO = smem_u32(sQdO);
-      const uint32_t k_lo = desc_lo_sw128(smem_u32(sK), 16), v_lo = desc_lo_sw128(smem_u32(sV), 16);
+      uint64_t dK_[8], dV_[8];  // K and V never move
+      descs_k(dK_, desc_lo_sw128(smem_u32(sK), 16), HALF_BYTES);
+      descs_k(dV_, desc_lo_sw128(smem_u32(sV), 16), HALF_BYTES);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      PROF_DECL(5);
       // S^T and dP^T of unit u into the region of its parity
       auto issue_sp = [&](int u) -> bool {
         const int st = u % KV_NST;
-        if (!mbar_wait_bounded(&full[st], (u / KV_NST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
-        tc_fence_after();
-        const uint32_t q_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, 16), do_lo = q_lo + (SUB_BYTES >> 4);
+        const uint32_t q_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, 16);
+        uint64_t dQ_[8], ddO_[8];
+        descs_k(dQ_, q_lo, SUB_BOX);
+        descs_k(ddO_, q_lo + (SUB_BYTES >> 4), SUB_BOX);
         const uint32_t tS = tReg + (u & 1) * 128, tP = tS + SUB;
+        PROF_LAP(3);
+        if (!mbar_wait_bounded(&full[st], (u / KV_NST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
+        PROF_LAP(4);
+        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss_lean<0>(tS, k_lo + koff_k(k, HALF_BYTES), q_lo + koff_k(k, SUB_BOX), kHi, idesc_st, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, dK_[k], dQ_[k], idesc_st, k != 0);
         umma_commit(&s_full[u & 1]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss_lean<0>(tP, v_lo + koff_k(k, HALF_BYTES), do_lo + koff_k(k, SUB_BOX), kHi, idesc_st, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tP, dV_[k], ddO_[k], idesc_st, k != 0);
         umma_commit(&dp_full[u & 1]);
         return true;
       };
       ok = ok && issue_sp(0);
       if (units > 1) ok = ok && issue_sp(1);
-      PROF_DECL(4);
       for (int u = 0; u < units && ok; ++u) {
         PROF_LAP(3);
         const int r = u & 1;
         const uint32_t ph = (u >> 1) & 1;
         const int st = u % KV_NST;
         // MN-major views of the unit's Q / dO sub-tiles (the box distance is the LBO field of the low word)
-        const uint32_t qmn_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, SUB_BOX), domn_lo = qmn_lo + (SUB_BYTES >> 4);
+        const uint32_t qmn_lo = desc_lo_sw128(aQdO + st * 2 * SUB_BYTES, SUB_BOX);
+        uint64_t dQmn[SUB / 16], ddOmn[SUB / 16];
+        descs_mn(dQmn, qmn_lo);
+        descs_mn(ddOmn, qmn_lo + (SUB_BYTES >> 4));
         const uint32_t tPT = tReg + r * 128, tdST = tPT + SUB;  // packed bf16 over the first 32 columns of S^T / dP^T
         const uint32_t acc0 = u != 0;
         ok = mbar_wait_bounded(&p_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
@@ -273,7 +299,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < SUB / 16; ++k)
-          umma_ts_lean(tdV, tPT + k * 8, domn_lo + koff_mn(k), kHi, idesc_acc, k == 0 ? acc0 : 1u);
+          umma_f16_ts(tdV, tPT + k * 8, ddOmn[k], idesc_acc, k == 0 ? acc0 : 1u);
         PROF_LAP(3);
         ok = mbar_wait_bounded(&ds_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
@@ -281,14 +307,14 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < SUB / 16; ++k)
-          umma_ts_lean(tdK, tdST + k * 8, qmn_lo + koff_mn(k), kHi, idesc_acc, k == 0 ? acc0 : 1u);
+          umma_f16_ts(tdK, tdST + k * 8, dQmn[k], idesc_acc, k == 0 ? acc0 : 1u);
         umma_commit(&empty[st]);
         PROF_LAP(3);
         if (u + 2 < units) ok = issue_sp(u + 2);  // overwrites P^T / dS^T of unit u only after the products above
         PROF_LAP(2);
       }
       if (ok) umma_commit(acc_full);
-      PROF_STORE(24, 4, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+      PROF_STORE(24, 5, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   } else {
     const int quad = warp & 3;
@@ -522,31 +548,38 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, BD, 0, 1);  // A = dS from TMEM, B = K contracted over its rows
-      const uint32_t q_lo = desc_lo_sw128(smem_u32(sQ), 16), do_lo = desc_lo_sw128(smem_u32(sdO), 16);
+      uint64_t dQ_[8], ddO_[8];  // Q and dO never move
+      descs_k(dQ_, desc_lo_sw128(smem_u32(sQ), 16), HALF_BYTES);
+      descs_k(ddO_, desc_lo_sw128(smem_u32(sdO), 16), HALF_BYTES);
       const uint32_t k_lo0 = desc_lo_sw128(smem_u32(sK), 16), v_lo0 = desc_lo_sw128(smem_u32(sV), 16);
       const uint32_t kmn_lo0 = desc_lo_sw128(smem_u32(sK), HALF_BYTES);  // MN-major view of the K stages
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, p.status, kStatusTimeoutMma);
+      PROF_DECL(6);
       // S(j) = Q K_j^T into R[j & 1]
       auto issue_s = [&](int j) -> bool {
         const int ks = j % DQ_KST;
+        uint64_t dK_[8];
+        descs_k(dK_, k_lo0 + ks * (TILE_BYTES >> 4), HALF_BYTES);
+        PROF_LAP(3);
         if (!mbar_wait_bounded(&k_full[ks], (j / DQ_KST) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
+        PROF_LAP(4);
         tc_fence_after();
-        const uint32_t k_lo = k_lo0 + ks * (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss_lean<0>(tR + (j & 1) * 128, q_lo + koff_k(k, HALF_BYTES), k_lo + koff_k(k, HALF_BYTES), kHi, idesc_kk, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tR + (j & 1) * 128, dQ_[k], dK_[k], idesc_kk, k != 0);
         umma_commit(&s_full[j & 1]);
         return true;
       };
       // dP(j) = dO V_j^T into X (the caller has made sure that X was read)
       auto issue_dp = [&](int j) -> bool {
         const int vs = j & 1;
+        uint64_t dV_[8];
+        descs_k(dV_, v_lo0 + vs * (TILE_BYTES >> 4), HALF_BYTES);
+        PROF_LAP(1);
         if (!mbar_wait_bounded(&v_full[vs], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutMma)) return false;
+        PROF_LAP(5);
         tc_fence_after();
-        const uint32_t v_lo = v_lo0 + vs * (TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss_lean<0>(tX, do_lo + koff_k(k, HALF_BYTES), v_lo + koff_k(k, HALF_BYTES), kHi, idesc_kk, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tX, ddO_[k], dV_[k], idesc_kk, k != 0);
         umma_commit(&dp_full[j & 1]);
         umma_commit(&v_empty[vs]);
         return true;
@@ -554,7 +587,6 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       ok = ok && issue_s(0);
       if (n_kv > 1) ok = ok && issue_s(1);
       ok = ok && issue_dp(0);
-      PROF_DECL(4);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int r = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -567,22 +599,22 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
           if (!ok) break;
           PROF_LAP(1);
         }
+        const int ks = j % DQ_KST;
+        uint64_t dKmn[8];
+        descs_mn(dKmn, kmn_lo0 + ks * (TILE_BYTES >> 4));
+        const uint32_t acc0 = j != 0;
         ok = mbar_wait_bounded(&ds_full[r], ph, abort_flag, p.status, kStatusTimeoutMma);
         if (!ok) break;
         PROF_LAP(2);
         tc_fence_after();
-        const int ks = j % DQ_KST;
-        const uint32_t kmn_lo = kmn_lo0 + ks * (TILE_BYTES >> 4);
-        const uint32_t acc0 = j != 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ts_lean(tdQ, tR + r * 128 + k * 8, kmn_lo + koff_mn(k), kHi, idesc_dq, k == 0 ? acc0 : 1u);
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tR + r * 128 + k * 8, dKmn[k], idesc_dq, k == 0 ? acc0 : 1u);
         umma_commit(&k_empty[ks]);
         if (j + 2 < n_kv) ok = issue_s(j + 2);  // overwrites dS(j) only after dQ(j): same thread, in order
       }
       if (ok) umma_commit(acc_full);
       PROF_LAP(3);
-      PROF_STORE(8, 4, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+      PROF_STORE(8, 6, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   } else {
     const int quad = warp & 3;

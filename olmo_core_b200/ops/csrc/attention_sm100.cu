@@ -159,8 +159,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(AT_TILE, AT_TILE, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(AT_TILE, AT_D, 0, 1);
-      const uint32_t q_lo = desc_lo_sw128(smem_u32(sQ), 16), k_lo = desc_lo_sw128(smem_u32(sK), 16);
-      const uint32_t v_lo = desc_lo_sw128(smem_u32(sV), AT_HALF_BYTES);
+      // every k-step descriptor lives in registers: Q, K and V tiles have fixed places in shared memory
+      uint64_t dQ_[8], dK_[8], dV_[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        dQ_[k] = pack_u32x2(desc_lo_sw128(smem_u32(sQ), 16) + koff_k(k), kHi);
+        dK_[k] = pack_u32x2(desc_lo_sw128(smem_u32(sK), 16) + koff_k(k), kHi);
+        dV_[k] = pack_u32x2(desc_lo_sw128(smem_u32(sV), AT_HALF_BYTES) + koff_mn(k), kHi);
+      }
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kStatusTimeoutMma);
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
@@ -174,7 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < AT_D / 16; ++k)
-          umma_ss_lean<0>(tmem_S, q_lo + koff_k(k), k_lo + koff_k(k), kHi, idesc_qk, k != 0);
+          umma_f16_ss(tmem_S, dQ_[k], dK_[k], idesc_qk, k != 0);
         umma_commit(k_empty);
         umma_commit(s_full);
         ok = mbar_wait_bounded(p_full, ph, abort_flag, p.status, kStatusTimeoutMma);
@@ -185,7 +191,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         const uint32_t acc0 = j != 0;
 #pragma unroll
         for (int k = 0; k < AT_TILE / 16; ++k)
-          umma_ts_lean(tmem_O, tmem_P + k * 8, v_lo + koff_mn(k), kHi, idesc_pv, k == 0 ? acc0 : 1u);
+          umma_f16_ts(tmem_O, tmem_P + k * 8, dV_[k], idesc_pv, k == 0 ? acc0 : 1u);
         umma_commit(v_empty);
         umma_commit(o_full);
       }
