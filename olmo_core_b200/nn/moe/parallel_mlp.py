@@ -113,6 +113,17 @@ class ParallelDroplessMLP(ParallelMLPBase):
     def parallel_forward_once(self, x, expert_weights, expert_indices, batch_size_per_expert) -> torch.Tensor:
         ep, E_local = self.ep_world_size, self.num_local_experts
         indices, bin_ids, bins = self.indices_and_bins(expert_indices, batch_size_per_expert)
+        from ...ops import moe_peer
+
+        if indices.dtype == torch.int32 and moe_peer.peer_exchange_enabled(x, self._ep_pg):
+            # permutation + transfer in one kernel over peer memory, both ways; rows arrive grouped by local expert
+            ex = moe_peer.PeerExpertExchange.get(self._ep_pg, x.shape[1], indices.numel(), x.device)
+            tables = ex.tables(batch_size_per_expert, E_local)
+            recv = moe_peer.dispatch(x, indices, self.top_k, ex, tables)
+            tables.offsets._is_offsets = True  # type: ignore[attr-defined]
+            ys = self.mlp(recv, tables.offsets)
+            back = moe_peer.combine(ys, indices.numel(), ex, tables)
+            return ops.scatter(back, indices, bin_ids, expert_weights, bins, self.top_k)
         # Tokens per (destination rank, local expert) that we send, and that every peer sends us.
         send_counts = batch_size_per_expert.to(torch.int64).view(ep, E_local)
         recv_counts = torch.empty_like(send_counts)

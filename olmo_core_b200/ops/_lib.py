@@ -52,6 +52,8 @@ _SIGS = {
     "ocb_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
     "ocb_moe_scatter": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
     "ocb_moe_rowdot": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p],
+    "ocb_moe_push_rows": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                          c_longlong, c_int, c_longlong, c_longlong, c_void_p, c_void_p],
     "ocb_rmsnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                         c_longlong, c_float, c_int, c_int, c_void_p],
     "ocb_norm_bwd_partials": [],

@@ -66,6 +66,13 @@ int ocb_moe_scatter(const void* ys, const int* dest, const float* w, void* y, in
 // dw[j] = <ys[dest[j]], dy[j / top_k]>
 int ocb_moe_rowdot(const void* ys, const int* dest, const void* dy, float* dw, int n_copies, int cols, int top_k,
                    long long lds, long long ldd, cudaStream_t stream);
+// Expert-parallel exchange over peer memory (moe_peer_sm100.cu): segment s moves rows [src_start[s], +count[s]) of src
+// (row i read from gather_idx[i] / gather_div when gather_idx is given) to rows dst_start[s]... of rank dst_rank[s]'s
+// buffer peer_ptrs[dst_rank[s]]. Rows that would land beyond dst_capacity_rows are skipped and reported in *status.
+int ocb_moe_push_rows(const void* src, const int* gather_idx, int gather_div, const int* seg_src_start,
+                      const int* seg_count, const int* seg_dst_rank, const long long* seg_dst_start, int num_segments,
+                      void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols, long long ld_src,
+                      long long ld_dst, int* status, cudaStream_t stream);
 
 // ---- normalisation / rotary / activation (elementwise.cu) -------------------------------------------
 // y = rmsnorm(x) * w  (+ resid).  x,y,resid: [rows, cols] with row strides ldx/ldy/ldr. w: [cols].
