@@ -246,8 +246,9 @@ reduce_partials_kernel(const float* __restrict__ partial, O* __restrict__ out, i
 // ----------------------------------------------------------------------------------------------------
 constexpr int kMaxPv = 2;  // up to 2*256 pair vectors = 8192 channels per row
 
-template <typename T, typename W, bool BWD>
-__global__ void __launch_bounds__(kNormThreads)
+// PV = pair vectors per thread (1 covers rows of up to 4096 channels and leaves room for 3-4 resident blocks per SM).
+template <typename T, typename W, bool BWD, int PV>
+__global__ void __launch_bounds__(kNormThreads, PV == 1 ? (BWD ? 3 : 4) : 2)
 norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const W* __restrict__ w,
                  float* __restrict__ rstd_io, T* __restrict__ out, float* __restrict__ dw_partial,
                  const float* __restrict__ sin_t, const float* __restrict__ cos_t, const int* __restrict__ pos_ids,
@@ -258,9 +259,9 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
   const int pv_per_head = half / 8;  // power of two, <= 32 (checked by the launcher)
   const int n_pv = n_heads * pv_per_head;
   const int cols = n_heads * head_dim;
-  float dwa[kMaxPv][8], dwb[kMaxPv][8];
+  float dwa[PV][8], dwb[PV][8];
 #pragma unroll
-  for (int i = 0; i < kMaxPv; ++i)
+  for (int i = 0; i < PV; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwa[i][j] = dwb[i][j] = 0.f;
 
@@ -271,10 +272,10 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
     const T* inr = in + static_cast<long long>(row) * ld_in;
     T* outr = out + static_cast<long long>(row) * ld_out;
     if (!BWD) {
-      float xa[kMaxPv][8], xb[kMaxPv][8], rstd_h[kMaxPv];
+      float xa[PV][8], xb[PV][8], rstd_h[PV];
       float ss_row = 0.f;
 #pragma unroll
-      for (int i = 0; i < kMaxPv; ++i) {
+      for (int i = 0; i < PV; ++i) {
         const int pv = threadIdx.x + i * kNormThreads;
         const bool on = pv < n_pv;
         const int h = on ? pv / pv_per_head : 0, o = on ? (pv % pv_per_head) * 8 : 0;
@@ -300,7 +301,7 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
         if (threadIdx.x == 0 && rstd_io) rstd_io[row] = rstd_row;
       }
 #pragma unroll
-      for (int i = 0; i < kMaxPv; ++i) {
+      for (int i = 0; i < PV; ++i) {
         const int pv = threadIdx.x + i * kNormThreads;
         if (pv < n_pv) {
           const int h = pv / pv_per_head, o = (pv % pv_per_head) * 8;
@@ -336,11 +337,11 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
       }
     } else {
       const T* xr = x_saved + static_cast<long long>(row) * ld_x;
-      float ga[kMaxPv][8], gb[kMaxPv][8], c_h[kMaxPv];
+      float ga[PV][8], gb[PV][8], c_h[PV];
       float dot_row = 0.f;
       const float rstd_row = norm_mode == 1 ? rstd_io[row] : 1.f;
 #pragma unroll
-      for (int i = 0; i < kMaxPv; ++i) {
+      for (int i = 0; i < PV; ++i) {
         const int pv = threadIdx.x + i * kNormThreads;
         const bool on = pv < n_pv;
         const int h = on ? pv / pv_per_head : 0, o = on ? (pv % pv_per_head) * 8 : 0;
@@ -380,7 +381,7 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
       float c_row = 0.f;
       if (norm_mode == 1) c_row = group_sum(dot_row, kNormThreads, sbuf) / static_cast<float>(cols);
 #pragma unroll
-      for (int i = 0; i < kMaxPv; ++i) {
+      for (int i = 0; i < PV; ++i) {
         const int pv = threadIdx.x + i * kNormThreads;
         if (pv < n_pv) {
           const int h = pv / pv_per_head, o = (pv % pv_per_head) * 8;
@@ -414,9 +415,11 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
   }
   if (BWD && dw_partial != nullptr && norm_mode != 0) {
     const int wcols = norm_mode == 1 ? cols : head_dim;
-    float* prow = dw_partial + static_cast<long long>(blockIdx.x) * wcols;
+    // Blocks b and b + kNormBwdBlocks share a partial row (zeroed by the launcher). A row gets at most two fp32
+    // addends in the full-row mode, and a sum of two is the same in either order, so the result stays reproducible.
+    float* prow = dw_partial + static_cast<long long>(blockIdx.x % kNormBwdBlocks) * wcols;
 #pragma unroll
-    for (int i = 0; i < kMaxPv; ++i) {
+    for (int i = 0; i < PV; ++i) {
       const int pv = threadIdx.x + i * kNormThreads;
       if (pv < n_pv) {
         const int h = pv / pv_per_head, o = (pv % pv_per_head) * 8;
@@ -424,8 +427,8 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (norm_mode == 1) {
-            prow[wofs + o + j] = dwa[i][j];
-            prow[wofs + half + o + j] = dwb[i][j];
+            atomicAdd(&prow[wofs + o + j], dwa[i][j]);
+            atomicAdd(&prow[wofs + half + o + j], dwb[i][j]);
           } else {
             atomicAdd(&prow[o + j], dwa[i][j]);
             atomicAdd(&prow[half + o + j], dwb[i][j]);
@@ -824,8 +827,10 @@ extern "C" int ocb_norm_rope_fwd(const void* x, const void* w, void* y, float* r
   if (head_dim % 16 != 0 || (half / 8) > 32 || ((half / 8) & (half / 8 - 1)) != 0) return -1;
   if (n_heads * (half / 8) > kMaxPv * kNormThreads) return -1;
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const bool one_pv = n_heads * (half / 8) <= kNormThreads;
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
-    norm_rope_kernel<T, W, false><<<grid, kNormThreads, 0, stream>>>(
+    auto kern = one_pv ? norm_rope_kernel<T, W, false, 1> : norm_rope_kernel<T, W, false, 2>;
+    kern<<<grid, kNormThreads, 0, stream>>>(
         static_cast<const T*>(x), nullptr, static_cast<const W*>(w), rstd, static_cast<T*>(y), nullptr, sin_t, cos_t,
         pos_ids, rows, n_heads, head_dim, seq_len, pos_offset, norm_mode, ldx, 0, ldy, eps);
   })
@@ -840,14 +845,19 @@ extern "C" int ocb_norm_rope_bwd(const void* dy, const void* x, const void* w, c
   const int half = head_dim / 2;
   if (head_dim % 16 != 0 || (half / 8) > 32 || ((half / 8) & (half / 8 - 1)) != 0) return -1;
   if (n_heads * (half / 8) > kMaxPv * kNormThreads) return -1;
-  const int grid = rows < kNormBwdBlocks ? rows : kNormBwdBlocks;
+  const bool one_pv = n_heads * (half / 8) <= kNormThreads;
+  // every block must be resident at once (a persistent grid that spills into a second wave doubles the run time):
+  // three blocks per SM fit with one pair vector per thread, two otherwise
+  const int max_blocks = one_pv ? kNormBwdBlocks + kNormBwdBlocks / 2 : kNormBwdBlocks;
+  const int grid = rows < max_blocks ? rows : max_blocks;
   if (dw_partial != nullptr && norm_mode != 0) {
     const int wcols = norm_mode == 1 ? n_heads * head_dim : head_dim;
     if (cudaMemsetAsync(dw_partial, 0, sizeof(float) * static_cast<size_t>(kNormBwdBlocks) * wcols, stream) != cudaSuccess)
       return -4;
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
-    norm_rope_kernel<T, W, true><<<grid, kNormThreads, 0, stream>>>(
+    auto kern = one_pv ? norm_rope_kernel<T, W, true, 1> : norm_rope_kernel<T, W, true, 2>;
+    kern<<<grid, kNormThreads, 0, stream>>>(
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), const_cast<float*>(rstd),
         static_cast<T*>(dx), dw_partial, sin_t, cos_t, pos_ids, rows, n_heads, head_dim, seq_len, pos_offset, norm_mode,
         lddy, ldx, lddx, 0.f);
