@@ -25,7 +25,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["attention", "attention_reference", "build_attention_mask", "has_flash_kernel"]
+__all__ = ["attention", "attention_reference", "build_attention_mask", "has_flash_kernel", "sharded_attention",
+           "ShardedSequenceLayout"]
 
 
 def build_attention_mask(
@@ -118,6 +119,18 @@ def has_flash_kernel() -> bool:
              c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_longlong, c_float, c_int,
              c_int, c_void_p, c_void_p],
         )
+        if hasattr(lib, "ocb_attention_fwd_sharded"):
+            _lib.register_signature(
+                "ocb_attention_fwd_sharded",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                 c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_longlong, c_float, c_int, c_void_p, c_void_p],
+            )
+            _lib.register_signature(
+                "ocb_attention_bwd_sharded",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                 c_longlong, c_longlong, c_float, c_int, c_void_p, c_void_p],
+            )
         _FLASH_BOUND = True
     return True
 
@@ -127,28 +140,36 @@ def _row_stride(t: torch.Tensor) -> int:
     return t.stride(1)
 
 
-def _visibility_bounds(B: int, T: int, window: int, cu_seqlens: Optional[torch.Tensor], device) -> Optional[torch.Tensor]:
+def _visibility_bounds(B: int, T: int, window: int, cu_seqlens: Optional[torch.Tensor], device, *, Tk: Optional[int] = None,
+                       q_pos: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """
-    int32 ``[2, B * T]`` for the flash kernels: per query the lowest visible key, per key the highest query that sees it
-    (indices inside the sequence). One pair of arrays expresses sliding windows, document boundaries and both together;
-    ``None`` when neither applies. Documents never span two rows of the batch (``cu_seqlens`` counts over ``B * T``).
+    int32 ``[B * Tq + B * Tk]`` for the flash kernels: per query the lowest visible key, then per key the position of the
+    last query that sees it (key indices / query positions inside the ``Tk``-long sequence). One pair of arrays expresses
+    sliding windows, document boundaries and both together; ``None`` when neither applies. Documents never span two rows
+    of the batch (``cu_seqlens`` counts over ``B * T``) and need ``Tq == Tk``. ``q_pos`` (int64 ``[Tq]``) gives the
+    queries' positions when they are not the last ``Tq`` of the sequence (a shard of a context-parallel group).
     """
     if not window and cu_seqlens is None:
         return None
-    flat = torch.arange(B * T, device=device, dtype=torch.int64)
-    t = flat % T
-    lo = torch.zeros_like(t)
-    hi = torch.full_like(t, T - 1)
+    Tk = T if Tk is None else Tk
+    if q_pos is None:
+        q_pos = torch.arange(Tk - T, Tk, device=device, dtype=torch.int64)
+    tq = q_pos.to(device=device, dtype=torch.int64).repeat(B)
+    tk = torch.arange(Tk, device=device, dtype=torch.int64).repeat(B)
+    lo = torch.zeros_like(tq)
+    hi = torch.full_like(tk, Tk - 1)
     if cu_seqlens is not None:
+        assert T == Tk, "document boundaries need queries and keys of one length"
+        flat = torch.arange(B * T, device=device, dtype=torch.int64)
         cu = cu_seqlens.to(device=device, dtype=torch.int64)
         doc = torch.bucketize(flat, cu[1:], right=True).clamp(max=cu.numel() - 2)
-        base = flat - t
+        base = flat - tk
         lo = torch.maximum(lo, cu[doc] - base)
         hi = torch.minimum(hi, cu[doc + 1] - 1 - base)
     if window:
-        lo = torch.maximum(lo, t - (window - 1))
-        hi = torch.minimum(hi, t + (window - 1))
-    return torch.stack([lo, hi]).to(torch.int32).contiguous()
+        lo = torch.maximum(lo, tq - (window - 1))
+        hi = torch.minimum(hi, tk + (window - 1))
+    return torch.cat([lo, hi]).to(torch.int32).contiguous()
 
 
 class _FlashAttention(torch.autograd.Function):
@@ -160,7 +181,7 @@ class _FlashAttention(torch.autograd.Function):
                    for t in (q, k, v))
         out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
-        cu = _visibility_bounds(B, Tq, window, cu_seqlens, q.device)
+        cu = _visibility_bounds(B, Tq, window, cu_seqlens, q.device, Tk=Tk)
         rc = _lib.lib().ocb_attention_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _lib.ptr(cu),
             B, Tq, Tk, H, Hkv, D, _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(out), scale,
@@ -190,6 +211,104 @@ class _FlashAttention(torch.autograd.Function):
         )
         _lib.check(rc, "ocb_attention_bwd")
         return dq, dk, dv, None, None, None, None
+
+
+class ShardedSequenceLayout:
+    """
+    Where the tiles of a sequence that is sharded over a context-parallel group live, for the sharded attention kernels
+    (``csrc/attn_seq_map.cuh``): the local queries are one or two chunks of ``q_chunk_tiles`` 128-row tiles that start
+    at global tiles ``q_tile0``; the keys, in global order, are chunks of ``kv_chunk_tiles`` tiles, chunk ``c`` held by
+    rank ``kv_chunks[c][0]`` from tile ``kv_chunks[c][1]`` of its local buffer.
+    """
+
+    def __init__(self, q_chunk_tiles: int, q_tile0: Tuple[int, int], kv_chunk_tiles: int, kv_chunks):
+        self.q_chunk_tiles = int(q_chunk_tiles)
+        self.q_tile0 = (int(q_tile0[0]), int(q_tile0[1]))
+        self.kv_chunk_tiles = int(kv_chunk_tiles)
+        self.kv_chunks = [(int(a), int(b)) for a, b in kv_chunks]
+        flat = [self.q_chunk_tiles, *self.q_tile0, self.kv_chunk_tiles, len(self.kv_chunks)]
+        for a, b in self.kv_chunks:
+            flat += [a, b]
+        self.c_array = (c_int * len(flat))(*flat)
+
+    @classmethod
+    def for_rank(cls, local_len: int, rank: int, cp: int, zig_zag: bool) -> "ShardedSequenceLayout":
+        """Layout of rank ``rank`` holding ``local_len`` tokens: contiguous shards, or the mirrored zig-zag chunks."""
+        if not zig_zag:
+            tiles = local_len // 128
+            return cls(tiles, (rank * tiles, 0), tiles, [(r, 0) for r in range(cp)])
+        tiles = local_len // 256
+        chunks = [(c, 0) if c < cp else (2 * cp - 1 - c, tiles) for c in range(2 * cp)]
+        return cls(tiles, (rank * tiles, (2 * cp - 1 - rank) * tiles), tiles, chunks)
+
+    def query_positions(self, device) -> torch.Tensor:
+        """Global position of every local query row (int64)."""
+        n = self.q_chunk_tiles * 128
+        parts = [torch.arange(self.q_tile0[0] * 128, self.q_tile0[0] * 128 + n, device=device)]
+        if self.q_tile0[1]:
+            parts.append(torch.arange(self.q_tile0[1] * 128, self.q_tile0[1] * 128 + n, device=device))
+        return torch.cat(parts)
+
+
+class _ShardedFlashAttention(torch.autograd.Function):
+    """Attention of local queries over keys / values that stay on their owners (see :func:`sharded_attention`)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, exchange, layout, scale: float, window: int):  # type: ignore[override]
+        B, Tq, H, D = q.shape
+        T_local, Hkv = k.shape[1], k.shape[2]
+        Tk = layout.kv_chunk_tiles * 128 * len(layout.kv_chunks)
+        q = q.contiguous()
+        k_ptrs, v_ptrs = exchange.publish(k, v)
+        out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
+        bounds = _visibility_bounds(B, Tq, window, None, q.device, Tk=Tk, q_pos=layout.query_positions(q.device)[:Tq])
+        ld_kv = Hkv * D
+        rc = _lib.lib().ocb_attention_fwd_sharded(
+            q.data_ptr(), k_ptrs, v_ptrs, exchange.world_size, T_local, layout.c_array, out.data_ptr(), lse.data_ptr(),
+            _lib.ptr(bounds), B, Tq, Tk, H, Hkv, D, _row_stride(q), ld_kv, ld_kv, _row_stride(out), scale, 1,
+            _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
+        )
+        _lib.check(rc, "ocb_attention_fwd_sharded")
+        ctx.save_for_backward(q, k, v, out, lse, bounds if bounds is not None else torch.empty(0, device=q.device))
+        ctx.cfg = (exchange, layout, scale, bounds is not None, Tk)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):  # type: ignore[override]
+        q, k, v, out, lse, bounds = ctx.saved_tensors
+        exchange, layout, scale, has_bounds, Tk = ctx.cfg
+        B, Tq, H, D = q.shape
+        T_local, Hkv = k.shape[1], k.shape[2]
+        dout = dout.contiguous()
+        k_ptrs, v_ptrs = exchange.publish(k, v)  # the peers' K / V of this layer are needed once more
+        dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
+        dk_all = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
+        dv_all = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
+        delta = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
+        ld_kv = Hkv * D
+        rc = _lib.lib().ocb_attention_bwd_sharded(
+            q.data_ptr(), k_ptrs, v_ptrs, exchange.world_size, T_local, layout.c_array, out.data_ptr(), dout.data_ptr(),
+            lse.data_ptr(), dq.data_ptr(), dk_all.data_ptr(), dv_all.data_ptr(), bounds.data_ptr() if has_bounds else None,
+            delta.data_ptr(), B, Tq, Tk, H, Hkv, D, _row_stride(q), ld_kv, ld_kv, _row_stride(out), scale, 1,
+            _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
+        )
+        _lib.check(rc, "ocb_attention_bwd_sharded")
+        dk, dv = exchange.reduce_to_owners(dk_all, dv_all)
+        return dq, dk, dv, None, None, None, None
+
+
+def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, exchange, layout: ShardedSequenceLayout,
+                      scale: Optional[float] = None, window_size: Optional[int] = None) -> torch.Tensor:
+    """
+    Causal attention of this rank's queries ``q [B, T_local, H, 128]`` over the whole sequence of a context-parallel
+    group. ``k, v [B, T_local, Hkv, 128]`` are this rank's keys / values; nothing is gathered: ``exchange``
+    (:class:`olmo_core_b200.parallel.context.KVExchange`) places them in peer-mapped memory and the kernels read every
+    key / value tile from the GPU that owns it. Sliding windows are supported; key / value gradients are summed onto
+    their owners by ``exchange.reduce_to_owners``.
+    """
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    return _ShardedFlashAttention.apply(q, k, v, exchange, layout, scale, int(window_size or 0))
 
 
 def _sdpa_path(q, k, v, *, causal, window_size, cu_seqlens, cu_seqlens_k, scale, dropout_p):
@@ -237,8 +356,9 @@ def attention(
         and dropout_p == 0.0
         and cu_seqlens_k is None
         and (causal or (cu_seqlens is None and not window_size))
-        and q.shape[1] == k.shape[1]
+        and (q.shape[1] == k.shape[1] or (causal and cu_seqlens is None and q.shape[1] < k.shape[1]))
         and q.shape[1] % 128 == 0
+        and k.shape[1] % 128 == 0
         and has_flash_kernel()
     )
     if use_flash:

@@ -18,6 +18,7 @@
 // Recomputing S and dP in both kernels costs two extra tile products (7 instead of 5) and buys independence.
 
 #include "common.cuh"
+#include "attn_seq_map.cuh"
 #include "ocb_api.h"
 #include "tmap.h"
 
@@ -50,11 +51,13 @@ struct AttnBwdParams {
   __nv_bfloat16* dk;   // [B, T, Hkv, D]
   __nv_bfloat16* dv;
   long long ld_dq, ld_dk, ld_dv;
-  int T, H, Hkv;
+  AttnSeqMap m;  // where query tiles sit in the global sequence and where key / value tiles are fetched from
+  int H, Hkv;
   float scale, scale_log2;
   int causal;
-  // Optional visibility bounds (sliding windows and document boundaries), as indices inside the sequence, int32 [B * T],
-  // both non-decreasing: query i sees key j iff row_lo[i] <= j <= i; col_hi[j] is the last query that sees key j.
+  // Optional visibility bounds (sliding windows and document boundaries), both non-decreasing: row_lo int32 [B * Tq] is
+  // the lowest key index a query sees, col_hi int32 [B * Tk] the position of the last query that sees a key (key indices
+  // and query positions in the global sequence): the query at position i sees key j iff row_lo[i] <= j <= i.
   const int* row_lo;
   const int* col_hi;
   int* status;
@@ -182,14 +185,32 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
   const int jt = blockIdx.x;  // K/V tile
   const int hk = blockIdx.y, b = blockIdx.z;
   const int group = p.H / p.Hkv;
-  // query tiles [i_first, n_q) can see this key tile: up to the tile of the last query that sees its last key
-  const int n_q = p.col_hi ? p.col_hi[b * p.T + jt * BT + BT - 1] / BT + 1 : p.T / BT;
-  const int i_first = p.causal ? jt : 0;
+  // LOCAL query tiles [i_first, n_q) can see this key tile: from the first one at or after the key tile's place in the
+  // global sequence up to the tile of the last query that sees its last key (local tiles are in global order)
+  const int kv_g0 = b * p.m.Tk + jt * BT;  // the tile's first key in the global [B * Tk] key space (bounds, outputs)
+  int i_first = 0, n_q = p.m.Tq / BT;
+  if (p.causal)
+    while (i_first < n_q && attn_q_gtile(p.m, i_first) < jt) ++i_first;
+  if (p.col_hi) {
+    const int hi_last = p.col_hi[kv_g0 + BT - 1];
+    while (n_q > i_first && attn_q_gtile(p.m, n_q - 1) * BT > hi_last) --n_q;
+  }
   const int per_head = (n_q - i_first) * 2;  // units per query head
   const int units = per_head * group;
-  const int kv_row0 = b * p.T + jt * BT;
+  int kv_src;
+  const int kv_row0 = attn_kv_row0(p.m, b, jt, kv_src);  // the tile's first row in its source buffer
   // last query that sees the FIRST key of the tile: units that reach beyond it need the element-wise mask
-  const int hi_first = p.col_hi ? p.col_hi[kv_row0] : p.T - 1;
+  const int hi_first = p.col_hi ? p.col_hi[kv_g0] : p.m.Tk - 1;
+  if (units == 0) {
+    // no local query sees this tile (possible only when the queries are a shard of the sequence): its gradients are zero
+    for (int i = threadIdx.x; i < BT * (BD / 8); i += BWD_THREADS) {
+      const long long token = static_cast<long long>(kv_g0) + i / (BD / 8);
+      const int c = (i % (BD / 8)) * 8;
+      *reinterpret_cast<uint4*>(p.dk + token * p.ld_dk + hk * BD + c) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(p.dv + token * p.ld_dv + hk * BD + c) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -220,21 +241,23 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
   if (warp == 0) {
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
-      tma_load_2d(sK, &tma_k, kv_full, hk * BD, kv_row0);
-      tma_load_2d(sK + HALF_BYTES, &tma_k, kv_full, hk * BD + 64, kv_row0);
-      tma_load_2d(sV, &tma_v, kv_full, hk * BD, kv_row0);
-      tma_load_2d(sV + HALF_BYTES, &tma_v, kv_full, hk * BD + 64, kv_row0);
+      const CUtensorMap* mk = attn_k_map(p.m, &tma_k, kv_src);
+      const CUtensorMap* mv = attn_v_map(p.m, &tma_v, kv_src);
+      tma_load_2d(sK, mk, kv_full, hk * BD, kv_row0);
+      tma_load_2d(sK + HALF_BYTES, mk, kv_full, hk * BD + 64, kv_row0);
+      tma_load_2d(sV, mv, kv_full, hk * BD, kv_row0);
+      tma_load_2d(sV + HALF_BYTES, mv, kv_full, hk * BD + 64, kv_row0);
       bool ok = true;
       for (int u = 0; u < units && ok; ++u) {
         const int h = hk * group + u / per_head;
         const int rem = u % per_head;
-        const int q0 = (i_first + (rem >> 1)) * BT + (rem & 1) * SUB;  // position of the unit's first query
-        const int q_row0 = b * p.T + q0;
+        const int q0 = (i_first + (rem >> 1)) * BT + (rem & 1) * SUB;  // local row of the unit's first query
+        const int q_row0 = b * p.m.Tq + q0;
         const int st = u % KV_NST;
         uint8_t* q_dst = sQdO + st * 2 * SUB_BYTES;
         uint8_t* do_dst = q_dst + SUB_BYTES;
         float* stat_dst = sStat + st * 2 * SUB;
-        const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + q0;
+        const long long stat = (static_cast<long long>(b) * p.H + h) * p.m.Tq + q0;
         ok = mbar_wait_bounded(&empty[st], ((u / KV_NST) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(&full[st], 2 * SUB_BYTES + STAT_BYTES);
@@ -323,7 +346,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int kv_pos = jt * BT + row;  // position of this thread's key in the sequence
     const int vis_lo = p.causal ? kv_pos : 0;                               // first and
-    const int vis_hi = p.col_hi ? p.col_hi[b * p.T + kv_pos] : p.T - 1;    // last query that sees the key
+    const int vis_hi = p.col_hi ? p.col_hi[b * p.m.Tk + kv_pos] : p.m.Tk - 1;  // last query that sees the key
     const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nlog2 = pack_f32x2(-LOG2E, -LOG2E);
     const uint64_t scl2 = pack_f32x2(p.scale, p.scale), nscl2 = pack_f32x2(-p.scale, -p.scale);
     const uint32_t tS = tReg + grp * 128 + lane_addr, tP = tS + SUB;
@@ -333,7 +356,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
       PROF_LAP(4);
       const uint32_t ph = (u >> 1) & 1;
       const int rem = u % per_head;
-      const int q0 = (i_first + (rem >> 1)) * BT + (rem & 1) * SUB;
+      const int q0 = attn_q_gtile(p.m, i_first + (rem >> 1)) * BT + (rem & 1) * SUB;  // global position
       const int st = u % KV_NST;
       const float* st_lse = sStat + st * 2 * SUB;
       const float* st_dl = st_lse + SUB;
@@ -425,7 +448,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q /* 64-row boxes */, c
     }
     if (ok) {
       tc_fence_after();
-      const long long token = static_cast<long long>(kv_row0) + row;  // accumulator row = key row
+      const long long token = static_cast<long long>(kv_g0) + row;  // accumulator row = key row
       store_acc_row(p.dv + token * p.ld_dv + hk * BD, tdV + lane_addr, grp * 2);
       store_acc_row(p.dk + token * p.ld_dk + hk * BD, tdK + lane_addr, grp * 2);
     }
@@ -482,11 +505,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
   const int qt = gridDim.x - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
-  const int q_row0 = b * p.T + qt * BT;
+  const int gt = attn_q_gtile(p.m, qt);  // the tile's place in the global sequence
+  const int q_row0 = b * p.m.Tq + qt * BT;
   const int lo_first = p.row_lo ? p.row_lo[q_row0] : 0;
   const int lo_last = p.row_lo ? p.row_lo[q_row0 + BT - 1] : 0;
   const int j_lo = lo_first / BT;  // first key tile any row of this query tile can see; `j` counts tiles from there
-  const int n_kv = (p.causal ? qt + 1 : p.T / BT) - j_lo;
+  const int n_kv = (p.causal ? gt + 1 : p.m.Tk / BT) - j_lo;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -525,20 +549,23 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       tma_load_2d(sdO + HALF_BYTES, &tma_do, qdo_full, h * BD + 64, q_row0);
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int kv_row0 = b * p.T + (j_lo + j) * BT;
+        int src;
+        const int kv_row0 = attn_kv_row0(p.m, b, j_lo + j, src);
+        const CUtensorMap* mk = attn_k_map(p.m, &tma_k, src);
+        const CUtensorMap* mv = attn_v_map(p.m, &tma_v, src);
         const int ks = j % DQ_KST, vs = j & 1;
         uint8_t* dK_ = sK + ks * TILE_BYTES;
         uint8_t* dV_ = sV + vs * TILE_BYTES;
         ok = mbar_wait_bounded(&k_empty[ks], ((j / DQ_KST) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(&k_full[ks], TILE_BYTES);
-        tma_load_2d(dK_, &tma_k, &k_full[ks], hk * BD, kv_row0);
-        tma_load_2d(dK_ + HALF_BYTES, &tma_k, &k_full[ks], hk * BD + 64, kv_row0);
+        tma_load_2d(dK_, mk, &k_full[ks], hk * BD, kv_row0);
+        tma_load_2d(dK_ + HALF_BYTES, mk, &k_full[ks], hk * BD + 64, kv_row0);
         ok = mbar_wait_bounded(&v_empty[vs], ((j >> 1) & 1) ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(&v_full[vs], TILE_BYTES);
-        tma_load_2d(dV_, &tma_v, &v_full[vs], hk * BD, kv_row0);
-        tma_load_2d(dV_ + HALF_BYTES, &tma_v, &v_full[vs], hk * BD + 64, kv_row0);
+        tma_load_2d(dV_, mv, &v_full[vs], hk * BD, kv_row0);
+        tma_load_2d(dV_ + HALF_BYTES, mv, &v_full[vs], hk * BD + 64, kv_row0);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -621,7 +648,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
     const int grp = (warp - 2) >> 2;  // 0: even tiles (and dQ columns [0,64) at the end), 1: odd tiles ([64,128))
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const long long stat = (static_cast<long long>(b) * p.H + h) * p.T + qt * BT + row;
+    const long long stat = (static_cast<long long>(b) * p.H + h) * p.m.Tq + qt * BT + row;
     const float lse2 = p.lse[stat] * LOG2E;
     const float dl = p.delta[stat];
     const int my_lo = p.row_lo ? p.row_lo[q_row0 + row] : 0;
@@ -634,7 +661,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant_
       PROF_LAP(4);
       const uint32_t ph = (j >> 1) & 1;
       const int kv0 = (j_lo + j) * BT;
-      const bool on_diag = p.causal && j_lo + j == qt;
+      const bool on_diag = p.causal && j_lo + j == gt;
       const bool diag = on_diag || kv0 < lo_last;
       const int hi_col = on_diag ? row : BT - 1;
       const int lo_col = my_lo - kv0;
@@ -753,26 +780,19 @@ extern "C" int ocb_attention_prof_read(long long* host32) {
 }
 #endif
 
-// Gradients of ocb_attention_fwd. dout/out/q/dq: [B, T, H, D]; k, v, dk, dv: [B, T, Hkv, D]; lse: [B, H, T] from the
-// forward pass; delta: [B, H, T] fp32 scratch (written here). dq/dk/dv are written densely (row stride heads * D).
-extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                                 const float* lse, void* dq, void* dk, void* dv, const int* bounds, float* delta, int B,
-                                 int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
-                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
-  if (B <= 0 || Tq <= 0) return 0;
-  (void)window;  // folded into `bounds` (int32 [2, B * T]: row_lo then col_hi, see ocb_attention_fwd) by the caller
-  if (D != BD || Tq != Tk || (Tq % BT) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0 ||
-      delta == nullptr)
-    return -5;
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+// Shared by the two entry points below: `mk` / `mv` are the tensor maps of the caller's own K / V (ignored by the
+// kernels when m.kv_maps is set). dk / dv cover ALL Tk keys of the global sequence, densely.
+static int attn_bwd_launch(const void* q, const CUtensorMap& mk, const CUtensorMap& mv, const void* out, const void* dout,
+                           const float* lse, void* dq, void* dk, void* dv, const int* bounds, float* delta, int B, int H,
+                           int Hkv, long long ldq, long long ldo, float scale, int causal, const AttnSeqMap& m, int* status,
+                           cudaStream_t stream) {
+  const int Tq = m.Tq, Tk = m.Tk;
   const long long rows = static_cast<long long>(B) * Tq;
   const long long ld_do = static_cast<long long>(H) * BD;  // dout is dense
-  CUtensorMap mq, mk, mv, mdo, mq_sub, mdo_sub;  // *_sub: 64-row boxes for the dK/dV kernel's query sub-tiles
+  CUtensorMap mq, mdo, mq_sub, mdo_sub;  // *_sub: 64-row boxes for the dK/dV kernel's query sub-tiles
   if (!make_map(&mq_sub, q, rows, H, ldq, SUB)) return -1005;
   if (!make_map(&mdo_sub, dout, rows, H, ld_do, SUB)) return -1006;
   if (!make_map(&mq, q, rows, H, ldq)) return -1001;
-  if (!make_map(&mk, k, rows, Hkv, ldk)) return -1002;
-  if (!make_map(&mv, v, rows, Hkv, ldv)) return -1003;
   if (!make_map(&mdo, dout, rows, H, ld_do)) return -1004;
   static bool configured = false;
   if (!configured) {
@@ -795,7 +815,7 @@ extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, co
   p.dv = static_cast<__nv_bfloat16*>(dv);
   p.ld_dq = static_cast<long long>(H) * BD;
   p.ld_dk = p.ld_dv = static_cast<long long>(Hkv) * BD;
-  p.T = Tq;
+  p.m = m;
   p.H = H;
   p.Hkv = Hkv;
   p.scale = scale;
@@ -804,7 +824,51 @@ extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, co
   p.row_lo = bounds;
   p.col_hi = bounds ? bounds + static_cast<long long>(B) * Tq : nullptr;
   p.status = status;
-  attn_dkdv_kernel<<<dim3(Tq / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq_sub, mk, mv, mdo_sub, p);
+  attn_dkdv_kernel<<<dim3(Tk / BT, Hkv, B), BWD_THREADS, DKDV_SMEM, stream>>>(mq_sub, mk, mv, mdo_sub, p);
   attn_dq_kernel<<<dim3(Tq / BT, H, B), BWD_THREADS, DQ_SMEM, stream>>>(mq, mk, mv, mdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Gradients of ocb_attention_fwd. dout/out/q/dq: [B, Tq, H, D]; k, v, dk, dv: [B, Tk, Hkv, D]; lse: [B, H, Tq] from the
+// forward pass; delta: [B, H, Tq] fp32 scratch (written here). dq/dk/dv are written densely (row stride heads * D).
+// `bounds` as for ocb_attention_fwd (int32: [B * Tq] row_lo, then [B * Tk] col_hi).
+extern "C" int ocb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                 const float* lse, void* dq, void* dk, void* dv, const int* bounds, float* delta, int B,
+                                 int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
+                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  (void)window;
+  if (D != BD || Tq > Tk || (Tq % BT) != 0 || (Tk % BT) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 ||
+      (H % Hkv) != 0 || delta == nullptr)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  CUtensorMap mk, mv;
+  if (!make_map(&mk, k, static_cast<long long>(B) * Tk, Hkv, ldk)) return -1002;
+  if (!make_map(&mv, v, static_cast<long long>(B) * Tk, Hkv, ldv)) return -1003;
+  return attn_bwd_launch(q, mk, mv, out, dout, lse, dq, dk, dv, bounds, delta, B, H, Hkv, ldq, ldo, scale, causal,
+                         attn_plain_map(Tq, Tk), status, stream);
+}
+
+// Gradients of ocb_attention_fwd_sharded (same description of the key / value sources). dk / dv: [B, Tk, Hkv, D] in GLOBAL
+// key order on this GPU: the local queries' contribution to every key of the sequence (zero where no local query sees
+// a key); the caller sums them over the ranks onto the owners.
+extern "C" int ocb_attention_bwd_sharded(const void* q, const void* const* k_srcs, const void* const* v_srcs, int n_src,
+                                         int kv_rows_src, const int* layout, const void* out, const void* dout,
+                                         const float* lse, void* dq, void* dk, void* dv, const int* bounds, float* delta,
+                                         int B, int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk,
+                                         long long ldv, long long ldo, float scale, int causal, int* status,
+                                         cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  if (D != BD || (Tq % BT) != 0 || (Tk % BT) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0 ||
+      delta == nullptr)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  AttnSeqMap m;
+  const int rc = attn_sharded_map(&m, B, Tq, Tk, Hkv, k_srcs, v_srcs, n_src, kv_rows_src, ldk, ldv, layout, stream);
+  if (rc != 0) return rc;
+  CUtensorMap mk, mv;
+  if (!make_map(&mk, k_srcs[0], static_cast<long long>(B) * kv_rows_src, Hkv, ldk)) return -1002;
+  if (!make_map(&mv, v_srcs[0], static_cast<long long>(B) * kv_rows_src, Hkv, ldv)) return -1003;
+  return attn_bwd_launch(q, mk, mv, out, dout, lse, dq, dk, dv, bounds, delta, B, H, Hkv, ldq, ldo, scale, causal, m, status,
+                         stream);
 }

@@ -19,6 +19,9 @@
 // Every wait is bounded (see common.cuh); a kernel that gives up sets the status word and frees its TMEM.
 
 #include "common.cuh"
+
+#include <mutex>
+#include "attn_seq_map.cuh"
 #include "ocb_api.h"
 #include "tmap.h"
 
@@ -49,11 +52,12 @@ struct AttnFwdParams {
   __nv_bfloat16* out;
   float* lse;
   long long ld_out;  // elements between consecutive tokens of `out`
-  int T, H, Hkv;
+  AttnSeqMap m;  // where query tiles sit in the global sequence and where key / value tiles are fetched from
+  int H, Hkv;
   float scale_log2;  // softmax scale * log2(e)
   int causal;
-  // Optional per-query lower bound of the visible keys (index inside the sequence, int32 [B * T], non-decreasing along
-  // the sequence): key j is visible to query i iff row_lo[i] <= j (and j <= i when causal). It encodes sliding windows
+  // Optional per-query lower bound of the visible keys (global key index, int32 [B * Tq], non-decreasing along
+  // the sequence): key j is visible to query i iff row_lo[i] <= j (and j <= position of i when causal). It encodes sliding windows
   // and document boundaries at once. nullptr = no lower bound.
   const int* row_lo;
   int* status;
@@ -92,13 +96,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int qt = gridDim.x - 1 - blockIdx.x;  // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
-  const int q_row0 = b * p.T + qt * AT_TILE;
+  const int gt = attn_q_gtile(p.m, qt);  // the tile's place in the global sequence
+  const int q_row0 = b * p.m.Tq + qt * AT_TILE;
   // The bounds are non-decreasing, so the tile's first row has the smallest one (where the key loop starts) and its last
   // row the largest (tiles that start below it need the element-wise mask). `j` below counts tiles from j_lo.
   const int lo_first = p.row_lo ? p.row_lo[q_row0] : 0;
   const int lo_last = p.row_lo ? p.row_lo[q_row0 + AT_TILE - 1] : 0;
   const int j_lo = lo_first / AT_TILE;
-  const int n_kv = (p.causal ? qt + 1 : p.T / AT_TILE) - j_lo;
+  const int n_kv = (p.causal ? gt + 1 : p.m.Tk / AT_TILE) - j_lo;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -138,17 +143,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
-        const int kv_row0 = b * p.T + (j_lo + j) * AT_TILE;
+        int src;
+        const int kv_row0 = attn_kv_row0(p.m, b, j_lo + j, src);
+        const CUtensorMap* mk = attn_k_map(p.m, &tma_k, src);
+        const CUtensorMap* mv = attn_v_map(p.m, &tma_v, src);
         ok = mbar_wait_bounded(k_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(k_full, AT_TILE_BYTES);
-        tma_load_2d(sK, &tma_k, k_full, hk * AT_D, kv_row0);
-        tma_load_2d(sK + AT_HALF_BYTES, &tma_k, k_full, hk * AT_D + 64, kv_row0);
+        tma_load_2d(sK, mk, k_full, hk * AT_D, kv_row0);
+        tma_load_2d(sK + AT_HALF_BYTES, mk, k_full, hk * AT_D + 64, kv_row0);
         ok = mbar_wait_bounded(v_empty, ph ^ 1u, abort_flag, p.status, kStatusTimeoutProducer);
         if (!ok) break;
         mbar_arrive_expect_tx(v_full, AT_TILE_BYTES);
-        tma_load_2d(sV, &tma_v, v_full, hk * AT_D, kv_row0);
-        tma_load_2d(sV + AT_HALF_BYTES, &tma_v, v_full, hk * AT_D + 64, kv_row0);
+        tma_load_2d(sV, mv, v_full, hk * AT_D, kv_row0);
+        tma_load_2d(sV + AT_HALF_BYTES, mv, v_full, hk * AT_D + 64, kv_row0);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before shared memory goes away
@@ -215,7 +223,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       PROF_LAP(0);
       tc_fence_after();
       const int kv0 = (j_lo + j) * AT_TILE;
-      const bool on_diag = p.causal && j_lo + j == qt;
+      const bool on_diag = p.causal && j_lo + j == gt;
       const bool diag = on_diag || kv0 < lo_last;  // the tile needs the element-wise mask
       const int hi_col = on_diag ? row : AT_TILE - 1;  // visible columns of this row: [lo_col, hi_col]
       const int lo_col = my_lo - kv0;
@@ -339,7 +347,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       // natural-log log-sum-exp of the scaled scores
-      p.lse[(static_cast<long long>(b) * p.H + h) * p.T + qt * AT_TILE + row] = m_ref * 0.6931471805599453f + logf(l);
+      p.lse[(static_cast<long long>(b) * p.H + h) * p.m.Tq + qt * AT_TILE + row] = m_ref * 0.6931471805599453f + logf(l);
     }
   }
 
@@ -368,23 +376,63 @@ extern "C" int ocb_attention_fwd_prof_read(long long* host16) {
 }
 #endif
 
-// q,out: [B, Tq, H, D]; k,v: [B, Tk, Hkv, D]; bf16, D contiguous, heads contiguous (stride D), tokens `ld*` elements
-// apart and batches Tq*ld (Tk*ld) apart. lse: [B, H, Tq] fp32. Supported: D == 128, Tq == Tk, T % 128 == 0, no
-// other cases return -5 so that the caller can take another path. Sliding windows and document boundaries are passed
-// as `bounds`: int32 [2, B * T] = per-query lowest visible key, then per-key highest query that sees it (both as indices
-// inside the sequence, non-decreasing); they need causal != 0. `window` is unused (folded into the bounds by the caller).
-extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* bounds,
-                                 int B, int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
-                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
-  if (B <= 0 || Tq <= 0) return 0;
-  (void)window;
-  if (D != AT_D || Tq != Tk || (Tq % AT_TILE) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0)
-    return -5;
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
-  CUtensorMap mq, mk, mv;
-  if (!make_qkv_map(&mq, q, static_cast<long long>(B) * Tq, H, ldq)) return -1001;
-  if (!make_qkv_map(&mk, k, static_cast<long long>(B) * Tk, Hkv, ldk)) return -1002;
-  if (!make_qkv_map(&mv, v, static_cast<long long>(B) * Tk, Hkv, ldv)) return -1003;
+namespace ocb {
+
+// Device copies of per-source tensor maps: a ring of slots, one per call. A slot is rewritten only after 64 further
+// calls, and the copy into it is ordered on the caller's stream behind the kernels that read it.
+CUtensorMap* attn_map_ring_slot(const CUtensorMap* host_maps, int count, cudaStream_t stream) {
+  constexpr int kSlots = 64, kPerSlot = 2 * ATTN_MAX_SOURCES;
+  static CUtensorMap* ring = nullptr;
+  static int next = 0;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> g(mu);
+  if (count > kPerSlot) return nullptr;
+  if (ring == nullptr && cudaMalloc(&ring, sizeof(CUtensorMap) * kPerSlot * kSlots) != cudaSuccess) return nullptr;
+  CUtensorMap* slot = ring + static_cast<size_t>(next) * kPerSlot;
+  next = (next + 1) % kSlots;
+  if (cudaMemcpyAsync(slot, host_maps, sizeof(CUtensorMap) * count, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return nullptr;
+  return slot;
+}
+
+// Fills `m` from the flat description the C entry points take and builds the per-source K / V maps. Returns 0, or a
+// negative code. `layout` = {q_chunk_tiles, q_tile0[0], q_tile0[1], kv_chunk_tiles, n_chunks, then per chunk: source,
+// first tile}.
+int attn_sharded_map(AttnSeqMap* m, int B, int Tq, int Tk, int Hkv, const void* const* k_srcs, const void* const* v_srcs,
+                     int n_src, int kv_rows_src, long long ldk, long long ldv, const int* layout, cudaStream_t stream) {
+  if (n_src <= 0 || n_src > ATTN_MAX_SOURCES || layout == nullptr) return -1;
+  const int n_chunks = layout[4];
+  if (n_chunks <= 0 || n_chunks > ATTN_MAX_KV_CHUNKS || layout[0] <= 0 || layout[3] <= 0) return -1;
+  if (layout[3] * n_chunks * AT_TILE != Tk || (kv_rows_src % AT_TILE) != 0) return -1;
+  const int q_tiles = Tq / AT_TILE;
+  if (q_tiles != layout[0] && q_tiles != 2 * layout[0]) return -1;
+  *m = attn_plain_map(Tq, Tk);
+  m->q_chunk_tiles = layout[0];
+  m->q_tile0[0] = layout[1];
+  m->q_tile0[1] = layout[2];
+  m->kv_chunk_tiles = layout[3];
+  m->kv_rows_src = kv_rows_src;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int src = layout[5 + 2 * c], t0 = layout[6 + 2 * c];
+    if (src < 0 || src >= n_src || t0 < 0 || (t0 + layout[3]) * AT_TILE > kv_rows_src) return -1;
+    m->kv_src[c] = static_cast<unsigned char>(src);
+    m->kv_tile0[c] = static_cast<short>(t0);
+  }
+  CUtensorMap maps[2 * ATTN_MAX_SOURCES];
+  for (int r = 0; r < n_src; ++r) {
+    if (!make_qkv_map(&maps[r], k_srcs[r], static_cast<long long>(B) * kv_rows_src, Hkv, ldk)) return -1002;
+    if (!make_qkv_map(&maps[n_src + r], v_srcs[r], static_cast<long long>(B) * kv_rows_src, Hkv, ldv)) return -1003;
+  }
+  m->n_src = n_src;
+  m->kv_maps = attn_map_ring_slot(maps, 2 * n_src, stream);
+  return m->kv_maps ? 0 : -3;
+}
+
+static int attn_fwd_launch(const void* q, const CUtensorMap& mk, const CUtensorMap& mv, void* out, float* lse,
+                           const int* bounds, int B, int H, int Hkv, long long ldq, long long ldo, float scale, int causal,
+                           const AttnSeqMap& m, int* status, cudaStream_t stream) {
+  CUtensorMap mq;
+  if (!make_qkv_map(&mq, q, static_cast<long long>(B) * m.Tq, H, ldq)) return -1001;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM) != cudaSuccess) return -3;
@@ -394,14 +442,60 @@ extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, vo
   p.out = static_cast<__nv_bfloat16*>(out);
   p.lse = lse;
   p.ld_out = ldo;
-  p.T = Tq;
+  p.m = m;
   p.H = H;
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.row_lo = bounds;
   p.status = status;
-  dim3 grid(Tq / AT_TILE, H, B);
+  dim3 grid(m.Tq / AT_TILE, H, B);
   attn_fwd_kernel<<<grid, AT_THREADS, AT_FWD_SMEM, stream>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ocb
+
+// q,out: [B, Tq, H, D]; k,v: [B, Tk, Hkv, D]; bf16, D contiguous, heads contiguous (stride D), tokens `ld*` elements
+// apart and batches Tq*ld (Tk*ld) apart. lse: [B, H, Tq] fp32. Supported: D == 128, Tq and Tk multiples of 128 with
+// Tq <= Tk (the queries are the LAST Tq positions of the sequence: causal masking is aligned at the end); other cases
+// return -5 so that the caller can take another path. Sliding windows and document boundaries are passed as `bounds`:
+// int32 [B * Tq] per-query lowest visible key, then [B * Tk] per-key position of the last query that sees it (key indices
+// and query positions inside the Tk-long sequence, non-decreasing); they need causal != 0. `window` is unused (folded
+// into the bounds by the caller).
+extern "C" int ocb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* bounds,
+                                 int B, int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
+                                 long long ldo, float scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  (void)window;
+  if (D != AT_D || Tq > Tk || (Tq % AT_TILE) != 0 || (Tk % AT_TILE) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 ||
+      (H % Hkv) != 0)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  CUtensorMap mk, mv;
+  if (!make_qkv_map(&mk, k, static_cast<long long>(B) * Tk, Hkv, ldk)) return -1002;
+  if (!make_qkv_map(&mv, v, static_cast<long long>(B) * Tk, Hkv, ldv)) return -1003;
+  return attn_fwd_launch(q, mk, mv, out, lse, bounds, B, H, Hkv, ldq, ldo, scale, causal, attn_plain_map(Tq, Tk), status,
+                         stream);
+}
+
+// Context-parallel forward: the local queries attend to a sequence whose keys and values are sharded over `n_src`
+// buffers (k_srcs[r] / v_srcs[r]: [B, kv_rows_src, Hkv, D] on rank r, as mapped into this GPU's address space; the
+// caller's own buffer included). Key / value tiles are read from their owners' memory inside the kernel; the caller
+// orders the kernel behind the peers' writes with its own barrier. `layout` is described at attn_sharded_map.
+extern "C" int ocb_attention_fwd_sharded(const void* q, const void* const* k_srcs, const void* const* v_srcs, int n_src,
+                                         int kv_rows_src, const int* layout, void* out, float* lse, const int* bounds, int B,
+                                         int Tq, int Tk, int H, int Hkv, int D, long long ldq, long long ldk, long long ldv,
+                                         long long ldo, float scale, int causal, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tq <= 0) return 0;
+  if (D != AT_D || (Tq % AT_TILE) != 0 || (Tk % AT_TILE) != 0 || (bounds != nullptr && !causal) || Hkv <= 0 || (H % Hkv) != 0)
+    return -5;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -1;
+  AttnSeqMap m;
+  const int rc = attn_sharded_map(&m, B, Tq, Tk, Hkv, k_srcs, v_srcs, n_src, kv_rows_src, ldk, ldv, layout, stream);
+  if (rc != 0) return rc;
+  CUtensorMap mk, mv;  // unused by the kernel when m.kv_maps is set, but must be valid maps
+  if (!make_qkv_map(&mk, k_srcs[0], static_cast<long long>(B) * kv_rows_src, Hkv, ldk)) return -1002;
+  if (!make_qkv_map(&mv, v_srcs[0], static_cast<long long>(B) * kv_rows_src, Hkv, ldv)) return -1003;
+  return attn_fwd_launch(q, mk, mv, out, lse, bounds, B, H, Hkv, ldq, ldo, scale, causal, m, status, stream);
 }

@@ -9,6 +9,11 @@ the group (autograd-aware: the backward pass reduce-scatters their gradients) an
 query chunk, being a contiguous range of global positions ``[a, b)``, then runs ordinary causal attention against keys
 ``[0, b)`` aligned at the end. Compared with a ring exchange this trades ``cp``-times more resident K/V (small next to
 180 GB: 2 x T x Hkv x D x 2 bytes per layer) for a single collective per layer and one attention call per chunk.
+
+On B200s with peer-mapped memory the gather disappears: :class:`KVExchange` keeps each rank's keys / values in a
+symmetric buffer and the flash-attention kernels fetch every key / value tile from the GPU that owns it with TMA loads
+over NVLink (``ops.attention.sharded_attention``), forward and backward; sliding windows skip the tiles (and the
+NVLink traffic) they cannot see. Only the key / value gradients still travel through a reduce-scatter.
 """
 
 from __future__ import annotations
@@ -18,7 +23,7 @@ from typing import List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["ring_attention", "local_position_ranges"]
+__all__ = ["ring_attention", "local_position_ranges", "KVExchange"]
 
 
 class _AllGatherSeq(torch.autograd.Function):
@@ -67,6 +72,91 @@ def _to_global_order(gathered: torch.Tensor, cp: int, zig_zag: bool) -> torch.Te
     return torch.cat(chunks, dim=1)  # type: ignore[arg-type]
 
 
+class KVExchange:
+    """
+    Peer-mapped home of one rank's keys and values for the sharded attention kernels. ``publish`` copies the local
+    ``k, v [B, T_local, Hkv, D]`` into this rank's symmetric buffer and returns, after a stream-ordered barrier, the C
+    arrays of every rank's K and V addresses as mapped on this GPU. Two slots alternate, so one barrier per call is
+    enough: a slot is rewritten only after a later barrier has shown that every peer's kernels that read it are done.
+    One instance serves all layers of a model (the backward pass publishes a layer's K / V again instead of keeping
+    ``n_layers`` peer-visible copies).
+    """
+
+    _instances: dict = {}
+
+    def __init__(self, group, zig_zag: bool):
+        self.group = group
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.zig_zag = zig_zag
+        self._buf = None
+        self._numel = 0
+        self._calls = 0
+        self._arrays: dict = {}
+
+    @classmethod
+    def for_group(cls, group, zig_zag: bool) -> "KVExchange":
+        key = (id(group), zig_zag)
+        if key not in cls._instances:
+            cls._instances[key] = cls(group, zig_zag)
+        return cls._instances[key]
+
+    def publish(self, k: torch.Tensor, v: torch.Tensor):
+        import ctypes
+
+        from .symmetric import SymmetricBuffer
+
+        n = k.numel()
+        assert v.numel() == n and k.dtype == v.dtype
+        if self._buf is None or n > self._numel or self._buf.tensor.dtype != k.dtype:
+            self._buf = SymmetricBuffer(4 * n, k.dtype, k.device, self.group)  # [slot][K | V]
+            self._numel = n
+            self._arrays = {}
+        slot = self._calls & 1
+        self._calls += 1
+        base = slot * 2 * self._numel
+        self._buf.tensor[base: base + n].view_as(k).copy_(k)
+        self._buf.tensor[base + self._numel: base + self._numel + n].view_as(v).copy_(v)
+        self._buf.barrier()
+        if slot not in self._arrays:
+            es = k.element_size()
+            ptrs = [int(p) for p in self._buf.handle.buffer_ptrs]
+            self._arrays[slot] = (
+                (ctypes.c_void_p * self.world_size)(*[p + base * es for p in ptrs]),
+                (ctypes.c_void_p * self.world_size)(*[p + (base + self._numel) * es for p in ptrs]),
+            )
+        return self._arrays[slot]
+
+    def reduce_to_owners(self, dk_all: torch.Tensor, dv_all: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``[B, T, Hkv, D]`` partial gradients in global key order -> this rank's ``[B, T_local, Hkv, D]`` sums."""
+        cp = self.world_size
+        B, T = dk_all.shape[0], dk_all.shape[1]
+        tail = tuple(dk_all.shape[2:])
+        g = torch.stack([dk_all, dv_all])  # [2, B, T, ...]
+        if self.zig_zag:
+            order = [c for r in range(cp) for c in (r, 2 * cp - 1 - r)]
+            g = g.view(2, B, 2 * cp, T // (2 * cp), *tail)[:, :, order]
+        g = g.reshape(2, B, cp, T // cp, *tail).permute(2, 0, 1, 3, *range(4, 4 + len(tail))).contiguous()
+        out = torch.empty_like(g[0])
+        dist.reduce_scatter_tensor(out.view(-1), g.view(-1), op=dist.ReduceOp.SUM, group=self.group)
+        return out[0], out[1]
+
+
+def _sharded_kernels_usable(q: torch.Tensor, k: torch.Tensor, group, zig_zag: bool) -> bool:
+    import os
+
+    from ..ops.attention import has_flash_kernel
+    from .symmetric import symmetric_memory_enabled
+
+    if os.environ.get("OLMO_CORE_B200_CP_IN_KERNEL", "1") == "0":
+        return False
+    return (
+        q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
+        and q.shape[1] == k.shape[1] and q.shape[1] % (256 if zig_zag else 128) == 0
+        and symmetric_memory_enabled(q.device, group) and has_flash_kernel()
+    )
+
+
 def ring_attention(backend, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, group, style,
                    cu_doc_lens: Optional[torch.Tensor] = None, cu_doc_lens_q: Optional[torch.Tensor] = None,
                    cu_doc_lens_k: Optional[torch.Tensor] = None, local_k_slice: Optional[slice] = None) -> torch.Tensor:
@@ -82,6 +172,13 @@ def ring_attention(backend, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *
     cp, rank = dist.get_world_size(group), dist.get_rank(group)
     zig_zag = style.load_balancer == RingAttentionLoadBalancerType.zig_zag
     T_local = q.shape[1]
+    if _sharded_kernels_usable(q, k, group, zig_zag):
+        from ..ops.attention import ShardedSequenceLayout, sharded_attention
+
+        layout = ShardedSequenceLayout.for_rank(T_local, rank, cp, zig_zag)
+        return sharded_attention(q, k.contiguous(), v.contiguous(), exchange=KVExchange.for_group(group, zig_zag),
+                                 layout=layout, scale=getattr(backend, "scale", None),
+                                 window_size=getattr(backend, "window", None))
     k_all = _to_global_order(_AllGatherSeq.apply(k, group), cp, zig_zag)
     v_all = _to_global_order(_AllGatherSeq.apply(v, group), cp, zig_zag)
     outs = []

@@ -117,3 +117,100 @@ def test_flash_attention_windows_and_documents(B, T, H, Hkv, window, docs):
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
     for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
         torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 2e-2)
+
+
+@pytest.mark.parametrize("B,Tq,Tk,H,Hkv,window", [
+    (1, 128, 512, 2, 1, None),     # one query tile at the end of a longer key sequence
+    (2, 256, 1024, 4, 2, None),
+    (1, 512, 1536, 2, 2, 300),     # with a sliding window
+])
+def test_flash_attention_queries_at_the_end_of_longer_keys(B, Tq, Tk, H, Hkv, window):
+    """Fewer queries than keys (causal masking aligned at the end) stays on the flash kernels."""
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(Tq + Tk)
+    dev = torch.device("cuda")
+    q = torch.randn(B, Tq, H, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, Tk, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, Tk, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    dout = torch.randn(B, Tq, H, 128, device=dev, dtype=torch.bfloat16)
+    launches = _lib.launch_count
+    out = attention(q, k, v, causal=True, window_size=window)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_device_status(dev)
+    assert _lib.launch_count == launches + 2
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qf, kf, vf, causal=True, window_size=window)
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 2e-2)
+
+
+class _OneGpuExchange:
+    """All shards of a context-parallel group on one GPU: the kernels only see addresses, so this exercises the sharded
+    tile lookup (sources, chunks, zig-zag order) without peers."""
+
+    def __init__(self, ks, vs):
+        import ctypes
+
+        self.world_size = len(ks)
+        self.k_ptrs = (ctypes.c_void_p * len(ks))(*[t.data_ptr() for t in ks])
+        self.v_ptrs = (ctypes.c_void_p * len(vs))(*[t.data_ptr() for t in vs])
+        self.partials = None
+
+    def publish(self, k, v):
+        return self.k_ptrs, self.v_ptrs
+
+    def reduce_to_owners(self, dk_all, dv_all):
+        self.partials = (dk_all, dv_all)
+        n = dk_all.shape[1] // self.world_size
+        return torch.zeros_like(dk_all[:, :n]), torch.zeros_like(dv_all[:, :n])
+
+
+@pytest.mark.parametrize("cp,zig_zag,T,window", [
+    (2, False, 512, None),
+    (4, True, 2048, None),
+    (4, False, 2048, 300),
+    (2, True, 1024, 200),
+])
+def test_sharded_attention_reads_tiles_from_their_owners(cp, zig_zag, T, window):
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.attention import ShardedSequenceLayout, attention_reference, sharded_attention
+    from olmo_core_b200.parallel.context import local_position_ranges
+
+    torch.manual_seed(T + cp)
+    dev = torch.device("cuda")
+    B, H, Hkv = 2, 4, 2
+    q = torch.randn(B, T, H, 128, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, T, Hkv, 128, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, T, Hkv, 128, device=dev, dtype=torch.bfloat16)
+    dout = torch.randn(B, T, H, 128, device=dev, dtype=torch.bfloat16)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qf, kf, vf, causal=True, window_size=window)
+    ref.backward(dout.float())
+
+    T_local = T // cp
+    rows = [torch.cat([torch.arange(a, b, device=dev) for a, b in local_position_ranges(T_local, r, cp, zig_zag)])
+            for r in range(cp)]
+    ks = [k[:, idx].contiguous() for idx in rows]
+    vs = [v[:, idx].contiguous() for idx in rows]
+    dk_sum = torch.zeros_like(kf)
+    dv_sum = torch.zeros_like(vf)
+    for r in range(cp):
+        ex = _OneGpuExchange(ks, vs)
+        layout = ShardedSequenceLayout.for_rank(T_local, r, cp, zig_zag)
+        ql = q[:, rows[r]].contiguous().requires_grad_(True)
+        out = sharded_attention(ql, ks[r], vs[r], exchange=ex, layout=layout, window_size=window)
+        out.backward(dout[:, rows[r]].contiguous())
+        torch.cuda.synchronize()
+        _lib.check_device_status(dev)
+        torch.testing.assert_close(out.float(), ref[:, rows[r]], rtol=2e-2, atol=2e-2)
+        want = qf.grad[:, rows[r]]
+        torch.testing.assert_close(ql.grad.float(), want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 2e-2)
+        dk_sum += ex.partials[0].float()
+        dv_sum += ex.partials[1].float()
+    for got, want in ((dk_sum, kf.grad), (dv_sum, vf.grad)):
+        torch.testing.assert_close(got, want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 3e-2)
