@@ -241,6 +241,13 @@ class ShardedSequenceLayout:
         chunks = [(c, 0) if c < cp else (2 * cp - 1 - c, tiles) for c in range(2 * cp)]
         return cls(tiles, (rank * tiles, (2 * cp - 1 - rank) * tiles), tiles, chunks)
 
+    def gathered(self) -> "ShardedSequenceLayout":
+        """The same queries over keys that sit, in sequence order, in ONE buffer."""
+        if getattr(self, "_gathered", None) is None:
+            self._gathered = ShardedSequenceLayout(self.q_chunk_tiles, self.q_tile0, self.kv_chunk_tiles * len(self.kv_chunks),
+                                                   [(0, 0)])
+        return self._gathered
+
     def query_positions(self, device) -> torch.Tensor:
         """Global position of every local query row (int64)."""
         n = self.q_chunk_tiles * 128
@@ -259,36 +266,37 @@ class _ShardedFlashAttention(torch.autograd.Function):
         T_local, Hkv = k.shape[1], k.shape[2]
         Tk = layout.kv_chunk_tiles * 128 * len(layout.kv_chunks)
         q = q.contiguous()
-        k_ptrs, v_ptrs = exchange.publish(k, v)
+        k_ptrs, v_ptrs, n_src, rows_src, kv_layout = exchange.publish(k, v, layout, window or None)
         out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
         bounds = _visibility_bounds(B, Tq, window, None, q.device, Tk=Tk, q_pos=layout.query_positions(q.device)[:Tq])
         ld_kv = Hkv * D
         rc = _lib.lib().ocb_attention_fwd_sharded(
-            q.data_ptr(), k_ptrs, v_ptrs, exchange.world_size, T_local, layout.c_array, out.data_ptr(), lse.data_ptr(),
+            q.data_ptr(), k_ptrs, v_ptrs, n_src, rows_src, kv_layout, out.data_ptr(), lse.data_ptr(),
             _lib.ptr(bounds), B, Tq, Tk, H, Hkv, D, _row_stride(q), ld_kv, ld_kv, _row_stride(out), scale, 1,
             _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
         )
         _lib.check(rc, "ocb_attention_fwd_sharded")
         ctx.save_for_backward(q, k, v, out, lse, bounds if bounds is not None else torch.empty(0, device=q.device))
-        ctx.cfg = (exchange, layout, scale, bounds is not None, Tk)
+        ctx.cfg = (exchange, layout, scale, bounds is not None, Tk, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         q, k, v, out, lse, bounds = ctx.saved_tensors
-        exchange, layout, scale, has_bounds, Tk = ctx.cfg
+        exchange, layout, scale, has_bounds, Tk, window = ctx.cfg
         B, Tq, H, D = q.shape
         T_local, Hkv = k.shape[1], k.shape[2]
         dout = dout.contiguous()
-        k_ptrs, v_ptrs = exchange.publish(k, v)  # the peers' K / V of this layer are needed once more
+        # the peers' K / V of this layer are needed once more
+        k_ptrs, v_ptrs, n_src, rows_src, kv_layout = exchange.publish(k, v, layout, window or None)
         dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         dk_all = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
         dv_all = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
         delta = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
         ld_kv = Hkv * D
         rc = _lib.lib().ocb_attention_bwd_sharded(
-            q.data_ptr(), k_ptrs, v_ptrs, exchange.world_size, T_local, layout.c_array, out.data_ptr(), dout.data_ptr(),
+            q.data_ptr(), k_ptrs, v_ptrs, n_src, rows_src, kv_layout, out.data_ptr(), dout.data_ptr(),
             lse.data_ptr(), dq.data_ptr(), dk_all.data_ptr(), dv_all.data_ptr(), bounds.data_ptr() if has_bounds else None,
             delta.data_ptr(), B, Tq, Tk, H, Hkv, D, _row_stride(q), ld_kv, ld_kv, _row_stride(out), scale, 1,
             _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
@@ -302,9 +310,10 @@ def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, exch
                       scale: Optional[float] = None, window_size: Optional[int] = None) -> torch.Tensor:
     """
     Causal attention of this rank's queries ``q [B, T_local, H, 128]`` over the whole sequence of a context-parallel
-    group. ``k, v [B, T_local, Hkv, 128]`` are this rank's keys / values; nothing is gathered: ``exchange``
-    (:class:`olmo_core_b200.parallel.context.KVExchange`) places them in peer-mapped memory and the kernels read every
-    key / value tile from the GPU that owns it. Sliding windows are supported; key / value gradients are summed onto
+    group. ``k, v [B, T_local, Hkv, 128]`` are this rank's keys / values. ``exchange``
+    (:class:`olmo_core_b200.parallel.context.KVExchange`) moves them through peer-mapped memory -- pushed once into every
+    rank's sequence-ordered buffer, or left with their owner and read tile by tile by the kernels -- and tells the
+    kernels where each key / value tile is. Sliding windows are supported; key / value gradients are summed onto
     their owners by ``exchange.reduce_to_owners``.
     """
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])

@@ -74,58 +74,130 @@ def _to_global_order(gathered: torch.Tensor, cp: int, zig_zag: bool) -> torch.Te
 
 class KVExchange:
     """
-    Peer-mapped home of one rank's keys and values for the sharded attention kernels. ``publish`` copies the local
-    ``k, v [B, T_local, Hkv, D]`` into this rank's symmetric buffer and returns, after a stream-ordered barrier, the C
-    arrays of every rank's K and V addresses as mapped on this GPU. Two slots alternate, so one barrier per call is
-    enough: a slot is rewritten only after a later barrier has shown that every peer's kernels that read it are done.
-    One instance serves all layers of a model (the backward pass publishes a layer's K / V again instead of keeping
-    ``n_layers`` peer-visible copies).
+    Peer-mapped home of a context-parallel group's keys and values for the sharded attention kernels. Two modes:
+
+    * ``push`` (default): ``publish`` launches one kernel per tensor that stores this rank's ``k, v [B, T_local, Hkv, D]``
+      chunks straight into EVERY rank's sequence-ordered buffer ``[B, T, Hkv, D]`` over NVLink (ranks that cannot see a
+      chunk -- later in the causal order, or beyond a sliding window -- are skipped, so a windowed layer only moves its
+      halo). Every tile crosses NVLink once; after the barrier the attention kernels read local memory.
+    * ``direct`` (``OLMO_CORE_B200_CP_KV=direct``): only a local copy is made and the attention kernels fetch every key /
+      value tile from its owner with TMA loads over NVLink. No gathered copy exists, but a tile is re-read by every
+      query tile that needs it (remote reads are not cached on the reading GPU), which costs more than it saves unless
+      few query tiles share a key tile.
+
+    Either way ``publish`` ends with a stream-ordered barrier and returns what the kernels need: the C arrays of K and V
+    base addresses, the number of sources, the rows per batch entry in a source, and the tile layout. Two slots
+    alternate, so one barrier per call is enough: a slot is rewritten only after a later barrier has shown that every
+    peer's kernels that read it are done. One instance serves all layers of a model (the backward pass publishes a
+    layer's K / V again instead of keeping ``n_layers`` peer-visible copies).
     """
 
     _instances: dict = {}
 
-    def __init__(self, group, zig_zag: bool):
+    def __init__(self, group, zig_zag: bool, mode: Optional[str] = None):
+        import os
+
         self.group = group
         self.world_size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.zig_zag = zig_zag
+        self.mode = mode or os.environ.get("OLMO_CORE_B200_CP_KV", "push")
+        assert self.mode in ("push", "direct")
         self._buf = None
         self._numel = 0
         self._calls = 0
         self._arrays: dict = {}
+        self._tables: dict = {}
 
     @classmethod
     def for_group(cls, group, zig_zag: bool) -> "KVExchange":
-        key = (id(group), zig_zag)
+        import os
+
+        key = (id(group), zig_zag, os.environ.get("OLMO_CORE_B200_CP_KV", "push"))
         if key not in cls._instances:
-            cls._instances[key] = cls(group, zig_zag)
+            cls._instances[key] = cls(group, zig_zag, key[2])
         return cls._instances[key]
 
-    def publish(self, k: torch.Tensor, v: torch.Tensor):
+    def _slot_arrays(self, slot: int, per_tensor: int, es: int):
         import ctypes
 
-        from .symmetric import SymmetricBuffer
-
-        n = k.numel()
-        assert v.numel() == n and k.dtype == v.dtype
-        if self._buf is None or n > self._numel or self._buf.tensor.dtype != k.dtype:
-            self._buf = SymmetricBuffer(4 * n, k.dtype, k.device, self.group)  # [slot][K | V]
-            self._numel = n
-            self._arrays = {}
-        slot = self._calls & 1
-        self._calls += 1
-        base = slot * 2 * self._numel
-        self._buf.tensor[base: base + n].view_as(k).copy_(k)
-        self._buf.tensor[base + self._numel: base + self._numel + n].view_as(v).copy_(v)
-        self._buf.barrier()
         if slot not in self._arrays:
-            es = k.element_size()
+            base = slot * 2 * per_tensor
             ptrs = [int(p) for p in self._buf.handle.buffer_ptrs]
             self._arrays[slot] = (
                 (ctypes.c_void_p * self.world_size)(*[p + base * es for p in ptrs]),
-                (ctypes.c_void_p * self.world_size)(*[p + (base + self._numel) * es for p in ptrs]),
+                (ctypes.c_void_p * self.world_size)(*[p + (base + per_tensor) * es for p in ptrs]),
             )
         return self._arrays[slot]
+
+    def _push_table(self, B: int, T_local: int, window: Optional[int], device):
+        """Segments (source row, rows, destination rank, destination row) of this rank's chunks for every rank that sees them."""
+        key = (B, T_local, window)
+        if key not in self._tables:
+            cp, T = self.world_size, T_local * self.world_size
+            mine = local_position_ranges(T_local, self.rank, cp, self.zig_zag)
+            rows = []
+            piece = 1024  # rows per segment: the kernel gives every segment a fixed number of blocks
+            for d in range(cp):
+                theirs = local_position_ranges(T_local, d, cp, self.zig_zag)
+                off = 0
+                for a, b in mine:
+                    # keys [a, b) are visible to queries [qa, qb) where they precede qb and, under a window, reach into
+                    # [qa - (window - 1), ...): only that part (from its 128-row tile boundary on) is sent
+                    lo, hi = b, a
+                    for qa, qb in theirs:
+                        first = max(a, ((qa - (window - 1)) // 128) * 128) if window else a
+                        last = min(b, qb)
+                        if first < last:
+                            lo, hi = min(lo, first), max(hi, last)
+                    for start in range(lo, hi, piece):
+                        n = min(piece, hi - start)
+                        rows += [(bi * T_local + off + start - a, n, d, bi * T + start) for bi in range(B)]
+                    off += b - a
+            cols = list(zip(*rows))
+            self._tables[key] = (
+                torch.tensor(cols[0], dtype=torch.int32, device=device), torch.tensor(cols[1], dtype=torch.int32, device=device),
+                torch.tensor(cols[2], dtype=torch.int32, device=device), torch.tensor(cols[3], dtype=torch.int64, device=device),
+            )
+        return self._tables[key]
+
+    def publish(self, k: torch.Tensor, v: torch.Tensor, layout, window: Optional[int] = None):
+        import ctypes
+
+        from ..ops import _lib
+        from .symmetric import SymmetricBuffer
+
+        n = k.numel()
+        assert v.numel() == n and k.dtype == v.dtype and k.is_contiguous() and v.is_contiguous()
+        per_tensor = n * self.world_size if self.mode == "push" else n
+        if self._buf is None or per_tensor > self._numel or self._buf.tensor.dtype != k.dtype:
+            self._buf = SymmetricBuffer(4 * per_tensor, k.dtype, k.device, self.group)  # [slot][K | V]
+            self._numel = per_tensor
+            self._arrays = {}
+        slot = self._calls & 1
+        self._calls += 1
+        k_ptrs, v_ptrs = self._slot_arrays(slot, self._numel, k.element_size())
+        B, T_local = k.shape[0], k.shape[1]
+        if self.mode == "direct":
+            base = slot * 2 * self._numel
+            self._buf.tensor[base: base + n].view_as(k).copy_(k)
+            self._buf.tensor[base + self._numel: base + self._numel + n].view_as(v).copy_(v)
+            self._buf.barrier()
+            return k_ptrs, v_ptrs, self.world_size, T_local, layout.c_array
+        src_start, count, dst_rank, dst_start = self._push_table(B, T_local, window, k.device)
+        cols = k.shape[2] * k.shape[3]
+        status = _lib.status_buffer(k.device)
+        for t, ptrs in ((k, k_ptrs), (v, v_ptrs)):
+            rc = _lib.lib().ocb_moe_push_rows(
+                t.data_ptr(), None, 1, src_start.data_ptr(), count.data_ptr(), dst_rank.data_ptr(), dst_start.data_ptr(),
+                src_start.numel(), ctypes.cast(ptrs, ctypes.c_void_p), self.world_size, B * T_local * self.world_size, cols,
+                cols, cols, status.data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "ocb_moe_push_rows")
+        self._buf.barrier()
+        r = self.rank
+        own_k = (ctypes.c_void_p * 1)(k_ptrs[r])
+        own_v = (ctypes.c_void_p * 1)(v_ptrs[r])
+        return own_k, own_v, 1, T_local * self.world_size, layout.gathered().c_array
 
     def reduce_to_owners(self, dk_all: torch.Tensor, dv_all: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """``[B, T, Hkv, D]`` partial gradients in global key order -> this rank's ``[B, T_local, Hkv, D]`` sums."""

@@ -161,8 +161,8 @@ class _OneGpuExchange:
         self.v_ptrs = (ctypes.c_void_p * len(vs))(*[t.data_ptr() for t in vs])
         self.partials = None
 
-    def publish(self, k, v):
-        return self.k_ptrs, self.v_ptrs
+    def publish(self, k, v, layout, window=None):
+        return self.k_ptrs, self.v_ptrs, self.world_size, k.shape[1], layout.c_array
 
     def reduce_to_owners(self, dk_all, dv_all):
         self.partials = (dk_all, dv_all)

@@ -131,3 +131,57 @@ def _tp_fused_worker():
 @requires_multi_gpu
 def test_tensor_parallel_fused_collective_gemms():
     run_distributed_test(_tp_fused_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
+
+
+def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
+    """Context-parallel attention with K / V exchanged over peer memory (pushed once, or read tile by tile from the
+    owning GPU inside the attention kernels), against attention over the whole sequence."""
+    import torch.distributed as dist
+
+    os.environ["OLMO_CORE_B200_CP_KV"] = mode
+
+    from olmo_core_b200.nn.attention.ring import RingAttentionLoadBalancerType
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.attention import attention, attention_reference
+    from olmo_core_b200.parallel import context
+
+    rank, cp = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    B, T, H, Hkv = 2, 2048, 4, 2
+    gen = torch.Generator().manual_seed(11)
+    q, k, v, dout = (torch.randn(B, T, h, 128, generator=gen).to(dev, torch.bfloat16) for h in (H, Hkv, Hkv, H))
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qf, kf, vf, causal=True, window_size=window)
+    ref.backward(dout.float())
+
+    class Style:
+        load_balancer = RingAttentionLoadBalancerType.zig_zag if zig_zag else RingAttentionLoadBalancerType.llama3
+
+    class Backend:
+        scale = None
+
+        def _local(self, q_, k_, v_, causal=True):
+            return attention(q_, k_, v_, causal=causal, window_size=window)
+
+    Backend.window = window
+    rows = torch.cat([torch.arange(a, b, device=dev) for a, b in context.local_position_ranges(T // cp, rank, cp, zig_zag)])
+    for _ in range(3):  # several calls: the two slots of the exchange buffer are reused
+        ql, kl, vl = (t[:, rows].contiguous().requires_grad_(True) for t in (q, k, v))
+        assert context._sharded_kernels_usable(ql, kl, dist.group.WORLD, zig_zag)
+        out = context.ring_attention(Backend(), ql, kl, vl, group=dist.group.WORLD, style=Style())
+        out.backward(dout[:, rows].contiguous())
+        torch.cuda.synchronize()
+        _lib.check_device_status(dev)
+        torch.testing.assert_close(out.float(), ref[:, rows], rtol=2e-2, atol=2e-2)
+        for got, want in ((ql.grad, qf.grad), (kl.grad, kf.grad), (vl.grad, vf.grad)):
+            want = want[:, rows]
+            torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2 * float(want.abs().max()) / 2 + 3e-2)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+@pytest.mark.parametrize("zig_zag,window,mode", [
+    (False, None, "push"), (True, None, "push"), (False, 300, "push"), (True, None, "direct"), (False, 300, "direct"),
+])
+def test_context_parallel_attention_over_peer_memory(zig_zag, window, mode):
+    run_distributed_test(_cp_in_kernel_worker, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(zig_zag, window, mode))
