@@ -5,7 +5,8 @@ Context-parallel configuration and the Ulysses sequence<->head exchanges
 ``cp2hp`` turns a sequence-sharded tensor ``[B, T/CP, H, D]`` into a head-sharded one ``[B, T, H/CP, D]``
 so that ordinary attention can run over the full sequence; ``hp2cp`` is the inverse. On one NVSwitch box
 every pair of GPUs has a direct full-bandwidth path, so the exchange is a single all-to-all whose
-pack/unpack permutes are done once on each side.
+pack/unpack permutes are done once on each side -- or, with peer-mapped memory (``olmo_core_b200.parallel.ulysses``),
+one kernel that stores every head group / sequence shard straight into its final place on the receiving GPU.
 """
 
 from __future__ import annotations
@@ -49,6 +50,10 @@ def all_to_all_single_cp2hp(x: torch.Tensor, group: Optional[dist.ProcessGroup] 
     B, t, H, D = x.shape
     if H % cp != 0:
         raise ValueError(f"number of heads ({H}) must be divisible by the context-parallel degree ({cp})")
+    from ...parallel import ulysses
+
+    if ulysses.peer_exchange_usable(x, group):
+        return ulysses.cp2hp(x, group)
     # [B, t, cp, H/cp, D] -> [cp, B, t, H/cp, D]: slice r goes to rank r
     send = x.view(B, t, cp, H // cp, D).permute(2, 0, 1, 3, 4).contiguous()
     recv = all_to_all_single(group, send.view(cp * B * t, H // cp, D))
@@ -65,6 +70,10 @@ def all_to_all_single_hp2cp(x: torch.Tensor, group: Optional[dist.ProcessGroup] 
     if T % cp != 0:
         raise ValueError(f"sequence length ({T}) must be divisible by the context-parallel degree ({cp})")
     t = T // cp
+    from ...parallel import ulysses
+
+    if ulysses.peer_exchange_usable(x, group):
+        return ulysses.hp2cp(x, group)
     send = x.view(B, cp, t, h, D).permute(1, 0, 2, 3, 4).contiguous()
     recv = all_to_all_single(group, send.view(cp * B * t, h, D))
     # received chunk r holds head group r
@@ -74,7 +83,9 @@ def all_to_all_single_hp2cp(x: torch.Tensor, group: Optional[dist.ProcessGroup] 
 def all_to_all_cp2hp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
     """Batched :func:`all_to_all_single_cp2hp`: tensors that share ``[B, T/CP, *, D]`` go in one exchange."""
     cp = _size(group)
-    if cp == 1 or len(tensors) == 1:
+    from ...parallel import ulysses
+
+    if cp == 1 or len(tensors) == 1 or ulysses.peer_exchange_usable(tensors[0], group):  # no packing for the peer kernel
         return [all_to_all_single_cp2hp(t, group) for t in tensors]
     heads = [t.shape[2] for t in tensors]
     packed = torch.cat([t.view(t.shape[0], t.shape[1], cp, h // cp, t.shape[3]) for t, h in zip(tensors, heads)], dim=3)
@@ -86,7 +97,9 @@ def all_to_all_cp2hp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGr
 def all_to_all_hp2cp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
     """Batched :func:`all_to_all_single_hp2cp`."""
     cp = _size(group)
-    if cp == 1 or len(tensors) == 1:
+    from ...parallel import ulysses
+
+    if cp == 1 or len(tensors) == 1 or ulysses.peer_exchange_usable(tensors[0], group):
         return [all_to_all_single_hp2cp(t, group) for t in tensors]
     local_heads = [t.shape[2] for t in tensors]
     packed = torch.cat(tensors, dim=2)

@@ -27,6 +27,8 @@ struct PushParams {
   const int* seg_count;         // [S]
   const int* seg_dst_rank;      // [S]
   const long long* seg_dst_start;  // [S]
+  const int* seg_src_col;       // nullable [S]: first 16-byte vector of the segment inside a source row
+  const int* seg_dst_col;       // nullable [S]: first 16-byte vector inside a destination row
   uint4* peer[PUSH_MAX_PEERS];  // base of every rank's destination buffer
   long long dst_capacity_rows;
   int vecs_per_row;             // cols / 8
@@ -50,8 +52,8 @@ __global__ void __launch_bounds__(PUSH_WARPS * 32) moe_push_rows_kernel(const Pu
     }
     const int sorted_row = src0 + r;
     const long long src_row = p.gather_idx ? p.gather_idx[sorted_row] / p.gather_div : sorted_row;
-    const uint4* src = p.src + src_row * p.ld_src_vec;
-    uint4* dst = dst_base + dst_row * p.ld_dst_vec;
+    const uint4* src = p.src + src_row * p.ld_src_vec + (p.seg_src_col ? p.seg_src_col[s] : 0);
+    uint4* dst = dst_base + dst_row * p.ld_dst_vec + (p.seg_dst_col ? p.seg_dst_col[s] : 0);
     // two vectors in flight per lane: the loads of the second overlap the NVLink stores of the first
     int v = lane;
     for (; v + 32 < p.vecs_per_row; v += 64) {
@@ -70,10 +72,11 @@ using namespace ocb;
 
 // src: [*, ld_src] bf16 rows of `cols` elements (cols % 8 == 0, row starts 16-byte aligned). peer_ptrs: host array of
 // `world` device pointers (each rank's destination base, already offset to the half of the double buffer in use).
-extern "C" int ocb_moe_push_rows(const void* src, const int* gather_idx, int gather_div, const int* seg_src_start,
-                                 const int* seg_count, const int* seg_dst_rank, const long long* seg_dst_start,
-                                 int num_segments, void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols,
-                                 long long ld_src, long long ld_dst, int* status, cudaStream_t stream) {
+static int push_rows(const void* src, const int* gather_idx, int gather_div, const int* seg_src_start,
+                     const int* seg_count, const int* seg_dst_rank, const long long* seg_dst_start,
+                     const int* seg_src_col, const int* seg_dst_col, int num_segments, void* const* peer_ptrs, int world,
+                     long long dst_capacity_rows, int cols, long long ld_src, long long ld_dst, int* status,
+                     cudaStream_t stream) {
   if (num_segments <= 0) return 0;
   if (world < 1 || world > PUSH_MAX_PEERS || (cols % 8) || (ld_src % 8) || (ld_dst % 8) || gather_div < 1 || status == nullptr)
     return -5;
@@ -85,6 +88,8 @@ extern "C" int ocb_moe_push_rows(const void* src, const int* gather_idx, int gat
   p.seg_count = seg_count;
   p.seg_dst_rank = seg_dst_rank;
   p.seg_dst_start = seg_dst_start;
+  p.seg_src_col = seg_src_col;
+  p.seg_dst_col = seg_dst_col;
   for (int i = 0; i < PUSH_MAX_PEERS; ++i) p.peer[i] = static_cast<uint4*>(i < world ? peer_ptrs[i] : nullptr);
   p.dst_capacity_rows = dst_capacity_rows;
   p.vecs_per_row = cols / 8;
@@ -93,4 +98,24 @@ extern "C" int ocb_moe_push_rows(const void* src, const int* gather_idx, int gat
   p.status = status;
   moe_push_rows_kernel<<<dim3(PUSH_BLOCKS_PER_SEGMENT, num_segments), PUSH_WARPS * 32, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ocb_moe_push_rows(const void* src, const int* gather_idx, int gather_div, const int* seg_src_start,
+                                 const int* seg_count, const int* seg_dst_rank, const long long* seg_dst_start,
+                                 int num_segments, void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols,
+                                 long long ld_src, long long ld_dst, int* status, cudaStream_t stream) {
+  return push_rows(src, gather_idx, gather_div, seg_src_start, seg_count, seg_dst_rank, seg_dst_start, nullptr, nullptr,
+                   num_segments, peer_ptrs, world, dst_capacity_rows, cols, ld_src, ld_dst, status, stream);
+}
+
+// The same transfer for row SLICES: segment s reads `cols` elements from column seg_src_col_vec[s] * 8 of its source
+// rows and writes them from column seg_dst_col_vec[s] * 8 of its destination rows (both in 16-byte vectors). This is the
+// sequence <-> head exchange of Ulysses context parallelism as one kernel: a head group of every local token goes to
+// the rank that owns the group (or comes back), with no packing copy on either side.
+extern "C" int ocb_push_row_slices(const void* src, const int* seg_src_start, const int* seg_count, const int* seg_dst_rank,
+                                   const long long* seg_dst_start, const int* seg_src_col_vec, const int* seg_dst_col_vec,
+                                   int num_segments, void* const* peer_ptrs, int world, long long dst_capacity_rows,
+                                   int cols, long long ld_src, long long ld_dst, int* status, cudaStream_t stream) {
+  return push_rows(src, nullptr, 1, seg_src_start, seg_count, seg_dst_rank, seg_dst_start, seg_src_col_vec, seg_dst_col_vec,
+                   num_segments, peer_ptrs, world, dst_capacity_rows, cols, ld_src, ld_dst, status, stream);
 }

@@ -73,6 +73,12 @@ int ocb_moe_push_rows(const void* src, const int* gather_idx, int gather_div, co
                       const int* seg_count, const int* seg_dst_rank, const long long* seg_dst_start, int num_segments,
                       void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols, long long ld_src,
                       long long ld_dst, int* status, cudaStream_t stream);
+// Same, for row slices: segment s copies `cols` elements from 16-byte vector seg_src_col_vec[s] of its source rows to vector
+// seg_dst_col_vec[s] of its destination rows (the Ulysses sequence <-> head exchange).
+int ocb_push_row_slices(const void* src, const int* seg_src_start, const int* seg_count, const int* seg_dst_rank,
+                        const long long* seg_dst_start, const int* seg_src_col_vec, const int* seg_dst_col_vec,
+                        int num_segments, void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols,
+                        long long ld_src, long long ld_dst, int* status, cudaStream_t stream);
 
 // ---- normalisation / rotary / activation (elementwise.cu) -------------------------------------------
 // y = rmsnorm(x) * w  (+ resid).  x,y,resid: [rows, cols] with row strides ldx/ldy/ldr. w: [cols].

@@ -186,3 +186,44 @@ def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
 ])
 def test_context_parallel_attention_over_peer_memory(zig_zag, window, mode):
     run_distributed_test(_cp_in_kernel_worker, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(zig_zag, window, mode))
+
+
+def _ulysses_peer_worker():
+    """Sequence <-> head exchange by the peer-memory kernel against the all-to-all path, values and gradients."""
+    import torch.distributed as dist
+
+    from olmo_core_b200.distributed.parallel.context_parallel import all_to_all_cp2hp, all_to_all_single_hp2cp
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.parallel import ulysses
+
+    rank, cp = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    B, t, D = 2, 1500, 128  # more tokens than one segment piece
+    gen = torch.Generator().manual_seed(5 + rank)
+    results = {}
+    for flag in ("1", "0"):
+        os.environ["OLMO_CORE_B200_ULYSSES_PEER"] = flag
+        q = torch.randn(B, t, 4 * cp, D, generator=torch.Generator().manual_seed(5 + rank)).to(dev, torch.bfloat16).requires_grad_(True)
+        k = torch.randn(B, t, 2 * cp, D, generator=torch.Generator().manual_seed(50 + rank)).to(dev, torch.bfloat16).requires_grad_(True)
+        assert ulysses.peer_exchange_usable(q, dist.group.WORLD) == (flag == "1")
+        for _ in range(3):  # both halves of the receive buffer get reused
+            qh, kh = all_to_all_cp2hp([q, k], dist.group.WORLD)
+            assert qh.shape == (B, cp * t, 4, D) and kh.shape == (B, cp * t, 2, D)
+            back = all_to_all_single_hp2cp(qh * 2, dist.group.WORLD)
+            assert back.shape == q.shape
+        q.grad = k.grad = None
+        w = torch.randn(back.shape, generator=torch.Generator().manual_seed(9)).to(dev, torch.bfloat16)
+        ((back * w).float().sum() + (kh.float() ** 2).sum()).backward()
+        torch.cuda.synchronize()
+        _lib.check_device_status(dev)
+        results[flag] = [t_.detach().float().cpu() for t_ in (qh, kh, back, q.grad, k.grad)]
+    del gen
+    for a, b in zip(results["1"], results["0"]):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
+    torch.testing.assert_close(results["1"][2], 2 * q.detach().float().cpu(), rtol=0, atol=0)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+def test_ulysses_exchange_over_peer_memory():
+    run_distributed_test(_ulysses_peer_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
