@@ -291,8 +291,11 @@ class _ShardedFlashAttention(torch.autograd.Function):
         # the peers' K / V of this layer are needed once more
         k_ptrs, v_ptrs, n_src, rows_src, kv_layout = exchange.publish(k, v, layout, window or None)
         dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
-        dk_all = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
-        dv_all = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
+        if hasattr(exchange, "grad_buffers"):
+            dk_all, dv_all = exchange.grad_buffers(B, Tk, Hkv, D, k.dtype, k.device)
+        else:
+            dk_all = torch.empty((B, Tk, Hkv, D), dtype=k.dtype, device=k.device)
+            dv_all = torch.empty((B, Tk, Hkv, D), dtype=v.dtype, device=v.device)
         delta = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
         ld_kv = Hkv * D
         rc = _lib.lib().ocb_attention_bwd_sharded(
@@ -302,7 +305,7 @@ class _ShardedFlashAttention(torch.autograd.Function):
             _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr(),
         )
         _lib.check(rc, "ocb_attention_bwd_sharded")
-        dk, dv = exchange.reduce_to_owners(dk_all, dv_all)
+        dk, dv = exchange.reduce_to_owners(dk_all, dv_all, window or None)
         return dq, dk, dv, None, None, None, None
 
 

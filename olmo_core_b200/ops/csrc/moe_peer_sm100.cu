@@ -65,6 +65,66 @@ __global__ void __launch_bounds__(PUSH_WARPS * 32) moe_push_rows_kernel(const Pu
   }
 }
 
+
+// Sum of row ranges over peers: segment s produces rows [dst_start[s], +count[s]) of the local output as the fp32 sum,
+// over the ranks set in peer_mask[s], of rows [src_start[s], +count[s]) of that rank's buffer (bf16, read over NVLink
+// with 16-byte loads, four peers' loads in flight per lane). The fixed rank order makes the sum reproducible.
+struct ReduceParams {
+  const uint4* peer[PUSH_MAX_PEERS];
+  uint4* out;
+  const long long* seg_src_start;
+  const long long* seg_dst_start;
+  const int* seg_count;
+  const int* seg_peer_mask;
+  int world;
+  int vecs_per_row;
+  long long ld_src_vec, ld_dst_vec;
+};
+
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(PUSH_WARPS * 32) peer_reduce_rows_kernel(const ReduceParams p) {
+  const int s = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int count = p.seg_count[s];
+  const int mask = p.seg_peer_mask[s];
+  int ranks[PUSH_MAX_PEERS];
+  int n = 0;
+  for (int r = 0; r < p.world; ++r)
+    if (mask & (1 << r)) ranks[n++] = r;
+  const long long src0 = p.seg_src_start[s], dst0 = p.seg_dst_start[s];
+  for (int r = blockIdx.x * PUSH_WARPS + warp; r < count; r += gridDim.x * PUSH_WARPS) {
+    for (int v = lane; v < p.vecs_per_row; v += 32) {
+      const long long off = (src0 + r) * p.ld_src_vec + v;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      int i = 0;
+      for (; i + 4 <= n; i += 4) {
+        const uint4 a = p.peer[ranks[i]][off], b = p.peer[ranks[i + 1]][off];
+        const uint4 c = p.peer[ranks[i + 2]][off], d = p.peer[ranks[i + 3]][off];
+        add_bf16x8(acc, a);
+        add_bf16x8(acc, b);
+        add_bf16x8(acc, c);
+        add_bf16x8(acc, d);
+      }
+      for (; i < n; ++i) add_bf16x8(acc, p.peer[ranks[i]][off]);
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      p.out[(dst0 + r) * p.ld_dst_vec + v] = o;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace ocb
 
@@ -118,4 +178,27 @@ extern "C" int ocb_push_row_slices(const void* src, const int* seg_src_start, co
                                    int cols, long long ld_src, long long ld_dst, int* status, cudaStream_t stream) {
   return push_rows(src, nullptr, 1, seg_src_start, seg_count, seg_dst_rank, seg_dst_start, seg_src_col_vec, seg_dst_col_vec,
                    num_segments, peer_ptrs, world, dst_capacity_rows, cols, ld_src, ld_dst, status, stream);
+}
+
+// out rows [seg_dst_start[s], +seg_count[s]) = sum over the ranks in seg_peer_mask[s] of rows [seg_src_start[s], ...) of
+// peer_ptrs[rank] (bf16 rows of `cols` elements, fp32 accumulation in rank order). The caller's barrier orders this
+// kernel behind the peers' writes. Used to bring key / value gradients of context-parallel attention to their owners.
+extern "C" int ocb_peer_reduce_rows(void* const* peer_ptrs, int world, void* out, const long long* seg_src_start,
+                                    const long long* seg_dst_start, const int* seg_count, const int* seg_peer_mask,
+                                    int num_segments, int cols, long long ld_src, long long ld_dst, cudaStream_t stream) {
+  if (num_segments <= 0) return 0;
+  if (world < 1 || world > PUSH_MAX_PEERS || (cols % 8) || (ld_src % 8) || (ld_dst % 8)) return -5;
+  ReduceParams p;
+  for (int i = 0; i < PUSH_MAX_PEERS; ++i) p.peer[i] = static_cast<const uint4*>(i < world ? peer_ptrs[i] : nullptr);
+  p.out = static_cast<uint4*>(out);
+  p.seg_src_start = seg_src_start;
+  p.seg_dst_start = seg_dst_start;
+  p.seg_count = seg_count;
+  p.seg_peer_mask = seg_peer_mask;
+  p.world = world;
+  p.vecs_per_row = cols / 8;
+  p.ld_src_vec = ld_src / 8;
+  p.ld_dst_vec = ld_dst / 8;
+  peer_reduce_rows_kernel<<<dim3(PUSH_BLOCKS_PER_SEGMENT, num_segments), PUSH_WARPS * 32, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -75,6 +75,11 @@ int ocb_moe_push_rows(const void* src, const int* gather_idx, int gather_div, co
                       long long ld_dst, int* status, cudaStream_t stream);
 // Same, for row slices: segment s copies `cols` elements from 16-byte vector seg_src_col_vec[s] of its source rows to vector
 // seg_dst_col_vec[s] of its destination rows (the Ulysses sequence <-> head exchange).
+// out rows [seg_dst_start[s], +seg_count[s]) = sum over the ranks in seg_peer_mask[s] of rows [seg_src_start[s], ...) of
+// peer_ptrs[rank]; bf16 rows of `cols` elements, fp32 accumulation in rank order.
+int ocb_peer_reduce_rows(void* const* peer_ptrs, int world, void* out, const long long* seg_src_start,
+                         const long long* seg_dst_start, const int* seg_count, const int* seg_peer_mask, int num_segments,
+                         int cols, long long ld_src, long long ld_dst, cudaStream_t stream);
 int ocb_push_row_slices(const void* src, const int* seg_src_start, const int* seg_count, const int* seg_dst_rank,
                         const long long* seg_dst_start, const int* seg_src_col_vec, const int* seg_dst_col_vec,
                         int num_segments, void* const* peer_ptrs, int world, long long dst_capacity_rows, int cols,

@@ -108,6 +108,10 @@ class KVExchange:
         self._calls = 0
         self._arrays: dict = {}
         self._tables: dict = {}
+        self._gbuf = None
+        self._gnumel = 0
+        self._gcalls = 0
+        self._ghalf = None
 
     @classmethod
     def for_group(cls, group, zig_zag: bool) -> "KVExchange":
@@ -199,11 +203,90 @@ class KVExchange:
         own_v = (ctypes.c_void_p * 1)(v_ptrs[r])
         return own_k, own_v, 1, T_local * self.world_size, layout.gathered().c_array
 
-    def reduce_to_owners(self, dk_all: torch.Tensor, dv_all: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def grad_buffers(self, B: int, T: int, Hkv: int, D: int, dtype, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        """
+        Peer-visible ``[B, T, Hkv, D]`` homes (sequence order) for this rank's partial key / value gradients, from which
+        ``reduce_to_owners`` lets every owner collect its rows. Two halves alternate like the K / V slots.
+        """
+        import os
+
+        from .symmetric import SymmetricBuffer
+
+        if os.environ.get("OLMO_CORE_B200_CP_GRAD", "peer") != "peer":
+            return (torch.empty((B, T, Hkv, D), dtype=dtype, device=device),
+                    torch.empty((B, T, Hkv, D), dtype=dtype, device=device))
+        n = B * T * Hkv * D
+        if self._gbuf is None or 2 * n > self._gnumel or self._gbuf.tensor.dtype != dtype:
+            self._gbuf = SymmetricBuffer(4 * n, dtype, device, self.group)  # [half][dK | dV]
+            self._gnumel = 2 * n
+        half = self._gcalls & 1
+        self._gcalls += 1
+        base = half * self._gnumel
+        self._ghalf = (half, n)
+        flat = self._gbuf.tensor
+        return flat[base: base + n].view(B, T, Hkv, D), flat[base + n: base + 2 * n].view(B, T, Hkv, D)
+
+    def _reduce_table(self, B: int, T_local: int, window: Optional[int], device):
+        """Segments of this rank's rows with the ranks whose queries can see them (both tensors: dK rows, then dV rows)."""
+        key = ("reduce", B, T_local, window)
+        if key not in self._tables:
+            cp, T = self.world_size, T_local * self.world_size
+            mine = local_position_ranges(T_local, self.rank, cp, self.zig_zag)
+            piece, rows = 1024, []
+            for which in range(2):  # dK, dV: the source holds [2, B * T] rows, the output [2, B * T_local]
+                off = 0
+                for a, b in mine:
+                    for start in range(a, b, piece):
+                        end = min(b, start + piece)
+                        mask = 0
+                        for p in range(cp):
+                            for qa, qb in local_position_ranges(T_local, p, cp, self.zig_zag):
+                                if start < qb and (not window or end > qa - (window - 1)):
+                                    mask |= 1 << p
+                        for bi in range(B):
+                            rows.append((which * B * T + bi * T + start, which * B * T_local + bi * T_local + off + start - a,
+                                         end - start, mask))
+                    off += b - a
+            cols = list(zip(*rows))
+            self._tables[key] = (
+                torch.tensor(cols[0], dtype=torch.int64, device=device), torch.tensor(cols[1], dtype=torch.int64, device=device),
+                torch.tensor(cols[2], dtype=torch.int32, device=device), torch.tensor(cols[3], dtype=torch.int32, device=device),
+            )
+        return self._tables[key]
+
+    def reduce_to_owners(self, dk_all: torch.Tensor, dv_all: torch.Tensor, window: Optional[int] = None
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
         """``[B, T, Hkv, D]`` partial gradients in global key order -> this rank's ``[B, T_local, Hkv, D]`` sums."""
+        import ctypes
+
+        from ..ops import _lib
+
         cp = self.world_size
         B, T = dk_all.shape[0], dk_all.shape[1]
         tail = tuple(dk_all.shape[2:])
+        if self._gbuf is not None and self._ghalf is not None and dk_all.data_ptr() == (
+                self._gbuf.tensor.data_ptr() + self._ghalf[0] * self._gnumel * dk_all.element_size()):
+            # every owner sums its rows straight out of the peers' buffers (fp32, rank order): no packing, no collective
+            half, n = self._ghalf
+            self._ghalf = None
+            self._gbuf.barrier()
+            es = dk_all.element_size()
+            ptrs = (ctypes.c_void_p * cp)(*[int(p) + half * self._gnumel * es for p in self._gbuf.handle.buffer_ptrs])
+            src, dst, count, mask = self._reduce_table(B, T // cp, window, dk_all.device)
+            out = torch.empty((2, B, T // cp) + tail, dtype=dk_all.dtype, device=dk_all.device)
+            cols = tail[0] * tail[1]
+            lib = _lib.lib()
+            if not getattr(KVExchange, "_reduce_bound", False):
+                from ctypes import c_int, c_longlong, c_void_p
+
+                _lib.register_signature("ocb_peer_reduce_rows", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                                  c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p])
+                KVExchange._reduce_bound = True
+            rc = lib.ocb_peer_reduce_rows(ctypes.cast(ptrs, ctypes.c_void_p), cp, out.data_ptr(), src.data_ptr(),
+                                          dst.data_ptr(), count.data_ptr(), mask.data_ptr(), src.numel(), cols, cols, cols,
+                                          _lib.stream_ptr())
+            _lib.check(rc, "ocb_peer_reduce_rows")
+            return out[0], out[1]
         g = torch.stack([dk_all, dv_all])  # [2, B, T, ...]
         if self.zig_zag:
             order = [c for r in range(cp) for c in (r, 2 * cp - 1 - r)]

@@ -164,7 +164,7 @@ class _OneGpuExchange:
     def publish(self, k, v, layout, window=None):
         return self.k_ptrs, self.v_ptrs, self.world_size, k.shape[1], layout.c_array
 
-    def reduce_to_owners(self, dk_all, dv_all):
+    def reduce_to_owners(self, dk_all, dv_all, window=None):
         self.partials = (dk_all, dv_all)
         n = dk_all.shape[1] // self.world_size
         return torch.zeros_like(dk_all[:, :n]), torch.zeros_like(dv_all[:, :n])
