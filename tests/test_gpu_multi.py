@@ -227,3 +227,53 @@ def _ulysses_peer_worker():
 @requires_multi_gpu
 def test_ulysses_exchange_over_peer_memory():
     run_distributed_test(_ulysses_peer_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
+
+
+def _model_cp_worker(style_name: str):
+    """A small transformer with its sequence split over two GPUs against the same model on the whole sequence."""
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from olmo_core_b200.config import DType
+    from olmo_core_b200.nn.attention.ring import RingContextParallelStyle, UlyssesContextParallelStyle
+    from olmo_core_b200.nn.transformer import TransformerConfig
+    from olmo_core_b200.ops import _lib
+
+    rank, cp = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    cfg = TransformerConfig.llama_like(vocab_size=512, d_model=512, n_layers=2, n_heads=4, dtype=DType.bfloat16)
+    torch.manual_seed(3)
+    ref_model = cfg.build(init_device="cpu")
+    ref_model.init_weights(device=dev, max_seq_len=1024)
+    model = cfg.build(init_device="cpu")
+    model.init_weights(device=dev, max_seq_len=1024)
+    model.load_state_dict(ref_model.state_dict())
+    mesh = init_device_mesh("cuda", (cp,), mesh_dim_names=("cp",))
+    if style_name == "ulysses":
+        model.apply_cp(mesh, uly=UlyssesContextParallelStyle())
+    else:
+        model.apply_cp(mesh, ring=getattr(RingContextParallelStyle, style_name)())
+    ids = torch.randint(0, 512, (2, 1024), generator=torch.Generator().manual_seed(4)).to(dev)
+    labels = torch.roll(ids, -1, 1)
+    want = ref_model(ids, labels=labels, loss_reduction="sum")
+    got = model(ids, labels=labels, loss_reduction="sum")
+    total = got.loss.detach().float().clone()
+    dist.all_reduce(total)
+    torch.cuda.synchronize()
+    _lib.check_device_status(dev)
+    torch.testing.assert_close(total, want.loss.detach().float(), rtol=2e-2, atol=2e-2 * float(want.loss.abs()))
+    got.loss.backward()
+    want.loss.backward()
+    g = model.blocks["0"].attention.w_k.weight.grad.float().clone()
+    dist.all_reduce(g)
+    w = ref_model.blocks["0"].attention.w_k.weight.grad.float()
+    torch.testing.assert_close(g, w, rtol=5e-2, atol=5e-2 * float(w.abs().max()))
+    _lib.check_device_status(dev)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+@pytest.mark.parametrize("style_name", ["zig_zag", "llama3", "ulysses"])
+def test_transformer_under_context_parallelism(style_name):
+    run_distributed_test(_model_cp_worker, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(style_name,))
