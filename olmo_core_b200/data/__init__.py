@@ -46,7 +46,10 @@ from .source_mixture import SourceMixtureConfig, SourceMixtureDatasetConfig, Sou
 from .tokenizer import TokenizerConfig, TokenizerName
 from .types import LongDocStrategy, NumpyDatasetDType
 
+from . import composable  # noqa: E402,F401
+
 __all__ = [
+    "composable",
     "NumpyDatasetBase", "NumpyFSLDatasetBase", "NumpyFSLDataset", "NumpyFSLDatasetMixture", "NumpyPaddedFSLDataset",
     "NumpyPackedFSLDataset", "NumpyInterleavedFSLDataset", "NumpyVSLDataset", "VSLCurriculum", "VSLNaturalCurriculum",
     "VSLGrowthCurriculum", "VSLGrowP2Curriculum", "VSLGrowLinearCurriculum", "NumpyDatasetConfig", "NumpyFSLDatasetConfig",

@@ -18,7 +18,13 @@ from .configs import __all__ as _config_names
 from .data_loader import ComposableDataLoader, ComposableDataLoaderConfig, InstanceFilterConfig, ShuffleStrategy
 from .instance_source import *  # noqa: F401,F403
 from .instance_source import __all__ as _instance_names
-from .numpy_document_source import NumpyDocumentSource, NumpyDocumentSourceConfig, NumpyDocumentSourceMixConfig
+from ..types import LongDocStrategy
+from .numpy_document_source import (
+    NumpyDocumentSource,
+    NumpyDocumentSourceConfig,
+    NumpyDocumentSourceConfigBase,
+    NumpyDocumentSourceMixConfig,
+)
 from .source_abc import SourceABC
 from .token_source import *  # noqa: F401,F403
 from .token_source import __all__ as _token_names
@@ -27,6 +33,7 @@ from .visualize import render_source, visualize_source
 
 __all__ = [
     "SourceABC", "NumpyDocumentSource", "NumpyDocumentSourceConfig", "NumpyDocumentSourceMixConfig",
+    "NumpyDocumentSourceConfigBase", "LongDocStrategy",
     "ComposableDataLoader", "ComposableDataLoaderConfig", "InstanceFilterConfig", "ShuffleStrategy", "SEED_NOT_SET",
     "calculate_sample_sizes", "set_composable_seed", "reset_composable_seed", "resolve_seed", "render_source",
     "visualize_source", *_token_names, *_instance_names, *_config_names,

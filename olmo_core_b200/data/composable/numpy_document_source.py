@@ -21,7 +21,7 @@ from ...exceptions import OLMoConfigurationError
 from ...io import get_file_size, glob_directory, is_url, join_path, normalize_path
 from ..mixes import DataMix, DataMixBase
 from ..tokenizer import TokenizerConfig
-from ..types import NumpyDatasetDType
+from ..types import LongDocStrategy, NumpyDatasetDType
 from ..utils import iter_document_indices, load_array_slice
 from .token_source import DocumentSource, TokenRange
 
@@ -55,8 +55,12 @@ class NumpyDocumentSource(DocumentSource):
     DISPLAY_ICON = ""
 
     def __init__(self, *, source_paths: Sequence[PathOrStr], dtype, work_dir: PathOrStr, tokenizer: TokenizerConfig,
-                 label_mask_paths: Optional[Sequence[PathOrStr]] = None, label: Optional[str] = None):
+                 label_mask_paths: Optional[Sequence[PathOrStr]] = None, label: Optional[str] = None,
+                 max_document_length: Optional[int] = None,
+                 long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate):
         super().__init__(work_dir=work_dir, label=label)
+        self._max_document_length = max_document_length
+        self._long_doc_strategy = LongDocStrategy(long_doc_strategy)
         if not source_paths:
             raise OLMoConfigurationError("At least one source path is required.")
         if label_mask_paths is not None and len(label_mask_paths) != len(source_paths):
@@ -95,7 +99,17 @@ class NumpyDocumentSource(DocumentSource):
             h.update(f"{p}:{n},".encode())
         for p in self._mask_paths or ():
             h.update(f"mask={p},".encode())
+        if self._max_document_length is not None:
+            h.update(f"max_document_length={self._max_document_length},{self._long_doc_strategy},".encode())
         return h.hexdigest()
+
+    @property
+    def max_document_length(self) -> Optional[int]:
+        return self._max_document_length
+
+    @property
+    def long_doc_strategy(self) -> LongDocStrategy:
+        return self._long_doc_strategy
 
     @property
     def num_tokens(self) -> int:
@@ -140,23 +154,72 @@ class NumpyDocumentSource(DocumentSource):
         return offsets
 
     def get_document_offsets(self) -> Iterable[Tuple[int, int]]:
-        base = 0
+        # Documents longer than ``max_document_length`` are cut to their first part (truncate) or into consecutive
+        # parts (fragment), as in src/olmo_core/data/utils.py:253-285. The end of a file always ends a document.
+        base, limit = 0, self._max_document_length
         for path, n in zip(self._paths, self._sizes.tolist()):
+            last = 0
             for s, e in self._file_offsets(path).tolist():
-                yield base + s, base + e
+                if limit is None or e - s <= limit:
+                    yield base + s, base + e
+                elif self._long_doc_strategy == LongDocStrategy.truncate:
+                    yield base + s, base + s + limit
+                else:
+                    for start in range(s, e, limit):
+                        yield base + start, base + min(e, start + limit)
+                last = e
+            if last != n:
+                yield base + last, base + n
             base += n
 
 
-@dataclass
-class NumpyDocumentSourceConfig(Config):
+@dataclass(kw_only=True)
+class NumpyDocumentSourceConfigBase(Config):
+    """What :class:`NumpyDocumentSourceConfig` and :class:`NumpyDocumentSourceMixConfig` share
+    (src/olmo_core/data/composable/numpy_document_source.py:33-77)."""
+
+    tokenizer: TokenizerConfig
+    dtype: Optional[NumpyDatasetDType] = None
+    source_permutation_seed: Optional[int] = None
+    """Shuffles the source files before they are grouped into sources."""
+    source_group_size: int = 1
+    """Number of files per source; ``-1`` puts all files into one source."""
+    label: Optional[str] = None
+    max_document_length: Optional[int] = None
+    """Longer documents are truncated or fragmented (``long_doc_strategy``) when documents are iterated."""
+    long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate
+
+    def __post_init__(self):
+        if self.source_group_size < -1 or self.source_group_size == 0:
+            raise OLMoConfigurationError("'source_group_size' must be -1 or a positive integer.")
+
+    def get_dtype(self):
+        return _dtype_for(self.tokenizer, self.dtype)
+
+    def _grouped(self, paths: List[str], masks: Optional[List[str]]):
+        """Files (and their masks) in source order, cut into groups."""
+        order = list(range(len(paths)))
+        if self.source_permutation_seed is not None:
+            order = np.random.default_rng(self.source_permutation_seed).permutation(len(paths)).tolist()
+        paths = [paths[i] for i in order]
+        masks = None if masks is None else [masks[i] for i in order]
+        g = len(paths) if self.source_group_size == -1 else self.source_group_size
+        for i in range(0, len(paths), max(1, g)):
+            yield paths[i:i + g], None if masks is None else masks[i:i + g]
+
+    def _source(self, paths, masks, work_dir, label) -> "NumpyDocumentSource":
+        return NumpyDocumentSource(source_paths=paths, dtype=self.get_dtype(), work_dir=work_dir, tokenizer=self.tokenizer,
+                                   label_mask_paths=masks, label=label, max_document_length=self.max_document_length,
+                                   long_doc_strategy=self.long_doc_strategy)
+
+
+@dataclass(kw_only=True)
+class NumpyDocumentSourceConfig(NumpyDocumentSourceConfigBase):
     """``source_paths`` may hold glob patterns; files are grouped ``source_group_size`` at a time into sources."""
 
     source_paths: List[str]
-    tokenizer: TokenizerConfig
-    dtype: Optional[NumpyDatasetDType] = None
     label_mask_paths: Optional[List[str]] = None
-    source_group_size: int = 1
-    label: Optional[str] = None
+    expand_glob: Optional[bool] = None
 
     @classmethod
     def from_source_groups(cls, source_groups: Dict[str, List[str]], *, tokenizer: TokenizerConfig,
@@ -170,38 +233,27 @@ class NumpyDocumentSourceConfig(Config):
         masks = None if self.label_mask_paths is None else _expand(self.label_mask_paths)
         if masks is not None and len(masks) != len(paths):
             raise OLMoConfigurationError("'label_mask_paths' must match 'source_paths' one to one after globbing")
-        dtype = _dtype_for(self.tokenizer, self.dtype)
-        g = max(1, self.source_group_size)
-        return [NumpyDocumentSource(source_paths=paths[i:i + g], dtype=dtype, work_dir=work_dir, tokenizer=self.tokenizer,
-                                    label_mask_paths=None if masks is None else masks[i:i + g], label=self.label)
-                for i in range(0, len(paths), g)]
+        return [self._source(ps, ms, work_dir, self.label) for ps, ms in self._grouped(paths, masks)]
 
 
-@dataclass
-class NumpyDocumentSourceMixConfig(Config):
+@dataclass(kw_only=True)
+class NumpyDocumentSourceMixConfig(NumpyDocumentSourceConfigBase):
     """Sources for a named data mix (a manifest of ``label,relative/path`` lines resolved under ``mix_base_dir``)."""
 
-    tokenizer: TokenizerConfig
     mix: Union[str, DataMixBase]
     mix_base_dir: str
-    dtype: Optional[NumpyDatasetDType] = None
-    source_group_size: int = 1
 
     def build(self, work_dir: PathOrStr) -> List[NumpyDocumentSource]:
         if self.tokenizer.identifier is None:
             raise OLMoConfigurationError("Missing tokenizer identifier required to construct data mix")
         mix = self.mix if isinstance(self.mix, DataMixBase) else DataMix(self.mix)
         paths, labels = mix.build(self.mix_base_dir, self.tokenizer.identifier)
-        dtype = _dtype_for(self.tokenizer, self.dtype)
         by_label: Dict[str, List[str]] = {}
         for p, l in zip(paths, labels):
             by_label.setdefault(l, []).append(p)
-        g = max(1, self.source_group_size)
         out: List[NumpyDocumentSource] = []
         for label, group in by_label.items():
-            group = _expand(group)
-            out += [NumpyDocumentSource(source_paths=group[i:i + g], dtype=dtype, work_dir=work_dir,
-                                        tokenizer=self.tokenizer, label=label) for i in range(0, len(group), g)]
+            out += [self._source(ps, None, work_dir, label) for ps, _ in self._grouped(_expand(group), None)]
         return out
 
 

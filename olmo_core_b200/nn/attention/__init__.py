@@ -38,6 +38,7 @@ from .backend import (
     TorchAttentionBackend,
 )
 from .kv_cache import KVCacheManager
+from .recurrent import GatedDeltaNet, GatedDeltaNetConfig
 from .ring import (
     RingAttentionLlama3LoadBalancer,
     RingAttentionLoadBalancer,
@@ -49,6 +50,8 @@ from .ring import (
 )
 
 __all__ = [
+    "GatedDeltaNet",
+    "GatedDeltaNetConfig",
     "SequenceMixer",
     "SequenceMixerConfig",
     "SlidingWindowAttentionConfig",

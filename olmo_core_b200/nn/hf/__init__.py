@@ -14,5 +14,15 @@ from .convert import (
 )
 from .convert_checkpoint import convert_checkpoint_to_hf, load_config, validate_conversion
 
-__all__ = ["convert_checkpoint_to_hf", "convert_state_from_hf", "convert_state_to_hf", "get_converter_from_hf",
+from .hybrid import (
+    convert_hybrid_state_to_hf,
+    convert_qwen3_5_state_from_hf,
+    get_hybrid_hf_config,
+    get_hybrid_layer_types,
+    is_olmo_hybrid_model,
+    save_hf_hybrid_model,
+)
+
+__all__ = ["convert_hybrid_state_to_hf", "convert_qwen3_5_state_from_hf", "get_hybrid_hf_config", "get_hybrid_layer_types",
+           "is_olmo_hybrid_model", "save_hf_hybrid_model", "convert_checkpoint_to_hf", "convert_state_from_hf", "convert_state_to_hf", "get_converter_from_hf",
            "get_converter_to_hf", "get_hf_config", "load_config", "load_hf_model", "save_hf_model", "validate_conversion"]

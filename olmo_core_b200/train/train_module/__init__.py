@@ -10,6 +10,7 @@ from .transformer import (
     TransformerDataParallelWrappingStrategy,
     TransformerExpertParallelConfig,
     TransformerPipelineParallelConfig,
+    TransformerPipelineTrainModuleConfig,
     TransformerPipelineTrainModule,
     TransformerTensorParallelConfig,
     TransformerTrainModule,
@@ -25,6 +26,7 @@ __all__ = [
     "TransformerTrainModule",
     "TransformerTrainModuleConfig",
     "TransformerPipelineTrainModule",
+    "TransformerPipelineTrainModuleConfig",
     "TransformerActivationCheckpointingConfig",
     "TransformerActivationCheckpointingMode",
     "TransformerDataParallelConfig",

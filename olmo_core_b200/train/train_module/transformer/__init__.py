@@ -6,6 +6,7 @@ from .config import (
     TransformerDataParallelWrappingStrategy,
     TransformerExpertParallelConfig,
     TransformerPipelineParallelConfig,
+    TransformerPipelineTrainModuleConfig,
     TransformerTensorParallelConfig,
     TransformerTrainModuleConfig,
 )
@@ -16,6 +17,7 @@ __all__ = [
     "TransformerTrainModule",
     "TransformerTrainModuleConfig",
     "TransformerPipelineTrainModule",
+    "TransformerPipelineTrainModuleConfig",
     "TransformerActivationCheckpointingConfig",
     "TransformerActivationCheckpointingMode",
     "TransformerDataParallelConfig",

@@ -40,6 +40,7 @@ from ..config import TrainModuleConfig
 
 __all__ = [
     "TransformerTrainModuleConfig",
+    "TransformerPipelineTrainModuleConfig",
     "TransformerDataParallelConfig",
     "TransformerDataParallelWrappingStrategy",
     "TransformerTensorParallelConfig",
@@ -187,3 +188,13 @@ class TransformerTrainModuleConfig(TrainModuleConfig):
             kwargs["autocast_precision"] = DType(ap).as_pt()
         cls = TransformerPipelineTrainModule if self.pp_config is not None else TransformerTrainModule
         return cls(model=model, device=device, **kwargs)
+
+
+@dataclass
+class TransformerPipelineTrainModuleConfig(TransformerTrainModuleConfig):
+    """Older name of a :class:`TransformerTrainModuleConfig` whose ``pp_config`` is set
+    (src/olmo_core/train/train_module/transformer/config.py:379-386)."""
+
+    def __post_init__(self):
+        if self.pp_config is None:
+            raise OLMoConfigurationError("'pp_config' is required")

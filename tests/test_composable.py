@@ -171,3 +171,35 @@ def test_loader_intra_source_keeps_source_order(tmp_path):
     loader.reshuffle(1)
     order = np.concatenate([batch["index"].numpy() for batch in loader])
     assert (order[:16] < 16).all() and (order[16:] >= 16).all()
+
+
+def test_numpy_document_source_long_documents_and_file_order(tmp_path):
+    from olmo_core_b200.data.composable import LongDocStrategy, NumpyDocumentSourceConfigBase
+
+    tok = TokenizerConfig.gpt2()
+    eos = tok.eos_token_id
+    data = np.concatenate([np.arange(1, 12), [eos], np.arange(20, 23), [eos], np.arange(30, 33)]).astype(np.uint16)
+    for i in range(3):
+        (data + i).astype(np.uint16).tofile(tmp_path / f"f-{i}.npy")
+    pattern = [str(tmp_path / "f-*.npy")]
+    assert issubclass(NumpyDocumentSource.Config, NumpyDocumentSourceConfigBase)
+
+    # a 12-token document with a limit of 5: cut to its first 5 tokens, or into parts of 5, 5 and 2; the unterminated
+    # tail of a file always counts as a document
+    (trunc,) = NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_group_size=-1, max_document_length=5,
+                                          long_doc_strategy=LongDocStrategy.truncate).build(tmp_path / "w1")
+    assert list(trunc.get_document_offsets())[:3] == [(0, 5), (12, 16), (16, 19)]
+    (frag,) = NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_group_size=-1, max_document_length=5,
+                                         long_doc_strategy=LongDocStrategy.fragment).build(tmp_path / "w2")
+    assert list(frag.get_document_offsets())[:5] == [(0, 5), (5, 10), (10, 12), (12, 16), (16, 19)]
+    assert trunc.fingerprint != frag.fingerprint
+
+    # the permutation seed reorders the files before they are grouped; the same seed gives the same order
+    plain = NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok).build(tmp_path / "w3")
+    assert [s.source_paths[0][-7:] for s in plain] == ["f-0.npy", "f-1.npy", "f-2.npy"]
+    a = NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_permutation_seed=3).build(tmp_path / "w4")
+    b = NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_permutation_seed=3).build(tmp_path / "w5")
+    assert [s.source_paths for s in a] == [s.source_paths for s in b]
+    assert sorted(s.source_paths[0] for s in a) == sorted(s.source_paths[0] for s in plain)
+    with pytest.raises(Exception):
+        NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_group_size=0)
