@@ -412,3 +412,15 @@ class MixingInstanceSource(_Indexed):
     @property
     def seed(self) -> Optional[int]:
         return self._seed
+
+
+_CONFIG_NAMES = ('InstanceSourceConfig', 'ConcatenatedInstanceSourceConfig', 'SplitInstanceSourceConfig')
+
+
+def __getattr__(name: str):
+    # the config classes live in ``configs.py`` (which imports this module); they stay reachable under this module's name
+    if name in _CONFIG_NAMES:
+        from . import configs
+
+        return getattr(configs, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -436,3 +436,15 @@ class MixingDocumentSource(MixingTokenSource, DocumentSource):
             for s, e in child.get_document_offsets():
                 yield base + s, base + e
             base += child.num_tokens
+
+
+_CONFIG_NAMES = ('TokenSourceConfig', 'DocumentSourceConfig', 'ConcatenatedTokenSourceConfig', 'ConcatenatedDocumentSourceConfig', 'SplitTokenSourceConfig')
+
+
+def __getattr__(name: str):
+    # the config classes live in ``configs.py`` (which imports this module); they stay reachable under this module's name
+    if name in _CONFIG_NAMES:
+        from . import configs
+
+        return getattr(configs, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -153,3 +153,23 @@ def build_global_indices(total_instances: int, *, sequence_length: int, max_sequ
     if group == 1:
         return order
     return (order[:, None] * group + np.arange(group, dtype=dtype)[None, :]).reshape(-1)
+
+
+def path_map(func, paths, *, max_workers: Optional[int] = None, method: str = "threads"):
+    """
+    ``[func(p) for p in paths]`` computed by a pool of threads or processes, results in the order of ``paths``
+    (src/olmo_core/data/composable/utils.py:41-90). ``max_workers=0`` runs in the calling thread.
+    """
+    import concurrent.futures
+
+    paths = list(paths)
+    if max_workers == 0 or len(paths) <= 1:
+        return [func(p) for p in paths]
+    if method == "threads":
+        pool_cls = concurrent.futures.ThreadPoolExecutor
+    elif method == "processes":
+        pool_cls = concurrent.futures.ProcessPoolExecutor
+    else:
+        raise ValueError(method)
+    with pool_cls(max_workers=max_workers) as pool:
+        return list(pool.map(func, paths))

@@ -393,6 +393,25 @@ class InstancePacker:
         self.instances: List[List[int]] = []
         self._space: List[int] = []
 
+    def reset(self) -> None:
+        """Forget all instances."""
+        self.instances = []
+        self._space = []
+
+    @property
+    def instance_bins(self) -> List[List[int]]:
+        return self.instances
+
+    @property
+    def total_tokens(self) -> int:
+        """Capacity of all open instances."""
+        return self.max_sequence_length * len(self.instances)
+
+    @property
+    def total_padding(self) -> int:
+        """Free tokens left over all instances (documents packed one by one with :meth:`pack_document`)."""
+        return int(sum(self._space))
+
     def _best_fit(self, length: int) -> Optional[int]:
         best, best_space = None, None
         for i, s in enumerate(self._space):
@@ -463,3 +482,124 @@ def pack_documents_into_instances(path: PathOrStr, max_sequence_length: int, *, 
             docs.append((start, end))
     arr = np.asarray(docs, dtype=indices_dtype).reshape(-1, 2)
     return InstancePacker(max_sequence_length).pack_documents(arr)
+
+
+def iter_document_indices_with_max_sequence_length(
+    data_path: PathOrStr, max_sequence_length: int, *, local_cache: Optional[PathOrStr] = None,
+    use_array_if_local: Optional[bool] = None, eos_token_id: Optional[int] = None, bos_token_id: Optional[int] = None,
+    dtype=None, long_doc_strategy="truncate",
+) -> Generator[Tuple[int, int], None, None]:
+    """
+    :func:`iter_document_indices` with documents longer than ``max_sequence_length`` cut to their first part
+    (``truncate``) or into consecutive parts (``fragment``) (src/olmo_core/data/utils.py:253-285).
+    """
+    from .types import LongDocStrategy
+
+    strategy = LongDocStrategy(long_doc_strategy)
+    kwargs = {} if use_array_if_local is None else {"use_array_if_local": use_array_if_local}
+    for start, end in iter_document_indices(data_path, local_cache=local_cache, eos_token_id=eos_token_id,
+                                            bos_token_id=bos_token_id, dtype=dtype, **kwargs):
+        if end - start <= max_sequence_length:
+            yield start, end
+        elif strategy == LongDocStrategy.truncate:
+            yield start, start + max_sequence_length
+        elif strategy == LongDocStrategy.fragment:
+            for s in range(start, end, max_sequence_length):
+                yield s, min(end, s + max_sequence_length)
+        else:
+            raise NotImplementedError(strategy)
+
+
+def run_worker_func(func, *args, **kwargs):
+    """Entry point of data worker processes: runs ``func`` (remote-storage clients are created lazily per process here)."""
+    return func(*args, **kwargs)
+
+
+def find_end_first_consecutive_true(arr: np.ndarray) -> int:
+    """End (exclusive) of the run of ``True`` that starts at position 0; 0 when the array starts with ``False``."""
+    arr = np.asarray(arr, dtype=bool)
+    if arr.size == 0 or not arr[0]:
+        return 0
+    false_at = np.flatnonzero(~arr)
+    return int(false_at[0]) if false_at.size else int(arr.size)
+
+
+def find_start_last_consecutive_true(arr: np.ndarray) -> int:
+    """Start of the run of ``True`` that ends at the last position; -1 when the array ends with ``False``."""
+    n = find_end_first_consecutive_true(np.asarray(arr)[::-1])
+    return len(arr) - n if n > 0 else -1
+
+
+def group_consecutive_values(arr: np.ndarray, stepsize: int = 1) -> List[np.ndarray]:
+    """Split ``arr`` wherever the difference between neighbours is not ``stepsize``."""
+    return np.split(arr, np.flatnonzero(np.diff(arr) != stepsize) + 1)
+
+
+class SegmentTreeNode:
+    """A node of :class:`SegmentTree`: ``weight`` is the largest weight among the leaves below it."""
+
+    __slots__ = ("_tree", "_pos")
+
+    def __init__(self, tree: "SegmentTree", pos: int):
+        self._tree, self._pos = tree, pos
+
+    @property
+    def weight(self) -> int:
+        return int(self._tree._w[self._pos])
+
+    @property
+    def is_root(self) -> bool:
+        return self._pos == 1
+
+    @property
+    def is_leaf(self) -> bool:
+        return self._pos >= self._tree.N
+
+    @property
+    def leaf_id(self) -> Optional[int]:
+        return self._pos - self._tree.N if self.is_leaf else None
+
+    @property
+    def parent(self) -> Optional["SegmentTreeNode"]:
+        return None if self.is_root else SegmentTreeNode(self._tree, self._pos >> 1)
+
+    @property
+    def children(self) -> Optional[Tuple["SegmentTreeNode", "SegmentTreeNode"]]:
+        if self.is_leaf:
+            return None
+        return SegmentTreeNode(self._tree, 2 * self._pos), SegmentTreeNode(self._tree, 2 * self._pos + 1)
+
+    def update(self, weight: Optional[int] = None) -> None:
+        """Set a leaf's weight (or recompute an inner node) and refresh the maxima up to the root."""
+        w, pos = self._tree._w, self._pos
+        if weight is not None:
+            assert self.is_leaf
+            w[pos] = weight
+            pos >>= 1
+        while pos >= 1:
+            w[pos] = max(w[2 * pos], w[2 * pos + 1])
+            pos >>= 1
+
+
+class SegmentTree:
+    """
+    Max segment tree over ``N`` leaves (``N`` a power of two), heap-ordered in one array. Used for best-fit packing
+    (src/olmo_core/data/utils.py:745-803): leaf ``i`` carries weight ``i + 1`` while some open instance has exactly
+    ``i + 1`` free tokens, and ``query(w)`` descends to the LEFTMOST leaf whose weight is at least ``w``, i.e. the
+    tightest free space that still fits. The last leaf starts with weight ``N`` (a fresh instance always fits).
+    """
+
+    def __init__(self, N: int):
+        assert N > 0 and N & (N - 1) == 0, "N should be a power of 2"
+        self.N = N
+        self._w = np.zeros(2 * N, dtype=np.int64)
+        self.leaf_nodes = [SegmentTreeNode(self, N + i) for i in range(N)]
+        self.root_node = SegmentTreeNode(self, 1)
+        self.leaf_nodes[-1].update(N)
+
+    def query(self, weight: int) -> SegmentTreeNode:
+        pos = 1
+        assert weight <= self._w[1]
+        while pos < self.N:
+            pos = 2 * pos if weight <= self._w[2 * pos] else 2 * pos + 1
+        return SegmentTreeNode(self, pos)

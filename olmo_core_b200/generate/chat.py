@@ -186,3 +186,69 @@ def main(argv: Optional[List[str]] = None) -> None:
 if __name__ == "__main__":
     prepare_cli_environment()
     main()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Panels of the terminal front end (names of src/olmo_core/generate/chat.py:34-160; they need ``rich``)
+# ---------------------------------------------------------------------------------------------------------------
+
+def _bubble(message: str, title: str, colour: str, style: str):
+    from rich.panel import Panel
+    from rich.text import Text
+
+    return Panel(Text(message, style=style), title=f"[bold {colour}]{title}[/bold {colour}]", title_align="left",
+                 border_style=colour, padding=(0, 1))
+
+
+def render_user_message(message: str):
+    """A user turn as a chat bubble."""
+    return _bubble(message, "User", "cyan", "default")
+
+
+def render_assistant_message(message: str):
+    """A model turn as a chat bubble."""
+    return _bubble(message, "Assistant", "magenta", "default")
+
+
+def render_system_message(message: str):
+    """The system prompt, dimmed."""
+    return _bubble(message, "System", "yellow", "dim")
+
+
+def _two_columns(title: str, left: List[str], right: List[str], colour: str):
+    from rich.columns import Columns
+    from rich.panel import Panel
+    from rich.text import Text
+
+    return Panel(Columns([Text("\n".join(left)), Text("\n".join(right))], equal=True, expand=True),
+                 title=f"[bold {colour}]{title}[/bold {colour}]", title_align="left", border_style=colour, padding=(0, 1))
+
+
+def render_tokenizer_info(tokenizer_config: TokenizerConfig, tokenizer, chat_template: str):
+    """The tokenizer settings of the checkpoint next to those of the loaded Hugging Face tokenizer."""
+    left = ["OLMo-core TokenizerConfig:", f"  • Identifier: {tokenizer_config.identifier or 'N/A'}",
+            f"  • Vocab size: {tokenizer_config.vocab_size:,}", f"  • EOS token ID: {tokenizer_config.eos_token_id}",
+            f"  • Pad token ID: {tokenizer_config.pad_token_id}", f"  • BOS token ID: {tokenizer_config.bos_token_id}"]
+    right = ["HuggingFace Tokenizer:", f"  • Vocab size: {getattr(tokenizer, 'vocab_size', 0):,}",
+             f"  • Model max length: {getattr(tokenizer, 'model_max_length', None)}"]
+    special = getattr(tokenizer, "all_special_tokens", None)
+    if special:
+        shown = ", ".join(special[:6]) + (", ..." if len(special) > 6 else "")
+        right.append(f"  • Special tokens: {shown}")
+    first_line = (chat_template or "").strip().splitlines()[0] if (chat_template or "").strip() else "N/A"
+    right.append(f"  • Chat template: {first_line[:60]}")
+    return _two_columns("Tokenizer", left, right, "green")
+
+
+def render_generation_config(generation_config: GenerationConfig):
+    """Sampling and cache settings of the session."""
+    left = [f"• Max new tokens: {generation_config.max_new_tokens}"]
+    right = [f"• Max length: {generation_config.max_length}"]
+    if generation_config.do_sample:
+        top_k = "unlimited" if generation_config.top_k == -1 else str(generation_config.top_k)
+        left += ["• Sampling: enabled", f"• Temperature: {generation_config.temperature}", f"• Top-k: {top_k}",
+                 f"• Top-p: {generation_config.top_p}"]
+    else:
+        left.append("• Sampling: disabled (greedy)")
+    right.append(f"• KV cache: {'enabled' if generation_config.use_cache else 'disabled'}")
+    return _two_columns("Generation config", left, right, "blue")

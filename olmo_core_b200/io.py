@@ -48,6 +48,7 @@ __all__ = [
     "clear_directory",
     "list_directory",
     "glob_directory",
+    "deterministic_glob_directory",
     "init_client",
     "deserialize_from_tensor",
     "serialize_to_tensor",
@@ -514,3 +515,8 @@ def serialize_to_tensor(x: Any) -> torch.Tensor:
 
 def deserialize_from_tensor(data: torch.Tensor) -> Any:
     return pickle.loads(bytearray(data.cpu().numpy().tobytes()))
+
+
+def deterministic_glob_directory(pattern: str) -> List[str]:
+    """:func:`glob_directory` as a sorted list, so that every rank and every run sees the same order."""
+    return sorted(glob_directory(pattern))

@@ -89,3 +89,21 @@ def binned_scatter_wgrad(x: torch.Tensor, grad: torch.Tensor, indices: torch.Ten
         entries = indices[starts[e]:starts[e] + n].long()
         out[entries] = (x[e, :n].float() * grad[entries // top_k].float()).sum(-1)
     return out.to(x.dtype)
+
+
+def assert_is_tensor(x, ndim):
+    if x.ndim != ndim:
+        raise ValueError(f"Expected {ndim}-tensor but got {x.ndim}-tensor")
+
+
+def assert_is_matrix(x):
+    assert_is_tensor(x, 2)
+
+
+def assert_is_vector(x):
+    assert_is_tensor(x, 1)
+
+
+def assert_equal(a, b):
+    if a != b:
+        raise ValueError(f"Expected dimensions to be equal but got {a} and {b}.")

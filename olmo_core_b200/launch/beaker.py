@@ -12,6 +12,7 @@ from __future__ import annotations
 import dataclasses
 import logging
 import os
+import re
 import threading
 from contextlib import contextmanager
 from dataclasses import dataclass
@@ -27,7 +28,7 @@ log = logging.getLogger(__name__)
 __all__ = [
     "is_running_in_beaker", "is_running_in_beaker_batch_job", "get_beaker_experiment_id", "get_beaker_client",
     "OLMoCoreBeakerImage", "BeakerEnvVar", "BeakerEnvSecret", "BeakerWekaBucket", "BeakerLaunchConfig",
-    "BEAKER_RESULT_DIR",
+    "BEAKER_RESULT_DIR", "GantryMonitorCallback", "main",
 ]
 
 BEAKER_RESULT_DIR = "/results"
@@ -250,3 +251,150 @@ class BeakerLaunchConfig(Config):
         )
         return recipe.launch(show_logs=follow, start_timeout=self.launch_timeout, inactive_timeout=self.step_timeout,
                              inactive_soft_timeout=self.step_soft_timeout)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Watching a launched workload (role of ``GantryMonitorCallback``, src/olmo_core/launch/beaker.py:698-800)
+# ---------------------------------------------------------------------------------------------------------------
+
+_STEP_LINE = re.compile(r"\[.*step=\d+.*\]")
+
+
+class GantryMonitorCallback:
+    """
+    Follows the log stream of a launched workload: announces start / failure on Slack, warns when the trainer has not
+    logged a step for ``step_soft_timeout`` seconds (at most once per ``warning_frequency``) and interrupts the workload
+    after ``step_timeout`` seconds without a step. Before the first step is seen the clocks only start once the run has
+    been up for half an hour (soft) / an hour (hard), so that slow start-ups are not killed.
+
+    The hooks are the ones the ``beaker-gantry`` client calls on its callbacks (``on_start``, ``on_log``,
+    ``on_no_new_logs``, ``on_timeout``, ...). ``send`` posts a message (default: the Slack webhook), ``interrupt`` stops
+    the workload, ``clock`` is the time source; all three can be replaced, which is how the timeouts are tested.
+    """
+
+    def __init__(self, slack_webhook_url: Optional[str] = None, step_timeout: Optional[int] = None,
+                 step_soft_timeout: Optional[int] = None, warning_frequency: int = 3600, *,
+                 workload_name: str = "workload", workload_url: str = "", send=None, interrupt=None, clock=None):
+        import time
+
+        self.slack_webhook_url = slack_webhook_url
+        self.step_timeout = step_timeout
+        self.step_soft_timeout = step_soft_timeout
+        self.warning_frequency = warning_frequency
+        self.workload_name, self.workload_url = workload_name, workload_url
+        self._send = send if send is not None else self._post_to_slack
+        self._interrupt = interrupt
+        self._clock = clock if clock is not None else time.monotonic
+        self._start_time = self._clock()
+        self._first_step_detected = False
+        self._last_step_time = 0.0
+        self._last_inactivity_warning = 0.0
+
+    def _post_to_slack(self, text: str) -> None:
+        if not self.slack_webhook_url:
+            return
+        try:
+            import requests
+
+            requests.post(self.slack_webhook_url, json={"text": text}, timeout=10)
+        except Exception as e:  # a notification must never take the monitor down
+            log.warning(f"Failed to send Slack message: {e}")
+
+    def _say(self, emoji: str, what: str) -> None:
+        link = f"<{self.workload_url}|*{self.workload_name}*>" if self.workload_url else f"*{self.workload_name}*"
+        self._send(f"{emoji} Workload {link} {what}")
+
+    def interrupt_workload(self) -> None:
+        if self._interrupt is not None:
+            self._interrupt()
+
+    def on_start(self, job=None) -> None:
+        self._start_time = self._clock()
+        self._say(":check:", "has started! :runner:")
+
+    def on_start_timeout(self, job=None) -> None:
+        self._say(":warning:", "failed to start in time!")
+
+    def on_log(self, job=None, log_line: str = "", log_time: float = 0.0) -> None:
+        if self.step_timeout is None and self.step_soft_timeout is None:
+            return
+        if _STEP_LINE.search(log_line) is not None:
+            self._first_step_detected = True
+            self._last_step_time = self._clock()
+        self._check_timeouts()
+
+    def on_no_new_logs(self, job=None) -> None:
+        self._check_timeouts()
+
+    def _overdue(self, limit: Optional[int], grace: int, now: float) -> bool:
+        if limit is None:
+            return False
+        armed = self._first_step_detected or (now - self._start_time) > max(limit, grace)
+        return armed and (now - self._last_step_time) > limit
+
+    def _check_timeouts(self) -> None:
+        now = self._clock()
+        if self._overdue(self.step_soft_timeout, 1800, now) and (now - self._last_inactivity_warning) > self.warning_frequency:
+            self._say(":zzz:", "hasn't stepped recently!")
+            log.warning("Workload hasn't stepped recently!")
+            self._last_inactivity_warning = self._clock()
+        if self._overdue(self.step_timeout, 3600, now):
+            self._say(":warning:", "failed to step in time!")
+            log.error("Workload has failed to step in time, stopping...")
+            self.interrupt_workload()
+
+    def on_timeout(self, job=None) -> None:
+        self._say(":warning:", "failed to complete in time!")
+
+    def _inactive(self) -> None:
+        if (self._clock() - self._last_inactivity_warning) > self.warning_frequency:
+            self._say(":zzz:", "appears to be inactive!")
+            self._last_inactivity_warning = self._clock()
+
+    def on_inactive_timeout(self, job=None) -> None:
+        self._inactive()
+
+    def on_inactive_soft_timeout(self, job=None) -> None:
+        self._inactive()
+
+    def on_success(self, job=None) -> None:
+        self._say(":check:", "succeeded!")
+
+    def on_failure(self, job=None, *args, **kwargs) -> None:
+        self._say(":warning:", "failed!")
+
+
+def main(argv: Optional[List[str]] = None) -> None:
+    """``python -m olmo_core_b200.launch.beaker [options] -- command ...``: launch a command as a Beaker experiment."""
+    import argparse
+
+    ap = argparse.ArgumentParser(prog="olmo_core_b200.launch.beaker", description=main.__doc__)
+    ap.add_argument("--name", default="olmo-core-job")
+    ap.add_argument("--gpus", type=int, default=8)
+    ap.add_argument("--nodes", type=int, default=1)
+    ap.add_argument("--cluster", action="append", default=None, help="may be given several times")
+    ap.add_argument("--budget", default=None)
+    ap.add_argument("--workspace", default=None)
+    ap.add_argument("--priority", default=None)
+    ap.add_argument("--preemptible", action="store_true")
+    ap.add_argument("--allow-dirty", action="store_true")
+    ap.add_argument("--dry-run", action="store_true")
+    ap.add_argument("command", nargs=argparse.REMAINDER)
+    opts = ap.parse_args(argv)
+    command = [c for c in opts.command if c != "--"]
+    if not command:
+        ap.error("a command to run is required after '--'")
+    kwargs: Dict[str, Any] = dict(name=opts.name, cmd=command, num_gpus=opts.gpus, num_nodes=opts.nodes,
+                                  clusters=opts.cluster or [], preemptible=opts.preemptible, allow_dirty=opts.allow_dirty)
+    for key in ("budget", "workspace", "priority"):
+        if getattr(opts, key) is not None:
+            kwargs[key] = getattr(opts, key)
+    config = BeakerLaunchConfig(**kwargs)
+    if opts.dry_run:
+        config.dry_run()
+    else:
+        config.launch(follow=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -12,7 +12,7 @@ import logging
 from collections import defaultdict
 from dataclasses import dataclass
 from pathlib import Path
-from typing import Dict, List, Optional, Sequence, Set
+from typing import Any, Dict, List, Optional, Sequence, Set, Tuple
 
 from ..exceptions import BeakerInsufficientResourcesError, OLMoEnvironmentError
 
@@ -93,6 +93,24 @@ def get_hosts_metadata_from_gcp(zone: str, *, credentials_path: Optional[Path] =
                 topo = inst.resource_status.physical_host_topology
                 out[f"{inst.name}.reviz.ai2.in"] = HostMetadata(topo.block, topo.subblock, topo.host)
     return out
+
+
+_PRIORITY_ORDER = ["low", "normal", "high", "urgent"]
+
+
+def node_is_occupied(beaker, node, beaker_priority) -> Tuple[Any, bool]:
+    """``(node, True)`` when the node runs a job that holds slots and that ``beaker_priority`` cannot preempt."""
+    want = str(getattr(beaker_priority, "value", beaker_priority)).lower()
+    want_rank = _PRIORITY_ORDER.index(want) if want in _PRIORITY_ORDER else 1
+    for job in beaker.job.list(scheduled_on_node=node):
+        details = getattr(job, "assignment_details", None)
+        slots = getattr(getattr(details, "resource_assignment", None), "assigned_slots_count", 1)
+        have = str(getattr(getattr(job, "priority", None), "value", getattr(job, "priority", None)) or "normal").lower()
+        have_rank = _PRIORITY_ORDER.index(have) if have in _PRIORITY_ORDER else 1
+        preemptible = bool(getattr(job, "preemptible", False)) and have_rank < want_rank
+        if slots > 0 and not preemptible:
+            return node, True
+    return node, False
 
 
 def get_occupied_beaker_hosts(hosts_metadata: Dict[str, HostMetadata], beaker_cluster: str, priority: str) -> Set[str]:

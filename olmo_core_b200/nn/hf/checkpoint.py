@@ -81,3 +81,12 @@ def load_hf_model(model_name_or_path: PathOrStr, model_state_dict: Dict[str, Any
             from ...distributed.utils import get_local_tensor
 
             get_local_tensor(target).copy_(get_local_tensor(src))
+
+
+def __getattr__(name: str):
+    # defined in ``hybrid.py``; reachable under this module's name as well
+    if name in ('save_hf_hybrid_model',):
+        from . import hybrid
+
+        return getattr(hybrid, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

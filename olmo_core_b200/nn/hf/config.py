@@ -55,3 +55,12 @@ def get_hf_config(model):
         layer_types = ["sliding_attention" if getattr(b.attention, "window_size", None) else "full_attention" for b in blocks]
         return Olmo3Config(**common, sliding_window=windows.pop(), layer_types=layer_types)
     return Olmo2Config(**common)
+
+
+def __getattr__(name: str):
+    # defined in ``hybrid.py``; reachable under this module's name as well
+    if name in ('is_olmo_hybrid_model', 'get_hybrid_layer_types', 'get_hybrid_hf_config'):
+        from . import hybrid
+
+        return getattr(hybrid, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

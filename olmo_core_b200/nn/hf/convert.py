@@ -122,3 +122,12 @@ def convert_state_from_hf(hf_config, hf_state: Dict[str, Any], model_type: Optio
     if "lm_head.w_out.weight" not in converted and "embeddings.weight" in converted:
         converted["lm_head.w_out.weight"] = converted["embeddings.weight"]  # tied embeddings
     return converted
+
+
+def __getattr__(name: str):
+    # defined in ``hybrid.py``; reachable under this module's name as well
+    if name in ('convert_hybrid_state_to_hf', 'convert_qwen3_5_state_from_hf'):
+        from . import hybrid
+
+        return getattr(hybrid, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -9,7 +9,7 @@ experts (all-to-all with per-rank counts), runs its local experts, and sends res
 
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Any, List, NamedTuple, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -19,7 +19,21 @@ from ...distributed.utils import get_world_size
 from ...ops import moe as ops
 from .mlp import DroplessMoEMLP, MoEMLP, MoEMLPBase
 
-__all__ = ["ParallelMLPBase", "ParallelMLP", "ParallelDroplessMLP"]
+__all__ = ["ParallelMLPBase", "ParallelMLP", "ParallelDroplessMLP", "PermutedAllToAllOutput"]
+
+
+class PermutedAllToAllOutput(NamedTuple):
+    """What a dispatch hands to the expert computation (field names of src/olmo_core/nn/moe/parallel_mlp.py:22-31)."""
+
+    parallel_x: torch.Tensor
+    parallel_indices: torch.Tensor
+    parallel_bin_ids: Optional[torch.Tensor]
+    parallel_bins: torch.Tensor
+    parallel_batch_size_per_expert: torch.Tensor
+    recv_counts: Optional[List[int]]
+    send_counts: Optional[List[int]]
+    expert_capacity: int
+    handle: Any
 
 
 class ParallelMLPBase(nn.Module):

@@ -5,10 +5,10 @@ Operator layer. Each op runs a hand-written sm_100a kernel (``csrc/*.cu``, bound
 
 import torch
 
-__all__ = ["attach_auxiliary_loss"]
+__all__ = ["attach_auxiliary_loss", "AutoAuxiliaryLoss"]
 
 
-class _AuxLoss(torch.autograd.Function):
+class AutoAuxiliaryLoss(torch.autograd.Function):
     """Identity on ``x`` that feeds a gradient of one into ``aux_loss`` during backward."""
 
     @staticmethod
@@ -27,4 +27,4 @@ def attach_auxiliary_loss(x: torch.Tensor, aux_loss: torch.Tensor) -> torch.Tens
     Tie ``aux_loss`` to ``x`` so that ``backward`` through ``x`` also back-propagates the auxiliary loss
     (src/olmo_core/ops/__init__.py:4-28).
     """
-    return _AuxLoss.apply(x, aux_loss)
+    return AutoAuxiliaryLoss.apply(x, aux_loss)

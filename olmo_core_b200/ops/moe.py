@@ -283,3 +283,41 @@ class _AllToAllAsync(torch.autograd.Function):
 def all_to_all(x: torch.Tensor, output_split_sizes=None, input_split_sizes=None, group=None, async_op: bool = False):
     """Row exchange with variable split sizes; returns ``(output, work handle or None)``."""
     return _AllToAllAsync.apply(x, output_split_sizes, input_split_sizes, group, async_op)
+
+
+class _OpNamespace:
+    """``Name.apply(...)`` spelling of an op, for code written against the autograd-function classes of
+    src/olmo_core/ops/moe.py (``GatherOp``, ``ScatterOp``, ``BinnedGatherOp``, ``BinnedScatterOp``, ``AllToAllOp``)."""
+
+    _fn = None
+
+    @classmethod
+    def apply(cls, *args):
+        return cls._fn(*args)
+
+
+class GatherOp(_OpNamespace):
+    """``apply(x, indices, bin_ids, bins, top_k)``"""
+
+    _fn = staticmethod(gather)
+
+
+class ScatterOp(_OpNamespace):
+    """``apply(x, indices, bin_ids, weights, bins, top_k)``"""
+
+    _fn = staticmethod(scatter)
+
+
+class BinnedGatherOp(_OpNamespace):
+    """``apply(x, indices, bins, bin_size, top_k)``"""
+
+    _fn = staticmethod(binned_gather)
+
+
+class BinnedScatterOp(_OpNamespace):
+    """``apply(x, indices, weights, bins, top_k)``"""
+
+    _fn = staticmethod(binned_scatter)
+
+
+AllToAllOp = _AllToAllAsync

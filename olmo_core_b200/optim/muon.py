@@ -13,9 +13,10 @@ import torch
 import torch.nn as nn
 from torch.optim.optimizer import Optimizer
 
+from ..config import StrEnum
 from .config import MatrixAwareOptimConfig, OptimConfig
 
-__all__ = ["Muon", "MuonConfig", "NorMuonConfig", "newton_schulz"]
+__all__ = ["Muon", "MuonConfig", "NorMuonConfig", "MuonAdjustLRStrategy", "newton_schulz"]
 
 
 def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
@@ -34,12 +35,27 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
     return x.to(g.dtype)
 
 
+class MuonAdjustLRStrategy(StrEnum):
+    """How the step of an orthogonalised ``[rows, cols]`` update is scaled (src/olmo_core/optim/muon.py:35-40)."""
+
+    spectral_norm = "spectral_norm"
+    """``sqrt(max(1, rows / cols))``: keeps the update's spectral norm comparable across widths (learning-rate transfer)."""
+    rms_norm = "rms_norm"
+    """``0.2 * sqrt(max(rows, cols))``: the update's RMS matches AdamW's, so AdamW learning rates carry over."""
+
+    def scale(self, rows: int, cols: int) -> float:
+        if self == MuonAdjustLRStrategy.spectral_norm:
+            return max(1.0, rows / cols) ** 0.5
+        return 0.2 * max(rows, cols) ** 0.5
+
+
 class Muon(Optimizer):
     def __init__(self, params, lr: float = 0.02, mu: float = 0.95, betas: Tuple[float, float] = (0.9, 0.95),
                  weight_decay: float = 0.01, eps: float = 1e-8, nesterov: bool = True, ns_steps: int = 5,
-                 normalize: bool = False):
+                 normalize: bool = False, adjust_lr: Optional[str] = "spectral_norm", cautious_wd: bool = False):
         super().__init__(params, dict(lr=lr, mu=mu, betas=betas, weight_decay=weight_decay, eps=eps, nesterov=nesterov,
-                                      ns_steps=ns_steps, normalize=normalize, algorithm="muon"))
+                                      ns_steps=ns_steps, normalize=normalize, algorithm="muon", adjust_lr=adjust_lr,
+                                      cautious_wd=cautious_wd))
 
     @torch.no_grad()
     def step(self, closure=None) -> None:
@@ -65,9 +81,13 @@ class Muon(Optimizer):
                         v = state["row_var"].mul_(group["betas"][1]).add_(upd.pow(2).mean(dim=-1, keepdim=True), alpha=1 - group["betas"][1])
                         upd = upd / (v.sqrt() + group["eps"])
                         upd = upd * (upd.numel() ** 0.5 / (upd.norm() + group["eps"])) * 0.2
+                    elif group.get("adjust_lr") is not None:
+                        upd = upd * MuonAdjustLRStrategy(group["adjust_lr"]).scale(p.shape[0], p[0].numel())
+                    if group.get("cautious_wd"):  # decay only the entries that the update is already shrinking
+                        p.addcmul_(p, (upd * p > 0).to(p.dtype), value=-group["lr"] * group["weight_decay"])
                     else:
-                        upd = upd * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
-                    p.mul_(1 - group["lr"] * group["weight_decay"]).add_(upd, alpha=-group["lr"])
+                        p.mul_(1 - group["lr"] * group["weight_decay"])
+                    p.add_(upd, alpha=-group["lr"])
                 else:
                     if not state:
                         state["step"] = 0
@@ -85,15 +105,22 @@ class Muon(Optimizer):
 @OptimConfig.register("muon")
 @dataclass
 class MuonConfig(MatrixAwareOptimConfig[Muon]):
-    lr: float = 0.02
+    # defaults of src/olmo_core/optim/muon.py:60-90
+    lr: float = 0.01
     mu: float = 0.95
     betas: Tuple[float, float] = (0.9, 0.95)
-    weight_decay: float = 0.01
+    weight_decay: float = 0.1
     eps: float = 1e-8
-    nesterov: bool = True
+    nesterov: bool = False
     ns_steps: int = 5
     scalar_lr: Optional[float] = None
     normalize: bool = False
+    adjust_lr: Optional[MuonAdjustLRStrategy] = MuonAdjustLRStrategy.rms_norm
+    cautious_wd: bool = False
+    flatten: bool = True
+    """Tensors with more than two dimensions are always treated as ``[shape[0], -1]`` matrices."""
+    use_triton: bool = False
+    """Accepted for compatibility; the orthogonalisation runs on the in-tree GEMM path either way."""
 
     @classmethod
     def optimizer(cls) -> Type[Muon]:
@@ -113,7 +140,8 @@ class MuonConfig(MatrixAwareOptimConfig[Muon]):
 
     def build(self, model: nn.Module, strict: bool = True) -> Muon:
         kwargs = self.as_dict()
-        for k in ("group_overrides", "compile", "fixed_fields", "embedding_lr", "lm_head_lr", "vector_lr", "scalar_lr"):
+        for k in ("group_overrides", "compile", "fixed_fields", "embedding_lr", "lm_head_lr", "vector_lr", "scalar_lr",
+                  "flatten", "use_triton"):
             kwargs.pop(k)
         optim = Muon(self.build_groups(model, strict), **kwargs)
         for g in optim.param_groups:

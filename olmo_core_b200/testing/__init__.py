@@ -58,6 +58,14 @@ def requires_gpu(func):
     return _apply(GPU_MARKS, func)
 
 
+has_mps = bool(getattr(torch.backends, "mps", None)) and torch.backends.mps.is_available()
+MPS_MARKS = (pytest.mark.skipif(not has_mps, reason="Requires MPS"),)
+
+
+def requires_mps(func):
+    return _apply(MPS_MARKS, func)
+
+
 def requires_multi_gpu(func):
     return _apply(MULTI_GPU_MARKS, func)
 

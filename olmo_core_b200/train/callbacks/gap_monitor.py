@@ -176,3 +176,19 @@ class GAPMonitorCallback(Callback):
         for h in self._handles or []:
             h.remove()
         self._handles = None
+
+
+def var_mean(tensor: torch.Tensor, dim: Optional[int] = None):
+    """``torch.var_mean`` that also takes a sharded ``DTensor`` (reduced to full values; unbiased variance)."""
+    import math
+
+    from torch.distributed.tensor import DTensor
+
+    from ...distributed.utils import get_full_tensor
+
+    if not isinstance(tensor, DTensor):
+        return torch.var_mean(tensor, dim=dim)
+    numel = tensor.numel() if dim is None else tensor.size(dim)
+    mean = get_full_tensor(tensor.mean(dim=dim))
+    spread = get_full_tensor(torch.linalg.vector_norm(tensor - mean, dim=dim)) / math.sqrt(max(1, numel - 1))
+    return spread ** 2, mean

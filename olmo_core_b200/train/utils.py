@@ -21,7 +21,16 @@ from ..config import Config
 from ..distributed.utils import get_reduce_divide_factor, get_world_size, is_distributed
 from .common import ReduceType
 
-__all__ = ["EnvRngStates", "move_metrics", "reduce_metrics", "check_metrics_consistent"]
+__all__ = ["EnvRngStates", "LibRngState", "move_metrics", "reduce_metrics", "check_metrics_consistent",
+           "get_metrics_reduce_type_by_step", "get_metric_world_sizes_by_step"]
+
+
+@dataclass
+class LibRngState:
+    """One library's generator state with the library version it was taken under."""
+
+    version: Tuple[int, int]
+    state: Any
 
 
 @dataclass
@@ -163,3 +172,32 @@ def reduce_metrics(
     for i, s in enumerate(steps):
         out[s] = {n: float(host_vals[i, j]) for j, n in enumerate(names) if host_present[i, j] > 0}
     return out
+
+
+def _gather_reduce_types(metrics_reduce_type, process_group) -> List[Dict[str, Optional[ReduceType]]]:
+    if not is_distributed():
+        return [metrics_reduce_type]
+    gathered: List[Any] = [None] * get_world_size(process_group)
+    dist.all_gather_object(gathered, metrics_reduce_type, group=process_group)
+    return gathered
+
+
+def get_metrics_reduce_type_by_step(metrics: Dict[int, Dict[str, torch.Tensor]],
+                                    metrics_reduce_type: Dict[str, Optional[ReduceType]],
+                                    process_group: Optional[dist.ProcessGroup] = None) -> Dict[int, Dict[str, Optional[ReduceType]]]:
+    """For every step, the reduce type of every metric that ANY rank recorded (ranks may record different metrics)."""
+    merged: Dict[str, Optional[ReduceType]] = {}
+    for per_rank in _gather_reduce_types(metrics_reduce_type, process_group):
+        merged.update(per_rank)
+    return {step: dict(merged) for step in metrics}
+
+
+def get_metric_world_sizes_by_step(metrics: Dict[int, Dict[str, torch.Tensor]],
+                                   metrics_reduce_type: Dict[str, Optional[ReduceType]],
+                                   process_group: Optional[dist.ProcessGroup] = None) -> Dict[int, Dict[str, int]]:
+    """For every step, how many ranks recorded each metric (the divisor of a mean over the ranks that have it)."""
+    counts: Dict[str, int] = {}
+    for per_rank in _gather_reduce_types(metrics_reduce_type, process_group):
+        for name in per_rank:
+            counts[name] = counts.get(name, 0) + 1
+    return {step: dict(counts) for step in metrics}
