@@ -71,6 +71,21 @@ class AttentionBackendName(StrEnum):
     def assert_supported(self) -> None:
         self.get_class().assert_supported()
 
+    def assert_supports_swa(self) -> None:
+        self.get_class().assert_supports_swa()
+
+    def assert_supports_ring_cp(self) -> None:
+        self.get_class().assert_supports_ring_cp()
+
+    def assert_supports_ulysses_cp(self) -> None:
+        self.get_class().assert_supports_ulysses_cp()
+
+    def assert_supports_packed_qkv(self) -> None:
+        self.get_class().assert_supports_packed_qkv()
+
+    def assert_supports_kv_cache(self) -> None:
+        self.get_class().assert_supports_kv_cache()
+
 
 class AttentionBackend(nn.Module):
     """

@@ -73,6 +73,18 @@ class RingAttentionLoadBalancer(metaclass=ABCMeta):
                                 length_multiple: Optional[int] = None) -> Tuple[List[torch.Tensor], Dict[str, Any]]:
         raise NotImplementedError
 
+    def pad(self, x: torch.Tensor, seq_dim: int, value: Union[int, float],
+            length_multiple: Optional[int] = None) -> Tuple[torch.Tensor, int]:
+        """``x`` padded at the end of ``seq_dim`` to a multiple of ``length_multiple`` (default: what this balancer's
+        sharding needs), and the number of positions added."""
+        multiple = length_multiple if length_multiple is not None else self._default_multiple()
+        before = x.shape[seq_dim]
+        out = self._padded(x, seq_dim, multiple, value)
+        return out, out.shape[seq_dim] - before
+
+    def _default_multiple(self) -> int:
+        return self.cp_world_size
+
     def _padded(self, x: torch.Tensor, dim: int, multiple: int, value: Optional[Union[int, float]]) -> torch.Tensor:
         n = x.shape[dim]
         target = ensure_multiple_of(n, multiple)
@@ -84,6 +96,9 @@ class RingAttentionLoadBalancer(metaclass=ABCMeta):
 
 
 class RingAttentionZigZagLoadBalancer(RingAttentionLoadBalancer):
+    def _default_multiple(self) -> int:
+        return 2 * self.cp_world_size
+
     def _take(self, x: torch.Tensor, dim: int) -> torch.Tensor:
         chunks = x.chunk(2 * self.cp_world_size, dim=dim)
         return torch.cat((chunks[self.cp_rank], chunks[2 * self.cp_world_size - 1 - self.cp_rank]), dim=dim)

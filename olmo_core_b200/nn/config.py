@@ -33,5 +33,14 @@ class ModelConfig(Config):
     def num_non_embedding_params(self) -> int:
         raise NotImplementedError
 
+    @property
+    def num_active_params(self) -> int:
+        """Parameters that take part in one token's forward pass (all of them unless the model is sparse)."""
+        return self.num_params
+
+    @property
+    def num_active_non_embedding_params(self) -> int:
+        return self.num_non_embedding_params
+
     def num_flops_per_token(self, seq_len: int) -> int:
         raise NotImplementedError

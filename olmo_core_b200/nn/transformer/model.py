@@ -142,6 +142,27 @@ class Transformer(nn.Module):
         return self._tp_enabled
 
     @property
+    def fsdp_enabled(self) -> bool:
+        return bool(getattr(self, "_fsdp_enabled", False))
+
+    def compute_auxiliary_metrics(self, reset: bool = True):
+        """Model-internal metrics to log (none for a dense model; the MoE model reports router statistics)."""
+        del reset
+        return {}
+
+    def reset_auxiliary_metrics(self) -> None:
+        pass
+
+    def get_rope_buffers(self, seq_len: int, device: Optional[torch.device] = None):
+        """Per layer, the rotary tables of its attention for ``seq_len`` positions (``None`` for layers without RoPE)."""
+        device = device if device is not None else self.device
+        out = {}
+        for key, block in self.blocks.items():
+            rope = getattr(getattr(block, "attention", None), "rope", None)
+            out[int(key)] = None if rope is None else rope.get_buffers(seq_len, device)
+        return out
+
+    @property
     def cp_enabled(self) -> bool:
         return self._cp_load_balancer is not None
 
