@@ -54,7 +54,14 @@ def parse_args():
     ap.add_argument("--no-compile", action="store_true", help="debugging only: skip torch.compile")
     ap.add_argument("--ac", choices=["none", "full"], default="none",
                     help="activation checkpointing; 'full' is selected automatically when one GPU runs out of memory")
+    ap.add_argument("--no-foreach", action="store_true",
+                    help="SkipStepAdamWConfig(foreach=False): the reference's own single-tensor update, without the "
+                         "multi-tensor temporaries; selected automatically as the last attempt on one GPU")
     return ap.parse_args()
+
+
+class _OverBudget(RuntimeError):
+    pass
 
 
 def _free_port() -> int:
@@ -144,6 +151,11 @@ def main() -> None:
     if "baseline/_ref" not in olmo_core.__file__.replace(os.sep, "/"):
         _unavailable(f"'olmo_core' resolved to {olmo_core.__file__}, not to the reference install under baseline/_ref")
 
+    # Wall-clock budget of the whole arm, restarts included. A box with several GPUs is running a sweep over N with a
+    # limit of 870 s per run; a one-GPU box runs this arm alone with a longer limit.
+    chain_t0 = float(os.environ.setdefault("OCB_REF_T0", repr(time.time())))
+    time_budget_s = float(os.environ.get("OCB_BENCH_TIME_BUDGET_S", 845 if torch.cuda.device_count() > 1 else 1700))
+
     prepare_training_environment(seed=1234)
     rank = dist.get_rank()
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -165,7 +177,7 @@ def main() -> None:
     tm_config = TransformerTrainModuleConfig(
         rank_microbatch_size=args.micro_batch * args.seq_len,
         max_sequence_length=args.seq_len,
-        optim=SkipStepAdamWConfig(lr=3e-4, weight_decay=0.1, betas=(0.9, 0.95),
+        optim=SkipStepAdamWConfig(lr=3e-4, weight_decay=0.1, betas=(0.9, 0.95), foreach=not args.no_foreach,
                                   group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
         compile_model=not args.no_compile,
         dp_config=TransformerDataParallelConfig(name=DataParallelType.fsdp, param_dtype=DType.bfloat16,
@@ -223,6 +235,9 @@ def main() -> None:
         """Brackets steps ``warmup+1 .. warmup+steps`` with barrier + synchronize and CUDA events."""
 
         def pre_step(self, batch):
+            if self.step == 2 and total_steps > 4:
+                torch.cuda.synchronize()
+                result["probe_t0"] = time.perf_counter()
             if self.step == args.warmup + 1:
                 dist.barrier()
                 torch.cuda.synchronize()
@@ -234,6 +249,17 @@ def main() -> None:
                 result["start"].record()
 
         def post_step(self):
+            if self.step == 2 and "probe_t0" in result:
+                # Project the end of the run from the second step (the first one includes compilation). A run that
+                # cannot end inside the time budget stops here with an `unavailable` line instead of being killed
+                # at the limit, which would also end whatever the caller runs after this arm.
+                torch.cuda.synchronize()
+                step_s = time.perf_counter() - result.pop("probe_t0")
+                projected = torch.tensor([time.time() - chain_t0 + step_s * (total_steps - 2) + 10.0], device=device)
+                dist.all_reduce(projected, op=dist.ReduceOp.MAX)
+                if projected.item() > time_budget_s:
+                    raise _OverBudget(f"{step_s:.1f} s per step, projected {projected.item():.0f} s for "
+                                      f"{total_steps} steps")
             if self.step == args.warmup + args.steps:
                 result["end"].record()
                 dist.barrier()
@@ -254,6 +280,13 @@ def main() -> None:
         train_module, SyntheticLoader())
     try:
         trainer.fit()
+    except _OverBudget as e:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": (
+                f"the reference runs this config (activation_checkpointing={args.ac}, foreach={not args.no_foreach}) "
+                f"but too slowly for the time budget of {time_budget_s:.0f} s per run: {e}")}), flush=True)
+        sys.stdout.flush()
+        os._exit(0)
     except torch.OutOfMemoryError as e:
         if world == 1 and args.ac == "none":
             # fp32 parameters, gradients and Adam moments of 7.3 B parameters take 117 GB unsharded; with the activations
@@ -262,6 +295,12 @@ def main() -> None:
             print("reference ran out of memory on one GPU; retrying with full activation checkpointing", flush=True)
             sys.stdout.flush()
             os.execv(sys.executable, [sys.executable] + sys.argv + ["--ac", "full"])
+        if world == 1 and not args.no_foreach:
+            # Last attempt: the multi-tensor AdamW update allocates temporaries as large as the parameters; the
+            # reference's own foreach=False option updates one tensor at a time.
+            print("reference ran out of memory again; retrying with SkipStepAdamWConfig(foreach=False)", flush=True)
+            sys.stdout.flush()
+            os.execv(sys.executable, [sys.executable] + sys.argv + ["--no-foreach"])
         _unavailable(f"reference ran out of device memory on this config: {e}")
         return
 
@@ -280,7 +319,7 @@ def main() -> None:
             "config": {"model": args.model, "n_layers": model_config.n_layers, "global_batch": seqs * world,
                        "seq_len": seq_len, "micro_batch": args.micro_batch, "parallelism": f"fsdp{world}",
                        "optimizer": "SkipStepAdamW, clip 1.0", "attention_backend": str(backend),
-                       "compile_model": not args.no_compile, "activation_checkpointing": args.ac,
+                       "compile_model": not args.no_compile, "activation_checkpointing": args.ac, "foreach": not args.no_foreach,
                        "l2": "working set per step is far larger than the 126 MB L2"},
             "clocks": result["clocks"],
             "e2e": {"value": tokens_per_step * args.steps / (ms[1].item() / 1e3), "unit": "tokens/s",
