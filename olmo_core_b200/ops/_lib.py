@@ -37,6 +37,13 @@ class KernelError(RuntimeError):
 _SIGS = {
     "ocb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                       c_int, c_int, c_void_p, c_void_p],
+    "ocb_gemm_bf16_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                           c_int, c_int, c_void_p, c_void_p],
+    "ocb_gemm_set_pair_mode": [c_int],
+    "ocb_gemm_swiglu_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                            c_longlong, c_void_p, c_void_p],
+    "ocb_gemm_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                            c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
     "ocb_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
                               c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "ocb_gemm_bf16_tp": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,

@@ -676,11 +676,30 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 using namespace ocb;
 
+extern "C" int ocb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status,
+                                  cudaStream_t stream);
+
+// Which kernel serves ocb_gemm_bf16: 1 = CTA pairs (gemm_pair_sm100.cu) whenever the problem fills at least one wave of
+// 256 x 256 pair tiles, 0 = always the one-CTA-per-tile kernel of this file. Initial value from OCB_GEMM_PAIR (default 1).
+static int g_pair_mode = [] {
+  const char* v = getenv("OCB_GEMM_PAIR");
+  return (v == nullptr || v[0] != '0') ? 1 : 0;
+}();
+extern "C" int ocb_gemm_set_pair_mode(int mode) {
+  const int old = g_pair_mode;
+  g_pair_mode = mode ? 1 : 0;
+  return old;
+}
+
 // Returns 0 on success, negative on a host-side failure (bad argument, tensor-map error, launch error).
 extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                              long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status,
                              cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (g_pair_mode && epilogue <= EPI_BF16_ACC &&
+      static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= num_sms() / 2)
+    return ocb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, status, stream);
   if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -1;
   CUtensorMap ta, tb;
