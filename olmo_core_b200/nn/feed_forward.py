@@ -20,7 +20,7 @@ import torch.nn.functional as F
 from ..config import DType, StrEnum
 from ..exceptions import OLMoConfigurationError
 from ..ops.elementwise import swiglu
-from ..ops.gemm import linear, multi_linear
+from ..ops.gemm import linear, multi_linear, swiglu_mlp
 from .config import ModuleConfig
 from .layer_norm import l2_normalize
 
@@ -134,6 +134,11 @@ class FeedForward(nn.Module):
         self.w3 = _Proj(d_model, hidden_size, bias, dtype, init_device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if (self.activation == ActivationFunction.silu and x.is_cuda and self.w1.bias is None
+                and all(getattr(w, "float8", None) is None for w in (self.w1, self.w2, self.w3))):
+            y = swiglu_mlp(x, self.w1.weight, self.w3.weight, self.w2.weight)  # activation inside the GEMM epilogues
+            if y is not None:
+                return y
         a, b = multi_linear(x, (self.w1, self.w3))  # one saved input, input gradients summed in the GEMM epilogue
         if self.activation == ActivationFunction.silu:
             return self.w2(swiglu(a, b))

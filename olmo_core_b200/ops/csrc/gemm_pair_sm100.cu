@@ -46,7 +46,8 @@ constexpr int STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGING_BYTES = 4 * 2 * 32 * 128;  // four epilogue warps, two 32-row x 128-byte buffers each
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
@@ -135,16 +136,114 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gm;
 }
 
-__device__ __forceinline__ float silu_f(float a) { return a / (1.f + __expf(-a)); }
+
+// ---- epilogue staging ------------------------------------------------------------------------------------------------
+constexpr int STG_BYTES = 32 * 128;  // one warp's 32 rows x 128 bytes
+enum : int { ST_PLAIN = 0, ST_BF16_ADD = 1, ST_F32_ADD = 2 };
+
+// 16-byte slot `chunk` (0..7) of staged row `row` (0..31); the XOR keeps both the row-per-thread and the
+// 8-lanes-per-row access patterns free of bank conflicts.
+__device__ __forceinline__ uint4* stg_slot(uint8_t* stg, int row, int chunk) {
+  return reinterpret_cast<uint4*>(stg + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Moves a staged block to global memory: 8 lanes cover the 128 bytes of one row, 4 rows per instruction.
+// gbase: address of (first row, first byte); valid_bytes per row may be short of 128 at the matrix edge (a multiple of
+// the element size). MODE adds to what is in memory (bf16: read-modify-write; fp32: reductions performed in L2).
+template <int MODE>
+__device__ __forceinline__ void stg_store(uint8_t* stg, uint8_t* gbase, long long ld_bytes, int rows_valid, int valid_bytes,
+                                          int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    if (rr >= rows_valid || cc * 16 >= valid_bytes) continue;
+    const uint4 v = *stg_slot(stg, rr, cc);
+    uint8_t* dst = gbase + rr * ld_bytes + cc * 16;
+    if (cc * 16 + 16 <= valid_bytes) {
+      if (MODE == ST_PLAIN) {
+        *reinterpret_cast<uint4*>(dst) = v;
+      } else if (MODE == ST_F32_ADD) {
+        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v.x)),
+                     "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                     : "memory");
+      } else {
+        const uint4 old = *reinterpret_cast<const uint4*>(dst);
+        const uint32_t nw[4] = {v.x, v.y, v.z, v.w}, ow[4] = {old.x, old.y, old.z, old.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16x2(nw[j]), b = unpack_bf16x2(ow[j]);
+          o[j] = pack_bf16x2(a.x + b.x, a.y + b.y);
+        }
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    } else {
+      // ragged end of a row: element by element
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      if (MODE == ST_F32_ADD) {
+        for (int j = 0; j < 4 && cc * 16 + 4 * j < valid_bytes; ++j) atomicAdd(reinterpret_cast<float*>(dst) + j, __uint_as_float(w[j]));
+      } else {
+        for (int j = 0; j < 8 && cc * 16 + 2 * j < valid_bytes; ++j) {
+          // (fp32 plain stores reach here with 4-byte elements: two 2-byte halves per element, both inside valid_bytes)
+          uint16_t e = (j & 1) ? static_cast<uint16_t>(w[j >> 1] >> 16) : static_cast<uint16_t>(w[j >> 1] & 0xffffu);
+          if (MODE == ST_BF16_ADD) {
+            const __nv_bfloat16 old = reinterpret_cast<const __nv_bfloat16*>(dst)[j];
+            const __nv_bfloat16 nv = __float2bfloat16_rn(__bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&e)) + __bfloat162float(old));
+            e = *reinterpret_cast<const uint16_t*>(&nv);
+          }
+          reinterpret_cast<uint16_t*>(dst)[j] = e;
+        }
+      }
+    }
+  }
+}
+
+// The reverse for two blocks at once (the a and b chunks of the gated-MLP backward): 32 x 128 bytes of global memory each
+// into a staging buffer, zeros where the matrix ends.
+__device__ __forceinline__ uint4 load_16b_edge(const uint8_t* src, int bytes_left) {
+  if (bytes_left >= 16) return __ldg(reinterpret_cast<const uint4*>(src));
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
+  for (int j = 0; j < 8 && 2 * j < bytes_left; ++j)
+    w[j >> 1] |= static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(src)[j]) << ((j & 1) * 16);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+// Issues the sixteen loads of a lane (a and b chunk); ab_stash moves them into the staging buffers later, so other work
+// can be placed between the two.
+__device__ __forceinline__ void ab_fetch(uint4 (&va)[8], uint4 (&vb)[8], const uint8_t* ga, const uint8_t* gb,
+                                         long long ld_bytes, int rows_valid, int valid_bytes, int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    va[i] = make_uint4(0u, 0u, 0u, 0u);
+    vb[i] = va[i];
+    if (rr < rows_valid && cc * 16 < valid_bytes) {
+      const long long off = rr * ld_bytes + cc * 16;
+      va[i] = load_16b_edge(ga + off, valid_bytes - cc * 16);
+      vb[i] = load_16b_edge(gb + off, valid_bytes - cc * 16);
+    }
+  }
+}
+__device__ __forceinline__ void ab_stash(const uint4 (&va)[8], const uint4 (&vb)[8], uint8_t* stg_a, uint8_t* stg_b, int lane) {
+  const int cc = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    *stg_slot(stg_a, rr, cc) = va[i];
+    *stg_slot(stg_b, rr, cc) = vb[i];
+  }
+}
+
+__device__ __forceinline__ float silu_f(float a) { return __fdividef(a, 1.f + __expf(-a)); }
 
 template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const Params p) {
-  constexpr bool kFused = EPI == EPI_SWIGLU_FWD || EPI == EPI_SWIGLU_BWD;
   constexpr int TILE_N = EPI == EPI_SWIGLU_FWD ? BNH : BN;  // columns of p.N one pair tile covers
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_STAGING_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -271,11 +370,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // A thread owns one accumulator row (tcgen05.ld 32x32b). Writing rows straight to memory would make every warp
+    // store touch 32 different lines, so each warp turns its 32 x 128-byte block through two staging buffers in shared
+    // memory (16-byte slots, XOR-swizzled by row) and moves it to / from global memory with 8 lanes per 128-byte line.
     const int quad = warp & 3;
+    uint8_t* stg0 = smem + STAGES * STAGE_BYTES + (warp - 2) * (2 * STG_BYTES);
+    uint8_t* stg1 = stg0 + STG_BYTES;
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty_bar[0]), 0);
-    const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty_bar[1]), 0);
     bool ok = true;
     int it = 0;
+    uint4 va[8], vb[8];  // EPI_SWIGLU_BWD: the a | b chunk requested ahead of its use
+    if (EPI == EPI_SWIGLU_BWD && pair < num_tiles) {
+      int tm, tn;
+      tile_coords(pair, tiles_m, tiles_n, p.group_m, tm, tn);
+      const int frow0 = tm * (2 * BM) + static_cast<int>(cta) * BM + quad * 32, fh0 = tn * BN;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.AB) + (static_cast<long long>(frow0) * p.ldab + fh0) * 2;
+      ab_fetch(va, vb, src, src + static_cast<long long>(p.H) * 2, p.ldab * 2, min(32, p.M - frow0), min(64, p.N - fh0) * 2, lane);
+    }
     for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -285,185 +396,184 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
-      const int row = tm * (2 * BM) + static_cast<int>(cta) * BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row0 = tm * (2 * BM) + static_cast<int>(cta) * BM + quad * 32;  // first row of this warp
+      const int rows_valid = min(32, p.M - row0);                               // <= 0: nothing to store
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      if (!kFused) {
+      // hands the accumulator back to the MMA issuer as soon as its last column has been read into registers
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader0 + acc * 8);
+      };
+      if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
         const int n0 = tn * BN;
+        uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(row0) * p.ldc + n0) * 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          if (c == BN / 64 - 1) release_acc();
+          const int cols_valid = min(64, p.N - (n0 + c * 64));
+          if (rows_valid <= 0 || cols_valid <= 0) continue;
+          uint8_t* stg = (c & 1) ? stg1 : stg0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            *stg_slot(stg, lane, v) = make_uint4(pack_bf16x2(__uint_as_float(r0[8 * v + 0]), __uint_as_float(r0[8 * v + 1])),
+                                                 pack_bf16x2(__uint_as_float(r0[8 * v + 2]), __uint_as_float(r0[8 * v + 3])),
+                                                 pack_bf16x2(__uint_as_float(r0[8 * v + 4]), __uint_as_float(r0[8 * v + 5])),
+                                                 pack_bf16x2(__uint_as_float(r0[8 * v + 6]), __uint_as_float(r0[8 * v + 7])));
+            *stg_slot(stg, lane, 4 + v) = make_uint4(pack_bf16x2(__uint_as_float(r1[8 * v + 0]), __uint_as_float(r1[8 * v + 1])),
+                                                     pack_bf16x2(__uint_as_float(r1[8 * v + 2]), __uint_as_float(r1[8 * v + 3])),
+                                                     pack_bf16x2(__uint_as_float(r1[8 * v + 4]), __uint_as_float(r1[8 * v + 5])),
+                                                     pack_bf16x2(__uint_as_float(r1[8 * v + 6]), __uint_as_float(r1[8 * v + 7])));
+          }
+          __syncwarp();
+          stg_store<EPI == EPI_BF16_ACC ? ST_BF16_ADD : ST_PLAIN>(stg, c_base + c * 128, p.ldc * 2, rows_valid, cols_valid * 2, lane);
+          // the other buffer serves the next chunk; this one is rewritten two chunks later, after the syncwarp above
+        }
+        __syncwarp();
+      } else if (EPI == EPI_F32 || EPI == EPI_F32_ACC) {
+        const int n0 = tn * BN;
+        uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(row0) * p.ldc + n0) * 4;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
-          const int col = n0 + c * 32;
-          if (!row_ok || col >= p.N) continue;
-          if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-            if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          if (c == BN / 32 - 1) release_acc();
+          const int cols_valid = min(32, p.N - (n0 + c * 32));
+          if (rows_valid <= 0 || cols_valid <= 0) continue;
+          uint8_t* stg = (c & 1) ? stg1 : stg0;
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 o;
-                if (EPI == EPI_BF16_ACC) {
-                  const uint4 old = reinterpret_cast<const uint4*>(dst)[v];
-                  const float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
-                               a3 = unpack_bf16x2(old.w);
-                  o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) + a0.x, __uint_as_float(r[8 * v + 1]) + a0.y);
-                  o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) + a1.x, __uint_as_float(r[8 * v + 3]) + a1.y);
-                  o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) + a2.x, __uint_as_float(r[8 * v + 5]) + a2.y);
-                  o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) + a3.x, __uint_as_float(r[8 * v + 7]) + a3.y);
-                } else {
-                  o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                  o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                  o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                  o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                }
-                reinterpret_cast<uint4*>(dst)[v] = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (col + j < p.N) {
-                  float v = __uint_as_float(r[j]);
-                  if (EPI == EPI_BF16_ACC) v += __bfloat162float(dst[j]);
-                  dst[j] = __float2bfloat16_rn(v);
-                }
-              }
-            }
-          } else {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-            if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
-                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                if (EPI == EPI_F32_ACC) {
-                  const float4 old = reinterpret_cast<const float4*>(dst)[v];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                reinterpret_cast<float4*>(dst)[v] = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (col + j < p.N) {
-                  float v = __uint_as_float(r[j]);
-                  if (EPI == EPI_F32_ACC) v += dst[j];
-                  dst[j] = v;
-                }
-              }
-            }
-          }
+          for (int v = 0; v < 8; ++v) *stg_slot(stg, lane, v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+          __syncwarp();
+          stg_store<EPI == EPI_F32_ACC ? ST_F32_ADD : ST_PLAIN>(stg, c_base + c * 128, p.ldc * 4, rows_valid, cols_valid * 4, lane);
         }
+        __syncwarp();
       } else if (EPI == EPI_SWIGLU_FWD) {
         // accumulator columns [0,128): a for H-columns tn*128.., [128,256): b for the same columns
         const int h0 = tn * BNH;
-        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
-        __nv_bfloat16* h_row = reinterpret_cast<__nv_bfloat16*>(p.C2) + static_cast<long long>(row) * p.ldc2;
+        uint8_t* a_base = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(row0) * p.ldc + h0) * 2;
+        uint8_t* b_base = a_base + static_cast<long long>(p.H) * 2;
+        uint8_t* h_base = reinterpret_cast<uint8_t*>(p.C2) + (static_cast<long long>(row0) * p.ldc2 + h0) * 2;
 #pragma unroll 1
-        for (int c = 0; c < BNH / 16; ++c) {
-          uint32_t ra[16], rb[16];
-          tmem_ld_32x16(t_row + c * 16, ra);
-          tmem_ld_32x16(t_row + BNH + c * 16, rb);
-          tmem_ld_wait();
-          const int col = h0 + c * 16;
-          if (!row_ok || col >= p.N) continue;
-          uint32_t oa[8], ob[8], oh[8];
+        for (int c = 0; c < BNH / 64; ++c) {
+          uint32_t oh[32];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            // a and b are rounded to bf16 first so that h is exactly what the backward pass recomputes from them
-            oa[j] = pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
-            ob[j] = pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
-            const float2 fa = unpack_bf16x2(oa[j]), fb = unpack_bf16x2(ob[j]);
-            oh[j] = pack_bf16x2(silu_f(fa.x) * fb.x, silu_f(fa.y) * fb.y);
-          }
-          if (col + 16 <= p.N) {
-            uint4* da = reinterpret_cast<uint4*>(c_row + col);
-            uint4* db = reinterpret_cast<uint4*>(c_row + p.H + col);
-            uint4* dh = reinterpret_cast<uint4*>(h_row + col);
-            da[0] = make_uint4(oa[0], oa[1], oa[2], oa[3]); da[1] = make_uint4(oa[4], oa[5], oa[6], oa[7]);
-            db[0] = make_uint4(ob[0], ob[1], ob[2], ob[3]); db[1] = make_uint4(ob[4], ob[5], ob[6], ob[7]);
-            dh[0] = make_uint4(oh[0], oh[1], oh[2], oh[3]); dh[1] = make_uint4(oh[4], oh[5], oh[6], oh[7]);
-          } else {
-            for (int j = 0; j < 16 && col + j < p.N; ++j) {
-              const uint32_t wa = oa[j >> 1], wb = ob[j >> 1], wh = oh[j >> 1];
-              const uint16_t sa16 = (j & 1) ? (wa >> 16) : (wa & 0xffffu), sb16 = (j & 1) ? (wb >> 16) : (wb & 0xffffu),
-                             sh16 = (j & 1) ? (wh >> 16) : (wh & 0xffffu);
-              reinterpret_cast<uint16_t*>(c_row)[col + j] = sa16;
-              reinterpret_cast<uint16_t*>(c_row)[p.H + col + j] = sb16;
-              reinterpret_cast<uint16_t*>(h_row)[col + j] = sh16;
+          for (int half = 0; half < 2; ++half) {
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32(t_row + c * 64 + half * 32, ra);
+            tmem_ld_32x32(t_row + BNH + c * 64 + half * 32, rb);
+            tmem_ld_wait();
+            if (c == BNH / 64 - 1 && half == 1) release_acc();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t wa[4], wb[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                // a and b are rounded to bf16 first so that h is exactly what the backward pass recomputes from them
+                wa[j] = pack_bf16x2(__uint_as_float(ra[8 * v + 2 * j]), __uint_as_float(ra[8 * v + 2 * j + 1]));
+                wb[j] = pack_bf16x2(__uint_as_float(rb[8 * v + 2 * j]), __uint_as_float(rb[8 * v + 2 * j + 1]));
+                const float2 fa = unpack_bf16x2(wa[j]), fb = unpack_bf16x2(wb[j]);
+                oh[half * 16 + v * 4 + j] = pack_bf16x2(silu_f(fa.x) * fb.x, silu_f(fa.y) * fb.y);
+              }
+              *stg_slot(stg0, lane, half * 4 + v) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+              *stg_slot(stg1, lane, half * 4 + v) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
             }
           }
+          const int cols_valid = min(64, p.N - (h0 + c * 64));
+          const bool live = rows_valid > 0 && cols_valid > 0;
+          __syncwarp();
+          if (live) {
+            stg_store<ST_PLAIN>(stg0, a_base + c * 128, p.ldc * 2, rows_valid, cols_valid * 2, lane);
+            stg_store<ST_PLAIN>(stg1, b_base + c * 128, p.ldc * 2, rows_valid, cols_valid * 2, lane);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int v = 0; v < 8; ++v) *stg_slot(stg0, lane, v) = make_uint4(oh[4 * v], oh[4 * v + 1], oh[4 * v + 2], oh[4 * v + 3]);
+          __syncwarp();
+          if (live) stg_store<ST_PLAIN>(stg0, h_base + c * 128, p.ldc2 * 2, rows_valid, cols_valid * 2, lane);
+          __syncwarp();
         }
       } else {
-        // EPI_SWIGLU_BWD: the accumulator is dh for H-columns tn*256..; a | b come from memory
+        // EPI_SWIGLU_BWD: the accumulator is dh for H-columns tn*256..; a | b come from memory. Their loads do not
+        // depend on the accumulator: the first chunk was requested before the wait above, and every further chunk is
+        // requested before the stores of the chunk in front of it.
         const int h0 = tn * BN;
-        const __nv_bfloat16* ab_row = reinterpret_cast<const __nv_bfloat16*>(p.AB) + static_cast<long long>(row) * p.ldab;
-        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
-        __nv_bfloat16* h_row = p.C2 == nullptr ? nullptr
-                                               : reinterpret_cast<__nv_bfloat16*>(p.C2) + static_cast<long long>(row) * p.ldc2;
+        uint8_t* da_base = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(row0) * p.ldc + h0) * 2;
+        uint8_t* db_base = da_base + static_cast<long long>(p.H) * 2;
+        uint8_t* h_base = p.C2 == nullptr ? nullptr
+                                          : reinterpret_cast<uint8_t*>(p.C2) + (static_cast<long long>(row0) * p.ldc2 + h0) * 2;
 #pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-          uint32_t rd[16];
-          tmem_ld_32x16(t_row + c * 16, rd);
-          const int col = h0 + c * 16;
-          const bool live = row_ok && col < p.N;
-          uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
-          const bool vec = col + 16 <= p.N;
-          if (live && vec) {
-            a0 = __ldg(reinterpret_cast<const uint4*>(ab_row + col));
-            a1 = __ldg(reinterpret_cast<const uint4*>(ab_row + col) + 1);
-            b0 = __ldg(reinterpret_cast<const uint4*>(ab_row + p.H + col));
-            b1 = __ldg(reinterpret_cast<const uint4*>(ab_row + p.H + col) + 1);
-          }
-          tmem_ld_wait();
-          if (!live) continue;
-          uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-          uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-          if (!vec) {
-            for (int j = 0; j < 16; ++j) {
-              uint32_t ea = 0, eb = 0;
-              if (col + j < p.N) {
-                ea = reinterpret_cast<const uint16_t*>(ab_row)[col + j];
-                eb = reinterpret_cast<const uint16_t*>(ab_row)[p.H + col + j];
-              }
-              if (j & 1) { wa[j >> 1] |= ea << 16; wb[j >> 1] |= eb << 16; }
-              else { wa[j >> 1] = ea; wb[j >> 1] = eb; }
-            }
-          }
-          uint32_t oda[8], odb[8], oh[8];
+        for (int c = 0; c < BN / 64; ++c) {
+          const int cols_valid = min(64, p.N - (h0 + c * 64));
+          const bool live = rows_valid > 0 && cols_valid > 0;
+          ab_stash(va, vb, stg0, stg1, lane);
+          uint32_t oh[32];
+          __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float2 fa = unpack_bf16x2(wa[j]), fb = unpack_bf16x2(wb[j]);
-            const float d0 = __uint_as_float(rd[2 * j]), d1 = __uint_as_float(rd[2 * j + 1]);
-            const float s0 = 1.f / (1.f + __expf(-fa.x)), s1 = 1.f / (1.f + __expf(-fa.y));
-            const float si0 = fa.x * s0, si1 = fa.y * s1;  // silu(a)
-            // d silu(a) / da = s (1 + a (1 - s))
-            oda[j] = pack_bf16x2(d0 * fb.x * s0 * (1.f + fa.x * (1.f - s0)), d1 * fb.y * s1 * (1.f + fa.y * (1.f - s1)));
-            odb[j] = pack_bf16x2(d0 * si0, d1 * si1);
-            oh[j] = pack_bf16x2(si0 * fb.x, si1 * fb.y);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t rd[32];
+            tmem_ld_32x32(t_row + c * 64 + half * 32, rd);
+            tmem_ld_wait();
+            if (c == BN / 64 - 1 && half == 1) release_acc();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4* sa = stg_slot(stg0, lane, half * 4 + v);
+              uint4* sb = stg_slot(stg1, lane, half * 4 + v);
+              const uint4 xa = *sa, xb = *sb;
+              const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
+              uint32_t oda[4], odb[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 fa = unpack_bf16x2(wa[j]), fb = unpack_bf16x2(wb[j]);
+                const float d0 = __uint_as_float(rd[8 * v + 2 * j]), d1 = __uint_as_float(rd[8 * v + 2 * j + 1]);
+                const float s0 = __fdividef(1.f, 1.f + __expf(-fa.x)), s1 = __fdividef(1.f, 1.f + __expf(-fa.y));
+                const float si0 = fa.x * s0, si1 = fa.y * s1;  // silu(a)
+                // d silu(a) / da = s (1 + a (1 - s))
+                oda[j] = pack_bf16x2(d0 * fb.x * s0 * (1.f + fa.x * (1.f - s0)), d1 * fb.y * s1 * (1.f + fa.y * (1.f - s1)));
+                odb[j] = pack_bf16x2(d0 * si0, d1 * si1);
+                oh[half * 16 + v * 4 + j] = pack_bf16x2(si0 * fb.x, si1 * fb.y);
+              }
+              *sa = make_uint4(oda[0], oda[1], oda[2], oda[3]);  // in place: the slot belongs to this thread's row
+              *sb = make_uint4(odb[0], odb[1], odb[2], odb[3]);
+            }
           }
-          if (vec) {
-            uint4* da = reinterpret_cast<uint4*>(c_row + col);
-            uint4* db = reinterpret_cast<uint4*>(c_row + p.H + col);
-            da[0] = make_uint4(oda[0], oda[1], oda[2], oda[3]); da[1] = make_uint4(oda[4], oda[5], oda[6], oda[7]);
-            db[0] = make_uint4(odb[0], odb[1], odb[2], odb[3]); db[1] = make_uint4(odb[4], odb[5], odb[6], odb[7]);
-            if (h_row != nullptr) {
-              uint4* dh = reinterpret_cast<uint4*>(h_row + col);
-              dh[0] = make_uint4(oh[0], oh[1], oh[2], oh[3]); dh[1] = make_uint4(oh[4], oh[5], oh[6], oh[7]);
+          __syncwarp();
+          // request the next chunk (of this tile, or the first one of this CTA's next tile) before storing this one
+          {
+            int nrow0 = row0, nh0 = h0 + (c + 1) * 64;
+            bool more = true;
+            if (c == BN / 64 - 1) {
+              const int ntile = tile + num_pairs;
+              more = ntile < num_tiles;
+              if (more) {
+                int ntm, ntn;
+                tile_coords(ntile, tiles_m, tiles_n, p.group_m, ntm, ntn);
+                nrow0 = ntm * (2 * BM) + static_cast<int>(cta) * BM + quad * 32;
+                nh0 = ntn * BN;
+              }
             }
-          } else {
-            for (int j = 0; j < 16 && col + j < p.N; ++j) {
-              const uint32_t xa = oda[j >> 1], xb = odb[j >> 1], xh = oh[j >> 1];
-              reinterpret_cast<uint16_t*>(c_row)[col + j] = (j & 1) ? (xa >> 16) : (xa & 0xffffu);
-              reinterpret_cast<uint16_t*>(c_row)[p.H + col + j] = (j & 1) ? (xb >> 16) : (xb & 0xffffu);
-              if (h_row != nullptr) reinterpret_cast<uint16_t*>(h_row)[col + j] = (j & 1) ? (xh >> 16) : (xh & 0xffffu);
-            }
+            const int nrows = more ? min(32, p.M - nrow0) : 0, ncols = min(64, p.N - nh0);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.AB) + (static_cast<long long>(nrow0) * p.ldab + nh0) * 2;
+            ab_fetch(va, vb, src, src + static_cast<long long>(p.H) * 2, p.ldab * 2, ncols > 0 ? nrows : 0, ncols * 2, lane);
+          }
+          if (live) {
+            stg_store<ST_PLAIN>(stg0, da_base + c * 128, p.ldc * 2, rows_valid, cols_valid * 2, lane);
+            stg_store<ST_PLAIN>(stg1, db_base + c * 128, p.ldc * 2, rows_valid, cols_valid * 2, lane);
+          }
+          __syncwarp();
+          if (h_base != nullptr) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) *stg_slot(stg0, lane, v) = make_uint4(oh[4 * v], oh[4 * v + 1], oh[4 * v + 2], oh[4 * v + 3]);
+            __syncwarp();
+            if (live) stg_store<ST_PLAIN>(stg0, h_base + c * 128, p.ldc2 * 2, rows_valid, cols_valid * 2, lane);
+            __syncwarp();
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc == 0 ? tempty_leader0 : tempty_leader1);
     }
   }
 

@@ -697,7 +697,9 @@ extern "C" int ocb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
                              long long ldc, int a_mn_major, int b_mn_major, int epilogue, int* status,
                              cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (g_pair_mode && epilogue <= EPI_BF16_ACC &&
+  // the pair kernel moves its output in 16-byte pieces
+  const long long c_elem = (epilogue == EPI_BF16 || epilogue == EPI_BF16_ACC) ? 2 : 4;
+  if (g_pair_mode && epilogue <= EPI_BF16_ACC && (ldc * c_elem) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= num_sms() / 2)
     return ocb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, status, stream);
   if ((lda % 8) != 0 || (ldb % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))

@@ -20,7 +20,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gemm", "linear", "LinearFunction", "compute_weight"]
+__all__ = ["gemm", "linear", "LinearFunction", "compute_weight", "swiglu_mlp", "stacked_pair"]
 
 
 def _row_stride(t: torch.Tensor) -> int:
@@ -300,3 +300,104 @@ def multi_linear(x: torch.Tensor, projections) -> tuple:
     if not plain:
         return tuple(p(x) for p in projections)
     return MultiLinearFunction.apply(x, *[p.weight for p in projections])
+
+
+# ------------------------------------------------------------------------------------------------------
+# Gated MLP with the activation inside the GEMM epilogues
+# ------------------------------------------------------------------------------------------------------
+
+
+def stacked_pair(first: torch.Tensor, second: torch.Tensor) -> Optional[torch.Tensor]:
+    """
+    ``[first; second]`` as ONE matrix without copying, when the two equally shaped row-major matrices sit back to back
+    in memory (the sharded-parameter runtime lays out ``w1`` / ``w3`` of a gated MLP, and their gradient buffers, that
+    way). ``None`` when they do not.
+    """
+    if (first.shape != second.shape or first.dtype != second.dtype or first.dim() != 2 or not first.is_contiguous()
+            or not second.is_contiguous() or first.device != second.device
+            or second.data_ptr() != first.data_ptr() + first.numel() * first.element_size()):
+        return None
+    if first.untyped_storage().data_ptr() != second.untyped_storage().data_ptr():
+        return None
+    rows, cols = first.shape
+    return first.as_strided((2 * rows, cols), (cols, 1), first.storage_offset())
+
+
+class SwiGLUMLPFunction(torch.autograd.Function):
+    """
+    ``y = (silu(x W1^T) * (x W3^T)) W2^T`` in three GEMM launches forward and four backward, with no element-wise
+    kernel in between (reference: src/olmo_core/nn/feed_forward.py:161-171 runs three GEMMs, ``silu`` and a product):
+
+    * forward: one GEMM over ``[W1; W3]`` whose epilogue stores ``a | b`` and ``h = silu(a) * b``; ``y = h W2^T``;
+    * backward: ``dh = dy W2`` goes through the activation in the epilogue (``da | db`` stored, ``dh`` never is);
+      ``dx = [da | db] [W1; W3]`` and ``d[W1; W3] += [da | db]^T x`` are one GEMM each; ``dW2 += dy^T h``.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, w3, w2):  # type: ignore[override]
+        w13 = stacked_pair(w1._lowp, w3._lowp)
+        w2l = w2._lowp
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M, K = x2.shape
+        H = w1.shape[0]
+        ab = torch.empty((M, 2 * H), dtype=torch.bfloat16, device=x2.device)
+        h = torch.empty((M, H), dtype=torch.bfloat16, device=x2.device)
+        rc = _lib.lib().ocb_gemm_swiglu_fwd(x2.data_ptr(), w13.data_ptr(), ab.data_ptr(), h.data_ptr(), M, H, K, K, K, 2 * H,
+                                            H, _lib.status_buffer(x2.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "ocb_gemm_swiglu_fwd")
+        y = gemm(h, w2l, trans_b=True)
+        ctx.save_for_backward(x2, ab, h, w13, w2l)
+        ctx.weight_refs = (w1, w3, w2)
+        ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
+        return y.view(*x.shape[:-1], w2l.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x2, ab, h, w13, w2l = ctx.saved_tensors
+        w1, w3, w2 = ctx.weight_refs
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        M, D = dy2.shape
+        H = w1.shape[0]
+        gemm(dy2, h, trans_a=True, trans_b=False, out=w2.main_grad, accumulate=True)
+        dab = torch.empty_like(ab)
+        rc = _lib.lib().ocb_gemm_swiglu_bwd(dy2.data_ptr(), w2l.data_ptr(), ab.data_ptr(), dab.data_ptr(), None, M, H, D, D, H,
+                                            2 * H, 2 * H, H, _lib.status_buffer(dy2.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "ocb_gemm_swiglu_bwd")
+        g13 = stacked_pair(w1.main_grad, w3.main_grad)
+        gemm(dab, x2, trans_a=True, trans_b=False, out=g13, accumulate=True)
+        for w in (w1, w3, w2):
+            if hasattr(w, "grad_added_to_main_grad"):
+                w.grad_added_to_main_grad = True
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dab, w13, trans_b=False).view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        return dx, None, None, None
+
+
+def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor) -> Optional[torch.Tensor]:
+    """
+    The gated MLP through :class:`SwiGLUMLPFunction`, or ``None`` when its conditions do not hold: CUDA, bf16 resident
+    copies of the three weights with ``w1`` / ``w3`` (and their fp32 gradient buffers) back to back in memory, sizes
+    that are multiples of 8. The caller then runs the projections one by one.
+    """
+    if not x.is_cuda or x.shape[-1] % 8 != 0 or w1.shape[0] % 8 != 0:
+        return None
+    for w in (w1, w3, w2):
+        lp, mg = getattr(w, "_lowp", None), getattr(w, "main_grad", None)
+        if lp is None or mg is None or lp.dtype != torch.bfloat16 or mg.dtype != torch.float32 or lp.shape != w.shape:
+            return None
+        if getattr(w, "_tp_sharded", False) or not w.requires_grad:
+            return None
+    if stacked_pair(w1._lowp, w3._lowp) is None or stacked_pair(w1.main_grad, w3.main_grad) is None:
+        return None
+    return SwiGLUMLPFunction.apply(x, w1, w3, w2)

@@ -131,6 +131,26 @@ class ShardedParamRuntime:
                     continue
                 fq = f"{mname}.{pname}" if mname else pname
                 entries.append((fq, module, p, pname))
+        # The two up-projections of a gated MLP go back to back (w1, then w3) in every flat buffer: stacked, they are one
+        # GEMM operand [w1; w3] for the kernels that apply the activation in their epilogue.
+        from ..nn.feed_forward import FeedForward
+
+        follower = {}
+        for _, module in self.model.named_modules():
+            if isinstance(module, FeedForward) and module.w1.weight.shape == module.w3.weight.shape:
+                follower[id(module.w1.weight)] = id(module.w3.weight)
+        if follower:
+            by_id = {id(e[2]): e for e in entries}
+            moved = set(follower.values())
+            ordered = []
+            for e in entries:
+                if id(e[2]) in moved:
+                    continue
+                ordered.append(e)
+                nxt = follower.get(id(e[2]))
+                if nxt is not None and nxt in by_id:
+                    ordered.append(by_id[nxt])
+            entries = ordered
         for fq, module, p, pname in entries:
             full_shape = tuple(p.shape)
             aware = _is_aware(module, pname)
