@@ -50,7 +50,11 @@ def init_tensor_(x: torch.Tensor, *, std: Optional[float], generator: Optional[t
             # Parameter owned by the sharded-parameter runtime: draw the full tensor, keep our rows.
             full = torch.zeros(shard_info.full_shape, dtype=x.dtype, device=x.device)
             fill(full)
-            x.copy_(full.narrow(0, shard_info.row_start, x.shape[0]))
+            real = max(0, min(x.shape[0], shard_info.full_shape[0] - shard_info.row_start))  # the rest is padding
+            if real > 0:
+                x[:real].copy_(full.narrow(0, shard_info.row_start, real))
+            if real < x.shape[0]:
+                x[real:].zero_()
             return
         fill(x)
 

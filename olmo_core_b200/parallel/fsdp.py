@@ -17,6 +17,18 @@ instead of the reference's per-micro-batch, per-block all-gathers and reduce-sca
 result is the same up to fp32 summation order: gradients are summed over micro-batches locally and then
 averaged over ranks.
 
+Two memory modes. *Resident* (above) costs 6 bytes per parameter on every rank regardless of the world size and is
+the fast path while that fits (a 7B model: 44 GB). *Streamed* is chosen when it would not (or with
+``OLMO_CORE_B200_FSDP_STREAMED=1``): the transformer blocks keep only this rank's rows (bf16 ``lowp_shard``, fp32
+``grad_shard``); a block's full bf16 weights are assembled into a two-slot ring one block ahead of the compute
+(``ocb_peer_gather_segments``: plain loads from the owners' memory on a side stream, or NCCL all-gather), and its
+full-size gradients leave the ring right after the block's backward (``ocb_peer_scatter_add_segments``: fp32
+reductions into the owners' shards, or NCCL reduce-scatter). Per-GPU memory then scales with 1 / world size, which is
+what a 32B model needs. Embeddings, the final norm and the LM head stay resident in both modes.
+
+Parameters whose leading dimension is not a multiple of the world size are padded (the last ranks own fewer real
+rows, the same split ``torch.chunk`` / FSDP2 use), never replicated.
+
 Parameters consumed by ops that know about the low-precision copy (dense projections, embeddings, RMSNorm
 weights, expert weights) are sharded; all others (biases, router weights, nGPT scalers, ...) are kept
 replicated in fp32 and their gradients all-reduced.
@@ -25,6 +37,7 @@ replicated in fp32 and their gradients all-reduced.
 from __future__ import annotations
 
 import logging
+import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -37,6 +50,8 @@ from ..ops import optim as optim_ops
 log = logging.getLogger(__name__)
 
 __all__ = ["ShardedParamRuntime", "ShardInfo", "ParamSlot"]
+
+STREAMED_ENV_VAR = "OLMO_CORE_B200_FSDP_STREAMED"
 
 
 @dataclass
@@ -61,6 +76,16 @@ class ParamSlot:
     full_offset: int  # offset into the flat lowp / main_grad buffers (-1 for replicated fp32-only params)
     full_numel: int
     aware: bool  # consumed through ``_lowp`` / ``main_grad`` by the ops
+    flat_numel: int = 0  # elements the full copy occupies in a flat buffer (padded rows included)
+    padded_rows: int = 0  # leading dimension rounded up to a multiple of the world size (sharded slots)
+    unit: int = -1  # streamed mode: index of the transformer block whose ring slot holds the full copy; -1 = resident
+
+    @property
+    def real_local_rows(self) -> int:
+        """Rows of this rank's shard that exist in the parameter (the rest is padding)."""
+        if not self.sharded or not self.full_shape:
+            return self.local_rows
+        return max(0, min(self.local_rows, self.full_shape[0] - self.row_start))
 
 
 def _is_aware(module: nn.Module, pname: str) -> bool:
@@ -91,8 +116,10 @@ class ShardedParamRuntime:
         reduce_dtype: torch.dtype = torch.float32,
         shard: bool = True,
         device: Optional[torch.device] = None,
+        streamed: Optional[bool] = None,
     ):
         self.model = model
+        self._streamed_request = streamed
         self.replicate_group: Optional[dist.ProcessGroup] = None
         if group is not None and hasattr(group, "mesh_dim_names") and getattr(group, "ndim", 1) == 2:
             self.replicate_group = group.get_group(0)
@@ -113,6 +140,9 @@ class ShardedParamRuntime:
         self.grad_shard: Optional[torch.Tensor] = None
         self._first_microbatch = True
         self._materialized = False
+        self.streamed = False
+        self.units: List[List[ParamSlot]] = []
+        self.lowp_shard: Optional[torch.Tensor] = None
         self._plan()
 
     # ------------------------------------------------------------------------------------------------
@@ -151,32 +181,76 @@ class ShardedParamRuntime:
                 if nxt is not None and nxt in by_id:
                     ordered.append(by_id[nxt])
             entries = ordered
+        # Streamed mode: the parameters of transformer block i form unit i; their full copies live in a ring slot.
+        unit_of: Dict[int, int] = {}
+        blocks = getattr(self.model, "blocks", None)
+        if self._want_streamed(entries) and blocks is not None and len(blocks) >= 2:
+            for i, block in enumerate(blocks.values() if hasattr(blocks, "values") else blocks):
+                for bp in block.parameters():
+                    unit_of.setdefault(id(bp), i)
+            self.streamed = True
+        unit_off: Dict[int, int] = {}
         for fq, module, p, pname in entries:
             full_shape = tuple(p.shape)
             aware = _is_aware(module, pname)
-            can_shard = self.shard and aware and len(full_shape) >= 1 and full_shape[0] % ws == 0 and full_shape[0] >= ws
-            rows = full_shape[0] // ws if can_shard else (full_shape[0] if full_shape else 1)
-            row_start = rank * rows if can_shard else 0
+            can_shard = self.shard and aware and len(full_shape) >= 1
             inner = 1
             for s in full_shape[1:]:
                 inner *= s
+            if can_shard:
+                rows = -(-full_shape[0] // ws)  # torch.chunk's split: ceil-sized shards, the last ones short or empty
+                padded_rows = rows * ws
+                row_start = rank * rows
+            else:
+                rows = full_shape[0] if full_shape else 1
+                padded_rows = rows
+                row_start = 0
             local_numel = rows * inner if full_shape else 1
             full_numel = p.numel()
+            flat_numel = padded_rows * inner if full_shape else 1
+            unit = unit_of.get(id(p), -1) if (aware and can_shard) else -1
             # 16-byte alignment of every slot in every buffer (fp32: 4 elements, bf16: 8 elements)
             master_off = (master_off + 7) // 8 * 8
-            full_off = (full_off + 7) // 8 * 8
+            if unit >= 0:
+                off = (unit_off.get(unit, 0) + 7) // 8 * 8
+                unit_off[unit] = off + flat_numel
+            else:
+                full_off = (full_off + 7) // 8 * 8
+                off = full_off
             slot = ParamSlot(
                 name=fq, param=p, full_shape=full_shape, sharded=can_shard, local_rows=rows, row_start=row_start,
-                master_offset=master_off, local_numel=local_numel, full_offset=full_off if aware else -1,
-                full_numel=full_numel, aware=aware,
+                master_offset=master_off, local_numel=local_numel, full_offset=off if aware else -1,
+                full_numel=full_numel, aware=aware, padded_rows=padded_rows, unit=unit, flat_numel=flat_numel,
             )
             self.slots.append(slot)
             seen[id(p)] = slot
             master_off += local_numel
-            if aware:
-                full_off += full_numel
+            if aware and unit < 0:
+                full_off += flat_numel
         self._master_numel = (master_off + 7) // 8 * 8
         self._full_numel = (full_off + 7) // 8 * 8
+        self._unit_numel = (max(unit_off.values()) + 7) // 8 * 8 if unit_off else 0
+        if self.streamed:
+            n_units = max(unit_off) + 1
+            self.units = [[s for s in self.slots if s.unit == u] for u in range(n_units)]
+
+    def _want_streamed(self, entries) -> bool:
+        """Streamed mode on request, or when the resident layout would take more than 35 % of the device's memory."""
+        if not self.shard:
+            return False
+        env = os.environ.get(STREAMED_ENV_VAR)
+        if env is not None:
+            return env not in ("0", "")
+        if self._streamed_request is not None:
+            return bool(self._streamed_request)
+        if not torch.cuda.is_available():
+            return False
+        resident = 6 * sum(e[2].numel() for e in entries)
+        try:
+            total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+        except Exception:
+            return False
+        return resident > 0.35 * total
 
     @property
     def materialized(self) -> bool:
@@ -187,24 +261,28 @@ class ShardedParamRuntime:
         if self._materialized:
             return
         self.device = device
+        self._check_memory(device)
         self.master = torch.zeros(self._master_numel, dtype=torch.float32, device=device)
+        lowp_dtype = self.param_dtype or torch.float32  # without a compute dtype the full copy is fp32 (same layout)
+        self._sym_lowp = self._sym_grad = None
+        tensor_parallel = any(hasattr(s.param, "_tp_sharded") or hasattr(s.param, "_tp_partial_grad") for s in self.slots)
+        peer_ok = (self.shard and self.replicate_group is None and lowp_dtype == torch.bfloat16
+                   and self.reduce_dtype == torch.float32 and not tensor_parallel)
         if self._full_numel > 0:
-            # without a low-precision compute dtype the full copy is fp32 (same layout, same code paths)
-            lowp_dtype = self.param_dtype or torch.float32
-            self._sym_lowp = self._sym_grad = None
-            tensor_parallel = any(hasattr(s.param, "_tp_sharded") or hasattr(s.param, "_tp_partial_grad") for s in self.slots)
-            if (self.shard and self.replicate_group is None and lowp_dtype == torch.bfloat16
-                    and self.reduce_dtype == torch.float32 and not tensor_parallel):
+            if peer_ok and not self.streamed:
                 self._try_symmetric(device)
             if self._sym_grad is not None:
                 self.lowp, self.main_grad = self._sym_lowp.tensor, self._sym_grad.tensor
             else:
                 self.lowp = torch.zeros(self._full_numel, dtype=lowp_dtype, device=device)
                 self.main_grad = torch.zeros(self._full_numel, dtype=self.reduce_dtype, device=device)
-        if self.world_size > 1 or self.main_grad is None or self.reduce_dtype != torch.float32:
+        if (self.world_size > 1 or self.main_grad is None or self.reduce_dtype != torch.float32
+                or self.replicate_group is not None or self.streamed):
             self.grad_shard = torch.zeros(self._master_numel, dtype=torch.float32, device=device)
         else:
             self.grad_shard = None  # single rank, fp32: the shard of a gradient *is* the gradient (see grad_view)
+        if self.streamed:
+            self._materialize_streamed(device, lowp_dtype, peer_ok)
         tied: Dict[int, nn.Parameter] = {}
         for slot in self.slots:
             old = slot.param
@@ -212,15 +290,21 @@ class ShardedParamRuntime:
             view = self.master[slot.master_offset : slot.master_offset + slot.local_numel].view(local_shape)
             if old.device.type != "meta":
                 src = old.data.to(device=device, dtype=torch.float32)
-                view.copy_(src.narrow(0, slot.row_start, slot.local_rows) if slot.sharded else src)
+                if slot.sharded:
+                    real = slot.real_local_rows
+                    if real > 0:
+                        view[:real].copy_(src.narrow(0, slot.row_start, real))
+                else:
+                    view.copy_(src)
             new = nn.Parameter(view, requires_grad=old.requires_grad)
             new._shard_info = ShardInfo(slot.full_shape, slot.row_start, slot.sharded)  # type: ignore[attr-defined]
             for attr in ("_tp_partial_grad", "_tp_sharded"):  # set by olmo_core_b200.parallel.tensor
                 if hasattr(old, attr):
                     setattr(new, attr, getattr(old, attr))
             if slot.aware:
-                new._lowp = self.lowp[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
-                new.main_grad = self.main_grad[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
+                lowp_buf, grad_buf = self._full_buffers(slot)
+                new._lowp = lowp_buf[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
+                new.main_grad = grad_buf[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)  # type: ignore[attr-defined]
             tied[id(old)] = new
             slot.param = new
         # swap parameters inside the modules (handles tied parameters: same object everywhere)
@@ -229,6 +313,32 @@ class ShardedParamRuntime:
                 if id(p) in tied:
                     module._parameters[pname] = tied[id(p)]
         self._materialized = True
+
+    def _full_buffers(self, slot: ParamSlot) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The flat buffers that hold the full low-precision copy / full-size gradient of ``slot``."""
+        if slot.unit >= 0:
+            return self._ring_lowp[slot.unit % 2], self._ring_grad[slot.unit % 2]
+        return self.lowp, self.main_grad
+
+    def _check_memory(self, device: torch.device) -> None:
+        """Refuse a layout that cannot fit instead of dying in an allocation half way through."""
+        if device.type != "cuda":
+            return
+        from ..exceptions import OLMoConfigurationError
+
+        master = 12 * self._master_numel  # fp32 master + two fp32 moments
+        if self.streamed:
+            state = master + 6 * self._master_numel + 6 * self._full_numel + 2 * 6 * self._unit_numel
+        else:
+            state = master + 6 * self._full_numel + (4 * self._master_numel if self.world_size > 1 else 0)
+        total = torch.cuda.get_device_properties(device).total_memory
+        if state > 0.95 * total:
+            gb = 1 << 30
+            raise OLMoConfigurationError(
+                f"parameters, gradients and optimizer state need {state / gb:.1f} GiB per GPU "
+                f"({'streamed' if self.streamed else 'resident'} layout: {self._full_numel * 6 / gb:.1f} GiB full copies, "
+                f"{master / gb:.1f} GiB sharded state) but the device has {total / gb:.1f} GiB; use more data-parallel "
+                f"ranks{'' if self.streamed else f' or set {STREAMED_ENV_VAR}=1'}")
 
     # ------------------------------------------------------------------------------------------------
     # peer-mapped buffers for the fused optimizer step
@@ -296,9 +406,9 @@ class ShardedParamRuntime:
                 continue
             # small or oddly sized parameters: NCCL all-reduce of the whole tensor
             if slot.aware:
-                full = self.main_grad[slot.full_offset: slot.full_offset + slot.full_numel]
+                full = self._flat(self.main_grad, slot)
                 dist.all_reduce(full, op=dist.ReduceOp.SUM, group=self.group)
-                src = full.view(slot.full_shape).narrow(0, slot.row_start, slot.local_rows).reshape(-1) if slot.sharded else full
+                src = full[self.rank * slot.local_numel: (self.rank + 1) * slot.local_numel] if slot.sharded else full
                 out.copy_(src).div_(self.world_size)
             else:
                 g = slot.param.grad
@@ -315,41 +425,54 @@ class ShardedParamRuntime:
     # ------------------------------------------------------------------------------------------------
     # parameter synchronisation
     # ------------------------------------------------------------------------------------------------
+    def _flat(self, buf: torch.Tensor, slot: ParamSlot) -> torch.Tensor:
+        """The (padded) full extent of ``slot`` inside a flat full-size buffer."""
+        return buf[slot.full_offset : slot.full_offset + slot.flat_numel]
+
     def _own_rows_lowp(self, slot: ParamSlot) -> torch.Tensor:
-        full = self.lowp[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)
-        return full.narrow(0, slot.row_start, slot.local_rows) if slot.sharded else full
+        """This rank's rows of the low-precision copy of ``slot`` (what the optimizer refreshes after an update)."""
+        local_shape = (slot.local_rows,) + slot.full_shape[1:] if slot.full_shape else ()
+        if slot.unit >= 0:
+            return self.lowp_shard[slot.master_offset : slot.master_offset + slot.local_numel].view(local_shape)
+        if not slot.sharded:
+            return self.lowp[slot.full_offset : slot.full_offset + slot.full_numel].view(slot.full_shape)
+        flat = self._flat(self.lowp, slot)
+        return flat[self.rank * slot.local_numel : (self.rank + 1) * slot.local_numel].view(local_shape)
 
     @torch.no_grad()
     def sync_lowp(self) -> None:
-        """Refresh the resident low-precision copies from the fp32 master shards (cast + all-gather)."""
-        if self.lowp is None:
+        """Refresh the low-precision copies from the fp32 master shards (cast + all-gather of the resident part)."""
+        if self.lowp is None and self.lowp_shard is None:
             return
         for slot in self.slots:
             if slot.aware:
                 self._own_rows_lowp(slot).copy_(slot.param.data)
         self.all_gather_lowp()
+        self.finish_scatter()
 
     @torch.no_grad()
     def all_gather_lowp(self, only_unfused: bool = False) -> None:
         """
-        All-gather every sharded parameter's bf16 rows into the full resident copy (in place). With ``only_unfused``
-        the parameters whose rows the fused optimizer kernel has already stored into all peers are left out.
+        All-gather every resident sharded parameter's bf16 rows into the full copy (in place). With ``only_unfused`` the
+        parameters whose rows the fused optimizer kernel has already stored into all peers are left out. Streamed
+        blocks are not touched: their full copies are assembled block by block during the next forward pass.
         """
         if not self.shard or self.lowp is None:
             return
-        sharded = [s for s in self.slots if s.aware and s.sharded and not (only_unfused and self._fusable(s))]
+        sharded = [s for s in self.slots
+                   if s.aware and s.sharded and s.unit < 0 and not (only_unfused and self._fusable(s))]
         if not sharded:
             return
         backend_batch = getattr(dist, "_coalescing_manager", None)
         if backend_batch is not None and self.lowp.is_cuda:
             with dist._coalescing_manager(group=self.group, device=self.lowp.device, async_ops=False):
                 for slot in sharded:
-                    full = self.lowp[slot.full_offset : slot.full_offset + slot.full_numel]
-                    dist.all_gather_into_tensor(full, self._own_rows_lowp(slot).reshape(-1), group=self.group)
+                    dist.all_gather_into_tensor(self._flat(self.lowp, slot), self._own_rows_lowp(slot).reshape(-1),
+                                                group=self.group)
         else:
             for slot in sharded:
-                full = self.lowp[slot.full_offset : slot.full_offset + slot.full_numel]
-                dist.all_gather_into_tensor(full, self._own_rows_lowp(slot).reshape(-1).clone(), group=self.group)
+                dist.all_gather_into_tensor(self._flat(self.lowp, slot), self._own_rows_lowp(slot).reshape(-1).clone(),
+                                            group=self.group)
 
     # ------------------------------------------------------------------------------------------------
     # gradients
@@ -370,6 +493,12 @@ class ShardedParamRuntime:
             slot.param.grad = None
         if self.symmetric:
             self._sumsq_valid = False
+        if self.streamed and self._materialized:
+            self._flush_dirty_units()
+            self._wait_comm()
+            self.grad_shard.zero_()  # streamed blocks accumulate their reduced gradients here across micro-batches
+            for g in self._ring_grad:
+                g.zero_()
 
     @torch.no_grad()
     def adamw_scatter(self, slot: ParamSlot, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, step: torch.Tensor, *,
@@ -404,6 +533,10 @@ class ShardedParamRuntime:
         """Barrier after the last :meth:`adamw_scatter` of a step: all peers' parameter stores have landed."""
         if self.symmetric:
             self._sym_lowp.barrier()
+        if self.streamed and self._materialized:
+            self._slot_unit = [-1, -1]  # the ring holds last step's weights
+            if self._sym_shard_lowp is not None:
+                self._sym_shard_lowp.barrier()  # every rank's updated rows are in place before anybody gathers them
 
     @torch.no_grad()
     def reduce_gradients(self) -> None:
@@ -414,6 +547,11 @@ class ShardedParamRuntime:
         if self.symmetric:
             self._reduce_gradients_fused()
             return
+        if self.streamed:
+            self._flush_dirty_units()
+            self._wait_comm()
+            if self._sym_shard_grad is not None:
+                self._sym_shard_grad.barrier()  # the reductions every peer sent into this rank's shard have landed
         self._reduce_gradients_nccl()
         self._sync_tensor_parallel_partials()
 
@@ -444,8 +582,10 @@ class ShardedParamRuntime:
         for slot in self.slots:
             if not slot.param.requires_grad:
                 continue
+            if slot.unit >= 0:
+                continue  # reduced into grad_shard right after the block's backward
             if slot.aware:
-                full = self.main_grad[slot.full_offset : slot.full_offset + slot.full_numel]
+                full = self._flat(self.main_grad, slot)
                 if slot.param.grad is not None:  # an op without main_grad support produced a regular gradient
                     g = slot.param.grad
                     if slot.sharded:
@@ -461,7 +601,7 @@ class ShardedParamRuntime:
                     if not full.is_cuda:
                         # Gloo has no reduce-scatter: all-reduce the full gradient and keep our rows.
                         dist.all_reduce(full, op=dist.ReduceOp.SUM, group=self.group)
-                        out.copy_(full.view(slot.full_shape).narrow(0, slot.row_start, slot.local_rows).reshape(-1)).div_(ws)
+                        out.copy_(full[self.rank * slot.local_numel: (self.rank + 1) * slot.local_numel]).div_(ws)
                     elif full.dtype == torch.float32:
                         dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.AVG, group=self.group)
                     else:
@@ -539,6 +679,156 @@ class ShardedParamRuntime:
         return total
 
     # ------------------------------------------------------------------------------------------------
+    # streamed blocks: per-block gather ahead of the compute, per-block gradient reduction behind it
+    # ------------------------------------------------------------------------------------------------
+    def _materialize_streamed(self, device: torch.device, lowp_dtype: torch.dtype, peer_ok: bool) -> None:
+        from .symmetric import SymmetricBuffer, symmetric_memory_enabled
+
+        self._ring_lowp = [torch.zeros(self._unit_numel, dtype=lowp_dtype, device=device) for _ in range(2)]
+        self._ring_grad = [torch.zeros(self._unit_numel, dtype=self.reduce_dtype, device=device) for _ in range(2)]
+        # Saved-for-backward weight views would trip autograd's version check when their ring slot is refilled between
+        # a block's forward and its backward (with the same values); `.data` aliases carry their own version counter.
+        self._ring_lowp_raw = [t.data for t in self._ring_lowp]
+        self._sym_shard_lowp = self._sym_shard_grad = None
+        if peer_ok and device.type == "cuda" and symmetric_memory_enabled(device, self.group):
+            try:
+                self._sym_shard_lowp = SymmetricBuffer(self._master_numel, torch.bfloat16, device, self.group)
+                self._sym_shard_grad = SymmetricBuffer(self._master_numel, torch.float32, device, self.group)
+            except Exception as e:
+                log.warning(f"Peer-mapped shards unavailable ({type(e).__name__}: {e}); streaming blocks with NCCL")
+                self._sym_shard_lowp = self._sym_shard_grad = None
+        if self._sym_shard_grad is not None:
+            self.lowp_shard, self.grad_shard = self._sym_shard_lowp.tensor, self._sym_shard_grad.tensor
+        else:
+            self.lowp_shard = torch.zeros(self._master_numel, dtype=lowp_dtype, device=device)
+        self._slot_unit = [-1, -1]  # which block's weights each ring slot holds (or is being filled with)
+        self._slot_dirty = [-1, -1]  # which block's gradients sit unreduced in each gradient slot
+        self._gather_done: List[Optional[torch.cuda.Event]] = [None, None]
+        self._reduce_done: List[Optional[torch.cuda.Event]] = [None, None]
+        self._comm_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
+        self._unit_segs = [
+            torch.tensor([[s.master_offset, s.full_offset, s.local_numel] for s in unit], dtype=torch.int64, device=device)
+            for unit in self.units]
+        blocks = self.model.blocks
+        for u, block in enumerate(blocks.values() if hasattr(blocks, "values") else blocks):
+            block.register_forward_pre_hook(lambda m, args, u=u: self._pre_forward(u))
+            block.register_full_backward_pre_hook(lambda m, grad_out, u=u: self._pre_backward(u))
+            block.register_full_backward_hook(lambda m, grad_in, grad_out, u=u: self._post_backward(u))
+        log.info(f"Sharded-parameter runtime streams {len(self.units)} blocks through a two-slot ring "
+                 f"({'peer memory' if self._sym_shard_grad is not None else 'collectives'}): {self.memory_summary()}")
+
+    def _wait_comm(self) -> None:
+        if self._comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+
+    def _pre_forward(self, u: int) -> None:
+        self._ensure_unit(u)
+        in_backward = torch._C._current_graph_task_id() != -1  # a checkpointed block recomputing its forward
+        if not in_backward and u + 1 < len(self.units):
+            self._ensure_unit(u + 1, wait=False)
+
+    def _pre_backward(self, u: int) -> None:
+        self._ensure_unit(u)
+        k = u % 2
+        if self._slot_dirty[k] not in (-1, u):
+            self._reduce_unit(self._slot_dirty[k])  # its post-backward hook never fired (input without gradient)
+        if self._reduce_done[k] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._reduce_done[k])  # slot cleared by its last user
+        self._slot_dirty[k] = u
+        if u > 0:
+            self._ensure_unit(u - 1, wait=False)
+
+    def _post_backward(self, u: int) -> None:
+        if self._slot_dirty[u % 2] == u:
+            self._reduce_unit(u)
+
+    def _flush_dirty_units(self) -> None:
+        for k in range(2):
+            if self._slot_dirty[k] >= 0:
+                self._reduce_unit(self._slot_dirty[k])
+
+    @torch.no_grad()
+    def _ensure_unit(self, u: int, wait: bool = True) -> None:
+        """Have block ``u``'s full weights in its ring slot: start the gather if needed, optionally wait for it."""
+        k = u % 2
+        if self._slot_unit[k] != u:
+            self._gather_unit(u)
+        if wait and self._gather_done[k] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._gather_done[k])
+
+    @torch.no_grad()
+    def _gather_unit(self, u: int) -> None:
+        k = u % 2
+        dst = self._ring_lowp_raw[k]
+        if self._comm_stream is None:  # CPU / gloo
+            for s in self.units[u]:
+                own = self.lowp_shard[s.master_offset : s.master_offset + s.local_numel]
+                dist.all_gather_into_tensor(dst[s.full_offset : s.full_offset + s.flat_numel], own.clone(), group=self.group)
+            self._slot_unit[k] = u
+            return
+        cur = torch.cuda.current_stream(self.device)
+        self._comm_stream.wait_stream(cur)  # the slot's previous occupant is no longer read, the shards are up to date
+        with torch.cuda.stream(self._comm_stream):
+            if self._sym_shard_lowp is not None:
+                from ..ops import _lib
+
+                rc = _lib.lib().ocb_peer_gather_segments(self._sym_shard_lowp.peer_ptrs, self.world_size,
+                                                         self._unit_segs[u].data_ptr(), len(self.units[u]), dst.data_ptr(),
+                                                         self._comm_stream.cuda_stream)
+                _lib.check(rc, "ocb_peer_gather_segments")
+            else:
+                with dist._coalescing_manager(group=self.group, device=self.device, async_ops=False):
+                    for s in self.units[u]:
+                        own = self.lowp_shard[s.master_offset : s.master_offset + s.local_numel]
+                        dist.all_gather_into_tensor(dst[s.full_offset : s.full_offset + s.flat_numel], own, group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(self._comm_stream)
+        self._gather_done[k] = ev
+        self._slot_unit[k] = u
+
+    @torch.no_grad()
+    def _reduce_unit(self, u: int) -> None:
+        """Average block ``u``'s full-size gradients over the ranks into the owners' shards and clear its ring slot."""
+        k = u % 2
+        ws = self.world_size
+        src = self._ring_grad[k]
+        self._slot_dirty[k] = -1
+        if self._comm_stream is None:  # CPU / gloo: no reduce-scatter, all-reduce and keep our rows
+            for s in self.units[u]:
+                full = src[s.full_offset : s.full_offset + s.flat_numel]
+                dist.all_reduce(full, op=dist.ReduceOp.SUM, group=self.group)
+                mine = full[self.rank * s.local_numel : (self.rank + 1) * s.local_numel]
+                self.grad_shard[s.master_offset : s.master_offset + s.local_numel].add_(mine.to(torch.float32), alpha=1.0 / ws)
+                full.zero_()
+            return
+        cur = torch.cuda.current_stream(self.device)
+        self._comm_stream.wait_stream(cur)  # the block's backward has written all of its gradients
+        with torch.cuda.stream(self._comm_stream):
+            if self._sym_shard_grad is not None:
+                from ..ops import _lib
+
+                rc = _lib.lib().ocb_peer_scatter_add_segments(self._sym_shard_grad.peer_ptrs, ws, self._unit_segs[u].data_ptr(),
+                                                              len(self.units[u]), src.data_ptr(), 1.0 / ws,
+                                                              self._comm_stream.cuda_stream)
+                _lib.check(rc, "ocb_peer_scatter_add_segments")
+            else:
+                for s in self.units[u]:
+                    full = src[s.full_offset : s.full_offset + s.flat_numel]
+                    out = self.grad_shard[s.master_offset : s.master_offset + s.local_numel]
+                    if full.dtype == torch.float32:
+                        tmp = torch.empty_like(out)
+                        dist.reduce_scatter_tensor(tmp, full, op=dist.ReduceOp.AVG, group=self.group)
+                        out.add_(tmp)
+                    else:
+                        tmp = torch.empty(s.local_numel, dtype=full.dtype, device=full.device)
+                        dist.reduce_scatter_tensor(tmp, full, op=dist.ReduceOp.SUM, group=self.group)
+                        out.add_(tmp.to(torch.float32), alpha=1.0 / ws)
+                src[: self._unit_numel].zero_()
+            ev = torch.cuda.Event()
+            ev.record(self._comm_stream)
+        self._reduce_done[k] = ev
+
+    # ------------------------------------------------------------------------------------------------
     # micro-batch bookkeeping
     # ------------------------------------------------------------------------------------------------
     def named_slots(self) -> Iterable[Tuple[str, ParamSlot]]:
@@ -559,6 +849,10 @@ class ShardedParamRuntime:
             parts.append(f"main_grad {self.main_grad.numel() * self.main_grad.element_size() / gb:.2f} GiB")
         if self.grad_shard is not None:
             parts.append(f"grad_shard {self.grad_shard.numel() * 4 / gb:.2f} GiB")
+        if self.streamed and self.lowp_shard is not None:
+            parts.append(f"lowp_shard {self.lowp_shard.numel() * self.lowp_shard.element_size() / gb:.2f} GiB")
+            ring = sum(t.numel() * t.element_size() for t in self._ring_lowp + self._ring_grad)
+            parts.append(f"block ring {ring / gb:.2f} GiB ({len(self.units)} streamed blocks)")
         return ", ".join(parts)
 
     # ------------------------------------------------------------------------------------------------
@@ -577,4 +871,10 @@ class ShardedParamRuntime:
         if not hasattr(self, "_ckpt_mesh"):
             ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world_size))
             self._ckpt_mesh = DeviceMesh.from_group(self.group or dist.group.WORLD, local.device.type, mesh=ranks)
+        if slot.padded_rows != slot.full_shape[0]:
+            # uneven split: present only the rows that exist, with the global shape spelled out
+            shape = torch.Size(slot.full_shape)
+            stride = torch.empty(shape, device="meta").stride()
+            return DTensor.from_local(local[: slot.real_local_rows], self._ckpt_mesh, [Shard(0)], run_check=False,
+                                      shape=shape, stride=stride)
         return DTensor.from_local(local, self._ckpt_mesh, [Shard(0)], run_check=False)

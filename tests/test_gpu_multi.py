@@ -13,9 +13,10 @@ from olmo_core_b200.testing import requires_multi_gpu, run_distributed_test
 VOCAB, SEQ = 512, 128
 
 
-def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3):
+def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streamed: str = "0"):
     os.environ["OLMO_CORE_B200_SYMMETRIC"] = symmetric
     os.environ["OLMO_CORE_B200_MULTIMEM"] = multimem
+    os.environ["OLMO_CORE_B200_FSDP_STREAMED"] = streamed
     import torch.distributed as dist
 
     from olmo_core_b200.config import DType
@@ -33,6 +34,31 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3):
         dp_config=TransformerDataParallelConfig(name="fsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32),
     )
     rt = tm.runtime
+    if streamed == "1":
+        assert rt.streamed and (rt._sym_shard_grad is not None) == (symmetric == "1")
+        norms = []
+        gen = torch.Generator().manual_seed(100 + rank)
+        for _ in range(steps):
+            ids = torch.randint(0, VOCAB, (4, SEQ), generator=gen)
+            tm.zero_grads()
+            tm.train_batch({"input_ids": ids})
+            tm.optim_step()
+            norms.append(float(rt.grad_norm_sq().sqrt()))
+        torch.cuda.synchronize()
+        from olmo_core_b200.ops import _lib
+
+        _lib.check_device_status(device)
+        full = {}
+        for s in rt.slots:
+            if not s.aware:
+                continue
+            local = s.param.data.contiguous()
+            parts = [torch.empty_like(local) for _ in range(dist.get_world_size())]
+            dist.all_gather(parts, local)
+            full[s.name] = torch.cat(parts, 0)[: s.full_shape[0]].to(torch.bfloat16).float().cpu()
+        if rank == 0:
+            torch.save({"params": full, "norms": norms}, out_path)
+        return
     assert rt.symmetric == (symmetric == "1"), (rt.symmetric, symmetric)
     if symmetric == "1" and multimem == "1" and rt._sym_grad.multicast_ptr is None:
         if rank == 0:
@@ -56,10 +82,23 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3):
         torch.save({"params": full, "norms": norms}, out_path)
 
 
-def _run(tmp_path, name: str, symmetric: str, multimem: str):
+def _run(tmp_path, name: str, symmetric: str, multimem: str, streamed: str = "0"):
     out = str(tmp_path / f"{name}.pt")
-    run_distributed_test(_train, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(out, symmetric, multimem))
+    run_distributed_test(_train, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(out, symmetric, multimem, 3, streamed))
     return torch.load(out, weights_only=False)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+@pytest.mark.parametrize("symmetric", ["0", "1"])
+def test_streamed_blocks_match_resident_parameters(tmp_path, symmetric):
+    """Per-block gather / gradient reduction (NCCL, and the peer-memory kernels) against the resident NCCL path."""
+    ref = _run(tmp_path, "nccl", "0", "0")
+    got = _run(tmp_path, f"streamed{symmetric}", symmetric, "0", streamed="1")
+    for a, b in zip(ref["norms"], got["norms"]):
+        assert a == pytest.approx(b, rel=2e-3)
+    for name, want in ref["params"].items():
+        torch.testing.assert_close(got["params"][name], want, rtol=0, atol=1e-2, msg=name)
 
 
 @pytest.mark.gpu
