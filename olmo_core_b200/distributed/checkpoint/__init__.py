@@ -132,10 +132,31 @@ def _ensure_optim_state(model: nn.Module, optim: torch.optim.Optimizer) -> None:
             st["step"].zero_()
 
 
-def optim_state(model: nn.Module, optim: torch.optim.Optimizer) -> Dict[str, Any]:
-    """Flattened optimizer state: ``state.<fqn>.<field>`` tensors and ``param_groups.<fqn>.<field>`` values."""
+def optim_state(model: nn.Module, optim: torch.optim.Optimizer, *, flatten: bool = True) -> Dict[str, Any]:
+    """
+    Optimizer state keyed by parameter name. Flattened (what trainer checkpoints use): ``state.<fqn>.<field>`` tensors
+    and ``param_groups.<fqn>.<field>`` values. Unflattened (the default of the reference's stand-alone
+    ``save_model_and_optim_state``): the same ``state.<fqn>.<field>`` tensors, and ``param_groups`` as a list with one
+    dict per group whose ``params`` entry lists parameter names; on disk that list appears as
+    ``optim.param_groups.<i>.<field>``.
+    """
     name_of = {id(p): n for n, p in model.named_parameters()}
     out: Dict[str, Any] = {}
+    if not flatten:
+        groups = []
+        for group in optim.param_groups:
+            names = [name_of[id(p)] for p in group["params"] if id(p) in name_of]
+            groups.append({"params": names, **{k: v for k, v in group.items() if k != "params"}})
+            for p in group["params"]:
+                n = name_of.get(id(p))
+                if n is None:
+                    continue
+                for field, value in optim.state.get(p, {}).items():
+                    if torch.is_tensor(value) and value.dim() > 0:
+                        value = _present(model, p, value)
+                    out[f"state.{n}.{field}"] = value
+        out["param_groups"] = groups
+        return out
     for group in optim.param_groups:
         for p in group["params"]:
             n = name_of.get(id(p))
@@ -179,6 +200,15 @@ def load_model_state(model: nn.Module, state: Dict[str, torch.Tensor], *, strict
 def load_optim_state(model: nn.Module, optim: torch.optim.Optimizer, state: Dict[str, Any]) -> None:
     _ensure_optim_state(model, optim)
     name_of = {id(p): n for n, p in model.named_parameters()}
+    saved_groups = state.get("param_groups")
+    if isinstance(saved_groups, list):  # unflattened layout: one dict per group, in the optimizer's group order
+        if len(saved_groups) != len(optim.param_groups):
+            raise ValueError(f"checkpoint has {len(saved_groups)} optimizer param groups, the optimizer has "
+                             f"{len(optim.param_groups)}")
+        for group, saved in zip(optim.param_groups, saved_groups):
+            for field, value in saved.items():
+                if field not in ("params", "initial_lr") and field in group:
+                    group[field] = value
     for group in optim.param_groups:
         for p in group["params"]:
             n = name_of.get(id(p))
@@ -305,13 +335,18 @@ def load_state_dict(
                                    no_dist=not is_distributed())
 
 
-def _model_optim_state(model: nn.Module, optim: Optional[torch.optim.Optimizer], *, for_load: bool = False) -> Dict[str, Any]:
+def _model_optim_state(model: nn.Module, optim: Optional[torch.optim.Optimizer], *, for_load: bool = False,
+                       flatten: bool = True) -> Dict[str, Any]:
     sd: Dict[str, Any] = {"model": model_state(model)}
     if optim is not None:
         if for_load:
             _ensure_optim_state(model, optim)
-        sd["optim"] = optim_state(model, optim)
+        sd["optim"] = optim_state(model, optim, flatten=flatten)
     return sd
+
+
+UNFLATTENED_MARKER = "optim.param_groups.0.params"
+"""Present in a checkpoint's metadata exactly when its optimizer state was written unflattened."""
 
 
 @torch.no_grad()
@@ -331,8 +366,7 @@ def save_model_and_optim_state(
     Save model (and optimizer) state under the keys ``model.*`` / ``optim.*``. The result can be loaded with any
     other sharding, world size or wrapping, and by the reference implementation.
     """
-    del flatten_optimizer_state  # the optimizer state is always keyed by parameter name
-    save_state_dict(dir, _model_optim_state(model, optim), process_group=process_group, save_overwrite=save_overwrite,
+    save_state_dict(dir, _model_optim_state(model, optim, flatten=flatten_optimizer_state), process_group=process_group, save_overwrite=save_overwrite,
                     thread_count=thread_count, throttle_uploads=throttle_uploads, enable_plan_caching=enable_plan_caching)
 
 
@@ -349,8 +383,7 @@ def async_save_model_and_optim_state(
     throttle_uploads: bool = False,
     enable_plan_caching: bool = False,
 ) -> Future:
-    del flatten_optimizer_state
-    return async_save_state_dict(dir, _model_optim_state(model, optim), process_group=process_group,
+    return async_save_state_dict(dir, _model_optim_state(model, optim, flatten=flatten_optimizer_state), process_group=process_group,
                                  save_overwrite=save_overwrite, thread_count=thread_count,
                                  throttle_uploads=throttle_uploads, enable_plan_caching=enable_plan_caching)
 
@@ -373,11 +406,16 @@ def load_model_and_optim_state(
     Load a checkpoint written by :func:`save_model_and_optim_state` (here or by the reference) into ``model`` and
     ``optim``. ``key_mapping`` maps current parameter names to the names used in the checkpoint.
     """
-    del flatten_optimizer_state
     dir = normalize_path(dir)
-    sd = _model_optim_state(model, optim, for_load=True)
     reader = RemoteFileSystemReader(dir, thread_count=thread_count, pre_download=pre_download, work_dir=work_dir)
     metadata = reader.read_metadata()
+    # the layout on disk decides, whatever the caller asked for (both layouts are in use: see optim_state)
+    on_disk_flat = UNFLATTENED_MARKER not in metadata.state_dict_metadata
+    if optim is not None and on_disk_flat != flatten_optimizer_state and any(
+            k.startswith("optim.") for k in metadata.state_dict_metadata):
+        log.info(f"Checkpoint at '{dir}' holds {'a flattened' if on_disk_flat else 'an unflattened'} optimizer state; "
+                 "loading it in that layout")
+    sd = _model_optim_state(model, optim, for_load=True, flatten=on_disk_flat)
     if key_mapping is not None:
         swap_param_keys(sd, key_mapping, metadata=metadata)
     if not strict:

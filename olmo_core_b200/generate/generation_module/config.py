@@ -27,19 +27,22 @@ class GenerationConfig(Config):
         self.validate()
 
     def validate(self) -> None:
-        if self.pad_token_id < 0:
-            raise ValueError(f"pad_token_id must be non-negative, got {self.pad_token_id}")
-        if self.eos_token_id < 0:
-            raise ValueError(f"eos_token_id must be non-negative, got {self.eos_token_id}")
-        if self.pad_token_id == self.eos_token_id:
-            raise ValueError(f"pad_token_id and eos_token_id must be different, got {self.pad_token_id} and {self.eos_token_id}")
-        if self.max_length is not None and self.max_length <= 0:
-            raise ValueError(f"max_length must be positive, got {self.max_length}")
-        if self.max_new_tokens is not None and self.max_new_tokens <= 0:
-            raise ValueError(f"max_new_tokens must be positive, got {self.max_new_tokens}")
-        if self.temperature < 0:
-            raise ValueError(f"temperature must be non-negative, got {self.temperature}")
-        if self.top_k <= 0 and self.top_k != -1:
-            raise ValueError(f"top_k must be positive or -1, got {self.top_k}")
-        if self.top_p <= 0.0 or self.top_p > 1.0:
-            raise ValueError(f"top_p must be in (0, 1], got {self.top_p}")
+        """Reject settings that no sampler can honour. All problems are reported at once."""
+        problems = []
+
+        def require(ok: bool, what: str) -> None:
+            if not ok:
+                problems.append(what)
+
+        for name in ("pad_token_id", "eos_token_id"):
+            require(getattr(self, name) >= 0, f"{name}={getattr(self, name)} is not a token id (negative)")
+        require(self.pad_token_id != self.eos_token_id,
+                f"pad_token_id and eos_token_id are both {self.pad_token_id}; padding could not be told from the end of text")
+        for name in ("max_length", "max_new_tokens"):
+            value = getattr(self, name)
+            require(value is None or value > 0, f"{name}={value} leaves no room for tokens")
+        require(self.temperature >= 0, f"temperature={self.temperature} is below zero")
+        require(self.top_k == -1 or self.top_k > 0, f"top_k={self.top_k}: use -1 to switch it off or a count of at least 1")
+        require(0.0 < self.top_p <= 1.0, f"top_p={self.top_p} lies outside (0, 1]")
+        if problems:
+            raise ValueError("invalid generation settings: " + "; ".join(problems))

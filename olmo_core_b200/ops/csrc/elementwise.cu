@@ -1018,9 +1018,15 @@ extern "C" int ocb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
                                       long long ldx, long long lddx, int act_dtype, int w_dtype, int dw_dtype,
                                       cudaStream_t stream) {
   using namespace ocb;
-  if (rows <= 0) return 0;
   if (group <= 0 || cols % group != 0 || group % 8 != 0) return -1;
   if (dw != nullptr && group > OCB_STATIC_SCRATCH_MAX_GROUP) return OCB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  if (rows <= 0) {
+    // an empty batch contributes nothing: "overwrite" still has to leave zeros behind, "accumulate" leaves dw as it is
+    if (dw != nullptr && !dw_accumulate &&
+        cudaMemsetAsync(dw, 0, static_cast<size_t>(group) * (dw_dtype == OCB_F32 ? 4 : 2), stream) != cudaSuccess)
+      return -4;
+    return 0;
+  }
   const int gpr = cols / group;
   const long long n_groups = static_cast<long long>(rows) * gpr;
   const int maxv = group <= 2 * kNormThreads * 8 ? 2 : kMaxVec;

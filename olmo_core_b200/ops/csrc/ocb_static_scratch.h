@@ -22,6 +22,9 @@
 //   * Set-up: the first call on each device resolves the array's device address
 //     (cudaGetSymbolAddress). That first call may initialise the CUDA module, so make it before starting
 //     a stream capture; later calls on that device only enqueue work on `stream`.
+//   * Device: the array that is used is the one of the CURRENT device (cudaGetDevice) at the time of the call, so
+//     the current device must be the device `stream` belongs to.
+//   * Empty input (rows <= 0): nothing is launched; with dw_accumulate == 0 the weight gradient is set to zero.
 //   * Shared state: every call on a device uses the same array. The rows a call is going to use are
 //     cleared (cudaMemsetAsync on `stream`) before its kernel runs, so consecutive calls on ONE stream
 //     are safe. Calls that can overlap -- different streams, or different host threads on different
@@ -39,7 +42,7 @@ extern "C" {
 #define OCB_ERR_STATIC_SCRATCH_SETUP (-7)
 
 // Largest `group` accepted together with a weight gradient (= OCB_STATIC_SCRATCH_MAX_GROUP).
-int ocb_rmsnorm_bwd_static_max_group();
+int ocb_rmsnorm_bwd_static_max_group(void);
 
 // dx = d rmsnorm(x)*w / dx given dy, and dw[c] (+)= sum over rows and groups of dy * x * rstd.
 //   dy, x, dx : [rows, cols] activations (act_dtype), row strides lddy / ldx / lddx (elements)

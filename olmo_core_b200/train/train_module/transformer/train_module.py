@@ -166,13 +166,21 @@ class TransformerTrainModule(TrainModule):
                 return self.runtime.sharded_tensor(slot, local)
         return local
 
-    def state_dict(self, *, optim: Optional[bool] = None) -> Dict[str, Any]:
+    def state_dict(self, *, optim: Optional[bool] = None, flatten_optimizer_state: bool = True) -> Dict[str, Any]:
         """
         ``{"model": {fqn: tensor}, "optim": {"state.<fqn>.<field>": tensor, "param_groups.<fqn>.<field>": value}}``.
         Sharded tensors are presented as dim-0 ``DTensor`` shards so that the checkpoint layer writes the same
-        per-parameter shards, under the same keys, as the reference's flattened optimizer state dicts.
+        per-parameter shards, under the same keys, as the reference's flattened optimizer state dicts. With
+        ``flatten_optimizer_state=False`` the param groups are one list of dicts instead (the layout the reference
+        writes when flattening is off; on disk ``optim.param_groups.<i>.<field>``).
         """
         optim = True if optim is None else optim
+        if optim and not flatten_optimizer_state:
+            from ....distributed.checkpoint import optim_state
+
+            sd = self.state_dict(optim=False)
+            sd["optim"] = optim_state(self.model, self.optim, flatten=False)
+            return sd
         params = self._named_params()
         sd: Dict[str, Any] = {"model": {n: self._present(n, p, p.data) for n, p in params.items()}}
         for n, b in self.model.named_buffers():
@@ -208,7 +216,10 @@ class TransformerTrainModule(TrainModule):
             raise RuntimeError("Checkpoint does not contain optimizer state, but 'optim=True' was requested")
         if optim:
             self._ensure_optim_state()
-        sd = self.state_dict(optim=optim)
+        # the checkpoint decides the optimizer-state layout (the reference switches the same way:
+        # src/olmo_core/train/train_module/transformer/train_module.py:278-293)
+        flat = "optim.param_groups.0.params" not in keys
+        sd = self.state_dict(optim=optim, flatten_optimizer_state=flat)
         if self.load_key_mapping is not None:
             from ....distributed.checkpoint import swap_param_keys
 
@@ -260,6 +271,11 @@ class TransformerTrainModule(TrainModule):
                 self._ensure_optim_state()
                 name_of = {id(p): n for n, p in params.items()}
                 osd = state_dict["optim"]
+                if isinstance(osd.get("param_groups"), list):  # unflattened layout
+                    for group, saved in zip(self.optim.param_groups, osd["param_groups"]):
+                        for field, value in saved.items():
+                            if field not in ("params", "initial_lr") and field in group:
+                                group[field] = value
                 for group in self.optim.param_groups:
                     for p in group["params"]:
                         n = name_of.get(id(p))
@@ -295,6 +311,20 @@ class TransformerTrainModule(TrainModule):
             batch["labels"] = get_labels(batch, label_ignore_index=self.label_ignore_index)
         # total target tokens of this rank's batch; the loss of every micro-batch is divided by it
         batch_num_tokens_for_loss = move_to_device((batch["labels"] != self.label_ignore_index).sum(), self.device)
+        total_tokens = batch["labels"].numel()
+        if not dry_run and total_tokens > 0:
+            # both metrics are proportions in [0, 1]; the names are the ones dashboards built on the reference expect
+            self.record_metric("train/masked labels (%)", 1.0 - batch_num_tokens_for_loss / total_tokens, ReduceType.mean)
+        instance_mask = batch.get("instance_mask")
+        if instance_mask is not None:
+            dropped = move_to_device((~instance_mask).sum(), self.device)
+            if not dry_run:
+                self.record_metric("train/masked instances (%)", dropped / max(instance_mask.numel(), 1), ReduceType.mean)
+            # Instances removed by the instance filter still count, with zero loss, towards the divisor: every rank then
+            # divides by the token count of a full batch whatever the filter dropped locally, which keeps the ranks'
+            # contributions comparable without a collective (same convention as the reference:
+            # src/olmo_core/train/train_module/transformer/train_module.py:368-380).
+            batch_num_tokens_for_loss = batch_num_tokens_for_loss + dropped * batch["labels"].shape[1]
         ce_batch_loss = torch.zeros((), dtype=torch.float32, device=self.device)
         z_batch_loss = torch.zeros((), dtype=torch.float32, device=self.device) if self.z_loss_multiplier is not None else None
 

@@ -90,7 +90,7 @@ def test_model_and_optim_round_trip(tmp_path):
     model = _tiny_model(0)
     optim = AdamWConfig(lr=1e-3).build(model)
     _train_a_little(model, optim)
-    save_model_and_optim_state(tmp_path / "c", model, optim)
+    save_model_and_optim_state(tmp_path / "c", model, optim, flatten_optimizer_state=True)
     keys = set(get_checkpoint_metadata(tmp_path / "c").state_dict_metadata)
     assert "model.embeddings.weight" in keys
     assert "optim.state.embeddings.weight.exp_avg" in keys and "optim.param_groups.embeddings.weight.lr" in keys
@@ -202,3 +202,25 @@ def test_reshard_one_rank_to_two(tmp_path):
     save_model_and_optim_state(path, model, optim)
     torch.save({n: p.data.clone() for n, p in model.named_parameters()}, f"{path}-ref.pt")
     run_distributed_test(_load_sharded, world_size=2, func_args=(path,))
+
+
+@pytest.mark.parametrize("flatten", [False, True])
+def test_optimizer_state_layouts_round_trip(tmp_path, flatten):
+    """Both on-disk layouts of the optimizer state load, whatever layout the loading call asks for."""
+    from olmo_core_b200.distributed.checkpoint import UNFLATTENED_MARKER, get_checkpoint_metadata
+
+    path = str(tmp_path / "c")
+    model = _tiny_model(0)
+    optim = AdamWConfig(lr=3e-3, weight_decay=0.05).build(model)
+    _train_a_little(model, optim, steps=2)
+    save_model_and_optim_state(path, model, optim, flatten_optimizer_state=flatten)
+    keys = set(get_checkpoint_metadata(path).state_dict_metadata.keys())
+    assert (UNFLATTENED_MARKER in keys) == (not flatten)
+    assert "optim.state.embeddings.weight.exp_avg" in keys
+    model2 = _tiny_model(4)
+    optim2 = AdamWConfig(lr=1.0, weight_decay=0.5).build(model2)
+    load_model_and_optim_state(path, model2, optim2, flatten_optimizer_state=not flatten)
+    assert optim2.param_groups[0]["lr"] == pytest.approx(3e-3) and optim2.param_groups[0]["weight_decay"] == pytest.approx(0.05)
+    for (n, p), (_, q) in zip(model.named_parameters(), model2.named_parameters()):
+        assert torch.equal(p.data, q.data), n
+        assert torch.equal(optim.state[p]["exp_avg"], optim2.state[q]["exp_avg"]), n

@@ -95,10 +95,15 @@ def test_static_scratch_matches_existing_entry_point_twice(rows, cols, group):
         dx_old, dw_old = _existing(_lib, handle, dy, x, w, rstd, group)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = _static(_lib, handle, dy, x, w, rstd, group, dx, dw)
         torch.cuda.synchronize()
         assert rc == 0, handle.ocb_rmsnorm_bwd_static_strerror(rc)
         assert torch.cuda.memory_allocated() == before
+        if call == 1:
+            # The caching allocator's counter cannot see a raw cudaMalloc inside the library; the driver's count of
+            # free device memory can. The first call may still load the module, the second must leave it unchanged.
+            assert torch.cuda.mem_get_info()[0] == free_before
         # same kernel, same inputs: dx is bitwise equal; dw differs only by the order of the fp32 atomics
         assert torch.equal(dx, dx_old)
         torch.testing.assert_close(dw, dw_old, rtol=1e-4, atol=1e-3)
@@ -121,6 +126,22 @@ def test_static_scratch_accumulates_into_dw():
     once = dw.clone()
     assert _static(_lib, handle, dy, x, w, rstd, cols, dx, dw, accumulate=1) == 0
     torch.testing.assert_close(dw, 2 * once, rtol=1e-4, atol=1e-3)
+
+
+def test_static_scratch_empty_batch_zeroes_dw():
+    _lib, handle = _bind()
+    dev = torch.device("cuda")
+    cols = 1024
+    x = torch.empty(0, cols, dtype=torch.bfloat16, device=dev)
+    w = torch.ones(cols, device=dev)
+    rstd = torch.empty(0, device=dev)
+    dw = torch.full((cols,), 3.0, device=dev)
+    assert _static(_lib, handle, x, x, w, rstd, cols, x, dw, accumulate=1) == 0
+    torch.cuda.synchronize()
+    assert bool((dw == 3.0).all())
+    assert _static(_lib, handle, x, x, w, rstd, cols, x, dw, accumulate=0) == 0
+    torch.cuda.synchronize()
+    assert bool((dw == 0.0).all())
 
 
 def test_static_scratch_rejects_groups_beyond_its_size():
