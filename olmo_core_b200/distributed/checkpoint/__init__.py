@@ -331,8 +331,21 @@ def load_state_dict(
     """Load ``dir`` into ``state_dict`` in place (tensors are filled, other leaves replaced)."""
     dir = normalize_path(dir)
     reader = RemoteFileSystemReader(dir, thread_count=thread_count, pre_download=pre_download, work_dir=work_dir)
-    dist_cp.state_dict_loader.load(state_dict, checkpoint_id=dir, storage_reader=reader, process_group=process_group,
-                                   no_dist=not is_distributed())
+    _dcp_load(state_dict, dir, reader, process_group)
+
+
+def _dcp_load(state_dict: Dict[str, Any], dir: str, reader: RemoteFileSystemReader,
+              process_group: Optional[dist.ProcessGroup]) -> None:
+    """``dist_cp.load`` with its failures (a ``BaseException`` subclass that wraps per-rank tracebacks) turned into one
+    :class:`OLMoCheckpointError` that names the checkpoint and the first underlying cause."""
+    from torch.distributed.checkpoint.api import CheckpointException
+
+    try:
+        dist_cp.state_dict_loader.load(state_dict, checkpoint_id=dir, storage_reader=reader, process_group=process_group,
+                                       no_dist=not is_distributed())
+    except CheckpointException as e:
+        causes = [f"rank {r}: {type(x).__name__}: {x}" for r, x in sorted(getattr(e, "failures", {}).items())]
+        raise OLMoCheckpointError(f"could not load checkpoint '{dir}': " + ("; ".join(causes) or str(e))) from e
 
 
 def _model_optim_state(model: nn.Module, optim: Optional[torch.optim.Optimizer], *, for_load: bool = False,
@@ -416,14 +429,19 @@ def load_model_and_optim_state(
         log.info(f"Checkpoint at '{dir}' holds {'a flattened' if on_disk_flat else 'an unflattened'} optimizer state; "
                  "loading it in that layout")
     sd = _model_optim_state(model, optim, for_load=True, flatten=on_disk_flat)
+    if optim is not None and not on_disk_flat:
+        # another optimizer class may have written other group fields: ask only for those that are on disk
+        for i, group in enumerate(sd["optim"]["param_groups"]):
+            for field in list(group.keys()):
+                if f"optim.param_groups.{i}.{field}" not in metadata.state_dict_metadata:
+                    del group[field]
     if key_mapping is not None:
         swap_param_keys(sd, key_mapping, metadata=metadata)
     if not strict:
         pruned = prune_state_dict(sd, set(metadata.state_dict_metadata.keys()))
         if pruned:
             log.warning(f"Checkpoint at '{dir}' is missing keys: {sorted(pruned)}")
-    dist_cp.state_dict_loader.load(sd, checkpoint_id=dir, storage_reader=reader, process_group=process_group,
-                                   no_dist=not is_distributed())
+    _dcp_load(sd, dir, reader, process_group)
     if key_mapping is not None:
         swap_param_keys(sd, key_mapping, reverse=True, quiet=True)
     load_model_state(model, sd["model"], strict=strict)

@@ -252,10 +252,18 @@ class RemoteFileSystemReader(dist_cp.StorageReader):
     def _load_item(self, item: ReadItem, planner: LoadPlanner) -> None:
         info = self.storage_data[item.storage_index]
         raw = self._read_entry(info)
+        if len(raw) != info.length:
+            raise OLMoCheckpointError(
+                f"'{self.path}/{info.relative_path}' is truncated: entry '{item.storage_index.fqn}' needs bytes "
+                f"[{info.offset}, {info.offset + info.length}) but only {len(raw)} could be read")
         if item.type == LoadItemType.BYTE_IO:
             planner.load_bytes(item, io.BytesIO(raw))
             return
-        tensor = torch.load(io.BytesIO(raw), map_location="cpu", weights_only=False)
+        try:
+            tensor = torch.load(io.BytesIO(raw), map_location="cpu", weights_only=False)
+        except Exception as e:
+            raise OLMoCheckpointError(f"'{self.path}/{info.relative_path}' is damaged: entry '{item.storage_index.fqn}' "
+                                      f"cannot be decoded ({type(e).__name__}: {e})") from e
         for dim, (off, length) in enumerate(zip(item.storage_offsets, item.lengths)):
             tensor = torch.narrow(tensor, dim, off, length)
         target = planner.resolve_tensor(item).detach()

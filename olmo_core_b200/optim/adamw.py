@@ -213,6 +213,12 @@ class AdamWConfig(OptimConfig[torch.optim.AdamW]):
                                   group_overrides=self.group_overrides, compile=self.compile, fixed_fields=self.fixed_fields)
         optim = cfg.build(model, strict=strict)
         optim.skip_enabled = False
+        # The param groups carry the fields torch.optim.AdamW groups have, so a checkpoint written here loads into an
+        # optimizer that the reference builds from the same AdamWConfig (its loader wants every field of its groups).
+        for group in optim.param_groups:
+            for field, value in (("amsgrad", False), ("maximize", False), ("foreach", self.foreach), ("capturable", False),
+                                 ("differentiable", False), ("fused", self.fused), ("decoupled_weight_decay", True)):
+                group.setdefault(field, value)
         return optim
 
 
