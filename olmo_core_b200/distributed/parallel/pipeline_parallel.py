@@ -52,6 +52,11 @@ class PipelineParallelConfig(Config):
     schedule: PipelineScheduleType = PipelineScheduleType.single_1F1B
     style: Optional[PipelineSplitStyle] = None
 
+    def __post_init__(self):
+        self.schedule = PipelineScheduleType(self.schedule)
+        if self.style is not None:
+            self.style = PipelineSplitStyle(self.style)
+
     def infer_style(self) -> PipelineSplitStyle:
         return self.style or self.schedule.default_style
 

@@ -85,28 +85,49 @@ class TransformerPipelineTrainModule(TrainModule):
         return self._schedule
 
     def state_dict(self, *, optim: Optional[bool] = None) -> Dict[str, Any]:
-        sd: Dict[str, Any] = {"model": {}, "optim": {}}
+        """
+        The same layout as the non-pipelined train module writes: ``model.<fqn>`` and, flattened,
+        ``optim.state.<fqn>.<field>`` / ``optim.param_groups.<fqn>.<field>``, with sharded tensors presented as dim-0
+        ``DTensor`` shards. Every rank contributes the parameters of its own stages; block names keep their global
+        index, so a checkpoint written with one pipeline layout loads with another, or without pipelining
+        (reference: src/olmo_core/train/train_module/transformer/pipeline_train_module.py:343).
+        """
+        from ....distributed.checkpoint import model_state, optim_state
+
+        sd: Dict[str, Any] = {"model": {}}
+        if optim is not False:
+            sd["optim"] = {}
         for part, opt in zip(self.model_parts, self.optimizers):
-            sd["model"].update({n: p.data for n, p in part.named_parameters()})
+            sd["model"].update(model_state(part))
             if optim is not False:
-                names = {id(p): n for n, p in part.named_parameters()}
-                for g in opt.param_groups:
-                    for p in g["params"]:
-                        for f, v in opt.state.get(p, {}).items():
-                            sd["optim"][f"state.{names[id(p)]}.{f}"] = v
-        if optim is False:
-            sd.pop("optim")
+                sd["optim"].update(optim_state(part, opt, flatten=True))
         return sd
 
+    def state_dict_to_save(self, *, optim: Optional[bool] = None) -> Dict[str, Any]:
+        return self.state_dict(optim=optim)
+
+    def state_dict_to_load(self, metadata, *, optim: Optional[bool] = None) -> Dict[str, Any]:
+        from ....distributed.checkpoint import _ensure_optim_state
+
+        keys = set(getattr(metadata, "state_dict_metadata", {}).keys()) if metadata is not None else set()
+        has_optim = any(k.startswith("optim.") for k in keys)
+        if optim is None:
+            optim = has_optim
+        elif optim and not has_optim:
+            raise RuntimeError("Checkpoint does not contain optimizer state, but 'optim=True' was requested")
+        if optim:
+            for part, opt in zip(self.model_parts, self.optimizers):
+                _ensure_optim_state(part, opt)
+        return self.state_dict(optim=optim)
+
     def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
-        with torch.no_grad():
-            for part in self.model_parts:
-                for n, p in part.named_parameters():
-                    if n in state_dict["model"]:
-                        p.data.copy_(state_dict["model"][n])
-                rt = getattr(part, "_sharding_runtime", None)
-                if rt is not None:
-                    rt.sync_lowp()
+        from ....distributed.checkpoint import load_model_state, load_optim_state
+
+        for part, opt in zip(self.model_parts, self.optimizers):
+            names = {n for n, _ in part.named_parameters()} | {n for n, _ in part.named_buffers()}
+            load_model_state(part, {k: v for k, v in state_dict["model"].items() if k in names}, strict=False)
+            if "optim" in state_dict:
+                load_optim_state(part, opt, state_dict["optim"])
 
     def train_batch(self, batch: Dict[str, Any], dry_run: bool = False) -> None:
         for p in self.model_parts:
@@ -126,6 +147,7 @@ class TransformerPipelineTrainModule(TrainModule):
         value = loss.detach() if loss is not None else torch.zeros((), device=self.device)
         pp_group = self.pp_mesh.get_group()
         dist.all_reduce(value, group=pp_group)  # only the last-stage rank contributes a non-zero value
+        self.latest_ce_loss = value
         self.record_ce_loss(value, ReduceType.mean)
         for opt in self.optimizers:
             if isinstance(opt, SkipStepOptimizer):
