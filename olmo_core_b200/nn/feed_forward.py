@@ -132,11 +132,14 @@ class FeedForward(nn.Module):
         self.w1 = _Proj(d_model, hidden_size, bias, dtype, init_device)
         self.w2 = _Proj(hidden_size, d_model, bias, dtype, init_device)
         self.w3 = _Proj(d_model, hidden_size, bias, dtype, init_device)
+        self.recompute_activation = False
+        """Do not keep ``silu(a) * b`` for the backward pass; the fused backward kernel re-derives it ('selected_ops')."""
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if (self.activation == ActivationFunction.silu and x.is_cuda and self.w1.bias is None
                 and all(getattr(w, "float8", None) is None for w in (self.w1, self.w2, self.w3))):
-            y = swiglu_mlp(x, self.w1.weight, self.w3.weight, self.w2.weight)  # activation inside the GEMM epilogues
+            y = swiglu_mlp(x, self.w1.weight, self.w3.weight, self.w2.weight,  # activation inside the GEMM epilogues
+                           save_activation=not self.recompute_activation)
             if y is not None:
                 return y
         a, b = multi_linear(x, (self.w1, self.w3))  # one saved input, input gradients summed in the GEMM epilogue

@@ -64,6 +64,24 @@ class Embedding(nn.Module):
         return f"{self.num_embeddings}, {self.embedding_dim}"
 
 
+def _checkpoint_module(module: nn.Module) -> None:
+    """Recompute ``module``'s forward in the backward pass (while training with gradients on) instead of saving its
+    intermediate activations. Idempotent."""
+    if getattr(module, "_checkpointed_forward", None) is not None:
+        return
+    inner = module.forward
+
+    def forward(*args, **kwargs):
+        if module.training and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint
+
+            return checkpoint(inner, *args, use_reentrant=False, **kwargs)
+        return inner(*args, **kwargs)
+
+    module._checkpointed_forward = inner  # type: ignore[assignment]
+    module.forward = forward  # type: ignore[method-assign]
+
+
 class Transformer(nn.Module):
     def __init__(
         self,
@@ -416,11 +434,18 @@ class Transformer(nn.Module):
         activation_memory_budget: Optional[float] = None,
     ) -> None:
         """
-        ``full``: every block is recomputed in backward; ``selected_blocks``: every ``block_interval``-th
-        block; ``selected_modules``: blocks whose name matches one of the ``modules`` globs; ``budget``: the
-        fraction ``1 - activation_memory_budget`` of blocks (evenly spaced) is recomputed; ``selected_ops``
-        keeps GEMM and attention outputs and recomputes element-wise ops, which is what the fused
-        kernels already do by construction, so it marks nothing.
+        Choose what is recomputed in the backward pass instead of being kept from the forward pass
+        (reference: src/olmo_core/nn/transformer/model.py:726-838).
+
+        * ``full``: every block; ``selected_blocks``: every ``block_interval``-th block; ``budget``: the fraction
+          ``1 - activation_memory_budget`` of the blocks, evenly spaced.
+        * ``selected_modules``: every module whose dotted name matches one of the ``modules`` globs, at any depth
+          (``"blocks.*.feed_forward"``, ``"blocks.3"``, ``"*.attention"``). A match inside an already selected module
+          is dropped: its parent recomputes it anyway.
+        * ``selected_ops``: keep the outputs of GEMMs and attention, recompute the element-wise results between them.
+          With the fused kernels the only such tensor of any size is the gated activation ``silu(a) * b`` of every MLP;
+          the backward kernel of the down-projection re-derives it from ``a | b`` in its epilogue, so the forward pass
+          stops saving it (one ``[tokens, hidden]`` tensor per layer).
         """
         from fnmatch import fnmatch
 
@@ -436,7 +461,19 @@ class Transformer(nn.Module):
         elif mode == TransformerActivationCheckpointingMode.selected_modules:
             if not modules:
                 raise ValueError("'modules' is required for 'selected_modules' activation checkpointing")
-            chosen = [k for k, _ in blocks if any(fnmatch(f"blocks.{k}", pat) for pat in modules)]
+            matched = [(name, m) for name, m in self.named_modules()
+                       if name and any(fnmatch(name, pat) for pat in modules)]
+            if not matched:
+                raise ValueError(f"no module matches any of {modules}")
+            taken: List[str] = []
+            for name, module in sorted(matched, key=lambda nm: nm[0].count(".")):
+                if any(name.startswith(parent + ".") for parent in taken):
+                    continue
+                taken.append(name)
+                if name.startswith("blocks.") and name.count(".") == 1:
+                    chosen.append(name.split(".")[1])
+                else:
+                    _checkpoint_module(module)
         elif mode == TransformerActivationCheckpointingMode.budget:
             if activation_memory_budget is None:
                 raise ValueError("'activation_memory_budget' is required for 'budget' activation checkpointing")
@@ -444,6 +481,12 @@ class Transformer(nn.Module):
             if n_ckpt > 0:
                 stride = len(blocks) / n_ckpt
                 chosen = [blocks[min(int(i * stride), len(blocks) - 1)][0] for i in range(n_ckpt)]
+        elif mode == TransformerActivationCheckpointingMode.selected_ops:
+            from ..feed_forward import FeedForward
+
+            for module in self.modules():
+                if isinstance(module, FeedForward):
+                    module.recompute_activation = True
         for key in chosen:
             self.blocks[key]._activation_checkpointing = True
 

@@ -334,7 +334,7 @@ class SwiGLUMLPFunction(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w1, w3, w2):  # type: ignore[override]
+    def forward(ctx, x, w1, w3, w2, save_activation=True):  # type: ignore[override]
         w13 = stacked_pair(w1._lowp, w3._lowp)
         w2l = w2._lowp
         x2 = x.reshape(-1, x.shape[-1])
@@ -350,14 +350,22 @@ class SwiGLUMLPFunction(torch.autograd.Function):
                                             H, _lib.status_buffer(x2.device).data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "ocb_gemm_swiglu_fwd")
         y = gemm(h, w2l, trans_b=True)
-        ctx.save_for_backward(x2, ab, h, w13, w2l)
+        if save_activation:
+            ctx.save_for_backward(x2, ab, h, w13, w2l)
+        else:
+            ctx.save_for_backward(x2, ab, w13, w2l)  # h comes back out of the backward kernel's epilogue
+        ctx.saved_h = bool(save_activation)
         ctx.weight_refs = (w1, w3, w2)
         ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
         return y.view(*x.shape[:-1], w2l.shape[0])
 
     @staticmethod
     def backward(ctx, dy):  # type: ignore[override]
-        x2, ab, h, w13, w2l = ctx.saved_tensors
+        if ctx.saved_h:
+            x2, ab, h, w13, w2l = ctx.saved_tensors
+        else:
+            x2, ab, w13, w2l = ctx.saved_tensors
+            h = None
         w1, w3, w2 = ctx.weight_refs
         dy2 = dy.reshape(-1, dy.shape[-1])
         if dy2.dtype != torch.bfloat16:
@@ -366,11 +374,15 @@ class SwiGLUMLPFunction(torch.autograd.Function):
             dy2 = dy2.contiguous()
         M, D = dy2.shape
         H = w1.shape[0]
-        gemm(dy2, h, trans_a=True, trans_b=False, out=w2.main_grad, accumulate=True)
         dab = torch.empty_like(ab)
-        rc = _lib.lib().ocb_gemm_swiglu_bwd(dy2.data_ptr(), w2l.data_ptr(), ab.data_ptr(), dab.data_ptr(), None, M, H, D, D, H,
+        h_out = None
+        if h is None:
+            h = h_out = torch.empty((M, H), dtype=torch.bfloat16, device=ab.device)
+        rc = _lib.lib().ocb_gemm_swiglu_bwd(dy2.data_ptr(), w2l.data_ptr(), ab.data_ptr(), dab.data_ptr(),
+                                            None if h_out is None else h_out.data_ptr(), M, H, D, D, H,
                                             2 * H, 2 * H, H, _lib.status_buffer(dy2.device).data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "ocb_gemm_swiglu_bwd")
+        gemm(dy2, h, trans_a=True, trans_b=False, out=w2.main_grad, accumulate=True)
         g13 = stacked_pair(w1.main_grad, w3.main_grad)
         gemm(dab, x2, trans_a=True, trans_b=False, out=g13, accumulate=True)
         for w in (w1, w3, w2):
@@ -381,10 +393,11 @@ class SwiGLUMLPFunction(torch.autograd.Function):
             dx = gemm(dab, w13, trans_b=False).view(ctx.x_shape)
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
-        return dx, None, None, None
+        return dx, None, None, None, None
 
 
-def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor) -> Optional[torch.Tensor]:
+def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, *,
+               save_activation: bool = True) -> Optional[torch.Tensor]:
     """
     The gated MLP through :class:`SwiGLUMLPFunction`, or ``None`` when its conditions do not hold: CUDA, bf16 resident
     copies of the three weights with ``w1`` / ``w3`` (and their fp32 gradient buffers) back to back in memory, sizes
@@ -400,4 +413,4 @@ def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Te
             return None
     if stacked_pair(w1._lowp, w3._lowp) is None or stacked_pair(w1.main_grad, w3.main_grad) is None:
         return None
-    return SwiGLUMLPFunction.apply(x, w1, w3, w2)
+    return SwiGLUMLPFunction.apply(x, w1, w3, w2, save_activation)

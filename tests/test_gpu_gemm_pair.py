@@ -161,6 +161,13 @@ def test_feed_forward_fused_matches_unfused():
 
     y1, dx1, g1 = run(True)
     y0, dx0, g0 = run(False)
+    # 'selected_ops' activation checkpointing: the gated activation is not kept, the backward kernel re-derives it
+    ff.recompute_activation = True
+    y2, dx2, g2 = run(True)
+    ff.recompute_activation = False
+    assert torch.equal(y2, y1) and torch.equal(dx2, dx1)
+    for n in g1:
+        assert torch.equal(g2[n], g1[n]), n
     torch.testing.assert_close(y1, y0, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(dx1, dx0, atol=2e-2, rtol=2e-2)
     for n in g0:

@@ -136,3 +136,45 @@ def test_moe_dropless_and_capacity_agree_when_nothing_is_dropped():
         assert ya.shape == yb.shape == x.shape
     counts = dropless.router(x)[2]
     assert int(counts.sum()) == 2 * 10 * 2  # every token routed to top_k experts
+
+
+def test_activation_checkpointing_modes_give_identical_gradients():
+    """Every mode only changes what is kept for the backward pass, never the result."""
+    import torch
+
+    from olmo_core_b200.nn.transformer import TransformerConfig
+
+    torch.manual_seed(0)
+    ids = torch.randint(0, 128, (2, 16))
+
+    def run(**ac):
+        torch.manual_seed(1)
+        model = TransformerConfig.olmo2_30M(vocab_size=128, n_layers=3).build(init_device="cpu")
+        model.init_weights(max_seq_len=16, device=torch.device("cpu"))
+        if ac:
+            model.apply_activation_checkpointing(**ac)
+        model.train()
+        out = model(ids, labels=ids)
+        out.loss.backward()
+        return float(out.loss), {n: p.grad.clone() for n, p in model.named_parameters()}, model
+
+    loss0, g0, _ = run()
+    cases = [dict(mode="full"), dict(mode="selected_blocks", block_interval=2), dict(mode="budget", activation_memory_budget=0.5),
+             dict(mode="selected_modules", modules=["blocks.*.feed_forward", "blocks.1"]),
+             dict(mode="selected_modules", modules=["*.attention"]), dict(mode="selected_ops")]
+    for ac in cases:
+        loss, g, model = run(**ac)
+        assert loss == loss0, ac
+        for n in g0:
+            torch.testing.assert_close(g[n], g0[n], rtol=1e-5, atol=1e-7, msg=f"{ac}: {n}")
+    # what got wrapped: sub-modules by name at any depth; a whole block goes through the block-level path
+    _, _, model = run(mode="selected_modules", modules=["blocks.*.feed_forward", "blocks.1"])
+    assert getattr(model.blocks["1"], "_activation_checkpointing", False)
+    assert model.blocks["0"].feed_forward._checkpointed_forward is not None
+    assert getattr(model.blocks["1"].feed_forward, "_checkpointed_forward", None) is None  # inside a selected block
+    _, _, model = run(mode="selected_ops")
+    assert all(b.feed_forward.recompute_activation for b in model.blocks.values())
+    import pytest
+
+    with pytest.raises(ValueError):
+        run(mode="selected_modules", modules=["no.such.module"])
