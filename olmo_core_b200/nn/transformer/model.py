@@ -390,6 +390,15 @@ class Transformer(nn.Module):
         return self.lm_head(h, **head_kwargs)
 
     def _run_block(self, block: nn.Module, h: torch.Tensor, kwargs: Dict[str, Any]) -> torch.Tensor:
+        if h.is_cuda:
+            from ...ops import _lib
+
+            if _lib.nvtx_enabled():
+                with torch.cuda.nvtx.range(f"block.{getattr(block, 'block_idx', '?')}"):
+                    return self._run_block_inner(block, h, kwargs)
+        return self._run_block_inner(block, h, kwargs)
+
+    def _run_block_inner(self, block: nn.Module, h: torch.Tensor, kwargs: Dict[str, Any]) -> torch.Tensor:
         if getattr(block, "_activation_checkpointing", False) and self.training and torch.is_grad_enabled():
             from torch.utils.checkpoint import checkpoint
 

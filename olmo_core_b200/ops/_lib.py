@@ -9,6 +9,7 @@ PyTorch kernels. On CPU-only machines nothing is loaded and the ops use their Py
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
@@ -17,7 +18,7 @@ import torch
 
 from .build import LIB_PATH
 
-_lib: Optional[ctypes.CDLL] = None
+_lib: Optional["_Library"] = None
 _lock = threading.Lock()
 
 DT_BF16 = 0
@@ -98,12 +99,55 @@ _OPTIONAL_SIGS = {
 }
 
 
+class _Library:
+    """
+    The loaded kernel library. Entry points resolve once and are cached as plain attributes. With NVTX ranges switched
+    on (:func:`set_nvtx`, or ``OLMO_CORE_B200_NVTX=1`` in the environment) every launcher call is bracketed by a range
+    named after its entry point, so a timeline shows which op issued which kernels.
+    """
+
+    def __init__(self, handle: ctypes.CDLL):
+        object.__setattr__(self, "_handle", handle)
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._handle, name)
+        if _nvtx_enabled and callable(fn):
+            raw = fn
+
+            def fn(*args, _raw=raw, _name=name):  # type: ignore[no-redef]
+                torch.cuda.nvtx.range_push(_name)
+                try:
+                    return _raw(*args)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+
+            fn.argtypes, fn.restype = raw.argtypes, raw.restype  # type: ignore[attr-defined]
+        object.__setattr__(self, name, fn)
+        return fn
+
+
+_nvtx_enabled = os.environ.get("OLMO_CORE_B200_NVTX", "0") not in ("0", "")
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Switch NVTX ranges around the kernel launchers (and around transformer blocks) on or off."""
+    global _nvtx_enabled
+    _nvtx_enabled = bool(enabled)
+    if isinstance(_lib, _Library):
+        for name in [k for k in vars(_lib) if k != "_handle"]:
+            object.__delattr__(_lib, name)
+
+
+def nvtx_enabled() -> bool:
+    return _nvtx_enabled
+
+
 def available() -> bool:
     """True when the CUDA kernels should be used (a CUDA device is present)."""
     return torch.cuda.is_available()
 
 
-def lib() -> ctypes.CDLL:
+def lib() -> "_Library":
     global _lib
     if _lib is not None:
         return _lib
@@ -120,13 +164,13 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = c_int
-        _lib = handle
+        _lib = _Library(handle)
     return _lib
 
 
 def register_signature(name: str, argtypes) -> None:
     """Declare the signature of an additional entry point (used by ops that live in their own .cu)."""
-    fn = getattr(lib(), name)
+    fn = getattr(lib()._handle, name)
     fn.argtypes = argtypes
     fn.restype = c_int
 

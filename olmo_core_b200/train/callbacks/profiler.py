@@ -33,6 +33,8 @@ class ProfilerCallback(Callback):
     profile_memory: bool = False
     enable_cuda_sync_events: bool = False
     enabled: bool = True
+    nvtx: bool = True
+    """Bracket every kernel launcher call and every transformer block with an NVTX range while profiling."""
     ranks: Optional[str] = None
     """``None``: rank 0 only; ``"all"``; or ``"dp"|"tp"|"cp"|"pp"|"ep"``: the first rank of each such group."""
 
@@ -71,6 +73,11 @@ class ProfilerCallback(Callback):
 
             experimental = _ExperimentalConfig(enable_cuda_sync_events=True)
         self._exit_stack = ExitStack()
+        if self.nvtx and self.trainer.device.type == "cuda":
+            from ...ops import _lib
+
+            _lib.set_nvtx(True)
+            self._exit_stack.callback(_lib.set_nvtx, False)
         self._profiler = self._exit_stack.enter_context(profile(
             activities=activities, record_shapes=False, profile_memory=self.profile_memory, with_stack=self.with_stack,
             schedule=schedule(wait=self.wait, warmup=self.warmup, active=self.active, repeat=self.repeat,
