@@ -338,14 +338,17 @@ class Attention(SequenceMixer):
                 return False
         return (self.q_norm is None) == (self.k_norm is None)
 
-    def _norm_rope_fused(self, q, k, T, start_pos, pos_sin, pos_cos, cu_doc_lens):
+    def _norm_rope_fused(self, q, k, T, start_pos, pos_sin, pos_cos, cu_doc_lens, rope_pos_ids=None):
         assert isinstance(self.rope, RotaryEmbedding)
         offset = int(start_pos) if start_pos is not None else 0
         if pos_sin is None or pos_cos is None:
-            bufs = self.rope.get_buffers(offset + T, q.device)
+            need = offset + T if rope_pos_ids is None else int(getattr(self, "_rope_table_len", None) or offset + T)
+            bufs = self.rope.get_buffers(need, q.device)
             pos_sin, pos_cos = bufs.pos_sin, bufs.pos_cos
         pos_ids = None
-        if cu_doc_lens is not None:
+        if rope_pos_ids is not None:
+            pos_ids = rope_pos_ids.reshape(-1).to(device=q.device, dtype=torch.int32)
+        elif cu_doc_lens is not None:
             flat = torch.arange(q.shape[0] * T, device=q.device, dtype=cu_doc_lens.dtype)
             doc = torch.bucketize(flat, cu_doc_lens[1:], right=True)
             pos_ids = (flat - cu_doc_lens[doc]).to(torch.int32)
@@ -371,16 +374,25 @@ class Attention(SequenceMixer):
         pos_cos: Optional[torch.Tensor] = None,
         freqs_cis: Optional[torch.Tensor] = None,
         cache_leftpad: Optional[torch.Tensor] = None,
+        rope_pos_ids: Optional[torch.Tensor] = None,
+        rope_table_len: Optional[int] = None,
     ) -> torch.Tensor:
+        """
+        ``rope_pos_ids`` (int ``[B, T]``) gives the rotary position of every token explicitly; a context-parallel shard of
+        packed documents needs it (positions restart per document and the shard is not a contiguous range), together
+        with ``rope_table_len``, the length of the whole sequence.
+        """
         B, T, _ = x.shape
         hd = self.head_dim
         q, k, v = multi_linear(x, (self.w_q, self.w_k, self.w_v))
         start_pos = self.kv_cache_manager.current_position() if self.kv_cache_manager is not None else None
-        if self.cp_enabled and self.rope is not None and pos_sin is None and pos_cos is None and freqs_cis is None:
+        if (self.cp_enabled and self.rope is not None and pos_sin is None and pos_cos is None and freqs_cis is None
+                and rope_pos_ids is None):
             raise RuntimeError("RoPE buffers must be passed to attention after being sharded by the context-parallel load balancer")
+        self._rope_table_len = rope_table_len
 
         if self._fusable(x, start_pos, freqs_cis):
-            q, k = self._norm_rope_fused(q, k, T, start_pos, pos_sin, pos_cos, cu_doc_lens)
+            q, k = self._norm_rope_fused(q, k, T, start_pos, pos_sin, pos_cos, cu_doc_lens, rope_pos_ids)
             q, k, v = q.view(B, T, -1, hd), k.view(B, T, -1, hd), v.view(B, T, -1, hd)
         else:
             if self.clip_qkv is not None:
@@ -397,8 +409,11 @@ class Attention(SequenceMixer):
                 if self.k_norm is not None:
                     k = self.k_norm(k)
             if self.rope is not None:
-                q, k = self.rope(q, k, head_first=False, start_pos=start_pos, pos_sin=pos_sin, pos_cos=pos_cos,
-                                 freqs_cis=freqs_cis, cu_doc_lens=cu_doc_lens)
+                if rope_pos_ids is not None:
+                    q, k = self.rope(q, k, head_first=False, pos_ids=rope_pos_ids, table_len=rope_table_len)
+                else:
+                    q, k = self.rope(q, k, head_first=False, start_pos=start_pos, pos_sin=pos_sin, pos_cos=pos_cos,
+                                     freqs_cis=freqs_cis, cu_doc_lens=cu_doc_lens)
 
         att = self.backend(
             (q, k, v),

@@ -144,15 +144,15 @@ def dispatch_ring_flash_attn(q, k, v, *, group: dist.ProcessGroup, strategy, cu_
     del heads_k_stride, local_k_slice, max_seqlen, max_seqlen_q, max_seqlen_k
     if dropout_p:
         raise NotImplementedError("dropout is not supported with context parallelism")
-    if any(x is not None for x in (cu_seqlens, cu_seqlens_q, cu_seqlens_k)):
-        raise NotImplementedError("packed documents are not supported with context parallelism yet")
+    if cu_seqlens_q is not None or cu_seqlens_k is not None:
+        raise NotImplementedError("pass the document boundaries of the whole sequence as `cu_seqlens`")
     if not causal:
         raise NotImplementedError("context-parallel attention is causal")
     zig_zag = RingAttentionLoadBalancerType(strategy) == RingAttentionLoadBalancerType.zig_zag
     style = RingContextParallelStyle.zig_zag() if zig_zag else RingContextParallelStyle.llama3()
     backend = TorchAttentionBackend(head_dim=q.shape[-1], n_heads=q.shape[2], n_kv_heads=k.shape[2], scale=softmax_scale,
                                     window_size=window_size)
-    return ring_attention(backend, q, k, v, group=group, style=style)
+    return ring_attention(backend, q, k, v, group=group, style=style, cu_doc_lens=cu_seqlens)
 
 
 def dispatch_ring_flash_attn_qkvpacked(qkv: torch.Tensor, *, group: dist.ProcessGroup, strategy, **kwargs) -> torch.Tensor:

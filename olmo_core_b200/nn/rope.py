@@ -282,11 +282,24 @@ class RotaryEmbedding(RotaryEmbeddingBase):
         pos_cos: Optional[torch.Tensor] = None,
         freqs_cis: Optional[torch.Tensor] = None,
         cu_doc_lens: Optional[torch.Tensor] = None,
+        pos_ids: Optional[torch.Tensor] = None,
+        table_len: Optional[int] = None,
     ) -> Tuple[torch.Tensor, torch.Tensor]:
         """
         ``q``/``k``: ``[B, H, T, D]`` when ``head_first`` else ``[B, T, H, D]``. ``start_pos`` is the absolute
-        position of the first token (decoding); ``cu_doc_lens`` restarts positions at each packed document.
+        position of the first token (decoding); ``cu_doc_lens`` restarts positions at each packed document;
+        ``pos_ids`` (int ``[B, T]``) names every token's position outright (tables of ``table_len`` rows).
         """
+        if pos_ids is not None:
+            seq_dim = 2 if head_first else 1
+            qf, kf = (q.float(), k.float()) if self.full_precision else (q, k)
+            with torch.autocast(q.device.type, enabled=False):
+                ids = pos_ids.to(q.device).long()
+                ps, pc = self._tables(int(table_len or (int(ids.max()) + 1)), q.device)
+                s_, c_ = ps.type_as(qf)[ids], pc.type_as(qf)[ids]  # [B, T, D]
+                s_, c_ = (s_.unsqueeze(1), c_.unsqueeze(1)) if head_first else (s_.unsqueeze(2), c_.unsqueeze(2))
+                qf, kf = self._rotate(qf, s_, c_), self._rotate(kf, s_, c_)
+            return qf.type_as(q), kf.type_as(k)
         if freqs_cis is not None:
             raise RuntimeError(f"'freqs_cis' is invalid for {self.__class__.__name__}")
         if cu_doc_lens is not None and start_pos is not None:

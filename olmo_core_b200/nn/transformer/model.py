@@ -303,7 +303,7 @@ class Transformer(nn.Module):
             for key, block in self.blocks.items():
                 att = block.attention
                 rope = getattr(att, "rope", None)
-                if rope is None:
+                if rope is None or cu_doc_lens is not None:  # packed documents: explicit positions instead (below)
                     continue
                 bufs = rope.get_buffers(S, torch.device("cpu"))
                 for name in ("pos_sin", "pos_cos", "freqs_cis"):
@@ -313,15 +313,23 @@ class Transformer(nn.Module):
                         seq_dims.append(0)
                         pad_values.append(0.0)
                         rope_keys.append((int(key), name))
+            # The sequence is sharded by POSITION whatever it contains; with packed documents every rank additionally gets
+            # the document boundaries of the whole sequence and the attention kernels mask by them (the reference shards
+            # document by document instead, src/olmo_core/nn/transformer/model.py:426-499; the attended pairs are the same).
             if cu_doc_lens is not None:
-                if B != 1:
-                    raise RuntimeError("intra-document masking with context parallelism needs a batch size of 1")
-                shards, extra = lb.batch_shard_by_document(inputs=inputs, seq_dims=seq_dims, cu_doc_lens=cu_doc_lens.cpu(),
-                                                           pad_values=pad_values, length_multiple=16)
-                for k, v in extra.items():
-                    block_kwargs[k] = move_to_device(v, self.device) if torch.is_tensor(v) else v
-            else:
-                shards = lb.batch_shard(inputs=inputs, seq_dims=seq_dims, pad_values=pad_values)
+                # rotary positions restart at every document; each rank gets the positions of ITS tokens
+                cu_cpu = cu_doc_lens.cpu().long()
+                flat = torch.arange(B * S, dtype=torch.long)
+                doc = torch.bucketize(flat, cu_cpu[1:], right=True).clamp(max=cu_cpu.numel() - 2)
+                inputs.append((flat - cu_cpu[doc]).view(B, S))
+                seq_dims.append(1)
+                pad_values.append(0)
+            shards = lb.batch_shard(inputs=inputs, seq_dims=seq_dims, pad_values=pad_values)
+            if cu_doc_lens is not None:
+                block_kwargs["cu_doc_lens"] = move_to_device(cu_doc_lens, self.device)
+                block_kwargs["max_doc_len"] = max_doc_len
+                block_kwargs["rope_pos_ids"] = move_to_device(shards.pop(), self.device)
+                block_kwargs["rope_table_len"] = S
             input_ids = shards[0]
             n = 1
             if labels is not None:

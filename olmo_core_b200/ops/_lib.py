@@ -46,7 +46,7 @@ _SIGS = {
     "ocb_gemm_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                             c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
     "ocb_peer_gather_segments": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
-    "ocb_peer_scatter_add_segments": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p],
+    "ocb_peer_pull_reduce_segments": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p],
     "ocb_peer_barrier_flag_words": [],
     "ocb_peer_barrier": [c_void_p, c_int, c_int, c_int, ctypes.c_uint, c_longlong, c_int, c_void_p, c_void_p],
     "ocb_grouped_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,

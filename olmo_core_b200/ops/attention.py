@@ -68,8 +68,10 @@ def attention_reference(
     cu_seqlens_k: Optional[torch.Tensor] = None,
     scale: Optional[float] = None,
     dropout_p: float = 0.0,
+    doc_ids: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
 ) -> torch.Tensor:
-    """fp32 masked-softmax attention; returns ``[B, Tq, H, D]`` in ``q.dtype``."""
+    """fp32 masked-softmax attention; returns ``[B, Tq, H, D]`` in ``q.dtype``. ``doc_ids`` gives the document of every
+    query and of every key (``[B, Tq]``, ``[B, Tk]``) directly, for queries that are not the last ``Tq`` positions."""
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -81,7 +83,9 @@ def attention_reference(
         kf = kf.repeat_interleave(rep, dim=1)
         vf = vf.repeat_interleave(rep, dim=1)
     dq = dk = None
-    if cu_seqlens is not None:
+    if doc_ids is not None:
+        dq, dk = doc_ids
+    elif cu_seqlens is not None:
         dq = _doc_ids(cu_seqlens, B, Tq)
         dk = _doc_ids(cu_seqlens_k if cu_seqlens_k is not None else cu_seqlens, B, Tk)
     mask = build_attention_mask(Tq, Tk, q.device, causal=causal, window_size=window_size, doc_ids_q=dq, doc_ids_k=dk)
@@ -146,8 +150,8 @@ def _visibility_bounds(B: int, T: int, window: int, cu_seqlens: Optional[torch.T
     int32 ``[B * Tq + B * Tk]`` for the flash kernels: per query the lowest visible key, then per key the position of the
     last query that sees it (key indices / query positions inside the ``Tk``-long sequence). One pair of arrays expresses
     sliding windows, document boundaries and both together; ``None`` when neither applies. Documents never span two rows
-    of the batch (``cu_seqlens`` counts over ``B * T``) and need ``Tq == Tk``. ``q_pos`` (int64 ``[Tq]``) gives the
-    queries' positions when they are not the last ``Tq`` of the sequence (a shard of a context-parallel group).
+    of the batch (``cu_seqlens`` counts over ``B * Tk``). ``q_pos`` (int64 ``[Tq]``) gives the queries' positions when
+    they are not the last ``Tq`` of the sequence (a shard of a context-parallel group).
     """
     if not window and cu_seqlens is None:
         return None
@@ -159,13 +163,15 @@ def _visibility_bounds(B: int, T: int, window: int, cu_seqlens: Optional[torch.T
     lo = torch.zeros_like(tq)
     hi = torch.full_like(tk, Tk - 1)
     if cu_seqlens is not None:
-        assert T == Tk, "document boundaries need queries and keys of one length"
-        flat = torch.arange(B * T, device=device, dtype=torch.int64)
+        # documents are ranges of the flattened [B * Tk] sequence; a query's document follows from its position
         cu = cu_seqlens.to(device=device, dtype=torch.int64)
-        doc = torch.bucketize(flat, cu[1:], right=True).clamp(max=cu.numel() - 2)
-        base = flat - tk
-        lo = torch.maximum(lo, cu[doc] - base)
-        hi = torch.minimum(hi, cu[doc + 1] - 1 - base)
+        rows = torch.arange(B, device=device, dtype=torch.int64)
+        base_q = rows.repeat_interleave(tq.numel() // B) * Tk
+        base_k = rows.repeat_interleave(Tk) * Tk
+        doc_q = torch.bucketize(base_q + tq, cu[1:], right=True).clamp(max=cu.numel() - 2)
+        doc_k = torch.bucketize(base_k + tk, cu[1:], right=True).clamp(max=cu.numel() - 2)
+        lo = torch.maximum(lo, cu[doc_q] - base_q)
+        hi = torch.minimum(hi, cu[doc_k + 1] - 1 - base_k)
     if window:
         lo = torch.maximum(lo, tq - (window - 1))
         hi = torch.minimum(hi, tk + (window - 1))
@@ -261,7 +267,7 @@ class _ShardedFlashAttention(torch.autograd.Function):
     """Attention of local queries over keys / values that stay on their owners (see :func:`sharded_attention`)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, exchange, layout, scale: float, window: int):  # type: ignore[override]
+    def forward(ctx, q, k, v, exchange, layout, scale: float, window: int, cu_seqlens=None):  # type: ignore[override]
         B, Tq, H, D = q.shape
         T_local, Hkv = k.shape[1], k.shape[2]
         Tk = layout.kv_chunk_tiles * 128 * len(layout.kv_chunks)
@@ -269,7 +275,7 @@ class _ShardedFlashAttention(torch.autograd.Function):
         k_ptrs, v_ptrs, n_src, rows_src, kv_layout = exchange.publish(k, v, layout, window or None)
         out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
-        bounds = _visibility_bounds(B, Tq, window, None, q.device, Tk=Tk, q_pos=layout.query_positions(q.device)[:Tq])
+        bounds = _visibility_bounds(B, Tq, window, cu_seqlens, q.device, Tk=Tk, q_pos=layout.query_positions(q.device)[:Tq])
         ld_kv = Hkv * D
         rc = _lib.lib().ocb_attention_fwd_sharded(
             q.data_ptr(), k_ptrs, v_ptrs, n_src, rows_src, kv_layout, out.data_ptr(), lse.data_ptr(),
@@ -306,33 +312,37 @@ class _ShardedFlashAttention(torch.autograd.Function):
         )
         _lib.check(rc, "ocb_attention_bwd_sharded")
         dk, dv = exchange.reduce_to_owners(dk_all, dv_all, window or None)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
 def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, exchange, layout: ShardedSequenceLayout,
-                      scale: Optional[float] = None, window_size: Optional[int] = None) -> torch.Tensor:
+                      scale: Optional[float] = None, window_size: Optional[int] = None,
+                      cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """
     Causal attention of this rank's queries ``q [B, T_local, H, 128]`` over the whole sequence of a context-parallel
     group. ``k, v [B, T_local, Hkv, 128]`` are this rank's keys / values. ``exchange``
     (:class:`olmo_core_b200.parallel.context.KVExchange`) moves them through peer-mapped memory -- pushed once into every
     rank's sequence-ordered buffer, or left with their owner and read tile by tile by the kernels -- and tells the
     kernels where each key / value tile is. Sliding windows are supported; key / value gradients are summed onto
-    their owners by ``exchange.reduce_to_owners``.
+    their owners by ``exchange.reduce_to_owners``. ``cu_seqlens`` are the cumulative document lengths of the WHOLE
+    (unsharded, flattened ``[B * T]``) sequence: tokens only attend inside their document, wherever its pieces live.
     """
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    return _ShardedFlashAttention.apply(q, k, v, exchange, layout, scale, int(window_size or 0))
+    return _ShardedFlashAttention.apply(q, k, v, exchange, layout, scale, int(window_size or 0), cu_seqlens)
 
 
-def _sdpa_path(q, k, v, *, causal, window_size, cu_seqlens, cu_seqlens_k, scale, dropout_p):
+def _sdpa_path(q, k, v, *, causal, window_size, cu_seqlens, cu_seqlens_k, scale, dropout_p, doc_ids=None):
     """Masked ``scaled_dot_product_attention``: used for dtypes / head sizes the flash kernel does not take."""
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
     mask = None
-    is_causal = causal and Tq == Tk and window_size is None and cu_seqlens is None
-    if not is_causal and (causal or window_size is not None or cu_seqlens is not None):
+    is_causal = causal and Tq == Tk and window_size is None and cu_seqlens is None and doc_ids is None
+    if not is_causal and (causal or window_size is not None or cu_seqlens is not None or doc_ids is not None):
         dq = dk = None
-        if cu_seqlens is not None:
+        if doc_ids is not None:
+            dq, dk = doc_ids
+        elif cu_seqlens is not None:
             dq = _doc_ids(cu_seqlens, B, Tq)
             dk = _doc_ids(cu_seqlens_k if cu_seqlens_k is not None else cu_seqlens, B, Tk)
         mask = build_attention_mask(Tq, Tk, q.device, causal=causal, window_size=window_size, doc_ids_q=dq, doc_ids_k=dk)

@@ -1,7 +1,9 @@
 """
 Micro-benchmarks of the sm_100a kernels against their library counterparts.
 
-``python -m olmo_core_b200.ops.bench_kernels <gemm|attention|norm> [--iters N] [--profile]``
+``python -m olmo_core_b200.ops.bench_kernels <case> [--iters N] [--profile]`` with ``case`` one of ``gemm``, ``mlp`` (gated
+MLP with the activation in the GEMM epilogues), ``fp8``, ``grouped``, ``attention``, ``norm``, ``norm_rope``,
+``swiglu``, ``ce``, ``adamw``, ``router``.
 
 Each case is timed with CUDA events on the launching stream after warm-up, with a buffer larger than L2 rewritten
 between iterations, and printed as one JSON line per case: milliseconds, achieved TFLOP/s or GB/s, and the same
@@ -146,16 +148,228 @@ def bench_norm(args, peaks) -> None:
                "bwd_gbs": round(1.5 * nbytes / t_b / 1e6, 1)}, peaks)
 
 
+def bench_mlp(args, peaks) -> None:
+    """Gated MLP of a 7B layer: fused up-projection (a | b and silu(a) * b in one epilogue) and fused backward through it."""
+    from . import _lib
+    from .elementwise import swiglu
+    from .gemm import gemm
+
+    M, H, K = 8192, 11008, 4096
+    L = _lib.lib()
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w13 = torch.randn(2 * H, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    w2 = torch.randn(K, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    dy = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    ab = torch.empty(M, 2 * H, device="cuda", dtype=torch.bfloat16)
+    dab = torch.empty_like(ab)
+    h = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    st = _lib.status_buffer(torch.device("cuda")).data_ptr()
+
+    def fused_fwd():
+        _lib.check(L.ocb_gemm_swiglu_fwd(x.data_ptr(), w13.data_ptr(), ab.data_ptr(), h.data_ptr(), M, H, K, K, K, 2 * H, H,
+                                         st, _lib.stream_ptr()), "ocb_gemm_swiglu_fwd")
+
+    def fused_bwd():
+        _lib.check(L.ocb_gemm_swiglu_bwd(dy.data_ptr(), w2.data_ptr(), ab.data_ptr(), dab.data_ptr(), None, M, H, K, K, H,
+                                         2 * H, 2 * H, H, st, _lib.stream_ptr()), "ocb_gemm_swiglu_bwd")
+
+    a_, b_ = ab[:, :H], ab[:, H:]
+
+    def unfused_fwd():
+        gemm(x, w13[:H], trans_b=True, out=a_)
+        gemm(x, w13[H:], trans_b=True, out=b_)
+        with torch.no_grad():
+            swiglu(a_.contiguous(), b_.contiguous())
+
+    if args.profile:
+        fused_fwd()
+        fused_bwd()
+        torch.cuda.synchronize()
+        return
+    for name, fn, flops in (("mlp_up_fused_swiglu", fused_fwd, 2.0 * M * 2 * H * K),
+                            ("mlp_up_two_gemms_plus_swiglu_kernel", unfused_fwd, 2.0 * M * 2 * H * K),
+                            ("mlp_down_dgrad_fused_swiglu_bwd", fused_bwd, 2.0 * M * H * K)):
+        t = time_ms(fn, args.iters)
+        _emit({"kernel": name, "M": M, "H": H, "K": K, "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)}, peaks)
+    _lib.check_device_status()
+
+
+def bench_fp8(args, peaks) -> None:
+    from .fp8 import gemm_fp8, quantize_colwise_transposed, quantize_rowwise
+
+    M, N, K = 8192, 4096, 4096
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    aq, asc = quantize_rowwise(a)
+    wq, wsc = quantize_rowwise(w)
+    if args.profile:
+        quantize_rowwise(a)
+        quantize_colwise_transposed(a)
+        gemm_fp8(aq, asc, wq, wsc)
+        torch.cuda.synchronize()
+        return
+    t = time_ms(lambda: gemm_fp8(aq, asc, wq, wsc), args.iters)
+    _emit({"kernel": "gemm_e4m3_rowwise", "M": M, "N": N, "K": K, "ms": round(t, 4),
+           "tflops": round(2.0 * M * N * K / t / 1e9, 1)}, None)
+    for name, fn in (("quantize_e4m3_rowwise", lambda: quantize_rowwise(a)),
+                     ("quantize_e4m3_colwise_transposed", lambda: quantize_colwise_transposed(a))):
+        t = time_ms(fn, args.iters)
+        _emit({"kernel": name, "rows": M, "cols": K, "ms": round(t, 4), "gbs": round(M * K * 3.0 / t / 1e6, 1)}, peaks)
+
+
+def bench_grouped(args, peaks) -> None:
+    """Expert MLP shapes of OLMoE-1B-7B: 64 experts, d_model 2048, hidden 1024, 32768 x 8 routed rows."""
+    from .gemm import grouped_gemm, grouped_gemm_wgrad
+
+    E, D, Hh, R = 64, 2048, 1024, 32768 * 8
+    x = torch.randn(R, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E * Hh, D, device="cuda", dtype=torch.bfloat16) * 0.02
+    counts = torch.full((E,), R // E, dtype=torch.int32, device="cuda")
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int32, device="cuda"), counts.cumsum(0).to(torch.int32)])
+    g = torch.randn(R, Hh, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(E * Hh, D, device="cuda", dtype=torch.float32)
+    if args.profile:
+        grouped_gemm(x, w, offsets, trans_b=True)
+        grouped_gemm_wgrad(g, x, offsets, dw, accumulate=True)
+        torch.cuda.synchronize()
+        return
+    flops = 2.0 * R * Hh * D
+    t = time_ms(lambda: grouped_gemm(x, w, offsets, trans_b=True), args.iters)
+    _emit({"kernel": "grouped_gemm_rows", "experts": E, "rows": R, "N": Hh, "K": D, "ms": round(t, 4),
+           "tflops": round(flops / t / 1e9, 1)}, peaks)
+    t = time_ms(lambda: grouped_gemm_wgrad(g, x, offsets, dw, accumulate=True), args.iters)
+    _emit({"kernel": "grouped_gemm_wgrad_f32acc", "experts": E, "rows": R, "M": Hh, "N": D, "ms": round(t, 4),
+           "tflops": round(flops / t / 1e9, 1)}, peaks)
+
+
+def bench_norm_rope(args, peaks) -> None:
+    from .elementwise import norm_rope
+
+    B, S, H, D = 2, 4096, 32, 128
+    x = torch.randn(B, S, H * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(H * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    pos = torch.arange(S, device="cuda", dtype=torch.float32)[:, None]
+    inv = 1.0 / (500000 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+    ang = torch.cat([pos * inv, pos * inv], dim=-1)
+    sin, cos = ang.sin().contiguous(), ang.cos().contiguous()
+    g = torch.randn_like(x)
+    if args.profile:
+        norm_rope(x, w, sin, cos, H).backward(g)
+        torch.cuda.synchronize()
+        return
+    nbytes = 2.0 * x.numel() * 2
+    with torch.no_grad():
+        t_f = time_ms(lambda: norm_rope(x, w, sin, cos, H), args.iters)
+    out = norm_rope(x, w, sin, cos, H)
+    t_b = time_ms(lambda: torch.autograd.grad(out, (x, w), g, retain_graph=True), args.iters)
+    _emit({"kernel": "qk_norm_rope", "tokens": B * S, "width": H * D, "fwd_ms": round(t_f, 4), "gbs": round(nbytes / t_f / 1e6, 1),
+           "bwd_ms": round(t_b, 4), "bwd_gbs": round(1.5 * nbytes / t_b / 1e6, 1)}, peaks)
+
+
+def bench_swiglu(args, peaks) -> None:
+    from .elementwise import swiglu
+
+    rows, cols = 8192, 11008
+    a = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    if args.profile:
+        swiglu(a, b).backward(g)
+        torch.cuda.synchronize()
+        return
+    n = rows * cols * 2.0
+    with torch.no_grad():
+        t_f = time_ms(lambda: swiglu(a, b), args.iters)
+    out = swiglu(a, b)
+    t_b = time_ms(lambda: torch.autograd.grad(out, (a, b), g, retain_graph=True), args.iters)
+    _emit({"kernel": "swiglu_standalone", "rows": rows, "cols": cols, "fwd_ms": round(t_f, 4), "gbs": round(3 * n / t_f / 1e6, 1),
+           "bwd_ms": round(t_b, 4), "bwd_gbs": round(5 * n / t_b / 1e6, 1)}, peaks)
+
+
+def bench_ce(args, peaks) -> None:
+    """LM head + loss of the 7B model on one 8192-token micro-batch (vocabulary 100352)."""
+    from .loss import fused_linear_cross_entropy
+
+    T, V, D = 8192, 100352, 4096
+    h = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, D, device="cuda", dtype=torch.bfloat16) * 0.02).requires_grad_(True)
+    labels = torch.randint(0, V, (T,), device="cuda")
+
+    def step():
+        ce, z = fused_linear_cross_entropy(h, w, labels, z_loss_multiplier=1e-5)
+        (ce + z).backward()
+        h.grad = None
+        w.grad = None
+
+    if args.profile:
+        step()
+        torch.cuda.synchronize()
+        return
+    t = time_ms(step, max(3, args.iters // 2))
+    _emit({"kernel": "fused_linear_cross_entropy_fwd_bwd", "tokens": T, "vocab": V, "d_model": D, "ms": round(t, 4),
+           "tflops": round(3 * 2.0 * T * V * D / t / 1e9, 1)}, peaks)
+
+
+def bench_adamw(args, peaks) -> None:
+    from .optim import adamw_step_, sumsq
+
+    n = 202_391_552  # one 7B block
+    p, m, v, g = (torch.randn(n, device="cuda") * 0.01 for _ in range(4))
+    v.abs_()
+    lowp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    step = torch.ones((), device="cuda")
+
+    def run():
+        adamw_step_(p, m, v, g, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, step=step, lowp=lowp)
+
+    if args.profile:
+        run()
+        sumsq(g)
+        torch.cuda.synchronize()
+        return
+    t = time_ms(run, args.iters)
+    _emit({"kernel": "adamw_fp32_master_bf16_copy", "numel": n, "ms": round(t, 4), "gbs": round(n * 30.0 / t / 1e6, 1)}, peaks)
+    t = time_ms(lambda: sumsq(g), args.iters)
+    _emit({"kernel": "sum_of_squares", "numel": n, "ms": round(t, 4), "gbs": round(n * 4.0 / t / 1e6, 1)}, peaks)
+
+
+def bench_router(args, peaks) -> None:
+    from ..nn.moe.router import _FusedSoftmaxTopK
+    from .moe import indices_and_bins
+
+    N, E, k = 32768, 64, 8
+    logits = torch.randn(N, E, device="cuda", dtype=torch.bfloat16)
+    if args.profile:
+        _, _, ids, _ = _FusedSoftmaxTopK.apply(logits, k)
+        indices_and_bins(ids, E)
+        torch.cuda.synchronize()
+        return
+    with torch.no_grad():
+        t = time_ms(lambda: _FusedSoftmaxTopK.apply(logits, k), args.iters)
+        _emit({"kernel": "router_softmax_topk", "tokens": N, "experts": E, "top_k": k, "ms": round(t, 4),
+               "gbs": round((N * E * 6.0 + N * k * 8.0) / t / 1e6, 1)}, peaks)
+        ids = _FusedSoftmaxTopK.apply(logits, k)[2]
+        t = time_ms(lambda: indices_and_bins(ids, E), args.iters)
+        _emit({"kernel": "routing_counting_sort", "copies": N * k, "ms": round(t, 4)}, None)
+        t = time_ms(lambda: torch.sort(ids.reshape(-1), stable=True), args.iters)
+        _emit({"kernel": "routing_torch_sort_library", "copies": N * k, "ms": round(t, 4)}, None)
+
+
+CASES = {"gemm": bench_gemm, "mlp": bench_mlp, "fp8": bench_fp8, "grouped": bench_grouped, "attention": bench_attention,
+         "norm": bench_norm, "norm_rope": bench_norm_rope, "swiglu": bench_swiglu, "ce": bench_ce, "adamw": bench_adamw,
+         "router": bench_router}
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["gemm", "attention", "norm"])
+    ap.add_argument("case", choices=sorted(CASES))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--peaks", default=None)
     args = ap.parse_args(argv)
     peaks = json.load(open(args.peaks)) if args.peaks else None
     torch.manual_seed(0)
-    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm}[args.case](args, peaks)
+    CASES[args.case](args, peaks)
     assert math.isfinite(torch.cuda.memory_allocated())
 
 

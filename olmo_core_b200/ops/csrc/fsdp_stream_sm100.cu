@@ -2,20 +2,25 @@
 // memory (the reference gets both from FSDP2's per-block NCCL all-gather / reduce-scatter:
 // src/olmo_core/nn/transformer/model.py:859-935).
 //
-// Every rank keeps only its rows of every parameter: bf16 in `param_shard`, fp32 gradients in `grad_shard`, both in
-// symmetric memory with the same layout on every rank. A block's parameters are needed in full only while the block
-// computes, so they are assembled into a small local ring just in time:
+// Every rank keeps only its rows of every parameter: bf16 in `param_shard` (symmetric memory, the same layout on every
+// rank) and fp32 gradients in `grad_shard` (local). A block's parameters are needed in full only while the block computes,
+// so they are assembled into a small local ring just in time, and the block's full-size gradients sit in a ring slot
+// (symmetric memory again) only until the owners of the rows have collected them:
 //
 //   ocb_peer_gather_segments       full[seg.full_off + r * seg.n + i] = param_shard_r[seg.shard_off + i]   for all ranks r
 //                                  (plain loads from the owners' memory; runs on a side stream one block ahead of
 //                                  the GEMMs that consume the assembled weights)
-//   ocb_peer_scatter_add_segments  grad_shard_r[seg.shard_off + i] += scale * grad_full[seg.full_off + r * seg.n + i]
-//                                  with fire-and-forget fp32 reductions performed at the owner's L2, then the local
-//                                  full-size gradient block is cleared for the next block that uses the ring slot.
-//                                  No rank waits for any other: one barrier before the optimizer step is enough.
+//   ocb_peer_pull_reduce_segments  grad_shard[seg.shard_off + i] += scale * sum_r grad_full_r[seg.full_off + me * seg.n + i]
+//                                  every rank pulls ITS rows of the block's gradient out of all ranks' ring slots (plain
+//                                  loads, summed in rank order in registers: reproducible bit for bit) and accumulates
+//                                  them into its shard. The caller brackets the kernel with two stream barriers across
+//                                  the ranks (all ranks have finished the block's backward / all ranks have finished
+//                                  pulling, so the slots may be cleared and reused); both run on the side stream, behind
+//                                  the next block's backward. Pushing with fp32 reductions instead needs no barrier but
+//                                  reached only 165 GB/s here (reductions of 16 bytes at the owner's L2), against
+//                                  785 GB/s for plain loads.
 //
-// fp32 additions from different ranks arrive in no fixed order, so a reduced gradient is reproducible up to the rounding
-// of a `world`-term fp32 sum. Plain ld / st / red only: no TMA, no multimem.
+// Plain ld / st only: no TMA, no multimem, no atomics.
 
 #include "common.cuh"
 #include "ocb_api.h"
@@ -63,36 +68,36 @@ peer_gather_segments_kernel(StreamPeers shards, int world, const StreamSegment* 
 }
 
 __global__ void __launch_bounds__(kStreamThreads)
-peer_scatter_add_segments_kernel(StreamPeers grad_shards, int world, const StreamSegment* __restrict__ segs, int nseg,
-                                 float* __restrict__ grad_full, float scale) {
+peer_pull_reduce_segments_kernel(StreamPeers grad_fulls, int world, int rank, const StreamSegment* __restrict__ segs, int nseg,
+                                 float* __restrict__ grad_shard, float scale) {
   for (int s = 0; s < nseg; ++s) {
     const StreamSegment seg = segs[s];
     const long long n4 = seg.n >> 2;
-    const long long total = n4 * world;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+    const long long src_off = seg.full_off + static_cast<long long>(rank) * seg.n;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-      const int r = static_cast<int>(i / n4);
-      const long long j = i - r * n4;
-      float4* src = reinterpret_cast<float4*>(grad_full + seg.full_off + r * seg.n) + j;
-      const float4 v = *src;
-      *src = make_float4(0.f, 0.f, 0.f, 0.f);
-      float* dst = static_cast<float*>(grad_shards.p[r]) + seg.shard_off + 4 * j;
-      asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x * scale), "f"(v.y * scale),
-                   "f"(v.z * scale), "f"(v.w * scale)
-                   : "memory");
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float* src = static_cast<const float*>(grad_fulls.p[r]) + src_off + 4 * i;
+        float4 v;
+        asm volatile("ld.global.relaxed.sys.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src) : "memory");
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      float4* dst = reinterpret_cast<float4*>(grad_shard + seg.shard_off) + i;
+      float4 o = *dst;
+      o.x += acc.x * scale; o.y += acc.y * scale; o.z += acc.z * scale; o.w += acc.w * scale;
+      *dst = o;
     }
     const long long tail = seg.n & 3;
-    if (tail != 0 && blockIdx.x == 0) {
-      for (long long i = threadIdx.x; i < tail * world; i += blockDim.x) {
-        const int r = static_cast<int>(i / tail);
-        const long long j = (seg.n - tail) + (i - r * tail);
-        float* src = grad_full + seg.full_off + r * seg.n + j;
-        const float v = *src;
-        *src = 0.f;
-        asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(static_cast<float*>(grad_shards.p[r]) + seg.shard_off + j),
-                     "f"(v * scale)
-                     : "memory");
+    if (tail != 0 && blockIdx.x == 0 && threadIdx.x < tail) {
+      const long long j = (seg.n - tail) + threadIdx.x;
+      float acc = 0.f;
+      for (int r = 0; r < world; ++r) {
+        float v;
+        asm volatile("ld.global.relaxed.sys.f32 %0, [%1];" : "=f"(v) : "l"(static_cast<const float*>(grad_fulls.p[r]) + src_off + j) : "memory");
+        acc += v;
       }
+      grad_shard[seg.shard_off + j] += acc * scale;
     }
   }
 }
@@ -115,15 +120,15 @@ extern "C" int ocb_peer_gather_segments(void* const* shard_ptrs, int world, cons
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-// grad_shard_ptrs[r]: rank r's fp32 gradient shard as mapped on this GPU; grad_full: this GPU's full-size gradient
-// block, cleared by the kernel. scale: 1 / world for an average.
-extern "C" int ocb_peer_scatter_add_segments(void* const* grad_shard_ptrs, int world, const void* segs, int nseg,
-                                             void* grad_full, float scale, cudaStream_t stream) {
-  if (world < 1 || world > kStreamMaxRanks || nseg < 0) return -1;
+// grad_full_ptrs[r]: rank r's full-size fp32 gradient block (its ring slot) as mapped on this GPU; grad_shard: this
+// rank's shard, accumulated into. scale: 1 / world for an average. The slots are not modified.
+extern "C" int ocb_peer_pull_reduce_segments(void* const* grad_full_ptrs, int world, int rank, const void* segs, int nseg,
+                                             void* grad_shard, float scale, cudaStream_t stream) {
+  if (world < 1 || world > kStreamMaxRanks || rank < 0 || rank >= world || nseg < 0) return -1;
   if (nseg == 0) return 0;
   StreamPeers p;
-  for (int r = 0; r < world; ++r) p.p[r] = grad_shard_ptrs[r];
-  peer_scatter_add_segments_kernel<<<296, kStreamThreads, 0, stream>>>(p, world, static_cast<const StreamSegment*>(segs), nseg,
-                                                                       static_cast<float*>(grad_full), scale);
+  for (int r = 0; r < world; ++r) p.p[r] = grad_full_ptrs[r];
+  peer_pull_reduce_segments_kernel<<<296, kStreamThreads, 0, stream>>>(p, world, rank, static_cast<const StreamSegment*>(segs),
+                                                                       nseg, static_cast<float*>(grad_shard), scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

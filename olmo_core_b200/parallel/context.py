@@ -319,8 +319,10 @@ def ring_attention(backend, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *
     Causal attention of the local queries ``q [B, T_local, H, D]`` over the whole (sharded) sequence. ``backend`` is the
     attention backend whose ``_local`` computes attention on one device; ``style`` names the shard layout.
     """
-    if cu_doc_lens is not None or cu_doc_lens_q is not None or cu_doc_lens_k is not None:
-        raise NotImplementedError("document masking is not supported together with ring context parallelism yet")
+    if cu_doc_lens_q is not None or cu_doc_lens_k is not None:
+        raise NotImplementedError(
+            "per-rank document lengths are not used here: the sequence is sharded by position and `cu_doc_lens` holds "
+            "the document boundaries of the whole sequence")
     del local_k_slice
     from ..nn.attention.ring import RingAttentionLoadBalancerType
 
@@ -333,15 +335,30 @@ def ring_attention(backend, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *
         layout = ShardedSequenceLayout.for_rank(T_local, rank, cp, zig_zag)
         return sharded_attention(q, k.contiguous(), v.contiguous(), exchange=KVExchange.for_group(group, zig_zag),
                                  layout=layout, scale=getattr(backend, "scale", None),
-                                 window_size=getattr(backend, "window", None))
+                                 window_size=getattr(backend, "window", None), cu_seqlens=cu_doc_lens)
     k_all = _to_global_order(_AllGatherSeq.apply(k, group), cp, zig_zag)
     v_all = _to_global_order(_AllGatherSeq.apply(v, group), cp, zig_zag)
     outs = []
     offset = 0
+    docs = None
+    if cu_doc_lens is not None:
+        # document of every position of the whole sequence, [B, T]: tokens attend inside their document only
+        from ..ops.attention import _doc_ids
+
+        docs = _doc_ids(cu_doc_lens.to(q.device), q.shape[0], cp * T_local)
     for start, end in local_position_ranges(T_local, rank, cp, zig_zag):
         n = end - start
         q_chunk = q[:, offset: offset + n]
         # keys up to the chunk's last position; causal masking aligned at the end makes query i see keys <= start + i
-        outs.append(backend._local(q_chunk, k_all[:, :end], v_all[:, :end], causal=True))
+        if docs is None:
+            outs.append(backend._local(q_chunk, k_all[:, :end], v_all[:, :end], causal=True))
+        else:
+            from ..ops.attention import _sdpa_path, attention_reference
+
+            fn = _sdpa_path if q.is_cuda else attention_reference
+            kw = dict(dropout_p=0.0) if q.is_cuda else {}
+            outs.append(fn(q_chunk, k_all[:, :end], v_all[:, :end], causal=True, window_size=getattr(backend, "window", None),
+                           cu_seqlens=None, cu_seqlens_k=None, scale=getattr(backend, "scale", None),
+                           doc_ids=(docs[:, start:end], docs[:, :end]), **kw))
         offset += n
     return torch.cat(outs, dim=1) if len(outs) > 1 else outs[0]

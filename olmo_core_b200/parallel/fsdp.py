@@ -550,8 +550,6 @@ class ShardedParamRuntime:
         if self.streamed:
             self._flush_dirty_units()
             self._wait_comm()
-            if self._sym_shard_grad is not None:
-                self._sym_shard_grad.barrier()  # the reductions every peer sent into this rank's shard have landed
         self._reduce_gradients_nccl()
         self._sync_tensor_parallel_partials()
 
@@ -685,22 +683,29 @@ class ShardedParamRuntime:
         from .symmetric import SymmetricBuffer, symmetric_memory_enabled
 
         self._ring_lowp = [torch.zeros(self._unit_numel, dtype=lowp_dtype, device=device) for _ in range(2)]
-        self._ring_grad = [torch.zeros(self._unit_numel, dtype=self.reduce_dtype, device=device) for _ in range(2)]
+        self._sym_shard_lowp = self._sym_ring_grad = None
+        if peer_ok and device.type == "cuda" and symmetric_memory_enabled(device, self.group):
+            try:
+                import ctypes
+
+                self._sym_shard_lowp = SymmetricBuffer(self._master_numel, torch.bfloat16, device, self.group)
+                self._sym_ring_grad = SymmetricBuffer(2 * self._unit_numel, torch.float32, device, self.group)
+                base = [int(p) for p in self._sym_ring_grad.handle.buffer_ptrs]
+                self._ring_grad_peers = [(ctypes.c_void_p * len(base))(*[b + k * self._unit_numel * 4 for b in base])
+                                         for k in range(2)]
+            except Exception as e:
+                log.warning(f"Peer-mapped shards unavailable ({type(e).__name__}: {e}); streaming blocks with NCCL")
+                self._sym_shard_lowp = self._sym_ring_grad = None
+        if self._sym_ring_grad is not None:
+            flat = self._sym_ring_grad.tensor
+            self._ring_grad = [flat[: self._unit_numel], flat[self._unit_numel:]]
+            self.lowp_shard = self._sym_shard_lowp.tensor
+        else:
+            self._ring_grad = [torch.zeros(self._unit_numel, dtype=self.reduce_dtype, device=device) for _ in range(2)]
+            self.lowp_shard = torch.zeros(self._master_numel, dtype=lowp_dtype, device=device)
         # Saved-for-backward weight views would trip autograd's version check when their ring slot is refilled between
         # a block's forward and its backward (with the same values); `.data` aliases carry their own version counter.
         self._ring_lowp_raw = [t.data for t in self._ring_lowp]
-        self._sym_shard_lowp = self._sym_shard_grad = None
-        if peer_ok and device.type == "cuda" and symmetric_memory_enabled(device, self.group):
-            try:
-                self._sym_shard_lowp = SymmetricBuffer(self._master_numel, torch.bfloat16, device, self.group)
-                self._sym_shard_grad = SymmetricBuffer(self._master_numel, torch.float32, device, self.group)
-            except Exception as e:
-                log.warning(f"Peer-mapped shards unavailable ({type(e).__name__}: {e}); streaming blocks with NCCL")
-                self._sym_shard_lowp = self._sym_shard_grad = None
-        if self._sym_shard_grad is not None:
-            self.lowp_shard, self.grad_shard = self._sym_shard_lowp.tensor, self._sym_shard_grad.tensor
-        else:
-            self.lowp_shard = torch.zeros(self._master_numel, dtype=lowp_dtype, device=device)
         self._slot_unit = [-1, -1]  # which block's weights each ring slot holds (or is being filled with)
         self._slot_dirty = [-1, -1]  # which block's gradients sit unreduced in each gradient slot
         self._gather_done: List[Optional[torch.cuda.Event]] = [None, None]
@@ -715,7 +720,7 @@ class ShardedParamRuntime:
             block.register_full_backward_pre_hook(lambda m, grad_out, u=u: self._pre_backward(u))
             block.register_full_backward_hook(lambda m, grad_in, grad_out, u=u: self._post_backward(u))
         log.info(f"Sharded-parameter runtime streams {len(self.units)} blocks through a two-slot ring "
-                 f"({'peer memory' if self._sym_shard_grad is not None else 'collectives'}): {self.memory_summary()}")
+                 f"({'peer memory' if self._sym_ring_grad is not None else 'collectives'}): {self.memory_summary()}")
 
     def _wait_comm(self) -> None:
         if self._comm_stream is not None:
@@ -804,13 +809,17 @@ class ShardedParamRuntime:
         cur = torch.cuda.current_stream(self.device)
         self._comm_stream.wait_stream(cur)  # the block's backward has written all of its gradients
         with torch.cuda.stream(self._comm_stream):
-            if self._sym_shard_grad is not None:
+            if self._sym_ring_grad is not None:
                 from ..ops import _lib
 
-                rc = _lib.lib().ocb_peer_scatter_add_segments(self._sym_shard_grad.peer_ptrs, ws, self._unit_segs[u].data_ptr(),
-                                                              len(self.units[u]), src.data_ptr(), 1.0 / ws,
+                self._sym_ring_grad.barrier()  # every rank has finished this block's backward
+                rc = _lib.lib().ocb_peer_pull_reduce_segments(self._ring_grad_peers[k], ws, self.rank,
+                                                              self._unit_segs[u].data_ptr(), len(self.units[u]),
+                                                              self.grad_shard.data_ptr(), 1.0 / ws,
                                                               self._comm_stream.cuda_stream)
-                _lib.check(rc, "ocb_peer_scatter_add_segments")
+                _lib.check(rc, "ocb_peer_pull_reduce_segments")
+                self._sym_ring_grad.barrier()  # every rank has collected its rows: the slots may be cleared and reused
+                src.zero_()
             else:
                 for s in self.units[u]:
                     full = src[s.full_offset : s.full_offset + s.flat_numel]

@@ -35,7 +35,7 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streame
     )
     rt = tm.runtime
     if streamed == "1":
-        assert rt.streamed and (rt._sym_shard_grad is not None) == (symmetric == "1")
+        assert rt.streamed and (rt._sym_ring_grad is not None) == (symmetric == "1")
         norms = []
         gen = torch.Generator().manual_seed(100 + rank)
         for _ in range(steps):
@@ -174,7 +174,7 @@ def test_tensor_parallel_fused_collective_gemms():
     run_distributed_test(_tp_fused_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
 
 
-def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
+def _cp_in_kernel_worker(zig_zag: bool, window, mode: str, docs: bool = False):
     """Context-parallel attention with K / V exchanged over peer memory (pushed once, or read tile by tile from the
     owning GPU inside the attention kernels), against attention over the whole sequence."""
     import torch.distributed as dist
@@ -192,7 +192,10 @@ def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
     gen = torch.Generator().manual_seed(11)
     q, k, v, dout = (torch.randn(B, T, h, 128, generator=gen).to(dev, torch.bfloat16) for h in (H, Hkv, Hkv, H))
     qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
-    ref = attention_reference(qf, kf, vf, causal=True, window_size=window)
+    cu = None
+    if docs:  # packed documents across the shard boundaries, counted over the flattened [B * T] sequence
+        cu = torch.tensor([0, 300, 1100, 1900, T, T + 777, T + 1500, 2 * T], dtype=torch.int32, device=dev)
+    ref = attention_reference(qf, kf, vf, causal=True, window_size=window, cu_seqlens=cu)
     ref.backward(dout.float())
 
     class Style:
@@ -209,7 +212,7 @@ def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
     for _ in range(3):  # several calls: the two slots of the exchange buffer are reused
         ql, kl, vl = (t[:, rows].contiguous().requires_grad_(True) for t in (q, k, v))
         assert context._sharded_kernels_usable(ql, kl, dist.group.WORLD, zig_zag)
-        out = context.ring_attention(Backend(), ql, kl, vl, group=dist.group.WORLD, style=Style())
+        out = context.ring_attention(Backend(), ql, kl, vl, group=dist.group.WORLD, style=Style(), cu_doc_lens=cu)
         out.backward(dout[:, rows].contiguous())
         torch.cuda.synchronize()
         _lib.check_device_status(dev)
@@ -221,11 +224,13 @@ def _cp_in_kernel_worker(zig_zag: bool, window, mode: str):
 
 @pytest.mark.gpu
 @requires_multi_gpu
-@pytest.mark.parametrize("zig_zag,window,mode", [
-    (False, None, "push"), (True, None, "push"), (False, 300, "push"), (True, None, "direct"), (False, 300, "direct"),
+@pytest.mark.parametrize("zig_zag,window,mode,docs", [
+    (False, None, "push", False), (True, None, "push", False), (False, 300, "push", False), (True, None, "direct", False),
+    (False, 300, "direct", False), (True, None, "push", True), (False, 300, "push", True),
 ])
-def test_context_parallel_attention_over_peer_memory(zig_zag, window, mode):
-    run_distributed_test(_cp_in_kernel_worker, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(zig_zag, window, mode))
+def test_context_parallel_attention_over_peer_memory(zig_zag, window, mode, docs):
+    run_distributed_test(_cp_in_kernel_worker, world_size=2, backend="cuda:nccl,cpu:gloo",
+                         func_args=(zig_zag, window, mode, docs))
 
 
 def _ulysses_peer_worker():
