@@ -73,3 +73,35 @@ def test_code_export_round_trip(tmp_path):
     with pytest.raises(ValueError):
         build_documents_and_stats([{"file_contents": "x" * 20}], _Tok(), language="c", max_doc_tokens_before_eos=10)
     assert "python" in CODE_FRESH_LANGUAGES and get_export_dir_name("allenai/dolma2-tokenizer").endswith("dolma2-tokenizer")
+
+
+def test_reshard_checkpoint_script(tmp_path):
+    """Two shards in, three shards out (uneven split), same tensors."""
+    import torch
+
+    from olmo_core_b200.distributed.checkpoint import get_checkpoint_metadata, load_keys, save_state_dict
+    from olmo_core_b200.scripts.reshard_checkpoint import reshard
+
+    state = {"model": {"w": torch.arange(70.0).view(10, 7), "b": torch.ones(3)}, "optim": {"state.w.step": torch.tensor(5.0)}}
+    save_state_dict(str(tmp_path / "src"), state)
+    reshard(str(tmp_path / "src"), str(tmp_path / "dst"), ranks=3)
+    files = sorted(p.name for p in (tmp_path / "dst").iterdir() if p.name.endswith(".distcp"))
+    assert {f.split("_")[2] for f in files} == {"0", "1", "2"}
+    w, b, step = load_keys(str(tmp_path / "dst"), ["model.w", "model.b", "optim.state.w.step"])
+    assert torch.equal(w, state["model"]["w"]) and torch.equal(b, state["model"]["b"]) and float(step) == 5.0
+    assert set(get_checkpoint_metadata(str(tmp_path / "dst")).state_dict_metadata) == {"model.w", "model.b", "optim.state.w.step"}
+    reshard(str(tmp_path / "src"), str(tmp_path / "dst2"), ranks=2, skip_optimizer_state=True)
+    assert set(get_checkpoint_metadata(str(tmp_path / "dst2")).state_dict_metadata) == {"model.w", "model.b"}
+
+
+def test_compare_wandb_configs_on_local_files(tmp_path, capsys):
+    import json
+
+    from olmo_core_b200.scripts import compare_wandb_configs as cw
+
+    assert cw.run_path("https://wandb.ai/ai2/proj/runs/abc123?x=1") == "ai2/proj/abc123" and cw.run_path("a/b/c") == "a/b/c"
+    (tmp_path / "l.json").write_text(json.dumps({"model": {"d_model": 128, "n_layers": 2}, "seed": 1}))
+    (tmp_path / "r.json").write_text(json.dumps({"model": {"d_model": 256, "n_layers": 2}, "lr": 0.1}))
+    cw.main([str(tmp_path / "l.json"), str(tmp_path / "r.json")])
+    out = capsys.readouterr().out
+    assert "model.d_model: 128 -> 256" in out and "seed = 1" in out and "lr = 0.1" in out and "n_layers" not in out
