@@ -1,5 +1,5 @@
 """
-Memory and time of :class:`olmo_core_b200.nn.OutputDiscardCheckpoint` against plain autograd and against
+Memory and time of :class:`olmo_core_b200.nn.output_discard_checkpoint.OutputDiscardCheckpoint` against plain autograd and against
 ``torch.utils.checkpoint`` (the role of src/scripts/benchmark_odc.py)::
 
     python -m olmo_core_b200.scripts.benchmark_odc [--d-model 2048 --d-ff 8192 --batch 2 --seq 2048 --n-layers 4]
@@ -28,7 +28,7 @@ class _Layer(nn.Module):
 
     def forward(self, x):
         if self.mode == "odc":
-            from ..nn import OutputDiscardCheckpoint
+            from ..nn.output_discard_checkpoint import OutputDiscardCheckpoint
 
             odc = OutputDiscardCheckpoint()
             h = odc.checkpoint(lambda t: torch.nn.functional.silu(self.up(t)), x)  # the fat [tokens, d_ff] tensor
