@@ -52,6 +52,7 @@ class Recipe:
     full_activation_checkpointing: bool = False
     project: str = "OLMo-core"
     model_kwargs: Optional[Dict[str, Any]] = None
+    hybrid: bool = False  # three Gated-DeltaNet layers for every attention layer (the OLMo-hybrid layout)
 
 
 RECIPES: Dict[str, Recipe] = {
@@ -65,6 +66,22 @@ RECIPES: Dict[str, Recipe] = {
     "OLMo3-7B-long-context": Recipe("olmo3_7B", sequence_length=65536, global_batch_sequences=64, microbatch_sequences=1,
                                     lr=2e-4, warmup_steps=200, max_tokens=int(50e9), shard_degree=1, cp_degree=8,
                                     float8=True, project="OLMo3-7B-long-context"),
+    # -- the published OLMo-3 / OLMo-hybrid runs (src/scripts/official/): batch sizes in sequences of the recipe's length
+    "OLMo3-7B-midtrain": Recipe("olmo3_7B", sequence_length=8192, global_batch_sequences=256, microbatch_sequences=1,
+                                lr=0.00020712352850360292, warmup_steps=0, max_tokens=int(100e9), project="OLMo3-7B-midtrain"),
+    "OLMo3-32B": Recipe("olmo3_32B", sequence_length=8192, global_batch_sequences=1024, microbatch_sequences=1, lr=6e-4,
+                        max_tokens=int(5.5e12), shard_degree=64, full_activation_checkpointing=True, project="OLMo3-32B"),
+    "OLMo3-32B-midtrain": Recipe("olmo3_32B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
+                                 lr=0.0002071235285, warmup_steps=0, max_tokens=int(100e9), shard_degree=64,
+                                 full_activation_checkpointing=True, project="OLMo3-32B-midtrain"),
+    "OLMo3-32B-long-context": Recipe("olmo3_32B", sequence_length=65536, global_batch_sequences=128, microbatch_sequences=1,
+                                     lr=0.0002071235285, warmup_steps=200, max_tokens=int(100e9), shard_degree=8, cp_degree=8,
+                                     full_activation_checkpointing=True, float8=True, project="OLMo3-32B-long-context"),
+    "OLMo-hybrid-7B": Recipe("olmo3_7B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
+                             hybrid=True, project="OLMo-hybrid-7B"),
+    "OLMo-hybrid-7B-midtrain": Recipe("olmo3_7B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
+                                      lr=0.00020712352850360292, warmup_steps=0, max_tokens=int(100e9), hybrid=True,
+                                      project="OLMo-hybrid-7B-midtrain"),
     "Llama3-8B": Recipe("llama3_8B", sequence_length=8192, global_batch_sequences=512, microbatch_sequences=1,
                         project="Llama3-8B"),
     "OLMoE-1B-7B": Recipe("olmoe_1B_7B", global_batch_sequences=1024, microbatch_sequences=2, lr=4e-4, max_tokens=int(5e12),
@@ -82,7 +99,37 @@ def _on_b200() -> bool:
 
 def _model(recipe: Recipe, common: CommonComponents) -> TransformerConfig:
     factory: Callable[..., TransformerConfig] = getattr(TransformerConfig, recipe.model)
-    return factory(vocab_size=common.tokenizer.padded_vocab_size(), **(recipe.model_kwargs or {}))
+    config = factory(vocab_size=common.tokenizer.padded_vocab_size(), **(recipe.model_kwargs or {}))
+    return _hybridize(config) if recipe.hybrid else config
+
+
+def _hybridize(config: TransformerConfig, remove_heads: int = 2) -> TransformerConfig:
+    """
+    The OLMo-hybrid layout (src/scripts/official/OLMo-hybrid/OLMo-hybrid-7B-pretrain.py:60-85): two attention heads fewer
+    (and ``d_model`` narrower by as many heads of 128), then every group of four layers is three Gated-DeltaNet layers
+    (head size 0.75 x 128, two value channels per key channel) followed by one attention layer.
+    """
+    import copy
+
+    from ...nn.attention import GatedDeltaNetConfig
+
+    attn_block = config.block
+    mixer = attn_block.sequence_mixer if getattr(attn_block, "sequence_mixer", None) is not None else attn_block.attention
+    config.d_model -= remove_heads * 128
+    mixer.n_heads -= remove_heads
+    if getattr(mixer, "n_kv_heads", None) is not None and mixer.n_kv_heads > mixer.n_heads:
+        mixer.n_kv_heads = mixer.n_heads
+    gdn_block = copy.deepcopy(attn_block)
+    gdn = GatedDeltaNetConfig(n_heads=mixer.n_heads, head_dim=int(0.75 * 128), expand_v=2.0, allow_neg_eigval=True)
+    if getattr(gdn_block, "sequence_mixer", None) is not None:
+        gdn_block.sequence_mixer = gdn
+    else:
+        gdn_block.attention = gdn
+    config.block = {"gdn": gdn_block, "attn": attn_block}
+    config.block_pattern = ["gdn", "gdn", "gdn", "attn"]
+    if config.n_layers % 4 != 0:
+        raise ValueError(f"the hybrid pattern needs a multiple of 4 layers, got {config.n_layers}")
+    return config
 
 
 def _train_module(recipe: Recipe, common: CommonComponents) -> TransformerTrainModuleConfig:
