@@ -173,13 +173,22 @@ def bench_mlp(args, peaks) -> None:
         _lib.check(L.ocb_gemm_swiglu_bwd(dy.data_ptr(), w2.data_ptr(), ab.data_ptr(), dab.data_ptr(), None, M, H, K, K, H,
                                          2 * H, 2 * H, H, st, _lib.stream_ptr()), "ocb_gemm_swiglu_bwd")
 
-    a_, b_ = ab[:, :H], ab[:, H:]
+    a_ = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    b_ = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    dh = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
 
     def unfused_fwd():
         gemm(x, w13[:H], trans_b=True, out=a_)
         gemm(x, w13[H:], trans_b=True, out=b_)
         with torch.no_grad():
-            swiglu(a_.contiguous(), b_.contiguous())
+            swiglu(a_, b_)
+
+    a_g, b_g = a_.clone().requires_grad_(True), b_.clone().requires_grad_(True)
+    h_g = swiglu(a_g, b_g)
+
+    def unfused_bwd():
+        gemm(dy, w2, trans_b=False, out=dh)
+        torch.autograd.grad(h_g, (a_g, b_g), dh, retain_graph=True)
 
     if args.profile:
         fused_fwd()
@@ -188,7 +197,8 @@ def bench_mlp(args, peaks) -> None:
         return
     for name, fn, flops in (("mlp_up_fused_swiglu", fused_fwd, 2.0 * M * 2 * H * K),
                             ("mlp_up_two_gemms_plus_swiglu_kernel", unfused_fwd, 2.0 * M * 2 * H * K),
-                            ("mlp_down_dgrad_fused_swiglu_bwd", fused_bwd, 2.0 * M * H * K)):
+                            ("mlp_down_dgrad_fused_swiglu_bwd", fused_bwd, 2.0 * M * H * K),
+                            ("mlp_down_dgrad_plus_swiglu_bwd_kernel", unfused_bwd, 2.0 * M * H * K)):
         t = time_ms(fn, args.iters)
         _emit({"kernel": name, "M": M, "H": H, "K": K, "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)}, peaks)
     _lib.check_device_status()

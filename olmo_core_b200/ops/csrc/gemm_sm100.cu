@@ -286,13 +286,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (!ok) break;
           tc_fence_after();
           if (GROUPED == GROUP_REDUCTION && A_MN == 1 && kb == t.num_kb - 1 && t.k_tail < BK) {
-            // The last block reaches into the next group's rows. A reduction row is one 128-byte line of each
-            // [BK x 64] box (the swizzle only permutes within a line), so blanking A's lines [k_tail, BK) makes those
-            // rows contribute exactly zero whatever B holds there.
+            // The last block reaches into the next group's rows (or, past the last group, into rows nobody wrote). A
+            // reduction row is one 128-byte line of each [BK x 64] box (the swizzle only permutes within a line), so
+            // blanking the lines [k_tail, BK) of BOTH operands makes those rows contribute exactly zero; blanking only
+            // one side would still let a NaN or infinity on the other side through (0 x NaN).
             const int first = t.k_tail * 8, count = (BK - t.k_tail) * 8;  // in 16-byte units
             uint8_t* sa_ptr = smem + stage * STAGE_BYTES;
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) {
+            for (int j = 0; j < (BM + BN) / 64; ++j) {  // the A boxes, then (B_MN == 1 in this mode) the B boxes
               uint4* box = reinterpret_cast<uint4*>(sa_ptr + j * (64 * BK * 2)) + first;
               for (int i = lane; i < count; i += 32) box[i] = make_uint4(0u, 0u, 0u, 0u);
             }

@@ -138,18 +138,16 @@ class PeerExpertExchange:
         self.transfers += 1
 
     def to_experts(self, src: torch.Tensor, gather_idx: Optional[torch.Tensor], gather_div: int, t: SegmentTables) -> torch.Tensor:
-        """Deliver expert-sorted rows to the owners of their experts; returns this rank's received rows ``[total, cols]``."""
+        """Deliver expert-sorted rows to the owners of their experts; returns this rank's receive buffer ``[capacity, cols]``
+        whose first ``t.offsets[-1]`` rows (a device-side count) are the received rows, grouped by local expert."""
         half = self._recv_halves[self._recv_turn]
         self._recv_turn ^= 1
         self._push(src, gather_idx, gather_div, t.to_experts, half, self.capacity)
         self._recv.barrier()
-        total = int(t.total.item())  # the one host synchronisation of the layer (it overlaps the transfer)
-        if total > self.capacity:
-            raise _lib.KernelError(
-                f"expert-parallel receive buffer overflow: {total} rows routed to rank {self.rank}, capacity "
-                f"{self.capacity}; raise OLMO_CORE_B200_EP_CAPACITY"
-            )
-        return half.view[:total].clone()
+        # No host read: the whole receive half is handed on (rows past the last group belong to no expert: the grouped
+        # kernels never read them as data), and a rank that is sent more rows than the half holds is caught on the device
+        # (the push kernel skips them and sets the status word; `check_device_status` raises, naming the capacity knob).
+        return half.view.clone()
 
     def to_tokens(self, src: torch.Tensor, t: SegmentTables, n_rows: int, clone: bool) -> torch.Tensor:
         """Return rows in the receive layout to the ranks (and sorted positions) they came from; ``[n_rows, cols]``."""

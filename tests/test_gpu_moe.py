@@ -180,3 +180,31 @@ def test_dropless_moe_block_matches_cpu_reference():
             grad = pg.grad if pg.grad is not None else getattr(pg, "main_grad", None)
             assert grad is not None, name
             assert _rel_err(grad.cpu(), pr.grad) < 6e-2 + 2.0 * flips ** 0.5, name
+
+
+def test_grouped_kernels_ignore_rows_past_the_last_group():
+    """Buffers sized for a capacity hold rows that belong to no group (here NaN and infinity on purpose). The grouped
+    kernels must neither read them as data nor let them leak through the ragged tail of the last reduction block."""
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.ops.gemm import grouped_gemm, grouped_gemm_wgrad
+
+    torch.manual_seed(5)
+    sizes = [70, 0, 133, 40]  # 243 rows used, a tail block of the last group that is far from full
+    used, capacity, M, N = sum(sizes), 512, 128, 264
+    offsets = _offsets(sizes)
+    a = torch.randn(capacity, M, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(capacity, N, device=DEV, dtype=torch.bfloat16)
+    a[used:] = float("nan")
+    b[used:] = float("inf")
+    got = torch.zeros(len(sizes) * M, N, device=DEV, dtype=torch.float32)
+    grouped_gemm_wgrad(a, b, offsets, got, accumulate=False)
+    ref = torch.zeros_like(got)
+    grouped_gemm_wgrad(a[:used].contiguous(), b[:used].contiguous(), offsets, ref, accumulate=False)
+    _lib.check_device_status()
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-4)
+    # rows-grouped mode: outputs of the used rows do not depend on what follows them
+    w = torch.randn(len(sizes) * N, M, device=DEV, dtype=torch.bfloat16)
+    y = grouped_gemm(a, w, offsets, trans_b=True)
+    y_ref = grouped_gemm(a[:used].contiguous(), w, offsets, trans_b=True)
+    assert torch.isfinite(y[:used].float()).all() and torch.equal(y[:used], y_ref)
