@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--seqs-per-gpu", type=int, default=128)
     ap.add_argument("--vocab-size", type=int, default=100352)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--config", default="olmo2_7B_fsdp")
     ap.add_argument("--no-compile", action="store_true", help="debugging only: skip torch.compile")
     ap.add_argument("--ac", choices=["none", "full"], default="none",
                     help="activation checkpointing; 'full' is selected automatically when one GPU runs out of memory")
@@ -113,6 +114,8 @@ class _Clocks:
 
 def main() -> None:
     args = parse_args()
+    if args.config != "olmo2_7B_fsdp":
+        _unavailable(f"the reference arm is written for the headline configuration (olmo2_7B_fsdp) only, not '{args.config}'")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1")

@@ -27,6 +27,20 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 PEAK_BF16_FLOPS = 2.25e15  # dense bf16 peak the reference's MFU meter uses for B200
 
 
+# The benchmark configurations: the headline one (OLMo-2 7B, sharded data parallel) and the other model / parallelism
+# combinations the same step function is measured on. Each entry overrides command-line defaults; an explicit flag wins.
+CONFIGS = {
+    "olmo2_7B_fsdp": dict(model="olmo2_7B", seq_len=4096, micro_batch=2, seqs_per_gpu=128, vocab_size=100352),
+    # OLMo-2 32B, tensor parallel 2 (sequence parallel) x sharded data parallel N/2, row-wise fp8 linear layers
+    "olmo2_32B_tp2_fsdp4_fp8": dict(model="olmo2_32B", seq_len=4096, micro_batch=1, seqs_per_gpu=8, vocab_size=100352,
+                                    tp=2, fp8=True),
+    # OLMoE-1B-7B, experts spread over all N GPUs, the rest sharded data parallel
+    "olmoe_1B_7B_ep8": dict(model="olmoe_1B_7B", seq_len=4096, micro_batch=4, seqs_per_gpu=32, vocab_size=50304, ep=0),
+    # OLMo-3 7B long context: ONE 65536-token sequence per context-parallel group of all N GPUs
+    "olmo3_7B_cp8": dict(model="olmo3_7B", seq_len=65536, micro_batch=1, seqs_per_gpu=1, vocab_size=100352, cp=0),
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -40,7 +54,19 @@ def parse_args():
     ap.add_argument("--seqs-per-gpu", type=int, default=128, help="sequences per GPU per optimizer step")
     ap.add_argument("--vocab-size", type=int, default=100352)
     ap.add_argument("--no-e2e", action="store_true", help="accepted for compatibility; both numbers come from one loop")
-    return ap.parse_args()
+    ap.add_argument("--config", default="olmo2_7B_fsdp", choices=sorted(CONFIGS),
+                    help="which of the benchmark configurations to run (default: the headline one)")
+    a = ap.parse_args()
+    cfg = CONFIGS[a.config]
+    given = {x.split("=")[0] for x in sys.argv[1:] if x.startswith("--")}
+    for key, flag in (("model", "--model"), ("seq_len", "--seq-len"), ("micro_batch", "--micro-batch"),
+                      ("seqs_per_gpu", "--seqs-per-gpu"), ("vocab_size", "--vocab-size")):
+        if flag not in given:
+            setattr(a, key, cfg[key])
+    a.tp, a.fp8 = cfg.get("tp"), bool(cfg.get("fp8"))
+    a.ep = a.gpus if cfg.get("ep") == 0 else cfg.get("ep")  # 0: all GPUs of the job
+    a.cp = a.gpus if cfg.get("cp") == 0 else cfg.get("cp")
+    return a
 
 
 class ClockSampler:
@@ -121,9 +147,32 @@ def run_ours(args):
     cfg.lm_head.loss_implementation = LMLossImplementation.fused_linear
     model = cfg.build(init_device="meta")
     flops_per_token = model.num_flops_per_token(args.seq_len)
+    extra = {}
+    parallelism = f"fsdp{world}"
+    if args.tp and args.tp > 1:
+        from olmo_core_b200.train.train_module import TransformerTensorParallelConfig
+
+        extra["tp_config"] = TransformerTensorParallelConfig(degree=args.tp)
+        parallelism = f"tp{args.tp} x fsdp{world // args.tp}"
+    if args.ep and args.ep > 1:
+        from olmo_core_b200.train.train_module import TransformerExpertParallelConfig
+
+        extra["ep_config"] = TransformerExpertParallelConfig(degree=args.ep)
+        parallelism = f"ep{args.ep} + fsdp{world}"
+    if args.cp and args.cp > 1:
+        from olmo_core_b200.train.train_module import TransformerContextParallelConfig
+
+        extra["cp_config"] = TransformerContextParallelConfig.zig_zag(degree=args.cp)
+        parallelism = f"cp{args.cp} (zig-zag) x dp{world // args.cp}"
+    if args.fp8:
+        from olmo_core_b200.float8 import Float8Config
+
+        extra["float8_config"] = Float8Config(enabled=True)
+        parallelism += ", fp8 row-wise linear layers"
     tm = TransformerTrainModuleConfig(
         rank_microbatch_size=args.micro_batch * args.seq_len,
         max_sequence_length=args.seq_len,
+        **extra,
         optim=AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
                           group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
         max_grad_norm=1.0,
@@ -132,8 +181,9 @@ def run_ours(args):
     ).build(model, device=device)
 
     seqs = args.seqs_per_gpu
-    tokens_per_step_global = seqs * args.seq_len * world
-    gen = torch.Generator().manual_seed(1234 + rank)
+    dp_ranks = world // (args.cp or 1) // (args.tp or 1)  # ranks of a context- / tensor-parallel group share their batch
+    tokens_per_step_global = seqs * args.seq_len * dp_ranks
+    gen = torch.Generator().manual_seed(1234 + rank // ((args.cp or 1) * (args.tp or 1)))  # one batch per data-parallel rank
     n_host_batches = args.warmup + args.steps
     host_batches = [torch.randint(0, args.vocab_size, (seqs, args.seq_len), generator=gen, dtype=torch.int64).pin_memory()
                     for _ in range(min(n_host_batches, 4))]
@@ -187,7 +237,8 @@ def run_ours(args):
     value = tokens_per_step_global / (ms_per_step / 1e3)
     if rank == 0:
         out = {
-            "metric": "tokens/sec/GPU + MFU, OLMo-2 7B FSDP bf16 at 1/2/4/8 B200, device-timed (value = whole-job tokens/s)",
+            "metric": ("tokens/sec/GPU + MFU, OLMo-2 7B FSDP bf16 at 1/2/4/8 B200, device-timed (value = whole-job tokens/s)"
+                       if args.config == "olmo2_7B_fsdp" else f"tokens/sec, {args.config}, device-timed (value = whole-job tokens/s)"),
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
@@ -197,12 +248,13 @@ def run_ours(args):
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
-            "dtype": "bf16",
+            "dtype": "bf16 (fp8 e4m3 linear layers)" if args.fp8 else "bf16",
             "data": "synthetic uniform-random token ids, random-init weights",
             "tokens_per_sec_per_gpu": value / world,
             "mfu": value / world * flops_per_token / PEAK_BF16_FLOPS,
-            "config": {"model": args.model, "n_layers": cfg.n_layers, "global_batch": seqs * world, "seq_len": args.seq_len,
-                       "micro_batch": args.micro_batch, "parallelism": f"fsdp{world}", "optimizer": "AdamW, clip 1.0",
+            "config": {"name": args.config, "model": args.model, "n_layers": cfg.n_layers, "global_batch": seqs * dp_ranks,
+                       "seq_len": args.seq_len, "micro_batch": args.micro_batch, "parallelism": parallelism,
+                       "optimizer": "AdamW, clip 1.0",
                        "l2": "working set per step (14.6 GB bf16 weights + activations) is far larger than the 126 MB L2"},
             "clocks": clocks,
             "e2e": e2e,
