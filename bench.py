@@ -158,12 +158,16 @@ def run_ours(args):
         from olmo_core_b200.train.train_module import TransformerExpertParallelConfig
 
         extra["ep_config"] = TransformerExpertParallelConfig(degree=args.ep)
-        parallelism = f"ep{args.ep} + fsdp{world}"
+        # expert parallelism rides on the shard dimension of hybrid sharding (one replica group here)
+        extra["dp_config"] = TransformerDataParallelConfig(name="hsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32,
+                                                           shard_degree=args.ep)
+        parallelism = f"ep{args.ep} + hsdp(shard {args.ep})"
     if args.cp and args.cp > 1:
         from olmo_core_b200.train.train_module import TransformerContextParallelConfig
 
-        extra["cp_config"] = TransformerContextParallelConfig.zig_zag(degree=args.cp)
-        parallelism = f"cp{args.cp} (zig-zag) x dp{world // args.cp}"
+        # contiguous shards: the layout that works with sliding-window layers (the published long-context recipe uses it)
+        extra["cp_config"] = TransformerContextParallelConfig.llama3(degree=args.cp)
+        parallelism = f"cp{args.cp} (llama3 layout) x dp{world // args.cp}"
     if args.fp8:
         from olmo_core_b200.float8 import Float8Config
 
@@ -172,12 +176,13 @@ def run_ours(args):
     tm = TransformerTrainModuleConfig(
         rank_microbatch_size=args.micro_batch * args.seq_len,
         max_sequence_length=args.seq_len,
-        **extra,
         optim=AdamWConfig(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
                           group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
         max_grad_norm=1.0,
         z_loss_multiplier=1e-5,
-        dp_config=TransformerDataParallelConfig(name="fsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32),
+        dp_config=extra.pop("dp_config", None) or TransformerDataParallelConfig(
+            name="fsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32),
+        **extra,
     ).build(model, device=device)
 
     seqs = args.seqs_per_gpu

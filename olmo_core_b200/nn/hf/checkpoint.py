@@ -43,6 +43,10 @@ def save_hf_model(save_dir: PathOrStr, model_state_dict: Dict[str, Any], model, 
             hf_config.vocab_size = vocab_size
         with torch.device("meta"):
             hf_model = AutoModelForCausalLM.from_config(hf_config)
+        if any(k.endswith("experts.gate_up_proj") for k in hf_model.state_dict()):
+            from .convert import fuse_expert_weights  # this transformers version holds the experts of a layer stacked
+
+            hf_state = fuse_expert_weights(hf_state, hf_config.num_hidden_layers, int(getattr(hf_config, "num_experts", 0) or 0))
         hf_model.load_state_dict(hf_state, assign=True)
         target = Path(tempfile.mkdtemp(dir=work_dir)) if is_url(save_dir) else Path(save_dir)
         if target.exists() and any(target.iterdir()) and not save_overwrite:

@@ -18,6 +18,47 @@ def _rope_scaling(rope) -> Optional[Dict[str, Any]]:
     return out
 
 
+def _moe_hf_config(model):
+    """
+    Mixture-of-experts models: ``FlexOlmoConfig`` for reordered-norm blocks (norms on the sub-layer outputs, as in OLMo-2),
+    ``OlmoeConfig`` for pre-norm blocks. Both Hugging Face architectures route with a softmax over all experts followed
+    by top-k, one SwiGLU MLP per expert and no shared expert; anything else has no counterpart there.
+    """
+    from ..transformer.block import MoEReorderedNormTransformerBlock
+
+    blocks = list(model.blocks.values())
+    first = blocks[0]
+    if any(not hasattr(b, "feed_forward_moe") or hasattr(b, "feed_forward") for b in blocks):
+        raise NotImplementedError("only models whose every block is a pure mixture-of-experts block can be exported")
+    moe, attn = first.feed_forward_moe, first.attention
+    router = moe.router
+    if getattr(moe, "shared_mlp", None) is not None:
+        raise NotImplementedError("shared experts have no counterpart in the Hugging Face OLMoE / FlexOlmo architectures")
+    if str(getattr(router, "gating_function", "softmax")).split(".")[-1] != "softmax":
+        raise NotImplementedError("only softmax routers can be exported")
+    common = dict(
+        vocab_size=model.vocab_size, hidden_size=model.d_model, intermediate_size=moe.experts.mlp.hidden_size,
+        num_hidden_layers=model.n_layers, num_attention_heads=attn.n_heads, num_key_value_heads=attn.n_kv_heads,
+        hidden_act="silu", max_position_embeddings=-1, attention_bias=attn.w_out.bias is not None,
+        pad_token_id=None, bos_token_id=None, eos_token_id=None, rms_norm_eps=first.feed_forward_norm.eps,
+        tie_word_embeddings=getattr(model, "tie_word_embeddings", False), num_experts=moe.num_experts,
+        num_experts_per_tok=router.top_k, norm_topk_prob=bool(getattr(router, "normalize_expert_weights", None)),
+    )
+    rope = attn.rope
+    if isinstance(first, MoEReorderedNormTransformerBlock):
+        from transformers import FlexOlmoConfig
+
+        params = {"rope_type": "default", "rope_theta": rope.theta} if rope is not None else None
+        scaling = _rope_scaling(rope) if rope is not None else None
+        if scaling:
+            params = {**scaling, "rope_theta": rope.theta}
+        return FlexOlmoConfig(**common, rope_parameters=params)
+    from transformers import OlmoeConfig
+
+    return OlmoeConfig(**common, rope_theta=rope.theta if rope is not None else None,
+                       rope_scaling=_rope_scaling(rope) if rope is not None else None)
+
+
 def get_hf_config(model):
     """``Olmo2Config`` (``Olmo3Config`` with sliding windows) for reordered-norm blocks, ``LlamaConfig`` for pre-norm blocks."""
     from transformers import LlamaConfig, Olmo2Config
@@ -28,8 +69,7 @@ def get_hf_config(model):
     if isinstance(model, NormalizedTransformer):
         raise NotImplementedError(f"Building HF config not implemented for {type(model).__name__}")
     if isinstance(model, MoETransformer):
-        raise NotImplementedError("Mixture-of-experts export uses the expert templates of nn.hf.convert; build the HF "
-                                  "config for the target architecture explicitly")
+        return _moe_hf_config(model)
     blocks = list(model.blocks.values())
     first = blocks[0]
     attn = first.attention

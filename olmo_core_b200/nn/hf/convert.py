@@ -14,7 +14,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
-__all__ = ["convert_state_to_hf", "convert_state_from_hf", "get_converter_to_hf", "get_converter_from_hf",
+__all__ = ["convert_state_to_hf", "convert_state_from_hf", "fuse_expert_weights", "split_expert_weights", "get_converter_to_hf", "get_converter_from_hf",
            "OLMO_CORE_TO_HF_TEMPLATES", "StateConverter"]
 
 # (this framework, Hugging Face). Norm names depend on the block type, see ``_norm_templates``.
@@ -67,22 +67,42 @@ class StateConverter:
 
     def to_hf(self, state: Dict[str, Any]) -> Dict[str, Any]:
         out = {theirs: state[ours] for ours, theirs in self.pairs if ours in state}
-        for ours_t, theirs_t, transpose in _MOE_EXPERT_TEMPLATES:
+        for i in range(self.n_layers):
+            # the router is stored flat here and as [experts, d_model] there
+            key = f"model.layers.{i}.mlp.gate.weight"
+            if key in out and out[key].dim() == 1 and self.n_experts:
+                out[key] = out[key].view(self.n_experts, -1)
+        for ours_t, theirs_t, _ in _MOE_EXPERT_TEMPLATES:
             for i in range(self.n_layers):
                 ours = ours_t.format(layer=i)
                 if ours not in state:
                     continue
+                d_model = state["embeddings.weight"].shape[1] if "embeddings.weight" in state else None
                 for e, piece in enumerate(state[ours].chunk(self.n_experts, dim=0)):
+                    # HF: gate / up are [hidden, d_model], down is [d_model, hidden]. The stacked matrices here are
+                    # [E * hidden, d_model] (dropless experts, all three) or [E * d_model, hidden] (w1, w3 of the
+                    # fixed-capacity experts): transpose whichever piece is the other way round.
+                    want_rows_d_model = "down_proj" in theirs_t
+                    rows_are_d_model = d_model is not None and piece.shape[0] == d_model and piece.shape[1] != d_model
+                    transpose = rows_are_d_model != want_rows_d_model if piece.shape[0] != piece.shape[1] else False
                     out[theirs_t.format(layer=i, expert=e)] = piece.t().contiguous() if transpose else piece.contiguous()
         return out
 
-    def from_hf(self, hf_state: Dict[str, Any]) -> Dict[str, Any]:
+    def from_hf(self, hf_state: Dict[str, Any], dropless: bool = True) -> Dict[str, Any]:
+        """``dropless``: the target stores all three expert matrices as ``[E * hidden, d_model]`` (else w1 / w3 as
+        ``[E * d_model, hidden]``)."""
         out = {ours: hf_state[theirs] for ours, theirs in self.pairs if theirs in hf_state}
-        for ours_t, theirs_t, transpose in _MOE_EXPERT_TEMPLATES:
+        for i in range(self.n_layers):
+            key = f"blocks.{i}.feed_forward_moe.router.weight"
+            if key in out and out[key].dim() == 2:
+                out[key] = out[key].reshape(-1)
+        for ours_t, theirs_t, _ in _MOE_EXPERT_TEMPLATES:
             for i in range(self.n_layers):
                 names = [theirs_t.format(layer=i, expert=e) for e in range(self.n_experts)]
                 if not names or names[0] not in hf_state:
                     continue
+                down = "down_proj" in theirs_t
+                transpose = down if dropless else not down  # HF: gate/up [hidden, d], down [d, hidden]
                 pieces = [hf_state[n].t() if transpose else hf_state[n] for n in names]
                 out[ours_t.format(layer=i)] = torch.cat(pieces, dim=0).contiguous()
         return out
@@ -105,19 +125,58 @@ def get_converter_from_hf(hf_config=None, model_type: Optional[str] = None) -> S
     return get_converter_to_hf(hf_config, model_type)
 
 
-def convert_state_to_hf(hf_config, state: Dict[str, Any]) -> Dict[str, Any]:
-    """State dict of this framework's transformer -> state dict of the HF causal LM described by ``hf_config``."""
+def fuse_expert_weights(hf_state: Dict[str, Any], n_layers: int, n_experts: int) -> Dict[str, Any]:
+    """
+    Per-expert ``experts.<e>.{gate,up,down}_proj.weight`` entries (the layout of checkpoints on the hub) -> the stacked
+    ``experts.gate_up_proj [E, 2 * hidden, d_model]`` / ``experts.down_proj [E, d_model, hidden]`` parameters that
+    ``transformers`` >= 5 models hold in memory.
+    """
+    out = dict(hf_state)
+    for i in range(n_layers):
+        base = f"model.layers.{i}.mlp.experts"
+        if f"{base}.0.gate_proj.weight" not in out:
+            continue
+        gate = [out.pop(f"{base}.{e}.gate_proj.weight") for e in range(n_experts)]
+        up = [out.pop(f"{base}.{e}.up_proj.weight") for e in range(n_experts)]
+        down = [out.pop(f"{base}.{e}.down_proj.weight") for e in range(n_experts)]
+        out[f"{base}.gate_up_proj"] = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gate, up)])
+        out[f"{base}.down_proj"] = torch.stack(down)
+    return out
+
+
+def split_expert_weights(hf_state: Dict[str, Any], n_layers: int) -> Dict[str, Any]:
+    """The inverse of :func:`fuse_expert_weights`."""
+    out = dict(hf_state)
+    for i in range(n_layers):
+        base = f"model.layers.{i}.mlp.experts"
+        if f"{base}.gate_up_proj" not in out:
+            continue
+        gate_up, down = out.pop(f"{base}.gate_up_proj"), out.pop(f"{base}.down_proj")
+        hidden = gate_up.shape[1] // 2
+        for e in range(gate_up.shape[0]):
+            out[f"{base}.{e}.gate_proj.weight"] = gate_up[e, :hidden]
+            out[f"{base}.{e}.up_proj.weight"] = gate_up[e, hidden:]
+            out[f"{base}.{e}.down_proj.weight"] = down[e]
+    return out
+
+
+def convert_state_to_hf(hf_config, state: Dict[str, Any], fused_experts: bool = False) -> Dict[str, Any]:
+    """State dict of this framework's transformer -> state dict of the HF causal LM described by ``hf_config``
+    (``fused_experts``: stacked expert parameters as ``transformers`` >= 5 models expect them in memory)."""
     converted = _converter_for(hf_config).to_hf(state)
+    if fused_experts:
+        converted = fuse_expert_weights(converted, hf_config.num_hidden_layers, int(getattr(hf_config, "num_experts", 0) or 0))
     if getattr(hf_config, "tie_word_embeddings", False):
         converted.pop("lm_head.weight", None)
     missing = [k for k in state if not any(k == ours for ours, _ in _converter_for(hf_config).pairs)
-               and "experts.mlp" not in k]
+               and "experts.mlp" not in k and not k.endswith(("router.score_bias", "batch_size_per_expert"))]
     if missing:
         raise KeyError(f"no Hugging Face counterpart for parameters: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
     return converted
 
 
 def convert_state_from_hf(hf_config, hf_state: Dict[str, Any], model_type: Optional[str] = None) -> Dict[str, Any]:
+    hf_state = split_expert_weights(hf_state, hf_config.num_hidden_layers)
     converted = _converter_for(hf_config).from_hf(hf_state)
     if "lm_head.w_out.weight" not in converted and "embeddings.weight" in converted:
         converted["lm_head.w_out.weight"] = converted["embeddings.weight"]  # tied embeddings
