@@ -135,8 +135,55 @@ class GatedDeltaNet(nn.Module):
         self.w_out = nn.Linear(self.value_dim, d_model, **lin)
         self.cp_enabled = False
 
+    def _forward_ulysses(self, x: torch.Tensor, cu_doc_lens: Optional[torch.Tensor]) -> torch.Tensor:
+        """
+        Context parallelism for a recurrent mixer: the state runs along the whole sequence, so instead of the sequence
+        the HEADS are split. Projections act on this rank's tokens; one sequence<->head exchange hands every rank all
+        tokens of its heads (the depth-wise convolutions use the matching channel slice of their weights), the delta rule
+        runs per head over the full sequence, and a second exchange brings the outputs back to the local tokens
+        (reference: src/olmo_core/nn/attention/recurrent.py:164-238).
+        """
+        from ...distributed.parallel.context_parallel import (
+            all_to_all_cp2hp,
+            all_to_all_single_cp2hp,
+            all_to_all_single_hp2cp,
+        )
+
+        B, Tl, _ = x.shape
+        cp, rank = self._cp_size, self._cp_rank
+        q = self.w_q(x).view(B, Tl, self.n_heads, self.head_k_dim)
+        k = self.w_k(x).view(B, Tl, self.n_heads, self.head_k_dim)
+        v = self.w_v(x).view(B, Tl, self.n_v_heads, self.head_v_dim)
+        ab = torch.stack([self.w_a(x).float(), self.w_b(x).float()], dim=-1)  # [B, Tl, Hv, 2]
+        q, k = all_to_all_cp2hp([q, k], self._cp_pg)  # [B, T, H / cp, hk]
+        v = all_to_all_single_cp2hp(v, self._cp_pg)
+        ab = all_to_all_single_cp2hp(ab, self._cp_pg)  # [B, T, Hv / cp, 2]
+        T = q.shape[1]
+        hv = slice(rank * self.n_v_heads // cp, (rank + 1) * self.n_v_heads // cp)
+        beta = ab[..., 1].sigmoid().to(x.dtype)
+        if self.allow_neg_eigval:
+            beta = beta * 2.0
+        g = -self.A_log.float()[hv].exp() * F.softplus(ab[..., 0] + self.dt_bias[hv])
+        q = self.q_conv1d(q.reshape(B, T, -1), cu_seqlens=cu_doc_lens).view(B, T, -1, self.head_k_dim)
+        k = self.k_conv1d(k.reshape(B, T, -1), cu_seqlens=cu_doc_lens).view(B, T, -1, self.head_k_dim)
+        v = self.v_conv1d(v.reshape(B, T, -1), cu_seqlens=cu_doc_lens).view(B, T, -1, self.head_v_dim)
+        if self.n_v_heads > self.n_heads:
+            r = self.n_v_heads // self.n_heads
+            q, k = q.repeat_interleave(r, dim=-2), k.repeat_interleave(r, dim=-2)
+        if cu_doc_lens is None:
+            o = gated_delta_rule(q, k, v, g, beta)
+        else:
+            bounds = cu_doc_lens.tolist()
+            o = torch.cat([gated_delta_rule(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], beta[:, a:b])
+                           for a, b in zip(bounds[:-1], bounds[1:])], dim=1)
+        o = all_to_all_single_hp2cp(o.contiguous(), self._cp_pg)  # [B, Tl, Hv, hv]
+        gate = self.w_g(x).view(B, Tl, -1, self.head_v_dim)
+        return self.w_out(self.o_norm(o, gate).reshape(B, Tl, -1))
+
     def forward(self, x: torch.Tensor, cu_doc_lens: Optional[torch.Tensor] = None, **kwargs) -> torch.Tensor:
         del kwargs  # the block passes attention-only arguments (RoPE buffers, ...) to every mixer
+        if self.cp_enabled:
+            return self._forward_ulysses(x, cu_doc_lens)
         B, T, _ = x.shape
         q, k, v = self.w_q(x), self.w_k(x), self.w_v(x)
         beta = self.w_b(x).sigmoid()
@@ -161,8 +208,20 @@ class GatedDeltaNet(nn.Module):
     def apply_tp(self, tp_mesh, **kwargs) -> None:
         raise NotImplementedError("tensor parallelism is not implemented for GatedDeltaNet")
 
-    def apply_cp(self, cp_mesh, **kwargs) -> None:
-        raise NotImplementedError("context parallelism is not implemented for GatedDeltaNet")
+    def apply_cp(self, cp_mesh, ring=None, uly=None, **kwargs) -> None:
+        """Ulysses (head-split) context parallelism; a ring over the sequence cannot carry the recurrent state."""
+        del kwargs
+        if ring is not None or uly is None:
+            raise NotImplementedError("GatedDeltaNet supports Ulysses context parallelism only: its state runs along the "
+                                      "whole sequence, so the heads are split, not the sequence")
+        cp = cp_mesh.size()
+        if self.n_heads % cp != 0 or self.n_v_heads % cp != 0:
+            raise ValueError(f"the number of key heads ({self.n_heads}) and value heads ({self.n_v_heads}) must be "
+                             f"multiples of the context-parallel degree ({cp})")
+        self._cp_pg, self._cp_size, self._cp_rank = cp_mesh.get_group(), cp, cp_mesh.get_local_rank()
+        for conv in (self.q_conv1d, self.k_conv1d, self.v_conv1d):
+            conv.apply_cp(cp_mesh)
+        self.cp_enabled = cp > 1
 
     @torch.no_grad()
     def init_weights(self, *, init_method=None, d_model: Optional[int] = None, block_idx: int = 0, num_blocks: int = 1,

@@ -152,3 +152,38 @@ def _model_docs_worker(layout: str):
 @pytest.mark.parametrize("layout", ["zig_zag", "llama3"])
 def test_transformer_with_packed_documents_under_context_parallelism(layout):
     run_distributed_test(_model_docs_worker, world_size=2, func_args=(layout,))
+
+
+def _gdn_ulysses_worker():
+    """Gated DeltaNet with its heads split over the ranks (Ulysses) against the same layer on the whole sequence."""
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from olmo_core_b200.nn.attention.recurrent import GatedDeltaNet
+    from olmo_core_b200.nn.attention.ring import UlyssesContextParallelStyle
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(0)
+    layer = GatedDeltaNet(d_model=64, n_heads=4, n_v_heads=8, head_dim=16, init_device="cpu")
+    layer.init_weights(std=0.05)
+    ref = GatedDeltaNet(d_model=64, n_heads=4, n_v_heads=8, head_dim=16, init_device="cpu")
+    ref.load_state_dict(layer.state_dict())
+    x = torch.randn(2, 32, 64, generator=torch.Generator().manual_seed(1))
+    want = ref(x)
+    want.pow(2).sum().backward()
+    mesh = init_device_mesh("cpu", (ws,), mesh_dim_names=("cp",))
+    layer.apply_cp(mesh, uly=UlyssesContextParallelStyle())
+    sl = slice(rank * 32 // ws, (rank + 1) * 32 // ws)
+    got = layer(x[:, sl].contiguous())
+    torch.testing.assert_close(got, want[:, sl], rtol=1e-4, atol=1e-5)
+    got.pow(2).sum().backward()
+    for (n, p), q in zip(layer.named_parameters(), ref.parameters()):
+        g = p.grad.clone()
+        dist.all_reduce(g)  # every rank saw its tokens (projections) or its heads (decay, convolutions) only
+        torch.testing.assert_close(g, q.grad, rtol=1e-3, atol=1e-5, msg=n)
+    with pytest.raises(NotImplementedError):
+        GatedDeltaNet(d_model=64, n_heads=4, head_dim=16, init_device="cpu").apply_cp(mesh, ring=object())
+
+
+def test_gated_delta_net_under_ulysses_context_parallelism():
+    run_distributed_test(_gdn_ulysses_worker, world_size=2)
