@@ -1,10 +1,12 @@
 """
 Float8 training configuration (API of src/olmo_core/float8/__init__.py:17-162 and src/olmo_core/float8/ao.py:54-239).
 
-The reference swaps ``nn.Linear`` for torchao's ``Float8Linear`` / ``MXLinear``. Here the same config classes
-select the in-tree scaled-fp8 linear op (``olmo_core_b200.ops.fp8``): row-wise (per-token activation scale,
-per-output-channel weight scale, power-of-two rounding optional) e4m3 quantisation of both GEMM operands with
-fp32 accumulation, bf16 output; gradients use the bf16 tcgen05 GEMM unless ``cast_grads`` is set.
+The reference swaps ``nn.Linear`` for torchao's ``Float8Linear`` / ``MXLinear``. Here the same config classes select
+the in-tree 8-bit linear ops: ``ao`` / ``ao_recipe`` the row-wise scaled e4m3 GEMM (``olmo_core_b200.ops.fp8``:
+per-token activation scale, per-output-channel weight scale, power-of-two rounding optional, fp32 accumulation), and
+``ao_mx`` the block-scaled MX GEMM (``olmo_core_b200.ops.mx``: one E8M0 scale per 32 reduction elements, applied by
+``tcgen05.mma.kind::mxf8f6f4.block_scale``). Forward, dgrad and wgrad all run in 8 bits unless the recipe keeps the
+weight gradient in bf16.
 """
 
 from __future__ import annotations
@@ -47,7 +49,7 @@ class AOFloat8LinearConfig(Config):
 
 @dataclass
 class AOMXLinearConfig(Config):
-    """Micro-scaling (32-element blocks, E8M0 scales) variant; requires compute capability 10.0."""
+    """Micro-scaling (32-element blocks, E8M0 scales, e4m3 elements); ``scale_rounding``: "rceil" or "floor"."""
 
     block_size: int = 32
     elem_dtype: str = "float8_e4m3fn"
@@ -93,8 +95,20 @@ class Float8Config(Config):
                 continue
             if module.in_features % 16 != 0 or module.out_features % 16 != 0:
                 continue
-            module.float8 = dict(recipe=self.recipe, pow2_scales=pow2, mx=self.ao_mx)  # type: ignore[attr-defined]
+            # "cast the weights once per step" (the reference's fp8 all-gather + scale precompute) = keep the quantised
+            # copies of a weight until the next parameter update: one extra byte per parameter and layout
+            cache = {} if (self.ao is not None and self.ao.enable_fsdp_float8_all_gather) else None
+            module.float8 = dict(recipe=self.recipe, pow2_scales=pow2, mx=self.ao_mx,  # type: ignore[attr-defined]
+                                 weight_cache=cache)
 
 
 def refresh_float8_scales(model: nn.Module) -> None:
-    """Hook after each optimizer step. Scales are computed dynamically inside the quantisation kernel, so nothing is cached."""
+    """
+    Hook after each optimizer step (src/olmo_core/nn/transformer/model.py:617-635 calls torchao's scale precompute
+    there): activation scales are computed inside the quantisation kernels, so only the cached quantised weights have to
+    be dropped; the first micro-batch of the next step re-creates them from the updated parameters.
+    """
+    for module in model.modules():
+        f8 = getattr(module, "float8", None)
+        if isinstance(f8, dict) and f8.get("weight_cache") is not None:
+            f8["weight_cache"].clear()

@@ -99,11 +99,17 @@ class _Proj(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         f8 = getattr(self, "float8", None)  # set by Float8Config.apply_float8_linear
+        if f8 is not None and f8.get("mx") is not None:
+            from ..ops.mx import mx_linear
+
+            return mx_linear(x, self.weight, self.bias, scale_rounding=str(getattr(f8["mx"], "scale_rounding", "rceil")),
+                             weight_cache=f8.get("weight_cache"))
         if f8 is not None and x.is_cuda and x.numel() // x.shape[-1] % 16 == 0:
             from ..ops.fp8 import fp8_linear
 
             return fp8_linear(x, self.weight, self.bias, pow2_scales=bool(f8.get("pow2_scales")),
-                              wgrad_high_precision=str(f8.get("recipe")) == "rowwise_with_gw_hp")
+                              wgrad_high_precision=str(f8.get("recipe")) == "rowwise_with_gw_hp",
+                              weight_cache=f8.get("weight_cache"))
         return linear(x, self.weight, self.bias)
 
     def extra_repr(self) -> str:

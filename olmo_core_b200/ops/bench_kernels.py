@@ -2,7 +2,7 @@
 Micro-benchmarks of the sm_100a kernels against their library counterparts.
 
 ``python -m olmo_core_b200.ops.bench_kernels <case> [--iters N] [--profile]`` with ``case`` one of ``gemm``, ``mlp`` (gated
-MLP with the activation in the GEMM epilogues), ``fp8``, ``grouped``, ``attention``, ``norm``, ``norm_rope``,
+MLP with the activation in the GEMM epilogues), ``fp8``, ``mx``, ``grouped``, ``attention``, ``norm``, ``norm_rope``,
 ``swiglu``, ``ce``, ``adamw``, ``router``.
 
 Each case is timed with CUDA events on the launching stream after warm-up, with a buffer larger than L2 rewritten
@@ -227,6 +227,49 @@ def bench_fp8(args, peaks) -> None:
         _emit({"kernel": name, "rows": M, "cols": K, "ms": round(t, 4), "gbs": round(M * K * 3.0 / t / 1e6, 1)}, peaks)
 
 
+def bench_mx(args, peaks) -> None:
+    """Block-scaled (MX) e4m3 GEMM on the 7B layer shapes, its two quantisers, and a whole linear layer fwd+bwd next to bf16."""
+    from .gemm import linear
+    from .mx import gemm_mx, mx_linear, quantize_mx_colwise_transposed, quantize_mx_rowwise
+
+    M = 8192
+    a = torch.randn(M, 4096, device="cuda", dtype=torch.bfloat16)
+    if args.profile:
+        w = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+        aq, asf = quantize_mx_rowwise(a)
+        wq, wsf = quantize_mx_rowwise(w)
+        quantize_mx_colwise_transposed(a)
+        gemm_mx(aq, asf, wq, wsf)
+        torch.cuda.synchronize()
+        return
+    for N, K in ((4096, 4096), (22016, 4096), (4096, 11008)):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        xq, xsf = quantize_mx_rowwise(x)
+        wq, wsf = quantize_mx_rowwise(w)
+        t = time_ms(lambda: gemm_mx(xq, xsf, wq, wsf), args.iters)
+        tl = time_ms(lambda: torch.matmul(x, w.t()), args.iters)
+        _emit({"kernel": "gemm_mx_e4m3", "M": M, "N": N, "K": K, "ms": round(t, 4), "tflops": round(2.0 * M * N * K / t / 1e9, 1),
+               "cublas_bf16_ms": round(tl, 4)}, None)
+    for name, fn in (("quantize_mx_rowwise", lambda: quantize_mx_rowwise(a)),
+                     ("quantize_mx_colwise_transposed", lambda: quantize_mx_colwise_transposed(a))):
+        t = time_ms(fn, args.iters)
+        _emit({"kernel": name, "rows": M, "cols": 4096, "ms": round(t, 4), "gbs": round(M * 4096 * 3.0 / t / 1e6, 1)}, peaks)
+    for N, K in ((4096, 4096), (11008, 4096)):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+
+        def run(fn):
+            x.grad = w.grad = None
+            fn(x, w).backward(dy)
+
+        t_mx = time_ms(lambda: run(mx_linear), args.iters)
+        t_bf = time_ms(lambda: run(linear), args.iters)
+        _emit({"kernel": "linear_fwd_bwd", "M": M, "N": N, "K": K, "mx_ms": round(t_mx, 4), "bf16_ms": round(t_bf, 4),
+               "speedup": round(t_bf / t_mx, 3)}, None)
+
+
 def bench_grouped(args, peaks) -> None:
     """Expert MLP shapes of OLMoE-1B-7B: 64 experts, d_model 2048, hidden 1024, 32768 x 8 routed rows."""
     from .gemm import grouped_gemm, grouped_gemm_wgrad
@@ -365,7 +408,7 @@ def bench_router(args, peaks) -> None:
         _emit({"kernel": "routing_torch_sort_library", "copies": N * k, "ms": round(t, 4)}, None)
 
 
-CASES = {"gemm": bench_gemm, "mlp": bench_mlp, "fp8": bench_fp8, "grouped": bench_grouped, "attention": bench_attention,
+CASES = {"gemm": bench_gemm, "mlp": bench_mlp, "fp8": bench_fp8, "mx": bench_mx, "grouped": bench_grouped, "attention": bench_attention,
          "norm": bench_norm, "norm_rope": bench_norm_rope, "swiglu": bench_swiglu, "ce": bench_ce, "adamw": bench_adamw,
          "router": bench_router}
 

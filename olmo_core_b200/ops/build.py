@@ -93,10 +93,12 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     digest = hashlib.sha256(b"".join(o.read_bytes() for o in objs)).hexdigest()
     if LIB_PATH.exists() and link_stamp.exists() and link_stamp.read_text() == digest:
         return LIB_PATH
-    cmd = [_nvcc(), "-shared", "-cudart", "shared", "-o", str(LIB_PATH), *map(str, objs)]
+    tmp = BUILD_DIR / (LIB_PATH.name + ".tmp")  # linked aside and renamed: a reader never sees a half-written library
+    cmd = [_nvcc(), "-shared", "-cudart", "shared", "-o", str(tmp), *map(str, objs)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp, LIB_PATH)
     link_stamp.write_text(digest)
     if verbose:
         print(f"[ocb build] linked {LIB_PATH}", file=sys.stderr)

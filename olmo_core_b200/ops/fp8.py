@@ -24,7 +24,7 @@ from . import _lib
 from .gemm import compute_weight, gemm
 
 __all__ = ["quantize_rowwise", "quantize_colwise_transposed", "gemm_fp8", "fp8_linear", "Float8LinearFunction",
-           "E4M3_MAX"]
+           "cached_weight_cast", "E4M3_MAX"]
 
 E4M3_MAX = 448.0
 
@@ -98,17 +98,35 @@ def gemm_fp8(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_scal
     return out
 
 
+def cached_weight_cast(cache: Optional[dict], key: str, make, version: int = 0):
+    """
+    ``make()`` once per optimizer step: ``cache`` is a dict owned by the layer and emptied by
+    :func:`olmo_core_b200.float8.refresh_float8_scales` after every parameter update, so the quantised copies of a weight
+    are shared by all micro-batches of a step and by forward and backward (the effect the reference gets from casting
+    weights once before the sharded all-gather: src/olmo_core/float8/__init__.py:141-162). ``None`` disables caching.
+    ``version`` (the parameter's autograd version counter) additionally drops an entry when the weight was rewritten by
+    an ordinary in-place tensor operation, e.g. when a checkpoint is loaded.
+    """
+    if cache is None:
+        return make()
+    hit = cache.get(key)
+    if hit is None or hit[0] != version:
+        hit = cache[key] = (version, make())
+    return hit[1]
+
+
 class Float8LinearFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, pow2: bool, wgrad_high_precision: bool):  # type: ignore[override]
+    def forward(ctx, x, weight, pow2: bool, wgrad_high_precision: bool, cache: Optional[dict] = None):  # type: ignore[override]
         w = compute_weight(weight, torch.bfloat16)
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
         xq, sx = quantize_rowwise(x2, pow2)
-        wq, sw = quantize_rowwise(w, pow2)
+        wq, sw = cached_weight_cast(cache, "row", lambda: quantize_rowwise(w, pow2), weight._version)
         y = gemm_fp8(xq, sx, wq, sw)
         ctx.save_for_backward(x2, w)
         ctx.opts = (pow2, wgrad_high_precision)
+        ctx.cache = cache
         ctx.weight_ref, ctx.x_shape, ctx.x_dtype = weight, x.shape, x.dtype
         return y.view(*x.shape[:-1], w.shape[0])
 
@@ -122,7 +140,7 @@ class Float8LinearFunction(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[0]:
             dyq, sdy = quantize_rowwise(dy2, pow2)
-            wtq, swt = quantize_colwise_transposed(w, pow2)  # [K, N]
+            wtq, swt = cached_weight_cast(ctx.cache, "col_t", lambda: quantize_colwise_transposed(w, pow2), weight._version)  # [K, N]
             dx = gemm_fp8(dyq, sdy, wtq, swt).view(ctx.x_shape).to(ctx.x_dtype)
         main_grad = getattr(weight, "main_grad", None)
         dw = None
@@ -139,11 +157,11 @@ class Float8LinearFunction(torch.autograd.Function):
                     gemm_fp8(dytq, sdyt, xtq, sxt, out=main_grad, accumulate=True)
                 else:
                     dw = gemm_fp8(dytq, sdyt, xtq, sxt, out_dtype=torch.float32).to(weight.dtype)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
 def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, pow2_scales: bool = False,
-               wgrad_high_precision: bool = False) -> torch.Tensor:
+               wgrad_high_precision: bool = False, weight_cache: Optional[dict] = None) -> torch.Tensor:
     """``x @ weight^T (+ bias)`` through the 8-bit kernels; dimensions must be multiples of 16."""
-    y = Float8LinearFunction.apply(x, weight, pow2_scales, wgrad_high_precision)
+    y = Float8LinearFunction.apply(x, weight, pow2_scales, wgrad_high_precision, weight_cache)
     return y if bias is None else y + bias.to(y.dtype)
