@@ -384,7 +384,13 @@ class Attention(SequenceMixer):
         """
         B, T, _ = x.shape
         hd = self.head_dim
-        q, k, v = multi_linear(x, (self.w_q, self.w_k, self.w_v))
+        tp_fused = getattr(self, "_tp_fused_call", False)
+        if tp_fused:
+            # x is this rank's SEQUENCE shard: the projections gather the other shards inside their GEMMs
+            q, k, v = self._tp_project_in(x)
+            T = q.shape[1]
+        else:
+            q, k, v = multi_linear(x, (self.w_q, self.w_k, self.w_v))
         start_pos = self.kv_cache_manager.current_position() if self.kv_cache_manager is not None else None
         if (self.cp_enabled and self.rope is not None and pos_sin is None and pos_cos is None and freqs_cis is None
                 and rope_pos_ids is None):
@@ -436,7 +442,37 @@ class Attention(SequenceMixer):
             else:
                 att = att * g.to(att.dtype).view(B, T, -1, hd)
         att = att.reshape(B, T, -1)
+        if tp_fused:
+            return self._tp_project_out(att)
         return self._project_out(att)
+
+    def _tp_project_in(self, x: torch.Tensor):
+        """
+        Column-parallel q / k / v of a sequence-sharded ``x [B, T/tp, D]``: each GEMM loads the peers' rows from their
+        memory tile by tile (no gathered copy of ``x`` exists). The kernels return rows in rank-major order
+        ``[tp, B, T/tp]``; for one sequence per batch that already is sequence order, otherwise one permuting copy
+        restores ``[B, T]``.
+        """
+        from ...parallel.tp_fused import gather_linear_multi
+
+        B, Tl, _ = x.shape
+        ws = torch.distributed.get_world_size(self.tp_group)
+        outs = []
+        for y in gather_linear_multi(x, (self.w_q.weight, self.w_k.weight, self.w_v.weight), self.tp_group, "attn-qkv"):
+            y = y.view(ws, B, Tl, -1)  # rows come back as [ws * B * Tl, F_local]
+            outs.append(y.view(1, ws * Tl, -1) if B == 1 else y.permute(1, 0, 2, 3).reshape(B, ws * Tl, -1))
+        return outs
+
+    def _tp_project_out(self, att: torch.Tensor) -> torch.Tensor:
+        """Row-parallel output projection: partial products leave the GEMM epilogue as reductions into the owners' rows."""
+        from ...parallel.tp_fused import linear_reduce_scatter
+
+        B, T, F = att.shape
+        ws = torch.distributed.get_world_size(self.tp_group)
+        Tl = T // ws
+        rows = att if B == 1 else att.view(B, ws, Tl, F).permute(1, 0, 2, 3)
+        y = linear_reduce_scatter(rows.reshape(ws * B * Tl, F), self.w_out.weight, self.tp_group, "attn-out")
+        return y.view(B, Tl, -1)
 
     def _full_width_norm(self, norm: nn.Module, t: torch.Tensor) -> torch.Tensor:
         if self.tp_enabled:

@@ -259,7 +259,40 @@ def shard_attention_(attn: nn.Module, tp_mesh) -> None:
             if hasattr(attn.backend, key):
                 setattr(attn.backend, key, getattr(attn, key))
     attn.tp_group = group
+    inner = attn.forward
     _wrap_forward(attn, group)
+    _fuse_attention(attn, group, inner)
+
+
+def _fuse_attention(attn: nn.Module, group, inner) -> None:
+    """
+    Route the attention projections through the kernels that carry the collective themselves (as the MLP below): q, k
+    and v gather the sequence shards of their input while they run, the output projection reduces its partial sums into
+    the owners' shards. Falls back to the gather / reduce-scatter wrapper for biases, gates, KV caches, fp8 projections,
+    CPU tensors, or when peer memory is unavailable.
+    """
+    from .tp_fused import fused_tp_available
+
+    if not hasattr(attn, "_tp_project_in"):
+        return
+    wrapped = attn.forward
+    projections = [getattr(attn, n, None) for n in ("w_q", "w_k", "w_v", "w_out")]
+    if any(p is None or getattr(p, "bias", None) is not None for p in projections) or getattr(attn, "w_g", None) is not None:
+        return
+
+    def forward(x, *args, **kwargs):
+        rows = x.numel() // x.shape[-1]
+        if (getattr(attn, "kv_cache_manager", None) is not None or getattr(attn, "clip_qkv", None) is not None
+                or any(getattr(p, "float8", None) is not None for p in projections)
+                or not fused_tp_available(x, group, rows)):
+            return wrapped(x, *args, **kwargs)
+        attn._tp_fused_call = True
+        try:
+            return inner(x, *args, **kwargs)
+        finally:
+            attn._tp_fused_call = False
+
+    attn.forward = forward  # type: ignore[method-assign]
 
 
 def shard_feed_forward_(ff: nn.Module, tp_mesh) -> None:
@@ -283,7 +316,7 @@ def _fuse_feed_forward(ff: nn.Module, group) -> None:
     """
     from ..nn.feed_forward import ActivationFunction
     from ..ops.elementwise import swiglu
-    from .tp_fused import fused_tp_available, gather_linear, linear_reduce_scatter
+    from .tp_fused import fused_tp_available, gather_linear_multi, linear_reduce_scatter
 
     wrapped = ff.forward
     if (getattr(ff, "activation", None) != ActivationFunction.silu
@@ -294,8 +327,7 @@ def _fuse_feed_forward(ff: nn.Module, group) -> None:
         rows = x.numel() // x.shape[-1]
         if args or kwargs or not fused_tp_available(x, group, rows):
             return wrapped(x, *args, **kwargs)
-        a = gather_linear(x, ff.w1.weight, group, "ffn-up")
-        b = gather_linear(x, ff.w3.weight, group, "ffn-gate")
+        a, b = gather_linear_multi(x, (ff.w1.weight, ff.w3.weight), group, "ffn-up")
         y = linear_reduce_scatter(swiglu(a, b), ff.w2.weight, group, "ffn-down")
         return y.view(x.shape)
 

@@ -34,7 +34,7 @@ from ..ops import _lib
 from ..ops.gemm import compute_weight, gemm
 from .symmetric import SymmetricBuffer, symmetric_memory_enabled
 
-__all__ = ["gather_linear", "linear_reduce_scatter", "fused_tp_available"]
+__all__ = ["gather_linear", "gather_linear_multi", "linear_reduce_scatter", "fused_tp_available"]
 
 ENV_VAR = "OLMO_CORE_B200_TP_FUSED"
 _buffers: Dict[Tuple[int, str, int, torch.dtype], SymmetricBuffer] = {}
@@ -79,38 +79,97 @@ def _reduce_scatter_rows(x: torch.Tensor, group) -> torch.Tensor:
     return full.chunk(ws, dim=0)[dist.get_rank(group)].contiguous()
 
 
-def _ag_gemm(x_local: torch.Tensor, w: torch.Tensor, trans_b: bool, group, tag: str) -> torch.Tensor:
-    """``[x_0; ...] @ op(w)`` with the gather inside the kernel. ``x_local [m, K]``; returns ``[tp * m, N]`` bf16."""
+def _ag_gemm_multi(x_local: torch.Tensor, weights, trans_b: bool, group, tag: str):
+    """
+    ``[x_0; ...] @ op(w)`` for every ``w`` of ``weights`` with the gather inside the kernels: the shard is published once
+    and every product pulls the peers' rows tile by tile. ``x_local [m, K]``; returns a list of ``[tp * m, N_i]`` bf16.
+    """
     m, K = x_local.shape
-    N = w.shape[0] if trans_b else w.shape[1]
     ws, rank = dist.get_world_size(group), dist.get_rank(group)
     stage = _buffer(group, f"ag-{tag}", m * K, torch.bfloat16, x_local.device)
     stage.tensor.view(m, K).copy_(x_local)
     stage.barrier()  # every rank's shard is in place
-    out = torch.empty((ws * m, N), dtype=torch.bfloat16, device=x_local.device)
-    rc = _lib.lib().ocb_gemm_bf16_tp(stage.peer_ptrs, w.data_ptr(), _ptr_array([out.data_ptr()]), m, N, K, K, w.stride(0),
-                                     out.stride(0), ws, rank, 1, 0, 0 if trans_b else 1, _lib.EPI_BF16,
-                                     _lib.status_buffer(x_local.device).data_ptr(), _lib.stream_ptr())
-    _lib.check(rc, "ocb_gemm_bf16_tp")
+    outs = []
+    for w in weights:
+        N = w.shape[0] if trans_b else w.shape[1]
+        out = torch.empty((ws * m, N), dtype=torch.bfloat16, device=x_local.device)
+        rc = _lib.lib().ocb_gemm_bf16_tp(stage.peer_ptrs, w.data_ptr(), _ptr_array([out.data_ptr()]), m, N, K, K, w.stride(0),
+                                         out.stride(0), ws, rank, 1, 0, 0 if trans_b else 1, _lib.EPI_BF16,
+                                         _lib.status_buffer(x_local.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "ocb_gemm_bf16_tp")
+        outs.append(out)
     stage.barrier()  # nobody still reads a shard when its owner reuses the staging buffer
-    return out
+    return outs
+
+
+def _ag_gemm(x_local: torch.Tensor, w: torch.Tensor, trans_b: bool, group, tag: str) -> torch.Tensor:
+    return _ag_gemm_multi(x_local, [w], trans_b, group, tag)[0]
+
+
+def _gemm_rs_multi(xs, weights, trans_b: bool, group, tag: str) -> torch.Tensor:
+    """
+    Rows ``[r*m, (r+1)*m)`` of ``sum_i sum_ranks xs[i] @ op(weights[i])`` on rank ``r``: every product adds its tiles into
+    the owners' fp32 shards from its epilogue, between one pair of barriers. ``xs[i] [tp * m, K_i]``; returns ``[m, N]``.
+    """
+    M = xs[0].shape[0]
+    N = weights[0].shape[0] if trans_b else weights[0].shape[1]
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    m = M // ws
+    acc = _buffer(group, f"rs-{tag}", m * N, torch.float32, xs[0].device)
+    acc.tensor.zero_()
+    acc.barrier()  # every shard is zero before the first partial product arrives
+    for x, w in zip(xs, weights):
+        rc = _lib.lib().ocb_gemm_bf16_tp(_ptr_array([x.data_ptr()]), w.data_ptr(), acc.peer_ptrs, m, N, x.shape[1], x.stride(0),
+                                         w.stride(0), N, ws, rank, 0, 1, 0 if trans_b else 1, _lib.EPI_F32_RED_PEER,
+                                         _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "ocb_gemm_bf16_tp")
+    acc.barrier()  # all partial products have landed
+    return acc.tensor.view(m, N).to(torch.bfloat16)
 
 
 def _gemm_rs(x: torch.Tensor, w: torch.Tensor, trans_b: bool, group, tag: str) -> torch.Tensor:
-    """Rows ``[r*m, (r+1)*m)`` of ``sum_ranks x @ op(w)`` on rank ``r``. ``x [tp * m, K_local]``; returns ``[m, N]`` bf16."""
-    M, K = x.shape
-    N = w.shape[0] if trans_b else w.shape[1]
-    ws, rank = dist.get_world_size(group), dist.get_rank(group)
-    m = M // ws
-    acc = _buffer(group, f"rs-{tag}", m * N, torch.float32, x.device)
-    acc.tensor.zero_()
-    acc.barrier()  # every shard is zero before the first partial product arrives
-    rc = _lib.lib().ocb_gemm_bf16_tp(_ptr_array([x.data_ptr()]), w.data_ptr(), acc.peer_ptrs, m, N, K, x.stride(0),
-                                     w.stride(0), N, ws, rank, 0, 1, 0 if trans_b else 1, _lib.EPI_F32_RED_PEER,
-                                     _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
-    _lib.check(rc, "ocb_gemm_bf16_tp")
-    acc.barrier()  # all partial products have landed
-    return acc.tensor.view(m, N).to(torch.bfloat16)
+    return _gemm_rs_multi([x], [w], trans_b, group, tag)
+
+
+class _GatherLinearMulti(torch.autograd.Function):
+    """Several column-parallel projections of one sequence-sharded input (q / k / v; the two halves of a gated MLP)."""
+
+    @staticmethod
+    def forward(ctx, x_local, group, tag, *weights):  # type: ignore[override]
+        ws_ = [compute_weight(w, torch.bfloat16) for w in weights]
+        x2 = x_local.reshape(-1, x_local.shape[-1]).contiguous()
+        ctx.fused = fused_tp_available(x2, group, x2.shape[0])
+        if ctx.fused:
+            ys = _ag_gemm_multi(x2, ws_, True, group, tag)
+        else:
+            x_full = _all_gather_rows(x2, group)
+            ys = [gemm(x_full, w, trans_b=True) for w in ws_]
+        ctx.save_for_backward(x2, *ws_)
+        ctx.group, ctx.tag, ctx.weight_refs, ctx.x_shape = group, tag, weights, x_local.shape
+        return tuple(ys)
+
+    @staticmethod
+    def backward(ctx, *dys):  # type: ignore[override]
+        x2, *ws_ = ctx.saved_tensors
+        group = ctx.group
+        dys = [dy.reshape(-1, dy.shape[-1]).contiguous() for dy in dys]
+        if ctx.fused:
+            dx = _gemm_rs_multi(dys, ws_, False, group, ctx.tag)
+        else:
+            partial = gemm(dys[0], ws_[0], trans_b=False)
+            for dy, w in zip(dys[1:], ws_[1:]):
+                partial = partial + gemm(dy, w, trans_b=False)
+            dx = _reduce_scatter_rows(partial, group)
+        x_full = _all_gather_rows(x2, group)
+        dws = []
+        for dy, weight in zip(dys, ctx.weight_refs):
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                gemm(dy, x_full, trans_a=True, trans_b=False, out=main_grad, accumulate=True)
+                dws.append(None)
+            else:
+                dws.append(gemm(dy, x_full, trans_a=True, trans_b=False, out_dtype=torch.float32).to(weight.dtype))
+        return (dx.view(ctx.x_shape), None, None, *dws)
 
 
 class _GatherLinear(torch.autograd.Function):
@@ -168,6 +227,14 @@ class _LinearReduceScatter(torch.autograd.Function):
         else:
             dw = gemm(dy_full, x2, trans_a=True, trans_b=False, out_dtype=torch.float32).to(weight.dtype)
         return dx.view(ctx.x_shape), dw, None, None
+
+
+def gather_linear_multi(x_local: torch.Tensor, weights, group, tag: str = "x"):
+    """
+    :func:`gather_linear` for several weights that share the input: the shard is published once, and the input gradient is
+    reduced once for all of them. Returns one ``[tp * m, N_i]`` tensor per weight.
+    """
+    return _GatherLinearMulti.apply(x_local, group, tag, *weights)
 
 
 def gather_linear(x_local: torch.Tensor, weight: torch.Tensor, group, tag: str = "x") -> torch.Tensor:

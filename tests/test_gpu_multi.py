@@ -174,6 +174,106 @@ def test_tensor_parallel_fused_collective_gemms():
     run_distributed_test(_tp_fused_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
 
 
+def _tp_multi_worker():
+    """Several projections of one sharded input: one published shard, one reduction of the input gradient."""
+    import torch.distributed as dist
+
+    from olmo_core_b200.ops import _lib
+    from olmo_core_b200.parallel.tp_fused import gather_linear_multi
+
+    rank, ws = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    m, K = 128, 256
+    widths = (384, 128, 128)
+    gen = torch.Generator().manual_seed(11)
+    x_all = torch.randn(ws, m, K, generator=gen)
+    w_all = [torch.randn(ws, n, K, generator=gen) * 0.05 for n in widths]
+    x = x_all[rank].to(dev, torch.bfloat16).requires_grad_(True)
+    weights = [w[rank].to(dev, torch.bfloat16).requires_grad_(True) for w in w_all]
+    ys = gather_linear_multi(x, weights, dist.group.WORLD, "multi")
+    ref_x = x_all.to(torch.bfloat16).float().reshape(ws * m, K)
+    gs = [torch.randn(ws * m, n, generator=torch.Generator().manual_seed(30 + rank + i)) for i, n in enumerate(widths)]
+    for y, w, n in zip(ys, w_all, widths):
+        torch.testing.assert_close(y.float().cpu(), ref_x @ w[rank].to(torch.bfloat16).float().t(), rtol=2e-2, atol=2e-2)
+    torch.autograd.backward(ys, [g.to(dev, torch.bfloat16) for g in gs])
+    partial = sum(g.to(torch.bfloat16).float() @ w[rank].to(torch.bfloat16).float() for g, w in zip(gs, w_all)).to(dev)
+    dist.all_reduce(partial)
+    torch.testing.assert_close(x.grad.float(), partial[rank * m:(rank + 1) * m], rtol=3e-2, atol=5e-2)
+    for wt, g in zip(weights, gs):
+        torch.testing.assert_close(wt.grad.float().cpu(), g.to(torch.bfloat16).float().t() @ ref_x, rtol=3e-2, atol=8e-2)
+    _lib.check_device_status()
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+def test_tensor_parallel_shared_input_projections():
+    run_distributed_test(_tp_multi_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
+
+
+def _tp_model_worker():
+    """A tensor-parallel model (attention and MLP projections with the collectives inside their GEMMs) against the same
+    model on one GPU: losses of three optimizer steps."""
+    import torch.distributed as dist
+
+    from olmo_core_b200.config import DType
+    from olmo_core_b200.nn.transformer import TransformerConfig
+    from olmo_core_b200.optim import AdamWConfig
+    from olmo_core_b200.parallel import tp_fused
+    from olmo_core_b200.train.train_module import (
+        TransformerDataParallelConfig,
+        TransformerTensorParallelConfig,
+        TransformerTrainModule,
+    )
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    seq, vocab = 256, 512
+    calls = {"n": 0}
+    real = tp_fused._ag_gemm_multi
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    tp_fused._ag_gemm_multi = counting
+
+    def losses(tp: bool):
+        torch.manual_seed(0)
+        model = TransformerConfig.olmo2_30M(vocab_size=vocab, n_layers=2).build(init_device="cpu")
+        torch.manual_seed(0)
+        model.init_weights(max_seq_len=seq, device=torch.device("cpu"))
+        model.init_weights = lambda *a, **k: None
+        model.to(dev)
+        tm = TransformerTrainModule(
+            model=model, optim=AdamWConfig(lr=1e-3, weight_decay=0.0), rank_microbatch_size=2 * seq, max_sequence_length=seq,
+            max_grad_norm=1.0, device=dev,
+            tp_config=TransformerTensorParallelConfig(degree=2) if tp else None,
+            dp_config=TransformerDataParallelConfig(name="ddp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32) if tp else None,
+        )
+        gen = torch.Generator().manual_seed(7)
+        out = []
+        for _ in range(3):
+            ids = torch.randint(0, vocab, (2, seq), generator=gen)
+            tm.zero_grads()
+            tm.train_batch({"input_ids": ids})
+            tm.optim_step()
+            out.append(float(tm.latest_ce_loss))
+        return out
+
+    got = losses(True)
+    assert calls["n"] >= 2 * 2 * 3, "the fused gather GEMMs did not run"  # (attention + MLP) x layers x steps, forward
+    tp_fused._ag_gemm_multi = real
+    # the same model without any parallelism: every rank trains its own copy on the same batches
+    want = losses(False)
+    assert got == pytest.approx(want, rel=2e-2), (got, want)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+def test_tensor_parallel_model_with_fused_projections():
+    run_distributed_test(_tp_model_worker, world_size=2, backend="cuda:nccl,cpu:gloo")
+
+
 def _cp_in_kernel_worker(zig_zag: bool, window, mode: str, docs: bool = False):
     """Context-parallel attention with K / V exchanged over peer memory (pushed once, or read tile by tile from the
     owning GPU inside the attention kernels), against attention over the whole sequence."""
