@@ -33,7 +33,10 @@ CONFIGS = {
     "olmo2_7B_fsdp": dict(model="olmo2_7B", seq_len=4096, micro_batch=2, seqs_per_gpu=128, vocab_size=100352),
     # OLMo-2 32B, tensor parallel 2 (sequence parallel) x sharded data parallel N/2, row-wise fp8 linear layers
     "olmo2_32B_tp2_fsdp4_fp8": dict(model="olmo2_32B", seq_len=4096, micro_batch=1, seqs_per_gpu=8, vocab_size=100352,
-                                    tp=2, fp8=True),
+                                    tp=2, fp8="rowwise"),
+    # the headline model with 8-bit linear layers: row-wise scaled e4m3, and block-scaled MX (32-element E8M0 scales)
+    "olmo2_7B_fsdp_fp8": dict(model="olmo2_7B", seq_len=4096, micro_batch=2, seqs_per_gpu=128, vocab_size=100352, fp8="rowwise"),
+    "olmo2_7B_fsdp_mxfp8": dict(model="olmo2_7B", seq_len=4096, micro_batch=2, seqs_per_gpu=128, vocab_size=100352, fp8="mx"),
     # OLMoE-1B-7B, experts spread over all N GPUs, the rest sharded data parallel
     "olmoe_1B_7B_ep8": dict(model="olmoe_1B_7B", seq_len=4096, micro_batch=4, seqs_per_gpu=32, vocab_size=50304, ep=0),
     # OLMo-3 7B long context: ONE 65536-token sequence per context-parallel group of all N GPUs
@@ -63,7 +66,7 @@ def parse_args():
                       ("seqs_per_gpu", "--seqs-per-gpu"), ("vocab_size", "--vocab-size")):
         if flag not in given:
             setattr(a, key, cfg[key])
-    a.tp, a.fp8 = cfg.get("tp"), bool(cfg.get("fp8"))
+    a.tp, a.fp8 = cfg.get("tp"), cfg.get("fp8")
     a.ep = a.gpus if cfg.get("ep") == 0 else cfg.get("ep")  # 0: all GPUs of the job
     a.cp = a.gpus if cfg.get("cp") == 0 else cfg.get("cp")
     return a
@@ -169,10 +172,17 @@ def run_ours(args):
         extra["cp_config"] = TransformerContextParallelConfig.llama3(degree=args.cp)
         parallelism = f"cp{args.cp} (llama3 layout) x dp{world // args.cp}"
     if args.fp8:
-        from olmo_core_b200.float8 import Float8Config
+        from olmo_core_b200.float8 import AOFloat8LinearConfig, AOMXLinearConfig, Float8Config
 
-        extra["float8_config"] = Float8Config(enabled=True)
-        parallelism += ", fp8 row-wise linear layers"
+        # quantised weights are kept for all micro-batches of a step (dropped after the parameter update)
+        ao = AOFloat8LinearConfig(enable_fsdp_float8_all_gather=True)
+        if args.fp8 == "mx":
+            f8 = Float8Config(enabled=True, ao_mx=AOMXLinearConfig.mxfp8_cublas_rceil(), cache_weight_casts=True)
+            parallelism += ", MX fp8 (e4m3, E8M0 scale per 32) linear layers"
+        else:
+            f8 = Float8Config(enabled=True, ao=ao)
+            parallelism += ", fp8 row-wise linear layers"
+        extra["float8_config"] = f8
     tm = TransformerTrainModuleConfig(
         rank_microbatch_size=args.micro_batch * args.seq_len,
         max_sequence_length=args.seq_len,

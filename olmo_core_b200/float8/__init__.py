@@ -67,6 +67,9 @@ class Float8Config(Config):
     ao_mx: Optional[AOMXLinearConfig] = None
     modules_to_ignore: Optional[List[str]] = None
     enabled: bool = True
+    cache_weight_casts: bool = False
+    """Keep the quantised copies of every weight (one byte per parameter and layout) for all micro-batches of a step;
+    implied by ``ao.enable_fsdp_float8_all_gather``."""
 
     def __post_init__(self):
         if sum(x is not None for x in (self.ao, self.ao_recipe, self.ao_mx)) > 1:
@@ -97,7 +100,8 @@ class Float8Config(Config):
                 continue
             # "cast the weights once per step" (the reference's fp8 all-gather + scale precompute) = keep the quantised
             # copies of a weight until the next parameter update: one extra byte per parameter and layout
-            cache = {} if (self.ao is not None and self.ao.enable_fsdp_float8_all_gather) else None
+            keep = (self.ao is not None and self.ao.enable_fsdp_float8_all_gather) or self.cache_weight_casts
+            cache = {} if keep else None
             module.float8 = dict(recipe=self.recipe, pow2_scales=pow2, mx=self.ao_mx,  # type: ignore[attr-defined]
                                  weight_cache=cache)
 

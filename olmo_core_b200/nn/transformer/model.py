@@ -203,6 +203,12 @@ class Transformer(nn.Module):
                 self._device = get_default_device()
         return self._device
 
+    def _apply(self, fn, *args, **kwargs):
+        # ``.to()`` / ``.cuda()`` / ``.cpu()`` move the parameters: forget the cached device so that inputs follow them
+        out = super()._apply(fn, *args, **kwargs)
+        self._device = None
+        return out
+
     # -- initialisation ------------------------------------------------------------------------------------
     @torch.no_grad()
     def init_weights(

@@ -342,6 +342,10 @@ class _EmbeddingFunction(torch.autograd.Function):
         table = _lowp_or_self(weight)
         if table.dtype != out_dtype:
             table = table.to(out_dtype)
+        if ids.device != table.device or ids.dtype != torch.int64:
+            # the kernel dereferences both pointers on the table's device: token ids left on the host (or 32-bit ones)
+            # would be read as garbage addresses
+            ids = ids.to(device=table.device, dtype=torch.int64)
         flat = ids.reshape(-1).contiguous()
         rows, dim = flat.numel(), table.shape[1]
         out = torch.empty((rows, dim), dtype=out_dtype, device=table.device)

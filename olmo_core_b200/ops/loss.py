@@ -41,8 +41,8 @@ def cross_entropy_rows(
     ce = torch.empty(rows, dtype=torch.float32, device=logits.device)
     z = torch.empty(rows, dtype=torch.float32, device=logits.device)
     labels = labels.reshape(-1)
-    if labels.dtype != torch.int64:
-        labels = labels.long()
+    if labels.dtype != torch.int64 or labels.device != logits.device:
+        labels = labels.to(device=logits.device, dtype=torch.int64)  # the kernel reads them on the logits' device
     labels = labels.contiguous()
     rc = _lib.lib().ocb_cross_entropy_fwd_bwd(
         logits.data_ptr(), labels.data_ptr(), ce.data_ptr(), z.data_ptr(), _lib.ptr(dlogits), rows, vocab,

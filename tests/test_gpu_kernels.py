@@ -311,3 +311,27 @@ def test_gemm_last_wave_split_matches_reference(M, N, K):
     assert _rel_err(out, ref) < 5e-3
     y = gemm(a.t().contiguous(), b.t().contiguous(), trans_b=True)  # the same product through the bf16 epilogue
     assert _rel_err(y, a.float().t() @ b.float()) < 5e-3
+
+
+def test_token_ids_and_labels_left_on_the_host_are_moved_not_dereferenced():
+    """A model moved with ``.to()`` after construction, fed host tensors: ids and labels follow the parameters."""
+    from olmo_core_b200.nn.transformer import TransformerConfig
+    from olmo_core_b200.ops.elementwise import embedding
+    from olmo_core_b200.ops.loss import cross_entropy_with_z_loss
+
+    table = torch.randn(64, 32, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 64, (3, 5))
+    torch.testing.assert_close(embedding(ids, table), table[ids.cuda()])
+    torch.testing.assert_close(embedding(ids.int().cuda(), table), table[ids.cuda()])
+    logits = torch.randn(15, 64, device="cuda", dtype=torch.bfloat16)
+    ce, _ = cross_entropy_with_z_loss(logits, ids.reshape(-1), reduction="sum")
+    ref = torch.nn.functional.cross_entropy(logits.float(), ids.reshape(-1).cuda(), reduction="sum")
+    torch.testing.assert_close(ce.float(), ref, rtol=2e-2, atol=2e-2)
+
+    model = TransformerConfig.olmo2_30M(vocab_size=128, n_layers=1).build(init_device="cpu")
+    model.init_weights(max_seq_len=16, device=torch.device("cpu"))
+    assert model.device.type == "cpu"
+    model.to("cuda")
+    assert model.device.type == "cuda"
+    out = model(torch.randint(0, 128, (2, 16)))
+    assert out.is_cuda and torch.isfinite(out.float()).all()
