@@ -59,8 +59,31 @@ def _moe_hf_config(model):
                        rope_scaling=_rope_scaling(rope) if rope is not None else None)
 
 
+def _gemma3_hf_config(model, blocks, common):
+    """Peri-norm blocks (norms on both sides of each sub-layer), GeGLU, local / global attention layers: Gemma-3 text."""
+    from transformers import Gemma3TextConfig
+
+    first = blocks[0].attention
+    layer_types = ["sliding_attention" if getattr(b.attention, "window_size", None) else "full_attention" for b in blocks]
+    windows = {b.attention.window_size for b in blocks if getattr(b.attention, "window_size", None)}
+    if len(windows) > 1:
+        raise ValueError(f"All sliding-window layers must share one window size, found {windows}")
+    thetas = {kind: next((b.attention.rope.theta for b, t in zip(blocks, layer_types) if t == kind and b.attention.rope is not None), None)
+              for kind in ("sliding_attention", "full_attention")}
+    params = {k: v for k, v in common.items() if k not in ("rope_theta", "rope_scaling", "hidden_act", "attention_bias")}
+    return Gemma3TextConfig(
+        **params, head_dim=first.head_dim, hidden_activation="gelu_pytorch_tanh", query_pre_attn_scalar=first.head_dim,
+        sliding_window=windows.pop() if windows else None, layer_types=layer_types,
+        rope_parameters={kind: {"rope_type": "default", "rope_theta": float(theta)} for kind, theta in thetas.items() if theta},
+        final_logit_softcapping=None, attn_logit_softcapping=None,
+    )
+
+
 def get_hf_config(model):
-    """``Olmo2Config`` (``Olmo3Config`` with sliding windows) for reordered-norm blocks, ``LlamaConfig`` for pre-norm blocks."""
+    """
+    ``Olmo2Config`` (``Olmo3Config`` with sliding windows) for reordered-norm blocks, ``Gemma3TextConfig`` for peri-norm
+    blocks, ``Qwen3Config`` for pre-norm blocks with per-head query / key norms, ``LlamaConfig`` for other pre-norm blocks.
+    """
     from transformers import LlamaConfig, Olmo2Config
 
     from ..transformer.block import ReorderedNormTransformerBlock
@@ -82,7 +105,17 @@ def get_hf_config(model):
         pad_token_id=None, bos_token_id=None, eos_token_id=None, rms_norm_eps=first.feed_forward_norm.eps,
         tie_word_embeddings=getattr(model, "tie_word_embeddings", False),
     )
+    if hasattr(first, "post_attention_norm") and hasattr(first, "post_feed_forward_norm"):
+        return _gemma3_hf_config(model, blocks, common)
     if not isinstance(first, ReorderedNormTransformerBlock):
+        if getattr(attn, "use_head_qk_norm", False) and attn.q_norm is not None:
+            from transformers import Qwen3Config
+
+            # pre-norm blocks with a per-head RMSNorm on queries and keys: the Qwen-3 architecture
+            params = dict(common)
+            theta, scaling = params.pop("rope_theta"), params.pop("rope_scaling")
+            return Qwen3Config(**params, head_dim=attn.head_dim, rope_parameters={**(scaling or {"rope_type": "default"}),
+                                                                                    "rope_theta": theta})
         return LlamaConfig(**common)
     windows = {b.attention.window_size for b in blocks if getattr(b.attention, "window_size", None)}
     if windows:

@@ -45,21 +45,41 @@ _MOE_EXPERT_TEMPLATES = [  # (stacked name here, per-expert HF name, transpose w
 ]
 
 
-def _norm_templates(reordered_norm: bool) -> List[Tuple[str, str]]:
-    if reordered_norm:  # OLMo-2 / OLMo-3: norms are applied to the sub-layer outputs
+def _norm_templates(style: str) -> List[Tuple[str, str]]:
+    """Block norms by architecture family (src/olmo_core/nn/hf/convert.py:99-121 lists the same per-model overrides)."""
+    if style == "reordered":  # OLMo-2 / OLMo-3 / FlexOlmo: norms are applied to the sub-layer outputs
         return [("blocks.{layer}.attention_norm.weight", "model.layers.{layer}.post_attention_layernorm.weight"),
                 ("blocks.{layer}.feed_forward_norm.weight", "model.layers.{layer}.post_feedforward_layernorm.weight")]
+    if style == "peri":  # Gemma-3: a norm on the input and on the output of both sub-layers
+        return [("blocks.{layer}.attention_norm.weight", "model.layers.{layer}.input_layernorm.weight"),
+                ("blocks.{layer}.post_attention_norm.weight", "model.layers.{layer}.post_attention_layernorm.weight"),
+                ("blocks.{layer}.feed_forward_norm.weight", "model.layers.{layer}.pre_feedforward_layernorm.weight"),
+                ("blocks.{layer}.post_feed_forward_norm.weight", "model.layers.{layer}.post_feedforward_layernorm.weight")]
+    # Llama, Qwen-3, OLMoE: norms on the sub-layer inputs
     return [("blocks.{layer}.attention_norm.weight", "model.layers.{layer}.input_layernorm.weight"),
             ("blocks.{layer}.feed_forward_norm.weight", "model.layers.{layer}.post_attention_layernorm.weight")]
+
+
+_NORM_STYLE_BY_MODEL_TYPE = {"olmo2": "reordered", "olmo3": "reordered", "flex_olmo": "reordered", "gemma3_text": "peri",
+                             "gemma3": "peri"}
+# Gemma's RMSNorm multiplies by (1 + weight) with zero-initialised weights; every norm here multiplies by its weight.
+_UNIT_OFFSET_NORM_MODEL_TYPES = ("gemma3_text", "gemma3")
+_NORM_SUFFIXES = ("attention_norm.weight", "post_attention_norm.weight", "feed_forward_norm.weight",
+                  "post_feed_forward_norm.weight", "lm_head.norm.weight", "q_norm.weight", "k_norm.weight")
+
+
+def _shift_norm_weights(state: Dict[str, Any], delta: float) -> Dict[str, Any]:
+    return {k: (v + delta if isinstance(v, torch.Tensor) and k.endswith(_NORM_SUFFIXES) else v) for k, v in state.items()}
 
 
 class StateConverter:
     """Expands the templates for a concrete number of layers / experts and renames (splits, merges) tensors."""
 
-    def __init__(self, n_layers: int, n_experts: int = 0, reordered_norm: bool = True):
+    def __init__(self, n_layers: int, n_experts: int = 0, reordered_norm: bool = True, norm_style: Optional[str] = None):
         self.n_layers, self.n_experts = n_layers, n_experts
         self.pairs: List[Tuple[str, str]] = []
-        for ours, theirs in OLMO_CORE_TO_HF_TEMPLATES + _norm_templates(reordered_norm):
+        style = norm_style or ("reordered" if reordered_norm else "pre")
+        for ours, theirs in OLMO_CORE_TO_HF_TEMPLATES + _norm_templates(style):
             if "{layer}" in ours:
                 self.pairs += [(ours.format(layer=i), theirs.format(layer=i)) for i in range(n_layers)]
             else:
@@ -110,9 +130,9 @@ class StateConverter:
 
 def _converter_for(hf_config, n_experts: Optional[int] = None) -> StateConverter:
     model_type = getattr(hf_config, "model_type", "olmo2")
-    reordered = model_type in ("olmo2", "olmo3", "flex_olmo", "olmoe") and model_type != "olmoe"
     experts = n_experts if n_experts is not None else int(getattr(hf_config, "num_experts", 0) or 0)
-    return StateConverter(hf_config.num_hidden_layers, n_experts=experts, reordered_norm=reordered)
+    return StateConverter(hf_config.num_hidden_layers, n_experts=experts,
+                          norm_style=_NORM_STYLE_BY_MODEL_TYPE.get(model_type, "pre"))
 
 
 def get_converter_to_hf(hf_config=None, model_type: Optional[str] = None) -> StateConverter:
@@ -163,6 +183,8 @@ def split_expert_weights(hf_state: Dict[str, Any], n_layers: int) -> Dict[str, A
 def convert_state_to_hf(hf_config, state: Dict[str, Any], fused_experts: bool = False) -> Dict[str, Any]:
     """State dict of this framework's transformer -> state dict of the HF causal LM described by ``hf_config``
     (``fused_experts``: stacked expert parameters as ``transformers`` >= 5 models expect them in memory)."""
+    if getattr(hf_config, "model_type", None) in _UNIT_OFFSET_NORM_MODEL_TYPES:
+        state = _shift_norm_weights(state, -1.0)
     converted = _converter_for(hf_config).to_hf(state)
     if fused_experts:
         converted = fuse_expert_weights(converted, hf_config.num_hidden_layers, int(getattr(hf_config, "num_experts", 0) or 0))
@@ -178,6 +200,8 @@ def convert_state_to_hf(hf_config, state: Dict[str, Any], fused_experts: bool = 
 def convert_state_from_hf(hf_config, hf_state: Dict[str, Any], model_type: Optional[str] = None) -> Dict[str, Any]:
     hf_state = split_expert_weights(hf_state, hf_config.num_hidden_layers)
     converted = _converter_for(hf_config).from_hf(hf_state)
+    if getattr(hf_config, "model_type", None) in _UNIT_OFFSET_NORM_MODEL_TYPES:
+        converted = _shift_norm_weights(converted, 1.0)
     if "lm_head.w_out.weight" not in converted and "embeddings.weight" in converted:
         converted["lm_head.w_out.weight"] = converted["embeddings.weight"]  # tied embeddings
     return converted
