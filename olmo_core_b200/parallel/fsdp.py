@@ -52,6 +52,7 @@ log = logging.getLogger(__name__)
 __all__ = ["ShardedParamRuntime", "ShardInfo", "ParamSlot"]
 
 STREAMED_ENV_VAR = "OLMO_CORE_B200_FSDP_STREAMED"
+EARLY_REDUCE_ENV_VAR = "OLMO_CORE_B200_FSDP_EARLY_REDUCE"
 
 
 @dataclass
@@ -79,6 +80,7 @@ class ParamSlot:
     flat_numel: int = 0  # elements the full copy occupies in a flat buffer (padded rows included)
     padded_rows: int = 0  # leading dimension rounded up to a multiple of the world size (sharded slots)
     unit: int = -1  # streamed mode: index of the transformer block whose ring slot holds the full copy; -1 = resident
+    block: int = -1  # resident mode: index of the transformer block that owns the parameter (-1: embeddings, head, ...)
 
     @property
     def real_local_rows(self) -> int:
@@ -189,6 +191,13 @@ class ShardedParamRuntime:
                 for bp in block.parameters():
                     unit_of.setdefault(id(bp), i)
             self.streamed = True
+        # Resident mode: which transformer block a parameter belongs to (its gradients can be reduced as soon as the last
+        # micro-batch's backward has left that block).
+        self._block_of: Dict[int, int] = {}
+        if blocks is not None and not self.streamed:
+            for i, block in enumerate(blocks.values() if hasattr(blocks, "values") else blocks):
+                for bp in block.parameters():
+                    self._block_of.setdefault(id(bp), i)
         unit_off: Dict[int, int] = {}
         for fq, module, p, pname in entries:
             full_shape = tuple(p.shape)
@@ -222,6 +231,7 @@ class ShardedParamRuntime:
                 master_offset=master_off, local_numel=local_numel, full_offset=off if aware else -1,
                 full_numel=full_numel, aware=aware, padded_rows=padded_rows, unit=unit, flat_numel=flat_numel,
             )
+            slot.block = self._block_of.get(id(p), -1)
             self.slots.append(slot)
             seen[id(p)] = slot
             master_off += local_numel
@@ -283,6 +293,8 @@ class ShardedParamRuntime:
             self.grad_shard = None  # single rank, fp32: the shard of a gradient *is* the gradient (see grad_view)
         if self.streamed:
             self._materialize_streamed(device, lowp_dtype, peer_ok)
+        elif self._sym_grad is not None:
+            self._install_early_reduce(device)
         tied: Dict[int, nn.Parameter] = {}
         for slot in self.slots:
             old = slot.param
@@ -383,26 +395,83 @@ class ShardedParamRuntime:
             return slot.full_offset + self.rank * slot.local_numel, slot.local_numel
         return slot.full_offset, slot.full_numel
 
+    # -- resident mode: reduction overlapped with the last micro-batch's backward -------------------------------------
+    def _install_early_reduce(self, device: torch.device) -> None:
+        """
+        Reduce a block's gradients on a side stream as soon as the backward pass of the LAST micro-batch of a step has
+        left the block (the reference's FSDP reduce-scatters per block inside backward:
+        src/olmo_core/train/train_module/transformer/train_module.py:565-584). Whoever drives the step announces the
+        micro-batches with :meth:`begin_microbatch`; without that announcement everything is reduced in
+        :meth:`reduce_gradients` as before. ``OLMO_CORE_B200_FSDP_EARLY_REDUCE=0`` switches the overlap off.
+        """
+        self._early_enabled = os.environ.get(EARLY_REDUCE_ENV_VAR, "0") != "0" and device.type == "cuda"
+        self._early_reduced: set = set()
+        self.early_reduce_blocks = 0  # blocks reduced behind their backward so far (diagnostics)
+        self._last_microbatch = False
+        self._early_stream = torch.cuda.Stream(device) if self._early_enabled else None
+        blocks = getattr(self.model, "blocks", None)
+        if not self._early_enabled or blocks is None:
+            return
+        for u, block in enumerate(blocks.values() if hasattr(blocks, "values") else blocks):
+            block.register_full_backward_hook(lambda m, grad_in, grad_out, u=u: self._early_reduce_block(u))
+
+    def begin_microbatch(self, index: int, count: int) -> None:
+        """Called by the train module before the forward pass of micro-batch ``index`` of ``count``."""
+        self._last_microbatch = index == count - 1
+
+    @torch.no_grad()
+    def _early_reduce_block(self, u: int) -> None:
+        if not (getattr(self, "_early_enabled", False) and self._last_microbatch) or u in self._early_reduced:
+            return
+        slots = [s for s in self.slots if getattr(s, "block", -1) == u and s.param.requires_grad and self._fusable(s)]
+        if not slots:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        side = self._early_stream
+        side.wait_stream(cur)  # this block's weight gradients are complete on this rank
+        with torch.cuda.stream(side):
+            if not self._early_reduced:
+                self._sumsq.zero_()
+            self._sym_grad.barrier()  # ... and on every other rank
+            self._launch_reduce(slots, side.cuda_stream)
+        self._early_reduced.add(u)
+        self.early_reduce_blocks += 1
+
+    def _launch_reduce(self, slots, stream: int) -> None:
+        from ..ops import _lib
+
+        lib, sym = _lib.lib(), self._sym_grad
+        for slot in slots:
+            out = self.grad_shard[slot.master_offset: slot.master_offset + slot.local_numel]
+            offset, n = self.shard_range(slot)
+            rc = lib.ocb_peer_reduce_sumsq(sym.peer_ptrs, sym.multicast_ptr, self.world_size, offset, n,
+                                           1.0 / self.world_size, out.data_ptr(), self._fused_scratch.data_ptr(),
+                                           self._sumsq[0 if slot.sharded else 1:].data_ptr(), stream)
+            _lib.check(rc, "ocb_peer_reduce_sumsq")
+
     @torch.no_grad()
     def _reduce_gradients_fused(self) -> None:
         from ..ops import _lib
 
         lib, stream = _lib.lib(), _lib.stream_ptr()
         sym = self._sym_grad
-        self._sumsq.zero_()
+        early = getattr(self, "_early_reduced", set())
+        if early:
+            torch.cuda.current_stream(self.device).wait_stream(self._early_stream)  # their sums are in grad_shard / _sumsq
+        else:
+            self._sumsq.zero_()
+        self._last_microbatch = False
         sym.barrier()  # every rank has finished accumulating into its gradient buffer
         for slot in self.slots:
             if not slot.param.requires_grad:
                 continue
+            if getattr(slot, "block", -1) in early and self._fusable(slot):
+                continue  # reduced behind its block's backward
             out = self.grad_shard[slot.master_offset: slot.master_offset + slot.local_numel]
             if slot.aware and slot.param.grad is not None:
                 raise RuntimeError(f"parameter '{slot.name}' received an autograd gradient besides its fused main_grad")
             if self._fusable(slot):
-                offset, n = self.shard_range(slot)
-                rc = lib.ocb_peer_reduce_sumsq(sym.peer_ptrs, sym.multicast_ptr, self.world_size, offset, n,
-                                               1.0 / self.world_size, out.data_ptr(), self._fused_scratch.data_ptr(),
-                                               self._sumsq[0 if slot.sharded else 1:].data_ptr(), stream)
-                _lib.check(rc, "ocb_peer_reduce_sumsq")
+                self._launch_reduce([slot], stream)
                 continue
             # small or oddly sized parameters: NCCL all-reduce of the whole tensor
             if slot.aware:
@@ -421,6 +490,8 @@ class ShardedParamRuntime:
                 out.div_(self.world_size)
             self._sumsq[0 if slot.sharded else 1] += out.float().pow(2).sum()
         self._sumsq_valid = True
+        if early:
+            early.clear()
 
     # ------------------------------------------------------------------------------------------------
     # parameter synchronisation

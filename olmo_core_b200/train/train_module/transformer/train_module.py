@@ -432,7 +432,11 @@ class TransformerTrainModule(TrainModule):
 
     @contextlib.contextmanager
     def _train_microbatch_context(self, micro_batch_idx: int, num_micro_batches: int) -> Generator[None, None, None]:
-        # Gradients accumulate locally in main_grad; cross-rank reduction happens once, in optim_step().
+        # Gradients accumulate locally in main_grad across micro-batches; the cross-rank reduction belongs to the last
+        # one: the runtime starts it block by block behind that micro-batch's backward and finishes it in optim_step().
+        begin = getattr(self.runtime, "begin_microbatch", None)
+        if begin is not None:
+            begin(micro_batch_idx, num_micro_batches)
         yield
 
     @contextlib.contextmanager

@@ -13,8 +13,9 @@ from olmo_core_b200.testing import requires_multi_gpu, run_distributed_test
 VOCAB, SEQ = 512, 128
 
 
-def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streamed: str = "0"):
+def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streamed: str = "0", early: str = "0"):
     os.environ["OLMO_CORE_B200_SYMMETRIC"] = symmetric
+    os.environ["OLMO_CORE_B200_FSDP_EARLY_REDUCE"] = early
     os.environ["OLMO_CORE_B200_MULTIMEM"] = multimem
     os.environ["OLMO_CORE_B200_FSDP_STREAMED"] = streamed
     import torch.distributed as dist
@@ -73,6 +74,8 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streame
         tm.optim_step()
         norms.append(float(rt.grad_norm_sq().sqrt()))
     torch.cuda.synchronize()
+    if early == "1":
+        assert rt.early_reduce_blocks == 2 * steps, rt.early_reduce_blocks  # both blocks, every step
     # every rank's resident bf16 copy must hold ALL parameters, including the rows owned by the peer
     full = {s.name: rt.lowp[s.full_offset: s.full_offset + s.full_numel].float().cpu() for s in rt.slots if s.aware}
     gathered = [None] * dist.get_world_size()
@@ -82,9 +85,10 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streame
         torch.save({"params": full, "norms": norms}, out_path)
 
 
-def _run(tmp_path, name: str, symmetric: str, multimem: str, streamed: str = "0"):
+def _run(tmp_path, name: str, symmetric: str, multimem: str, streamed: str = "0", early: str = "0"):
     out = str(tmp_path / f"{name}.pt")
-    run_distributed_test(_train, world_size=2, backend="cuda:nccl,cpu:gloo", func_args=(out, symmetric, multimem, 3, streamed))
+    run_distributed_test(_train, world_size=2, backend="cuda:nccl,cpu:gloo",
+                         func_args=(out, symmetric, multimem, 3, streamed, early))
     return torch.load(out, weights_only=False)
 
 
@@ -113,6 +117,20 @@ def test_fused_optimizer_collectives_match_nccl(tmp_path, multimem):
     for a, b in zip(ref["norms"], got["norms"]):
         # two bf16 training runs whose gradient sums are formed in different orders: agreement to bf16-level noise
         assert a == pytest.approx(b, rel=1e-3)
+    for name, want in ref["params"].items():
+        torch.testing.assert_close(got["params"][name], want, rtol=0, atol=1e-2, msg=name)
+
+
+@pytest.mark.gpu
+@requires_multi_gpu
+def test_gradient_reduction_behind_the_last_backward_matches_the_one_shot_reduction(tmp_path):
+    """Resident parameters: blocks reduced on a side stream while the last micro-batch's backward still runs give the
+    same gradients as the reduction after the backward (the squared norm is summed in another order, so the clipping
+    factor may differ in its last bits)."""
+    ref = _run(tmp_path, "oneshot", "1", "0")
+    got = _run(tmp_path, "early", "1", "0", early="1")
+    for a, b in zip(ref["norms"], got["norms"]):
+        assert a == pytest.approx(b, rel=1e-5)
     for name, want in ref["params"].items():
         torch.testing.assert_close(got["params"][name], want, rtol=0, atol=1e-2, msg=name)
 

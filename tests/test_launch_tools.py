@@ -105,3 +105,52 @@ def test_compare_wandb_configs_on_local_files(tmp_path, capsys):
     cw.main([str(tmp_path / "l.json"), str(tmp_path / "r.json")])
     out = capsys.readouterr().out
     assert "model.d_model: 128 -> 256" in out and "seed = 1" in out and "lr = 0.1" in out and "n_layers" not in out
+
+
+def test_healthcheck_reads_gpu_state_from_a_fake_nvidia_smi(monkeypatch):
+    from olmo_core_b200.scripts import healthcheck as hc
+
+    def smi_factory(rows, procs=""):
+        def smi(args):
+            return procs if any("compute-apps" in a for a in args) else rows
+        return smi
+
+    healthy = "\n".join(f"{i}, 31, 4, 1965, 1965, Not Active, Not Active, Not Active" for i in range(8))
+    rep = hc.Report()
+    hc.check_gpus(rep, expect_gpus=8, temp_warn=50, temp_fail=55, max_used_mib=1024, smi=smi_factory(healthy))
+    assert rep.ok and not rep.warnings
+
+    rep = hc.Report()
+    hc.check_gpus(rep, expect_gpus=8, temp_warn=50, temp_fail=55, max_used_mib=1024,
+                  smi=smi_factory(healthy.replace("0, 31", "0, 52").replace("3, 31, 4", "3, 61, 90000")
+                                  .replace("5, 31, 4, 1965, 1965", "5, 31, 4, 1965, 1200")
+                                  .replace("7, 31, 4, 1965, 1965, Not Active", "7, 31, 4, 1965, 1965, Active"),
+                                  procs="4242, python, 80000\n"))
+    text = " | ".join(rep.failures)
+    assert "GPU 3 is at 61 C" in text and "90000 MiB" in text and "hw_slowdown" in text and "compute process" in text
+    assert any("GPU 0 is at 52 C" in w for w in rep.warnings) and any("clock lock" in w for w in rep.warnings)
+
+    rep = hc.Report()
+    hc.check_gpus(rep, expect_gpus=8, temp_warn=50, temp_fail=55, max_used_mib=1024,
+                  smi=smi_factory("\n".join(healthy.splitlines()[:6])))
+    assert any("expected 8 GPUs" in f for f in rep.failures)
+    monkeypatch.setenv("OLMO_SKIP_HEALTHCHECKS", "1")
+    assert hc.main([]) == 0
+
+
+def test_slurm_script_rendering(tmp_path):
+    from olmo_core_b200.launch.slurm import SlurmLaunchConfig
+
+    cfg = SlurmLaunchConfig(name="olmo2-7b", cmd=["python", "-m", "olmo_core_b200.scripts.train", "OLMo2-7B", "--x=a b"],
+                            nodes=4, partition="b200", env={"NCCL_DEBUG": "WARN"}, exclude_nodes=["n13"])
+    text = cfg.render()
+    assert "#SBATCH --nodes=4" in text and "#SBATCH --gpus-per-node=8" in text and "#SBATCH --partition=b200" in text
+    assert "#SBATCH --exclude=n13" in text and "export NCCL_DEBUG=WARN" in text
+    assert "olmo_core_b200.scripts.healthcheck --expect-gpus 8" in text
+    assert "--nnodes=4 --nproc-per-node=8" in text and "-m olmo_core_b200.scripts.train OLMo2-7B '--x=a b'" in text
+    path = tmp_path / "job.sbatch"
+    assert cfg.launch(str(path), dry_run=True) is None and path.read_text() == text
+    import pytest
+
+    with pytest.raises(Exception):
+        SlurmLaunchConfig(name="x", cmd=[])
