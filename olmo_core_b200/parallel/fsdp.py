@@ -404,7 +404,7 @@ class ShardedParamRuntime:
         micro-batches with :meth:`begin_microbatch`; without that announcement everything is reduced in
         :meth:`reduce_gradients` as before. ``OLMO_CORE_B200_FSDP_EARLY_REDUCE=0`` switches the overlap off.
         """
-        self._early_enabled = os.environ.get(EARLY_REDUCE_ENV_VAR, "0") != "0" and device.type == "cuda"
+        self._early_enabled = os.environ.get(EARLY_REDUCE_ENV_VAR, "1") != "0" and device.type == "cuda"
         self._early_reduced: set = set()
         self.early_reduce_blocks = 0  # blocks reduced behind their backward so far (diagnostics)
         self._last_microbatch = False

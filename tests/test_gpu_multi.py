@@ -13,7 +13,7 @@ from olmo_core_b200.testing import requires_multi_gpu, run_distributed_test
 VOCAB, SEQ = 512, 128
 
 
-def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streamed: str = "0", early: str = "0"):
+def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streamed: str = "0", early: str = "1"):
     os.environ["OLMO_CORE_B200_SYMMETRIC"] = symmetric
     os.environ["OLMO_CORE_B200_FSDP_EARLY_REDUCE"] = early
     os.environ["OLMO_CORE_B200_MULTIMEM"] = multimem
@@ -74,7 +74,7 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streame
         tm.optim_step()
         norms.append(float(rt.grad_norm_sq().sqrt()))
     torch.cuda.synchronize()
-    if early == "1":
+    if early == "1" and symmetric == "1":
         assert rt.early_reduce_blocks == 2 * steps, rt.early_reduce_blocks  # both blocks, every step
     # every rank's resident bf16 copy must hold ALL parameters, including the rows owned by the peer
     full = {s.name: rt.lowp[s.full_offset: s.full_offset + s.full_numel].float().cpu() for s in rt.slots if s.aware}
@@ -85,7 +85,7 @@ def _train(out_path: str, symmetric: str, multimem: str, steps: int = 3, streame
         torch.save({"params": full, "norms": norms}, out_path)
 
 
-def _run(tmp_path, name: str, symmetric: str, multimem: str, streamed: str = "0", early: str = "0"):
+def _run(tmp_path, name: str, symmetric: str, multimem: str, streamed: str = "0", early: str = "1"):
     out = str(tmp_path / f"{name}.pt")
     run_distributed_test(_train, world_size=2, backend="cuda:nccl,cpu:gloo",
                          func_args=(out, symmetric, multimem, 3, streamed, early))
@@ -127,10 +127,11 @@ def test_gradient_reduction_behind_the_last_backward_matches_the_one_shot_reduct
     """Resident parameters: blocks reduced on a side stream while the last micro-batch's backward still runs give the
     same gradients as the reduction after the backward (the squared norm is summed in another order, so the clipping
     factor may differ in its last bits)."""
-    ref = _run(tmp_path, "oneshot", "1", "0")
+    ref = _run(tmp_path, "oneshot", "1", "0", early="0")
     got = _run(tmp_path, "early", "1", "0", early="1")
+    assert ref["norms"][0] == pytest.approx(got["norms"][0], rel=1e-6)  # first step: same gradients, other summing order
     for a, b in zip(ref["norms"], got["norms"]):
-        assert a == pytest.approx(b, rel=1e-5)
+        assert a == pytest.approx(b, rel=1e-3)  # later steps inherit bf16 rounding flips from the last bits of the clip factor
     for name, want in ref["params"].items():
         torch.testing.assert_close(got["params"][name], want, rtol=0, atol=1e-2, msg=name)
 
