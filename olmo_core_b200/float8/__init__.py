@@ -49,15 +49,42 @@ class AOFloat8LinearConfig(Config):
 
 @dataclass
 class AOMXLinearConfig(Config):
-    """Micro-scaling (32-element blocks, E8M0 scales, e4m3 elements); ``scale_rounding``: "rceil" or "floor"."""
+    """
+    Micro-scaling linear layers (fields of src/olmo_core/float8/ao.py:189-232): e4m3 elements in blocks of 32 along the
+    reduction dimension, one E8M0 scale per block. ``scale_calculation_mode``: "floor" (the format's default rule),
+    "rceil" (tightest power of two that avoids saturation; what ``mxfp8_cublas_rceil`` selects), "ceil" or "even".
+    The cast kernels and the GEMM are this package's own, so ``kernel_preference`` / ``mxfp8_cast_kernel_choice`` are
+    accepted for compatibility and select nothing.
+    """
 
-    block_size: int = 32
-    elem_dtype: str = "float8_e4m3fn"
-    scale_rounding: str = "rceil"
+    block_size: Optional[int] = None
+    elem_dtype: Optional[str] = None
+    elem_dtype_weight_override: Optional[str] = None
+    elem_dtype_grad_output_override: Optional[str] = None
+    kernel_preference: Optional[str] = None
+    mxfp8_cast_kernel_choice: Optional[str] = None
+    scale_calculation_mode: Optional[str] = None
+
+    def __post_init__(self):
+        if self.block_size not in (None, 32):
+            raise OLMoConfigurationError(f"MX block size must be 32, got {self.block_size}")
+        for name in ("elem_dtype", "elem_dtype_weight_override", "elem_dtype_grad_output_override"):
+            value = getattr(self, name)
+            if value is not None and str(value).split(".")[-1] not in ("float8_e4m3fn", "float8_e4m3"):
+                raise OLMoConfigurationError(f"{name}={value!r}: the MX kernels implement e4m3 elements only")
+        if self.scale_calculation_mode is not None and str(self.scale_calculation_mode).split(".")[-1] not in (
+                "floor", "rceil", "ceil", "even"):
+            raise OLMoConfigurationError(f"unknown scale_calculation_mode {self.scale_calculation_mode!r}")
+
+    @property
+    def scale_rounding(self) -> str:
+        return str(self.scale_calculation_mode).split(".")[-1] if self.scale_calculation_mode is not None else "floor"
 
     @classmethod
-    def mxfp8_cublas_rceil(cls) -> "AOMXLinearConfig":
-        return cls(block_size=32, elem_dtype="float8_e4m3fn", scale_rounding="rceil")
+    def mxfp8_cublas_rceil(cls, **kwargs) -> "AOMXLinearConfig":
+        kwargs.setdefault("mxfp8_cast_kernel_choice", "cuda")
+        kwargs.setdefault("scale_calculation_mode", "rceil")
+        return cls(**kwargs)
 
 
 @dataclass

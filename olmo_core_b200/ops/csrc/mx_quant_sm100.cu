@@ -12,7 +12,8 @@
 // ordered [row / 128][reduction / 128]. One 512-byte bulk copy per tile and stage then feeds tcgen05.cp unchanged.
 //
 // Scale rounding: mode 0 ("rceil") picks the smallest power of two s with amax / s <= 448, so nothing saturates;
-// mode 1 ("floor") is the OCP MX rule s = 2^(floor(log2 amax) - 8) with a saturating cast.
+// mode 1 ("floor") is the OCP MX rule s = 2^(floor(log2 amax) - 8) with a saturating cast; mode 2 ("ceil") rounds the
+// exponent of amax up instead, mode 3 ("even") rounds amax to the nearest value representable with e4m3's mantissa first.
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -36,7 +37,12 @@ __device__ __forceinline__ uint32_t e8m0_for(float amax, int mode) {
     const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.f));
     e = (bits >> 23) + ((bits & 0x7FFFFFu) != 0u ? 1u : 0u);
   } else {
-    const uint32_t ea = __float_as_uint(amax) >> 23;
+    // floor / ceil / even: the power of two at (below, above, nearest in e4m3's 3 mantissa bits to) the maximum, then
+    // 2^-8 of it, so that the maximum lands in e4m3's top binade
+    uint32_t bits = __float_as_uint(amax);
+    if (mode == 3) bits += 1u << 19;
+    uint32_t ea = bits >> 23;
+    if (mode == 2 && (bits & 0x7FFFFFu) != 0u) ea += 1u;
     e = ea > 8u ? ea - 8u : 0u;
   }
   return min(e, 253u);

@@ -28,7 +28,7 @@ __all__ = ["MX_BLOCK", "quantize_mx_rowwise", "quantize_mx_colwise_transposed", 
            "dequantize_mx", "gemm_mx", "mx_linear", "MXLinearFunction", "mx_supported"]
 
 MX_BLOCK = 32
-_MODES = {"rceil": 0, "floor": 1}
+_MODES = {"rceil": 0, "floor": 1, "ceil": 2, "even": 3}
 
 _lib_sigs_done = False
 
@@ -85,7 +85,13 @@ def _exponents(amax: torch.Tensor, mode: str) -> torch.Tensor:
         bits = (amax.float() / 448.0).view(torch.int32)
         e = (bits >> 23) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
     else:
-        e = ((amax.float().view(torch.int32) >> 23) - 8).clamp(min=0)
+        bits = amax.float().view(torch.int32)
+        if mode == "even":
+            bits = bits + (1 << 19)
+        ea = bits >> 23
+        if mode == "ceil":
+            ea = ea + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+        e = (ea - 8).clamp(min=0)
     return e.clamp(max=253)
 
 

@@ -24,7 +24,7 @@ def test_scale_layout_roundtrip():
     assert sf[1 * 512 + 1 * 16 + 1 * 4 + 1] == e[33, 5]
 
 
-@pytest.mark.parametrize("mode", ["rceil", "floor"])
+@pytest.mark.parametrize("mode", ["rceil", "floor", "ceil", "even"])
 def test_quantize_emulation_error(mode):
     x = _rand((256, 384), 0)
     q, sf = mx.quantize_mx_rowwise(x, mode)
@@ -33,8 +33,9 @@ def test_quantize_emulation_error(mode):
     blocks = x.float().view(256, -1, 32).abs().amax(-1, keepdim=True).expand(-1, -1, 32).reshape(256, 384)
     # e4m3 keeps 3 mantissa bits: the error is below 2^-3 of the block maximum after power-of-two scaling
     assert (err <= blocks * 2.0 ** -3 + 1e-30).all()
-    if mode == "rceil":
+    if mode in ("rceil", "ceil"):
         assert (q.view(torch.float8_e4m3fn).float().abs() <= 448).all()
+        assert (x.float().view(256, -1, 32).abs().amax(-1) <= 448 * torch.exp2(mx.scales_as_matrix(sf, 256, 384).float() - 127)).all()
     qt, sft = mx.quantize_mx_colwise_transposed(x.t().contiguous(), mode)
     assert torch.equal(qt, q) and torch.equal(sft, sf)
 
@@ -81,7 +82,7 @@ def test_config_routes_linear_through_mx():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["rceil", "floor"])
+@pytest.mark.parametrize("mode", ["rceil", "floor", "ceil", "even"])
 @pytest.mark.parametrize("shape", [(256, 512), (1000, 384), (128, 4096)])
 def test_gpu_quantize_rowwise_matches_emulation(shape, mode):
     x = _rand(shape, 3, device="cuda")
@@ -92,7 +93,7 @@ def test_gpu_quantize_rowwise_matches_emulation(shape, mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["rceil", "floor"])
+@pytest.mark.parametrize("mode", ["rceil", "floor", "ceil", "even"])
 @pytest.mark.parametrize("shape", [(256, 512), (384, 1000), (4096, 136)])
 def test_gpu_quantize_colwise_transposed_matches_emulation(shape, mode):
     x = _rand(shape, 4, device="cuda")
@@ -149,7 +150,9 @@ def test_weight_cast_cache_lives_for_one_optimizer_step():
 
     ff = FeedForward(d_model=128, hidden_size=256, bias=False, dtype=torch.float32)
     cfg = Float8Config(ao_mx=AOMXLinearConfig())
-    cfg.ao = None
+    assert cfg.ao_mx.scale_rounding == "floor" and AOMXLinearConfig.mxfp8_cublas_rceil().scale_rounding == "rceil"
+    with pytest.raises(Exception):
+        AOMXLinearConfig(elem_dtype="float4_e2m1fn_x2")
     cfg.apply_float8_linear(ff)
     assert ff.w1.float8["weight_cache"] is None  # off unless asked for
     ff2 = FeedForward(d_model=128, hidden_size=256, bias=False, dtype=torch.float32)
