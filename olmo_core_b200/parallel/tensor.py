@@ -325,8 +325,9 @@ def _fuse_feed_forward(ff: nn.Module, group) -> None:
 
     def forward(x, *args, **kwargs):
         rows = x.numel() // x.shape[-1]
-        if args or kwargs or not fused_tp_available(x, group, rows):
-            return wrapped(x, *args, **kwargs)
+        if (args or kwargs or not fused_tp_available(x, group, rows)
+                or any(getattr(getattr(ff, n), "float8", None) is not None for n in ("w1", "w2", "w3"))):
+            return wrapped(x, *args, **kwargs)  # 8-bit projections keep their own GEMMs between NCCL collectives
         a, b = gather_linear_multi(x, (ff.w1.weight, ff.w3.weight), group, "ffn-up")
         y = linear_reduce_scatter(swiglu(a, b), ff.w2.weight, group, "ffn-down")
         return y.view(x.shape)
