@@ -198,7 +198,9 @@ class PackingInstanceSource(InstanceSource):
                 for s, e in sources[i].get_document_offsets():
                     rows.extend(self._fit(i, s, e))
             table = np.array(rows, dtype=np.int64).reshape(-1, 3)
-            instances, _, _ = InstancePacker(sequence_length).pack_documents(table[:, 1:])
+            packer = InstancePacker(sequence_length)
+            instances, _, _ = packer.pack_documents(table[:, 1:])
+            table = table[packer.last_order]  # the instances refer to the documents longest first
             base = len(self._docs)
             self._instance_docs.extend([[base + d for d in inst] for inst in instances])
             self._docs = np.concatenate([self._docs, table], axis=0)

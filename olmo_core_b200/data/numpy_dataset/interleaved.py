@@ -18,6 +18,7 @@ from ...aliases import PathOrStr
 from ...distributed.utils import barrier
 from ...exceptions import OLMoConfigurationError
 from ..utils import get_rng, write_array_to_disk
+from .base import locate
 from .fsl import NumpyPaddedFSLDataset, _mmap
 
 log = logging.getLogger(__name__)
@@ -86,6 +87,13 @@ class NumpyInterleavedFSLDataset(NumpyPaddedFSLDataset):
     def __len__(self) -> int:
         order, exempt = self._load_order()
         return len(order) // self._docs_per_instance + len(exempt)
+
+    def _source_of(self, index: int) -> Tuple[int, int]:
+        # indices handed to the padded base class address DOCUMENTS, of which there are more than instances
+        offsets = self.offsets
+        if self._starts is None:
+            self._starts = [o[0] for o in offsets]
+        return locate(offsets, self._starts, int(index), offsets[-1][1])
 
     def _weave(self, parts: List[torch.Tensor]) -> torch.Tensor:
         chunks = [p.tensor_split(self._chunks_per_doc) for p in parts]

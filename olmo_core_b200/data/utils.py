@@ -194,35 +194,48 @@ def load_array_slice_into_tensor(path: PathOrStr, start_idx: int, end_idx: int, 
     return torch.from_numpy(np.ascontiguousarray(arr)).long() if arr.dtype != np.bool_ else torch.from_numpy(arr.copy())
 
 
-def iter_document_indices(data_path: PathOrStr, local_cache: Optional[PathOrStr] = None, use_array_if_local: bool = True,
-                          eos_token_id: Optional[int] = None, bos_token_id: Optional[int] = None,
-                          dtype=None) -> Generator[Tuple[int, int], None, None]:
+def iter_document_indices(data_path: PathOrStr, local_cache: Optional[PathOrStr] = None,
+                          use_array_if_local: Optional[bool] = None, eos_token_id: Optional[int] = None,
+                          bos_token_id: Optional[int] = None, dtype=None) -> Generator[Tuple[int, int], None, None]:
     """
-    ``(start, end)`` token offsets of every document in a token file. Uses the ``.csv.gz`` metadata file
-    next to the data when one exists, else scans the array for EOS tokens.
+    ``(start, end)`` token offsets of every document in a token file (src/olmo_core/data/utils.py:170-250).
+
+    A local file is scanned for end-of-sequence tokens when ``eos_token_id`` and ``dtype`` are given (with
+    ``bos_token_id``, a document ends only where an EOS is followed by a BOS, or at an EOS that ends the file); otherwise
+    the ``.csv.gz`` metadata file next to the data lists the documents. Tokens after the last end-of-sequence token belong
+    to no document.
     """
+    if use_array_if_local is None:
+        use_array_if_local = eos_token_id is not None and dtype is not None and not is_url(data_path)
+    if use_array_if_local and not is_url(data_path):
+        if eos_token_id is None or dtype is None:
+            raise ValueError("'eos_token_id' and 'dtype' are required to use the local array for finding document indices")
+        n = get_file_size(data_path) // _array_itemsize(dtype)
+        arr = load_array_slice(data_path, 0, n, dtype)
+        if bos_token_id is None:
+            ends = np.nonzero(arr == eos_token_id)[0] + 1
+        else:
+            ends = np.nonzero(np.logical_and(arr[:-1] == eos_token_id, arr[1:] == bos_token_id))[0] + 1
+            if n > 0 and arr[-1] == eos_token_id:
+                ends = np.append(ends, n)
+        start = 0
+        for end in ends.tolist():
+            yield start, end
+            start = end
+        return
     meta = str(data_path).replace(".npy", ".csv.gz")
     try:
         meta_path = resource_path(os.path.dirname(meta), os.path.basename(meta), local_cache=local_cache)
-        if Path(meta_path).is_file():
-            with gzip.open(meta_path, "rt") as f:
-                for line in f:
-                    start, end, *_ = line.split(",")
-                    yield int(start), int(end)
-            return
-    except (FileNotFoundError, OSError):
-        pass
-    if eos_token_id is None or dtype is None:
-        raise FileNotFoundError(f"no document metadata for {data_path} and no EOS id / dtype to scan with")
-    n = get_file_size(data_path) // _array_itemsize(dtype)
-    arr = load_array_slice(data_path, 0, n, dtype)
-    ends = np.nonzero(arr == eos_token_id)[0] + 1
-    start = 0
-    for end in ends.tolist():
-        yield start, end
-        start = end
-    if start < n:
-        yield start, n
+    except FileNotFoundError as e:
+        raise RuntimeError(
+            f"Source metadata file '{os.path.basename(meta)}' is required to calculate document indices for '{data_path}'. "
+            "If the source data file is local (on-disk) and 'eos_token_id' and 'dtype' are provided, then the document "
+            "indices can be inferred from the source file."
+        ) from e
+    with gzip.open(meta_path, "rt") as f:
+        for line in f:
+            start, end, *_ = line.split(",")
+            yield int(start), int(end)
 
 
 def get_document_indices(data_path: PathOrStr, local_cache: Optional[PathOrStr] = None, **kwargs) -> List[Tuple[int, int]]:
@@ -404,8 +417,8 @@ class InstancePacker:
 
     @property
     def total_tokens(self) -> int:
-        """Capacity of all open instances."""
-        return self.max_sequence_length * len(self.instances)
+        """Tokens held by all instances (their capacity minus the free space left in them)."""
+        return self.max_sequence_length * len(self.instances) - self.total_padding
 
     @property
     def total_padding(self) -> int:
@@ -418,6 +431,9 @@ class InstancePacker:
             if s >= length and (best_space is None or s < best_space):
                 best, best_space = i, s
         return best
+
+    def _pack_document(self, document_id: int, document_length: int) -> int:
+        return self.pack_document(document_id, document_length)
 
     def pack_document(self, document_id: int, document_length: int) -> int:
         if document_length > self.max_sequence_length:
@@ -432,22 +448,34 @@ class InstancePacker:
         return i
 
     def pack_documents(self, document_indices: np.ndarray) -> Tuple[List[List[int]], np.ndarray, int]:
-        """``document_indices``: ``[n, 2]`` (start, end). Returns (instances, indices, total tokens)."""
-        lengths = document_indices[:, 1] - document_indices[:, 0]
-        order = np.argsort(-lengths, kind="stable")
-        # bucket free space by size so best-fit is a bisect over distinct free sizes
+        """
+        ``document_indices``: ``[n, 2]`` (start, end). Returns ``(instances, sorted indices, total tokens)``: the documents
+        are re-ordered longest first, the returned array holds them in that order and the instances refer to rows of
+        it (``last_order`` keeps the permutation). Ties are resolved exactly as the reference does
+        (src/olmo_core/data/utils.py:857-877: the same ``argsort`` call, and among instances with the same free space the
+        one that reached it first), so a given file packs into the same instances in both implementations.
+        """
         import bisect
+        from collections import deque
 
-        space_keys: List[int] = []
-        by_space: Dict[int, List[int]] = {}
-        for doc_id in order.tolist():
-            n = int(lengths[doc_id])
+        if self.instances:
+            raise RuntimeError("call 'reset()' before packing another set of documents")
+        lengths = document_indices[:, 1] - document_indices[:, 0]
+        order = np.argsort(-1 * lengths.astype(np.int64))
+        self.last_order = order
+        document_indices = np.take(document_indices, order, axis=0)
+        space_keys: List[int] = []  # distinct free sizes, ascending: best fit is a bisect
+        by_space: Dict[int, Any] = {}
+        total = 0
+        for doc_id, n in enumerate((document_indices[:, 1] - document_indices[:, 0]).tolist()):
+            n = int(n)
             if n > self.max_sequence_length:
                 raise ValueError("document is longer than the maximum sequence length")
+            total += n
             k = bisect.bisect_left(space_keys, n)
             if k < len(space_keys):
                 space = space_keys[k]
-                inst = by_space[space].pop()
+                inst = by_space[space].popleft()
                 if not by_space[space]:
                     del by_space[space]
                     space_keys.pop(k)
@@ -460,9 +488,13 @@ class InstancePacker:
             if left > 0:
                 if left not in by_space:
                     bisect.insort(space_keys, left)
-                    by_space[left] = []
+                    by_space[left] = deque()
                 by_space[left].append(inst)
-        return self.instances, document_indices, int(lengths.sum())
+        self._space = [0] * len(self.instances)
+        for space, insts in by_space.items():
+            for i in insts:
+                self._space[i] = space
+        return self.instances, document_indices, total
 
 
 def pack_documents_into_instances(path: PathOrStr, max_sequence_length: int, *, eos_token_id: int, dtype,

@@ -37,7 +37,7 @@ def test_data_helpers():
     packer = InstancePacker(8)
     for i, n in enumerate([5, 3, 4]):
         packer.pack_document(i, n)
-    assert packer.instance_bins == [[0, 1], [2]] and packer.total_tokens == 16 and packer.total_padding == 4
+    assert packer.instance_bins == [[0, 1], [2]] and packer.total_tokens == 12 and packer.total_padding == 4
     packer.reset()
     assert packer.instance_bins == []
     assert path_map(len, ["a", "bb", "ccc"], max_workers=2) == [1, 2, 3] and path_map(len, ["a"], max_workers=0) == [1]

@@ -139,3 +139,164 @@ def test_reference_weights_give_reference_loss_and_gradients(tmp_path):
         for pname, p in model.named_parameters():
             torch.testing.assert_close(p.grad, r["grads"][pname], rtol=2e-3, atol=1e-6,
                                        msg=lambda m, n=name, q=pname: f"{n} {q}: {m}")
+
+
+SCHEDULER_SPECS = [
+    "ConstantScheduler()",
+    "ConstantWithWarmup(warmup=10)",
+    "ConstantWithWarmup(warmup_fraction=0.1, warmup_min_lr=1e-5)",
+    "WSD(warmup=10, decay=20, decay_fraction=None)",
+    "WSD(warmup_fraction=0.05, decay_fraction=0.2, decay_min_lr=1e-5)",
+    "PowerLR(warmup=10)",
+    "PowerLR(warmup=7, b=-0.4, decay=15, decay_fraction=None, decay_min_lr=1e-6)",
+    "LinearWithWarmup(warmup=10)",
+    "LinearWithWarmup(warmup=5, alpha_f=0.0, t_max=80)",
+    "InvSqrtWithWarmup(warmup=12)",
+    "InvSqrtWithWarmup(warmup=12, alpha_f=0.3, warmup_min_lr=1e-4)",
+    "CosWithWarmup(warmup=10)",
+    "CosWithWarmup(warmup_fraction=0.1, alpha_f=0.01, t_max=150)",
+    "HalfCosWithWarmup(warmup=10)",
+    "CosWithWarmupAndLinearDecay(warmup=10, decay=10, decay_fraction=None)",
+    "CosWithWarmupAndLinearDecay(warmup=4, alpha_f=0.2, decay_fraction=0.25, decay_min_lr=1e-5)",
+    "ExponentialScheduler()",
+    "ExponentialScheduler(lr_min=1e-6)",
+    "WSDS(period_lengths=[40, 60], warmup=5, decay=10)",
+    "WSDS(period_lengths=[30, 30, 40], period_lr_multipliers=[1.0, 0.5, 0.25], warmup_fraction=0.1, decay_fraction=0.2, decay_min_lr=1e-5)",
+    "SequentialScheduler(schedulers=[LinearWithWarmup(warmup=10, alpha_f=0.5), CosWithWarmup(warmup=0)], schedulers_max=[50])",
+    "ComposableScheduler(stages=[ComposableSchedulerStage(duration=10, shape='linear', start_lr_fraction=0.0, end_lr_fraction=1.0),"
+    " ComposableSchedulerStage(duration=50, shape='cosine', end_lr_fraction=0.1), ComposableSchedulerStage(duration=40, shape='linear', end_lr_fraction=0.0)])",
+    "ComposableScheduler(stages=[ComposableSchedulerStage(duration=100, shape='linear', end_lr_fraction=0.5)],"
+    " override_decay=OverrideDecay(start=60, duration=20, shape='cosine', end_lr_fraction=0.01))",
+]
+
+
+def _schedule_values(module, specs):
+    out = {}
+    for spec in specs:
+        sched = eval(spec, vars(module))  # noqa: S307 - fixed strings above
+        out[spec] = [float(sched.get_lr(3e-4, t, 100)) for t in range(0, 101)]
+    return out
+
+
+def test_learning_rate_schedules_match_the_reference(tmp_path):
+    out = tmp_path / "ref_sched.json"
+    _run_reference(f"""
+        import json
+        import olmo_core.optim.scheduler as module
+        out = {{}}
+        for spec in {SCHEDULER_SPECS!r}:
+            sched = eval(spec, vars(module))
+            out[spec] = [float(sched.get_lr(3e-4, t, 100)) for t in range(0, 101)]
+        json.dump(out, open({str(out)!r}, "w"))
+    """, tmp_path)
+    import olmo_core_b200.optim.scheduler as module
+
+    want = json.loads(out.read_text())
+    got = _schedule_values(module, SCHEDULER_SPECS)
+    for spec in SCHEDULER_SPECS:
+        assert got[spec] == pytest.approx(want[spec], rel=1e-9, abs=1e-15), spec
+
+
+def test_data_loader_order_matches_the_reference(tmp_path):
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    files = []
+    for n, name in ((32 * 40, "a"), (32 * 25 + 7, "b")):
+        arr = rng.integers(2, 512, n).astype(np.uint16)
+        arr[31::32] = 1
+        arr.tofile(tmp_path / f"tokens_{name}.npy")
+        files.append(str(tmp_path / f"tokens_{name}.npy"))
+    body = """
+        import json, os, numpy as np
+        def batches(pkg, files, work, out):
+            os.makedirs(work, exist_ok=True)
+            tok = pkg.TokenizerConfig(vocab_size=512, eos_token_id=1, pad_token_id=0)
+            res = {}
+            for kind, cls in (("fsl", pkg.NumpyFSLDatasetConfig), ("padded", pkg.NumpyPaddedFSLDatasetConfig)):
+                ds = cls(tokenizer=tok, paths=files, sequence_length=32, work_dir=work).build()
+                ds.prepare()
+                res[kind + "_len"] = len(ds)
+                for ws, rank in ((1, 0), (2, 1)):
+                    loader = pkg.NumpyFSLDataLoader(ds, collator=pkg.DataCollator(pad_token_id=0), global_batch_size=8 * 32,
+                                                    work_dir=work, seed=7, dp_world_size=ws, dp_rank=rank, fs_local_rank=0)
+                    loader.reshuffle(epoch=1)
+                    seen = []
+                    for i, b in enumerate(loader):
+                        seen.append(b["input_ids"].tolist())
+                        if i == 2:
+                            break
+                    loader.reset()
+                    res[f"{kind}_ws{ws}"] = seen
+            json.dump(res, open(out, "w"))
+    """
+    ref_out, our_out = tmp_path / "ref.json", tmp_path / "ours.json"
+    _run_reference(body + f"""
+        import olmo_core.data as pkg
+        batches(pkg, {files!r}, {str(tmp_path / 'work_ref')!r}, {str(ref_out)!r})
+    """, tmp_path)
+    namespace = {}
+    exec(textwrap.dedent(body), namespace)  # noqa: S102 - the same fixed source the reference ran
+    import olmo_core_b200.data as pkg
+
+    namespace["batches"](pkg, files, str(tmp_path / "work_ours"), str(our_out))
+    want, got = json.loads(ref_out.read_text()), json.loads(our_out.read_text())
+    assert want.keys() == got.keys()
+    for key in want:
+        assert got[key] == want[key], key
+
+
+def test_packed_interleaved_and_variable_length_datasets_match_the_reference(tmp_path):
+    """Same token files, same seeds: the packed instances (best-fit-decreasing with the reference's tie rules), the woven
+    instances of the interleaved dataset, and the variable-length dataset's instances, buckets and batch order."""
+    import numpy as np
+
+    rng = np.random.default_rng(1)
+    files = []
+    for name, n in (("a", 3000), ("b", 2100)):
+        arr = rng.integers(2, 512, n).astype(np.uint16)
+        pos = 0
+        while pos < n:
+            pos += int(rng.integers(5, 90))
+            if pos < n:
+                arr[pos] = 1
+        arr[-1] = 1
+        arr.tofile(tmp_path / f"tok_{name}.npy")
+        files.append(str(tmp_path / f"tok_{name}.npy"))
+    body = """
+        import json, os, numpy as np
+        def dump(pkg, files, work, out):
+            os.makedirs(work, exist_ok=True)
+            tok = pkg.TokenizerConfig(vocab_size=512, eos_token_id=1, pad_token_id=0)
+            res = {}
+            ds = pkg.NumpyPackedFSLDatasetConfig(tokenizer=tok, paths=files, sequence_length=64, work_dir=work).build()
+            ds.prepare()
+            res["packed"] = [np.asarray(ds[i]["input_ids"]).tolist() for i in range(len(ds))]
+            ds = pkg.NumpyInterleavedFSLDatasetConfig(tokenizer=tok, paths=files, sequence_length=64, work_dir=work,
+                                                      docs_per_instance=2, chunks_per_doc=2, seed=5).build()
+            ds.prepare()
+            res["interleaved"] = [np.asarray(ds[i]["input_ids"]).tolist() for i in range(len(ds))]
+            ds = pkg.NumpyVSLDatasetConfig(tokenizer=tok, paths=files, max_sequence_length=64, min_sequence_length=8, work_dir=work,
+                                           vsl_curriculum=pkg.VSLCurriculumConfig(name="grow_p2", num_cycles=2, balanced=False)).build()
+            ds.prepare()
+            res["vsl"] = [np.asarray(ds[i]["input_ids"]).tolist() for i in range(len(ds))]
+            res["vsl_buckets"] = {str(s): np.asarray(ds.get_instance_bucket(s)).tolist() for s, _ in ds.instances_per_bucket}
+            per_bucket = ds.curriculum.batches_per_bucket(ds, 128)
+            res["vsl_batches_per_bucket"] = [[int(a), int(b)] for a, b in per_bucket]
+            res["vsl_batch_order"] = np.asarray(ds.curriculum.get_batch_indices(per_bucket, 4)).tolist()
+            json.dump(res, open(out, "w"))
+    """
+    ref_out, our_out = tmp_path / "ref.json", tmp_path / "ours.json"
+    _run_reference(body + f"""
+        import olmo_core.data as pkg
+        dump(pkg, {files!r}, {str(tmp_path / 'work_ref')!r}, {str(ref_out)!r})
+    """, tmp_path)
+    namespace = {}
+    exec(textwrap.dedent(body), namespace)  # noqa: S102 - the same fixed source the reference ran
+    import olmo_core_b200.data as pkg
+
+    namespace["dump"](pkg, files, str(tmp_path / "work_ours"), str(our_out))
+    want, got = json.loads(ref_out.read_text()), json.loads(our_out.read_text())
+    assert want.keys() == got.keys()
+    for key in want:
+        assert got[key] == want[key], key
