@@ -355,18 +355,25 @@ class Config:
         *,
         exclude_none: bool = False,
         exclude_private_fields: bool = False,
+        exclude: Optional[Iterable[str]] = None,
         include_class_name: bool = False,
+        include_registered_name: bool = False,
         json_safe: bool = False,
         recurse: bool = True,
     ) -> Dict[str, Any]:
         """
-        Convert to a dictionary. ``include_class_name`` injects ``_CLASS_`` (and the registered
-        ``type`` name); ``json_safe`` converts enums, dtypes and tuples; ``recurse=False`` keeps nested
-        configs as objects (the form builders pass to constructors).
+        Convert to a dictionary (options of src/olmo_core/config.py:84-151). ``exclude`` drops fields by name at every
+        level; ``include_class_name`` injects ``_CLASS_``; the registered ``type`` name of :class:`Registrable` configs is
+        added with ``include_registered_name`` (and alongside the class name); ``json_safe`` converts enums, dtypes and
+        tuples; ``recurse=False`` keeps nested configs as objects (the form builders pass to constructors). Fields that
+        are not constructor arguments are left out.
         """
+        excluded = set(exclude) if exclude is not None else set()
 
         def iter_fields(d) -> Generator[Tuple[str, Any], None, None]:
             for f in fields(d):
+                if f.name in excluded or not f.init:
+                    continue
                 value = getattr(d, f.name)
                 if exclude_none and value is None:
                     continue
@@ -381,10 +388,10 @@ class Config:
                 out = {k: convert(v) for k, v in iter_fields(d)}
                 if include_class_name:
                     out[Config.CLASS_NAME_FIELD] = f"{d.__class__.__module__}.{d.__class__.__qualname__}"
-                    if isinstance(d, Registrable) and "type" not in out:
-                        name = d.get_registered_name(type(d))
-                        if name is not None:
-                            out["type"] = name
+                if (include_class_name or include_registered_name) and isinstance(d, Registrable) and "type" not in out:
+                    name = d.get_registered_name(type(d))
+                    if name is not None:
+                        out["type"] = name
                 return out
             if isinstance(d, dict):
                 return {(encode(k) if json_safe else k): convert(v) for k, v in d.items()}
@@ -403,7 +410,8 @@ class Config:
 
     def as_config_dict(self) -> Dict[str, Any]:
         """JSON-safe dict that :meth:`from_dict` can rebuild the exact classes from."""
-        return self.as_dict(exclude_none=True, exclude_private_fields=True, include_class_name=True, json_safe=True)
+        return self.as_dict(exclude_none=True, exclude_private_fields=True, include_class_name=True,
+                            include_registered_name=True, json_safe=True)
 
     def apply(self, func: Callable[["Config"], None]) -> None:
         """Call ``func`` on this config and, recursively, every config nested inside it."""

@@ -232,15 +232,16 @@ class InstanceSourceConfig(Config):
     def resize(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingInstanceSourceConfig":
         return self.sample(factor=factor, seed=seed)
 
-    def split(self, ratio: float) -> Tuple["SplitInstanceSourceConfig", "SplitInstanceSourceConfig"]:
-        return (SplitInstanceSourceConfig(source=self, ratio=ratio, idx=0),
-                SplitInstanceSourceConfig(source=self, ratio=ratio, idx=1))
+    def split(self, ratio: float, seed: Optional[int] = None
+              ) -> Tuple["SplitInstanceSourceConfig", "SplitInstanceSourceConfig"]:
+        """Two disjoint parts (``ratio`` / ``1 - ratio`` of the instances); a ``seed`` deals the instances at random."""
+        seed = resolve_seed(seed)
+        return (SplitInstanceSourceConfig(source=self, ratio=ratio, idx=0, seed=seed),
+                SplitInstanceSourceConfig(source=self, ratio=ratio, idx=1, seed=seed))
 
     def random_split(self, ratio: float, seed: Optional[int] = SEED_NOT_SET
                      ) -> Tuple["SplitInstanceSourceConfig", "SplitInstanceSourceConfig"]:
-        seed = resolve_seed(seed)
-        return (SplitInstanceSourceConfig(source=self, ratio=ratio, idx=0, random=True, seed=seed),
-                SplitInstanceSourceConfig(source=self, ratio=ratio, idx=1, random=True, seed=seed))
+        return self.split(ratio, seed=seed)
 
 
 @dataclass
@@ -249,6 +250,20 @@ class ConcatAndChunkInstanceSourceConfig(InstanceSourceConfig):
     sequence_length: int
     max_sequence_length: Optional[int] = None
     label: Optional[str] = None
+
+    @classmethod
+    def from_npy(cls, *npy_paths: str, tokenizer: TokenizerConfig, sequence_length: int,
+                 max_sequence_length: Optional[int] = None, dtype=None, source_permutation_seed: Optional[int] = None,
+                 source_group_size: int = 1, label_mask_paths: Optional[List[str]] = None,
+                 expand_glob: Optional[bool] = None, label: Optional[str] = None) -> "ConcatAndChunkInstanceSourceConfig":
+        """Instances cut from one or more tokenized ``.npy`` files."""
+        from .numpy_document_source import NumpyDocumentSourceConfig
+
+        return cls(sources=[NumpyDocumentSourceConfig(
+            source_paths=list(npy_paths), tokenizer=tokenizer, dtype=dtype,
+            source_permutation_seed=resolve_seed(source_permutation_seed), source_group_size=source_group_size,
+            label_mask_paths=label_mask_paths, expand_glob=expand_glob)],
+            sequence_length=sequence_length, max_sequence_length=max_sequence_length, label=label)
 
     def build(self, work_dir: PathOrStr) -> ConcatAndChunkInstanceSource:
         return ConcatAndChunkInstanceSource(*_build_all(self.sources, work_dir), sequence_length=self.sequence_length,
@@ -266,26 +281,45 @@ class PackingInstanceSourceConfig(InstanceSourceConfig):
     source_group_size: int = 1
     label: Optional[str] = None
 
+    @classmethod
+    def from_npy(cls, *npy_paths: str, tokenizer: TokenizerConfig, sequence_length: int,
+                 max_sequence_length: Optional[int] = None, dtype=None, source_permutation_seed: Optional[int] = None,
+                 source_group_size: int = 1, label_mask_paths: Optional[List[str]] = None,
+                 expand_glob: Optional[bool] = None, label: Optional[str] = None,
+                 long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate) -> "PackingInstanceSourceConfig":
+        """Whole documents of one or more tokenized ``.npy`` files packed into instances."""
+        from .numpy_document_source import NumpyDocumentSourceConfig
+
+        return cls(sources=[NumpyDocumentSourceConfig(
+            source_paths=list(npy_paths), tokenizer=tokenizer, dtype=dtype,
+            source_permutation_seed=resolve_seed(source_permutation_seed), source_group_size=source_group_size,
+            label_mask_paths=label_mask_paths, expand_glob=expand_glob)],
+            sequence_length=sequence_length, tokenizer=tokenizer, max_sequence_length=max_sequence_length, label=label,
+            long_doc_strategy=long_doc_strategy, source_group_size=source_group_size)
+
     def build(self, work_dir: PathOrStr) -> PackingInstanceSource:
         return PackingInstanceSource(*_build_all(self.sources, work_dir), sequence_length=self.sequence_length,
                                      max_sequence_length=self.max_sequence_length,
-                                     pad_token_id=self.tokenizer.pad_token_id, long_doc_strategy=self.long_doc_strategy,
+                                     tokenizer=self.tokenizer, long_doc_strategy=self.long_doc_strategy,
                                      source_group_size=self.source_group_size, work_dir=work_dir, label=self.label)
 
 
 @dataclass
 class RandomInstanceSourceConfig(InstanceSourceConfig):
-    num_instances: int
+    tokenizer: TokenizerConfig
     sequence_length: int
-    vocab_size: int
-    max_sequence_length: Optional[int] = None
+    avg_document_length: int
     seed: Optional[int] = field(default_factory=_default_seed)
+    num_instances: Optional[int] = None
+    num_tokens: Optional[int] = None
+    max_sequence_length: Optional[int] = None
     label: Optional[str] = None
 
     def build(self, work_dir: PathOrStr) -> RandomInstanceSource:
-        return RandomInstanceSource(num_instances=self.num_instances, sequence_length=self.sequence_length,
-                                    vocab_size=self.vocab_size, max_sequence_length=self.max_sequence_length,
-                                    seed=self.seed, work_dir=work_dir, label=self.label)
+        return RandomInstanceSource(tokenizer=self.tokenizer, sequence_length=self.sequence_length,
+                                    avg_document_length=self.avg_document_length, seed=self.seed,
+                                    num_instances=self.num_instances, num_tokens=self.num_tokens,
+                                    max_sequence_length=self.max_sequence_length, label=self.label, work_dir=work_dir)
 
 
 @dataclass
@@ -302,17 +336,17 @@ class SplitInstanceSourceConfig(InstanceSourceConfig):
     source: InstanceSourceConfig
     ratio: float
     idx: int
-    random: bool = False
     seed: Optional[int] = None
 
     def __post_init__(self):
+        if not 0 < self.ratio < 1:
+            raise ValueError("'ratio' must be strictly between 0 and 1")
         if self.idx not in (0, 1):
             raise ValueError("'idx' must be 0 or 1")
+        self.seed = resolve_seed(self.seed)
 
     def build(self, work_dir: PathOrStr) -> InstanceSource:
-        source = self.source.build(work_dir)
-        parts = source.random_split(self.ratio, seed=self.seed) if self.random else source.split(self.ratio)
-        return parts[self.idx]
+        return self.source.build(work_dir).split(self.ratio, seed=self.seed)[self.idx]
 
 
 @dataclass
@@ -326,10 +360,11 @@ class SamplingInstanceSourceConfig(InstanceSourceConfig):
 
     def build(self, work_dir: PathOrStr) -> SamplingInstanceSource:
         built = [s.build(work_dir) for s in self.sources]
-        max_instances = self.max_instances
-        if self.factor is not None:
-            max_instances = int(self.factor * sum(len(s) for s in built))
-        return SamplingInstanceSource(*built, max_tokens=self.max_tokens, max_instances=max_instances, seed=self.seed,
+        max_tokens, max_instances = self.max_tokens, self.max_instances
+        if max_tokens is None and max_instances is None:
+            assert self.factor is not None
+            max_tokens = int(self.factor * sum(s.num_tokens for s in built))
+        return SamplingInstanceSource(*built, max_tokens=max_tokens, max_instances=max_instances, seed=self.seed,
                                       work_dir=work_dir, label=self.label)
 
 

@@ -21,7 +21,8 @@ from ..types import LongDocStrategy
 from ..utils import InstancePacker, get_rng
 from .source_abc import SourceABC
 from .token_source import DocumentSource, TokenSource
-from .utils import SEED_NOT_SET, as_ndarray, calculate_sample_sizes, resolve_seed
+from ...exceptions import OLMoConfigurationError
+from .utils import SEED_NOT_SET, as_ndarray, build_global_indices, calculate_sample_sizes, resolve_seed
 
 __all__ = [
     "Instance", "InstanceSource", "ConcatAndChunkInstanceSource", "PackingInstanceSource", "RandomInstanceSource",
@@ -93,32 +94,31 @@ class InstanceSource(SourceABC):
         if sum(given) != 1:
             raise ValueError("exactly one of 'max_tokens', 'max_instances' and 'factor' is required")
         if factor is not None:
-            max_instances = int(factor * len(self))
+            max_tokens = int(self.num_tokens * factor)
         return SamplingInstanceSource(self, max_tokens=max_tokens, max_instances=max_instances, seed=seed,
                                       work_dir=self.common_work_dir, label=self.label)
 
     def resize(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingInstanceSource":
-        return self.sample(factor=factor, seed=seed)
+        assert factor > 0
+        return self.sample(max_tokens=int(self.num_tokens * factor), seed=seed)
 
-    def split(self, ratio: float) -> Tuple["SlicedInstanceSource", "SlicedInstanceSource"]:
-        """Two contiguous parts; the cut falls on a ``max_sequence_length`` boundary."""
+    def split(self, ratio: float, seed: Optional[int] = None) -> Tuple["SlicedInstanceSource", "SlicedInstanceSource"]:
+        """
+        Two disjoint parts holding ``ratio`` and ``1 - ratio`` of the instances; the cut falls on a
+        ``max_sequence_length`` boundary. With a ``seed`` the instances are dealt to the parts at random (in units of
+        ``max_sequence_length``), without one the first part is the front of the source
+        (src/olmo_core/data/composable/instance_source.py:179-204).
+        """
         if not 0 < ratio < 1:
             raise ValueError("'ratio' must be strictly between 0 and 1")
-        group = self.max_sequence_length // self.sequence_length
-        cut = int(ratio * len(self)) // group * group
-        return (SlicedInstanceSource(self, slice(0, cut), work_dir=self.common_work_dir, label=self.label),
-                SlicedInstanceSource(self, slice(cut, len(self)), work_dir=self.common_work_dir, label=self.label))
+        cut = int(((ratio * self.num_tokens) // self.max_sequence_length) * (self.max_sequence_length // self.sequence_length))
+        return (SlicedInstanceSource(self, slice(0, cut), seed=seed, work_dir=self.common_work_dir),
+                SlicedInstanceSource(self, slice(cut, None), seed=seed, work_dir=self.common_work_dir))
 
     def random_split(self, ratio: float, seed: Optional[int] = SEED_NOT_SET
-                     ) -> Tuple["SamplingInstanceSource", "SamplingInstanceSource"]:
-        """Two disjoint random parts."""
-        if not 0 < ratio < 1:
-            raise ValueError("'ratio' must be strictly between 0 and 1")
-        seed = resolve_seed(seed)
-        order = np.arange(len(self)) if seed is None else get_rng(seed).permutation(len(self))
-        cut = int(ratio * len(self))
-        return tuple(SamplingInstanceSource(self, indices=np.sort(part), seed=seed, work_dir=self.common_work_dir,  # type: ignore[return-value]
-                                            label=self.label) for part in (order[:cut], order[cut:]))
+                     ) -> Tuple["SlicedInstanceSource", "SlicedInstanceSource"]:
+        """:meth:`split` with a (by default fresh) seed."""
+        return self.split(ratio, seed=seed)
 
     def visualize(self, icons: bool = True) -> None:
         from .visualize import visualize_source
@@ -177,11 +177,17 @@ class PackingInstanceSource(InstanceSource):
 
     DISPLAY_ICON = ""
 
-    def __init__(self, *sources: DocumentSource, sequence_length: int, pad_token_id: int, work_dir: PathOrStr,
-                 max_sequence_length: Optional[int] = None, long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate,
-                 source_group_size: int = 1, label: Optional[str] = None):
+    def __init__(self, *sources: DocumentSource, sequence_length: int, work_dir: PathOrStr, tokenizer=None,
+                 pad_token_id: Optional[int] = None, max_sequence_length: Optional[int] = None,
+                 long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate, source_group_size: int = 1,
+                 label: Optional[str] = None):
         if not sources:
             raise ValueError("At least one source must be provided.")
+        if tokenizer is not None:
+            pad_token_id = tokenizer.pad_token_id
+        if pad_token_id is None:
+            raise ValueError("a tokenizer config (or 'pad_token_id') is required")
+        self._tokenizer = tokenizer
         if max_sequence_length not in (None, sequence_length):
             raise ValueError("packed instances cannot be re-cut: 'max_sequence_length' must equal 'sequence_length'")
         super().__init__(work_dir=work_dir, sequence_length=sequence_length, label=label)
@@ -217,6 +223,30 @@ class PackingInstanceSource(InstanceSource):
         return self._sources
 
     @property
+    def sources(self) -> Tuple[DocumentSource, ...]:
+        return self._sources
+
+    @property
+    def source_groups(self) -> Tuple[Tuple[DocumentSource, ...], ...]:
+        return tuple(self._sources[g:g + self._group_size] for g in range(0, len(self._sources), self._group_size))
+
+    @property
+    def source_group_size(self) -> int:
+        return self._group_size
+
+    @property
+    def long_doc_strategy(self) -> LongDocStrategy:
+        return self._strategy
+
+    @property
+    def pad_token_id(self) -> int:
+        return self._pad
+
+    @property
+    def num_instances(self) -> int:
+        return len(self._instance_docs)
+
+    @property
     def fingerprint(self) -> str:
         return self._hash(*[s.fingerprint for s in self._sources], self.sequence_length, self._pad, self._strategy,
                           self._group_size)
@@ -240,30 +270,117 @@ class PackingInstanceSource(InstanceSource):
 
 
 class RandomInstanceSource(InstanceSource):
-    """Uniformly random token ids, reproducible per index; for benchmarks and tests."""
+    """
+    Random token ids with random document boundaries, reproducible per index: for benchmarks and tests
+    (src/olmo_core/data/composable/random_instance_source.py:44-196). Special tokens never appear inside a document;
+    every ``max_sequence_length`` window ends with EOS (and starts with BOS when the tokenizer has one) and holds about
+    ``max_sequence_length / avg_document_length`` documents.
+    """
 
     DISPLAY_ICON = ""
 
-    def __init__(self, *, num_instances: int, sequence_length: int, vocab_size: int, work_dir: PathOrStr,
-                 max_sequence_length: Optional[int] = None, seed: Optional[int] = SEED_NOT_SET, label: Optional[str] = None):
+    def __init__(self, *, tokenizer=None, sequence_length: int, avg_document_length: Optional[int] = None,
+                 seed: Optional[int] = SEED_NOT_SET, num_instances: Optional[int] = None, num_tokens: Optional[int] = None,
+                 max_sequence_length: Optional[int] = None, label: Optional[str] = None, work_dir: PathOrStr,
+                 vocab_size: Optional[int] = None):
+        if (num_tokens is None) == (num_instances is None):
+            raise ValueError("Either num_tokens or num_instances must be set, but not both.")
+        if num_tokens is None:
+            num_tokens = num_instances * sequence_length  # type: ignore[operator]
         super().__init__(work_dir=work_dir, sequence_length=sequence_length, max_sequence_length=max_sequence_length,
                          label=label)
-        self._n, self._vocab = num_instances, vocab_size
-        self._seed = resolve_seed(seed) or 0
+        if tokenizer is None:
+            if vocab_size is None:
+                raise ValueError("a tokenizer config (or 'vocab_size') is required")
+            from ..tokenizer import TokenizerConfig
+
+            tokenizer = TokenizerConfig(vocab_size=vocab_size, eos_token_id=0, pad_token_id=1)
+        self._tokenizer = tokenizer
+        self._num_tokens = self.max_sequence_length * (num_tokens // self.max_sequence_length)
+        self._avg_document_length = avg_document_length or self.max_sequence_length
+        seed = resolve_seed(seed)
+        assert seed is not None
+        self._seed = seed
+
+    @property
+    def num_tokens(self) -> int:
+        return self._num_tokens
+
+    @property
+    def seed(self) -> int:
+        return self._seed
+
+    @property
+    def eos_token_id(self) -> int:
+        return self._tokenizer.eos_token_id
+
+    @property
+    def bos_token_id(self) -> Optional[int]:
+        return self._tokenizer.bos_token_id
+
+    @property
+    def pad_token_id(self) -> int:
+        return self._tokenizer.pad_token_id
+
+    @property
+    def vocab_size(self) -> int:
+        return self._tokenizer.vocab_size
+
+    @property
+    def avg_document_length(self) -> int:
+        return self._avg_document_length
+
+    @property
+    def non_special_token(self) -> int:
+        special = (self.eos_token_id, self.bos_token_id, self.pad_token_id)
+        for token_id in range(self.vocab_size):
+            if token_id not in special:
+                return token_id
+        raise RuntimeError("No non-special token found in the vocabulary.")
+
+    @property
+    def dtype(self):
+        for dtype in (np.uint8, np.uint16, np.uint32):
+            if np.iinfo(dtype).max >= self.vocab_size:
+                return dtype
+        return np.uint64
 
     def children(self):
         return []
 
     @property
     def fingerprint(self) -> str:
-        return self._hash(self._n, self.sequence_length, self._vocab, self._seed)
+        return self._hash(self._num_tokens, self._seed, self.max_sequence_length, self.eos_token_id, self.bos_token_id,
+                          self.pad_token_id, self.vocab_size)
 
     def __len__(self) -> int:
-        return self._n
+        return self._num_tokens // self.sequence_length
 
     def __getitem__(self, idx: int) -> Instance:
         idx = self.validate_index(idx)
-        return {"input_ids": get_rng(self._seed + idx).integers(0, self._vocab, self.sequence_length, dtype=np.int64)}
+        per_window = self.max_sequence_length // self.sequence_length
+        window = idx // per_window
+        rng = get_rng(self._seed + window)
+        L = self.max_sequence_length
+        tokens = rng.integers(0, self.vocab_size, L, dtype=self.dtype)
+        filler = self.non_special_token
+        for special in (self.eos_token_id, self.pad_token_id, self.bos_token_id):
+            if special is not None:
+                tokens[tokens == special] = filler
+        num_docs = max(1, round(rng.integers(-3, 3) + L / self._avg_document_length))
+        tokens[-1] = self.eos_token_id
+        if self.bos_token_id is not None:
+            tokens[0] = self.bos_token_id
+        if num_docs > 1:
+            margin = 1 if self.bos_token_id is None else 2
+            ends = margin + rng.permutation(L - 2 * margin - 1)[: num_docs - 1]
+            tokens[ends] = self.eos_token_id
+            if self.bos_token_id is not None:
+                tokens[ends + 1] = self.bos_token_id
+        if per_window > 1:
+            start = (idx % per_window) * self.sequence_length
+            tokens = tokens[start: start + self.sequence_length]
+        return {"input_ids": tokens}
 
 
 # ------------------------------------------------------------------------------------------------ composites
@@ -317,65 +434,111 @@ class ConcatenatedInstanceSource(_Indexed):
 
 
 class SlicedInstanceSource(_Indexed):
+    """
+    A slice of the source's instances in the order :func:`build_global_indices` gives for ``seed`` (the source's own
+    order without one); whole ``max_sequence_length`` units only (src/olmo_core/data/composable/sliced_instance_source.py).
+    """
+
     DISPLAY_ICON = ""
 
-    def __init__(self, source: InstanceSource, source_slice: slice, *, work_dir: PathOrStr, label: Optional[str] = None):
-        idx = np.arange(len(source), dtype=np.int64)[source_slice]
-        self.source_slice = source_slice
-        super().__init__([source], np.zeros(len(idx), dtype=np.int32), idx, work_dir=work_dir, label=label)
+    def __init__(self, source: InstanceSource, source_slice: slice, *, seed: Optional[int] = None, work_dir: PathOrStr,
+                 label: Optional[str] = None):
+        self._slice = source_slice
+        self._seed = resolve_seed(seed)
+        order = build_global_indices(len(source), sequence_length=source.sequence_length,
+                                     max_sequence_length=source.max_sequence_length, seed=self._seed)[source_slice]
+        if order.size == 0:
+            raise OLMoConfigurationError(f"{type(self).__name__} created with an empty slice ({source_slice}) from source "
+                                         f"with {len(source):,d} instances.")
+        group = source.max_sequence_length // source.sequence_length
+        order = order[: group * (len(order) // group)]
+        super().__init__([source], np.zeros(len(order), dtype=np.int32), order.astype(np.int64), work_dir=work_dir,
+                         label=label if label is not None else source.label)
 
     @property
     def source(self) -> InstanceSource:
         return self._children[0]
 
+    @property
+    def source_slice(self) -> slice:
+        return self._slice
+
+    @property
+    def seed(self) -> Optional[int]:
+        return self._seed
+
+    @property
+    def num_instances(self) -> int:
+        return len(self)
+
+    @property
+    def fingerprint(self) -> str:
+        group = self.max_sequence_length // self.sequence_length
+        sl = self._slice
+        return self._hash(type(self).__name__, self._seed, self.max_sequence_length,
+                          (sl.start // group) if sl.start is not None else 0, (sl.stop // group) if sl.stop is not None else -1,
+                          (sl.step // group) if sl.step is not None else 1, self.source.fingerprint)
+
 
 class SamplingInstanceSource(_Indexed):
     """
-    ``max_instances`` (or ``max_tokens``) instances drawn from the sources in proportion to their sizes. Units of
-    ``max_sequence_length // sequence_length`` neighbouring instances are kept together. A source smaller than its
-    share is repeated whole before the remainder is drawn (at random with a seed, from the front without).
+    ``max_instances`` (or ``max_tokens``) instances drawn from the sources in proportion to their sizes, in whole
+    ``max_sequence_length`` units (src/olmo_core/data/composable/sampling_instance_source.py:62-234). Source ``i``
+    contributes its instances in the order :func:`build_global_indices` gives for ``seed + i`` (its own order without a
+    seed): that order repeated as often as it fits into the source's share, then its front.
     """
 
     DISPLAY_ICON = ""
 
     def __init__(self, *sources: InstanceSource, max_tokens: Optional[int] = None, max_instances: Optional[int] = None,
-                 indices: Optional[np.ndarray] = None, seed: Optional[int] = SEED_NOT_SET, work_dir: PathOrStr,
-                 label: Optional[str] = None):
+                 work_dir: PathOrStr, seed: Optional[int] = SEED_NOT_SET, label: Optional[str] = None):
         if not sources:
-            raise ValueError("At least one source must be provided.")
-        self._seed = resolve_seed(seed)
-        if indices is not None:  # explicit selection from a single source (used by random_split)
-            assert len(sources) == 1
-            super().__init__(sources, np.zeros(len(indices), dtype=np.int32), indices, work_dir=work_dir, label=label)
-            return
+            raise OLMoConfigurationError("At least one source must be provided.")
         seq, max_seq = sources[0].sequence_length, sources[0].max_sequence_length
         if (max_tokens is None) == (max_instances is None):
-            raise ValueError("exactly one of 'max_tokens' and 'max_instances' is required")
+            raise OLMoConfigurationError("Either max_tokens or max_instances must be set, but not both.")
         if max_instances is None:
-            max_instances = max_tokens // seq  # type: ignore[operator]
+            assert max_tokens is not None and max_tokens > 0
+            max_instances = max_tokens // seq
+        assert max_instances > 0
+        self._max_instances = max_instances
+        self._seed = resolve_seed(seed)
+        if self._seed is None:
+            import warnings
+
+            warnings.warn("No seed provided for SamplingInstanceSource. It's recommended to set a seed to ensure that the "
+                          "distribution of instances in child sources are preserved.")
+        total = sum(len(src) for src in sources)
         group = max_seq // seq
-        total = sum(len(s) for s in sources)
-        rng = None if self._seed is None else get_rng(self._seed)
-        ids, idx = [], []
-        for i, s in enumerate(sources):
-            units_available = len(s) // group
-            units_wanted = round(max_instances * len(s) / total) // group
-            if units_available == 0 or units_wanted == 0:
-                continue
-            picked = [np.arange(units_available)] * (units_wanted // units_available)
-            rest = units_wanted % units_available
-            if rest:
-                picked.append(np.arange(rest) if rng is None else np.sort(rng.choice(units_available, rest, replace=False)))
-            units = np.concatenate(picked)
-            inst = (units[:, None] * group + np.arange(group)[None, :]).reshape(-1)
-            ids.append(np.full(len(inst), i, dtype=np.int32))
-            idx.append(inst)
-        super().__init__(sources, np.concatenate(ids) if ids else np.empty(0, np.int32),
-                         np.concatenate(idx) if idx else np.empty(0, np.int64), work_dir=work_dir, label=label)
+        sizes, ids, idx = [], [], []
+        for i, src in enumerate(sources):
+            if src.sequence_length != seq or src.max_sequence_length != max_seq:
+                raise OLMoConfigurationError("All sources must have the same sequence length and max sequence length.")
+            size = group * (int(max_instances * (len(src) / total)) // group)
+            sizes.append(size)
+            order = build_global_indices(len(src), sequence_length=seq, max_sequence_length=max_seq,
+                                         seed=None if self._seed is None else self._seed + i)
+            picked = np.concatenate([np.tile(order, size // len(src)), order[: size % len(src)]]) if len(src) else order
+            ids.append(np.full(len(picked), i, dtype=np.int32))
+            idx.append(picked.astype(np.int64))
+        self._source_sample_sizes = tuple(sizes)
+        super().__init__(sources, np.concatenate(ids), np.concatenate(idx), work_dir=work_dir, label=label)
 
     @property
     def seed(self) -> Optional[int]:
         return self._seed
+
+    @property
+    def max_instances(self) -> int:
+        return self._max_instances
+
+    @property
+    def source_sample_sizes(self) -> Tuple[int, ...]:
+        return self._source_sample_sizes
+
+    @property
+    def num_instances(self) -> int:
+        return sum(self._source_sample_sizes)
 
 
 @dataclass
@@ -385,31 +548,47 @@ class MixingInstanceSourceSpec:
     max_repetition_factor: float = 1.0
     label: Optional[str] = None
 
+    def __post_init__(self):
+        if self.ratio <= 0:
+            raise OLMoConfigurationError("Ratio must be greater than 0.")
+        if self.max_repetition_factor < 1.0:
+            raise OLMoConfigurationError("Max repetition must be at least 1.0.")
+
 
 class MixingInstanceSource(_Indexed):
-    """Instance sources combined at given ratios; ``num_tokens`` / ``num_instances`` fixes the size of the mix."""
+    """
+    Instance sources combined at given ratios (src/olmo_core/data/composable/mixing_instance_source.py:111-245): the
+    shares are worked out in tokens, every source is then sampled with :class:`SamplingInstanceSource` (seed ``seed + i``)
+    and the samples are concatenated. ``num_tokens`` / ``num_instances`` fixes the size of the mix.
+    """
 
     DISPLAY_ICON = ""
     Spec = MixingInstanceSourceSpec
 
     def __init__(self, *source_specs: MixingInstanceSourceSpec, work_dir: PathOrStr, seed: Optional[int] = SEED_NOT_SET,
-                 num_tokens: Optional[int] = None, num_instances: Optional[int] = None, label: Optional[str] = None):
+                 label: Optional[str] = None, num_tokens: Optional[int] = None, num_instances: Optional[int] = None):
         if not source_specs:
-            raise ValueError("At least one source spec must be provided.")
+            raise OLMoConfigurationError("At least one source spec must be provided.")
         self._seed = resolve_seed(seed)
         seq = source_specs[0].source.sequence_length
-        if num_tokens is not None and num_instances is None:
-            num_instances = num_tokens // seq
+        if num_tokens is not None and num_instances is not None and num_tokens != num_instances * seq:
+            raise OLMoConfigurationError("`num_tokens` and `num_instances` are mutually exclusive")
+        if num_instances is not None:
+            num_tokens = num_instances * seq
         labels = [spec.label or spec.source.label or str(i) for i, spec in enumerate(source_specs)]
-        sizes = calculate_sample_sizes([len(spec.source) for spec in source_specs], [spec.ratio for spec in source_specs],
-                                       [spec.max_repetition_factor for spec in source_specs], target_size=num_instances,
-                                       labels=labels, unit="instances")
-        sampled = [SamplingInstanceSource(spec.source, max_instances=int(size),
+        sizes = calculate_sample_sizes([spec.source.num_tokens for spec in source_specs], [spec.ratio for spec in source_specs],
+                                       [spec.max_repetition_factor for spec in source_specs], target_size=num_tokens,
+                                       labels=labels)
+        sampled = [SamplingInstanceSource(spec.source, max_tokens=int(size),
                                           seed=None if self._seed is None else self._seed + i, work_dir=work_dir,
-                                          label=labels[i])
+                                          label=spec.label or spec.source.label)
                    for i, (spec, size) in enumerate(zip(source_specs, sizes.tolist()))]
-        self.sampled_sources = tuple(sampled)
+        self._sampled_sources = tuple(sampled)
         super().__init__(sampled, *_all_of(sampled), work_dir=work_dir, label=label)
+
+    @property
+    def sampled_sources(self) -> Tuple[SamplingInstanceSource, ...]:
+        return self._sampled_sources
 
     @property
     def seed(self) -> Optional[int]:

@@ -144,11 +144,22 @@ class InMemoryTokenSource(TokenSource):
 
 
 class InMemoryDocumentSource(InMemoryTokenSource, DocumentSource):
-    """Documents are delimited by ``eos_token_id`` (each document ends WITH it) or start at ``bos_token_id`` if given."""
+    """
+    Documents end WITH the tokenizer's EOS token (where a BOS token exists, only an EOS followed by a BOS ends a
+    document); whatever follows the last boundary is a document too
+    (src/olmo_core/data/composable/token_source.py:292-354). ``eos_token_id`` / ``bos_token_id`` may be given instead of
+    a tokenizer config.
+    """
 
-    def __init__(self, tokens: Sequence[int], *, eos_token_id: int, bos_token_id: Optional[int] = None,
-                 work_dir: PathOrStr, label_mask: Optional[Sequence[bool]] = None, label: Optional[str] = None):
+    def __init__(self, tokens: Sequence[int], *, tokenizer=None, work_dir: PathOrStr,
+                 label_mask: Optional[Sequence[bool]] = None, label: Optional[str] = None,
+                 eos_token_id: Optional[int] = None, bos_token_id: Optional[int] = None):
         super().__init__(tokens, work_dir=work_dir, label_mask=label_mask, label=label)
+        if tokenizer is not None:
+            eos_token_id, bos_token_id = tokenizer.eos_token_id, tokenizer.bos_token_id
+        if eos_token_id is None:
+            raise ValueError("a tokenizer config (or 'eos_token_id') is required")
+        self._tokenizer = tokenizer
         self._eos, self._bos = eos_token_id, bos_token_id
 
     @property
@@ -165,19 +176,16 @@ class InMemoryDocumentSource(InMemoryTokenSource, DocumentSource):
 
     def get_document_offsets(self) -> Iterable[Tuple[int, int]]:
         n = len(self._tokens)
-        if self._bos is not None:
-            starts = np.flatnonzero(self._tokens == self._bos)
-            if len(starts) == 0 or starts[0] != 0:
-                starts = np.concatenate([[0], starts])
-            ends = np.concatenate([starts[1:], [n]])
-        else:
+        if self._bos is None:
             ends = np.flatnonzero(self._tokens == self._eos) + 1
-            if len(ends) == 0 or ends[-1] != n:
-                ends = np.concatenate([ends, [n]])
-            starts = np.concatenate([[0], ends[:-1]])
-        for s, e in zip(starts.tolist(), ends.tolist()):
-            if e > s:
-                yield s, e
+        else:
+            ends = np.flatnonzero(np.logical_and(self._tokens[:-1] == self._eos, self._tokens[1:] == self._bos)) + 1
+        start = 0
+        for end in ends.tolist():
+            yield start, end
+            start = end
+        if start != n:
+            yield start, n
 
 
 # ------------------------------------------------------------------------------------------------ composites
@@ -285,17 +293,34 @@ class SlicedTokenSource(_Spliced):
     def source_slice(self) -> slice:
         return self._slice
 
+    @property
+    def slice_start(self) -> int:
+        return self._slice.start
+
+    @property
+    def slice_stop(self) -> int:
+        return self._slice.stop
+
+    @property
+    def slice_step(self) -> int:
+        return 1
+
 
 def _unwind(sources: Sequence[TokenSource]) -> List[TokenSource]:
-    """Replace samples / mixes by the sources they draw from, so that re-sampling keeps THEIR proportions."""
+    """
+    Replace mixes by their per-source samples and samples by the pieces they are made of, breadth first (the order of
+    src/olmo_core/data/composable/sampling_token_source.py:103-120), so that re-sampling keeps THEIR proportions.
+    """
+    from collections import deque
+
     out: List[TokenSource] = []
-    stack = list(reversed(sources))
-    while stack:
-        s = stack.pop()
+    frontier = deque(sources)
+    while frontier:
+        s = frontier.popleft()
         if isinstance(s, (MixingTokenSource, MixingDocumentSource)):
-            stack.extend(reversed(s.sampled_sources))
+            frontier.extend(s.sampled_sources)
         elif type(s) is SamplingTokenSource:
-            stack.extend(reversed(s.original_sources))
+            frontier.extend(s.sources)
         else:
             out.append(s)
     return out
@@ -307,7 +332,7 @@ class SamplingTokenSource(_Spliced):
     repetitions of a source first, then one contiguous window (at a random offset with a seed, at 0 without).
     """
 
-    DISPLAY_ICON = ""
+    DISPLAY_ICON = ""
 
     def __init__(self, *sources: TokenSource, max_tokens: int, seed: Optional[int] = SEED_NOT_SET, work_dir: PathOrStr,
                  label: Optional[str] = None):
@@ -318,17 +343,19 @@ class SamplingTokenSource(_Spliced):
         self._seed = resolve_seed(seed)
         rng = None if self._seed is None else get_rng(self._seed)
         self.original_sources = tuple(sources)
-        leaves = _unwind(sources)
-        total = sum(s.num_tokens for s in leaves)
-        pieces: List[Tuple[int, int, int]] = []
-        for i, s in enumerate(leaves):
-            want = round(max_tokens * s.num_tokens / total)
-            pieces += [(i, 0, s.num_tokens)] * (want // s.num_tokens)
-            rest = want % s.num_tokens
-            if rest:
-                at = 0 if rng is None else int(rng.integers(0, s.num_tokens - rest + 1))
-                pieces.append((i, at, at + rest))
-        super().__init__(leaves, np.array(pieces, dtype=np.int64).reshape(-1, 3), work_dir=work_dir, label=label)
+        total = sum(s.num_tokens for s in sources)
+        final: List[TokenSource] = []
+        for leaf in _unwind(sources):
+            want = round(max_tokens * (leaf.num_tokens / total))
+            final.extend([leaf] * (want // leaf.num_tokens))
+            rest = want % leaf.num_tokens
+            if rest > 0:
+                at = 0 if rng is None else int(rng.integers(0, leaf.num_tokens - rest))
+                final.append(SlicedTokenSource(leaf, slice(at, at + rest), work_dir=work_dir))
+        super().__init__(final, _whole(final), work_dir=work_dir, label=label)
+
+    def children(self):
+        return self.original_sources
 
     @property
     def seed(self) -> Optional[int]:
@@ -337,12 +364,12 @@ class SamplingTokenSource(_Spliced):
 
 class SamplingDocumentSource(_Spliced, DocumentSource):
     """
-    Whole documents drawn from the sources until ``max_tokens`` would be exceeded. With a seed the documents of every
-    pass are visited in a fresh random order; without one, in their natural order. More than one pass (up-sampling)
-    repeats every document before any document is repeated twice.
+    Whole documents drawn from the (concatenated) sources: with a seed the documents are shuffled once; that order is
+    repeated as often as it fits into ``max_tokens`` and followed by the longest prefix of it that fits into the rest
+    (src/olmo_core/data/composable/sampling_document_source.py:87-170). Without a seed the natural order is used.
     """
 
-    DISPLAY_ICON = ""
+    DISPLAY_ICON = ""
 
     def __init__(self, *sources: DocumentSource, max_tokens: int, seed: Optional[int] = SEED_NOT_SET,
                  work_dir: PathOrStr, label: Optional[str] = None):
@@ -351,25 +378,38 @@ class SamplingDocumentSource(_Spliced, DocumentSource):
         if max_tokens <= 0:
             raise ValueError("'max_tokens' must be positive")
         self._seed = resolve_seed(seed)
-        rng = None if self._seed is None else get_rng(self._seed)
+        self._max_tokens = max_tokens
         self.original_sources = tuple(sources)
-        docs = []
-        for i, s in enumerate(sources):
-            offsets = np.array(list(s.get_document_offsets()), dtype=np.int64).reshape(-1, 2)
-            docs.append(np.concatenate([np.full((len(offsets), 1), i, dtype=np.int64), offsets], axis=1))
-        table = np.concatenate(docs, axis=0)  # (child, start, end) of every document
-        lengths = table[:, 2] - table[:, 1]
-        chosen: List[np.ndarray] = []
-        budget = max_tokens
-        while budget > 0 and len(table):
-            order = np.arange(len(table)) if rng is None else rng.permutation(len(table))
-            fits = int(np.searchsorted(np.cumsum(lengths[order]), budget, side="right"))
-            chosen.append(order[:fits])
-            budget -= int(lengths[order[:fits]].sum())
-            if fits < len(order):
-                break  # the next document of this pass does not fit
-        picked = np.concatenate(chosen) if chosen else np.empty(0, dtype=np.int64)
-        super().__init__(sources, table[picked], work_dir=work_dir, label=label)
+        source = ConcatenatedDocumentSource(*sources, work_dir=work_dir) if len(sources) > 1 else sources[0]
+        self._source = source
+        if self._seed is None:
+            import warnings
+
+            warnings.warn("No seed provided for SamplingDocumentSource. It's recommended to set a seed to ensure that the "
+                          "distribution of documents in child sources are preserved.")
+        offsets = np.fromiter((i for pair in source.get_document_offsets() for i in pair), dtype=np.uint64).reshape(-1, 2)
+        if self._seed is not None:
+            get_rng(self._seed).shuffle(offsets, axis=0)
+        cumulative = np.cumsum(offsets[:, 1] - offsets[:, 0], dtype=np.uint64)
+        total = int(cumulative[-1])
+        picked = np.take(offsets, (cumulative <= max_tokens % total).nonzero()[0], axis=0)
+        if max_tokens // total > 0:
+            picked = np.concatenate([np.tile(offsets, (max_tokens // total, 1)), picked])
+        if picked.shape[0] == 0:
+            raise RuntimeError(f"Unable to sample {max_tokens} tokens from {source}")
+        pieces = np.concatenate([np.zeros((len(picked), 1), dtype=np.int64), picked.astype(np.int64)], axis=1)
+        super().__init__([source], pieces, work_dir=work_dir, label=label)
+
+    def children(self):
+        return self.original_sources
+
+    @property
+    def source(self) -> DocumentSource:
+        return self._source
+
+    @property
+    def max_tokens(self) -> int:
+        return self._max_tokens
 
     @property
     def seed(self) -> Optional[int]:

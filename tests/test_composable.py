@@ -203,3 +203,17 @@ def test_numpy_document_source_long_documents_and_file_order(tmp_path):
     assert sorted(s.source_paths[0] for s in a) == sorted(s.source_paths[0] for s in plain)
     with pytest.raises(Exception):
         NumpyDocumentSource.Config(source_paths=pattern, tokenizer=tok, source_group_size=0)
+
+
+def test_sampling_keeps_max_sequence_length_units_together(tmp_path):
+    a = InMemoryTokenSource(list(range(400)), work_dir=tmp_path)
+    wide = ConcatAndChunkInstanceSource(a, sequence_length=5, max_sequence_length=20, work_dir=tmp_path)
+    sample = wide.sample(max_instances=30, seed=2)
+    assert len(sample) == 28 and sample.source_sample_sizes == (28,)
+    firsts = [int(np.asarray(sample[i]["input_ids"])[0]) for i in range(len(sample))]
+    for k in range(0, 28, 4):  # four neighbouring 5-token instances = one 20-token unit
+        assert firsts[k] % 20 == 0 and firsts[k:k + 4] == [firsts[k] + 5 * j for j in range(4)]
+    front, back = wide.split(0.25, seed=3)
+    assert len(front) == 20 and len(back) == 60 and front.seed == 3
+    seen = {int(np.asarray(s[i]["input_ids"])[0]) for s in (front, back) for i in range(len(s))}
+    assert len(seen) == 80  # disjoint and complete

@@ -300,3 +300,80 @@ def test_packed_interleaved_and_variable_length_datasets_match_the_reference(tmp
     assert want.keys() == got.keys()
     for key in want:
         assert got[key] == want[key], key
+
+
+def test_composable_sources_match_the_reference(tmp_path):
+    """Token / document / instance sources of the composable data API: concatenation, splits, sampling (down and up),
+    mixing, chunking, packing and the global index order give the reference's tokens for the same seeds."""
+    body = """
+        import json, os, numpy as np
+        def dump(C, TokenizerConfig, build_global_indices, work, out):
+            os.makedirs(work, exist_ok=True)
+            res = {}
+            ids = lambda src: np.asarray(src[0:src.num_tokens]["input_ids"]).tolist()
+            firsts = lambda src: [np.asarray(src[i]["input_ids"]).tolist()[:2] for i in range(len(src))]
+            a = C.InMemoryTokenSource(list(range(100)), work_dir=work, label="a")
+            b = C.InMemoryTokenSource(list(range(100, 400)), work_dir=work, label="b")
+            res["cat"] = np.asarray((a + b)[95:105]["input_ids"]).tolist()
+            res["split"] = [s.num_tokens for s in (a + b).split(0.4)]
+            res["resize"] = ids(a.resize(2.5, seed=None))
+            res["sample"] = ids(a.sample(max_tokens=10, seed=3))
+            res["sample_b"] = ids(b.sample(max_tokens=50, seed=7))
+            res["resize_seeded"] = ids(a.resize(1.7, seed=5))
+            Spec = C.MixingTokenSource.Spec
+            res["mix"] = ids(C.MixingTokenSource(Spec(source=a, ratio=0.5), Spec(source=b, ratio=0.5), work_dir=work, seed=0))
+            res["mix_repeat"] = ids(C.MixingTokenSource(Spec(source=a, ratio=0.25, max_repetition_factor=3.0),
+                                                        Spec(source=b, ratio=0.75), work_dir=work, seed=2))
+            rng = np.random.default_rng(0)
+            tokens = []
+            for n in rng.integers(2, 9, size=40):
+                tokens += list(map(int, rng.integers(5, 50, size=n - 1))) + [0]
+            tok = TokenizerConfig(vocab_size=64, eos_token_id=0, pad_token_id=63)
+            docs = C.InMemoryDocumentSource(tokens, tokenizer=tok, work_dir=work)
+            res["doc_offsets"] = [list(map(int, o)) for o in docs.get_document_offsets()]
+            res["docs_half"] = ids(docs.sample_by_docs(max_tokens=len(tokens) // 2, seed=1))
+            res["docs_up"] = ids(docs.resize_by_docs(1.5, seed=2))
+            DSpec = C.MixingDocumentSource.Spec
+            res["doc_mix"] = ids(C.MixingDocumentSource(DSpec(source=docs, ratio=0.5), DSpec(source=docs.sample_by_docs(max_tokens=60, seed=4), ratio=0.5),
+                                                        work_dir=work, seed=6))
+            chunks = C.ConcatAndChunkInstanceSource(a + b, sequence_length=16, work_dir=work)
+            res["chunk"] = [len(chunks), np.asarray(chunks[3]["input_ids"]).tolist()]
+            packed = C.PackingInstanceSource(docs, sequence_length=16, work_dir=work, tokenizer=tok)
+            res["pack"] = [np.asarray(packed[i]["input_ids"]).tolist() for i in range(len(packed))]
+            ia = C.ConcatAndChunkInstanceSource(a, sequence_length=10, work_dir=work)
+            ib = C.ConcatAndChunkInstanceSource(b, sequence_length=10, work_dir=work)
+            iab = C.ConcatAndChunkInstanceSource(a + b, sequence_length=10, work_dir=work)
+            ISpec = C.MixingInstanceSource.Spec
+            res["inst_mix"] = firsts(C.MixingInstanceSource(ISpec(source=ia, ratio=0.5), ISpec(source=ib, ratio=0.5), work_dir=work, seed=1))
+            res["inst_sample"] = firsts(iab.sample(max_instances=17, seed=4))
+            res["inst_resize_up"] = firsts(ia.resize(2.5, seed=9))
+            front, back = iab.split(0.3)
+            res["inst_split"] = [firsts(front), firsts(back)]
+            front, back = iab.split(0.3, seed=11)
+            res["inst_split_seeded"] = [firsts(front), firsts(back)]
+            # (sampling a source whose max_sequence_length exceeds its sequence_length is left out: the reference writes
+            # those sample indices as 64-bit integers and reads them back as 32-bit ones, so every other index is 0)
+            rand = C.RandomInstanceSource(tokenizer=tok, sequence_length=16, avg_document_length=6, seed=3, num_instances=6,
+                                          max_sequence_length=32, work_dir=work)
+            res["random"] = [np.asarray(rand[i]["input_ids"]).tolist() for i in range(len(rand))]
+            res["global_indices"] = build_global_indices(40, sequence_length=8, max_sequence_length=32, seed=3).tolist()
+            json.dump(res, open(out, "w"), default=int)
+    """
+    ref_out, our_out = tmp_path / "ref.json", tmp_path / "ours.json"
+    _run_reference(body + f"""
+        import olmo_core.data.composable as C
+        from olmo_core.data import TokenizerConfig
+        from olmo_core.data.composable.utils import build_global_indices
+        dump(C, TokenizerConfig, build_global_indices, {str(tmp_path / 'work_ref')!r}, {str(ref_out)!r})
+    """, tmp_path)
+    namespace = {}
+    exec(textwrap.dedent(body), namespace)  # noqa: S102 - the same fixed source the reference ran
+    import olmo_core_b200.data.composable as C
+    from olmo_core_b200.data import TokenizerConfig
+    from olmo_core_b200.data.composable.utils import build_global_indices
+
+    namespace["dump"](C, TokenizerConfig, build_global_indices, str(tmp_path / "work_ours"), str(our_out))
+    want, got = json.loads(ref_out.read_text()), json.loads(our_out.read_text())
+    assert want.keys() == got.keys()
+    for key in want:
+        assert got[key] == want[key], key
