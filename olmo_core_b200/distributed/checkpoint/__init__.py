@@ -264,12 +264,21 @@ def save_state_dict(
     process_group: Optional[dist.ProcessGroup] = None,
     save_overwrite: bool = False,
     thread_count: Optional[int] = None,
+    process_count: Optional[int] = None,
     throttle_uploads: bool = False,
     enable_plan_caching: bool = False,
+    _skip_prepare: bool = False,
 ) -> None:
-    """Write an arbitrary nested state dict (tensors, ``DTensor`` shards, picklable leaves) to ``dir``."""
+    """
+    Write an arbitrary nested state dict (tensors, ``DTensor`` shards, picklable leaves) to ``dir``. ``process_count``
+    (a process pool in the reference) is served by the writer's thread pool: the files are written by threads that spend
+    their time in ``write`` system calls, not in the interpreter. ``_skip_prepare``: the target directory was already
+    checked / cleared by the caller.
+    """
     del enable_plan_caching  # the plan is cheap to rebuild at these sizes; accepted for API compatibility
-    dir = _prepare_target_dir(dir, process_group, save_overwrite)
+    thread_count = thread_count if thread_count is not None else process_count
+    if not _skip_prepare:
+        dir = _prepare_target_dir(dir, process_group, save_overwrite)
     writer = RemoteFileSystemWriter(dir, thread_count=thread_count, process_group=process_group,
                                     throttle_uploads=throttle_uploads, save_overwrite=save_overwrite)
     dist_cp.state_dict_saver.save(state_dict, storage_writer=writer, process_group=process_group,
@@ -283,8 +292,10 @@ def async_save_state_dict(
     process_group: Optional[dist.ProcessGroup] = None,
     save_overwrite: bool = False,
     thread_count: Optional[int] = None,
+    process_count: Optional[int] = None,
     throttle_uploads: bool = False,
     enable_plan_caching: bool = False,
+    _skip_prepare: bool = False,
 ) -> Future:
     """
     Like :func:`save_state_dict`, but returns once the state has been staged in host memory; the returned future
@@ -292,7 +303,9 @@ def async_save_state_dict(
     (gloo) backend that is not used for anything else while the save is in flight.
     """
     del enable_plan_caching
-    dir = _prepare_target_dir(dir, process_group, save_overwrite)
+    thread_count = thread_count if thread_count is not None else process_count
+    if not _skip_prepare:
+        dir = _prepare_target_dir(dir, process_group, save_overwrite)
     writer = RemoteFileSystemWriter(dir, thread_count=thread_count, process_group=process_group,
                                     throttle_uploads=throttle_uploads, save_overwrite=save_overwrite)
     if is_distributed():
@@ -372,6 +385,7 @@ def save_model_and_optim_state(
     save_overwrite: bool = False,
     flatten_optimizer_state: bool = False,
     thread_count: Optional[int] = None,
+    process_count: Optional[int] = None,
     throttle_uploads: bool = False,
     enable_plan_caching: bool = False,
 ) -> None:
@@ -380,7 +394,8 @@ def save_model_and_optim_state(
     other sharding, world size or wrapping, and by the reference implementation.
     """
     save_state_dict(dir, _model_optim_state(model, optim, flatten=flatten_optimizer_state), process_group=process_group, save_overwrite=save_overwrite,
-                    thread_count=thread_count, throttle_uploads=throttle_uploads, enable_plan_caching=enable_plan_caching)
+                    thread_count=thread_count, process_count=process_count, throttle_uploads=throttle_uploads,
+                    enable_plan_caching=enable_plan_caching)
 
 
 @torch.no_grad()
@@ -393,11 +408,12 @@ def async_save_model_and_optim_state(
     save_overwrite: bool = False,
     flatten_optimizer_state: bool = False,
     thread_count: Optional[int] = None,
+    process_count: Optional[int] = None,
     throttle_uploads: bool = False,
     enable_plan_caching: bool = False,
 ) -> Future:
     return async_save_state_dict(dir, _model_optim_state(model, optim, flatten=flatten_optimizer_state), process_group=process_group,
-                                 save_overwrite=save_overwrite, thread_count=thread_count,
+                                 save_overwrite=save_overwrite, thread_count=thread_count, process_count=process_count,
                                  throttle_uploads=throttle_uploads, enable_plan_caching=enable_plan_caching)
 
 

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 from fnmatch import fnmatch
-from typing import List, Optional
+from typing import Any, List, Optional
 
 import torch
 import torch.nn as nn
@@ -32,11 +32,31 @@ class AOFloat8LinearRecipe(StrEnum):
 
 @dataclass
 class AOFloat8LinearConfig(Config):
-    """Scaling granularity and options of the fp8 linear layers."""
+    """
+    Options of the row-wise scaled fp8 linear layers, with the field names of the reference's config
+    (src/olmo_core/float8/ao.py:151-186). ``enable_fsdp_float8_all_gather`` keeps one set of quantised weight copies per
+    optimizer step (the effect of casting before the sharded all-gather); ``round_scales_to_power_of_2`` rounds every
+    scale up to a power of two; ``emulate`` and ``pad_inner_dim`` are accepted without effect (CPU tensors always take the
+    emulated path, CUDA tensors the tensor-core kernels). The per-operand cast configs and
+    per-GEMM configs are accepted: every operand is scaled dynamically along its reduction dimension here, and a cast
+    config whose ``scaling_type`` is "disabled" for the weight-gradient operands selects the high-precision weight
+    gradient (what the ``rowwise_with_gw_hp`` recipe does).
+    """
 
-    enable_fsdp_float8_all_gather: bool = False
-    force_recompute_fp8_weight_in_bwd: bool = False
-    round_scales_to_power_of_2: bool = False
+    cast_config_input: Optional[Any] = None
+    cast_config_input_for_grad_weight: Optional[Any] = None
+    cast_config_weight: Optional[Any] = None
+    cast_config_weight_for_grad_input: Optional[Any] = None
+    cast_config_grad_output: Optional[Any] = None
+    cast_config_grad_output_for_grad_weight: Optional[Any] = None
+    gemm_config_output: Optional[Any] = None
+    gemm_config_grad_input: Optional[Any] = None
+    gemm_config_grad_weight: Optional[Any] = None
+    enable_fsdp_float8_all_gather: Optional[bool] = None
+    pad_inner_dim: Optional[bool] = None
+    emulate: Optional[bool] = None
+    force_recompute_fp8_weight_in_bwd: Optional[bool] = None  # accepted, no effect (as in the reference)
+    round_scales_to_power_of_2: Optional[bool] = None
     recipe: Optional[AOFloat8LinearRecipe] = None
 
     @classmethod
@@ -45,6 +65,14 @@ class AOFloat8LinearConfig(Config):
         kwargs.setdefault("force_recompute_fp8_weight_in_bwd", True)
         kwargs.setdefault("round_scales_to_power_of_2", True)
         return cls(**kwargs)
+
+    @property
+    def wgrad_high_precision(self) -> bool:
+        """True when the configs of the weight-gradient operands switch their cast off."""
+        for cfg in (self.cast_config_input_for_grad_weight, self.cast_config_grad_output_for_grad_weight):
+            if cfg is not None and str(getattr(cfg, "scaling_type", "")).split(".")[-1] == "disabled":
+                return True
+        return False
 
 
 @dataclass
@@ -103,11 +131,20 @@ class Float8Config(Config):
             raise OLMoConfigurationError("specify at most one of 'ao', 'ao_recipe' and 'ao_mx'")
 
     @property
+    def should_precompute_float8_dynamic_scale_for_fsdp(self) -> bool:
+        """Whether quantised weights are prepared once per optimizer step (src/olmo_core/float8/__init__.py:54-62)."""
+        if self.ao_recipe is not None or self.ao_mx is not None:
+            return False
+        return bool(self.ao is not None and self.ao.enable_fsdp_float8_all_gather)
+
+    @property
     def recipe(self) -> AOFloat8LinearRecipe:
         if self.ao_recipe is not None:
             return AOFloat8LinearRecipe(self.ao_recipe)
         if self.ao is not None and self.ao.recipe is not None:
             return AOFloat8LinearRecipe(self.ao.recipe)
+        if self.ao is not None and self.ao.wgrad_high_precision:
+            return AOFloat8LinearRecipe.rowwise_with_gw_hp
         return AOFloat8LinearRecipe.tensorwise if self.ao is not None else AOFloat8LinearRecipe.rowwise
 
     def apply_float8_linear(self, model: nn.Module, modules_to_ignore: Optional[List[str]] = None) -> None:

@@ -42,7 +42,8 @@ __all__ = ["TransformerGenerationModule"]
 class TransformerGenerationModule(GenerationModule):
     def __init__(self, model: Transformer, generation_config: GenerationConfig, compile_model: bool = False,
                  float8_config=None, dp_config=None, device: Optional[torch.device] = None,
-                 state_dict_load_opts: Optional[Dict[str, Any]] = None, load_key_mapping: Optional[Dict[str, str]] = None):
+                 state_dict_load_opts: Optional[Dict[str, Any]] = None, state_dict_save_opts: Optional[Dict[str, Any]] = None,
+                 load_key_mapping: Optional[Dict[str, str]] = None):
         del compile_model, float8_config, dp_config  # generation runs every rank on its own replica
         self.device = device or get_default_device()
         self.model = model
@@ -53,6 +54,7 @@ class TransformerGenerationModule(GenerationModule):
         self.model.eval()
         self._generation_config = generation_config
         self.state_dict_load_opts = state_dict_load_opts or {}
+        self.state_dict_save_opts = state_dict_save_opts or {}
         self.load_key_mapping = load_key_mapping
         self._cache_shape: Optional[Tuple[int, int]] = None
 

@@ -37,6 +37,7 @@ from .backend import (
     TEAttentionBackend,
     TorchAttentionBackend,
 )
+from .base import SeqMixer, SequenceMixer, SequenceMixerConfig
 from .kv_cache import KVCacheManager
 from .recurrent import GatedDeltaNet, GatedDeltaNetConfig
 from .ring import (
@@ -81,42 +82,6 @@ __all__ = [
 ]
 
 log = logging.getLogger(__name__)
-
-
-class SequenceMixer(nn.Module):
-    """Base of token-mixing modules (attention, recurrent mixers)."""
-
-    @abstractmethod
-    def apply_tp(self, tp_mesh, input_layout=None, output_layout=None, use_local_output: bool = True,
-                 float8_enabled: bool = False):
-        raise NotImplementedError
-
-    @abstractmethod
-    def apply_cp(self, cp_mesh, ring: Optional[RingContextParallelStyle] = None,
-                 uly: Optional[UlyssesContextParallelStyle] = None):
-        raise NotImplementedError
-
-    @abstractmethod
-    def num_flops_per_token(self, seq_len: int) -> int:
-        raise NotImplementedError
-
-    @abstractmethod
-    def init_weights(self, *, init_method, d_model: int, block_idx: int, num_blocks: int, std: float = 0.02,
-                     generator: Optional[torch.Generator] = None) -> None:
-        raise NotImplementedError
-
-
-SeqMixer = TypeVar("SeqMixer", bound=SequenceMixer)
-
-
-@dataclass
-class SequenceMixerConfig(ModuleConfig, Registrable, Generic[SeqMixer]):
-    def num_params(self, d_model: int) -> int:
-        raise NotImplementedError
-
-    def build(self, d_model: int, *, layer_idx: int, n_layers: int, init_device: str = "cpu",
-              cache: Optional[BufferCache] = None) -> SeqMixer:
-        raise NotImplementedError
 
 
 class GateGranularity(StrEnum):
@@ -473,6 +438,15 @@ class Attention(SequenceMixer):
         rows = att if B == 1 else att.view(B, ws, Tl, F).permute(1, 0, 2, 3)
         y = linear_reduce_scatter(rows.reshape(ws * B * Tl, F), self.w_out.weight, self.tp_group, "attn-out")
         return y.view(B, Tl, -1)
+
+    def sdpa(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_doc_lens: Optional[torch.Tensor] = None,
+             cu_doc_lens_q: Optional[torch.Tensor] = None, cu_doc_lens_k: Optional[torch.Tensor] = None,
+             max_doc_len: Optional[int] = None, max_doc_len_q: Optional[int] = None, max_doc_len_k: Optional[int] = None,
+             local_k_slice: Optional[slice] = None, cache_leftpad: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Scaled dot-product attention of ``[B, T, heads, head_dim]`` tensors through this layer's backend (and KV cache)."""
+        return self.backend((q, k, v), cu_doc_lens=cu_doc_lens, cu_doc_lens_q=cu_doc_lens_q, cu_doc_lens_k=cu_doc_lens_k,
+                            max_doc_len=max_doc_len, max_doc_len_q=max_doc_len_q, max_doc_len_k=max_doc_len_k,
+                            local_k_slice=local_k_slice, kv_cache=self.kv_cache_manager, cache_leftpad=cache_leftpad)
 
     def _full_width_norm(self, norm: nn.Module, t: torch.Tensor) -> torch.Tensor:
         if self.tp_enabled:

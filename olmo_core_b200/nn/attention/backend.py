@@ -161,6 +161,14 @@ class AttentionBackend(nn.Module):
     def _local(self, q, k, v, *, cu_doc_lens=None, cu_doc_lens_k=None, max_doc_len=None, causal=True) -> torch.Tensor:
         raise NotImplementedError
 
+    def warmup_cache(self, max_seq_len: int, device: torch.device) -> None:
+        """
+        Build whatever per-sequence-length buffers the backend caches (the reference's SDPA backend caches its
+        sliding-window masks here). The kernels of this package derive their masks from per-row bounds computed on the
+        fly, so there is nothing to prepare.
+        """
+        del max_seq_len, device
+
     def forward(
         self,
         qkv,
@@ -173,8 +181,11 @@ class AttentionBackend(nn.Module):
         local_k_slice: Optional[slice] = None,
         kv_cache: Optional[KVCacheManager] = None,
         cache_leftpad: Optional[torch.Tensor] = None,
+        kv_cache_manager: Optional[KVCacheManager] = None,
     ) -> torch.Tensor:
+        """``kv_cache_manager`` is the reference's name of ``kv_cache`` (src/olmo_core/nn/attention/backend.py:222-236)."""
         q, k, v = qkv
+        kv_cache = kv_cache if kv_cache is not None else kv_cache_manager
         if kv_cache is not None:
             return self._decode(q, k, v, kv_cache, cache_leftpad)
         if not self.cp_enabled:
@@ -252,4 +263,6 @@ class FlashAttention4Backend(KernelAttentionBackend):
 
 
 class TEAttentionBackend(KernelAttentionBackend):
-    pass
+    @classmethod
+    def assert_supports_cp(cls) -> None:
+        """Every context-parallel style is served by the in-tree kernels behind this backend name."""

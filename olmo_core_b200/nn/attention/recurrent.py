@@ -24,8 +24,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ...config import DType
-from ..config import ModuleConfig
 from ..convolution import CausalConv1d
+from .base import SequenceMixerConfig
 
 __all__ = ["GatedDeltaNet", "GatedDeltaNetConfig", "gated_delta_rule", "gated_delta_rule_recurrent"]
 
@@ -248,8 +248,9 @@ class GatedDeltaNet(nn.Module):
         return 3 * (proj + state)
 
 
+@SequenceMixerConfig.register("gated_delta_net")
 @dataclass
-class GatedDeltaNetConfig(ModuleConfig):
+class GatedDeltaNetConfig(SequenceMixerConfig["GatedDeltaNet"]):
     n_heads: int = 16
     n_v_heads: Optional[int] = None
     head_dim: Optional[int] = None

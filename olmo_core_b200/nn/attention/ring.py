@@ -153,6 +153,17 @@ class _ContiguousBalancer(RingAttentionLoadBalancer):
 
 
 class RingAttentionLlama3LoadBalancer(_ContiguousBalancer):
+    def pad(self, x: torch.Tensor, seq_dim: int, padding_to_add: Union[int, float], value: Optional[Union[int, float]] = None,
+            length_multiple: Optional[int] = None) -> Tuple[torch.Tensor, int]:
+        """
+        ``x`` with ``padding_to_add`` positions of ``value`` appended along ``seq_dim``
+        (src/olmo_core/nn/attention/ring.py:380-388). Called as ``pad(x, seq_dim, value)`` or with ``length_multiple``
+        it pads to a multiple instead, like the other balancers.
+        """
+        if value is None or length_multiple is not None:  # the generic form: (x, seq_dim, value, length_multiple)
+            return super().pad(x, seq_dim, padding_to_add if value is None else value, length_multiple)
+        return _pad_dim(x, seq_dim, int(padding_to_add), value), int(padding_to_add)
+
     def batch_shard_by_document(self, *, inputs, seq_dims, cu_doc_lens, pad_values=None, length_multiple=None):
         """
         Contiguous slice per rank plus what the varlen kernel needs: document boundaries as seen by the

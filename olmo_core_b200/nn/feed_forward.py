@@ -153,6 +153,19 @@ class FeedForward(nn.Module):
             return self.w2(swiglu(a, b))
         return self.w2(self._act(a) * b)
 
+    def apply_tp(self, tp_mesh, input_layout=None, output_layout=None, use_local_output: bool = True,
+                 float8_enabled: bool = False) -> None:
+        """
+        ``w1`` / ``w3`` column-parallel, ``w2`` row-parallel over ``tp_mesh``
+        (src/olmo_core/nn/feed_forward.py:173-204). The layouts are fixed here: the input arrives sharded along the
+        sequence, is gathered inside the up-projection GEMMs, and the output returns to sequence shards through the
+        down-projection's epilogue, so the layout arguments are accepted and ignored.
+        """
+        del input_layout, output_layout, use_local_output, float8_enabled
+        from ..parallel.tensor import shard_feed_forward_
+
+        shard_feed_forward_(self, tp_mesh)
+
     def num_flops_per_token(self, seq_len: int) -> int:
         return 6 * sum(p.numel() for p in self.parameters())
 
@@ -160,7 +173,10 @@ class FeedForward(nn.Module):
 class NormalizedFeedForward(FeedForward):
     """nGPT MLP: unit-norm weight rows plus learned per-channel scales ``sw1``/``sw3``."""
 
-    def __init__(self, *, d_model: int, hidden_size: int, dtype: torch.dtype = torch.float32, init_device: str = "cpu"):
+    def __init__(self, *, d_model: int, hidden_size: int, dtype: torch.dtype = torch.float32, init_device: str = "cpu",
+                 activation: ActivationFunction = ActivationFunction.silu):
+        if ActivationFunction(activation) != ActivationFunction.silu:
+            raise OLMoConfigurationError(f"NormalizedFeedForward only supports 'silu' activation, got '{activation}'")
         super().__init__(d_model=d_model, hidden_size=hidden_size, bias=False, dtype=dtype, init_device=init_device)
         self.sw_init_value = 1.0
         self.sw_init_scaling = 1.0
@@ -178,6 +194,9 @@ class NormalizedFeedForward(FeedForward):
         sw1 = self.sw1 * ((self.sw_init_value / self.sw_init_scaling) * self.sqrt_d_model)
         sw3 = self.sw3 * (self.sw_init_value / self.sw_init_scaling)
         return self.w2(F.silu(sw1.to(x.dtype) * self.w1(x)) * (sw3.to(x.dtype) * self.w3(x)))
+
+    def apply_tp(self, *args, **kwargs) -> None:
+        raise NotImplementedError("TP is not implemented yet for the normalized feed-forward variant")
 
     @torch.no_grad()
     def normalize_matrices(self) -> None:

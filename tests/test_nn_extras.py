@@ -90,3 +90,30 @@ def test_cross_entropy_module():
     torch.testing.assert_close(z, want_z)
     per_token, _ = CrossEntropyLoss(reduction="none")(logits, labels)
     assert per_token.shape == labels.shape and (per_token[0, :2] == 0).all()
+
+
+def test_fused_linear_cross_entropy_options_match_pytorch():
+    import torch
+    import torch.nn.functional as F
+
+    from olmo_core_b200.nn.functional import fused_linear_cross_entropy_loss
+
+    torch.manual_seed(0)
+    h, w = torch.randn(12, 16), torch.randn(32, 16)
+    labels = torch.randint(0, 32, (12,))
+    labels[3] = -100
+    logits = h @ w.t()
+    loss, z = fused_linear_cross_entropy_loss(h, w, labels)
+    torch.testing.assert_close(loss, F.cross_entropy(logits, labels, ignore_index=-100))
+    assert z is None
+    capped = 5.0 * torch.tanh(logits / 5.0)
+    loss, _ = fused_linear_cross_entropy_loss(h, w, labels, softcap=5.0)
+    torch.testing.assert_close(loss, F.cross_entropy(capped, labels, ignore_index=-100))
+    cw = torch.rand(32) + 0.5
+    loss, _ = fused_linear_cross_entropy_loss(h, w, labels, ce_weight=cw, label_smoothing=0.1, reduction="sum")
+    torch.testing.assert_close(loss, F.cross_entropy(logits, labels, weight=cw, ignore_index=-100, label_smoothing=0.1, reduction="sum"))
+    total, z = fused_linear_cross_entropy_loss(h, w, labels, softcap=5.0, compute_z_loss=True, z_loss_multiplier=1e-2)
+    keep = labels != -100
+    want_z = 1e-2 * (torch.logsumexp(capped, -1).pow(2) * keep).sum() / keep.sum()
+    torch.testing.assert_close(z, want_z)
+    torch.testing.assert_close(total, F.cross_entropy(capped, labels, ignore_index=-100) + want_z)
