@@ -21,12 +21,15 @@ log = logging.getLogger(__name__)
 __all__ = ["save_hf_model", "load_hf_model"]
 
 
-def save_hf_model(save_dir: PathOrStr, model_state_dict: Dict[str, Any], model, *, dtype: Optional[torch.dtype] = None,
-                  vocab_size: Optional[int] = None, process_group: Optional[dist.ProcessGroup] = None,
-                  work_dir: Optional[PathOrStr] = None, save_overwrite: bool = False) -> None:
+def save_hf_model(save_dir: PathOrStr, model_state_dict: Dict[str, Any], model, huggingface_tokenizer=None, *,
+                  dtype: Optional[torch.dtype] = None, vocab_size: Optional[int] = None,
+                  process_group: Optional[dist.ProcessGroup] = None, work_dir: Optional[PathOrStr] = None,
+                  save_overwrite: bool = False) -> None:
     """
     Write ``model`` (weights from ``model_state_dict``, possibly sharded) as a Hugging Face ``save_pretrained`` folder.
-    All ranks must call it (sharded tensors are gathered); rank 0 writes.
+    All ranks must call it (sharded tensors are gathered); rank 0 writes. With a ``huggingface_tokenizer`` the generation
+    config gets its end-of-text ids (``<|im_end|>``, ``<|endoftext|>``) and pad id from it, as the reference does
+    (src/olmo_core/nn/hf/checkpoint.py:184-188).
     """
     from transformers import AutoModelForCausalLM
 
@@ -48,6 +51,12 @@ def save_hf_model(save_dir: PathOrStr, model_state_dict: Dict[str, Any], model, 
 
             hf_state = fuse_expert_weights(hf_state, hf_config.num_hidden_layers, int(getattr(hf_config, "num_experts", 0) or 0))
         hf_model.load_state_dict(hf_state, assign=True)
+        if getattr(hf_model, "generation_config", None) is not None:
+            hf_model.generation_config.do_sample = True
+            if huggingface_tokenizer is not None:
+                hf_model.generation_config.eos_token_id = huggingface_tokenizer.convert_tokens_to_ids(
+                    ["<|im_end|>", "<|endoftext|>"])
+                hf_model.generation_config.pad_token = huggingface_tokenizer.pad_token_id
         target = Path(tempfile.mkdtemp(dir=work_dir)) if is_url(save_dir) else Path(save_dir)
         if target.exists() and any(target.iterdir()) and not save_overwrite:
             raise FileExistsError(f"'{target}' is not empty, use save_overwrite=True to overwrite it")

@@ -180,9 +180,10 @@ def split_expert_weights(hf_state: Dict[str, Any], n_layers: int) -> Dict[str, A
     return out
 
 
-def convert_state_to_hf(hf_config, state: Dict[str, Any], fused_experts: bool = False) -> Dict[str, Any]:
-    """State dict of this framework's transformer -> state dict of the HF causal LM described by ``hf_config``
+def convert_state_to_hf(config, olmo_core_state: Dict[str, Any], fused_experts: bool = False) -> Dict[str, Any]:
+    """State dict of this framework's transformer -> state dict of the HF causal LM described by the HF ``config``
     (``fused_experts``: stacked expert parameters as ``transformers`` >= 5 models expect them in memory)."""
+    hf_config, state = config, olmo_core_state
     if getattr(hf_config, "model_type", None) in _UNIT_OFFSET_NORM_MODEL_TYPES:
         state = _shift_norm_weights(state, -1.0)
     converted = _converter_for(hf_config).to_hf(state)
@@ -197,7 +198,9 @@ def convert_state_to_hf(hf_config, state: Dict[str, Any], fused_experts: bool = 
     return converted
 
 
-def convert_state_from_hf(hf_config, hf_state: Dict[str, Any], model_type: Optional[str] = None) -> Dict[str, Any]:
+def convert_state_from_hf(config, hf_state: Dict[str, Any], model_type: Optional[str] = None) -> Dict[str, Any]:
+    """State dict of the HF causal LM described by the HF ``config`` -> state dict of this framework's transformer."""
+    hf_config = config
     hf_state = split_expert_weights(hf_state, hf_config.num_hidden_layers)
     converted = _converter_for(hf_config).from_hf(hf_state)
     if getattr(hf_config, "model_type", None) in _UNIT_OFFSET_NORM_MODEL_TYPES:

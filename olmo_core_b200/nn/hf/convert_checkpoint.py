@@ -37,6 +37,7 @@ def convert_checkpoint_to_hf(original_checkpoint_path: PathOrStr, output_path: P
                              dtype: Optional[DType] = None, tokenizer_id: Optional[str] = None,
                              max_sequence_length: Optional[int] = None, validate: bool = True, debug: bool = False,
                              device: Optional[torch.device] = None, moe_capacity_factor: Optional[float] = None,
+                             validation_device: Optional[torch.device] = None,
                              validation_sliding_window: Optional[int] = None) -> None:
     """
     Build the model from its config, load weights (from ``model_state_dict`` or from the sharded checkpoint), write the
@@ -75,14 +76,16 @@ def convert_checkpoint_to_hf(original_checkpoint_path: PathOrStr, output_path: P
         except Exception as e:  # no network / unknown tokenizer: the weights are still exported
             log.warning(f"Could not export tokenizer '{identifier}': {e}")
     if validate:
-        validate_conversion(output_path, model, vocab_size or model.vocab_size, device=device, dtype=torch_dtype)
+        validate_conversion(output_path, model, vocab_size or model.vocab_size, device=validation_device or device, dtype=torch_dtype)
 
 
 @torch.no_grad()
-def validate_conversion(hf_path: PathOrStr, model, vocab_size: int, *, device: Optional[torch.device] = None,
-                        dtype: Optional[torch.dtype] = None, rtol: float = 1e-3, atol: float = 1e-3, **kwargs) -> None:
-    """Feed the same random token ids through both models and compare the logits over the real vocabulary."""
-    del kwargs
+def validate_conversion(hf_path: PathOrStr, model, vocab_size: int, debug: bool = False,
+                        dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None,
+                        sliding_window: Optional[int] = None, *, rtol: float = 1e-3, atol: float = 1e-3, **kwargs) -> None:
+    """Feed the same random token ids through both models and compare the logits over the real vocabulary
+    (``debug`` and ``sliding_window`` are accepted for call compatibility)."""
+    del kwargs, debug, sliding_window
     from transformers import AutoModelForCausalLM
 
     device = device or torch.device("cpu")

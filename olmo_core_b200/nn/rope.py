@@ -339,7 +339,23 @@ class RotaryEmbedding(RotaryEmbeddingBase):
 
 
 class FusedRotaryEmbedding(RotaryEmbedding):
-    """Accepted for config compatibility; the GPU path is always the fused kernel."""
+    """
+    The rotary embedding under its "fused" name. Called with one packed ``qkv`` tensor
+    ``[batch, seq, 3, heads, head_size]`` it rotates the query and key planes and returns the packed tensor
+    (the calling convention of src/olmo_core/nn/rope.py:668-705); called with ``(q, k, ...)`` it behaves like
+    :class:`RotaryEmbedding`. On CUDA both forms run the package's rotary kernel.
+    """
+
+    def forward(self, q: torch.Tensor, k: Optional[torch.Tensor] = None, *args, **kwargs):  # type: ignore[override]
+        if k is not None:
+            return super().forward(q, k, *args, **kwargs)
+        qkv = q
+        if qkv.dim() != 5 or qkv.shape[2] != 3:
+            raise ValueError("expected a packed qkv tensor of shape (batch, seq, 3, heads, head_size)")
+        if kwargs.get("freqs_cis") is not None:
+            raise RuntimeError(f"'freqs_cis' is invalid for {type(self).__name__}")
+        q_rot, k_rot = super().forward(qkv[:, :, 0], qkv[:, :, 1], head_first=False, *args, **kwargs)
+        return torch.stack([q_rot.to(qkv.dtype), k_rot.to(qkv.dtype), qkv[:, :, 2]], dim=2)
 
 
 class ComplexRotaryEmbedding(RotaryEmbeddingBase):

@@ -137,3 +137,39 @@ class MatrixAwareOptimConfig(OptimConfig[Opt], metaclass=ABCMeta):
             else:
                 cats["matrix"].append(n)
         return cats
+
+    def categorize_parameters(self, model: nn.Module) -> Dict[str, List[str]]:
+        """
+        Parameter names by role: ``embed``, ``matrix`` (two-dimensional block parameters), ``vector`` (norm gains,
+        biases, scales) and ``lm_head`` (src/olmo_core/optim/config.py:240-277).
+        """
+        return self.categorize(model)
+
+    def default_group_overrides(self, model: nn.Module) -> List["OptimGroupOverride"]:
+        """
+        The split the matrix-aware optimizers use: matrices go to the matrix algorithm, everything else to AdamW
+        (embeddings without weight decay).
+        """
+        cats = self.categorize_parameters(model)
+        return [OptimGroupOverride(params=cats["matrix"], opts={}),
+                OptimGroupOverride(params=cats["vector"], opts=dict(algorithm="adamw")),
+                OptimGroupOverride(params=cats["embed"], opts=dict(algorithm="adamw", weight_decay=0.0)),
+                OptimGroupOverride(params=cats["lm_head"], opts=dict(algorithm="adamw"))]
+
+    def build_parallelism_config(self) -> Dict[str, Any]:
+        """
+        What the optimizer needs to know about the sharding of its parameters. The matrix-aware optimizers here gather
+        a sharded matrix over the data-parallel group themselves (its group comes with the parameter's shard
+        information), so there is no mesh to hand over; tensor parallelism is not supported by them.
+        """
+        from ..distributed.parallel import MeshDimName, get_world_mesh
+
+        mesh = get_world_mesh()
+        if mesh is not None and mesh.mesh_dim_names is not None and MeshDimName.tp in mesh.mesh_dim_names:
+            raise NotImplementedError(f"Tensor parallelism is not supported for {type(self).__name__}")
+        return {}
+
+    def create_optimizer(self, model: nn.Module, strict: bool = True, **kwargs) -> Opt:
+        """Build the optimizer (same as :meth:`build`; extra keyword arguments override config fields)."""
+        self.build_parallelism_config()
+        return self.replace(**kwargs).build(model, strict=strict) if kwargs else self.build(model, strict=strict)

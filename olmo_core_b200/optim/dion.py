@@ -19,9 +19,10 @@ __all__ = ["Dion", "DionConfig"]
 
 class Dion(Optimizer):
     def __init__(self, params, lr: float = 0.01, mu: float = 0.95, betas: Tuple[float, float] = (0.9, 0.95),
-                 weight_decay: float = 0.01, eps: float = 1e-8, rank_fraction: float = 0.25, **unused):
+                 weight_decay: float = 0.01, eps: float = 1e-8, rank_fraction: float = 0.25, rank_multiple_of: int = 1,
+                 **unused):
         super().__init__(params, dict(lr=lr, mu=mu, betas=betas, weight_decay=weight_decay, eps=eps,
-                                      rank_fraction=rank_fraction, algorithm="dion"))
+                                      rank_fraction=rank_fraction, rank_multiple_of=rank_multiple_of, algorithm="dion"))
 
     @torch.no_grad()
     def step(self, closure=None) -> None:
@@ -36,6 +37,8 @@ class Dion(Optimizer):
                 if group.get("algorithm", "dion") == "dion" and p.ndim == 2:
                     m, n = p.shape
                     r = max(1, int(min(m, n) * group["rank_fraction"]))
+                    mult = max(1, int(group.get("rank_multiple_of", 1)))
+                    r = min(min(m, n), -(-r // mult) * mult)  # rounded up to the multiple, never above full rank
                     if not state:
                         state["momentum"] = torch.zeros_like(p)
                         state["Q"] = torch.linalg.qr(torch.randn(n, r, device=p.device, dtype=torch.float32))[0].to(p.dtype)
@@ -65,6 +68,8 @@ class Dion(Optimizer):
 class DionConfig(MuonConfig):
     lr: float = 0.01
     rank_fraction: float = 0.25
+    rank_multiple_of: int = 1
+    """Round the low-rank dimension up to a multiple of this number (useful for even sharding)."""
 
     @classmethod
     def optimizer(cls) -> Type[Dion]:
@@ -76,7 +81,7 @@ class DionConfig(MuonConfig):
             if g.get("algorithm") == "muon":
                 g["algorithm"] = "dion"
         optim = Dion(groups, lr=self.lr, mu=self.mu, betas=self.betas, weight_decay=self.weight_decay, eps=self.eps,
-                     rank_fraction=self.rank_fraction)
+                     rank_fraction=self.rank_fraction, rank_multiple_of=self.rank_multiple_of)
         for g in optim.param_groups:
             g.setdefault("initial_lr", g["lr"])
         return optim

@@ -78,8 +78,8 @@ class GAPMonitorCallback(Callback):
         for name, module in self._model().named_modules():
             if name == "":
                 continue
-            self._handles.append(module.register_forward_hook(functools.partial(self._forward_hook, module_name=name)))
-            self._handles.append(module.register_full_backward_pre_hook(functools.partial(self._backward_hook, module_name=name)))
+            self._handles.append(module.register_forward_hook(functools.partial(self.forward_hook, module_name=name)))
+            self._handles.append(module.register_full_backward_pre_hook(functools.partial(self.backward_hook, module_name=name)))
 
     def pre_step(self, batch: Dict[str, Any]) -> None:
         if self.enabled and self.monitor:
@@ -103,14 +103,14 @@ class GAPMonitorCallback(Callback):
         if self.dump_gradients:
             self._dump_gradients()
 
-    def _forward_hook(self, module: nn.Module, args, output, module_name: str) -> None:
+    def forward_hook(self, module: nn.Module, args, output, module_name: str) -> None:
         del module, args
         if isinstance(output, tuple):
             output = output[0]
         if isinstance(output, torch.Tensor):
             self.record_tensor_stats(module_name, output, "activation")
 
-    def _backward_hook(self, module: nn.Module, grad_output, module_name: str) -> None:
+    def backward_hook(self, module: nn.Module, grad_output, module_name: str) -> None:
         del module
         if isinstance(grad_output, tuple):
             grad_output = grad_output[0]
