@@ -64,9 +64,10 @@ class Embedding(nn.Module):
         return f"{self.num_embeddings}, {self.embedding_dim}"
 
 
-def _checkpoint_module(module: nn.Module) -> None:
+def _checkpoint_module(module: nn.Module, determinism_check: str = "default") -> None:
     """Recompute ``module``'s forward in the backward pass (while training with gradients on) instead of saving its
-    intermediate activations. Idempotent."""
+    intermediate activations. Idempotent. ``determinism_check``: "default" compares the metadata of recomputed tensors
+    with the forward pass', "none" skips that check."""
     if getattr(module, "_checkpointed_forward", None) is not None:
         return
     inner = module.forward
@@ -75,7 +76,7 @@ def _checkpoint_module(module: nn.Module) -> None:
         if module.training and torch.is_grad_enabled():
             from torch.utils.checkpoint import checkpoint
 
-            return checkpoint(inner, *args, use_reentrant=False, **kwargs)
+            return checkpoint(inner, *args, use_reentrant=False, determinism_check=determinism_check, **kwargs)
         return inner(*args, **kwargs)
 
     module._checkpointed_forward = inner  # type: ignore[assignment]
@@ -416,7 +417,10 @@ class Transformer(nn.Module):
         if getattr(block, "_activation_checkpointing", False) and self.training and torch.is_grad_enabled():
             from torch.utils.checkpoint import checkpoint
 
-            return checkpoint(block, h, use_reentrant=False, **kwargs)
+            return checkpoint(
+                block, h, use_reentrant=False,
+                determinism_check=getattr(block, "_checkpoint_determinism_check", "default"), **kwargs
+            )
         return block(h, **kwargs)
 
     # -- parallelism and memory --------------------------------------------------------------------------------
@@ -455,6 +459,7 @@ class Transformer(nn.Module):
         block_interval: Optional[int] = None,
         modules: Optional[List[str]] = None,
         activation_memory_budget: Optional[float] = None,
+        determinism_check: str = "default",
     ) -> None:
         """
         Choose what is recomputed in the backward pass instead of being kept from the forward pass
@@ -496,7 +501,7 @@ class Transformer(nn.Module):
                 if name.startswith("blocks.") and name.count(".") == 1:
                     chosen.append(name.split(".")[1])
                 else:
-                    _checkpoint_module(module)
+                    _checkpoint_module(module, determinism_check)
         elif mode == TransformerActivationCheckpointingMode.budget:
             if activation_memory_budget is None:
                 raise ValueError("'activation_memory_budget' is required for 'budget' activation checkpointing")
@@ -512,6 +517,7 @@ class Transformer(nn.Module):
                     module.recompute_activation = True
         for key in chosen:
             self.blocks[key]._activation_checkpointing = True
+            self.blocks[key]._checkpoint_determinism_check = determinism_check
 
     def apply_compile(self) -> None:
         """Accepted for API compatibility; the GPU path uses explicit fused kernels rather than a compiler."""
