@@ -108,8 +108,9 @@ class Registrable:
         return reg[name]
 
     @classmethod
-    def get_registered_name(cls, klass: Optional[type] = None) -> Optional[str]:
-        klass = klass or cls
+    def get_registered_name(cls, sub: Optional[type] = None) -> Optional[str]:
+        """Name under which ``sub`` (default: this class) was registered, or ``None``."""
+        klass = sub or cls
         return klass.__dict__.get("_registered_name")
 
     @classmethod

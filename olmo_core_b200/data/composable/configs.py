@@ -25,6 +25,7 @@ from .instance_source import (
     SamplingInstanceSource,
     SlicedInstanceSource,
 )
+from .config_base import DocumentSourceConfig, TokenSourceConfig
 from .numpy_document_source import NumpyDocumentSourceConfig, NumpyDocumentSourceMixConfig
 from .token_source import (
     ConcatenatedDocumentSource,
@@ -65,41 +66,6 @@ def _build_all(configs: List[Any], work_dir: PathOrStr) -> List[Any]:
 
 # --------------------------------------------------------------------------------------------------- token sources
 @dataclass
-class TokenSourceConfig(Config):
-    def build(self, work_dir: PathOrStr) -> List[TokenSource]:
-        raise NotImplementedError
-
-    def __add__(self, other: "TokenSourceConfig") -> "ConcatenatedTokenSourceConfig":
-        return ConcatenatedTokenSourceConfig(sources=[self, other])
-
-    def __mul__(self, factor: float) -> "SamplingTokenSourceConfig":
-        return self.resize(factor)
-
-    def sample(self, *, max_tokens: Optional[int] = None, factor: Optional[float] = None,
-               seed: Optional[int] = SEED_NOT_SET) -> "SamplingTokenSourceConfig":
-        return SamplingTokenSourceConfig(sources=[self], max_tokens=max_tokens, factor=factor, seed=resolve_seed(seed))
-
-    def resize(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingTokenSourceConfig":
-        return self.sample(factor=factor, seed=seed)
-
-    def split(self, ratio: float) -> Tuple["SplitTokenSourceConfig", "SplitTokenSourceConfig"]:
-        return (SplitTokenSourceConfig(source=self, ratio=ratio, idx=0), SplitTokenSourceConfig(source=self, ratio=ratio, idx=1))
-
-
-@dataclass
-class DocumentSourceConfig(TokenSourceConfig):
-    def build(self, work_dir: PathOrStr) -> List[DocumentSource]:  # type: ignore[override]
-        raise NotImplementedError
-
-    def sample_by_docs(self, *, max_tokens: Optional[int] = None, factor: Optional[float] = None,
-                       seed: Optional[int] = SEED_NOT_SET) -> "SamplingDocumentSourceConfig":
-        return SamplingDocumentSourceConfig(sources=[self], max_tokens=max_tokens, factor=factor, seed=resolve_seed(seed))
-
-    def resize_by_docs(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingDocumentSourceConfig":
-        return self.sample_by_docs(factor=factor, seed=seed)
-
-
-@dataclass
 class ConcatenatedTokenSourceConfig(TokenSourceConfig):
     sources: List[Any]
     label: Optional[str] = None
@@ -124,11 +90,17 @@ class SplitTokenSourceConfig(TokenSourceConfig):
     idx: int  # 0: the first part, 1: the second
 
     def __post_init__(self):
+        if not 0 < self.ratio < 1:
+            raise ValueError("'ratio' must be strictly between 0 and 1")
         if self.idx not in (0, 1):
             raise ValueError("'idx' must be 0 or 1")
 
     def build(self, work_dir: PathOrStr) -> List[TokenSource]:
-        return [s.split(self.ratio)[self.idx] for s in _build_all([self.source], work_dir)]
+        # several built sources are split as one: the cut falls at ``ratio`` of their total
+        # (src/olmo_core/data/composable/token_source.py:447-462)
+        sources = _build_all([self.source], work_dir)
+        source = sources[0] if len(sources) == 1 else ConcatenatedTokenSource(*sources, work_dir=work_dir)
+        return [source.split(self.ratio)[self.idx]]
 
 
 def _resolve_max_tokens(sources, max_tokens: Optional[int], factor: Optional[float]) -> int:

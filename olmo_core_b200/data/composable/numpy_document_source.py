@@ -23,6 +23,7 @@ from ..mixes import DataMix, DataMixBase
 from ..tokenizer import TokenizerConfig
 from ..types import LongDocStrategy, NumpyDatasetDType
 from ..utils import iter_document_indices, load_array_slice
+from .config_base import DocumentSourceConfig
 from .token_source import DocumentSource, TokenRange
 
 __all__ = ["NumpyDocumentSource", "NumpyDocumentSourceConfig", "NumpyDocumentSourceMixConfig"]
@@ -57,7 +58,8 @@ class NumpyDocumentSource(DocumentSource):
     def __init__(self, *, source_paths: Sequence[PathOrStr], dtype, work_dir: PathOrStr, tokenizer: TokenizerConfig,
                  label_mask_paths: Optional[Sequence[PathOrStr]] = None, label: Optional[str] = None,
                  max_document_length: Optional[int] = None,
-                 long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate):
+                 long_doc_strategy: LongDocStrategy = LongDocStrategy.truncate,
+                 _source_sizes: Optional[Sequence[int]] = None, _label_mask_sizes: Optional[Sequence[int]] = None):
         super().__init__(work_dir=work_dir, label=label)
         self._max_document_length = max_document_length
         self._long_doc_strategy = LongDocStrategy(long_doc_strategy)
@@ -69,11 +71,25 @@ class NumpyDocumentSource(DocumentSource):
         self._mask_paths = None if label_mask_paths is None else tuple(normalize_path(p) for p in label_mask_paths)
         self._dtype = dtype
         self._tokenizer = tokenizer
-        item = np.dtype(dtype).itemsize
-        with ThreadPoolExecutor(max_workers=min(16, len(self._paths))) as pool:
-            sizes = list(pool.map(get_file_size, self._paths))
-        self._sizes = np.array([s // item for s in sizes], dtype=np.int64)
+        # File sizes are given by a parent that was split (no second look at the files) or read here, in parallel.
+        def items(paths: Tuple[str, ...], item: int) -> List[int]:
+            with ThreadPoolExecutor(max_workers=min(16, len(paths))) as pool:
+                return [n // item for n in pool.map(get_file_size, paths)]
+
+        sizes = list(_source_sizes) if _source_sizes is not None else items(self._paths, np.dtype(dtype).itemsize)
+        if len(sizes) != len(self._paths):
+            raise OLMoConfigurationError("'_source_sizes' must match 'source_paths' one to one")
+        self._sizes = np.array(sizes, dtype=np.int64)
         self._ends = np.cumsum(self._sizes)
+        self._mask_sizes: Optional[Tuple[int, ...]] = None
+        if self._mask_paths is not None:
+            mask_sizes = list(_label_mask_sizes) if _label_mask_sizes is not None else items(self._mask_paths, 1)
+            self._mask_sizes = tuple(int(n) for n in mask_sizes)
+            for mp, mn, sp, sn in zip(self._mask_paths, self._mask_sizes, self._paths, sizes):
+                if mn != sn:
+                    raise OLMoConfigurationError(
+                        "Each file in 'label_mask_paths' should have the same number of items as the corresponding "
+                        f"file in 'source_paths', but found {mn:,d} in '{mp}' vs {sn:,d} in '{sp}'.")
 
     Config: type
 
@@ -83,6 +99,42 @@ class NumpyDocumentSource(DocumentSource):
     @property
     def source_paths(self) -> Tuple[str, ...]:
         return self._paths
+
+    @property
+    def source_sizes(self) -> Tuple[int, ...]:
+        """Tokens in each source file."""
+        return tuple(int(n) for n in self._sizes)
+
+    @property
+    def label_mask_paths(self) -> Optional[Tuple[str, ...]]:
+        return self._mask_paths
+
+    @property
+    def label_mask_sizes(self) -> Optional[Tuple[int, ...]]:
+        return self._mask_sizes
+
+    @property
+    def dtype(self):
+        return self._dtype
+
+    @property
+    def tokenizer(self) -> TokenizerConfig:
+        return self._tokenizer
+
+    def split_by_source(self, group_size: int = 1) -> List["NumpyDocumentSource"]:
+        """One source per ``group_size`` consecutive files
+        (src/olmo_core/data/composable/numpy_document_source.py:478-512)."""
+        assert group_size >= 1
+        out: List[NumpyDocumentSource] = []
+        for i in range(0, len(self._paths), group_size):
+            sel = slice(i, i + group_size)
+            out.append(self.__class__(
+                source_paths=self._paths[sel], dtype=self._dtype, work_dir=self.work_dir, tokenizer=self._tokenizer,
+                label_mask_paths=None if self._mask_paths is None else self._mask_paths[sel], label=self.label,
+                max_document_length=self._max_document_length, long_doc_strategy=self._long_doc_strategy,
+                _source_sizes=self.source_sizes[sel],
+                _label_mask_sizes=None if self._mask_sizes is None else self._mask_sizes[sel]))
+        return out
 
     @property
     def eos_token_id(self) -> int:
@@ -174,7 +226,7 @@ class NumpyDocumentSource(DocumentSource):
 
 
 @dataclass(kw_only=True)
-class NumpyDocumentSourceConfigBase(Config):
+class NumpyDocumentSourceConfigBase(DocumentSourceConfig):
     """What :class:`NumpyDocumentSourceConfig` and :class:`NumpyDocumentSourceMixConfig` share
     (src/olmo_core/data/composable/numpy_document_source.py:33-77)."""
 
@@ -227,6 +279,13 @@ class NumpyDocumentSourceConfig(NumpyDocumentSourceConfigBase):
         """One config per labelled group of paths."""
         return {label: cls(source_paths=list(paths), tokenizer=tokenizer, label=label, **kwargs)
                 for label, paths in source_groups.items()}
+
+    def get_num_tokens(self) -> int:
+        """Tokens over all source files, from their sizes alone."""
+        item = np.dtype(self.get_dtype()).itemsize
+        paths = _expand(self.source_paths)
+        with ThreadPoolExecutor(max_workers=min(16, max(1, len(paths)))) as pool:
+            return sum(n // item for n in pool.map(get_file_size, paths))
 
     def build(self, work_dir: PathOrStr) -> List[NumpyDocumentSource]:
         paths = _expand(self.source_paths)

@@ -155,11 +155,18 @@ class DataLoaderBase(ABC):
 class TextDataLoaderBase(DataLoaderBase):
     """Loaders whose batches hold ``input_ids``; batch sizes are in tokens."""
 
-    def __init__(self, *, collator: DataCollator, **kwargs):
-        super().__init__(**kwargs)
+    def __init__(self, *, collator: DataCollator, work_dir: PathOrStr, global_batch_size: int, dp_world_size: int = 1,
+                 dp_rank: int = 0, fs_local_rank: Optional[int] = None):
+        super().__init__(work_dir=work_dir, global_batch_size=global_batch_size, dp_world_size=dp_world_size,
+                         dp_rank=dp_rank, fs_local_rank=fs_local_rank)
         self.collator = collator
         self.tokens_processed: int = 0
         """Tokens (over all ranks) consumed so far in the current epoch."""
+
+    @property
+    def worker_info(self):
+        """The ``torch.utils.data`` worker this code runs in, or ``None`` in the main process."""
+        return torch.utils.data.get_worker_info()
 
     def __iter__(self) -> Iterator[Dict[str, Any]]:
         for batch in super().__iter__():

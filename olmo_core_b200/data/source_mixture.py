@@ -14,7 +14,7 @@ import math
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass
 from itertools import chain
-from typing import Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import numpy as np
 
@@ -236,6 +236,18 @@ class SourceMixtureDatasetConfig(Config):
             target = next(s.target_ratio for s in self.source_list.sources if s.source_name == name)
             log.info(f"{name}: {abs(got - target):.4f} difference from target ratio {target:.4f}")
         return SourceMixtureDataset(sources=outcome)
+
+    def table_to_text(self, table) -> Any:
+        """Plain-text form of a ``rich`` table, 250 columns wide, for log files
+        (src/olmo_core/data/source_mixture.py:582-591)."""
+        from rich.console import Console
+        from rich.text import Text
+
+        console = Console(width=250)
+        with console.capture() as capture:
+            table.width = 250
+            console.print(table)
+        return Text.from_ansi(capture.get())
 
     def render_mixture_outcome_tables(self, results: List[SourceTokenDetails]) -> None:
         rows = [r.for_table(self.requested_tokens) for r in results]

@@ -62,6 +62,17 @@ class MoEMLPBase(nn.Module):
         """Tensor parallelism for MoE = expert sharding over the TP group."""
         self._shard_experts(tp_mesh)
 
+    def prepare_experts_for_fsdp(self, *, world_mesh=None, **kwargs) -> None:
+        """
+        Called before the model is sharded for data parallelism (src/olmo_core/nn/moe/mlp.py:87-112). The local
+        expert block is an ordinary parameter here (marked with its expert-parallel rank), and the data-parallel
+        runtime partitions it over the ranks that hold the same block, so there is nothing to re-wrap.
+        """
+        del world_mesh, kwargs
+
+    def prepare_experts_for_ddp(self, *, world_mesh=None) -> None:
+        del world_mesh
+
 
 class MoEMLP(MoEMLPBase):
     """Capacity-based experts: ``x`` is ``[E_local, capacity, d]`` and each expert is a batched matmul."""

@@ -74,11 +74,20 @@ class ParallelMLPBase(nn.Module):
         self._ep_pg = tp_mesh.get_group()
         self._expert_parallel_enabled = True
 
+    @property
+    def hidden_sharding_degree(self) -> int:
+        return self.mlp.hidden_sharding_degree
+
+    def warmup_cache(self, max_local_microbatch_size: int) -> None:
+        """Pre-size per-batch buffers; only the capacity-based variant keeps any."""
+        del max_local_microbatch_size
+
     def prepare_experts_for_fsdp(self, **kwargs) -> None:
         """Expert weights are already partitioned by expert; data-parallel sharding treats them like any parameter."""
+        self.mlp.prepare_experts_for_fsdp(**kwargs)
 
     def prepare_experts_for_ddp(self, **kwargs) -> None:
-        pass
+        self.mlp.prepare_experts_for_ddp(**kwargs)
 
     def indices_and_bins(self, expert_indices: torch.Tensor, batch_size_per_expert: torch.Tensor):
         return ops.indices_and_bins(expert_indices, self.num_experts, batch_size_per_expert)

@@ -154,8 +154,27 @@ class MoERouter(nn.Module):
             cur += value.detach()
 
     @property
+    def device(self) -> torch.device:
+        """Device the metric accumulators live on (src/olmo_core/nn/moe/router.py:238-240)."""
+        from ...utils import get_default_device
+
+        return get_default_device()
+
+    @property
     def batch_size_per_expert(self) -> Optional[torch.Tensor]:
         return self._acc.get("counts")
+
+    @property
+    def score_bias_batch_size_per_expert(self) -> Optional[torch.Tensor]:
+        """Tokens per expert since the last score-bias update; ``None`` without auxiliary-loss-free balancing
+        (src/olmo_core/nn/moe/router.py:242-261)."""
+        if self.bias_gamma is None:
+            return None
+        return self._acc.get("bias_counts")
+
+    @score_bias_batch_size_per_expert.setter
+    def score_bias_batch_size_per_expert(self, value: torch.Tensor) -> None:
+        self._acc["bias_counts"] = value
 
     @property
     def load_balancing_loss(self) -> Optional[torch.Tensor]:

@@ -63,6 +63,11 @@ class TransformerBlockBase(nn.Module):
     def forward(self, x: torch.Tensor, *, loss_div_factor: Optional[Union[torch.Tensor, float]] = None, **kwargs) -> torch.Tensor:
         raise NotImplementedError
 
+    def apply_pp(self, pp_mesh) -> None:
+        """A block has nothing of its own to set up for pipeline parallelism
+        (src/olmo_core/nn/transformer/block.py:60-61)."""
+        del pp_mesh
+
     def apply_tp(self, tp_mesh, *, input_layout=None, float8_enabled: bool = False) -> None:
         from ...parallel.tensor import shard_block_
 
@@ -310,7 +315,21 @@ class MoEHybridTransformerBlockBase(MoETransformerBlock):
                          init_device=init_device, cache=cache)
         self.feed_forward = feed_forward.build(d_model=d_model, init_device=init_device)
         self.feed_forward_moe_norm = layer_norm.build(d_model, init_device=init_device)
-        self.use_combined_forward = False
+        self._use_combined_forward: Optional[bool] = None
+
+    @property
+    def use_combined_forward(self) -> bool:
+        """Whether the sparse branch runs on a side stream beside the dense branch. Unless set, it follows whether
+        the experts are partitioned over ranks (src/olmo_core/nn/transformer/block.py:744-759)."""
+        if self._use_combined_forward is not None:
+            return self._use_combined_forward
+        return bool(getattr(self, "_ep_enabled", False) or getattr(self, "_tp_enabled", False))
+
+    @use_combined_forward.setter
+    def use_combined_forward(self, should_use: bool) -> None:
+        if should_use and not (getattr(self, "_ep_enabled", False) or getattr(self, "_tp_enabled", False)):
+            raise RuntimeError("combined forward can only be used when expert parallelism is enabled")
+        self._use_combined_forward = should_use
 
     @abstractmethod
     def dense_forward(self, x: torch.Tensor, **kwargs) -> torch.Tensor:
@@ -338,11 +357,6 @@ class MoEHybridTransformerBlockBase(MoETransformerBlock):
         cur.wait_stream(side)
         sparse.record_stream(cur)
         return sparse + dense
-
-    def apply_ep(self, ep_mesh, **kwargs) -> None:
-        super().apply_ep(ep_mesh, **kwargs)
-        self.use_combined_forward = True
-
 
 @beta_feature
 class MoEHybridTransformerBlock(MoEHybridTransformerBlockBase):

@@ -42,7 +42,8 @@ from .config import (
 )
 from .init import InitMethod
 
-__all__ = ["Transformer", "NormalizedTransformer", "MoETransformer", "Embedding"]
+__all__ = ["Transformer", "NormalizedTransformer", "MoETransformer", "Embedding",
+           "TransformerDataParallelWrappingStrategy", "TransformerActivationCheckpointingMode"]
 
 log = logging.getLogger(__name__)
 

@@ -43,6 +43,7 @@ class TransformerPipelineTrainModule(TrainModule):
         self.world_mesh = get_world_mesh() or build_world_mesh(dp=dp_config, tp=tp_config, pp=pp_config,
                                                                device_type=self.device.type)
         self.pp_config = pp_config
+        self._tp_config, self._cp_config = tp_config, cp_config
         self.pp_mesh = get_pp_mesh(self.world_mesh)
         self.rank_microbatch_size = rank_microbatch_size
         self.max_sequence_length = max_sequence_length
@@ -69,6 +70,56 @@ class TransformerPipelineTrainModule(TrainModule):
     @property
     def eval_batch_spec(self) -> EvalBatchSpec:
         return EvalBatchSpec(self.rank_microbatch_size, max_sequence_length=self.max_sequence_length)
+
+    @property
+    def tp_enabled(self) -> bool:
+        return self._tp_config is not None
+
+    @property
+    def cp_enabled(self) -> bool:
+        return self._cp_config is not None
+
+    @property
+    def train_pp_schedule(self) -> PipelineSchedule:
+        """The schedule of the current batch shape; it exists once a batch has been seen."""
+        if self._schedule is None:
+            raise RuntimeError("the pipeline schedule is built by the first training batch")
+        return self._schedule
+
+    def loss_fn(self, output: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """Loss of the last stage's output for one micro-batch, already divided by the batch's target count."""
+        return self._loss_fn(output, labels)
+
+    def run_pipeline(self, input_ids: torch.Tensor, labels: torch.Tensor, batch_num_tokens_for_loss, **kwargs):
+        """
+        One pass of the schedule over the batch (forward and backward of every micro-batch). Returns the summed loss
+        on ranks that hold the last stage, ``None`` elsewhere
+        (reference: src/olmo_core/train/train_module/transformer/pipeline_train_module.py:552-609).
+        """
+        if not torch.is_tensor(batch_num_tokens_for_loss):
+            batch_num_tokens_for_loss = torch.tensor(float(batch_num_tokens_for_loss))
+        self._batch_tokens_for_loss = move_to_device(batch_num_tokens_for_loss, self.device)
+        seq_len = input_ids.shape[1]
+        n_mb = max(1, input_ids.shape[0] // max(1, self.rank_microbatch_size // seq_len))
+        _, loss = self._get_schedule(n_mb).step(input_ids, target=labels, **kwargs)
+        return loss
+
+    def reduce_send_recv(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """
+        Make a scalar that only the last stage's ranks hold known to every rank: those ranks pass it in and it is
+        averaged over their data-parallel group; the others pass ``None``. One sum over the pipeline group then
+        delivers it (reference: pipeline_train_module.py:465-504, which relays it stage by stage instead).
+        """
+        if x is None:
+            x = torch.zeros((), device=self.device)
+        else:
+            x = x.detach().clone().to(self.device)
+            group = self.dp_process_group
+            if group is not None and dist.get_world_size(group) > 1:
+                dist.all_reduce(x, group=group)
+                x.div_(dist.get_world_size(group))
+        dist.all_reduce(x, group=self.pp_mesh.get_group())
+        return x
 
     def _loss_fn(self, logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         ce, z = cross_entropy_loss(logits.view(-1, logits.size(-1)), labels.view(-1), ignore_index=self.label_ignore_index,
@@ -134,13 +185,9 @@ class TransformerPipelineTrainModule(TrainModule):
             p.train()
         if "labels" not in batch:
             batch["labels"] = get_labels(batch, self.label_ignore_index)
-        self._batch_tokens_for_loss = move_to_device((batch["labels"] != self.label_ignore_index).sum(), self.device)
-        seq_len = batch["input_ids"].shape[1]
-        n_mb = max(1, batch["input_ids"].shape[0] // max(1, self.rank_microbatch_size // seq_len))
-        sched = self._get_schedule(n_mb)
         input_ids = move_to_device(batch["input_ids"], self.device)
         labels = move_to_device(batch["labels"], self.device)
-        _, loss = sched.step(input_ids, target=labels)
+        loss = self.run_pipeline(input_ids, labels, (batch["labels"] != self.label_ignore_index).sum())
         if dry_run:
             return
         # The loss lives on the rank with the last stage: average over DP there, then hand it down the pipe.

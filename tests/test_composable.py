@@ -115,6 +115,19 @@ def test_numpy_document_source(tmp_path):
     assert src.num_tokens == 2 * len(data)
     np.testing.assert_array_equal(src[len(data) - 2:len(data) + 3]["input_ids"], [14, tok.eos_token_id, 1, 2, 3])
     assert list(src.get_document_offsets()) == [(0, 8), (8, 14), (14, 22), (22, 28)]
+    # per-file views, a config-level token count, and the config algebra of every document source config
+    cfg = NumpyDocumentSource.Config(source_paths=[str(tmp_path / "part-*.npy")], tokenizer=tok)
+    assert cfg.get_num_tokens() == 2 * len(data) and src.source_sizes == (len(data), len(data))
+    first, second = src.split_by_source()
+    assert first.source_paths == (paths[0],) and second.num_tokens == len(data) and src.dtype == np.uint16
+    np.testing.assert_array_equal(second[:3]["input_ids"], [1, 2, 3])
+    (half,) = cfg.resize(0.5, seed=None).build(tmp_path / "work")
+    assert half.num_tokens == len(data)
+    a, b = cfg.split(0.25)
+    (a_src,), (b_src,) = a.build(tmp_path / "work"), b.build(tmp_path / "work")
+    assert a_src.num_tokens == 7 and a_src.num_tokens + b_src.num_tokens == 2 * len(data)
+    (both,) = (cfg + cfg).build(tmp_path / "work")
+    assert both.num_tokens == 4 * len(data) and len(list(both.get_document_offsets())) == 8
 
 
 def test_global_indices_are_stable_across_sequence_lengths():
