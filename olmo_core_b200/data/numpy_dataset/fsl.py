@@ -300,6 +300,11 @@ class NumpyPackedFSLDataset(NumpyFSLDatasetBase):
             self._source_sizes = [s // item for s in self.file_sizes]
         return self._source_sizes
 
+    @property
+    def source_size_groups(self) -> List[List[int]]:
+        """:data:`source_sizes` cut into the groups that are packed together."""
+        return list(chunked(self.source_sizes, self._source_group_size))
+
     def _table_paths(self, group: Sequence[PathOrStr]) -> Tuple[Path, Path, Path]:
         params = dict(seq=self.sequence_length, long=str(self._long_doc_strategy), dt=np.dtype(self.indices_dtype).name)
         return (self._cache_path("document-indices", *group, **params),

@@ -47,6 +47,13 @@ __all__ = [
     "InstancePacker",
     "pack_documents_into_instances",
     "attention_mask_to_cache_leftpad",
+    "iter_document_indices_with_max_sequence_length",
+    "run_worker_func",
+    "find_end_first_consecutive_true",
+    "find_start_last_consecutive_true",
+    "group_consecutive_values",
+    "SegmentTreeNode",
+    "SegmentTree",
 ]
 
 
@@ -336,17 +343,23 @@ def bucket_documents(path: PathOrStr, target: Path, *, buckets: Sequence[int], e
 
 
 def segment_documents_into_instances(path: PathOrStr, target: Path, *, max_sequence_length: int, eos_token_id: int, dtype,
-                                     indices_dtype=np.uint32, sample: Optional[Tuple[int, int]] = None) -> Tuple[int, int]:
-    """One instance per document, truncated to ``max_sequence_length``; optionally a random sample of ``(n, seed)``."""
+                                     indices_dtype=np.uint32, bos_token_id: Optional[int] = None,
+                                     sample: Optional[Tuple[int, int]] = None) -> Tuple[int, int]:
+    """
+    One instance per document, truncated to ``max_sequence_length``, written to ``target`` as flat
+    ``start, end`` pairs. ``sample=(n, seed)`` draws ``n`` instances with replacement. Returns the number of
+    documents and of instances written (src/olmo_core/data/utils.py:535-578).
+    """
     idx: List[int] = []
-    n_docs = 0
-    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, dtype=dtype):
-        n_docs += 1
-        idx += [start, min(end, start + max_sequence_length)]
+    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, bos_token_id=bos_token_id, dtype=dtype):
+        idx += [start, start + min(end - start, max_sequence_length)]
     arr = np.asarray(idx, dtype=indices_dtype).reshape(-1, 2)
+    n_docs = arr.shape[0]
     if sample is not None:
         n, seed = sample
-        arr = arr[get_rng(seed).choice(arr.shape[0], size=min(n, arr.shape[0]), replace=False)]
+        arr = get_rng(seed).choice(arr, size=n)
+    if arr.size == 0:
+        raise RuntimeError(f"Failed to produce any documents from '{path}'")
     write_array_to_disk(arr.reshape(-1), target)
     return n_docs, arr.shape[0]
 
@@ -497,21 +510,25 @@ class InstancePacker:
         return self.instances, document_indices, total
 
 
-def pack_documents_into_instances(path: PathOrStr, max_sequence_length: int, *, eos_token_id: int, dtype,
-                                  indices_dtype=np.uint64, long_doc_strategy: str = "truncate") -> Tuple[List[List[int]], np.ndarray, int]:
-    """Pack the documents of a token file; documents longer than an instance are truncated or split."""
+def pack_documents_into_instances(*paths: PathOrStr, max_sequence_length: int, eos_token_id: int, dtype,
+                                  bos_token_id: Optional[int] = None, indices_dtype=np.uint64,
+                                  long_doc_strategy="truncate") -> Tuple[List[List[int]], np.ndarray, int]:
+    """
+    Best-fit-decreasing packing of the documents of one or more token files (taken as one concatenated file) into
+    instances of at most ``max_sequence_length`` tokens; longer documents are truncated or split. Returns the
+    document ids of every instance, the ``(num_documents, 2)`` boundaries, and the number of tokens packed
+    (src/olmo_core/data/utils.py:885-941).
+    """
+    if not paths:
+        raise RuntimeError("At least one source path must be provided")
     docs: List[Tuple[int, int]] = []
-    for start, end in iter_document_indices(path, eos_token_id=eos_token_id, dtype=dtype):
-        if end - start > max_sequence_length:
-            if long_doc_strategy == "truncate":
-                docs.append((start, start + max_sequence_length))
-            elif long_doc_strategy == "fragment":
-                for s in range(start, end, max_sequence_length):
-                    docs.append((s, min(end, s + max_sequence_length)))
-            else:
-                raise ValueError(long_doc_strategy)
-        else:
-            docs.append((start, end))
+    offset = 0
+    for path in paths:
+        for start, end in iter_document_indices_with_max_sequence_length(
+                path, max_sequence_length, eos_token_id=eos_token_id, bos_token_id=bos_token_id, dtype=dtype,
+                long_doc_strategy=long_doc_strategy):
+            docs.append((offset + start, offset + end))
+        offset += get_file_size(path) // _array_itemsize(dtype)
     arr = np.asarray(docs, dtype=indices_dtype).reshape(-1, 2)
     return InstancePacker(max_sequence_length).pack_documents(arr)
 

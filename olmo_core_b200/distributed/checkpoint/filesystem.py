@@ -138,12 +138,15 @@ def _write_file(items: List[WriteItem], planner: SavePlanner, rel_name: str, roo
 
 class RemoteFileSystemWriter(dist_cp.StorageWriter):
     def __init__(self, path: PathOrStr, thread_count: Optional[int] = None, save_overwrite: bool = False,
-                 process_group=None, throttle_uploads: bool = False):
+                 process_group=None, throttle_uploads: bool = False, process_count: Optional[int] = None):
         super().__init__()
         if thread_count is not None and thread_count <= 0:
             raise ValueError("thread count must be at least 1")
         self.path = normalize_path(path)
-        self.thread_count = thread_count or get_default_thread_count()
+        # Serialisation here is a device->host copy plus a file write, both of which release the interpreter lock,
+        # so a request for worker processes is served by as many writer threads.
+        self.process_count = process_count
+        self.thread_count = thread_count or process_count or get_default_thread_count()
         self.save_overwrite = save_overwrite
         self.process_group = process_group
         self.throttle_uploads = throttle_uploads
@@ -194,7 +197,7 @@ class RemoteFileSystemWriter(dist_cp.StorageWriter):
         metadata.storage_data = {r.index: r.storage_data for rank_results in results for r in rank_results}
         metadata.storage_meta = self.storage_meta()
         blob = pickle.dumps(metadata)
-        target = f"{self.path}/.metadata"
+        target = self.metadata_path
         if is_url(self.path):
             with tempfile.NamedTemporaryFile(delete=False) as tmp:
                 tmp.write(blob)
@@ -212,6 +215,15 @@ class RemoteFileSystemWriter(dist_cp.StorageWriter):
 
     def storage_meta(self) -> Optional[StorageMeta]:
         return StorageMeta(checkpoint_id=self.path, save_id=self.save_id)
+
+    @property
+    def metadata_path(self) -> str:
+        return f"{self.path}/.metadata"
+
+    @property
+    def checkpoint_id(self) -> str:
+        """Where the checkpoint is being written."""
+        return self.path
 
 
 class RemoteFileSystemReader(dist_cp.StorageReader):
@@ -231,6 +243,10 @@ class RemoteFileSystemReader(dist_cp.StorageReader):
             self.path = normalize_path(checkpoint_id)
         self._metadata = None
         self.storage_data = {}
+
+    @property
+    def checkpoint_id(self) -> str:
+        return self.path
 
     @classmethod
     def validate_checkpoint_id(cls, checkpoint_id: Union[str, os.PathLike]) -> bool:

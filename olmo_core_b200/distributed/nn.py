@@ -35,11 +35,12 @@ class _AllToAllSingle(torch.autograd.Function):
 
 def all_to_all_single(
     group: Optional[dist.ProcessGroup],
-    x: torch.Tensor,
+    input_: torch.Tensor,
     output_split_sizes: Optional[Sequence[int]] = None,
     input_split_sizes: Optional[Sequence[int]] = None,
 ) -> torch.Tensor:
-    """Exchange slices of dim 0 of ``x`` between the ranks of ``group`` (autograd-aware)."""
+    """Exchange slices of dim 0 of ``input_`` between the ranks of ``group`` (autograd-aware)."""
+    x = input_
     outs = list(output_split_sizes) if output_split_sizes is not None else None
     ins = list(input_split_sizes) if input_split_sizes is not None else None
     return _AllToAllSingle.apply(group, x, outs, ins)
@@ -61,8 +62,9 @@ class _AllToAll(torch.autograd.Function):
         return (None, None) + tuple(back)
 
 
-def all_to_all(group: Optional[dist.ProcessGroup], tensors: List[torch.Tensor],
+def all_to_all(group: Optional[dist.ProcessGroup], input_tensor_list: List[torch.Tensor],
                output_like: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
-    """List form: ``tensors[i]`` goes to rank ``i``; returns what each rank sent to us."""
+    """List form: ``input_tensor_list[i]`` goes to rank ``i``; returns what each rank sent to us."""
+    tensors = input_tensor_list
     output_like = output_like if output_like is not None else tensors
     return list(_AllToAll.apply(group, output_like, *tensors))

@@ -42,11 +42,14 @@ def _size(group) -> int:
     return dist.get_world_size(group) if dist.is_initialized() else 1
 
 
-def all_to_all_single_cp2hp(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """``[B, T/CP, H, D] -> [B, T, H/CP, D]``"""
+def all_to_all_single_cp2hp(input_: torch.Tensor, cp_group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """``[B, T/CP, H, D] -> [B, T, H/CP, D]``; a 3-D input ``[B, T/CP, H]`` is taken as ``D = 1``."""
+    x, group = input_, cp_group
     cp = _size(group)
     if cp == 1:
         return x
+    if x.dim() == 3:
+        return all_to_all_single_cp2hp(x.unsqueeze(-1), group).squeeze(-1)
     B, t, H, D = x.shape
     if H % cp != 0:
         raise ValueError(f"number of heads ({H}) must be divisible by the context-parallel degree ({cp})")
@@ -61,11 +64,14 @@ def all_to_all_single_cp2hp(x: torch.Tensor, group: Optional[dist.ProcessGroup] 
     return recv.view(cp, B, t, H // cp, D).permute(1, 0, 2, 3, 4).reshape(B, cp * t, H // cp, D)
 
 
-def all_to_all_single_hp2cp(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """``[B, T, H/CP, D] -> [B, T/CP, H, D]``"""
+def all_to_all_single_hp2cp(input_: torch.Tensor, cp_group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """``[B, T, H/CP, D] -> [B, T/CP, H, D]``; a 3-D input ``[B, T, H/CP]`` is taken as ``D = 1``."""
+    x, group = input_, cp_group
     cp = _size(group)
     if cp == 1:
         return x
+    if x.dim() == 3:
+        return all_to_all_single_hp2cp(x.unsqueeze(-1), group).squeeze(-1)
     B, T, h, D = x.shape
     if T % cp != 0:
         raise ValueError(f"sequence length ({T}) must be divisible by the context-parallel degree ({cp})")
@@ -80,9 +86,12 @@ def all_to_all_single_hp2cp(x: torch.Tensor, group: Optional[dist.ProcessGroup] 
     return recv.view(cp, B, t, h, D).permute(1, 2, 0, 3, 4).reshape(B, t, cp * h, D)
 
 
-def all_to_all_cp2hp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
+def all_to_all_cp2hp(inputs: List[torch.Tensor], cp_group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
     """Batched :func:`all_to_all_single_cp2hp`: tensors that share ``[B, T/CP, *, D]`` go in one exchange."""
+    tensors, group = inputs, cp_group
     cp = _size(group)
+    if any(t.dim() == 3 for t in tensors):  # mixed ranks: no common packing
+        return [all_to_all_single_cp2hp(t, group) for t in tensors]
     from ...parallel import ulysses
 
     if cp == 1 or len(tensors) == 1 or ulysses.peer_exchange_usable(tensors[0], group):  # no packing for the peer kernel
@@ -94,9 +103,12 @@ def all_to_all_cp2hp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGr
     return list(out.split([h // cp for h in heads], dim=2))
 
 
-def all_to_all_hp2cp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
+def all_to_all_hp2cp(inputs: List[torch.Tensor], cp_group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
     """Batched :func:`all_to_all_single_hp2cp`."""
+    tensors, group = inputs, cp_group
     cp = _size(group)
+    if any(t.dim() == 3 for t in tensors):
+        return [all_to_all_single_hp2cp(t, group) for t in tensors]
     from ...parallel import ulysses
 
     if cp == 1 or len(tensors) == 1 or ulysses.peer_exchange_usable(tensors[0], group):
@@ -109,8 +121,9 @@ def all_to_all_hp2cp(tensors: List[torch.Tensor], group: Optional[dist.ProcessGr
     return [o.reshape(B, t_, cp * h, D) for o, h in zip(out.split(local_heads, dim=3), local_heads)]
 
 
-def all_to_all_single_cp2hp_qkvpacked(qkv: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+def all_to_all_single_cp2hp_qkvpacked(input_: torch.Tensor, cp_group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """``[B, T/CP, 3, H, D] -> [B, T, 3, H/CP, D]``"""
+    qkv, group = input_, cp_group
     cp = _size(group)
     if cp == 1:
         return qkv
@@ -120,8 +133,9 @@ def all_to_all_single_cp2hp_qkvpacked(qkv: torch.Tensor, group: Optional[dist.Pr
     return out.view(B, cp * t, three, H // cp, D)
 
 
-def all_to_all_single_hp2cp_qkvpacked(qkv: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+def all_to_all_single_hp2cp_qkvpacked(input_: torch.Tensor, cp_group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """``[B, T, 3, H/CP, D] -> [B, T/CP, 3, H, D]``"""
+    qkv, group = input_, cp_group
     cp = _size(group)
     if cp == 1:
         return qkv

@@ -76,10 +76,14 @@ def normalize_path(path: PathOrStr) -> str:
     return p
 
 
-def join_path(path1: PathOrStr, path2: PathOrStr) -> PathOrStr:
-    if is_url(path1):
-        return f"{str(path1).rstrip('/')}/{str(path2).lstrip('/')}"
-    return Path(path1) / path2
+def join_path(path: PathOrStr, *paths: PathOrStr) -> PathOrStr:
+    """Join two or more paths / URL parts; a single argument is returned as is."""
+    for p in paths:
+        if is_url(path):
+            path = f"{str(path).rstrip('/')}/{str(p).lstrip('/')}"
+        else:
+            path = Path(path) / p
+    return path
 
 
 def get_parent(path: PathOrStr) -> PathOrStr:
@@ -92,8 +96,11 @@ def retriable(
     max_attempts: int = 3,
     retriable_errors: Tuple[Type[Exception], ...] = (OLMoNetworkError, ConnectionError, TimeoutError),
     backoff: float = 0.5,
+    retry_condition: Optional[Callable[[Exception], bool]] = None,
 ) -> Callable:
-    """Retry a function with exponential back-off and jitter on the given error types."""
+    """Retry a function with exponential back-off and jitter on the given error types, or on any error for which
+    ``retry_condition`` holds. The last failure is raised as :class:`OLMoNetworkError` (a type that a data-loader
+    worker can re-raise from its message alone)."""
 
     def deco(fn: Callable) -> Callable:
         @functools.wraps(fn)
@@ -103,9 +110,13 @@ def retriable(
                 attempt += 1
                 try:
                     return fn(*args, **kwargs)
-                except retriable_errors as e:
-                    if attempt >= max_attempts:
+                except Exception as e:
+                    if not (isinstance(e, retriable_errors) or (retry_condition is not None and retry_condition(e))):
                         raise
+                    if attempt >= max_attempts:
+                        if isinstance(e, OLMoNetworkError):
+                            raise
+                        raise OLMoNetworkError(f"'{fn.__name__}' failed {max_attempts} attempts with: {e}") from e
                     delay = backoff * (2 ** (attempt - 1)) * (1 + random.random())
                     log.warning("%s failed (%s); retry %d/%d in %.1fs", fn.__name__, e, attempt, max_attempts, delay)
                     time.sleep(delay)
@@ -414,22 +425,24 @@ def write_text(path: PathOrStr, text: str, overwrite: bool = True) -> None:
 
 
 @retriable()
-def upload(source: PathOrStr, target: str, save_overwrite: bool = False) -> None:
+def upload(source: PathOrStr, target: str, save_overwrite: bool = False, quiet: bool = False) -> None:
     """Upload local ``source`` to URL ``target``."""
     t = normalize_path(target)
     if not is_url(t):
-        copy_file(source, t, save_overwrite=save_overwrite)
+        copy_file(source, t, save_overwrite=save_overwrite, quiet=quiet)
         return
+    if not quiet:
+        log.info(f"Uploading {source} to {t}...")
     _client(t).upload(Path(source), t, save_overwrite)
 
 
-def copy_file(source: PathOrStr, target: PathOrStr, save_overwrite: bool = False) -> None:
+def copy_file(source: PathOrStr, target: PathOrStr, save_overwrite: bool = False, quiet: bool = False) -> None:
     s, t = normalize_path(source), normalize_path(target)
     if is_url(t):
         if is_url(s):
             write_bytes(t, read_bytes(s), overwrite=save_overwrite)
         else:
-            upload(s, t, save_overwrite=save_overwrite)
+            upload(s, t, save_overwrite=save_overwrite, quiet=quiet)
         return
     tp = Path(t)
     if tp.exists() and not save_overwrite:
@@ -441,16 +454,19 @@ def copy_file(source: PathOrStr, target: PathOrStr, save_overwrite: bool = False
         shutil.copyfile(s, t)
 
 
-def copy_dir(source: PathOrStr, target: PathOrStr, save_overwrite: bool = False, num_threads: Optional[int] = None) -> None:
+def copy_dir(source: PathOrStr, target: PathOrStr, save_overwrite: bool = False, num_threads: Optional[int] = None,
+             quiet: bool = False) -> None:
     from concurrent.futures import ThreadPoolExecutor
 
     s = normalize_path(source)
     files = list(list_directory(s, recurse=True, include_dirs=False))
+    if not quiet:
+        log.info(f"Copying {len(files):,d} files from {s} to {target}...")
     with ThreadPoolExecutor(max_workers=num_threads or 8) as pool:
         futs = []
         for f in files:
             rel = str(f)[len(s):].lstrip("/")
-            futs.append(pool.submit(copy_file, f, join_path(target, rel), save_overwrite))
+            futs.append(pool.submit(copy_file, f, join_path(target, rel), save_overwrite, True))
         for fu in futs:
             fu.result()
 

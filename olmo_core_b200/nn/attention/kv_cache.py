@@ -59,9 +59,15 @@ class KVCacheManager(nn.Module):
     def is_reusable(self, batch_size: int, max_seq_len: int) -> bool:
         return self._batch_size == batch_size and self._max_seq_len >= max_seq_len
 
-    def reallocate(self, batch_size: int, max_seq_len: int) -> None:
+    def reallocate(self, batch_size: int, max_seq_len: int, _explicitly_free_memory: bool = True) -> None:
         device, dtype = self.k_cache.device, self.k_cache.dtype
         del self.k_cache, self.v_cache, self.cache_leftpad
+        if _explicitly_free_memory and device.type == "cuda":
+            # the old cache can be most of the memory: hand it back before the new one is allocated
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
         self._allocate(batch_size, max_seq_len, device, dtype)
 
     def reset(self, batch_size: int, max_seq_len: int) -> None:

@@ -40,6 +40,16 @@ class BufferCache(MutableMapping):
     def __len__(self) -> int:
         return sum(1 for _ in self)
 
+    def get_for_device(self, key: str, device: torch.device) -> Optional[torch.Tensor]:
+        """The cached tensor, moved to (and re-cached on) ``device``; ``None`` when absent."""
+        tensor = self.get(key)
+        if tensor is None:
+            return None
+        if tensor.device != torch.device(device):
+            tensor = tensor.to(device, non_blocking=True)
+            self[key] = tensor
+        return tensor
+
     def with_namespace(self, namespace: str) -> "BufferCache":
         """A view on the same storage under a sub-namespace."""
         return BufferCache(self._key(namespace), self._store)

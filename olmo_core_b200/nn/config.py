@@ -14,6 +14,10 @@ __all__ = ["ModuleConfig", "ModelConfig"]
 class ModuleConfig(Config):
     """A config that knows how to build a sub-module."""
 
+    def build(self, *args, **kwargs) -> nn.Module:
+        """Build the module this config describes."""
+        raise NotImplementedError
+
 
 @dataclass
 class ModelConfig(Config):

@@ -8,12 +8,13 @@ __all__ = ["ResidualStream"]
 
 
 class ResidualStream(nn.Module):
-    def __init__(self, *, alpha: float = 1.0, dropout: float = 0.0):
+    def __init__(self, alpha: float = 1.0, dropout: float = 0.0):
         super().__init__()
         self.alpha = alpha
         self.dropout = dropout
 
-    def forward(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    def forward(self, residual: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """``residual + alpha * dropout(x)``"""
         if self.dropout > 0.0:
-            y = F.dropout(y, p=self.dropout, training=self.training)
-        return x + y if self.alpha == 1.0 else x + self.alpha * y
+            x = F.dropout(x, p=self.dropout, training=self.training)
+        return residual + x if self.alpha == 1.0 else torch.add(residual, x, alpha=self.alpha)

@@ -9,22 +9,22 @@ __all__ = ["attach_auxiliary_loss", "AutoAuxiliaryLoss"]
 
 
 class AutoAuxiliaryLoss(torch.autograd.Function):
-    """Identity on ``x`` that feeds a gradient of one into ``aux_loss`` during backward."""
+    """Identity on ``activation`` that feeds a gradient of one into ``aux_loss`` during backward."""
 
     @staticmethod
-    def forward(ctx, x, aux_loss):  # type: ignore[override]
+    def forward(ctx, activation, aux_loss):  # type: ignore[override]
         ctx.save_for_backward(aux_loss)
-        return x
+        return activation
 
     @staticmethod
-    def backward(ctx, grad):  # type: ignore[override]
+    def backward(ctx, grad_output):  # type: ignore[override]
         (aux_loss,) = ctx.saved_tensors
-        return grad, torch.ones_like(aux_loss)
+        return grad_output, torch.ones_like(aux_loss)
 
 
-def attach_auxiliary_loss(x: torch.Tensor, aux_loss: torch.Tensor) -> torch.Tensor:
+def attach_auxiliary_loss(activation: torch.Tensor, aux_loss: torch.Tensor) -> torch.Tensor:
     """
-    Tie ``aux_loss`` to ``x`` so that ``backward`` through ``x`` also back-propagates the auxiliary loss
-    (src/olmo_core/ops/__init__.py:4-28).
+    Tie ``aux_loss`` to ``activation`` so that ``backward`` through the activation also back-propagates the
+    auxiliary loss (src/olmo_core/ops/__init__.py:4-28). Returns the activation unchanged.
     """
-    return AutoAuxiliaryLoss.apply(x, aux_loss)
+    return AutoAuxiliaryLoss.apply(activation, aux_loss)

@@ -27,18 +27,23 @@ __all__ = [
     "repeat",
     "sum_tensor",
     "all_to_all",
+    "GatherOp",
+    "ScatterOp",
+    "BinnedGatherOp",
+    "BinnedScatterOp",
+    "AllToAllOp",
 ]
 
 
-def histc(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
-    """Count occurrences of each expert id (int64 result, any input shape)."""
-    return torch.bincount(indices.reshape(-1), minlength=num_experts)[:num_experts]
+def histc(x: torch.Tensor, num_classes: int) -> torch.Tensor:
+    """Count occurrences of each id in ``[0, num_classes)`` (int64 result, any input shape)."""
+    return torch.bincount(x.reshape(-1), minlength=num_classes)[:num_classes]
 
 
-def batched_histc(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
-    """Histogram over the last dimension: ``[..., k] -> [..., num_experts]``."""
-    out = torch.zeros(*indices.shape[:-1], num_experts, dtype=indices.dtype, device=indices.device)
-    out.scatter_add_(-1, indices, torch.ones_like(indices))
+def batched_histc(x: torch.Tensor, num_classes: int) -> torch.Tensor:
+    """Histogram over the last dimension: ``[..., k] -> [..., num_classes]``."""
+    out = torch.zeros(*x.shape[:-1], num_classes, dtype=x.dtype, device=x.device)
+    out.scatter_add_(-1, x, torch.ones_like(x))
     return out
 
 
@@ -210,11 +215,12 @@ def scatter(x: torch.Tensor, indices: torch.Tensor, bin_ids: Optional[torch.Tens
     return _Scatter.apply(x, indices, weights, top_k)
 
 
-def binned_gather(x: torch.Tensor, indices: torch.Tensor, bins: torch.Tensor, capacity: int, top_k: int) -> torch.Tensor:
+def binned_gather(x: torch.Tensor, indices: torch.Tensor, bins: torch.Tensor, bin_size: int, top_k: int) -> torch.Tensor:
     """
-    Capacity-limited layout ``[num_experts, capacity, d]``: the first ``capacity`` tokens routed to each
+    Capacity-limited layout ``[num_experts, bin_size, d]``: the first ``bin_size`` tokens routed to each
     expert are copied, the rest are dropped, unused slots are zero.
     """
+    capacity = bin_size
     E = bins.numel()
     pos = torch.arange(indices.numel(), device=x.device)
     starts = torch.cat([bins.new_zeros(1), bins[:-1]]).long()

@@ -406,7 +406,8 @@ class OverrideDecay(Config):
             raise OLMoConfigurationError("Specify exactly one of 'end_lr' or 'end_lr_fraction' for override decay.")
         _check_nonneg(end_lr=self.end_lr, end_lr_fraction=self.end_lr_fraction)
 
-    def apply(self, main_lr_at, initial_lr: LR, current: int) -> LR:
+    def lr_at(self, main_lr_at, initial_lr: LR, current: int) -> LR:
+        """Rate at ``current`` (>= ``start``), given the main schedule as a function of the step."""
         start_lr = main_lr_at(self.start)
         end_lr = _abs_or_fraction(initial_lr, self.end_lr, self.end_lr_fraction)
         t = current - self.start
@@ -448,7 +449,7 @@ class ComposableScheduler(Scheduler):
         current = max(current, 0)
         if self.override_decay is None or current < self.override_decay.start:
             return self._main_schedule_lr(initial_lr, current)
-        return self.override_decay.apply(lambda t: self._main_schedule_lr(initial_lr, t), initial_lr, current)
+        return self.override_decay.lr_at(lambda t: self._main_schedule_lr(initial_lr, t), initial_lr, current)
 
 
 @Scheduler.register("sequential")
@@ -494,7 +495,7 @@ class SequentialScheduler(Scheduler):
             warnings.warn(f"'{type(self).__name__}' ignores 't_max' once 'override_decay' is active (t_max={t_max}).",
                           UserWarning, stacklevel=2)
             self._warned_t_max_ignored = True
-        return self.override_decay.apply(lambda t: self._sequential_lr(initial_lr, t, t_max), initial_lr, current)
+        return self.override_decay.lr_at(lambda t: self._sequential_lr(initial_lr, t, t_max), initial_lr, current)
 
 
 @Scheduler.register("wsds")

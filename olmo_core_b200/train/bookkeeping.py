@@ -121,7 +121,8 @@ class BookkeepingMixin:
             if not self._metrics_consistent:
                 log.warning("Ranks record different sets of metrics (expected e.g. with pipeline parallelism).")
         self.run_bookkeeping_op(reduce_metrics, window, dict(self._metrics_reduce_type), self.bookkeeping_device,
-                                process_group=self.bookkeeping_pg, cb=self._check_and_pass_on_metrics)
+                                process_group=self.bookkeeping_pg, metrics_consistent=bool(self._metrics_consistent),
+                                cb=self._check_and_pass_on_metrics)
 
     def _check_and_pass_on_metrics(self, metrics: Dict[int, Dict[str, float]]) -> None:
         for step in sorted(metrics):

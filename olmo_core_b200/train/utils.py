@@ -118,13 +118,21 @@ def reduce_metrics(
     metrics_reduce_type: Dict[str, Optional[ReduceType]],
     device: torch.device,
     process_group: Optional[dist.ProcessGroup] = None,
+    metrics_consistent: bool = True,
 ) -> Dict[int, Dict[str, float]]:
     """
     Reduce a window of metrics across ranks. ``mean`` / ``sum`` / ``l2_norm`` go through one SUM all-reduce
     (l2 norms are squared first; sums are pre-divided by about sqrt(world) for fp range), ``max`` through one
     MAX all-reduce, metrics with reduce type ``None`` are taken from the local rank. A rank that lacks a
-    metric contributes zero and does not count towards its mean.
+    metric contributes zero and does not count towards its mean. With ``metrics_consistent=False`` the ranks first
+    exchange which metrics they know (one object gather), so that a metric recorded on some ranks only, e.g. the loss
+    on the last pipeline stage, still reduces over buffers of one shape.
     """
+    if not metrics_consistent and is_distributed():
+        merged: Dict[str, Optional[ReduceType]] = {}
+        for per_rank in _gather_reduce_types(metrics_reduce_type, process_group):
+            merged.update(per_rank)
+        metrics_reduce_type = merged
     steps = sorted(metrics)
     names = sorted({n for m in metrics.values() for n in m} | set(metrics_reduce_type))
     names = [n for n in names if any(n in metrics[s] for s in steps) or metrics_reduce_type.get(n) is not None]

@@ -202,9 +202,12 @@ def log_extra_field(field_name: str, field_value: Any) -> None:
     _LOG_EXTRA_FIELDS[field_name] = field_value
 
 
-def setup_logging(log_filter_type: LogFilterType = LogFilterType.rank0_only) -> None:
-    """Root logger with a rank-prefixed format and a filter that silences non-selected ranks below WARNING."""
+def setup_logging(log_filter_type: LogFilterType = LogFilterType.rank0_only, force: bool = False) -> None:
+    """Root logger with a rank-prefixed format and a filter that silences non-selected ranks below WARNING.
+    A second call does nothing unless ``force`` is set."""
     global _LOGGING_CONFIGURED
+    if _LOGGING_CONFIGURED and not force:
+        return
     from ..distributed.utils import get_local_rank, get_rank
 
     log_extra_field("hostname", socket.gethostname())

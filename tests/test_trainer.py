@@ -123,3 +123,28 @@ def test_two_sharded_ranks_match_one_rank(tmp_path):
     load_model_and_optim_state(two / "run" / "step4" / "model_and_optim", fresh)
     for (n, p), q in zip(trainer.train_module.model.named_parameters(), fresh.parameters()):
         torch.testing.assert_close(p, q, rtol=1e-3, atol=1e-5, msg=n)
+
+
+def _inconsistent_metrics_worker():
+    import torch.distributed as dist
+
+    from olmo_core_b200.train.common import ReduceType
+    from olmo_core_b200.train.utils import check_metrics_consistent, reduce_metrics
+
+    rank = dist.get_rank()
+    kinds = {"shared": ReduceType.mean, "norm": ReduceType.l2_norm}
+    metrics = {1: {"shared": torch.tensor(float(rank + 1)), "norm": torch.tensor(3.0 if rank == 0 else 4.0)}}
+    if rank == 1:  # only this rank knows the loss, as with the last stage of a pipeline
+        kinds["loss"] = ReduceType.mean
+        metrics[1]["loss"] = torch.tensor(2.5)
+        kinds["peak"] = ReduceType.max
+        metrics[1]["peak"] = torch.tensor(7.0)
+    consistent = check_metrics_consistent(kinds)
+    assert not consistent
+    out = reduce_metrics(metrics, kinds, torch.device("cpu"), metrics_consistent=consistent)
+    assert out[1]["shared"] == pytest.approx(1.5) and out[1]["norm"] == pytest.approx(5.0)
+    assert out[1]["loss"] == pytest.approx(2.5) and out[1]["peak"] == pytest.approx(7.0)
+
+
+def test_reduce_metrics_that_only_some_ranks_record():
+    run_distributed_test(_inconsistent_metrics_worker, world_size=2)
