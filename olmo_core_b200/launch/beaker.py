@@ -357,11 +357,17 @@ class GantryMonitorCallback:
     def on_inactive_soft_timeout(self, job=None) -> None:
         self._inactive()
 
-    def on_success(self, job=None) -> None:
+    def on_preemption(self, job=None) -> None:
+        self._say(":warning:", "was preempted!")
+
+    def on_cancellation(self, job=None) -> None:
+        self._say(":warning:", "was canceled!")
+
+    def on_success(self, job=None, *, metrics=None, results_ds=None) -> None:
         self._say(":check:", "succeeded!")
 
-    def on_failure(self, job=None, *args, **kwargs) -> None:
-        self._say(":warning:", "failed!")
+    def on_failure(self, job=None, *, metrics=None, results_ds=None) -> None:
+        self._say(":check-failed:", "failed!")
 
 
 def main(argv: Optional[List[str]] = None) -> None:

@@ -113,13 +113,14 @@ def node_is_occupied(beaker, node, beaker_priority) -> Tuple[Any, bool]:
     return node, False
 
 
-def get_occupied_beaker_hosts(hosts_metadata: Dict[str, HostMetadata], beaker_cluster: str, priority: str) -> Set[str]:
+def get_occupied_beaker_hosts(hosts_metadata: Dict[str, HostMetadata], beaker_cluster: str, beaker_priority: str) -> Set[str]:
     """Hosts of the cluster that run a job this priority cannot preempt."""
     try:
         from beaker import Beaker
     except ImportError as e:
         raise OLMoEnvironmentError("host selection needs the 'beaker-py' package") from e
     ranks = ["low", "normal", "high", "urgent"]
+    priority = str(beaker_priority).lower()
     beaker = Beaker.from_env()
     busy: Set[str] = set()
     for node in beaker.cluster.nodes(beaker_cluster):
