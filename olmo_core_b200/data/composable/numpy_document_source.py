@@ -23,8 +23,7 @@ from ..mixes import DataMix, DataMixBase
 from ..tokenizer import TokenizerConfig
 from ..types import LongDocStrategy, NumpyDatasetDType
 from ..utils import iter_document_indices, load_array_slice
-from .config_base import DocumentSourceConfig
-from .token_source import DocumentSource, TokenRange
+from .token_source import DocumentSource, DocumentSourceConfig, TokenRange
 
 __all__ = ["NumpyDocumentSource", "NumpyDocumentSourceConfig", "NumpyDocumentSourceMixConfig"]
 

@@ -1,31 +1,38 @@
 """
-Token and document sources (API of src/olmo_core/data/composable/token_source.py:37-677, sliced_token_source.py,
-sampling_token_source.py, sampling_document_source.py, mixing_token_source.py, mixing_document_source.py).
+Token and document sources and the bases of their configs
+(API of src/olmo_core/data/composable/token_source.py:37-677).
 
 A token source is an addressable sequence of token ids (optionally with a label mask); a document source also knows
-where documents start and end. Every composite here (concatenation, slice, sample, mix) is the SAME data structure: a
-list of pieces ``(child, start, end)`` with a prefix sum over their lengths, so that a token range is resolved with one
-binary search and a walk over the pieces it touches.
+where documents start and end. Every composite (concatenation here; slice, sample and mix in the modules named after
+them) is the SAME data structure: a list of pieces ``(child, start, end)`` with a prefix sum over their lengths, so that
+a token range is resolved with one binary search and a walk over the pieces it touches.
+
+Every source class has its serializable config at ``<Source>.Config``. Token-source configs ``build(work_dir)`` into a
+LIST of sources (a glob may expand into many).
 """
 
 from __future__ import annotations
 
 from abc import abstractmethod
 from dataclasses import dataclass
-from typing import Iterable, List, Optional, Sequence, Tuple, TypedDict, Union
+from typing import TYPE_CHECKING, Any, Iterable, List, Optional, Sequence, Tuple, TypedDict, Union
 
 import numpy as np
 
 from ...aliases import PathOrStr
-from ..utils import get_rng
+from ...config import Config
 from .source_abc import SourceABC
-from .utils import SEED_NOT_SET, as_ndarray, calculate_sample_sizes, resolve_seed
+from .utils import SEED_NOT_SET, as_ndarray, resolve_seed
+
+if TYPE_CHECKING:
+    from .sampling_document_source import SamplingDocumentSource, SamplingDocumentSourceConfig
+    from .sampling_token_source import SamplingTokenSource, SamplingTokenSourceConfig
+    from .sliced_token_source import SlicedTokenSource
 
 __all__ = [
     "TokenRange", "TokenSource", "DocumentSource", "InMemoryTokenSource", "InMemoryDocumentSource",
-    "ConcatenatedTokenSource", "ConcatenatedDocumentSource", "SlicedTokenSource", "SamplingTokenSource",
-    "SamplingDocumentSource", "MixingTokenSource", "MixingDocumentSource", "MixingTokenSourceSpec",
-    "MixingDocumentSourceSpec",
+    "ConcatenatedTokenSource", "ConcatenatedDocumentSource", "TokenSourceConfig", "DocumentSourceConfig",
+    "ConcatenatedTokenSourceConfig", "ConcatenatedDocumentSourceConfig", "SplitTokenSourceConfig",
 ]
 
 
@@ -80,6 +87,8 @@ class TokenSource(SourceABC):
             raise ValueError("exactly one of 'max_tokens' and 'factor' is required")
         if max_tokens is None:
             max_tokens = int(factor * self.num_tokens)  # type: ignore[operator]
+        from .sampling_token_source import SamplingTokenSource
+
         return SamplingTokenSource(self, max_tokens=max_tokens, seed=seed, work_dir=self.common_work_dir, label=self.label)
 
     def resize(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingTokenSource":
@@ -89,6 +98,8 @@ class TokenSource(SourceABC):
     def split(self, ratio: float) -> Tuple["SlicedTokenSource", "SlicedTokenSource"]:
         if not 0 < ratio < 1:
             raise ValueError("'ratio' must be strictly between 0 and 1")
+        from .sliced_token_source import SlicedTokenSource
+
         cut = int(ratio * self.num_tokens)
         return (SlicedTokenSource(self, slice(0, cut), work_dir=self.common_work_dir, label=self.label),
                 SlicedTokenSource(self, slice(cut, self.num_tokens), work_dir=self.common_work_dir, label=self.label))
@@ -106,6 +117,8 @@ class DocumentSource(TokenSource):
             raise ValueError("exactly one of 'max_tokens' and 'factor' is required")
         if max_tokens is None:
             max_tokens = int(factor * self.num_tokens)  # type: ignore[operator]
+        from .sampling_document_source import SamplingDocumentSource
+
         return SamplingDocumentSource(self, max_tokens=max_tokens, seed=seed, work_dir=self.common_work_dir,
                                       label=self.label)
 
@@ -275,216 +288,109 @@ class ConcatenatedDocumentSource(ConcatenatedTokenSource, DocumentSource):
             base += child.num_tokens
 
 
-class SlicedTokenSource(_Spliced):
-    DISPLAY_ICON = ""
 
-    def __init__(self, source: TokenSource, source_slice: slice, *, work_dir: PathOrStr, label: Optional[str] = None):
-        if source_slice.step not in (None, 1):
-            raise ValueError("only contiguous slices are supported")
-        start, end, _ = source_slice.indices(source.num_tokens)
-        self._slice = slice(start, end)
-        super().__init__([source], np.array([[0, start, end]]), work_dir=work_dir, label=label)
+# ----------------------------------------------------------------------------------------------------- configs
+@dataclass
+class TokenSourceConfig(Config):
+    def build(self, work_dir: PathOrStr) -> List["TokenSource"]:
+        raise NotImplementedError
 
-    @property
-    def source(self) -> TokenSource:
-        return self._children[0]
+    def __add__(self, other: "TokenSourceConfig") -> "TokenSourceConfig":
+        """Concatenation; two document sources give a document source."""
+        if isinstance(self, DocumentSourceConfig) and isinstance(other, DocumentSourceConfig):
+            return ConcatenatedDocumentSourceConfig(sources=[self, other])
+        if isinstance(other, TokenSourceConfig):
+            return ConcatenatedTokenSourceConfig(sources=[self, other])
+        raise TypeError(f"Cannot add {type(self)} with {type(other)}.")
 
-    @property
-    def source_slice(self) -> slice:
-        return self._slice
+    def __mul__(self, factor: float) -> "SamplingTokenSourceConfig":
+        if not isinstance(factor, (float, int)):
+            raise TypeError(f"Cannot multiply {type(self)} with {type(factor)}.")
+        return self.resize(factor)
 
-    @property
-    def slice_start(self) -> int:
-        return self._slice.start
+    def sample(self, *, max_tokens: Optional[int] = None, factor: Optional[float] = None,
+               seed: Optional[int] = SEED_NOT_SET) -> "SamplingTokenSourceConfig":
+        from .sampling_token_source import SamplingTokenSourceConfig
 
-    @property
-    def slice_stop(self) -> int:
-        return self._slice.stop
+        return SamplingTokenSourceConfig(sources=[self], max_tokens=max_tokens, factor=factor, seed=resolve_seed(seed))
 
-    @property
-    def slice_step(self) -> int:
-        return 1
+    def resize(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingTokenSourceConfig":
+        return self.sample(factor=factor, seed=seed)
+
+    def split(self, ratio: float) -> Tuple["SplitTokenSourceConfig", "SplitTokenSourceConfig"]:
+        return (SplitTokenSourceConfig(source=self, ratio=ratio, idx=0), SplitTokenSourceConfig(source=self, ratio=ratio, idx=1))
 
 
-def _unwind(sources: Sequence[TokenSource]) -> List[TokenSource]:
-    """
-    Replace mixes by their per-source samples and samples by the pieces they are made of, breadth first (the order of
-    src/olmo_core/data/composable/sampling_token_source.py:103-120), so that re-sampling keeps THEIR proportions.
-    """
-    from collections import deque
+@dataclass
+class DocumentSourceConfig(TokenSourceConfig):
+    def build(self, work_dir: PathOrStr) -> List["DocumentSource"]:  # type: ignore[override]
+        raise NotImplementedError
 
-    out: List[TokenSource] = []
-    frontier = deque(sources)
-    while frontier:
-        s = frontier.popleft()
-        if isinstance(s, (MixingTokenSource, MixingDocumentSource)):
-            frontier.extend(s.sampled_sources)
-        elif type(s) is SamplingTokenSource:
-            frontier.extend(s.sources)
-        else:
-            out.append(s)
+    def sample_by_docs(self, *, max_tokens: Optional[int] = None, factor: Optional[float] = None,
+                       seed: Optional[int] = SEED_NOT_SET) -> "SamplingDocumentSourceConfig":
+        from .sampling_document_source import SamplingDocumentSourceConfig
+
+        return SamplingDocumentSourceConfig(sources=[self], max_tokens=max_tokens, factor=factor, seed=resolve_seed(seed))
+
+    def resize_by_docs(self, factor: float, seed: Optional[int] = SEED_NOT_SET) -> "SamplingDocumentSourceConfig":
+        return self.sample_by_docs(factor=factor, seed=seed)
+
+
+def _default_seed() -> int:
+    return resolve_seed(SEED_NOT_SET)
+
+
+def _build_all(configs: List[Any], work_dir: PathOrStr) -> List[Any]:
+    out: List[Any] = []
+    for c in configs:
+        built = c.build(work_dir)
+        out.extend(built if isinstance(built, (list, tuple)) else [built])
     return out
 
 
-class SamplingTokenSource(_Spliced):
-    """
-    ``max_tokens`` tokens drawn from the sources in proportion to their sizes, ignoring document boundaries: whole
-    repetitions of a source first, then one contiguous window (at a random offset with a seed, at 0 without).
-    """
+@dataclass
+class ConcatenatedTokenSourceConfig(TokenSourceConfig):
+    sources: List[Any]
+    label: Optional[str] = None
 
-    DISPLAY_ICON = ""
-
-    def __init__(self, *sources: TokenSource, max_tokens: int, seed: Optional[int] = SEED_NOT_SET, work_dir: PathOrStr,
-                 label: Optional[str] = None):
-        if not sources:
-            raise ValueError("At least one source must be provided.")
-        if max_tokens <= 0:
-            raise ValueError("'max_tokens' must be positive")
-        self._seed = resolve_seed(seed)
-        rng = None if self._seed is None else get_rng(self._seed)
-        self.original_sources = tuple(sources)
-        total = sum(s.num_tokens for s in sources)
-        final: List[TokenSource] = []
-        for leaf in _unwind(sources):
-            want = round(max_tokens * (leaf.num_tokens / total))
-            final.extend([leaf] * (want // leaf.num_tokens))
-            rest = want % leaf.num_tokens
-            if rest > 0:
-                at = 0 if rng is None else int(rng.integers(0, leaf.num_tokens - rest))
-                final.append(SlicedTokenSource(leaf, slice(at, at + rest), work_dir=work_dir))
-        super().__init__(final, _whole(final), work_dir=work_dir, label=label)
-
-    def children(self):
-        return self.original_sources
-
-    @property
-    def seed(self) -> Optional[int]:
-        return self._seed
-
-
-class SamplingDocumentSource(_Spliced, DocumentSource):
-    """
-    Whole documents drawn from the (concatenated) sources: with a seed the documents are shuffled once; that order is
-    repeated as often as it fits into ``max_tokens`` and followed by the longest prefix of it that fits into the rest
-    (src/olmo_core/data/composable/sampling_document_source.py:87-170). Without a seed the natural order is used.
-    """
-
-    DISPLAY_ICON = ""
-
-    def __init__(self, *sources: DocumentSource, max_tokens: int, seed: Optional[int] = SEED_NOT_SET,
-                 work_dir: PathOrStr, label: Optional[str] = None):
-        if not sources:
-            raise ValueError("At least one source must be provided.")
-        if max_tokens <= 0:
-            raise ValueError("'max_tokens' must be positive")
-        self._seed = resolve_seed(seed)
-        self._max_tokens = max_tokens
-        self.original_sources = tuple(sources)
-        source = ConcatenatedDocumentSource(*sources, work_dir=work_dir) if len(sources) > 1 else sources[0]
-        self._source = source
-        if self._seed is None:
-            import warnings
-
-            warnings.warn("No seed provided for SamplingDocumentSource. It's recommended to set a seed to ensure that the "
-                          "distribution of documents in child sources are preserved.")
-        offsets = np.fromiter((i for pair in source.get_document_offsets() for i in pair), dtype=np.uint64).reshape(-1, 2)
-        if self._seed is not None:
-            get_rng(self._seed).shuffle(offsets, axis=0)
-        cumulative = np.cumsum(offsets[:, 1] - offsets[:, 0], dtype=np.uint64)
-        total = int(cumulative[-1])
-        picked = np.take(offsets, (cumulative <= max_tokens % total).nonzero()[0], axis=0)
-        if max_tokens // total > 0:
-            picked = np.concatenate([np.tile(offsets, (max_tokens // total, 1)), picked])
-        if picked.shape[0] == 0:
-            raise RuntimeError(f"Unable to sample {max_tokens} tokens from {source}")
-        pieces = np.concatenate([np.zeros((len(picked), 1), dtype=np.int64), picked.astype(np.int64)], axis=1)
-        super().__init__([source], pieces, work_dir=work_dir, label=label)
-
-    def children(self):
-        return self.original_sources
-
-    @property
-    def source(self) -> DocumentSource:
-        return self._source
-
-    @property
-    def max_tokens(self) -> int:
-        return self._max_tokens
-
-    @property
-    def seed(self) -> Optional[int]:
-        return self._seed
-
-    def get_document_offsets(self) -> Iterable[Tuple[int, int]]:
-        starts = np.concatenate([[0], self._ends[:-1]])
-        return zip(starts.tolist(), self._ends.tolist())
+    def build(self, work_dir: PathOrStr) -> List[TokenSource]:
+        return [ConcatenatedTokenSource(*_build_all(self.sources, work_dir), work_dir=work_dir, label=self.label)]
 
 
 @dataclass
-class MixingTokenSourceSpec:
-    source: TokenSource
-    ratio: float
-    max_repetition_factor: float = 1.0
+class ConcatenatedDocumentSourceConfig(DocumentSourceConfig):
+    sources: List[Any]
     label: Optional[str] = None
+
+    def build(self, work_dir: PathOrStr) -> List[DocumentSource]:
+        return [ConcatenatedDocumentSource(*_build_all(self.sources, work_dir), work_dir=work_dir, label=self.label)]
 
 
 @dataclass
-class MixingDocumentSourceSpec:
-    source: DocumentSource
+class SplitTokenSourceConfig(TokenSourceConfig):
+    source: Any
     ratio: float
-    max_repetition_factor: float = 1.0
-    label: Optional[str] = None
+    idx: int  # 0: the first part, 1: the second
+
+    def __post_init__(self):
+        if not 0 < self.ratio < 1:
+            raise ValueError("'ratio' must be strictly between 0 and 1")
+        if self.idx not in (0, 1):
+            raise ValueError("'idx' must be 0 or 1")
+
+    def build(self, work_dir: PathOrStr) -> List[TokenSource]:
+        # several built sources are split as one: the cut falls at ``ratio`` of their total
+        # (src/olmo_core/data/composable/token_source.py:447-462)
+        sources = _build_all([self.source], work_dir)
+        source = sources[0] if len(sources) == 1 else ConcatenatedTokenSource(*sources, work_dir=work_dir)
+        return [source.split(self.ratio)[self.idx]]
 
 
-class MixingTokenSource(ConcatenatedTokenSource):
-    """Sources combined at given ratios: each is sampled to the size the ratios call for, then concatenated."""
-
-    DISPLAY_ICON = ""
-    Spec = MixingTokenSourceSpec
-    _by_docs = False
-
-    def __init__(self, *source_specs, work_dir: PathOrStr, seed: Optional[int] = SEED_NOT_SET,
-                 num_tokens: Optional[int] = None, label: Optional[str] = None):
-        if not source_specs:
-            raise ValueError("At least one source spec must be provided.")
-        self._seed = resolve_seed(seed)
-        labels = [spec.label or spec.source.label or str(i) for i, spec in enumerate(source_specs)]
-        sizes = calculate_sample_sizes([spec.source.num_tokens for spec in source_specs],
-                                       [spec.ratio for spec in source_specs],
-                                       [spec.max_repetition_factor for spec in source_specs],
-                                       target_size=num_tokens, labels=labels)
-        sampled = []
-        for i, (spec, size) in enumerate(zip(source_specs, sizes.tolist())):
-            child_seed = None if self._seed is None else self._seed + i
-            cls = SamplingDocumentSource if self._by_docs else SamplingTokenSource
-            sampled.append(cls(spec.source, max_tokens=int(size), seed=child_seed, work_dir=work_dir, label=labels[i]))
-        self.sampled_sources = tuple(sampled)
-        _Spliced.__init__(self, sampled, _whole(sampled), work_dir=work_dir, label=label)
-
-    @property
-    def seed(self) -> Optional[int]:
-        return self._seed
+def _resolve_max_tokens(sources, max_tokens: Optional[int], factor: Optional[float]) -> int:
+    if (max_tokens is None) == (factor is None):
+        raise ValueError("exactly one of 'max_tokens' and 'factor' is required")
+    return max_tokens if max_tokens is not None else int(factor * sum(s.num_tokens for s in sources))  # type: ignore[operator]
 
 
-class MixingDocumentSource(MixingTokenSource, DocumentSource):
-    Spec = MixingDocumentSourceSpec
-    _by_docs = True
-
-    def get_document_offsets(self) -> Iterable[Tuple[int, int]]:
-        base = 0
-        for child in self.sampled_sources:
-            for s, e in child.get_document_offsets():
-                yield base + s, base + e
-            base += child.num_tokens
-
-
-_CONFIG_NAMES = ('TokenSourceConfig', 'DocumentSourceConfig', 'ConcatenatedTokenSourceConfig', 'ConcatenatedDocumentSourceConfig', 'SplitTokenSourceConfig')
-
-
-def __getattr__(name: str):
-    # the config classes live in ``configs.py`` (which imports this module); they stay reachable under this module's name
-    if name in _CONFIG_NAMES:
-        from . import configs
-
-        return getattr(configs, name)
-    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+ConcatenatedTokenSource.Config = ConcatenatedTokenSourceConfig  # type: ignore[attr-defined]
+ConcatenatedDocumentSource.Config = ConcatenatedDocumentSourceConfig  # type: ignore[attr-defined]
