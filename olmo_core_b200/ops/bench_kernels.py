@@ -146,6 +146,31 @@ def bench_norm(args, peaks) -> None:
         _emit({"kernel": "rmsnorm_" + name, "rows": rows, "cols": cols, "fwd_ms": round(t_f, 4),
                "gbs": round(nbytes / t_f / 1e6, 1), "bwd_ms": round(t_b, 4),
                "bwd_gbs": round(1.5 * nbytes / t_b / 1e6, 1)}, peaks)
+    # The backward numbers above include the host's launch gaps between the four launches of an autograd call. The
+    # kernels alone, through the C entry points with every buffer allocated once (with and without the residual):
+    from . import _lib
+
+    L, st = _lib.lib(), _lib.stream_ptr()
+    res = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    y, dx = torch.empty_like(g), torch.empty_like(g)
+    rstd = torch.empty(rows, device="cuda", dtype=torch.float32)
+    partial = torch.empty(L.ocb_norm_bwd_partials(), cols, device="cuda", dtype=torch.float32)
+    xd, wd = x.detach(), w.detach()
+    bf = _lib.dt(xd)
+
+    def fwd(r):
+        _lib.check(L.ocb_rmsnorm_fwd(xd.data_ptr(), wd.data_ptr(), _lib.ptr(r), y.data_ptr(), rstd.data_ptr(), rows, cols,
+                                     cols, cols, cols, cols if r is not None else 0, 1e-6, bf, bf, st), "ocb_rmsnorm_fwd")
+
+    def bwd():
+        _lib.check(L.ocb_rmsnorm_bwd(g.data_ptr(), xd.data_ptr(), wd.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                     partial.data_ptr(), rows, cols, cols, cols, cols, cols, bf, bf, st), "ocb_rmsnorm_bwd")
+
+    t0, t1, t2 = time_ms(lambda: fwd(None), args.iters), time_ms(lambda: fwd(res), args.iters), time_ms(bwd, args.iters)
+    _emit({"kernel": "rmsnorm_kernels_only", "rows": rows, "cols": cols, "fwd_ms": round(t0, 4),
+           "gbs": round(nbytes / t0 / 1e6, 1), "fwd_residual_ms": round(t1, 4),
+           "fwd_residual_gbs": round(1.5 * nbytes / t1 / 1e6, 1), "bwd_ms": round(t2, 4),
+           "bwd_gbs": round(1.5 * nbytes / t2 / 1e6, 1), "note": "bwd includes clearing the partial rows"}, peaks)
 
 
 def bench_mlp(args, peaks) -> None:
@@ -317,6 +342,30 @@ def bench_norm_rope(args, peaks) -> None:
     t_b = time_ms(lambda: torch.autograd.grad(out, (x, w), g, retain_graph=True), args.iters)
     _emit({"kernel": "qk_norm_rope", "tokens": B * S, "width": H * D, "fwd_ms": round(t_f, 4), "gbs": round(nbytes / t_f / 1e6, 1),
            "bwd_ms": round(t_b, 4), "bwd_gbs": round(1.5 * nbytes / t_b / 1e6, 1)}, peaks)
+    # kernels alone (no autograd, no allocation; the backward call includes clearing the partial rows)
+    from . import _lib
+
+    L, st = _lib.lib(), _lib.stream_ptr()
+    rows, cols = B * S, H * D
+    xd, wd = x.detach().view(rows, cols), w.detach()
+    y, dx, g2 = torch.empty_like(xd), torch.empty_like(xd), g.view(rows, cols)
+    rstd = torch.empty(rows, device="cuda", dtype=torch.float32)
+    partial = torch.empty(L.ocb_norm_bwd_partials(), cols, device="cuda", dtype=torch.float32)
+    bf = _lib.dt(xd)
+
+    def fwd():
+        _lib.check(L.ocb_norm_rope_fwd(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), rstd.data_ptr(), sin.data_ptr(),
+                                       cos.data_ptr(), None, rows, H, D, S, 0, 1, cols, cols, 1e-6, bf, bf, st),
+                   "ocb_norm_rope_fwd")
+
+    def bwd():
+        _lib.check(L.ocb_norm_rope_bwd(g2.data_ptr(), xd.data_ptr(), wd.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                       partial.data_ptr(), sin.data_ptr(), cos.data_ptr(), None, rows, H, D, S, 0, 1, cols,
+                                       cols, cols, bf, bf, st), "ocb_norm_rope_bwd")
+
+    t0, t1 = time_ms(fwd, args.iters), time_ms(bwd, args.iters)
+    _emit({"kernel": "qk_norm_rope_kernels_only", "tokens": rows, "width": cols, "fwd_ms": round(t0, 4),
+           "gbs": round(nbytes / t0 / 1e6, 1), "bwd_ms": round(t1, 4), "bwd_gbs": round(1.5 * nbytes / t1 / 1e6, 1)}, peaks)
 
 
 def bench_swiglu(args, peaks) -> None:

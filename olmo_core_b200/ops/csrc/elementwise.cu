@@ -439,6 +439,12 @@ norm_rope_kernel(const T* __restrict__ in, const T* __restrict__ x_saved, const 
   }
 }
 
+}  // namespace ocb
+
+#include "rownorm_pipe.cuh"
+
+namespace ocb {
+
 // ----------------------------------------------------------------------------------------------------
 // SwiGLU
 // ----------------------------------------------------------------------------------------------------
@@ -739,6 +745,30 @@ static inline int pick_tpg(int group, int max_vec = kMaxVec) {
 
 #define OCB_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -4)
 
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Dynamic shared memory above 48 KB has to be requested per kernel; the request is repeated per launch because it is
+// per device and costs about a microsecond.
+template <typename K>
+static inline bool allow_smem(K kernel, size_t bytes) {
+  // the 48 KB that need no request include the kernel's static shared memory, hence the margin
+  return bytes <= 40 * 1024 ||
+         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) == cudaSuccess;
+}
+
+static inline size_t pipe_bytes(int chunks_per_row, bool with_trig, int stages = kPipeStages) {
+  return sizeof(uint4) * stages * chunks_per_row * kNormThreads + (with_trig ? sizeof(float) * stages * 2 * 128 : 0);
+}
+
+// The pipelined kernels can be switched off for comparison (OCB_NORM_PIPE=0).
+static inline bool norm_pipe_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OCB_NORM_PIPE");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 }  // namespace ocb
 
 using namespace ocb;
@@ -761,6 +791,31 @@ extern "C" int ocb_rmsnorm_fwd(const void* x, const void* w, const void* resid, 
                                int w_dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (group <= 0 || cols % group != 0 || group % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0) return -1;
+  if (norm_pipe_enabled() && act_dtype == OCB_BF16 && group == cols && (cols == 2048 || cols == 4096) && ldx % 8 == 0 &&
+      ldy % 8 == 0 && (resid == nullptr || ldr % 8 == 0) && aligned16(x) && aligned16(y) && aligned16(resid) &&
+      aligned16(w) && (w_dtype == OCB_BF16 || w_dtype == OCB_F32)) {
+    const int grid = rows < 148 * 3 ? rows : 148 * 3;
+    const bf16* xp = static_cast<const bf16*>(x);
+    const bf16* rp = static_cast<const bf16*>(resid);
+    bf16* yp = static_cast<bf16*>(y);
+#define OCB_RMS_FWD_PIPE(WT, NV, RES)                                                                              \
+    {                                                                                                              \
+      auto kern = rmsnorm_fwd_pipe_kernel<WT, NV, RES>;                                                            \
+      const size_t bytes = pipe_bytes((RES ? 2 : 1) * NV, false);                                                  \
+      if (!allow_smem(kern, bytes)) return -4;                                                                     \
+      kern<<<grid, kNormThreads, bytes, stream>>>(xp, static_cast<const WT*>(w), rp, yp, rstd, rows, ldx, ldy, ldr, eps); \
+    }
+    const int nv = cols / 2048;
+    if (w_dtype == OCB_BF16) {
+      if (nv == 1) { if (resid) OCB_RMS_FWD_PIPE(bf16, 1, true) else OCB_RMS_FWD_PIPE(bf16, 1, false) }
+      else { if (resid) OCB_RMS_FWD_PIPE(bf16, 2, true) else OCB_RMS_FWD_PIPE(bf16, 2, false) }
+    } else {
+      if (nv == 1) { if (resid) OCB_RMS_FWD_PIPE(float, 1, true) else OCB_RMS_FWD_PIPE(float, 1, false) }
+      else { if (resid) OCB_RMS_FWD_PIPE(float, 2, true) else OCB_RMS_FWD_PIPE(float, 2, false) }
+    }
+#undef OCB_RMS_FWD_PIPE
+    return OCB_CHECK_LAUNCH();
+  }
   const int gpr = cols / group;
   const long long n_groups = static_cast<long long>(rows) * gpr;
   const int tpg = pick_tpg(group);
@@ -789,9 +844,29 @@ extern "C" int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   const int gpb = kNormThreads / tpg;
   long long want = (n_groups + gpb - 1) / gpb;
   const int grid = static_cast<int>(want < kNormBwdBlocks ? want : kNormBwdBlocks);
-  if (dw_partial != nullptr) {
+  const bool pipe = norm_pipe_enabled() && act_dtype == OCB_BF16 && group == cols && (cols == 2048 || cols == 4096) &&
+                    lddy % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) &&
+                    aligned16(w) && aligned16(dw_partial) && (w_dtype == OCB_BF16 || w_dtype == OCB_F32);
+  // The pipelined kernel stores one whole partial row per block: only rows without a block have to be cleared.
+  if (dw_partial != nullptr && !(pipe && grid == kNormBwdBlocks)) {
     if (cudaMemsetAsync(dw_partial, 0, sizeof(float) * static_cast<size_t>(kNormBwdBlocks) * group, stream) != cudaSuccess)
       return -4;
+  }
+  if (pipe) {
+    const bf16* gp = static_cast<const bf16*>(dy);
+    const bf16* xp = static_cast<const bf16*>(x);
+    bf16* dxp = static_cast<bf16*>(dx);
+#define OCB_RMS_BWD_PIPE(WT, NV)                                                                                   \
+    {                                                                                                              \
+      auto kern = rmsnorm_bwd_pipe_kernel<WT, NV>;                                                                 \
+      const size_t bytes = pipe_bytes(2 * NV, false, kPipeStagesBwd);                                             \
+      if (!allow_smem(kern, bytes)) return -4;                                                                     \
+      kern<<<grid, kNormThreads, bytes, stream>>>(gp, xp, static_cast<const WT*>(w), rstd, dxp, dw_partial, rows, lddy, ldx, lddx); \
+    }
+    if (w_dtype == OCB_BF16) { if (cols == 2048) OCB_RMS_BWD_PIPE(bf16, 1) else OCB_RMS_BWD_PIPE(bf16, 2) }
+    else { if (cols == 2048) OCB_RMS_BWD_PIPE(float, 1) else OCB_RMS_BWD_PIPE(float, 2) }
+#undef OCB_RMS_BWD_PIPE
+    return OCB_CHECK_LAUNCH();
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
     if (maxv == 2)
@@ -826,6 +901,26 @@ extern "C" int ocb_norm_rope_fwd(const void* x, const void* w, void* y, float* r
   const int half = head_dim / 2;
   if (head_dim % 16 != 0 || (half / 8) > 32 || ((half / 8) & (half / 8 - 1)) != 0) return -1;
   if (n_heads * (half / 8) > kMaxPv * kNormThreads) return -1;
+  if (norm_pipe_enabled() && act_dtype == OCB_BF16 && head_dim == 128 && n_heads * 8 <= kNormThreads && ldx % 8 == 0 &&
+      ldy % 8 == 0 && aligned16(x) && aligned16(y) && aligned16(w) && aligned16(sin_t) && aligned16(cos_t) &&
+      (w_dtype == OCB_BF16 || w_dtype == OCB_F32)) {
+    const int pgrid = rows < 148 * 3 ? rows : 148 * 3;
+    const size_t bytes = pipe_bytes(2, true);
+    if (w_dtype == OCB_BF16) {
+      auto kern = norm_rope_pipe_kernel<bf16, false>;
+      if (!allow_smem(kern, bytes)) return -4;
+      kern<<<pgrid, kNormThreads, bytes, stream>>>(static_cast<const bf16*>(x), nullptr, static_cast<const bf16*>(w), rstd,
+                                                   static_cast<bf16*>(y), nullptr, sin_t, cos_t, pos_ids, rows, n_heads,
+                                                   seq_len, pos_offset, norm_mode, ldx, 0, ldy, eps);
+    } else {
+      auto kern = norm_rope_pipe_kernel<float, false>;
+      if (!allow_smem(kern, bytes)) return -4;
+      kern<<<pgrid, kNormThreads, bytes, stream>>>(static_cast<const bf16*>(x), nullptr, static_cast<const float*>(w), rstd,
+                                                   static_cast<bf16*>(y), nullptr, sin_t, cos_t, pos_ids, rows, n_heads,
+                                                   seq_len, pos_offset, norm_mode, ldx, 0, ldy, eps);
+    }
+    return OCB_CHECK_LAUNCH();
+  }
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   const bool one_pv = n_heads * (half / 8) <= kNormThreads;
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
@@ -850,10 +945,37 @@ extern "C" int ocb_norm_rope_bwd(const void* dy, const void* x, const void* w, c
   // three blocks per SM fit with one pair vector per thread, two otherwise
   const int max_blocks = one_pv ? kNormBwdBlocks + kNormBwdBlocks / 2 : kNormBwdBlocks;
   const int grid = rows < max_blocks ? rows : max_blocks;
-  if (dw_partial != nullptr && norm_mode != 0) {
+  const bool pipe = norm_pipe_enabled() && act_dtype == OCB_BF16 && head_dim == 128 && n_heads * 8 <= kNormThreads &&
+                    lddy % 8 == 0 && lddx % 8 == 0 && (norm_mode == 0 || ldx % 8 == 0) && aligned16(dy) && aligned16(dx) &&
+                    aligned16(x) && aligned16(w) && aligned16(sin_t) && aligned16(cos_t) && aligned16(dw_partial) &&
+                    (w_dtype == OCB_BF16 || w_dtype == OCB_F32);
+  // In the full-row mode the pipelined kernel stores one whole partial row per block: only rows
+  // without a block have to be cleared. The per-head mode adds into its rows.
+  const bool all_rows_written = pipe && norm_mode == 1 && rows >= kNormBwdBlocks;
+  if (dw_partial != nullptr && norm_mode != 0 && !all_rows_written) {
     const int wcols = norm_mode == 1 ? n_heads * head_dim : head_dim;
     if (cudaMemsetAsync(dw_partial, 0, sizeof(float) * static_cast<size_t>(kNormBwdBlocks) * wcols, stream) != cudaSuccess)
       return -4;
+  }
+  if (pipe) {
+    const int pgrid = rows < kNormBwdBlocks ? rows : kNormBwdBlocks;
+    const size_t bytes = pipe_bytes(4, true, kPipeStagesBwd);
+    if (w_dtype == OCB_BF16) {
+      auto kern = norm_rope_pipe_kernel<bf16, true>;
+      if (!allow_smem(kern, bytes)) return -4;
+      kern<<<pgrid, kNormThreads, bytes, stream>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
+                                                   static_cast<const bf16*>(w), const_cast<float*>(rstd),
+                                                   static_cast<bf16*>(dx), dw_partial, sin_t, cos_t, pos_ids, rows, n_heads,
+                                                   seq_len, pos_offset, norm_mode, lddy, ldx, lddx, 0.f);
+    } else {
+      auto kern = norm_rope_pipe_kernel<float, true>;
+      if (!allow_smem(kern, bytes)) return -4;
+      kern<<<pgrid, kNormThreads, bytes, stream>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
+                                                   static_cast<const float*>(w), const_cast<float*>(rstd),
+                                                   static_cast<bf16*>(dx), dw_partial, sin_t, cos_t, pos_ids, rows, n_heads,
+                                                   seq_len, pos_offset, norm_mode, lddy, ldx, lddx, 0.f);
+    }
+    return OCB_CHECK_LAUNCH();
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
     auto kern = one_pv ? norm_rope_kernel<T, W, true, 1> : norm_rope_kernel<T, W, true, 2>;

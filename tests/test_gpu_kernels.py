@@ -160,6 +160,69 @@ def test_norm_rope(dtype, norm_mode, B, S, H, hd):
     assert _rel_err(y2, y2r) < tol
 
 
+@pytest.mark.parametrize("cols", [2048, 4096])
+@pytest.mark.parametrize("with_residual", [False, True])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_rms_norm_many_rows_per_block(cols, with_residual, wdtype):
+    """More rows than resident blocks: every block walks several rows through its copy ring (ragged last round)."""
+    from olmo_core_b200.ops.elementwise import rms_norm, rms_norm_reference
+
+    torch.manual_seed(11)
+    rows = 3001
+    wide = torch.randn(rows, cols + 64, device=DEV, dtype=torch.bfloat16)
+    x = wide[:, :cols].detach().requires_grad_(True)  # a strided view: leading dimension cols + 64
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(wdtype).requires_grad_(True)
+    res = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16, requires_grad=True) if with_residual else None
+    y = rms_norm(x, w, 1e-6, residual=res)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    rr = res.detach().float().requires_grad_(True) if with_residual else None
+    yr = rms_norm_reference(xr, wr, 1e-6, rr, cols)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=3e-2)
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    if with_residual:
+        assert _rel_err(res.grad, rr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("norm_mode", [0, 1, 2])
+@pytest.mark.parametrize("H", [32, 8])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_norm_rope_many_rows_per_block(norm_mode, H, wdtype):
+    """Rows of a fused projection output (strided), several rows per block, offsets and explicit position ids."""
+    from olmo_core_b200.ops.elementwise import norm_rope, norm_rope_reference
+
+    torch.manual_seed(12)
+    B, S, hd = 2, 1500, 128
+    fused = torch.randn(B, S, H * hd + 256, device=DEV, dtype=torch.bfloat16)
+    x = fused[..., 128:128 + H * hd].detach().requires_grad_(True)
+    wn = H * hd if norm_mode == 1 else hd
+    w = (1 + 0.1 * torch.randn(wn, device=DEV)).to(wdtype).requires_grad_(True) if norm_mode else None
+    inv = 500000.0 ** (-torch.arange(0, hd, 2, device=DEV).float() / hd)
+    fr = torch.outer(torch.arange(2048, device=DEV).float(), inv)
+    pos = torch.cat([fr, fr], -1)
+    sin, cos = pos.sin(), pos.cos()
+    for ids, offset in ((None, 5), (torch.randint(0, 2048, (B, S), device=DEV), 0)):
+        x.grad = None
+        if w is not None:
+            w.grad = None
+        y = norm_rope(x, w, sin, cos, H, 1e-6, norm_mode, ids, offset)
+        g = torch.randn_like(y)
+        y.backward(g)
+        xr = x.detach().float().requires_grad_(True)
+        wr = w.detach().float().requires_grad_(True) if norm_mode else None
+        yr = norm_rope_reference(xr, wr, sin, cos, H, 1e-6, norm_mode, ids, offset)
+        yr.backward(g.float())
+        torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=4e-2)
+        torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=4e-2)
+        assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2
+        if norm_mode:
+            assert _rel_err(w.grad, wr.grad) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_swiglu(dtype):
     from olmo_core_b200.ops.elementwise import swiglu
