@@ -154,3 +154,37 @@ def test_slurm_script_rendering(tmp_path):
 
     with pytest.raises(Exception):
         SlurmLaunchConfig(name="x", cmd=[])
+
+
+def test_every_training_recipe_builds_a_config():
+    """All named recipes assemble into an experiment config on a machine without GPUs or a scheduler."""
+    from olmo_core_b200.internal.experiment import CliContext, SubCmd
+    from olmo_core_b200.optim import LinearWithWarmup
+    from olmo_core_b200.optim.scheduler import WSD
+    from olmo_core_b200.scripts.train.recipes import RECIPES, config_builder_for
+
+    assert {"OLMo2-7B-long-context", "OLMo2-7B-anneal", "OLMo3-190M", "OLMo3-7B-anneal", "OLMo-hybrid-7B-long-context",
+            "OLMo3-7B-SFT", "OLMoE2-medium", "OLMoE2-large"} <= set(RECIPES)
+    for name, recipe in RECIPES.items():
+        ctx = CliContext(script="train.py", cmd=SubCmd.dry_run, run_name=f"test-{name}", cluster="local", overrides=[])
+        config = config_builder_for(name)(ctx)
+        tm = config.train_module
+        assert config.model.n_layers > 0 and tm.max_sequence_length == recipe.sequence_length, name
+        assert config.data_loader.global_batch_size == recipe.global_batch_sequences * recipe.sequence_length, name
+        if recipe.schedule == "decay":
+            assert isinstance(tm.scheduler, WSD), name
+        if recipe.schedule == "linear":
+            assert isinstance(tm.scheduler, LinearWithWarmup), name
+        if recipe.cp_degree:
+            assert tm.cp_config is not None and tm.cp_config.degree == recipe.cp_degree, name
+        if recipe.packed_documents:
+            assert config.dataset.label_mask_paths and tm.z_loss_multiplier is None, name
+        if recipe.hybrid:
+            assert config.model.block_pattern == ["gdn", "gdn", "gdn", "attn"], name
+    hybrid_lc = config_builder_for("OLMo-hybrid-7B-long-context")(
+        CliContext(script="train.py", cmd=SubCmd.dry_run, run_name="lc", cluster="local", overrides=[]))
+    attn = hybrid_lc.model.block["attn"]
+    assert (attn.sequence_mixer if getattr(attn, "sequence_mixer", None) is not None else attn.attention).rope is None
+    small = config_builder_for("OLMo3-190M")(
+        CliContext(script="train.py", cmd=SubCmd.dry_run, run_name="s", cluster="local", overrides=[]))
+    assert 2e9 < small.trainer.max_duration.value < 6e9  # 20 tokens per (non-embedding) parameter
