@@ -42,6 +42,98 @@ __device__ __forceinline__ void lds8(const float* p, float (&f)[8]) {
   f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
+// Eight fp32 values as four packed pairs: sm_100 executes mul / add / sub / fma on both halves of a pair in one
+// instruction, which halves the arithmetic instruction count of these kernels (they are close to issue-bound).
+struct V8 {
+  uint64_t p[4];
+};
+__device__ __forceinline__ V8 v8_from_bf16(const uint4& u) {
+  V8 r;
+  r.p[0] = bf16x2_to_f32x2(u.x); r.p[1] = bf16x2_to_f32x2(u.y);
+  r.p[2] = bf16x2_to_f32x2(u.z); r.p[3] = bf16x2_to_f32x2(u.w);
+  return r;
+}
+__device__ __forceinline__ V8 v8_from_floats(const float (&f)[8]) {
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = pack_f32x2(f[2 * k], f[2 * k + 1]);
+  return r;
+}
+__device__ __forceinline__ V8 v8_splat(float s) {
+  V8 r;
+  r.p[0] = r.p[1] = r.p[2] = r.p[3] = pack_f32x2(s, s);
+  return r;
+}
+__device__ __forceinline__ V8 v8_lds(const float* smem) {
+  float f[8];
+  lds8(smem, f);
+  return v8_from_floats(f);
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ V8 v8_mul(const V8& a, const V8& b) {
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = mul_f32x2(a.p[k], b.p[k]);
+  return r;
+}
+__device__ __forceinline__ V8 v8_mul(const V8& a, uint64_t s2) {
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = mul_f32x2(a.p[k], s2);
+  return r;
+}
+__device__ __forceinline__ V8 v8_add(const V8& a, const V8& b) {
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = add_f32x2(a.p[k], b.p[k]);
+  return r;
+}
+__device__ __forceinline__ V8 v8_sub(const V8& a, const V8& b) {
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = sub_f32x2(a.p[k], b.p[k]);
+  return r;
+}
+__device__ __forceinline__ V8 v8_fma(const V8& a, const V8& b, const V8& c) {  // a * b + c
+  V8 r;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) r.p[k] = fma_f32x2(a.p[k], b.p[k], c.p[k]);
+  return r;
+}
+__device__ __forceinline__ float v8_hsum(const V8& a) {
+  const uint64_t s = add_f32x2(add_f32x2(a.p[0], a.p[1]), add_f32x2(a.p[2], a.p[3]));
+  float lo, hi;
+  unpack_f32x2(s, lo, hi);
+  return lo + hi;
+}
+__device__ __forceinline__ uint4 v8_to_bf16(const V8& a) {
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float lo, hi;
+    unpack_f32x2(a.p[k], lo, hi);
+    w[k] = pack_bf16x2(lo, hi);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ V8 v8_round_bf16(const V8& a) { return v8_from_bf16(v8_to_bf16(a)); }
+__device__ __forceinline__ void v8_store_f32(float* dst, const V8& a) {
+  float f[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) unpack_f32x2(a.p[k], f[2 * k], f[2 * k + 1]);
+  Vec8<float>::store(dst, f);
+}
+template <typename W>
+__device__ __forceinline__ V8 v8_load_w(const W* w) {
+  float f[8];
+  Vec8<W>::load(w, f);
+  return v8_from_floats(f);
+}
+
 // Sum over the block's 8 warps through one of two alternating scratch rows: one barrier per call. A scratch row is
 // rewritten two calls later, by which time every thread has passed the barrier of the call in between.
 __device__ __forceinline__ float block_sum_alt(float v, float (*sbuf)[kNormThreads / 32], int it) {
@@ -78,17 +170,13 @@ norm_rope_pipe_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16*
   const int cols = n_heads * HD;
   const bool need_x = BWD && norm_mode != 0;
 
-  float wa[8], wb[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) wa[j] = wb[j] = 1.f;
+  V8 wa = v8_splat(1.f), wb = v8_splat(1.f);
   if (norm_mode != 0 && on) {
     const int wofs = norm_mode == 1 ? h * HD : 0;
-    Vec8<W>::load(w + wofs + o, wa);
-    Vec8<W>::load(w + wofs + HALF + o, wb);
+    wa = v8_load_w<W>(w + wofs + o);
+    wb = v8_load_w<W>(w + wofs + HALF + o);
   }
-  float dwa[8], dwb[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) dwa[j] = dwb[j] = 0.f;
+  V8 dwa = v8_splat(0.f), dwb = v8_splat(0.f);
 
   auto issue = [&](long long row, int st) {
     if (row < rows) {
@@ -129,29 +217,20 @@ norm_rope_pipe_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16*
     const int st = it % S;
     const float rs_next = saved_rstd(row + stride);
     cp_async_wait<S - 2>();  // all but the newest S-2 groups are complete: this thread's pieces of `row` have landed
-    float a[8], b[8], xa[8], xb[8];
+    V8 a = v8_splat(0.f), b = a, xa = a, xb = a;
     if (on) {
-      unpack8(data[(st * NCH + 0) * kNormThreads + t], a);
-      unpack8(data[(st * NCH + 1) * kNormThreads + t], b);
+      a = v8_from_bf16(data[(st * NCH + 0) * kNormThreads + t]);
+      b = v8_from_bf16(data[(st * NCH + 1) * kNormThreads + t]);
       if (need_x) {
-        unpack8(data[(st * NCH + 2) * kNormThreads + t], xa);
-        unpack8(data[(st * NCH + 3) * kNormThreads + t], xb);
+        xa = v8_from_bf16(data[(st * NCH + 2) * kNormThreads + t]);
+        xb = v8_from_bf16(data[(st * NCH + 3) * kNormThreads + t]);
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
-    }
-    if (!need_x) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) xa[j] = xb[j] = 0.f;
     }
     const float* cs = trig + (st * 2 + 0) * HD;
     const float* sn = trig + (st * 2 + 1) * HD;
 
     if (!BWD) {
-      float ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+      const float ss = v8_hsum(v8_fma(b, b, v8_mul(a, a)));
       float rs = 1.f;
       if (norm_mode == 2) {
         float hs = ss;
@@ -166,47 +245,29 @@ norm_rope_pipe_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16*
         if (t == 0 && rstd_io) rstd_io[row] = rs;
       }
       if (on) {
-        float c_lo[8], s_lo[8], c_hi[8], s_hi[8], oa[8], ob[8];
-        lds8(cs + o, c_lo);
-        lds8(sn + o, s_lo);
-        lds8(cs + HALF + o, c_hi);
-        lds8(sn + HALF + o, s_hi);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float ya = norm_mode != 0 ? round_bf16(a[j] * rs * wa[j]) : a[j];
-          const float yb = norm_mode != 0 ? round_bf16(b[j] * rs * wb[j]) : b[j];
-          oa[j] = ya * c_lo[j] - yb * s_lo[j];
-          ob[j] = yb * c_hi[j] + ya * s_hi[j];
+        V8 ya = a, yb = b;
+        if (norm_mode != 0) {  // (x * rstd) * w, rounded to bf16 as the unfused modules would
+          const uint64_t rs2 = pack_f32x2(rs, rs);
+          ya = v8_round_bf16(v8_mul(v8_mul(a, rs2), wa));
+          yb = v8_round_bf16(v8_mul(v8_mul(b, rs2), wb));
         }
+        const V8 oa = v8_sub(v8_mul(ya, v8_lds(cs + o)), v8_mul(yb, v8_lds(sn + o)));
+        const V8 ob = v8_fma(ya, v8_lds(sn + HALF + o), v8_mul(yb, v8_lds(cs + HALF + o)));
         __nv_bfloat16* dst = out + row * ld_out + h * HD + o;
-        *reinterpret_cast<uint4*>(dst) = pack8(oa);
-        *reinterpret_cast<uint4*>(dst + HALF) = pack8(ob);
+        *reinterpret_cast<uint4*>(dst) = v8_to_bf16(oa);
+        *reinterpret_cast<uint4*>(dst + HALF) = v8_to_bf16(ob);
       }
     } else {
       // The rotation's transpose needs sin/cos, which other threads copied: the barrier comes first here.
       const float rs = rs_bwd;
       __syncthreads();
       issue(row + (S - 1) * stride, (it + S - 1) % S);
-      float ga[8], gb[8];
-      {
-        float c_lo[8], s_lo[8], c_hi[8], s_hi[8];
-        lds8(cs + o, c_lo);
-        lds8(sn + o, s_lo);
-        lds8(cs + HALF + o, c_hi);
-        lds8(sn + HALF + o, s_hi);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ga[j] = a[j] * c_lo[j] + b[j] * s_hi[j];
-          gb[j] = b[j] * c_hi[j] - a[j] * s_lo[j];
-        }
-      }
-      float c = 0.f;
+      const V8 ga = v8_fma(b, v8_lds(sn + HALF + o), v8_mul(a, v8_lds(cs + o)));
+      const V8 gb = v8_sub(v8_mul(b, v8_lds(cs + HALF + o)), v8_mul(a, v8_lds(sn + o)));
       if (norm_mode != 0) {
-        float dot = 0.f;
-        if (on) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) dot += (ga[j] * wa[j] * xa[j] + gb[j] * wb[j] * xb[j]) * rs;
-        }
+        const V8 gwa = v8_mul(ga, wa), gwb = v8_mul(gb, wb);
+        float dot = on ? rs * v8_hsum(v8_fma(gwb, xb, v8_mul(gwa, xa))) : 0.f;
+        float c;
         if (norm_mode == 2) {
           for (int s2 = 4; s2 > 0; s2 >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s2);
           c = dot / static_cast<float>(HD);
@@ -214,25 +275,22 @@ norm_rope_pipe_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16*
           // second barrier of the row; its scratch row alternates like the forward kernel's
           c = block_sum_alt(dot, sbuf, it) / static_cast<float>(cols);
         }
-      }
-      if (on) {
-        float oa[8], ob[8];
-        if (norm_mode != 0) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float xha = xa[j] * rs, xhb = xb[j] * rs;
-            oa[j] = rs * (ga[j] * wa[j] - xha * c);
-            ob[j] = rs * (gb[j] * wb[j] - xhb * c);
-            dwa[j] += ga[j] * xha;
-            dwb[j] += gb[j] * xhb;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { oa[j] = ga[j]; ob[j] = gb[j]; }
+        if (on) {
+          const uint64_t rs2 = pack_f32x2(rs, rs);
+          const V8 c8 = v8_splat(c);
+          const V8 xha = v8_mul(xa, rs2), xhb = v8_mul(xb, rs2);
+          const V8 oa = v8_mul(v8_sub(gwa, v8_mul(xha, c8)), rs2);
+          const V8 ob = v8_mul(v8_sub(gwb, v8_mul(xhb, c8)), rs2);
+          dwa = v8_fma(ga, xha, dwa);
+          dwb = v8_fma(gb, xhb, dwb);
+          __nv_bfloat16* dst = out + row * ld_out + h * HD + o;
+          *reinterpret_cast<uint4*>(dst) = v8_to_bf16(oa);
+          *reinterpret_cast<uint4*>(dst + HALF) = v8_to_bf16(ob);
         }
+      } else if (on) {
         __nv_bfloat16* dst = out + row * ld_out + h * HD + o;
-        *reinterpret_cast<uint4*>(dst) = pack8(oa);
-        *reinterpret_cast<uint4*>(dst + HALF) = pack8(ob);
+        *reinterpret_cast<uint4*>(dst) = v8_to_bf16(ga);
+        *reinterpret_cast<uint4*>(dst + HALF) = v8_to_bf16(gb);
       }
     }
     rs_bwd = rs_next;
@@ -245,13 +303,18 @@ norm_rope_pipe_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16*
     const int wcols = norm_mode == 1 ? cols : HD;
     float* prow = dw_partial + static_cast<long long>(blockIdx.x) * wcols;
     if (norm_mode == 1) {
-      Vec8<float>::store(prow + h * HD + o, dwa);
-      Vec8<float>::store(prow + h * HD + HALF + o, dwb);
+      v8_store_f32(prow + h * HD + o, dwa);
+      v8_store_f32(prow + h * HD + HALF + o, dwb);
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(&prow[o + j], dwa[j]);
-        atomicAdd(&prow[HALF + o + j], dwb[j]);
+      for (int k = 0; k < 4; ++k) {
+        float a0, a1, b0, b1;
+        unpack_f32x2(dwa.p[k], a0, a1);
+        unpack_f32x2(dwb.p[k], b0, b1);
+        atomicAdd(&prow[o + 2 * k], a0);
+        atomicAdd(&prow[o + 2 * k + 1], a1);
+        atomicAdd(&prow[HALF + o + 2 * k], b0);
+        atomicAdd(&prow[HALF + o + 2 * k + 1], b1);
       }
     }
   }
@@ -273,13 +336,9 @@ rmsnorm_fwd_pipe_kernel(const __nv_bfloat16* __restrict__ x, const W* __restrict
   __shared__ float sbuf[2][kNormThreads / 32];
   const int t = threadIdx.x;
 
-  float wf[NV][8];
+  V8 wf[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) wf[i][j] = 1.f;
-    if (w != nullptr) Vec8<W>::load(w + (t + i * kNormThreads) * 8, wf[i]);
-  }
+  for (int i = 0; i < NV; ++i) wf[i] = w != nullptr ? v8_load_w<W>(w + (t + i * kNormThreads) * 8) : v8_splat(1.f);
 
   auto issue = [&](long long row, int st) {
     if (row < rows) {
@@ -298,30 +357,27 @@ rmsnorm_fwd_pipe_kernel(const __nv_bfloat16* __restrict__ x, const W* __restrict
   for (long long row = blockIdx.x; row < rows; row += stride, ++it) {
     const int st = it % S;
     cp_async_wait<S - 2>();
-    float f[NV][8], rf[NV][8];
-    float ss = 0.f;
+    V8 f[NV], rf[NV];
+    V8 sq = v8_splat(0.f);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      unpack8(data[(st * NCH + i) * kNormThreads + t], f[i]);
-      if (RESID) unpack8(data[(st * NCH + NV + i) * kNormThreads + t], rf[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += f[i][j] * f[i][j];
+      f[i] = v8_from_bf16(data[(st * NCH + i) * kNormThreads + t]);
+      if (RESID) rf[i] = v8_from_bf16(data[(st * NCH + NV + i) * kNormThreads + t]);
+      sq = v8_fma(f[i], f[i], sq);
     }
+    const float ss = v8_hsum(sq);
     // A thread reads only what it copied itself, so the slot of the previous row is free once every thread has
     // reached this barrier.
     const float total = block_sum_alt(ss, sbuf, it);
     issue(row + (S - 1) * stride, (it + S - 1) % S);
     const float rstd = rsqrtf(total / static_cast<float>(COLS) + eps);
     if (t == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    const uint64_t rstd2 = pack_f32x2(rstd, rstd);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      float o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[j] = f[i][j] * rstd * wf[i][j];
-        if (RESID) o[j] = rf[i][j] + round_bf16(o[j]);
-      }
-      *reinterpret_cast<uint4*>(y + row * ldy + (t + i * kNormThreads) * 8) = pack8(o);
+      V8 o = v8_mul(v8_mul(f[i], rstd2), wf[i]);
+      if (RESID) o = v8_add(rf[i], v8_round_bf16(o));
+      *reinterpret_cast<uint4*>(y + row * ldy + (t + i * kNormThreads) * 8) = v8_to_bf16(o);
     }
   }
   cp_async_wait<0>();
@@ -338,12 +394,11 @@ rmsnorm_bwd_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
   __shared__ float sbuf[2][kNormThreads / 32];
   const int t = threadIdx.x;
 
-  float wf[NV][8], dw[NV][8];
+  V8 wf[NV], dw[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { wf[i][j] = 1.f; dw[i][j] = 0.f; }
-    if (w != nullptr) Vec8<W>::load(w + (t + i * kNormThreads) * 8, wf[i]);
+    wf[i] = w != nullptr ? v8_load_w<W>(w + (t + i * kNormThreads) * 8) : v8_splat(1.f);
+    dw[i] = v8_splat(0.f);
   }
 
   auto issue = [&](long long row, int st) {
@@ -366,27 +421,25 @@ rmsnorm_bwd_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
     // the next row's statistic is requested a whole iteration before it is needed
     const float rstd_next = row + stride < rows ? rstd_in[row + stride] : 0.f;
     cp_async_wait<S - 2>();
-    float xf[NV][8], gf[NV][8];
-    float dot = 0.f;
+    V8 xf[NV], gf[NV], gw[NV];
+    V8 acc = v8_splat(0.f);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      unpack8(data[(st * NCH + i) * kNormThreads + t], xf[i]);
-      unpack8(data[(st * NCH + NV + i) * kNormThreads + t], gf[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) dot += gf[i][j] * wf[i][j] * xf[i][j] * rstd;
+      xf[i] = v8_from_bf16(data[(st * NCH + i) * kNormThreads + t]);
+      gf[i] = v8_from_bf16(data[(st * NCH + NV + i) * kNormThreads + t]);
+      gw[i] = v8_mul(gf[i], wf[i]);
+      acc = v8_fma(gw[i], xf[i], acc);
     }
-    const float c = block_sum_alt(dot, sbuf, it) / static_cast<float>(COLS);
+    const float c = block_sum_alt(rstd * v8_hsum(acc), sbuf, it) / static_cast<float>(COLS);
     issue(row + (S - 1) * stride, (it + S - 1) % S);
+    const uint64_t rstd2 = pack_f32x2(rstd, rstd);
+    const V8 c8 = v8_splat(c);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      float o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xhat = xf[i][j] * rstd;
-        o[j] = rstd * (gf[i][j] * wf[i][j] - xhat * c);
-        dw[i][j] += gf[i][j] * xhat;
-      }
-      *reinterpret_cast<uint4*>(dx + row * lddx + (t + i * kNormThreads) * 8) = pack8(o);
+      const V8 xhat = v8_mul(xf[i], rstd2);
+      const V8 o = v8_mul(v8_sub(gw[i], v8_mul(xhat, c8)), rstd2);
+      dw[i] = v8_fma(gf[i], xhat, dw[i]);
+      *reinterpret_cast<uint4*>(dx + row * lddx + (t + i * kNormThreads) * 8) = v8_to_bf16(o);
     }
     rstd = rstd_next;
   }
@@ -394,7 +447,7 @@ rmsnorm_bwd_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
   if (dw_partial != nullptr) {
     float* prow = dw_partial + static_cast<long long>(blockIdx.x) * COLS;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) Vec8<float>::store(prow + (t + i * kNormThreads) * 8, dw[i]);
+    for (int i = 0; i < NV; ++i) v8_store_f32(prow + (t + i * kNormThreads) * 8, dw[i]);
   }
 }
 
