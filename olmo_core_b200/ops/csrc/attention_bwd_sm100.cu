@@ -121,21 +121,44 @@ __device__ __forceinline__ void store_acc_row(__nv_bfloat16* dst, uint32_t tmem_
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// 1. delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]      (one warp per (token, head))
+// 1. delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]
+//    Sixteen lanes per (token, head) row with 16-byte loads; a warp takes 2 x kDeltaUnroll rows and issues all of
+//    its loads before the first sum, so that every thread has 128 bytes in flight.
 // ------------------------------------------------------------------------------------------------------------
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                  float* __restrict__ delta, long long rows, int T, int H, long long ld_o, long long ld_do) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= rows * H) return;
-  const long long token = w / H;
-  const int h = static_cast<int>(w % H);
-  const uint2 a = *reinterpret_cast<const uint2*>(o + token * ld_o + h * BD + lane * 4);
-  const uint2 g = *reinterpret_cast<const uint2*>(dout + token * ld_do + h * BD + lane * 4);
-  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
-  float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
-  s = warp_sum(s);
-  if (lane == 0) delta[(token / T * H + h) * T + token % T] = s;
+constexpr int kDeltaUnroll = 4;
+
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                  float* __restrict__ delta, long long rows, int T, int H, long long ld_o, long long ld_do) {
+  // 32-bit row arithmetic (the launcher checks that rows * H fits): 64-bit divisions would dominate the kernel
+  const int n = static_cast<int>(rows) * H;
+  const int warp = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31, half = lane >> 4, l = lane & 15;
+  uint4 a[kDeltaUnroll], g[kDeltaUnroll];
+  int w[kDeltaUnroll];
+#pragma unroll
+  for (int k = 0; k < kDeltaUnroll; ++k) {
+    w[k] = (warp * kDeltaUnroll + k) * 2 + half;
+    a[k] = g[k] = make_uint4(0u, 0u, 0u, 0u);
+    if (w[k] < n) {
+      const int token = w[k] / H, h = w[k] - token * H;
+      a[k] = *reinterpret_cast<const uint4*>(o + static_cast<long long>(token) * ld_o + h * BD + l * 8);
+      g[k] = *reinterpret_cast<const uint4*>(dout + static_cast<long long>(token) * ld_do + h * BD + l * 8);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kDeltaUnroll; ++k) {
+    const float2 a0 = unpack_bf16x2(a[k].x), a1 = unpack_bf16x2(a[k].y), a2 = unpack_bf16x2(a[k].z), a3 = unpack_bf16x2(a[k].w);
+    const float2 g0 = unpack_bf16x2(g[k].x), g1 = unpack_bf16x2(g[k].y), g2 = unpack_bf16x2(g[k].z), g3 = unpack_bf16x2(g[k].w);
+    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y + a3.x * g3.x + a3.y * g3.y;
+#pragma unroll
+    for (int sh = 8; sh > 0; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);  // stays inside the 16 lanes of a row
+    if (l == 0 && w[k] < n) {
+      const int token = w[k] / H, h = w[k] - token * H;
+      const int b = token / T, tq = token - b * T;
+      delta[(static_cast<long long>(b) * H + h) * T + tq] = s;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -800,8 +823,10 @@ static int attn_bwd_launch(const void* q, const CUtensorMap& mk, const CUtensorM
     if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM) != cudaSuccess) return -3;
     configured = true;
   }
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dout) & 15u) != 0) return -1;  // 16-byte loads
+  if (rows * H > 0x3fffffffLL) return -1;  // the delta kernel indexes (token, head) rows with 32-bit integers
   {
-    const long long warps = rows * H;
+    const long long warps = (rows * H + 2 * kDeltaUnroll - 1) / (2 * kDeltaUnroll);
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
     attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
