@@ -786,6 +786,31 @@ typedef __nv_bfloat16 bf16;
   else if (act == OCB_F32) { using T = float; __VA_ARGS__ } \
   else { return -1; }
 
+// The copy-ring RMSNorm backward (rows of 2048 / 4096 bf16 channels, 16-byte aligned operands). Returns 1 if the
+// shape is not eligible, 0 after a launch, a negative code on failure. Every block stores one whole row of `partial`.
+static int launch_rmsnorm_bwd_pipe(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                   float* partial, int rows, int cols, int group, int grid, long long lddy, long long ldx,
+                                   long long lddx, int act_dtype, int w_dtype, cudaStream_t stream) {
+  const bool pipe = norm_pipe_enabled() && act_dtype == OCB_BF16 && group == cols && (cols == 2048 || cols == 4096) &&
+                    lddy % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) &&
+                    aligned16(w) && aligned16(partial) && (w_dtype == OCB_BF16 || w_dtype == OCB_F32);
+  if (!pipe) return 1;
+  const bf16* gp = static_cast<const bf16*>(dy);
+  const bf16* xp = static_cast<const bf16*>(x);
+  bf16* dxp = static_cast<bf16*>(dx);
+#define OCB_RMS_BWD_PIPE(WT, NV)                                                                                   \
+  {                                                                                                                \
+    auto kern = rmsnorm_bwd_pipe_kernel<WT, NV>;                                                                   \
+    const size_t bytes = pipe_bytes(2 * NV, false, kPipeStagesBwd);                                                \
+    if (!allow_smem(kern, bytes)) return -4;                                                                       \
+    kern<<<grid, kNormThreads, bytes, stream>>>(gp, xp, static_cast<const WT*>(w), rstd, dxp, partial, rows, lddy, ldx, lddx); \
+  }
+  if (w_dtype == OCB_BF16) { if (cols == 2048) OCB_RMS_BWD_PIPE(bf16, 1) else OCB_RMS_BWD_PIPE(bf16, 2) }
+  else { if (cols == 2048) OCB_RMS_BWD_PIPE(float, 1) else OCB_RMS_BWD_PIPE(float, 2) }
+#undef OCB_RMS_BWD_PIPE
+  return OCB_CHECK_LAUNCH();
+}
+
 extern "C" int ocb_rmsnorm_fwd(const void* x, const void* w, const void* resid, void* y, float* rstd, int rows, int cols,
                                int group, long long ldx, long long ldy, long long ldr, float eps, int act_dtype,
                                int w_dtype, cudaStream_t stream) {
@@ -844,29 +869,19 @@ extern "C" int ocb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   const int gpb = kNormThreads / tpg;
   long long want = (n_groups + gpb - 1) / gpb;
   const int grid = static_cast<int>(want < kNormBwdBlocks ? want : kNormBwdBlocks);
-  const bool pipe = norm_pipe_enabled() && act_dtype == OCB_BF16 && group == cols && (cols == 2048 || cols == 4096) &&
-                    lddy % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) &&
-                    aligned16(w) && aligned16(dw_partial) && (w_dtype == OCB_BF16 || w_dtype == OCB_F32);
-  // The pipelined kernel stores one whole partial row per block: only rows without a block have to be cleared.
-  if (dw_partial != nullptr && !(pipe && grid == kNormBwdBlocks)) {
+  // The copy-ring kernel stores one whole partial row per block: only rows without a block have to be cleared first.
+  if (dw_partial != nullptr && grid < kNormBwdBlocks) {
     if (cudaMemsetAsync(dw_partial, 0, sizeof(float) * static_cast<size_t>(kNormBwdBlocks) * group, stream) != cudaSuccess)
       return -4;
   }
-  if (pipe) {
-    const bf16* gp = static_cast<const bf16*>(dy);
-    const bf16* xp = static_cast<const bf16*>(x);
-    bf16* dxp = static_cast<bf16*>(dx);
-#define OCB_RMS_BWD_PIPE(WT, NV)                                                                                   \
-    {                                                                                                              \
-      auto kern = rmsnorm_bwd_pipe_kernel<WT, NV>;                                                                 \
-      const size_t bytes = pipe_bytes(2 * NV, false, kPipeStagesBwd);                                             \
-      if (!allow_smem(kern, bytes)) return -4;                                                                     \
-      kern<<<grid, kNormThreads, bytes, stream>>>(gp, xp, static_cast<const WT*>(w), rstd, dxp, dw_partial, rows, lddy, ldx, lddx); \
-    }
-    if (w_dtype == OCB_BF16) { if (cols == 2048) OCB_RMS_BWD_PIPE(bf16, 1) else OCB_RMS_BWD_PIPE(bf16, 2) }
-    else { if (cols == 2048) OCB_RMS_BWD_PIPE(float, 1) else OCB_RMS_BWD_PIPE(float, 2) }
-#undef OCB_RMS_BWD_PIPE
-    return OCB_CHECK_LAUNCH();
+  {
+    const int rc = launch_rmsnorm_bwd_pipe(dy, x, w, rstd, dx, dw_partial, rows, cols, group, grid, lddy, ldx, lddx,
+                                           act_dtype, w_dtype, stream);
+    if (rc <= 0) return rc;
+  }
+  if (dw_partial != nullptr && grid == kNormBwdBlocks) {  // the register kernel adds into its rows
+    if (cudaMemsetAsync(dw_partial, 0, sizeof(float) * static_cast<size_t>(kNormBwdBlocks) * group, stream) != cudaSuccess)
+      return -4;
   }
   OCB_DISPATCH_TW(act_dtype, w_dtype, {
     if (maxv == 2)
@@ -1161,19 +1176,28 @@ extern "C" int ocb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
   if (dw != nullptr) {
     const int rc = static_partials(&partial);
     if (rc != 0) return rc;
+  }
+  // Same kernel selection as ocb_rmsnorm_bwd, so that both entry points give bit-identical dx. The copy-ring kernel
+  // overwrites the `grid` partial rows that are folded below; the register kernel adds into them.
+  int launched = launch_rmsnorm_bwd_pipe(dy, x, w, rstd, dx, partial, rows, cols, group, grid, lddy, ldx, lddx, act_dtype,
+                                         w_dtype, stream);
+  if (launched < 0) return launched;
+  if (launched == 1 && dw != nullptr) {
     // Only the `grid` rows this call accumulates into (and later folds) have to start at zero.
     if (cudaMemsetAsync(partial, 0, sizeof(float) * static_cast<size_t>(grid) * group, stream) != cudaSuccess) return -4;
   }
-  OCB_DISPATCH_TW(act_dtype, w_dtype, {
-    if (maxv == 2)
-      rmsnorm_bwd_kernel<T, W, 2><<<grid, kNormThreads, 0, stream>>>(
-          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
-          partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
-    else
-      rmsnorm_bwd_kernel<T, W, kMaxVec><<<grid, kNormThreads, 0, stream>>>(
-          static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
-          partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
-  })
+  if (launched == 1) {
+    OCB_DISPATCH_TW(act_dtype, w_dtype, {
+      if (maxv == 2)
+        rmsnorm_bwd_kernel<T, W, 2><<<grid, kNormThreads, 0, stream>>>(
+            static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+            partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+      else
+        rmsnorm_bwd_kernel<T, W, kMaxVec><<<grid, kNormThreads, 0, stream>>>(
+            static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const W*>(w), rstd, static_cast<T*>(dx),
+            partial, n_groups, gpr, group, tpg, lddy, ldx, lddx);
+    })
+  }
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (dw != nullptr) {
     const dim3 threads(32, 32);
