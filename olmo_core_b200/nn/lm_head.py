@@ -121,11 +121,19 @@ class LMHead(nn.Module):
         loss_div_factor: Optional[Union[torch.Tensor, float]] = None,
         return_logits: Optional[bool] = None,
         logits_to_keep: Union[int, torch.Tensor] = 0,
+        tp_sequence_sharded: bool = False,
     ) -> Union[torch.Tensor, LMOutputWithLoss]:
         """
         Without ``labels`` returns logits ``[B, T, V]``. With ``labels`` returns
         :class:`LMOutputWithLoss`; ``loss_div_factor`` divides the (sum- or none-reduced) losses.
+        ``tp_sequence_sharded``: ``x`` is this tensor-parallel rank's ``[B, T / tp, d]`` part of the sequence (``labels``
+        are whole); what is returned covers the whole sequence.
         """
+        if tp_sequence_sharded and self.tp_enabled:
+            return self._forward_sequence_parallel(
+                x, labels=labels, ignore_index=ignore_index, loss_reduction=loss_reduction,
+                z_loss_multiplier=z_loss_multiplier, loss_div_factor=loss_div_factor, return_logits=return_logits,
+                logits_to_keep=logits_to_keep)
         B = x.shape[0]
         h = self.norm(x) if self.norm is not None else x
         if isinstance(logits_to_keep, int):
@@ -153,7 +161,6 @@ class LMHead(nn.Module):
             and self.w_out.bias is None
             and loss_reduction in ("sum", "mean")
             and not return_logits
-            and not self.tp_enabled
         )
         if fused:
             scale = None
@@ -179,6 +186,86 @@ class LMHead(nn.Module):
                 ce_loss = ce_loss / div
                 z_loss = z_loss / div if z_loss is not None else None
             loss = ce_loss + z_loss if z_loss is not None else ce_loss
+        if return_logits is False:
+            logits = None
+        return LMOutputWithLoss(logits=logits, loss=loss, ce_loss=ce_loss.detach(),
+                                z_loss=z_loss.detach() if z_loss is not None else None)
+
+    def _forward_sequence_parallel(self, x, *, labels, ignore_index, loss_reduction, z_loss_multiplier, loss_div_factor,
+                                   return_logits, logits_to_keep):
+        """
+        Tensor parallelism: norm, projection and loss run on this rank's ``T / tp`` tokens with whole weights (what the
+        reference's sequence-parallel plan does, src/olmo_core/nn/lm_head.py:366-417); loss sums are added over the
+        group, logits and per-token losses are gathered along the sequence. The head's parameters get partial gradients.
+        """
+        from ..parallel.tensor import gather_from_sequence_parallel, local_sequence_shard, sum_partials
+
+        group = self.tp_group
+        if not (isinstance(logits_to_keep, int) and logits_to_keep == 0):
+            # "the last n positions" live on the last ranks only: evaluate on the gathered sequence (inference path;
+            # every rank repeats the work, so this form is not meant for training)
+            full = gather_from_sequence_parallel(x, group)
+            return self.forward(full, labels=labels, ignore_index=ignore_index, loss_reduction=loss_reduction,
+                                z_loss_multiplier=z_loss_multiplier, loss_div_factor=loss_div_factor,
+                                return_logits=return_logits, logits_to_keep=logits_to_keep)
+        B = x.shape[0]
+        h = self.norm(x) if self.norm is not None else x
+        if labels is None:
+            if return_logits is False:
+                raise RuntimeError("'return_logits=False' is only valid when 'labels' is provided")
+            return gather_from_sequence_parallel(self._project(h), group)
+        if loss_div_factor is not None and loss_reduction == "mean":
+            raise RuntimeError("'loss_div_factor' only makes sense with 'sum' or 'none' loss reduction")
+        div = self._effective_div_factor(loss_div_factor)
+        local_labels = local_sequence_shard(labels, group)
+        with_z = z_loss_multiplier is not None
+        logits: Optional[torch.Tensor] = None
+        if loss_reduction == "none":
+            local_logits = self._project(h)
+            ce, z = cross_entropy_loss(local_logits.reshape(-1, local_logits.shape[-1]), local_labels.reshape(-1),
+                                       ignore_index=ignore_index, reduction="none", compute_z_loss=with_z,
+                                       z_loss_multiplier=z_loss_multiplier or 1e-4)
+            ce_loss = gather_from_sequence_parallel(ce.view(B, -1), group)
+            z_loss = gather_from_sequence_parallel(z.view(B, -1), group) if z is not None else None
+            if return_logits:
+                logits = gather_from_sequence_parallel(local_logits, group)
+            if div is not None:
+                ce_loss = ce_loss / div
+                z_loss = z_loss / div if z_loss is not None else None
+        else:
+            # The scale is applied to the local sums BEFORE they are added: the fused loss forms its gradients during
+            # the forward pass, which is only right when the gradient that later arrives at its output is one.
+            scale: Optional[torch.Tensor] = None
+            if loss_reduction == "mean":
+                import torch.distributed as dist
+
+                count = (local_labels != ignore_index).sum().float()
+                dist.all_reduce(count, group=group)
+                scale = 1.0 / count.clamp(min=1.0)
+            elif div is not None:
+                scale = (1.0 / div) if torch.is_tensor(div) else torch.tensor(1.0 / div, dtype=torch.float32, device=h.device)
+            fused = (self.loss_implementation == LMLossImplementation.fused_linear and self.w_out.bias is None
+                     and not return_logits)
+            if fused:
+                total, z = fused_linear_cross_entropy_loss(
+                    h.reshape(-1, self.d_model), self.w_out.weight, local_labels.reshape(-1), ignore_index=ignore_index,
+                    reduction="sum", compute_z_loss=with_z, z_loss_multiplier=z_loss_multiplier or 1e-4, loss_scale=scale)
+                ce = total - z if z is not None else total
+            else:
+                local_logits = self._project(h)
+                ce, z = cross_entropy_loss(local_logits.reshape(-1, local_logits.shape[-1]), local_labels.reshape(-1),
+                                           ignore_index=ignore_index, reduction="sum", compute_z_loss=with_z,
+                                           z_loss_multiplier=z_loss_multiplier or 1e-4)
+                if scale is not None:
+                    ce = ce * scale
+                    z = z * scale if z is not None else None
+                if return_logits:
+                    logits = gather_from_sequence_parallel(local_logits, group)
+            parts = [ce.float().reshape(1)] + ([z.float().reshape(1)] if z is not None else [])
+            totals = sum_partials(torch.cat(parts), group)  # one exchange for both sums
+            ce_loss = totals[0]
+            z_loss = totals[1] if z is not None else None
+        loss = ce_loss + z_loss if z_loss is not None else ce_loss
         if return_logits is False:
             logits = None
         return LMOutputWithLoss(logits=logits, loss=loss, ce_loss=ce_loss.detach(),

@@ -392,15 +392,15 @@ class Transformer(nn.Module):
         if self._tp_enabled and self.embeddings is not None:
             from ...parallel.tensor import scatter_to_sequence_parallel
 
-            h = scatter_to_sequence_parallel(h, self._tp_mesh.get_group())
+            h = scatter_to_sequence_parallel(h, self._tp_mesh.get_group(),
+                                             partial_producer_grads=getattr(self, "_tp_embedding_partial", False))
         for key, block in self.blocks.items():
             h = self._run_block(block, h, {**block_kwargs, **per_block.get(int(key), {})})
         if self.lm_head is None:
             return h
         if self._tp_enabled:
-            from ...parallel.tensor import gather_from_sequence_parallel
-
-            h = gather_from_sequence_parallel(h, self._tp_mesh.get_group())
+            # the head works on this rank's sequence shard and gathers / sums only what it returns
+            head_kwargs["tp_sequence_sharded"] = True
         if labels is not None:
             head_kwargs["labels"] = labels
         return self.lm_head(h, **head_kwargs)

@@ -32,6 +32,8 @@ __all__ = [
     "shard_feed_forward_",
     "shard_block_",
     "shard_lm_head_",
+    "sum_partials",
+    "local_sequence_shard",
     "shard_model_",
 ]
 
@@ -112,6 +114,25 @@ class _ScatterFromReplicatedProducer(torch.autograd.Function):
         return _all_gather_seq(g, ctx.group), None
 
 
+class _ScatterKeepingLocalGradient(torch.autograd.Function):
+    """take the local sequence slice of a replicated tensor; backward leaves the other ranks' positions at zero, so the
+    producer's parameters receive this rank's part of their gradient only (a partial sum over the group)."""
+
+    @staticmethod
+    def forward(ctx, x, group):  # type: ignore[override]
+        ctx.group = group
+        ctx.seq = x.shape[1]
+        return _slice_seq(x, group)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        ws, rank = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        n = ctx.seq // ws
+        full = g.new_zeros((g.shape[0], ctx.seq) + tuple(g.shape[2:]))
+        full[:, rank * n:(rank + 1) * n] = g
+        return full, None
+
+
 def all_gather_sequence(x: torch.Tensor, group) -> torch.Tensor:
     """``[B, T/tp, ...] -> [B, T, ...]`` in front of a column-parallel projection."""
     return _GatherForPartialConsumer.apply(x, group)
@@ -127,9 +148,41 @@ def gather_from_sequence_parallel(x: torch.Tensor, group) -> torch.Tensor:
     return _GatherForReplicatedConsumer.apply(x, group)
 
 
-def scatter_to_sequence_parallel(x: torch.Tensor, group) -> torch.Tensor:
-    """Local sequence shard of a tensor that every rank computed identically (the embeddings)."""
+def scatter_to_sequence_parallel(x: torch.Tensor, group, partial_producer_grads: bool = False) -> torch.Tensor:
+    """
+    Local sequence shard of a tensor that every rank computed identically (the embeddings). By default the producer
+    gets the whole gradient on every rank (all-gather in backward). With ``partial_producer_grads`` it gets this rank's
+    part only: for producers whose parameters are summed over the group anyway (an embedding tied to the
+    sequence-parallel head).
+    """
+    if partial_producer_grads:
+        return _ScatterKeepingLocalGradient.apply(x, group)
     return _ScatterFromReplicatedProducer.apply(x, group)
+
+
+class _SumPartialsForReplicatedConsumer(torch.autograd.Function):
+    """Sum of per-rank partial results that every rank then uses identically (a loss summed over sequence shards): each
+    rank's partial enters the total with weight one, so the gradient passes through unchanged."""
+
+    @staticmethod
+    def forward(ctx, x, group):  # type: ignore[override]
+        y = x.clone()
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return g, None
+
+
+def sum_partials(x: torch.Tensor, group) -> torch.Tensor:
+    """Total over the group of a quantity each rank computed for its own sequence shard."""
+    return _SumPartialsForReplicatedConsumer.apply(x, group)
+
+
+def local_sequence_shard(x: torch.Tensor, group) -> torch.Tensor:
+    """This rank's ``[B, T/tp, ...]`` part of a tensor that needs no gradient (labels, masks)."""
+    return _slice_seq(x, group)
 
 
 class _AllReduceSum(torch.autograd.Function):
@@ -349,8 +402,14 @@ def shard_block_(block: nn.Module, tp_mesh) -> None:
 
 
 def shard_lm_head_(lm_head: nn.Module, tp_mesh) -> None:
-    """The head is evaluated on the gathered sequence by every rank (replicated weights, identical gradients)."""
-    lm_head.tp_group = tp_mesh.get_group()
+    """
+    Sequence-parallel head (the layout of src/olmo_core/nn/lm_head.py:366-417 with the fused loss): weights stay whole,
+    every rank evaluates norm, projection and loss on its own ``T / tp`` tokens and the loss sums are added over the
+    group. The parameters therefore see a sequence shard only: their gradients are partial sums.
+    """
+    group = tp_mesh.get_group()
+    lm_head.tp_group = group
+    _mark_partial(lm_head, group)
 
 
 def shard_model_(model: nn.Module, tp_mesh) -> None:
@@ -358,5 +417,11 @@ def shard_model_(model: nn.Module, tp_mesh) -> None:
         block.apply_tp(tp_mesh)
     if getattr(model, "lm_head", None) is not None:
         model.lm_head.apply_tp(tp_mesh)
-    if getattr(model, "embedding_norm", None) is not None:
-        pass  # evaluated before the sequence is scattered: replicated, full gradients
+        head_weight = getattr(getattr(model.lm_head, "w_out", None), "weight", None)
+        emb_weight = getattr(getattr(model, "embeddings", None), "weight", None)
+        # A tied embedding shares the head's weight, whose gradient is a partial sum over the group: the embedding's
+        # contribution has to be partial as well, or it would be counted once per rank.
+        model._tp_embedding_partial = head_weight is not None and head_weight is emb_weight
+        if model._tp_embedding_partial:
+            _mark_partial(getattr(model, "embedding_norm", None), tp_mesh.get_group())
+    # (an untied embedding and its norm are evaluated before the sequence is scattered: replicated, full gradients)
