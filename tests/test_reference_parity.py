@@ -433,3 +433,74 @@ def test_optimizers_match_the_reference(tmp_path):
         for key in want[name]:
             # a few fp32 roundings apart (the update is formed in a different order), far below one update (1e-2 to 1e-3)
             assert got[name][key] == pytest.approx(want[name][key], rel=1e-4, abs=2e-6), (name, key)
+
+
+def _run_both(tmp_path: Path, program: str, stem: str):
+    """Run ``program`` (a template with ``{package}``; writes JSON to ``sys.argv[1]``) under the reference and here."""
+    ref_out, our_out = tmp_path / f"ref_{stem}.json", tmp_path / f"our_{stem}.json"
+    script = tmp_path / f"{stem}_program.py"
+    script.write_text(program.format(package="olmo_core"))
+    _run_reference(f"import runpy, sys; sys.argv = ['x', {str(ref_out)!r}]; runpy.run_path({str(script)!r}, run_name='__main__')",
+                   tmp_path)
+    script.write_text(program.format(package="olmo_core_b200"))
+    proc = subprocess.run([sys.executable, str(script), str(our_out)], cwd=str(REPO), env=dict(os.environ, PYTHONPATH=str(REPO)),
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    return json.loads(ref_out.read_text()), json.loads(our_out.read_text())
+
+
+ROPE_PROGRAM = '''
+import json, sys, torch
+import {package}.nn.rope as R
+from {package}.nn.buffer_cache import BufferCache
+
+specs = {{
+    "default": lambda: R.RoPEConfig(name="default", theta=10000),
+    "default_full_precision": lambda: R.RoPEConfig(name="default", theta=500000, full_precision=True),
+    "abf": lambda: R.RoPEConfig(name="default", theta=10000, scaling=R.ABFRoPEScalingConfig(new_theta=500000)),
+    "position_interpolation": lambda: R.RoPEConfig(name="default", theta=10000, scaling=R.PIRoPEScalingConfig(factor=2.0)),
+    "stepwise": lambda: R.RoPEConfig(name="default", theta=500000, scaling=R.StepwiseRoPEScalingConfig()),
+    "yarn": lambda: R.RoPEConfig(name="default", theta=500000, scaling=R.YaRNRoPEScalingConfig(factor=8.0, old_context_len=64)),
+    "complex": lambda: R.RoPEConfig(name="complex", theta=10000),
+}}
+g = torch.Generator().manual_seed(0)
+q, k = torch.randn(2, 48, 4, 32, generator=g), torch.randn(2, 48, 2, 32, generator=g)
+out = {{}}
+for name, make in specs.items():
+    rope = make().build(head_size=32, cache=BufferCache())
+    qo, ko = rope(q.clone(), k.clone(), head_first=False)
+    out[name] = [qo.double().flatten().tolist(), ko.double().flatten().tolist()]
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_rotary_embeddings_match_the_reference(tmp_path):
+    want, got = _run_both(tmp_path, ROPE_PROGRAM, "rope")
+    assert set(got) == set(want)
+    for name in want:
+        for a, b in zip(got[name], want[name]):
+            assert a == pytest.approx(b, rel=1e-5, abs=1e-6), name
+
+
+INIT_PROGRAM = '''
+import json, sys, torch
+from {package}.nn.transformer import TransformerConfig
+
+out = {{}}
+for name, kw in (("olmo2_30M", dict(n_layers=2)), ("llama2_271M", dict(n_layers=2)), ("qwen3_0_6B", dict(n_layers=1)),
+                 ("gemma3_1B", dict(n_layers=2)), ("ngpt_271M", dict(n_layers=2)), ("olmo3_190M", dict(n_layers=2))):
+    torch.manual_seed(0)
+    model = getattr(TransformerConfig, name)(vocab_size=512, **kw).build(init_device="meta")
+    model.init_weights(max_seq_len=64, device=torch.device("cpu"))
+    out[name] = {{k: [float(v.double().sum()), float(v.double().abs().sum())] for k, v in model.state_dict().items()}}
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_weight_initialisation_matches_the_reference(tmp_path):
+    """Same seed, same parameters: every family draws its weights from the same streams in the same order."""
+    want, got = _run_both(tmp_path, INIT_PROGRAM, "init")
+    for name in want:
+        assert set(got[name]) == set(want[name]), name
+        for key, sums in want[name].items():
+            assert got[name][key] == pytest.approx(sums, rel=1e-6, abs=1e-6), (name, key)
