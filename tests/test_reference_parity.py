@@ -440,11 +440,12 @@ def _run_both(tmp_path: Path, program: str, stem: str):
     ref_out, our_out = tmp_path / f"ref_{stem}.json", tmp_path / f"our_{stem}.json"
     script = tmp_path / f"{stem}_program.py"
     script.write_text(program.format(package="olmo_core"))
-    _run_reference(f"import runpy, sys; sys.argv = ['x', {str(ref_out)!r}]; runpy.run_path({str(script)!r}, run_name='__main__')",
-                   tmp_path)
+    shared = tmp_path / f"{stem}_shared.pt"  # argv[2]: a file the first (reference) run may write for the second
+    _run_reference(f"import runpy, sys; sys.argv = ['x', {str(ref_out)!r}, {str(shared)!r}]; "
+                   f"runpy.run_path({str(script)!r}, run_name='__main__')", tmp_path)
     script.write_text(program.format(package="olmo_core_b200"))
-    proc = subprocess.run([sys.executable, str(script), str(our_out)], cwd=str(REPO), env=dict(os.environ, PYTHONPATH=str(REPO)),
-                          capture_output=True, text=True, timeout=900)
+    proc = subprocess.run([sys.executable, str(script), str(our_out), str(shared)], cwd=str(REPO),
+                          env=dict(os.environ, PYTHONPATH=str(REPO)), capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-3000:]
     return json.loads(ref_out.read_text()), json.loads(our_out.read_text())
 
@@ -504,3 +505,56 @@ def test_weight_initialisation_matches_the_reference(tmp_path):
         assert set(got[name]) == set(want[name]), name
         for key, sums in want[name].items():
             assert got[name][key] == pytest.approx(sums, rel=1e-6, abs=1e-6), (name, key)
+
+
+GENERATION_PROGRAM = '''
+import json, os, sys
+os.environ["TORCHDYNAMO_DISABLE"] = "1"  # the reference compiles its sampling helpers; no C++ toolchain for that on a CPU box
+import torch
+from {package}.nn.transformer import TransformerConfig
+from {package}.generate.generation_module.transformer.generation_module import TransformerGenerationModule
+from {package}.generate.generation_module.config import GenerationConfig
+
+torch.manual_seed(0)
+model = TransformerConfig.olmo2_30M(vocab_size=512, n_layers=2).build(init_device="cpu")
+model.init_weights(max_seq_len=128, device=torch.device("cpu"))
+if os.path.exists(sys.argv[2]):
+    model.load_state_dict(torch.load(sys.argv[2]))
+else:
+    torch.save(model.state_dict(), sys.argv[2])
+ids = torch.randint(2, 512, (3, 10), generator=torch.Generator().manual_seed(5))
+mask = torch.ones_like(ids, dtype=torch.bool)
+mask[1, :4] = False  # a left-padded prompt
+ids[1, :4] = 0
+out = {{}}
+# the reference's key / value cache needs a flash-attention backend; its uncached decoding is the oracle for both forms here
+for use_cache in ((False,) if "{package}" == "olmo_core" else (True, False)):
+    config = GenerationConfig(pad_token_id=0, eos_token_id=1, max_new_tokens=12, use_cache=use_cache, do_sample=False)
+    module = TransformerGenerationModule(model, config, device=torch.device("cpu"))
+    tokens, _, logprobs = module.generate_batch(ids, attention_mask=mask, return_logprobs=True, completions_only=True,
+                                                log_timing=False)
+    out[str(use_cache)] = dict(tokens=tokens.tolist(), logprobs=logprobs.double().tolist())
+    alone = ids[1:2, 4:]  # the padded row's prompt without its padding
+    tokens, _, _ = module.generate_batch(alone, attention_mask=torch.ones_like(alone, dtype=torch.bool),
+                                         completions_only=True, log_timing=False)
+    out[str(use_cache)]["unpadded_row"] = tokens[0].tolist()
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_greedy_generation_matches_the_reference(tmp_path):
+    """
+    Same weights, a batch whose middle row is a left-padded prompt. Decoding without the key / value cache gives the
+    reference's completions and log-probabilities for every row (neither implementation hides the padding from
+    attention in that form). Decoding with the cache agrees on the unpadded rows and, for the padded row, gives what
+    its prompt gives when decoded alone: the cache's left-pad offsets keep padding out of attention and positions.
+    """
+    want, got = _run_both(tmp_path, GENERATION_PROGRAM, "generation")
+    oracle = want["False"]
+    assert got["False"]["tokens"] == oracle["tokens"]
+    for a, b in zip(got["False"]["logprobs"], oracle["logprobs"]):
+        assert a == pytest.approx(b, rel=1e-3, abs=1e-4)
+    for row in (0, 2):
+        assert got["True"]["tokens"][row] == oracle["tokens"][row]
+        assert got["True"]["logprobs"][row] == pytest.approx(oracle["logprobs"][row], rel=1e-3, abs=1e-4)
+    assert got["True"]["tokens"][1] == got["True"]["unpadded_row"] == got["False"]["unpadded_row"] == oracle["unpadded_row"]
