@@ -654,17 +654,31 @@ class MoETransformer(Transformer):
         return any(getattr(b, "ep_enabled", False) for b in self.blocks.values())
 
     def compute_auxiliary_metrics(self, reset: bool = True) -> Dict[str, Tuple[torch.Tensor, Optional[object]]]:
+        """
+        Router statistics per block (``block NN/<name>``) and over all blocks under the bare name: sums for metrics that
+        are summed or averaged over ranks, the maximum for max-reduced ones
+        (src/olmo_core/nn/transformer/model.py:1114-1152). With pipeline parallelism a mean-reduced value is scaled by
+        the pipeline group size, because only one rank in that many holds the block.
+        """
+        from ...train.common import ReduceType
+
+        offset = float(getattr(self, "_pp_group_size", 1)) if self.pp_enabled else 1.0
         out: Dict[str, Tuple[torch.Tensor, Optional[object]]] = {}
-        sums: Dict[str, Tuple[torch.Tensor, Optional[object]]] = {}
         for key, block in self.blocks.items():
             if not isinstance(block, MoETransformerBlock):
                 continue
             for name, (val, reduce_type) in block.compute_metrics(reset=reset).items():
                 out[f"block {int(key):02d}/{name}"] = (val, reduce_type)
-                if "loss" in name:
-                    prev = sums.get(name)
-                    sums[name] = (val if prev is None else prev[0] + val, reduce_type)
-        out.update(sums)
+                if self.pp_enabled and reduce_type == ReduceType.mean:
+                    val = val.float() * offset
+                if name not in out:
+                    out[name] = (val, reduce_type)
+                elif reduce_type in (ReduceType.mean, ReduceType.sum):
+                    out[name] = (out[name][0] + val, reduce_type)
+                elif reduce_type == ReduceType.max:
+                    out[name] = (torch.max(out[name][0], val), reduce_type)
+                else:
+                    raise NotImplementedError(reduce_type)
         return out
 
     def reset_auxiliary_metrics(self) -> None:
