@@ -98,3 +98,4 @@ def test_moe_models_match_the_reference_on_the_gpu(tmp_path):
             got = model(ids).float().cpu()
         err = (got - r["logits"]).norm() / r["logits"].norm()
         assert err < 5e-3, f"{name}: relative logits error {err:.3e}"
+
