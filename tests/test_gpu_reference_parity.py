@@ -99,3 +99,80 @@ def test_moe_models_match_the_reference_on_the_gpu(tmp_path):
         err = (got - r["logits"]).norm() / r["logits"].norm()
         assert err < 5e-3, f"{name}: relative logits error {err:.3e}"
 
+
+DENSE_PROGRAM = '''
+import torch
+from {package}.config import DType
+from {package}.nn.transformer import TransformerBlockType, TransformerConfig
+
+def build(kind):
+    """Two bf16 layers with 128-wide heads (the head size of the attention kernels here), 512 tokens per sequence."""
+    if kind == "olmo2_like":  # norms on the branch outputs, QK-norm over the full width
+        return TransformerConfig.llama_like(d_model=512, vocab_size=512, n_layers=2, n_heads=4, qk_norm=True,
+                                            block_name=TransformerBlockType.reordered_norm, dtype=DType.bfloat16)
+    return TransformerConfig.llama_like(d_model=512, vocab_size=512, n_layers=2, n_heads=4, n_kv_heads=2,
+                                        dtype=DType.bfloat16)  # pre-norm blocks, grouped-query attention
+'''
+
+
+def test_dense_models_match_the_reference_on_the_gpu(tmp_path):
+    """bf16 dense models: the reference on its stock GPU path (cuBLAS, SDPA, eager normalisation and loss) against the
+    kernels of this package (tcgen05 GEMMs, flash attention, fused norm + rotary embedding, fused loss), same weights."""
+    out = tmp_path / "ref_dense.pt"
+    code = DENSE_PROGRAM.format(package="olmo_core") + f"""
+out = {{}}
+for kind in ("olmo2_like", "llama_like_gqa"):
+    torch.manual_seed(0)
+    model = build(kind).build(init_device="cuda")
+    model.init_weights(device=torch.device("cuda"), max_seq_len=512)
+    ids = torch.randint(0, 512, (2, 512), device="cuda")
+    labels = torch.roll(ids, -1, dims=1)
+    labels[:, -1] = -100
+    res = model(ids, labels=labels, loss_reduction="sum", z_loss_multiplier=1e-4, loss_div_factor=float((labels != -100).sum()))
+    res.loss.backward()
+    grads = {{k: p.grad.float().cpu() for k, p in model.named_parameters() if p.grad is not None}}
+    model.eval()
+    with torch.no_grad():
+        logits = model(ids)
+    out[kind] = dict(state={{k: v.detach().cpu() for k, v in model.state_dict().items()}}, ids=ids.cpu(), labels=labels.cpu(),
+                     logits=logits.float().cpu(), ce=res.ce_loss.detach().float().cpu(), z=res.z_loss.detach().float().cpu(),
+                     grads=grads)
+torch.save(out, {str(out)!r})
+"""
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(SHIMS), str(REF)]))
+    proc = subprocess.run([sys.executable, "-c", code], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+
+    scope: dict = {}
+    exec(DENSE_PROGRAM.format(package="olmo_core_b200"), scope)  # noqa: S102 - the fixed program above
+    from olmo_core_b200.ops import _lib
+
+    dev = torch.device("cuda")
+    ref = torch.load(out, weights_only=False)
+    for kind, r in ref.items():
+        model = scope["build"](kind).build(init_device="cuda")
+        model.init_weights(max_seq_len=512, device=dev)
+        assert {k: tuple(v.shape) for k, v in model.state_dict().items()} == {k: tuple(v.shape) for k, v in r["state"].items()}
+        model.load_state_dict(r["state"])
+        ids, labels = r["ids"].to(dev), r["labels"].to(dev)
+        launches = _lib.launch_count
+        res = model(ids, labels=labels, loss_reduction="sum", z_loss_multiplier=1e-4,
+                    loss_div_factor=float((labels != -100).sum()))
+        res.loss.backward()
+        assert _lib.launch_count - launches > 20, "this package's kernels did not run"
+        assert float(res.ce_loss) == pytest.approx(float(r["ce"]), rel=5e-3), kind
+        assert float(res.z_loss) == pytest.approx(float(r["z"]), rel=2e-2), kind
+        errors = {}
+        for pname, p in model.named_parameters():
+            grad = getattr(p, "main_grad", None) if p.grad is None else p.grad
+            if pname in r["grads"] and grad is not None:
+                want = r["grads"][pname]
+                errors[pname] = float((grad.float().cpu() - want).norm() / want.norm().clamp(min=1e-12))
+        assert errors, "no gradients to compare"
+        bad = {k: f"{v:.3e}" for k, v in errors.items() if v > 6e-2}
+        assert not bad, f"{kind}: relative gradient errors {bad}"
+        model.eval()
+        with torch.no_grad():
+            got = model(ids).float().cpu()
+        err = float((got - r["logits"]).norm() / r["logits"].norm())
+        assert err < 2e-2, f"{kind}: relative logits error {err:.3e}"
