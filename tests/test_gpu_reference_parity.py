@@ -176,3 +176,82 @@ torch.save(out, {str(out)!r})
             got = model(ids).float().cpu()
         err = float((got - r["logits"]).norm() / r["logits"].norm())
         assert err < 2e-2, f"{kind}: relative logits error {err:.3e}"
+
+WINDOWED_PROGRAM = '''
+import torch
+from {package}.config import DType
+from {package}.nn.attention import AttentionBackendName, SlidingWindowAttentionConfig
+from {package}.nn.transformer import TransformerConfig
+
+def build():
+    """Three bf16 layers, 128-wide heads; a 128-token window on the middle layer; the flash backend (needed for windows
+    and for packed documents in the reference)."""
+    config = TransformerConfig.llama_like(d_model=512, vocab_size=512, n_layers=3, n_heads=4, n_kv_heads=2, qk_norm=True,
+                                          dtype=DType.bfloat16)
+    mixer = config.block.sequence_mixer
+    mixer.sliding_window = SlidingWindowAttentionConfig(pattern=[-1, 128, -1], force_full_attention_on_first_layer=False,
+                                                        force_full_attention_on_last_layer=False)
+    mixer.backend = AttentionBackendName.flash_2
+    return config
+
+def batch(device):
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 512, (2, 512), generator=g).to(device)
+    labels = torch.roll(ids, -1, dims=1)
+    labels[:, -1] = -100
+    doc_lens = torch.tensor([[200, 312, 0], [64, 128, 320]], device=device)  # packed documents per sequence
+    return ids, labels, doc_lens, [312, 320]
+'''
+
+
+def test_sliding_window_and_packed_documents_match_the_reference_on_the_gpu(tmp_path):
+    """Sliding-window attention and attention confined to packed documents: the reference runs them through the
+    flash-attention library's variable-length kernels, this package through per-token visibility bounds in its own."""
+    out = tmp_path / "ref_window.pt"
+    code = WINDOWED_PROGRAM.format(package="olmo_core") + f"""
+torch.manual_seed(0)
+model = build().build(init_device="cuda")
+model.init_weights(device=torch.device("cuda"), max_seq_len=512)
+ids, labels, doc_lens, max_doc_lens = batch("cuda")
+out = dict(state={{k: v.detach().cpu() for k, v in model.state_dict().items()}})
+for name, kw in (("window", {{}}), ("window+documents", dict(doc_lens=doc_lens, max_doc_lens=max_doc_lens))):
+    model.zero_grad(set_to_none=True)
+    res = model(ids, labels=labels, loss_reduction="sum", loss_div_factor=float((labels != -100).sum()), **kw)
+    res.loss.backward()
+    out[name] = dict(ce=res.ce_loss.detach().float().cpu(),
+                     grads={{k: p.grad.float().cpu() for k, p in model.named_parameters() if p.grad is not None}})
+torch.save(out, {str(out)!r})
+"""
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(SHIMS), str(REF)]))
+    proc = subprocess.run([sys.executable, "-c", code], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=900)
+    if proc.returncode != 0 and ("No module named" in proc.stderr or "ImportError" in proc.stderr):
+        pytest.skip("the flash-attention library cannot be imported here: " + proc.stderr.strip().splitlines()[-1])
+    assert proc.returncode == 0, proc.stderr[-3000:]
+
+    scope: dict = {}
+    exec(WINDOWED_PROGRAM.format(package="olmo_core_b200"), scope)  # noqa: S102 - the fixed program above
+    dev = torch.device("cuda")
+    ref = torch.load(out, weights_only=False)
+    model = scope["build"]().build(init_device="cuda")
+    model.init_weights(max_seq_len=512, device=dev)
+    model.load_state_dict(ref["state"])
+    ids, labels, doc_lens, max_doc_lens = scope["batch"](dev)
+    losses = {}
+    for name, kw in (("window", {}), ("window+documents", dict(doc_lens=doc_lens, max_doc_lens=max_doc_lens))):
+        for p in model.parameters():
+            p.grad = None
+            if getattr(p, "main_grad", None) is not None:
+                p.main_grad.zero_()
+        res = model(ids, labels=labels, loss_reduction="sum", loss_div_factor=float((labels != -100).sum()), **kw)
+        res.loss.backward()
+        losses[name] = float(res.ce_loss)
+        assert losses[name] == pytest.approx(float(ref[name]["ce"]), rel=5e-3), name
+        errors = {}
+        for pname, p in model.named_parameters():
+            grad = getattr(p, "main_grad", None) if p.grad is None else p.grad
+            if pname in ref[name]["grads"] and grad is not None:
+                want = ref[name]["grads"][pname]
+                errors[pname] = float((grad.float().cpu() - want).norm() / want.norm().clamp(min=1e-12))
+        bad = {k: f"{v:.3e}" for k, v in errors.items() if v > 6e-2}
+        assert errors and not bad, f"{name}: relative gradient errors {bad}"
+    assert losses["window"] != losses["window+documents"]  # the document boundaries really changed what is attended
