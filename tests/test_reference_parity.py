@@ -558,3 +558,76 @@ def test_greedy_generation_matches_the_reference(tmp_path):
         assert got["True"]["tokens"][row] == oracle["tokens"][row]
         assert got["True"]["logprobs"][row] == pytest.approx(oracle["logprobs"][row], rel=1e-3, abs=1e-4)
     assert got["True"]["tokens"][1] == got["True"]["unpadded_row"] == got["False"]["unpadded_row"] == oracle["unpadded_row"]
+
+
+TRAIN_MODULE_PROGRAM = '''
+import json, os, sys
+os.environ["TORCHDYNAMO_DISABLE"] = "1"
+import torch
+from {package}.nn.transformer import TransformerConfig
+from {package}.optim import CosWithWarmup, OptimGroupOverride, SkipStepAdamWConfig
+from {package}.train.train_module import TransformerTrainModule
+
+
+class StubTrainer:
+    """What a train module asks of its trainer during a step."""
+
+    def __init__(self, global_batch_size, max_steps):
+        self.device = torch.device("cpu")
+        self.global_batch_size = global_batch_size
+        self.dp_process_group = None
+        self.global_step, self.max_steps = 0, max_steps
+        self.metrics = {{}}
+
+    def record_metric(self, name, value, reduce_type=None, namespace=None, **kwargs):
+        key = name if namespace is None else namespace + "/" + name
+        self.metrics.setdefault(key, []).append(float(value))
+
+    def record_ce_loss(self, value, reduce_type=None):
+        self.record_metric("ce", value)
+
+
+SEQ, VOCAB, STEPS = 32, 256, 5
+torch.manual_seed(0)
+model = TransformerConfig.olmo2_30M(vocab_size=VOCAB, n_layers=2).build(init_device="cpu")
+model.init_weights(max_seq_len=SEQ, device=torch.device("cpu"))
+if os.path.exists(sys.argv[2]):
+    model.load_state_dict(torch.load(sys.argv[2]))
+else:
+    torch.save(model.state_dict(), sys.argv[2])
+model.init_weights = lambda *a, **k: None  # keep these weights when the train module prepares the model
+module = TransformerTrainModule(
+    model=model,
+    optim=SkipStepAdamWConfig(lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95),
+                              group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
+    rank_microbatch_size=2 * SEQ, max_sequence_length=SEQ, scheduler=CosWithWarmup(warmup=2), max_grad_norm=0.5,
+    z_loss_multiplier=1e-4, device=torch.device("cpu"))
+trainer = StubTrainer(global_batch_size=4 * SEQ, max_steps=STEPS)
+module._attach_trainer(trainer)
+g = torch.Generator().manual_seed(9)
+for step in range(1, STEPS + 1):
+    trainer.global_step = step
+    ids = torch.randint(0, VOCAB, (4, SEQ), generator=g)  # two micro-batches of two sequences
+    module.zero_grads()
+    module.train_batch({{"input_ids": ids}})
+    module.optim_step()
+keep = ("ce", "train/CE loss", "optim/total grad norm", "optim/LR (group 0)", "optim/LR (group 1)", "train/Z loss")
+json.dump(dict(metrics={{k: v for k, v in trainer.metrics.items() if k in keep}},
+               weights={{k: [float(v.double().sum()), float(v.double().abs().sum())] for k, v in module.model.state_dict().items()}}),
+          open(sys.argv[1], "w"))
+'''
+
+
+def test_training_steps_match_the_reference(tmp_path):
+    """Five optimizer steps of the transformer train module on CPU from the same weights and batches: micro-batching,
+    loss normalisation, z-loss, gradient clipping, the learning-rate schedule, weight-decay groups and SkipStepAdamW
+    leave the same metrics and the same weights behind."""
+    want, got = _run_both(tmp_path, TRAIN_MODULE_PROGRAM, "train_module")
+    assert want["metrics"], "the reference recorded no metrics"
+    for key, values in want["metrics"].items():
+        assert key in got["metrics"], (key, sorted(got["metrics"]))
+        assert got["metrics"][key] == pytest.approx(values, rel=2e-4, abs=1e-7), key
+    for key, (total, magnitude) in want["weights"].items():
+        got_total, got_magnitude = got["weights"][key]
+        assert got_magnitude == pytest.approx(magnitude, rel=1e-5), key
+        assert abs(got_total - total) <= 1e-6 * magnitude + 1e-7, key  # the plain sum cancels: judge it by the magnitude
