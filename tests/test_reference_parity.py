@@ -631,3 +631,44 @@ def test_training_steps_match_the_reference(tmp_path):
         got_total, got_magnitude = got["weights"][key]
         assert got_magnitude == pytest.approx(magnitude, rel=1e-5), key
         assert abs(got_total - total) <= 1e-6 * magnitude + 1e-7, key  # the plain sum cancels: judge it by the magnitude
+
+
+SOURCE_MIXTURE_PROGRAM = '''
+import json, sys
+from pathlib import Path
+import numpy as np
+from {package}.data.source_mixture import SourceMixtureConfig, SourceMixtureDatasetConfig, SourceMixtureList
+
+root = Path(sys.argv[2] + ".data")
+root.mkdir(exist_ok=True)
+sizes = {{"web": [300_000, 250_000], "code": [120_000], "math": [60_000, 40_000, 30_000]}}
+paths = {{}}
+for name, counts in sizes.items():
+    paths[name] = []
+    for i, n in enumerate(counts):
+        p = root / (name + "-" + str(i) + ".npy")
+        if not p.exists():
+            np.random.default_rng(len(name) * 10 + i).integers(0, 1000, n, dtype=np.uint32).tofile(p)
+        paths[name].append(str(p))
+out = {{}}
+for label, ratios, extra in (
+    ("plain", dict(web=0.6, code=0.25, math=0.15), dict()),
+    ("repeat_small", dict(web=0.4, code=0.2, math=0.4), dict(math=dict(max_repetition_ratio=3.0))),
+    ("partial_source", dict(web=0.7, code=0.3), dict(web=dict(max_source_fraction=0.6))),
+):
+    sources = SourceMixtureList([SourceMixtureConfig(source_name=n, target_ratio=r, paths=paths[n], **extra.get(n, {{}}))
+                                 for n, r in ratios.items()])
+    config = SourceMixtureDatasetConfig(source_list=sources, requested_tokens=400_000, global_batch_size=64 * 256, seed=7,
+                                        quiet=True, render_tables=False)
+    config.validate()
+    mixture = config.build(npdtype=np.uint32, sequence_length=256)
+    out[label] = {{Path(p).name + ":" + str(i): int(t) for (p, i), t in mixture.to_index().items()}}
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_source_mixtures_match_the_reference(tmp_path):
+    """Token budgets per file of a sampled source mixture (plain ratios, a small source that is repeated, a source that
+    may only be used in part) come out as in the reference."""
+    want, got = _run_both(tmp_path, SOURCE_MIXTURE_PROGRAM, "source_mixture")
+    assert got == want
