@@ -672,3 +672,52 @@ def test_source_mixtures_match_the_reference(tmp_path):
     may only be used in part) come out as in the reference."""
     want, got = _run_both(tmp_path, SOURCE_MIXTURE_PROGRAM, "source_mixture")
     assert got == want
+
+
+HF_STATE_PROGRAM = '''
+import json, sys, torch
+from {package}.nn.hf.config import get_hf_config
+from {package}.nn.hf.convert import convert_state_from_hf, convert_state_to_hf
+from {package}.nn.transformer import TransformerConfig
+
+out = {{}}
+for name, kw in (("olmo2_30M", dict(n_layers=2)), ("olmo3_190M", dict(n_layers=4)), ("gemma3_1B", dict(n_layers=6))):
+    torch.manual_seed(0)
+    model = getattr(TransformerConfig, name)(vocab_size=512, **kw).build(init_device="cpu")
+    model.init_weights(max_seq_len=64, device=torch.device("cpu"))
+    try:
+        hf_config = get_hf_config(model)
+    except NotImplementedError as e:
+        out[name] = "not exportable: " + str(e)[:60]
+        continue
+    state = {{k: v.detach().clone() for k, v in model.state_dict().items()}}
+    hf_state = convert_state_to_hf(hf_config, state)
+    back = convert_state_from_hf(hf_config, {{k: v.clone() for k, v in hf_state.items()}}, model_type=hf_config.model_type)
+    out[name] = dict(
+        model_type=hf_config.model_type,
+        hf={{k: [list(v.shape), float(v.double().sum()), float(v.double().abs().sum())] for k, v in hf_state.items()}},
+        round_trip=sorted(k for k in state if k in back and torch.equal(back[k], state[k])),
+        config={{k: v for k, v in hf_config.to_dict().items()
+                 if k in ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
+                          "rope_theta", "rms_norm_eps", "vocab_size", "sliding_window", "layer_types", "head_dim",
+                          "tie_word_embeddings", "max_position_embeddings")}})
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_hugging_face_state_conversion_matches_the_reference(tmp_path):
+    """The Hugging Face config that is derived from a model, the converted state dict (names, shapes, values) and the way
+    back are those of the reference, for every family the reference can export."""
+    want, got = _run_both(tmp_path, HF_STATE_PROGRAM, "hf_state")
+    exportable = [name for name, value in want.items() if isinstance(value, dict)]
+    assert exportable, want
+    for name in exportable:
+        assert isinstance(got[name], dict), (name, got[name])
+        assert got[name]["model_type"] == want[name]["model_type"], name
+        assert got[name]["config"] == want[name]["config"], name
+        assert set(got[name]["hf"]) == set(want[name]["hf"]), name
+        for key, (shape, total, magnitude) in want[name]["hf"].items():
+            g_shape, g_total, g_magnitude = got[name]["hf"][key]
+            assert g_shape == shape and g_magnitude == pytest.approx(magnitude, rel=1e-6), (name, key)
+            assert abs(g_total - total) <= 1e-6 * magnitude + 1e-9, (name, key)
+        assert got[name]["round_trip"] == want[name]["round_trip"], name
