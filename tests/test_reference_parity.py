@@ -721,3 +721,45 @@ def test_hugging_face_state_conversion_matches_the_reference(tmp_path):
             assert g_shape == shape and g_magnitude == pytest.approx(magnitude, rel=1e-6), (name, key)
             assert abs(g_total - total) <= 1e-6 * magnitude + 1e-9, (name, key)
         assert got[name]["round_trip"] == want[name]["round_trip"], name
+
+
+HF_IMPORT_PROGRAM = '''
+import json, sys, torch, transformers
+from {package}.nn.hf.convert import convert_state_from_hf
+
+common = dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=64)
+configs = {{
+    "llama": transformers.LlamaConfig(**common),
+    "qwen3": transformers.Qwen3Config(head_dim=16, **common),
+    "olmo2": transformers.Olmo2Config(**common),
+    "olmo3": transformers.Olmo3Config(sliding_window=16, **common),
+    "gemma3_text": transformers.Gemma3TextConfig(head_dim=16, sliding_window=16, **common),
+}}
+out = {{}}
+for name, config in configs.items():
+    torch.manual_seed(1)
+    hf_state = transformers.AutoModelForCausalLM.from_config(config).state_dict()
+    try:
+        state = convert_state_from_hf(config, {{k: v.clone() for k, v in hf_state.items()}}, model_type=config.model_type)
+    except Exception as e:
+        out[name] = "error: " + type(e).__name__
+        continue
+    out[name] = {{k: [list(v.shape), float(v.double().sum()), float(v.double().abs().sum())] for k, v in state.items()}}
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_hugging_face_state_import_matches_the_reference(tmp_path):
+    """Hugging Face checkpoints of five architectures (random weights from one seed) convert to the same parameter names,
+    shapes and values as with the reference."""
+    want, got = _run_both(tmp_path, HF_IMPORT_PROGRAM, "hf_import")
+    converted = [name for name, value in want.items() if isinstance(value, dict)]
+    assert len(converted) >= 3, want
+    for name in converted:
+        assert isinstance(got[name], dict), (name, got[name])
+        assert set(got[name]) == set(want[name]), (name, sorted(set(got[name]) ^ set(want[name])))
+        for key, (shape, total, magnitude) in want[name].items():
+            g_shape, g_total, g_magnitude = got[name][key]
+            assert g_shape == shape and g_magnitude == pytest.approx(magnitude, rel=1e-6), (name, key)
+            assert abs(g_total - total) <= 1e-6 * magnitude + 1e-9, (name, key)
