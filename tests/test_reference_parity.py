@@ -763,3 +763,57 @@ def test_hugging_face_state_import_matches_the_reference(tmp_path):
             g_shape, g_total, g_magnitude = got[name][key]
             assert g_shape == shape and g_magnitude == pytest.approx(magnitude, rel=1e-6), (name, key)
             assert abs(g_total - total) <= 1e-6 * magnitude + 1e-9, (name, key)
+
+
+ROUTER_PROGRAM = '''
+import json, sys, torch
+from {package}.nn.moe import MoERouterConfig
+from {package}.nn.moe.router import MoERouterGatingFunction
+
+out = {{}}
+x = torch.randn(2, 24, 32, generator=torch.Generator().manual_seed(0))
+variants = {{
+    "softmax_top2": dict(top_k=2),
+    "softmax_top4_normalised": dict(top_k=4, normalize_expert_weights=1.0),
+    "sigmoid_top2": dict(top_k=2, gating_function=MoERouterGatingFunction.sigmoid),
+    "uniform_assignment": dict(top_k=2, uniform_expert_assignment=True),
+    "bias_balanced": dict(top_k=2, bias_gamma=0.01),
+}}
+for name, kw in variants.items():
+    torch.manual_seed(1)
+    router = MoERouterConfig(**kw).build(32, 8, lb_loss_weight=0.01, z_loss_weight=0.001, init_device="cpu")
+    with torch.no_grad():
+        for p in router.parameters():
+            p.copy_(torch.randn(p.shape, generator=torch.Generator().manual_seed(2)) * 0.5)
+    router.train()
+    xin = x.clone().requires_grad_(True)
+    weights, indices, counts, aux = router(xin, loss_div_factor=48.0)
+    total = weights.sum() * 0.1 + (aux if aux is not None else 0.0)
+    total.backward()
+    order = torch.argsort(indices, dim=-1)  # top-k order within a token is an implementation detail
+    out[name] = dict(indices=torch.gather(indices, -1, order).tolist(),
+                     weights=torch.gather(weights.detach(), -1, order).double().tolist(),
+                     counts=counts.tolist(), aux=None if aux is None else float(aux),
+                     dx=[float(xin.grad.double().sum()), float(xin.grad.double().abs().sum())],
+                     dw=[float(router.weight.grad.double().abs().sum())],
+                     metrics={{k: float(v[0]) for k, v in router.compute_metrics(reset=True).items()}})
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_moe_router_matches_the_reference(tmp_path):
+    """Expert choice, routing weights, token counts, the auxiliary losses with their gradients and the logged statistics
+    of the router, for five gating variants."""
+    want, got = _run_both(tmp_path, ROUTER_PROGRAM, "router")
+    for name in want:
+        w, g = want[name], got[name]
+        assert g["indices"] == w["indices"] and g["counts"] == w["counts"], name
+        assert g["aux"] == pytest.approx(w["aux"], rel=1e-5), name
+        for key in ("dx", "dw"):
+            assert g[key] == pytest.approx(w[key], rel=1e-4, abs=1e-7), (name, key)
+        for a, b in zip(g["weights"], w["weights"]):
+            for row_a, row_b in zip(a, b):
+                assert row_a == pytest.approx(row_b, rel=1e-5, abs=1e-7), name
+        assert set(g["metrics"]) == set(w["metrics"]), (name, sorted(set(g["metrics"]) ^ set(w["metrics"])))
+        for key, value in w["metrics"].items():
+            assert g["metrics"][key] == pytest.approx(value, rel=1e-5, abs=1e-8), (name, key)
