@@ -817,3 +817,43 @@ def test_moe_router_matches_the_reference(tmp_path):
         assert set(g["metrics"]) == set(w["metrics"]), (name, sorted(set(g["metrics"]) ^ set(w["metrics"])))
         for key, value in w["metrics"].items():
             assert g["metrics"][key] == pytest.approx(value, rel=1e-5, abs=1e-8), (name, key)
+
+
+BATCH_UTILS_PROGRAM = '''
+import json, sys, torch
+from {package}.data import DataCollator
+from {package}.data.utils import get_cumulative_document_lengths, get_document_lengths, get_labels, melt_batch, split_batch, truncate_batch
+
+g = torch.Generator().manual_seed(0)
+items = []
+for n in (16, 11, 16, 7):
+    ids = torch.randint(2, 50, (n,), generator=g)
+    ids[n // 2] = 1  # an end-of-document token
+    items.append(dict(input_ids=ids, label_mask=torch.rand(n, generator=g) > 0.2, doc_lens=torch.tensor([n // 2 + 1, n - n // 2 - 1]),
+                      max_doc_lens=[max(n // 2 + 1, n - n // 2 - 1)], metadata=dict(path="p", index=n)))
+batch = DataCollator(pad_token_id=0)(items)
+out = {{}}
+def dump(prefix, b):
+    for k, v in b.items():
+        out[prefix + "/" + k] = v.tolist() if torch.is_tensor(v) else (v if isinstance(v, (list, int, float, str)) else str(v))
+dump("collated", batch)
+out["labels"] = get_labels(batch).tolist()
+for i, part in enumerate(split_batch({{k: v for k, v in batch.items() if k != "metadata"}}, 2)):
+    dump("split" + str(i), part)
+full = dict(input_ids=torch.arange(64).view(2, 32), label_mask=torch.ones(2, 32, dtype=torch.bool))
+dump("melted", melt_batch(full, 8))
+dump("truncated", truncate_batch(full, 8))
+lens = get_document_lengths(torch.tensor([5, 1, 7, 8, 1, 9, 9, 9]), eos_token_id=1)
+out["doc_lens"] = lens.tolist()
+out["cu_doc_lens"] = get_cumulative_document_lengths(torch.tensor([[3, 5, 0], [4, 4, 0]])).tolist()
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_batch_utilities_match_the_reference(tmp_path):
+    """Collation with left/right padding, document lengths and masks; label shifting; splitting into micro-batches;
+    melting / truncating to a shorter sequence length; document-length helpers."""
+    want, got = _run_both(tmp_path, BATCH_UTILS_PROGRAM, "batch_utils")
+    assert set(got) == set(want), sorted(set(got) ^ set(want))
+    for key in want:
+        assert got[key] == want[key], key
