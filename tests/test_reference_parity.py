@@ -857,3 +857,66 @@ def test_batch_utilities_match_the_reference(tmp_path):
     assert set(got) == set(want), sorted(set(got) ^ set(want))
     for key in want:
         assert got[key] == want[key], key
+
+
+ATTENTION_PROGRAM = '''
+import json, sys, torch
+from {package}.nn.attention import AttentionConfig, AttentionType, GateConfig, GateGranularity
+from {package}.nn.layer_norm import LayerNormConfig, LayerNormType
+from {package}.nn.rope import RoPEConfig
+
+rms = LayerNormConfig(name=LayerNormType.rms, bias=False)
+variants = {{
+    "plain": dict(),
+    "grouped_query_bias": dict(n_kv_heads=2, bias=True),
+    "multi_query_clipped": dict(n_kv_heads=1, clip_qkv=0.4),
+    "full_width_qk_norm_rope": dict(qk_norm=rms, rope=RoPEConfig(theta=10000)),
+    "per_head_qk_norm_rope": dict(n_kv_heads=2, qk_norm=rms, use_head_qk_norm=True, rope=RoPEConfig(theta=500000)),
+    "explicit_head_dim": dict(head_dim=24, rope=RoPEConfig(theta=10000)),
+    "headwise_gate": dict(gate=GateConfig(granularity=GateGranularity.headwise)),
+    "elementwise_gate": dict(n_kv_heads=2, gate=GateConfig(granularity=GateGranularity.elementwise)),
+    "fused_qkv": dict(name=AttentionType.fused),
+}}
+out = {{}}
+x = torch.randn(2, 20, 64, generator=torch.Generator().manual_seed(0))
+for name, kw in variants.items():
+    try:
+        module = AttentionConfig(n_heads=4, **kw).build(64, layer_idx=0, n_layers=2, init_device="cpu")
+    except Exception as e:
+        out[name] = "build error: " + type(e).__name__
+        continue
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for p in module.parameters():
+            p.copy_(torch.randn(p.shape, generator=g) * (0.2 if p.dim() > 1 else 1.0))
+    xin = x.clone().requires_grad_(True)
+    try:
+        y = module(xin)
+    except Exception as e:
+        out[name] = "forward error: " + type(e).__name__
+        continue
+    (y * torch.linspace(-1, 1, y.numel()).view_as(y)).sum().backward()
+    out[name] = dict(params=sorted(k for k, _ in module.named_parameters()), y=y.detach().double().flatten().tolist(),
+                     dx=xin.grad.double().flatten().tolist(),
+                     dparams={{k: float(p.grad.double().abs().sum()) for k, p in module.named_parameters()}})
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_attention_module_variants_match_the_reference(tmp_path):
+    """The attention module on CPU for nine option sets (grouped / multi-query, biases, clipping, both QK-norm forms with
+    rotary embeddings, explicit head size, both output gates, fused projection): parameter names, outputs, input and
+    parameter gradients."""
+    want, got = _run_both(tmp_path, ATTENTION_PROGRAM, "attention")
+    ran = [name for name, value in want.items() if isinstance(value, dict)]
+    assert len(ran) >= 6, want
+    for name in ran:
+        g, w = got[name], want[name]
+        assert isinstance(g, dict), (name, g)
+        assert g["params"] == w["params"], name
+        assert g["y"] == pytest.approx(w["y"], rel=1e-4, abs=1e-5), name
+        assert g["dx"] == pytest.approx(w["dx"], rel=1e-4, abs=1e-5), name
+        for key, value in w["dparams"].items():
+            # (the key bias has a zero gradient in exact arithmetic: softmax ignores a shift of all scores of a query;
+            # what is left there is rounding noise, hence the absolute tolerance)
+            assert g["dparams"][key] == pytest.approx(value, rel=1e-4, abs=5e-4), (name, key)
