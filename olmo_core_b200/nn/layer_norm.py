@@ -52,12 +52,12 @@ class LayerNormConfig(ModuleConfig):
     dtype: Optional[DType] = None
 
     def num_params(self, size: int) -> int:
+        # every kind but the L2 norm has a weight and, unless switched off, a bias
+        # (src/olmo_core/nn/layer_norm.py:73-91: the RMS kinds inherit the layer norm's ``bias=True`` default)
         affine = self.elementwise_affine if self.elementwise_affine is not None else self.name != LayerNormType.l2_norm
         if not affine:
             return 0
-        has_bias = self.bias if self.bias is not None else self.name == LayerNormType.default
-        if self.name != LayerNormType.default:
-            has_bias = bool(self.bias) if self.bias is not None else False
+        has_bias = self.bias if self.bias is not None else self.name != LayerNormType.l2_norm
         return size * (2 if has_bias else 1)
 
     def build(self, size: int, init_device: str = "cpu") -> "LayerNorm":
@@ -136,7 +136,8 @@ class LayerNorm(nn.Module):
 
 
 class RMSNorm(LayerNorm):
-    """``x * rsqrt(mean(x^2) + eps) * weight`` with fp32 math; output in the input dtype."""
+    """``x * rsqrt(mean(x^2) + eps) * weight (+ bias)`` with fp32 math; output in the input dtype. As in the reference the
+    bias exists unless ``bias=False`` is given (every model factory gives it)."""
 
     def __init__(
         self,
@@ -144,7 +145,7 @@ class RMSNorm(LayerNorm):
         size: int,
         eps: float = 1e-5,
         elementwise_affine: bool = True,
-        bias: bool = False,
+        bias: bool = True,
         full_precision: bool = True,
         dtype: torch.dtype = torch.float32,
         init_device: str = "cpu",

@@ -103,12 +103,14 @@ def cross_entropy_with_z_loss(
     if not compute_z_loss:
         return loss, None
     mask = (labels_flat != ignore_index).to(lf.dtype)
-    zsq = torch.logsumexp(lf, dim=-1).pow(2) * mask
+    zsq = torch.logsumexp(lf, dim=-1).pow(2)
     if reduction == "mean":
-        z = z_loss_multiplier * zsq.sum() / mask.sum().clamp(min=1)
+        z = z_loss_multiplier * (zsq * mask).sum() / mask.sum().clamp(min=1)
     elif reduction == "sum":
-        z = z_loss_multiplier * zsq.sum()
+        z = z_loss_multiplier * (zsq * mask).sum()
     else:
+        # per-token values are returned for EVERY position, ignored ones included, as the reference does
+        # (src/olmo_core/nn/functional/cross_entropy_loss.py:41-50): whoever reduces them applies the mask
         z = (z_loss_multiplier * zsq).view(labels.shape)
     return loss, z
 

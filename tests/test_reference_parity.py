@@ -920,3 +920,69 @@ def test_attention_module_variants_match_the_reference(tmp_path):
             # (the key bias has a zero gradient in exact arithmetic: softmax ignores a shift of all scores of a query;
             # what is left there is rounding noise, hence the absolute tolerance)
             assert g["dparams"][key] == pytest.approx(value, rel=1e-4, abs=5e-4), (name, key)
+
+
+BLOCKS_PROGRAM = '''
+import json, sys, torch
+from {package}.nn.feed_forward import ActivationFunction, FeedForwardConfig
+from {package}.nn.layer_norm import LayerNormConfig, LayerNormType
+from {package}.nn.lm_head import LMHeadConfig
+from {package}.nn.transformer import TransformerBlockType, TransformerConfig
+
+out = {{}}
+x = torch.randn(3, 10, 48, generator=torch.Generator().manual_seed(0))
+
+def fill(module, seed):
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for p in module.parameters():
+            p.copy_(torch.randn(p.shape, generator=g) * (0.2 if p.dim() > 1 else 0.5) + (1.0 if p.dim() == 1 else 0.0))
+
+def run(name, module, *args, **kwargs):
+    fill(module, 5)
+    xin = x.clone().requires_grad_(True)
+    y = module(xin, *args, **kwargs)
+    y = y if torch.is_tensor(y) else y.loss
+    (y.float() * torch.linspace(-1, 1, y.numel()).view_as(y)).sum().backward()
+    out[name] = dict(params=sorted(k for k, _ in module.named_parameters()), y=y.detach().double().flatten().tolist(),
+                     dx=xin.grad.double().flatten().tolist())
+
+for kind in (LayerNormType.default, LayerNormType.rms, LayerNormType.qwen_rms):
+    for kw in (dict(), dict(bias=False), dict(elementwise_affine=False), dict(full_precision=False, eps=1e-3)):
+        try:
+            run("norm/" + str(kind) + "/" + json.dumps(kw, sort_keys=True), LayerNormConfig(name=kind, **kw).build(48, init_device="cpu"))
+        except Exception as e:
+            out["norm/" + str(kind) + "/" + json.dumps(kw, sort_keys=True)] = "error: " + type(e).__name__
+for act in (ActivationFunction.silu, ActivationFunction.gelu_tanh):
+    for bias in (False, True):
+        run("mlp/" + str(act) + "/" + str(bias), FeedForwardConfig(hidden_size=96, bias=bias, activation=act).build(48, init_device="cpu"))
+labels = torch.randint(0, 64, (3, 10), generator=torch.Generator().manual_seed(1))
+labels[0, :2] = -100
+for reduction, extra in (("mean", dict()), ("sum", dict(loss_div_factor=9.0, z_loss_multiplier=1e-3)), ("none", dict(z_loss_multiplier=1e-3))):
+    head = LMHeadConfig(layer_norm=LayerNormConfig(name=LayerNormType.rms), bias=True).build(d_model=48, vocab_size=64, init_device="cpu")
+    run("head/" + reduction, head, labels=labels, loss_reduction=reduction, **extra)
+ids = torch.randint(0, 64, (2, 12), generator=torch.Generator().manual_seed(2))
+for block in (TransformerBlockType.default, TransformerBlockType.default_scaled, TransformerBlockType.reordered_norm,
+              TransformerBlockType.peri_norm):
+    model = TransformerConfig.llama_like(d_model=48, vocab_size=64, n_layers=3, n_heads=4, block_name=block).build(init_device="cpu")
+    fill(model, 7)
+    model.eval()
+    with torch.no_grad():
+        out["model/" + str(block)] = dict(params=sorted(k for k, _ in model.named_parameters()),
+                                          y=model(ids).double().flatten().tolist(), dx=[])
+json.dump(out, open(sys.argv[1], "w"))
+'''
+
+
+def test_norms_mlps_heads_and_block_types_match_the_reference(tmp_path):
+    """Layer norms (three kinds, with / without affine parameters and bias, low precision), gated MLPs (two activations,
+    with bias), the LM head with its three loss reductions, and four block types in a small model."""
+    want, got = _run_both(tmp_path, BLOCKS_PROGRAM, "blocks")
+    ran = [name for name, value in want.items() if isinstance(value, dict)]
+    assert len(ran) >= 15, {k: v for k, v in want.items() if not isinstance(v, dict)}
+    for name in ran:
+        g, w = got[name], want[name]
+        assert isinstance(g, dict), (name, g)
+        assert g["params"] == w["params"], name
+        assert g["y"] == pytest.approx(w["y"], rel=2e-4, abs=2e-5), name
+        assert g["dx"] == pytest.approx(w["dx"], rel=2e-4, abs=2e-5), name
