@@ -986,3 +986,56 @@ def test_norms_mlps_heads_and_block_types_match_the_reference(tmp_path):
         assert g["params"] == w["params"], name
         assert g["y"] == pytest.approx(w["y"], rel=2e-4, abs=2e-5), name
         assert g["dx"] == pytest.approx(w["dx"], rel=2e-4, abs=2e-5), name
+
+
+CONFIG_PROGRAM = '''
+import json, sys
+from {package}.config import DType
+from {package}.data import TokenizerConfig
+from {package}.nn.transformer import TransformerConfig
+from {package}.optim import AdamWConfig, CosWithWarmup, OptimGroupOverride
+from {package}.train import Duration
+from {package}.train.train_module import TransformerDataParallelConfig, TransformerTrainModuleConfig
+
+out = {{}}
+for name in ("dolma2", "gpt_neox_olmo_dolma_v1_5", "gpt2", "llama2", "llama3") if True else ():
+    make = getattr(TokenizerConfig, name, None)
+    if make is None:
+        continue
+    tok = make()
+    out["tokenizer/" + name] = dict(tok.as_dict(), padded=tok.padded_vocab_size())
+
+def strip(d):
+    """Class names differ by package name only."""
+    if isinstance(d, dict):
+        return {{k: (v.replace("{package}", "PKG") if k == "_CLASS_" else strip(v)) for k, v in d.items()}}
+    if isinstance(d, list):
+        return [strip(v) for v in d]
+    return d
+
+model = TransformerConfig.olmo2_30M(vocab_size=512, n_layers=2)
+out["model/as_config_dict"] = strip(model.as_config_dict())
+merged = model.merge(["n_layers=5", "block.feed_forward.hidden_size=96", "lm_head.bias=true"])
+out["model/merged"] = [merged.n_layers, merged.block.feed_forward.hidden_size, merged.lm_head.bias, model.n_layers]
+out["model/round_trip_equal"] = TransformerConfig.from_dict(model.as_config_dict()) == model
+out["model/counts"] = [model.num_params, model.num_non_embedding_params, model.num_active_params]
+tm = TransformerTrainModuleConfig(
+    rank_microbatch_size=1024, max_sequence_length=128, z_loss_multiplier=1e-5, max_grad_norm=1.0,
+    optim=AdamWConfig(lr=1e-3, group_overrides=[OptimGroupOverride(params=["embeddings.weight"], opts=dict(weight_decay=0.0))]),
+    scheduler=CosWithWarmup(warmup=10),
+    dp_config=TransformerDataParallelConfig(name="hsdp", param_dtype=DType.bfloat16, reduce_dtype=DType.float32, shard_degree=4))
+out["train_module/as_config_dict"] = strip(tm.as_config_dict())
+out["train_module/merged"] = strip(tm.merge(["optim.lr=0.5", "dp_config.shard_degree=8", "scheduler.warmup=3"]).as_config_dict())
+out["duration"] = [[d.value, str(d.unit)] for d in (Duration.steps(5), Duration.epochs(2), Duration.tokens(10**9),
+                                                  Duration.chinchilla_tokens(2.0, model_params=10**6))]
+json.dump(out, open(sys.argv[1], "w"), default=str, sort_keys=True)
+'''
+
+
+def test_config_system_and_value_types_match_the_reference(tmp_path):
+    """Tokenizer presets, the serialised form of a model config and of a train-module config, dot-list overrides, the way
+    back from a dict, parameter / FLOP counts and durations."""
+    want, got = _run_both(tmp_path, CONFIG_PROGRAM, "config")
+    assert set(got) == set(want), sorted(set(got) ^ set(want))
+    for key in want:
+        assert got[key] == want[key], key
