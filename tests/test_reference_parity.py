@@ -1039,3 +1039,57 @@ def test_config_system_and_value_types_match_the_reference(tmp_path):
     assert set(got) == set(want), sorted(set(got) ^ set(want))
     for key in want:
         assert got[key] == want[key], key
+
+
+LOADER_STATE_PROGRAM = '''
+import json, os, sys
+import numpy as np
+import {package}.data as pkg
+
+root = sys.argv[2] + ".data"
+os.makedirs(root, exist_ok=True)
+path = os.path.join(root, "tokens.npy")
+if not os.path.exists(path):
+    arr = np.random.default_rng(0).integers(2, 512, 32 * 64).astype(np.uint16)
+    arr[31::32] = 1
+    arr.tofile(path)
+work = os.path.join(root, "work-{package}")
+tok = pkg.TokenizerConfig(vocab_size=512, eos_token_id=1, pad_token_id=0)
+ds = pkg.NumpyFSLDatasetConfig(tokenizer=tok, paths=[path], sequence_length=32, work_dir=work).build()
+ds.prepare()
+
+def loader(batch=8 * 32):
+    return pkg.NumpyFSLDataLoader(ds, collator=pkg.DataCollator(pad_token_id=0), global_batch_size=batch, work_dir=work, seed=3,
+                                  dp_world_size=1, dp_rank=0, fs_local_rank=0)
+
+first = loader()
+first.reshuffle(epoch=1)
+it = iter(first)
+seen = [next(it)["input_ids"].tolist() for _ in range(3)]
+state = first.state_dict()
+rest = [b["input_ids"].tolist() for b in it]
+first.reset()
+resumed = loader()
+resumed.load_state_dict(state)
+resumed.reshuffle(epoch=1)
+resumed_rest = [b["input_ids"].tolist() for b in resumed]
+resumed.reset()
+half = loader(batch=4 * 32)  # the batch size halves across the restart: the position in the data is kept
+half.load_state_dict(state)
+half.reshuffle(epoch=1)
+half_rest = [b["input_ids"].tolist() for b in half]
+half.reset()
+clean = {{k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(type(v).__name__)) for k, v in state.items()
+          if k != "dataset_fingerprint"}}
+json.dump(dict(state=clean, total=first.total_batches, resumed_equal=resumed_rest == rest, rest=rest, half_rest=half_rest,
+               tokens_per_batch=[len(b) * 32 for b in seen]), open(sys.argv[1], "w"), sort_keys=True)
+'''
+
+
+def test_data_loader_state_and_resumption_match_the_reference(tmp_path):
+    """The loader's state dict (keys and values), resuming in the middle of an epoch, and resuming with half the batch
+    size give the reference's state and the reference's remaining batches."""
+    want, got = _run_both(tmp_path, LOADER_STATE_PROGRAM, "loader_state")
+    assert want["resumed_equal"] is True and got["resumed_equal"] is True
+    for key in want:
+        assert got[key] == want[key], key
