@@ -365,6 +365,7 @@ class TransformerTrainModule(TrainModule):
         self.record_ce_loss(ce_batch_loss, ReduceType.mean)
         if z_batch_loss is not None:
             self.record_metric("Z loss", z_batch_loss, ReduceType.mean, namespace="train")
+            self.record_metric("Z loss unscaled", z_batch_loss / self.z_loss_multiplier, ReduceType.mean, namespace="train")
         if isinstance(self.model, MoETransformer):
             for name, (value, reduce_type) in self.model.compute_auxiliary_metrics(reset=True).items():
                 self.record_metric(name, value, reduce_type, namespace="train", merge_strategy=MetricMergeStrategy.sum)

@@ -1093,3 +1093,92 @@ def test_data_loader_state_and_resumption_match_the_reference(tmp_path):
     assert want["resumed_equal"] is True and got["resumed_equal"] is True
     for key in want:
         assert got[key] == want[key], key
+
+
+TRAINER_PROGRAM = '''
+import json, os, sys
+os.environ["TORCHDYNAMO_DISABLE"] = "1"
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Dict
+import numpy as np
+import torch
+from {package}.data import DataCollator, NumpyFSLDataLoader, NumpyFSLDatasetConfig, TokenizerConfig
+from {package}.nn.transformer import TransformerConfig
+from {package}.optim import AdamWConfig, CosWithWarmup
+from {package}.train import Duration, TrainerConfig
+from {package}.train.callbacks import Callback, CheckpointerCallback
+from {package}.train.train_module import TransformerTrainModule
+
+VOCAB, SEQ, STEPS = 512, 32, 6
+root = Path(sys.argv[2] + ".data")
+root.mkdir(exist_ok=True)
+data = root / "tokens.npy"
+if not data.exists():
+    arr = np.random.default_rng(0).integers(2, VOCAB, 64 * SEQ * 8).astype(np.uint16)
+    arr[SEQ - 1:: SEQ] = 1
+    arr.tofile(data)
+
+
+@dataclass
+class Recorder(Callback):
+    seen: Dict[int, Dict[str, float]] = field(default_factory=dict)
+
+    def log_metrics(self, step, metrics):
+        self.seen.setdefault(step, {{}}).update({{k: float(v) for k, v in metrics.items()}})
+
+
+work = root / "work-{package}"
+tok = TokenizerConfig(vocab_size=VOCAB, eos_token_id=1, pad_token_id=0)
+ds = NumpyFSLDatasetConfig(tokenizer=tok, paths=[str(data)], sequence_length=SEQ, work_dir=str(work)).build()
+ds.prepare()
+loader = NumpyFSLDataLoader(ds, collator=DataCollator(pad_token_id=0), global_batch_size=8 * SEQ, work_dir=work, seed=1,
+                            dp_world_size=1, dp_rank=0, fs_local_rank=0)
+torch.manual_seed(0)
+model = TransformerConfig.olmo2_30M(vocab_size=VOCAB, n_layers=2).build(init_device="cpu")
+model.init_weights(max_seq_len=SEQ, device=torch.device("cpu"))
+if os.path.exists(sys.argv[2]):
+    model.load_state_dict(torch.load(sys.argv[2]))
+else:
+    torch.save(model.state_dict(), sys.argv[2])
+model.init_weights = lambda *a, **k: None
+module = TransformerTrainModule(model=model, optim=AdamWConfig(lr=1e-3), rank_microbatch_size=2 * SEQ, max_sequence_length=SEQ,
+                                scheduler=CosWithWarmup(warmup=2), max_grad_norm=1.0, z_loss_multiplier=1e-5,
+                                device=torch.device("cpu"))
+rec = Recorder()
+run = root / "run-{package}"
+config = TrainerConfig(save_folder=str(run), max_duration=Duration.steps(STEPS), metrics_collect_interval=2, save_overwrite=True,
+                       device="cpu", cancel_check_interval=1,
+                       callbacks={{"rec": rec, "checkpointer": CheckpointerCallback(save_interval=3, save_async=False,
+                                                                                    pre_train_checkpoint=False)}})
+trainer = config.build(module, loader)
+trainer.fit()
+keep = ("train/CE loss", "train/Z loss", "train/PPL", "optim/total grad norm", "optim/LR (group 0)")
+files = sorted(str(p.relative_to(run)) for p in run.rglob("*") if p.is_file() and "model_and_optim" not in str(p))
+shards = sorted(p.name for p in (run / ("step" + str(STEPS)) / "model_and_optim").iterdir())
+json.dump(dict(metrics={{str(s): {{k: v for k, v in m.items() if k in keep}} for s, m in rec.seen.items()}},
+               metric_names=sorted({{k for m in rec.seen.values() for k in m if not k.startswith(("throughput", "system"))}}),
+               files=files, shards=shards, global_step=trainer.global_step, tokens=trainer.global_train_tokens_seen),
+          open(sys.argv[1], "w"), sort_keys=True)
+'''
+
+
+def test_a_short_training_run_matches_the_reference(tmp_path):
+    """
+    ``Trainer.fit`` for six steps on CPU from the same weights and data: the logged metrics (names and values per
+    step), the files a run leaves behind (checkpoint folders, trainer state, metadata) and the step / token counters.
+    No checkpoint is written before the first step: in the reference that save initialises the optimizer state through
+    ``torch.distributed.checkpoint``, which takes one optimizer step with zero gradients and a zero learning rate, so
+    that Adam's step counter (and with it the bias correction of the first updates) starts at one instead of zero.
+    Weights are untouched by it, and this package does not imitate it.
+    """
+    want, got = _run_both(tmp_path, TRAINER_PROGRAM, "trainer")
+    assert got["global_step"] == want["global_step"] and got["tokens"] == want["tokens"]
+    assert got["files"] == want["files"], (sorted(set(got["files"]) ^ set(want["files"])))
+    assert got["shards"] == want["shards"]
+    assert set(want["metric_names"]) <= set(got["metric_names"]), sorted(set(want["metric_names"]) - set(got["metric_names"]))
+    steps = lambda run: {s for s, values in run["metrics"].items() if values}  # noqa: E731  (steps with training metrics)
+    assert steps(got) == steps(want) == {str(s) for s in range(1, 7)}
+    for step, values in want["metrics"].items():
+        for key, value in values.items():
+            assert got["metrics"][step][key] == pytest.approx(value, rel=2e-4, abs=1e-7), (step, key)
