@@ -23,10 +23,8 @@ class LongDocStrategy(StrEnum):
 class NumpyDatasetDType(StrEnum):
     """Token-id storage types of ``.npy`` token files."""
 
-    uint8 = "uint8"
-    uint16 = "uint16"
-    uint32 = "uint32"
-    uint64 = "uint64"
+    uint8, uint16, uint32, uint64 = "uint8", "uint16", "uint32", "uint64"
 
     def as_np_dtype(self) -> NumpyUIntTypes:
-        return getattr(np, str(self))
+        """The numpy scalar type of the same name."""
+        return {"uint8": np.uint8, "uint16": np.uint16, "uint32": np.uint32, "uint64": np.uint64}[self.value]

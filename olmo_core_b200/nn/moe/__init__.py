@@ -3,26 +3,10 @@
 from .loss import MoELoadBalancingLossGranularity
 from .mlp import DroplessMoEMLP, MoEMLP
 from .moe import DroplessMoE, MoE, MoEBase, MoEConfig, MoEType
-from .router import (
-    MoELinearRouter,
-    MoERouter,
-    MoERouterConfig,
-    MoERouterGatingFunction,
-    MoERouterType,
-)
+from .router import MoELinearRouter, MoERouter, MoERouterConfig, MoERouterGatingFunction, MoERouterType
 
 __all__ = [
-    "MoEBase",
-    "MoE",
-    "DroplessMoE",
-    "MoEConfig",
-    "MoEType",
-    "MoEMLP",
-    "DroplessMoEMLP",
-    "MoERouter",
-    "MoELinearRouter",
-    "MoERouterConfig",
-    "MoERouterType",
-    "MoERouterGatingFunction",
-    "MoELoadBalancingLossGranularity",
+    "DroplessMoE", "DroplessMoEMLP", "MoE", "MoEBase", "MoEConfig", "MoELinearRouter",
+    "MoELoadBalancingLossGranularity", "MoEMLP", "MoERouter", "MoERouterConfig", "MoERouterGatingFunction",
+    "MoERouterType", "MoEType",
 ]

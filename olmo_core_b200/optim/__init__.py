@@ -8,57 +8,17 @@ from .lion import Lion, LionConfig, SkipStepLion, SkipStepLionConfig
 from .muon import MuonConfig, NorMuonConfig
 from .noop import NoOpConfig, NoOpOptimizer
 from .scheduler import (
-    WSD,
-    WSDS,
-    ComposableScheduler,
-    ConstantScheduler,
-    ConstantWithWarmup,
-    CosWithWarmup,
-    CosWithWarmupAndLinearDecay,
-    ExponentialScheduler,
-    HalfCosWithWarmup,
-    InvSqrtWithWarmup,
-    LinearWithWarmup,
-    PowerLR,
-    Scheduler,
-    SchedulerUnits,
-    SequentialScheduler,
+    ComposableScheduler, ConstantScheduler, ConstantWithWarmup, CosWithWarmup, CosWithWarmupAndLinearDecay,
+    ExponentialScheduler, HalfCosWithWarmup, InvSqrtWithWarmup, LinearWithWarmup, PowerLR, Scheduler,
+    SchedulerUnits, SequentialScheduler, WSD, WSDS,
 )
 from .skip_step_optimizer import SkipStepOptimizer
 
 __all__ = [
-    "OptimConfig",
-    "MatrixAwareOptimConfig",
-    "OptimGroupOverride",
-    "SkipStepOptimizer",
-    "AdamWConfig",
-    "SkipStepAdamWConfig",
-    "SkipStepAdamW",
-    "AdamConfig",
-    "LionConfig",
-    "Lion",
-    "MuonConfig",
-    "NorMuonConfig",
-    "DionConfig",
-    "SkipStepLionConfig",
-    "SkipStepLion",
-    "NoOpConfig",
-    "NoOpOptimizer",
-    "Scheduler",
-    "SchedulerUnits",
-    "ConstantScheduler",
-    "ConstantWithWarmup",
-    "CosWithWarmup",
-    "CosWithWarmupAndLinearDecay",
-    "ComposableScheduler",
-    "ExponentialScheduler",
-    "HalfCosWithWarmup",
-    "InvSqrtWithWarmup",
-    "LinearWithWarmup",
-    "SequentialScheduler",
-    "WSD",
-    "WSDS",
-    "PowerLR",
-    "LR_FIELD",
-    "INITIAL_LR_FIELD",
+    "AdamConfig", "AdamWConfig", "ComposableScheduler", "ConstantScheduler", "ConstantWithWarmup",
+    "CosWithWarmup", "CosWithWarmupAndLinearDecay", "DionConfig", "ExponentialScheduler", "HalfCosWithWarmup",
+    "INITIAL_LR_FIELD", "InvSqrtWithWarmup", "LR_FIELD", "LinearWithWarmup", "Lion", "LionConfig",
+    "MatrixAwareOptimConfig", "MuonConfig", "NoOpConfig", "NoOpOptimizer", "NorMuonConfig", "OptimConfig",
+    "OptimGroupOverride", "PowerLR", "Scheduler", "SchedulerUnits", "SequentialScheduler", "SkipStepAdamW",
+    "SkipStepAdamWConfig", "SkipStepLion", "SkipStepLionConfig", "SkipStepOptimizer", "WSD", "WSDS",
 ]

@@ -3,36 +3,18 @@
 from .config import TrainModuleConfig
 from .train_module import BasicTrainModule, EvalBatchSizeUnit, EvalBatchSpec, TrainModule
 from .transformer import (
-    TransformerActivationCheckpointingConfig,
-    TransformerActivationCheckpointingMode,
-    TransformerContextParallelConfig,
-    TransformerDataParallelConfig,
-    TransformerDataParallelWrappingStrategy,
-    TransformerExpertParallelConfig,
-    TransformerPipelineParallelConfig,
-    TransformerPipelineTrainModuleConfig,
-    TransformerPipelineTrainModule,
-    TransformerTensorParallelConfig,
-    TransformerTrainModule,
+    TransformerActivationCheckpointingConfig, TransformerActivationCheckpointingMode,
+    TransformerContextParallelConfig, TransformerDataParallelConfig, TransformerDataParallelWrappingStrategy,
+    TransformerExpertParallelConfig, TransformerPipelineParallelConfig, TransformerPipelineTrainModule,
+    TransformerPipelineTrainModuleConfig, TransformerTensorParallelConfig, TransformerTrainModule,
     TransformerTrainModuleConfig,
 )
 
 __all__ = [
-    "TrainModuleConfig",
-    "TrainModule",
-    "EvalBatchSpec",
-    "EvalBatchSizeUnit",
-    "BasicTrainModule",
-    "TransformerTrainModule",
-    "TransformerTrainModuleConfig",
-    "TransformerPipelineTrainModule",
-    "TransformerPipelineTrainModuleConfig",
-    "TransformerActivationCheckpointingConfig",
-    "TransformerActivationCheckpointingMode",
-    "TransformerDataParallelConfig",
-    "TransformerDataParallelWrappingStrategy",
-    "TransformerExpertParallelConfig",
-    "TransformerTensorParallelConfig",
-    "TransformerContextParallelConfig",
-    "TransformerPipelineParallelConfig",
+    "BasicTrainModule", "EvalBatchSizeUnit", "EvalBatchSpec", "TrainModule", "TrainModuleConfig",
+    "TransformerActivationCheckpointingConfig", "TransformerActivationCheckpointingMode",
+    "TransformerContextParallelConfig", "TransformerDataParallelConfig",
+    "TransformerDataParallelWrappingStrategy", "TransformerExpertParallelConfig",
+    "TransformerPipelineParallelConfig", "TransformerPipelineTrainModule", "TransformerPipelineTrainModuleConfig",
+    "TransformerTensorParallelConfig", "TransformerTrainModule", "TransformerTrainModuleConfig",
 ]
